@@ -1,0 +1,114 @@
+"""ctypes binding of ``libq4b200.so`` (the C ABI declared in ``include/q4b200.h``).
+
+The library is loaded on first use.  There is no fallback: if it is missing and cannot be
+built, or a call returns an error code, a ``RuntimeError`` carrying the library's own message
+is raised.
+"""
+from __future__ import annotations
+
+import ctypes
+import os
+import threading
+from ctypes import c_char_p, c_int, c_size_t, c_uint, c_void_p
+
+import torch
+
+_PKG = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_PKG, "libq4b200.so")
+
+Q4_F16, Q4_F32 = 0, 1
+GEMV_ACCUMULATE, GEMV_ACT_ORDER, GEMV_V1 = 1, 2, 4
+
+_lib = None
+_lock = threading.Lock()
+
+# name -> (restype, argtypes); mirrors include/q4b200.h one to one
+_SIGNATURES = {
+    "q4_version": (c_int, []),
+    "q4_last_error_string": (c_char_p, []),
+    "q4_recons_v2": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "q4_recons_v1": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
+    "q2_recons_v2": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
+    "q4_gemv_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "q4_gemv": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                        c_int, c_int, c_int, c_int, c_int, c_int, c_uint, c_void_p, c_size_t, c_void_p]),
+}
+
+
+def exported_symbols():
+    return sorted(_SIGNATURES)
+
+
+def lib() -> ctypes.CDLL:
+    """The loaded library (built in-tree on first use when nvcc is present)."""
+    global _lib
+    if _lib is not None:
+        return _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        if not os.path.exists(LIB_PATH):
+            from . import build as _build
+            _build.build()
+        handle = ctypes.CDLL(LIB_PATH)
+        for name, (res, args) in _SIGNATURES.items():
+            fn = getattr(handle, name)          # AttributeError here = header and library disagree
+            fn.restype, fn.argtypes = res, args
+        _lib = handle
+    return _lib
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        msg = lib().q4_last_error_string().decode("utf-8", "replace")
+        raise RuntimeError(f"q4b200 {what} failed ({code}): {msg}")
+
+
+def ptr(t) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def stream_of(t: torch.Tensor) -> int:
+    return torch.cuda.current_stream(t.device).cuda_stream
+
+
+def require_cuda(*tensors) -> torch.device:
+    """All tensors must live on one CUDA device and be contiguous; returns that device."""
+    dev = None
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise RuntimeError("q4b200: tensors must be CUDA tensors (there is no CPU path)")
+        if not t.is_contiguous():
+            raise RuntimeError("q4b200: tensors must be contiguous")
+        if dev is None:
+            dev = t.device
+        elif t.device != dev:
+            raise RuntimeError(f"q4b200: tensors on different devices ({dev} vs {t.device})")
+    return dev
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float16:
+        return Q4_F16
+    if dt == torch.float32:
+        return Q4_F32
+    raise RuntimeError(f"q4b200: unsupported dtype {dt} (float16 or float32)")
+
+
+_workspaces: dict = {}
+
+
+def workspace(device: torch.device, nbytes: int) -> torch.Tensor:
+    """Per-(device, stream) zero-initialised scratch that only ever grows.
+
+    The decode kernel keeps its arrival counters zero between launches, so the buffer is
+    cleared once, when it is (re)allocated.
+    """
+    key = (device.index, torch.cuda.current_stream(device).cuda_stream)
+    ws = _workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(nbytes, 1 << 20), dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws

@@ -1,0 +1,154 @@
+"""Dispatch layer with the names, flags and call signatures of the reference's
+``matmul_utils_4bit`` (matmul_utils_4bit.py:12-186), on the sm_100a kernels.
+
+Routing (``matmul4bit``, matmul_utils_4bit.py:146-170): ``zeros.dtype != int32`` means a v1
+layer, otherwise v2; ``prod(x.shape[:-1]) > auto_switch_thd`` goes to the large-M path,
+anything smaller to the decode kernel.  Module-level switches keep their reference names:
+
+  use_new, auto_switch, auto_switch_thd   as in the reference (threshold default 8; the decode
+                                          kernel itself accepts up to 16 rows per launch)
+  faster_mode                             'old_faster' | 'faster' | 'disable' — all three run the
+                                          same decode kernel; the value only selects whether the
+                                          groups come from ``groupsize`` or from ``g_idx``
+  act_order                               take the group of every row from ``g_idx``
+  cache_buffer / buffer_mat_dic           cache of dense fp16 buffers used by the reconstruct path
+  debug                                   print which variant ran
+"""
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from . import _lib, quant_cuda
+
+# Global Buffer
+buffer_mat_dic = {}
+use_new = True
+auto_switch = True
+auto_switch_thd = 8
+debug = False
+faster_mode = 'old_faster'  # set disable to disable it
+valid_faster_mode = ('faster', 'old_faster')
+act_order = False
+cache_buffer = True
+
+
+def get_buffer(shape_of_qweight, dtype=torch.float16, device='cuda', bits=4):
+    """Dense ``[K, N]`` scratch for the reconstruct path, cached per shape (matmul_utils_4bit.py:22-33)."""
+    target_shape = (shape_of_qweight[0] * (32 // bits), shape_of_qweight[1])
+    if not cache_buffer:
+        return torch.empty(target_shape, dtype=dtype, device=device)
+    buf = buffer_mat_dic.get(target_shape)
+    if buf is None or buf.device != torch.device(device) or buf.dtype != dtype:
+        buf = torch.empty(target_shape, dtype=dtype, device=device)
+        buffer_mat_dic[target_shape] = buf
+    return buf
+
+
+def _decode(x, qweight, scales, zeros, g_idx, groupsize, flags):
+    outshape = x.shape[:-1] + (qweight.shape[1],)
+    x2 = x.reshape(-1, x.shape[-1])
+    dtype = x2.dtype
+    xh = x2 if dtype == torch.float16 else x2.half()
+    y = torch.empty((x2.shape[0], qweight.shape[-1]), dtype=torch.float16 if dtype == torch.float16 else torch.float32,
+                    device=x.device)
+    sh = scales if scales.dtype == torch.float16 else scales.half()
+    quant_cuda.gemv(xh.contiguous(), qweight, y, sh, zeros, g_idx, groupsize, flags)
+    if y.dtype != dtype:
+        y = y.to(dtype)
+    return y.reshape(outshape)
+
+
+def _matmul4bit_v1(x, qweight, scales, zeros):
+    """Decode product on a v1 layer (matmul_utils_4bit.py:36-56): ``x @ (scales*q - zeros)``."""
+    if debug:
+        print('_matmul4bit_v1')
+    assert qweight.shape[0] * 8 == x.shape[-1]
+    sh = scales.half().reshape(-1).contiguous()
+    zh = zeros.half().reshape(-1).contiguous()
+    return _decode(x, qweight, sh, zh, None, x.shape[-1], _lib.GEMV_V1)
+
+
+def _matmul4bit_v2(x, qweight, scales, zeros, g_idx, groupsize=None):
+    """Decode product on a v2 layer (matmul_utils_4bit.py:59-95)."""
+    if debug:
+        print('_matmul4bit_v2')
+    assert qweight.shape[0] * 8 == x.shape[-1]
+    if faster_mode not in valid_faster_mode and faster_mode != 'disable':
+        raise ValueError('faster_mode should be in {}'.format(valid_faster_mode))
+    K = x.shape[-1]
+    if groupsize is None or groupsize <= 0:
+        groupsize = K // scales.shape[0]
+    # 'old_faster' derives the group from the row index (quant_cuda_kernel.cu:1023); the other
+    # reference variants read g_idx.  With sequential g_idx both agree, so only act_order (or a
+    # group size the sequential kernel cannot take) selects the per-row lookup.
+    by_index = act_order or (groupsize % 32 != 0)
+    if by_index and g_idx is None:
+        raise ValueError('act_order decode needs g_idx')
+    return _decode(x, qweight, scales, zeros, g_idx if by_index else None, groupsize,
+                   _lib.GEMV_ACT_ORDER if by_index else 0)
+
+
+def _dense_matmul(x, buffer, transpose):
+    """``x @ W`` or ``x @ W.T`` on a reconstructed dense weight (library GEMM)."""
+    return torch.matmul(x, buffer.T if transpose else buffer)
+
+
+def _check_inner(x, qweight, per_word, transpose):
+    inner = qweight.shape[1] if transpose else qweight.shape[0] * per_word
+    assert inner == x.shape[-1], f"inner dimension {x.shape[-1]} does not match the layer ({inner})"
+
+
+def _matmul4bit_v1_recons(x, qweight, scales, zeros, transpose=False):
+    """Large-M product on a v1 layer (matmul_utils_4bit.py:98-111)."""
+    if debug:
+        print('_matmul4bit_v1_recons')
+    _check_inner(x, qweight, 8, transpose)
+    buffer = get_buffer(qweight.shape, dtype=scales.dtype, device=qweight.device)
+    quant_cuda.vecquant4recons_v1(qweight, buffer, scales.reshape(-1), zeros.reshape(-1))
+    return _dense_matmul(x, buffer, transpose)
+
+
+def _matmul4bit_v2_recons(x, qweight, scales, zeros, g_idx, transpose=False):
+    """Large-M product on a v2 layer (matmul_utils_4bit.py:114-127): ``x @ W`` or, with
+    ``transpose``, ``x @ W.T`` (the backward of the layer)."""
+    if debug:
+        print('_matmul4bit_v2_recons')
+    _check_inner(x, qweight, 8, transpose)
+    buffer = get_buffer(qweight.shape, dtype=scales.dtype, device=qweight.device)
+    quant_cuda.vecquant4recons_v2(qweight, buffer, scales, zeros, g_idx)
+    return _dense_matmul(x, buffer, transpose)
+
+
+def _matmul2bit_v2_recons(x, qweight, scales, zeros, g_idx, transpose=False):
+    """Large-M product on a 2-bit v2 layer (matmul_utils_4bit.py:130-143)."""
+    if debug:
+        print('_matmul2bit_v2_recons')
+    _check_inner(x, qweight, 16, transpose)
+    buffer = get_buffer(qweight.shape, dtype=scales.dtype, device=qweight.device, bits=2)
+    quant_cuda.vecquant2recons_v2(qweight, buffer, scales, zeros, g_idx)
+    return _dense_matmul(x, buffer, transpose)
+
+
+def matmul4bit(x, qweight, scales, zeros, g_idx=None, groupsize=None):
+    """No-grad entry (matmul_utils_4bit.py:146-170): format from ``zeros.dtype``, kernel from M."""
+    rows = int(np.prod(x.shape[:-1]))
+    large = use_new and auto_switch and rows > auto_switch_thd
+    if zeros.dtype != torch.int32:            # v1: float zeros
+        if large:
+            return _matmul4bit_v1_recons(x.half(), qweight, scales.half(), zeros.half())
+        return _matmul4bit_v1(x, qweight, scales, zeros)
+    if g_idx is None:                         # v2 without g_idx: one group
+        g_idx = torch.zeros(qweight.shape[0] * 8, dtype=torch.int32, device=x.device)
+    if large:
+        return _matmul4bit_v2_recons(x.half(), qweight, scales.half(), zeros, g_idx)
+    return _matmul4bit_v2(x, qweight, scales, zeros, g_idx, groupsize)
+
+
+def v2_to_v1(scales, zeros):
+    """Float zero term ``(z + 1) * scales`` of a one-group v2 layer, i.e. its v1 form
+    (matmul_utils_4bit.py:173-186; a debugging aid in the reference)."""
+    assert zeros.shape[0] == 1
+    shifts = torch.arange(0, 32, 4, device=zeros.device, dtype=torch.int32)
+    z = ((zeros.reshape(-1, 1) >> shifts) & 0xF).reshape(-1).to(torch.float16)
+    return z * scales + scales

@@ -1,0 +1,169 @@
+"""Drop-in for the reference's ``quant_cuda`` extension module (quant_cuda.cpp:204-227).
+
+Same function names, same argument order, same in-place convention: every function returns
+``None`` and writes into a caller-allocated tensor; the ``*matmul*`` functions ADD into ``mul``
+(the reference kernels ``atomicAdd`` into a pre-zeroed buffer, quant_cuda_kernel.cu:535,974,1040).
+Unlike the reference, arguments are validated and launches go to torch's current stream.
+
+The four live decode entry points and the three reconstruct entry points run on the sm_100a
+kernels of ``libq4b200.so``.  The reference's 2/3/8-bit GEMVs and ``seq_v2`` are exported by its
+binding but never called from its Python code; they raise ``NotImplementedError`` here.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _lib
+
+__all__ = [
+    "vecquant2matmul", "vecquant3matmul", "vecquant4matmul", "vecquant8matmul",
+    "vecquant2matmul_faster", "vecquant3matmul_faster", "vecquant4matmul_faster",
+    "vecquant4matmul_old_faster", "vecquant4matmul_v1_faster", "vecquant4recons_v1",
+    "vecquant4recons_v2", "vecquant2recons_v2", "vecquant4matmul_seq_v2", "vecquant4matmul_g",
+]
+
+
+def _check_int32(t, name):
+    if t.dtype != torch.int32:
+        raise RuntimeError(f"quant_cuda: {name} must be int32, got {t.dtype}")
+
+
+def vecquant4recons_v2(mat, res, scales, zeros, g_idx) -> None:
+    """``res[K,N] = dequant(mat)``; dtype of ``res`` and ``scales`` half or float (quant_cuda.cpp:143-148)."""
+    dev = _lib.require_cuda(mat, res, scales, zeros, g_idx)
+    _check_int32(mat, "mat"); _check_int32(zeros, "zeros"); _check_int32(g_idx, "g_idx")
+    R, N = mat.shape
+    K = R * 8
+    if res.shape != (K, N) or res.dtype != scales.dtype:
+        raise RuntimeError(f"quant_cuda: res must be [{K},{N}] of {scales.dtype}")
+    G = scales.shape[0]
+    if scales.shape != (G, N) or zeros.shape != (G, N // 8) or g_idx.numel() < K:
+        raise RuntimeError("quant_cuda: scales/zeros/g_idx shapes do not match mat")
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().q4_recons_v2(mat.data_ptr(), res.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
+                                           g_idx.data_ptr(), K, N, G, _lib.dtype_code(scales.dtype),
+                                           _lib.stream_of(mat)), "recons_v2")
+
+
+def vecquant4recons_v1(mat, res, scales, zeros) -> None:
+    """v1 layers: per-column float scale and zero (quant_cuda.cpp:129-135)."""
+    dev = _lib.require_cuda(mat, res, scales, zeros)
+    _check_int32(mat, "mat")
+    R, N = mat.shape
+    K = R * 8
+    if res.shape != (K, N) or res.dtype != scales.dtype or zeros.dtype != scales.dtype:
+        raise RuntimeError(f"quant_cuda: res must be [{K},{N}] and share the dtype of scales and zeros")
+    if scales.numel() != N or zeros.numel() != N:
+        raise RuntimeError("quant_cuda: v1 scales and zeros hold one value per column")
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().q4_recons_v1(mat.data_ptr(), res.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
+                                           K, N, _lib.dtype_code(scales.dtype), _lib.stream_of(mat)), "recons_v1")
+
+
+def vecquant2recons_v2(mat, res, scales, zeros, g_idx) -> None:
+    """2-bit layers, 16 levels per word (quant_cuda.cpp:156-161)."""
+    dev = _lib.require_cuda(mat, res, scales, zeros, g_idx)
+    _check_int32(mat, "mat"); _check_int32(zeros, "zeros"); _check_int32(g_idx, "g_idx")
+    R, N = mat.shape
+    K = R * 16
+    G = scales.shape[0]
+    if res.shape != (K, N) or res.dtype != scales.dtype:
+        raise RuntimeError(f"quant_cuda: res must be [{K},{N}] of {scales.dtype}")
+    if scales.shape != (G, N) or zeros.shape != (G, N // 16) or g_idx.numel() < K:
+        raise RuntimeError("quant_cuda: scales/zeros/g_idx shapes do not match mat")
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().q2_recons_v2(mat.data_ptr(), res.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
+                                           g_idx.data_ptr(), K, N, G, _lib.dtype_code(scales.dtype),
+                                           _lib.stream_of(mat)), "recons2_v2")
+
+
+def gemv(x, qweight, y, scales, zeros, g_idx, groupsize, flags, bias=None) -> None:
+    """``y (+)= x @ W`` through ``q4_gemv`` in slabs of at most 16 rows; x, scales fp16."""
+    dev = _lib.require_cuda(x, qweight, y, scales, zeros, g_idx, bias)
+    M, K = x.shape
+    R, N = qweight.shape
+    if R * 8 != K or y.shape != (M, N):
+        raise RuntimeError(f"quant_cuda: shapes x{tuple(x.shape)} mat{tuple(qweight.shape)} mul{tuple(y.shape)} disagree")
+    if flags & _lib.GEMV_V1:
+        G = 1
+    else:
+        G = scales.shape[0]
+        if scales.shape != (G, N) or zeros.shape != (G, N // 8):
+            raise RuntimeError("quant_cuda: scales/zeros shapes do not match mat")
+    L = _lib.lib()
+    ydt = _lib.dtype_code(y.dtype)
+    with torch.cuda.device(dev):
+        st = _lib.stream_of(x)
+        for m0 in range(0, M, 16):
+            m = min(16, M - m0)
+            need = L.q4_gemv_workspace_bytes(m, K, N)
+            ws = _lib.workspace(dev, need)
+            _lib.check(L.q4_gemv(x[m0:m0 + m].data_ptr(), qweight.data_ptr(), y[m0:m0 + m].data_ptr(),
+                                 scales.data_ptr(), zeros.data_ptr(), _lib.ptr(g_idx), _lib.ptr(bias),
+                                 m, K, N, G, groupsize, ydt, flags, ws.data_ptr(), ws.numel(), st), "gemv")
+
+
+def _half(t):
+    return t if t.dtype == torch.float16 else t.half()
+
+
+def vecquant4matmul(vec, mat, mul, scales, zeros, g_idx) -> None:
+    """``mul += vec @ W`` with the group of every row taken from ``g_idx`` (quant_cuda.cpp:41-48).
+
+    The reference computes in the dtype of ``vec`` (float); here activations and scales are
+    rounded to fp16 on entry and the sum is kept in fp32.
+    """
+    _check_int32(mat, "mat"); _check_int32(zeros, "zeros"); _check_int32(g_idx, "g_idx")
+    if mul.dtype != vec.dtype:
+        raise RuntimeError("quant_cuda: vec and mul must share a dtype")
+    K = vec.shape[-1]
+    G = scales.shape[0]
+    gemv(_half(vec).contiguous(), mat, mul, _half(scales), zeros, g_idx, max(K // G, 1),
+         _lib.GEMV_ACCUMULATE | _lib.GEMV_ACT_ORDER)
+
+
+def vecquant4matmul_g(vec, mat, mul, scales, zeros, g_idx, vec_height=None) -> None:
+    """Act-order half GEMV (quant_cuda.cpp:195-202)."""
+    vecquant4matmul(vec, mat, mul, scales, zeros, g_idx)
+
+
+def vecquant4matmul_faster(vec, mat, mul, scales, zeros, g_idx, vec_height=None) -> None:
+    """Half GEMV, group from ``g_idx`` (quant_cuda.cpp:101-108); ``mul`` fp16."""
+    if vec.dtype != torch.float16 or mul.dtype != torch.float16:
+        raise RuntimeError("quant_cuda: vecquant4matmul_faster takes half vec and mul")
+    vecquant4matmul(vec, mat, mul, scales, zeros, g_idx)
+
+
+def vecquant4matmul_old_faster(vec, mat, mul, scales, zeros, groupsize, vec_height=None) -> None:
+    """Half-in / float-out GEMV with sequential groups ``k // groupsize`` (quant_cuda.cpp:116-123)."""
+    _check_int32(mat, "mat"); _check_int32(zeros, "zeros")
+    if vec.dtype != torch.float16 or mul.dtype != torch.float32:
+        raise RuntimeError("quant_cuda: vecquant4matmul_old_faster takes half vec and float mul")
+    gemv(vec.contiguous(), mat, mul, _half(scales), zeros, None, int(groupsize), _lib.GEMV_ACCUMULATE)
+
+
+def vecquant4matmul_v1_faster(vec, mat, mul, scales, zeros) -> None:
+    """v1-format half GEMV: ``mul += vec @ (scales[n]*q - zeros[n])`` (quant_cuda.cpp:168-174)."""
+    _check_int32(mat, "mat")
+    if vec.dtype != torch.float16 or mul.dtype != torch.float16:
+        raise RuntimeError("quant_cuda: vecquant4matmul_v1_faster takes half vec and mul")
+    K = vec.shape[-1]
+    gemv(vec.contiguous(), mat, mul, _half(scales).reshape(-1).contiguous(), _half(zeros).reshape(-1).contiguous(),
+         None, K, _lib.GEMV_ACCUMULATE | _lib.GEMV_V1)
+
+
+def _dead(name):
+    def f(*args, **kwargs):
+        raise NotImplementedError(
+            f"quant_cuda.{name}: exported by the reference binding but never called from its Python "
+            f"code; not provided by the sm_100a library")
+    f.__name__ = name
+    return f
+
+
+vecquant2matmul = _dead("vecquant2matmul")
+vecquant3matmul = _dead("vecquant3matmul")
+vecquant8matmul = _dead("vecquant8matmul")
+vecquant2matmul_faster = _dead("vecquant2matmul_faster")
+vecquant3matmul_faster = _dead("vecquant3matmul_faster")
+vecquant4matmul_seq_v2 = _dead("vecquant4matmul_seq_v2")

@@ -1,0 +1,316 @@
+#!/usr/bin/env python
+"""Benchmark of the int4 dequant decode product (M=1) on LLaMA-7B layer shapes.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+One "step" is one decode product ``y = x @ W`` (M=1, fp16) on every layer of a pool of
+synthetic GPTQ v2 layers (groupsize 128, no act-order): ``--copies`` distinct copies of each of
+the three LLaMA-7B shapes 4096x4096, 4096x11008, 11008x4096.  The pool is several times larger
+than L2, so every launch streams its weights from HBM.  The reported value is algorithmic
+bytes (every operand once) per second, summed over ranks; ranks are independent replicas with
+their own pool (the path has no cross-GPU exchange).
+
+``--impl reference`` times the reference's composition (reconstruct to fp16, fp32 matmul —
+matmul_utils_4bit.py:114-127) restated for the CPU in oracle/q4_oracle.py on this box's host
+cores: the reference has no CPU implementation and its CUDA extension does not build against
+the installed torch.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+import torch
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+from alpaca_lora_4bit_b200 import synth  # noqa: E402
+
+SHAPES = [(4096, 4096), (4096, 11008), (11008, 4096)]
+GROUPSIZE = 128
+METRIC = "int4_dequant_gemv_m1_gbs"
+UNIT = "GB/s"
+
+
+def load_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return float(d["hbm_gbs"]), "measured"
+    except Exception:
+        return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+         "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.rows, self.proc = index, [], None
+
+    def __enter__(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except Exception:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def __exit__(self, *a):
+        if self.proc is not None:
+            time.sleep(0.15)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=2)
+            except Exception:
+                self.proc.kill()
+
+    def summary(self):
+        sm, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            try:
+                sm.append(float(r[0])); mx = max(mx, float(r[1]))
+            except Exception:
+                continue
+            for name, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def make_pool(copies, device, seed):
+    """``copies`` x 3 layers generated on the device (same distributions as synth.make_layer)."""
+    gen = torch.Generator(device=device).manual_seed(seed)
+    pool = []
+    for _ in range(copies):
+        for K, N in SHAPES:
+            G = K // GROUPSIZE
+            qw = torch.randint(-2 ** 31, 2 ** 31 - 1, (K // 8, N), generator=gen, device=device, dtype=torch.int64).to(torch.int32)
+            zl = torch.randint(0, 15, (G, N), generator=gen, device=device, dtype=torch.int64)
+            sh = torch.arange(8, device=device, dtype=torch.int64) * 4
+            zw = (zl.reshape(G, N // 8, 8) << sh).sum(-1)
+            zw = torch.where(zw >= 2 ** 31, zw - 2 ** 32, zw).to(torch.int32)
+            sc = (torch.rand((G, N), generator=gen, device=device) * 0.018 + 0.002).half()
+            pool.append(synth.QuantLayer(qw, zw, sc, None, K, N, GROUPSIZE))
+    return pool
+
+
+def bytes_per_step(copies):
+    return copies * sum(synth.gemv_bytes(1, K, N, GROUPSIZE) for K, N in SHAPES)
+
+
+def run_ours(args, rank, world, local_rank):
+    from alpaca_lora_4bit_b200 import _lib, matmul_utils_4bit as mm4b
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    L = _lib.lib()
+    pool = make_pool(args.copies, dev, 1234 + rank)
+    gen = torch.Generator(device=dev).manual_seed(99 + rank)
+    xs = {K: torch.randn((1, K), generator=gen, device=dev).half() for K in (4096, 11008)}
+    ys = [torch.empty((1, l.N), dtype=torch.float16, device=dev) for l in pool]
+    ws = _lib.workspace(dev, max(L.q4_gemv_workspace_bytes(1, K, N) for K, N in SHAPES))
+    stream = torch.cuda.Stream(dev)
+    n_launch = len(pool)
+
+    def step():
+        st = torch.cuda.current_stream(dev).cuda_stream
+        for l, y in zip(pool, ys):
+            rc = L.q4_gemv(xs[l.K].data_ptr(), l.qweight.data_ptr(), y.data_ptr(), l.scales.data_ptr(),
+                           l.qzeros.data_ptr(), None, None, 1, l.K, l.N, l.K // GROUPSIZE, GROUPSIZE,
+                           _lib.Q4_F16, 0, ws.data_ptr(), ws.numel(), st)
+            if rc:
+                _lib.check(rc, "gemv")
+
+    def barrier():
+        if world > 1:
+            torch.distributed.barrier()
+
+    with torch.cuda.stream(stream):
+        for _ in range(max(args.warmup, 3)):
+            step()
+        stream.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            step()
+        for _ in range(max(args.warmup, 3)):
+            graph.replay()
+        stream.synchronize()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        with ClockSampler(local_rank) as clk:
+            torch.cuda.synchronize(dev)
+            e0.record(stream)
+            for _ in range(args.steps):
+                graph.replay()
+            e1.record(stream)
+            stream.synchronize()
+        torch.cuda.synchronize(dev)
+        barrier()
+        ms = e0.elapsed_time(e1)
+
+        # per-shape breakdown (same graph-free launches, one event pair per shape), rank 0 only
+        per_shape = {}
+        if rank == 0:
+            for K, N in SHAPES:
+                sel = [(l, y) for l, y in zip(pool, ys) if (l.K, l.N) == (K, N)]
+                g2 = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g2, stream=stream):
+                    st = torch.cuda.current_stream(dev).cuda_stream
+                    for l, y in sel:
+                        L.q4_gemv(xs[K].data_ptr(), l.qweight.data_ptr(), y.data_ptr(), l.scales.data_ptr(),
+                                  l.qzeros.data_ptr(), None, None, 1, K, N, K // GROUPSIZE, GROUPSIZE,
+                                  _lib.Q4_F16, 0, ws.data_ptr(), ws.numel(), st)
+                reps = 20
+                graph.replay()          # evict this shape's weights from L2 with the whole pool
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                tot = 0.0
+                for _ in range(reps):
+                    graph.replay()
+                    a.record(stream); g2.replay(); b.record(stream)
+                    stream.synchronize()
+                    tot += a.elapsed_time(b)
+                us = tot / reps / len(sel) * 1e3
+                per_shape[f"{K}x{N}"] = {"us_per_launch": round(us, 3),
+                                         "gbs": round(synth.gemv_bytes(1, K, N, GROUPSIZE) / us / 1e3, 1)}
+
+    # ---- end to end through the Python operator surface, host buffers in, host buffers out
+    for l in pool:
+        l.g_idx = (torch.arange(l.K, device=dev) // GROUPSIZE).to(torch.int32)
+    xh = {K: torch.randn((1, K)).half().pin_memory() for K in (4096, 11008)}
+    yh = [torch.empty((1, l.N), dtype=torch.float16).pin_memory() for l in pool]
+    h2d = sum(xh[l.K].numel() * 2 for l in pool)
+    d2h = sum(y.numel() * 2 for y in yh)
+
+    def e2e_step():
+        outs = []
+        for l in pool:
+            xd = xh[l.K].to(dev, non_blocking=True)
+            outs.append(mm4b.matmul4bit(xd, l.qweight, l.scales, l.qzeros, l.g_idx, GROUPSIZE))
+        for o, h in zip(outs, yh):
+            h.copy_(o, non_blocking=True)
+        torch.cuda.current_stream(dev).synchronize()
+
+    with torch.no_grad():
+        for _ in range(3):
+            e2e_step()
+        barrier()
+        torch.cuda.synchronize(dev)
+        e2e_steps = max(3, min(args.steps, 50))
+        t0 = time.perf_counter()
+        for _ in range(e2e_steps):
+            e2e_step()
+        torch.cuda.synchronize(dev)
+        e2e_ms = (time.perf_counter() - t0) * 1e3
+        barrier()
+
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms, e2e_ms = float(t[0]), float(t[1])
+    return dict(ms=ms, e2e_ms=e2e_ms, e2e_steps=e2e_steps, n_launch=n_launch, clocks=clk.summary(),
+                per_shape=per_shape, h2d=h2d, d2h=d2h)
+
+
+def cpu_reference(sample_layers=1, reps=3, threads=None):
+    """The reference composition on the host: reconstruct fp16 [K,N] + fp32 matmul, M=1."""
+    from oracle import q4_oracle as orc
+    if threads:
+        torch.set_num_threads(threads)
+    K, N = SHAPES[0]
+    layer = synth.make_layer(K, N, GROUPSIZE, False, seed=0)
+    x = synth.make_acts(1, K, seed=1)
+    orc.matmul4bit_ref(x, layer.qweight, layer.scales, layer.qzeros, layer.g_idx)      # warm-up
+    best = float("inf")
+    for _ in range(reps):
+        t0 = time.perf_counter()
+        for _ in range(sample_layers):
+            orc.matmul4bit_ref(x, layer.qweight, layer.scales, layer.qzeros, layer.g_idx)
+        best = min(best, (time.perf_counter() - t0) / sample_layers)
+    gbs = synth.gemv_bytes(1, K, N, GROUPSIZE) / best / 1e9
+    return gbs, best, torch.get_num_threads()
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--copies", type=int, default=8, help="distinct copies of each layer shape per GPU")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    config = {"workload": "C1 decode GEMV M=1, LLaMA-7B shapes 4096x4096+4096x11008+11008x4096, g128, "
+                          f"{args.copies} copies each per GPU (pool > 2x L2, no flush needed)",
+              "l2_policy": "inputs larger than L2", "launch": "cuda_graph", "parallelism": f"replicas x{world}"}
+
+    if args.impl == "reference":
+        if rank != 0:
+            return
+        steps = max(1, min(args.steps, 5))
+        gbs, sec, threads = cpu_reference(reps=max(1, min(args.warmup, 2)) + steps)
+        line = {"impl": "reference", "metric": METRIC, "value": round(gbs, 4), "unit": UNIT, "n_gpus": args.gpus,
+                "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sec * 1e3, 3),
+                "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
+                "data": "synthetic", "config": config,
+                "cpu_baseline": {"value": round(gbs, 4), "unit": UNIT, "cores": threads, "kind": "port",
+                                 "sample": "one 4096x4096 g128 layer, M=1: fp16 reconstruct + fp32 matmul, best of the steps"},
+                "e2e": {"value": round(gbs, 4), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
+        print(json.dumps(line))
+        return
+
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py: no CUDA device; the kernels have no CPU path")
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    r = run_ours(args, rank, world, local_rank)
+    if rank == 0:
+        peak, peak_kind = load_peaks()
+        bps = bytes_per_step(args.copies)
+        value = bps * world * args.steps / (r["ms"] * 1e-3) / 1e9
+        per_launch_us = r["ms"] * 1e3 / (args.steps * r["n_launch"])
+        achieved = bps / r["n_launch"] / (per_launch_us * 1e-6) / 1e9
+        e2e = bps * world * r["e2e_steps"] / (r["e2e_ms"] * 1e-3) / 1e9
+        line = {"metric": METRIC, "value": round(value, 1), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                "warmup": args.warmup, "ms_per_step": round(r["ms"] / args.steps, 5), "higher_is_better": True,
+                "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": config,
+                "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                             "frac": round(achieved / peak, 4), "traffic": None, "peak_kind": peak_kind,
+                             "kernel": "gemv_seq_kernel<1>", "avg_launch_us": round(per_launch_us, 3),
+                             "frac_of_nominal_8000": round(achieved / 8000.0, 4)},
+                "per_shape": r["per_shape"],
+                "e2e": {"value": round(e2e, 1), "unit": UNIT, "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": r["d2h"],
+                        "api": "matmul_utils_4bit.matmul4bit, pinned host x in, pinned host y out, weights resident"},
+                "gpu_launches": args.steps * r["n_launch"], "clocks": r["clocks"]}
+        if world == 1 and not args.no_cpu:
+            gbs, sec, threads = cpu_reference(reps=3)
+            line["cpu_baseline"] = {"value": round(gbs, 4), "unit": UNIT, "cores": threads, "kind": "port",
+                                    "sample": "one 4096x4096 g128 layer, M=1: fp16 reconstruct + fp32 matmul, best of 3"}
+        print(json.dumps(line))
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,93 @@
+/*
+ * q4b200 — C ABI of the B200 (sm_100a) GPTQ int4 dequant-matmul kernels.
+ *
+ * Every entry point takes plain device pointers, sizes and a CUDA stream handle; nothing here
+ * knows about torch.  The caller owns all memory and must have made the device that owns the
+ * pointers current on the calling thread.  Every function that launches work returns 0 on
+ * success or a negative Q4_E_* code; q4_last_error_string() then gives a human-readable
+ * reason (thread-local).  Launches are asynchronous on `stream`.
+ *
+ * Tensor conventions (GPTQ v2, as stored by Autograd4bitQuantLinear, autograd_4bit.py:176-189):
+ *   qweight int32 [K/8, N]   nibble j of word (r, n) is level q of row k = 8r + j, column n
+ *   qzeros  int32 [G, N/8]   nibble n%8 of word (g, n/8) is the stored zero point z (kernel adds 1)
+ *   scales  T     [G, N]
+ *   g_idx   int32 [K]        group of row k
+ *   W[k, n] = scales[g,n]*q - scales[g,n]*(z+1),  g = g_idx[k]
+ * All matrices are dense row-major.
+ */
+#ifndef Q4B200_H_
+#define Q4B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define Q4_VERSION 100
+
+/* element types of scales / outputs */
+#define Q4_F16 0
+#define Q4_F32 1
+
+/* status codes */
+#define Q4_OK            0
+#define Q4_E_BADARG     -1   /* null pointer, non-positive size, unknown enum */
+#define Q4_E_SHAPE      -2   /* size not supported by the kernel (divisibility) */
+#define Q4_E_ALIGN      -3   /* pointer not 16-byte aligned */
+#define Q4_E_WORKSPACE  -4   /* workspace missing or too small */
+#define Q4_E_CUDA       -5   /* a CUDA runtime / driver call failed */
+#define Q4_E_DEVICE     -6   /* device is not sm_100 */
+
+/* q4_gemv flags */
+#define Q4_GEMV_ACCUMULATE 1u  /* y += x*W instead of y = x*W (the reference kernels add into `mul`) */
+#define Q4_GEMV_ACT_ORDER  2u  /* take the group of every row from g_idx (else k / groupsize)      */
+#define Q4_GEMV_V1         4u  /* v1 layer: scales fp16 [N]; `qzeros` points at fp16 zeros [N];
+                                  W = scales[n]*q - zeros[n]; G, groupsize and g_idx are ignored */
+
+typedef void* q4_stream_t;     /* a cudaStream_t */
+
+int q4_version(void);
+const char* q4_last_error_string(void);
+
+/* Reconstruct the dense weight  W [K, N]  from a 4-bit v2 layer.
+ * Replaces quant_cuda.vecquant4recons_v2 (quant_cuda.cpp:137-148,
+ * quant_cuda_kernel.cu:1127-1183).  `dtype` is the type of `scales` and `out` (Q4_F16: three
+ * fp16 roundings, bit-exact with the reference; Q4_F32: one fused multiply-subtract).
+ * Needs N % 8 == 0, K % 8 == 0. */
+int q4_recons_v2(const int32_t* qweight, void* out, const void* scales, const int32_t* qzeros,
+                 const int32_t* g_idx, int K, int N, int G, int dtype, q4_stream_t stream);
+
+/* v1 layer: W[k,n] = scales[n]*q - zeros[n], per-column float scale and zero.
+ * Replaces quant_cuda.vecquant4recons_v1 (quant_cuda.cpp:125-135, quant_cuda_kernel.cu:1076-1125). */
+int q4_recons_v1(const int32_t* qweight, void* out, const void* scales, const void* zeros,
+                 int K, int N, int dtype, q4_stream_t stream);
+
+/* 2-bit v2 layer: qweight int32 [K/16, N], qzeros int32 [G, N/16], zero point = field + 1.
+ * Replaces quant_cuda.vecquant2recons_v2 (quant_cuda.cpp:150-161, quant_cuda_kernel.cu:1185-1241).
+ * Needs N % 16 == 0, K % 16 == 0. */
+int q2_recons_v2(const int32_t* qweight, void* out, const void* scales, const int32_t* qzeros,
+                 const int32_t* g_idx, int K, int N, int G, int dtype, q4_stream_t stream);
+
+/* Decode product  y [M, N] (+)= x [M, K] * W,  1 <= M <= 16, without materialising W.
+ * Replaces quant_cuda.vecquant4matmul / vecquant4matmul_faster / vecquant4matmul_old_faster /
+ * vecquant4matmul_v1_faster / vecquant4matmul_g (quant_cuda.cpp:35-48,95-108,110-123,163-174,
+ * 189-202; kernels quant_cuda_kernel.cu:475-536,910-975,978-1041,1243-1302,1488-1567).
+ *   x fp16 [M, K]; scales fp16 [G, N]; y of type y_dtype (Q4_F16 or Q4_F32); bias fp16 [N] or NULL.
+ *   Without Q4_GEMV_ACT_ORDER the group of row k is k / groupsize and g_idx may be NULL.
+ *   Needs K % 32 == 0, N % 32 == 0, groupsize % 32 == 0.
+ * `workspace` is caller-provided device scratch of at least q4_gemv_workspace_bytes(M, K, N)
+ * bytes that must be zero when first used and is left zero-filled where it has to be; calls
+ * that share a workspace must be ordered on one stream.  Summation order is fixed, so results
+ * are reproducible run to run. */
+size_t q4_gemv_workspace_bytes(int M, int K, int N);
+int q4_gemv(const void* x, const int32_t* qweight, void* y, const void* scales,
+            const int32_t* qzeros, const int32_t* g_idx, const void* bias,
+            int M, int K, int N, int G, int groupsize, int y_dtype, unsigned flags,
+            void* workspace, size_t workspace_bytes, q4_stream_t stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* Q4B200_H_ */

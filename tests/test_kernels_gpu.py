@@ -1,0 +1,244 @@
+"""Parity of the CUDA kernels (through the C ABI) with the CPU oracle and the golden fixtures."""
+import glob
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from alpaca_lora_4bit_b200 import _lib, quant_cuda, synth
+from oracle import q4_oracle as orc
+
+pytestmark = pytest.mark.gpu
+GOLD = os.path.join(os.path.dirname(__file__), "golden")
+DEV = "cuda:0"
+REL_TOL = 2e-3          # relative Frobenius error allowed on matmul outputs
+
+
+def rel_fro(got, want):
+    got, want = got.double().cpu(), want.double().cpu()
+    return float((got - want).norm() / want.norm())
+
+
+def bits_equal(a, b):
+    a, b = a.cpu().contiguous(), b.cpu().contiguous()
+    nan = torch.isnan(b)
+    if not torch.equal(torch.isnan(a), nan):
+        return False
+    it = torch.int16 if a.dtype == torch.float16 else torch.int32
+    return torch.equal(a.view(it)[~nan], b.view(it)[~nan])
+
+
+def guarded(shape, dtype, fill=-777.0):
+    """Output tensor with canary rows before and after, to catch out-of-bounds stores."""
+    rows = shape[0]
+    full = torch.full((rows + 16, shape[1]), fill, dtype=dtype, device=DEV)
+    return full, full[8:8 + rows]
+
+
+def canaries_intact(full, rows, fill=-777.0):
+    return bool((full[:8] == fill).all()) and bool((full[8 + rows:] == fill).all())
+
+
+def recons_gpu(layer, dtype=torch.float16):
+    L = layer.to(DEV)
+    full, out = guarded((layer.K, layer.N), dtype)
+    sc = L.scales.to(dtype)
+    if layer.bits == 4:
+        quant_cuda.vecquant4recons_v2(L.qweight, out, sc, L.qzeros, L.g_idx)
+    else:
+        quant_cuda.vecquant2recons_v2(L.qweight, out, sc, L.qzeros, L.g_idx)
+    torch.cuda.synchronize()
+    assert canaries_intact(full, layer.K)
+    return out
+
+
+def load_layer(npz):
+    d = np.load(npz)
+    return synth.QuantLayer(torch.from_numpy(d["qweight"]), torch.from_numpy(d["qzeros"]),
+                            torch.from_numpy(d["scales"]), torch.from_numpy(d["g_idx"]),
+                            int(d["K"]), int(d["N"]), int(d["groupsize"]), int(d["bits"])), d
+
+
+# ---------------------------------------------------------------- reconstruct: bit-exact
+@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(GOLD, "recons*_v2_*.npz"))))
+def test_recons_v2_golden(path):
+    layer, d = load_layer(path)
+    assert bits_equal(recons_gpu(layer), torch.from_numpy(d["w"]))
+
+
+def test_recons_v1_golden():
+    d = np.load(os.path.join(GOLD, "recons_v1_k128_n64.npz"))
+    qw = torch.from_numpy(d["qweight"]).to(DEV)
+    full, out = guarded((128, 64), torch.float16)
+    quant_cuda.vecquant4recons_v1(qw, out, torch.from_numpy(d["scales"]).to(DEV).reshape(-1),
+                                  torch.from_numpy(d["zeros"]).to(DEV).reshape(-1))
+    torch.cuda.synchronize()
+    assert canaries_intact(full, 128)
+    assert bits_equal(out, torch.from_numpy(d["w"]))
+
+
+@pytest.mark.parametrize("K,N,g,act", [(4096, 4096, 128, False), (4096, 4096, 128, True), (1024, 11008, 128, True),
+                                       (5120, 1024, 128, True), (256, 136, 64, True), (4096, 4096, -1, False),
+                                       (8, 8, 8, False)])
+def test_recons_v2_oracle(K, N, g, act):
+    layer = synth.make_layer(K, N, g, act, seed=K + N)
+    want = orc.recons_v2(layer.qweight, layer.scales, layer.qzeros, layer.g_idx)
+    assert bits_equal(recons_gpu(layer), want)
+
+
+def test_recons_v2_fp32_scales():
+    layer = synth.make_layer(1024, 512, 128, True, seed=5)
+    layer.scales = layer.scales  # fp16 source
+    L32 = synth.QuantLayer(layer.qweight, layer.qzeros, layer.scales.float() * 1.37, layer.g_idx, 1024, 512, 128)
+    want = orc.recons_v2(L32.qweight, L32.scales, L32.qzeros, L32.g_idx)
+    got = recons_gpu(L32, torch.float32)
+    assert bits_equal(got, want)
+
+
+def test_recons2_v2_oracle():
+    layer = synth.make_layer(2048, 1024, 128, True, seed=9, bits=2)
+    want = orc.recons2_v2(layer.qweight, layer.scales, layer.qzeros, layer.g_idx)
+    assert bits_equal(recons_gpu(layer), want)
+    got32 = recons_gpu(synth.QuantLayer(layer.qweight, layer.qzeros, layer.scales.float(), layer.g_idx,
+                                        2048, 1024, 128, 2), torch.float32)
+    assert bits_equal(got32, orc.recons2_v2(layer.qweight, layer.scales.float(), layer.qzeros, layer.g_idx))
+
+
+def test_recons_v1_oracle_both_dtypes():
+    gen = torch.Generator().manual_seed(21)
+    layer = synth.make_layer(2048, 1024, 2048, False, seed=21)
+    sc = (torch.rand(1024, generator=gen) * 0.018 + 0.002)
+    ze = sc * torch.randint(1, 16, (1024,), generator=gen)
+    for dt in (torch.float16, torch.float32):
+        full, out = guarded((2048, 1024), dt)
+        quant_cuda.vecquant4recons_v1(layer.qweight.to(DEV), out, sc.to(dt).to(DEV), ze.to(dt).to(DEV))
+        torch.cuda.synchronize()
+        assert canaries_intact(full, 2048)
+        assert bits_equal(out, orc.recons_v1(layer.qweight, sc.to(dt), ze.to(dt)))
+
+
+def test_recons_idempotent_and_full_overwrite():
+    layer = synth.make_layer(512, 256, 128, True, seed=2).to(DEV)
+    a = torch.full((512, 256), float("nan"), dtype=torch.float16, device=DEV)
+    quant_cuda.vecquant4recons_v2(layer.qweight, a, layer.scales, layer.qzeros, layer.g_idx)
+    b = torch.zeros_like(a)
+    quant_cuda.vecquant4recons_v2(layer.qweight, b, layer.scales, layer.qzeros, layer.g_idx)
+    assert not torch.isnan(a).any() and torch.equal(a, b)
+
+
+# ---------------------------------------------------------------- decode product
+def gemv_gpu(layer, x, ydtype=torch.float16, flags=0, groupsize=None, y0=None, bias=None):
+    L = layer.to(DEV)
+    M = x.shape[0]
+    full, y = guarded((M, layer.N), ydtype)
+    if y0 is not None:
+        y.copy_(y0)
+    quant_cuda.gemv(x.to(DEV), L.qweight, y, L.scales, L.qzeros,
+                    L.g_idx if flags & _lib.GEMV_ACT_ORDER else None,
+                    groupsize or layer.groupsize, flags, bias=bias)
+    torch.cuda.synchronize()
+    assert canaries_intact(full, M)
+    return y
+
+
+@pytest.mark.parametrize("name", ["recons_v2_seq_k128_n64_g32.npz", "recons_v2_act_k128_n64_g32.npz",
+                                  "recons_v2_act_k256_n32_g128.npz"])
+def test_gemv_golden(name):
+    layer, d = load_layer(os.path.join(GOLD, name))
+    act = "act" in name
+    y = gemv_gpu(layer, torch.from_numpy(d["x"]), torch.float32, _lib.GEMV_ACT_ORDER if act else 0)
+    assert rel_fro(y, torch.from_numpy(d["y"])) <= REL_TOL
+
+
+@pytest.mark.parametrize("K,N", [(4096, 4096), (4096, 11008), (11008, 4096)])
+@pytest.mark.parametrize("M", [1, 4, 8, 16])
+def test_gemv_llama7b_shapes(K, N, M):
+    layer = synth.make_layer(K, N, 128, False, seed=K // 7 + N)
+    x = synth.make_acts(M, K, seed=M)
+    want = orc.gemv_fp32(x, layer.qweight, layer.scales, layer.qzeros, layer.g_idx)
+    for dt in (torch.float16, torch.float32):
+        assert rel_fro(gemv_gpu(layer, x, dt), want) <= REL_TOL
+    # against the reference composition too: fp16 reconstruct, fp32 matmul
+    ref = orc.matmul4bit_ref(x, layer.qweight, layer.scales, layer.qzeros, layer.g_idx)
+    assert rel_fro(gemv_gpu(layer, x, torch.float32), ref) <= REL_TOL
+
+
+@pytest.mark.parametrize("M", [1, 3, 9, 16])
+@pytest.mark.parametrize("K,N,g", [(5120, 5120, 128), (512, 96, 64), (1024, 2048, 32)])
+def test_gemv_act_order(K, N, g, M):
+    layer = synth.make_layer(K, N, g, True, seed=K + M)
+    x = synth.make_acts(M, K, seed=M + 50)
+    want = orc.gemv_fp32(x, layer.qweight, layer.scales, layer.qzeros, layer.g_idx)
+    assert rel_fro(gemv_gpu(layer, x, torch.float32, _lib.GEMV_ACT_ORDER), want) <= REL_TOL
+
+
+@pytest.mark.parametrize("K,N,g,M", [(32, 32, 32, 1), (64, 32, 32, 5), (4096, 32, 128, 2), (2048, 4096, 64, 7),
+                                     (8192, 1024, -1, 16), (1056, 64, 96, 3)])
+def test_gemv_ragged_sizes(K, N, g, M):
+    layer = synth.make_layer(K, N, g, False, seed=K + N + M)
+    x = synth.make_acts(M, K, seed=3)
+    want = orc.gemv_fp32(x, layer.qweight, layer.scales, layer.qzeros, layer.g_idx)
+    assert rel_fro(gemv_gpu(layer, x, torch.float32), want) <= REL_TOL
+
+
+def test_gemv_accumulates_bias_and_is_reproducible():
+    layer = synth.make_layer(4096, 4096, 128, False, seed=77)
+    x = synth.make_acts(4, 4096, seed=8)
+    want = orc.gemv_fp32(x, layer.qweight, layer.scales, layer.qzeros, layer.g_idx)
+    y0 = torch.randn(4, 4096)
+    y = gemv_gpu(layer, x, torch.float32, _lib.GEMV_ACCUMULATE, y0=y0.to(DEV))
+    assert rel_fro(y, want + y0.double()) <= REL_TOL
+    bias = torch.randn(4096).half()
+    yb = gemv_gpu(layer, x, torch.float32, 0, bias=bias.to(DEV))
+    assert rel_fro(yb, want + bias.double()) <= REL_TOL
+    a = gemv_gpu(layer, x, torch.float32)
+    for _ in range(3):
+        assert torch.equal(a, gemv_gpu(layer, x, torch.float32))
+
+
+def test_gemv_linearity_full_size():
+    """y(x1 + x2) = y(x1) + y(x2) at the largest decode case (M=16, 11008x4096), where the
+    scalar oracle is too slow to be the checker; the fp16 rounding of x1 + x2 is inside the tolerance."""
+    layer = synth.make_layer(11008, 4096, 128, False, seed=1)
+    x1 = synth.make_acts(16, 11008, seed=31)
+    x2 = synth.make_acts(16, 11008, seed=32)
+    xs = (x1.float() + x2.float()).half()
+    y1, y2, ys = (gemv_gpu(layer, v, torch.float32) for v in (x1, x2, xs))
+    assert rel_fro(ys, y1 + y2) <= REL_TOL
+
+
+def test_gemv_v1_facade():
+    gen = torch.Generator().manual_seed(23)
+    layer = synth.make_layer(4096, 1024, 4096, False, seed=23)
+    sc = (torch.rand(1024, generator=gen) * 0.018 + 0.002).half()
+    ze = (sc.float() * torch.randint(1, 16, (1024,), generator=gen)).half()
+    x = synth.make_acts(2, 4096, seed=4)
+    y = torch.zeros((2, 1024), dtype=torch.float16, device=DEV)
+    quant_cuda.vecquant4matmul_v1_faster(x.to(DEV), layer.qweight.to(DEV), y, sc.reshape(-1, 1).to(DEV),
+                                         ze.reshape(-1, 1).to(DEV))
+    want = orc.matmul_recons(x, orc.recons_v1(layer.qweight, sc, ze))
+    assert rel_fro(y, want) <= REL_TOL
+
+
+def test_facade_matmul_variants_add_into_mul():
+    layer = synth.make_layer(4096, 4096, 128, False, seed=41)
+    L = layer.to(DEV)
+    x = synth.make_acts(20, 4096, seed=42)          # more than one 16-row slab
+    want = orc.gemv_fp32(x, layer.qweight, layer.scales, layer.qzeros, layer.g_idx)
+    y = torch.ones((20, 4096), dtype=torch.float32, device=DEV)
+    quant_cuda.vecquant4matmul_old_faster(x.to(DEV), L.qweight, y, L.scales.float(), L.qzeros, 128, 2048)
+    assert rel_fro(y, want + 1.0) <= REL_TOL
+    y = torch.zeros((20, 4096), dtype=torch.float16, device=DEV)
+    quant_cuda.vecquant4matmul_faster(x.to(DEV), L.qweight, y, L.scales, L.qzeros, L.g_idx, 2048)
+    assert rel_fro(y, want) <= REL_TOL
+    y = torch.zeros((20, 4096), dtype=torch.float32, device=DEV)
+    quant_cuda.vecquant4matmul(x.float().to(DEV), L.qweight, y, L.scales.float(), L.qzeros, L.g_idx)
+    assert rel_fro(y, want) <= REL_TOL
+
+
+def test_workspace_counters_return_to_zero():
+    layer = synth.make_layer(4096, 4096, 128, False, seed=3)
+    gemv_gpu(layer, synth.make_acts(1, 4096), torch.float16)
+    for ws in _lib._workspaces.values():
+        assert int(ws[:512].view(torch.int32).abs().sum()) == 0      # 128 tile counters
