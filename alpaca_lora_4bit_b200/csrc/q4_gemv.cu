@@ -26,6 +26,9 @@ namespace q4 {
 constexpr int GEMV_THREADS = 256;
 constexpr int GEMV_WARPS = 8;
 constexpr int GEMV_TN = 32;          // columns per CTA
+// Workspace layout: a fixed 64 KiB head of arrival counters (one per column tile, so the
+// counters of one shape never alias the partial sums of another), then the partial sums.
+constexpr size_t GEMV_WS_HEAD = 65536;
 
 struct GemvParams {
   const __half* x;
@@ -336,8 +339,7 @@ extern "C" size_t q4_gemv_workspace_bytes(int M, int K, int N) {
   if (M <= 0 || K <= 0 || N <= 0 || K % 32 || N % 32) return 0;
   int S, sps;
   gemv_plan(K, N, S, sps);
-  const size_t counters = ((size_t)(N / GEMV_TN) * sizeof(unsigned) + 255) / 256 * 256;
-  return counters + (S > 1 ? (size_t)S * M * N * sizeof(float) : 0);
+  return GEMV_WS_HEAD + (S > 1 ? (size_t)S * M * N * sizeof(float) : 0);
 }
 
 extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const void* scales,
@@ -375,9 +377,10 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
     if (!workspace || workspace_bytes < need)
       return fail(Q4_E_WORKSPACE, "gemv: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
     if (!aligned16(workspace)) return fail(Q4_E_ALIGN, "gemv: workspace must be 16-byte aligned");
-    const size_t counters = ((size_t)(N / GEMV_TN) * sizeof(unsigned) + 255) / 256 * 256;
+    if ((size_t)(N / GEMV_TN) * sizeof(unsigned) > GEMV_WS_HEAD)
+      return fail(Q4_E_SHAPE, "gemv: N=%d has more column tiles than the workspace head holds", N);
     p.counters = (unsigned*)workspace;
-    p.part = (float*)((char*)workspace + counters);
+    p.part = (float*)((char*)workspace + GEMV_WS_HEAD);
   } else {
     p.counters = nullptr; p.part = nullptr;
   }

@@ -241,4 +241,4 @@ def test_workspace_counters_return_to_zero():
     layer = synth.make_layer(4096, 4096, 128, False, seed=3)
     gemv_gpu(layer, synth.make_acts(1, 4096), torch.float16)
     for ws in _lib._workspaces.values():
-        assert int(ws[:512].view(torch.int32).abs().sum()) == 0      # 128 tile counters
+        assert int(ws[:65536].view(torch.int32).abs().sum()) == 0      # the counter head of the workspace
