@@ -41,3 +41,52 @@ int check_device() {
 
 extern "C" int q4_version(void) { return Q4_VERSION; }
 extern "C" const char* q4_last_error_string(void) { return q4::err_buf(); }
+
+// ---- tensor-map encoding through the driver entry point (no link-time dependency on libcuda) ----
+#include "q4_async.cuh"
+
+namespace q4 {
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn) return fn;
+  void* p = nullptr;
+  cudaDriverEntryPointQueryResult q;
+  if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+      q != cudaDriverEntryPointSuccess)
+    return nullptr;
+  fn = (EncodeTiledFn)p;
+  return fn;
+}
+
+int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int elem_bytes, uint64_t cols,
+                 uint64_t rows, uint64_t row_pitch_bytes, uint32_t box_cols, uint32_t box_rows,
+                 CUtensorMapSwizzle swizzle) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return fail(Q4_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  if (!aligned16(base) || row_pitch_bytes % 16 || (uint64_t)box_cols * elem_bytes % 16)
+    return fail(Q4_E_ALIGN, "tensor map: base, row pitch and box width must be multiples of 16 bytes");
+  cuuint64_t dims[2] = {cols, rows};
+  cuuint64_t strides[1] = {row_pitch_bytes};
+  cuuint32_t box[2] = {box_cols, box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(Q4_E_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  return Q4_OK;
+}
+
+int sm_count() {
+  static int n[64] = {0};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (!n[dev]) cudaDeviceGetAttribute(&n[dev], cudaDevAttrMultiProcessorCount, dev);
+  return n[dev] > 0 ? n[dev] : 148;
+}
+
+}  // namespace q4

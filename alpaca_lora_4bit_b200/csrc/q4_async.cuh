@@ -1,0 +1,103 @@
+// mbarrier / TMA / programmatic-dependent-launch helpers (inline PTX, sm_100a) and the host side
+// tensor-map encoder.  No cluster multicast is used anywhere: every CTA fetches its own tiles.
+#pragma once
+
+#include <cuda.h>
+
+#include "q4_common.cuh"
+
+namespace q4 {
+
+// ---- host: tensor maps ----------------------------------------------------------------------
+// 2-D row-major tensor of `elem_bytes`-wide elements, box = box_cols x box_rows.
+// swizzle: 0 none, 1 32B, 2 64B, 3 128B (CUtensorMapSwizzle values).
+int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int elem_bytes,
+                 uint64_t cols, uint64_t rows, uint64_t row_pitch_bytes, uint32_t box_cols, uint32_t box_rows,
+                 CUtensorMapSwizzle swizzle);
+
+#ifdef __CUDACC__
+
+// Device-visible status word values written when a bounded wait expires.
+constexpr unsigned Q4_STATUS_OK = 0u;
+constexpr unsigned Q4_STATUS_WAIT_EXPIRED = 0xDEAD0001u;
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_fence_init() { asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory"); }
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_expect_tx(uint64_t* bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+
+// Bounded wait.  Returns false if the phase did not complete within `limit` polls; the caller
+// then records Q4_STATUS_WAIT_EXPIRED and carries on without waiting (results are garbage but
+// every thread still reaches the end of the kernel, so nothing can hang).
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32_t limit) {
+  for (uint32_t i = 0; i < limit; ++i)
+    if (mbar_try_wait(bar, parity)) return true;
+  return false;
+}
+
+// Sleeping variant: the hardware may suspend the thread for up to `ns` nanoseconds per try, so a
+// waiting warp does not compete for issue slots with the warps that have work.
+__device__ __forceinline__ bool mbar_try_wait_sleep(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity), "r"(ns) : "memory");
+  return ok != 0;
+}
+
+// Warp-wide bounded wait: lane 0 sleeps on the barrier, then every lane confirms the phase with
+// one try of its own (which returns at once) so that each thread has acquired the data.
+// All 32 lanes must call it.  Returns false (on every lane) if the phase never completed.
+__device__ __forceinline__ bool mbar_wait_warp(uint64_t* bar, uint32_t parity, uint32_t limit) {
+  bool ok = true;
+  if ((threadIdx.x & 31) == 0) {
+    ok = false;
+    for (uint32_t i = 0; i < limit && !ok; ++i) ok = mbar_try_wait_sleep(bar, parity, 2000u);
+  }
+  ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+  if (ok) ok = mbar_try_wait(bar, parity);
+  return __all_sync(0xffffffffu, ok ? 1 : 0) != 0;
+}
+
+// 2-D tiled TMA load global -> shared, completion signalled on `bar` (no multicast).
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_prefetch_desc(const CUtensorMap* map) {
+  asm volatile("prefetch.tensormap [%0];" ::"l"(map) : "memory");
+}
+
+// Programmatic dependent launch: let the next kernel in the stream start early / wait for the
+// previous kernel's memory to be visible.  Both are no-ops when the launch has no such edge.
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+__device__ __forceinline__ void named_bar_sync(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+#endif  // __CUDACC__
+
+}  // namespace q4

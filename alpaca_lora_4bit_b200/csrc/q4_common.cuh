@@ -17,6 +17,8 @@ int fail(int code, const char* fmt, ...);
 int check_cuda(cudaError_t e, const char* what);
 // 0 if the current device is sm_100, else Q4_E_DEVICE (cached per device).
 int check_device();
+// Number of SMs of the current device (cached).
+int sm_count();
 
 static inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

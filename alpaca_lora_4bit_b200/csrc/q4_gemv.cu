@@ -1,25 +1,35 @@
 // Decode product  y[M,N] (+)= x[M,K] * W  for 1 <= M <= 16 straight from the packed int4 layer.
 //
 // Bound by HBM: per weight 0.5 B of qweight plus 1/64 B of scales and 1/256 B of zero points at
-// groupsize 128; x and y are noise.  Design:
-//   * A CTA owns 32 adjacent columns and one K-split; its 8 warps walk the split in chunks of
-//     128 rows (4 "steps" of 32 rows).  In a step lane (g,t) reads ONE 128-bit word group:
-//     packed row 4*step+t, columns 4g..4g+3, so a warp covers 4 packed rows x 128 contiguous
-//     bytes and every byte of qweight is requested once, with four such loads in flight per lane.
-//   * Nibbles are turned into fp16 with the exponent trick (w & 0x000F000F | 0x6400 = 1024+q,
-//     one LOP3 per two weights) and fed to mma.sync.m16n8k16 as the A operand (rows = 16 output
-//     columns); x is the B operand (columns = batch).  The contraction index of the MMA is
-//     free, so the (q_j, q_j+4) pairing that the mask produces is matched by permuting x with
-//     four PRMTs per step instead of un-shuffling the weights.
+// groupsize 128; x and y are noise.  Design of the main kernel (sequential groups and v1 layers):
+//   * Persistent: one CTA per SM.  The matrix is cut into boxes of 64 packed rows x 32 columns
+//     (8 KiB, 512 k-rows x 32 outputs); the boxes, ordered column tile by column tile, are dealt to
+//     the CTAs in equal contiguous runs (stream-K), so every SM streams the same number of bytes
+//     whatever the shape.
+//   * A producer thread keeps a ring of GEMV_STAGES boxes in flight with TMA tile loads
+//     (cp.async.bulk.tensor.2d + mbarrier complete_tx): ~80 KiB outstanding per SM, which is what
+//     HBM latency x bandwidth asks for, independent of how many registers the math needs.
+//   * Eight consumer warps take two 32-row "steps" of each box.  In a step lane (g,t) reads packed
+//     row 4*step+t, columns 4g..4g+3 with one conflict-free LDS.128.  Nibbles are turned into fp16
+//     with the exponent trick (w & 0x000F000F | 0x6400 = 1024+q, one LOP3 per two weights) and fed
+//     to mma.sync.m16n8k16 as the A operand (rows = 16 output columns); x is the B operand
+//     (columns = batch).  The contraction index of the MMA is free, so the (q_j, q_j+4) pairing the
+//     mask produces is matched by permuting x with four PRMTs instead of un-shuffling weights.
 //   * The +1024 offset and the zero point leave with one extra MMA against an all-ones A tile,
 //     which yields sum_k x[k] per batch column:  y += s * (acc - (1024 + z + 1) * xsum), applied
 //     once per quantisation group in fp32.
-//   * Cross-warp reduction in shared memory, cross-split reduction through a caller-provided
-//     workspace with a per-tile arrival counter: the last CTA to arrive adds the partials in
-//     split order, so the result does not depend on scheduling.  No atomics on y, no zero-fill.
+//   * When a CTA's run ends inside a column tile it writes its partial sums to the workspace and
+//     bumps the tile's arrival counter; the last contributor adds the partials in CTA order, so
+//     the result does not depend on scheduling.  No atomics on y, no zero-fill.
+//   * griddepcontrol: the kernel lets its successor start at once and itself waits for its
+//     predecessor only before it first touches x, y or the workspace - weights never depend on
+//     an earlier kernel, so back-to-back decode layers overlap their weight streams.
+//   * Every mbarrier wait is bounded; if one expires the kernel records a status word in the
+//     workspace, stops waiting and runs to its end (garbage out, no hang).
 // The act-order variant (group from g_idx per row) cannot factor the scale out of the
 // contraction; it dequantises per element from shared-memory scale tables instead.
-#include "q4_common.cuh"
+#include "q4_async.cuh"
+
 
 namespace q4 {
 
@@ -123,127 +133,392 @@ __device__ __forceinline__ void gemv_reduce_store(const GemvParams& p, float* re
   if (threadIdx.x == 0) p.counters[blockIdx.x] = 0u;    // ready for the next launch
 }
 
-// ---- sequential groups (group of row k = k / groupsize) ------------------------------------------
-template <int MT>
-__global__ void __launch_bounds__(GEMV_THREADS)
-gemv_seq_kernel(const GemvParams p) {
-  __shared__ float red[GEMV_WARPS * MT * 8 * GEMV_TN];
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int g = lane >> 2, t = lane & 3;
-  const int c0 = blockIdx.x * GEMV_TN;
-  const int split = blockIdx.y;
-  const int sb = split * p.steps_per_split;
-  const int se = min(sb + p.steps_per_split, p.steps_total);
-  const int N = p.N, K = p.K;
-  const int steps_per_group = p.groupsize >> 5;
+// ---- sequential groups (group of row k = k / groupsize) and v1 layers: TMA streaming kernel --------
+constexpr int GEMV_BOX_ROWS = 64;                 // packed rows per box (512 k-rows, 16 steps)
+constexpr int GEMV_BOX_STEPS = GEMV_BOX_ROWS / 4;
+constexpr int GEMV_BOX_WORDS = GEMV_BOX_ROWS * GEMV_TN;
+constexpr int GEMV_BOX_BYTES = GEMV_BOX_WORDS * 4;
+constexpr int GEMV_META_ROWS = 17;                // groups one box can touch at groupsize 32, +1 straddle
+constexpr int GEMV_SC_BYTES = 1152;               // 17 rows x 32 halves, rounded up to 128
+constexpr int GEMV_ZP_BYTES = 1152;               // 17 rows x 16 B (v2) or x 64 B (v1 fp16 zeros)
+constexpr int GEMV_STAGE_BYTES = GEMV_BOX_BYTES + GEMV_SC_BYTES + GEMV_ZP_BYTES;
+constexpr int GEMV_STAGES = 11;
+constexpr int GEMV_CWARPS = 16;                   // consumer warps: 4 box phases x 4 row slots
+constexpr int GEMV_PHASES = GEMV_CWARPS / 4;
+constexpr int GEMV_CONSUMERS = GEMV_CWARPS * 32;
+constexpr int GEMV_PWARPS = 4;                    // producer warps, each feeding every 4th box
+constexpr int GEMV_STREAM_THREADS = GEMV_CONSUMERS + 32 * GEMV_PWARPS;
+constexpr uint32_t GEMV_WAIT_LIMIT = 1u << 22;    // polls before a wait is declared dead
+constexpr int GEMV_XS_MAX_BYTES = 49152;          // largest x kept in shared memory
 
-  float yacc[MT][2][4];
-  float c[MT][2][4], co[MT][4];
+struct GemvStreamParams {
+  GemvParams g;
+  int boxes_per_tile, total_boxes, steps_per_tile;
+  int meta_rows;                                  // group rows fetched with each box
+  uint32_t stage_tx;                              // bytes TMA delivers per stage
+  float* cta_part;                                // [grid][2][MT*8][32]
+  unsigned* status;
+  int group_shift;                                // log2(steps per group), or -1 if not a power of two
+  unsigned long long* trace;                      // optional timing trace (64 slots per CTA), else null
+};
+
+template <int MT>
+__host__ __device__ constexpr size_t gemv_stream_smem() {
+  return (size_t)GEMV_STAGES * GEMV_STAGE_BYTES + sizeof(float) * 2 * GEMV_CWARPS * MT * 8 * GEMV_TN + 2 * GEMV_STAGES * 8 + 16;
+}
+
+__device__ __forceinline__ void trace_mark(unsigned long long* tr, int slot) {
+  if (tr && slot < 64) tr[(size_t)blockIdx.x * 64 + slot] = clock64();
+}
+
+// CTA that owns box b when `nb` boxes are dealt to `G` CTAs as [c*nb/G, (c+1)*nb/G).
+__device__ __forceinline__ int box_owner(long long b, int G, int nb) { return (int)(((b + 1) * G + nb - 1) / nb) - 1; }
+
+// MMA whose accumulator starts at zero (first k-step of a group).
+__device__ __forceinline__ void mma16816_first(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
+                                               uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.f16.f16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+               : "=f"(c[0]), "=f"(c[1]), "=f"(c[2]), "=f"(c[3])
+               : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "f"(0.f));
+}
+__device__ __forceinline__ void named_bar_arrive(int id, int threads) {
+  asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+
+// FAST: the group size is a multiple of 128 rows (or the layer is v1), so the 128 rows a warp
+// takes from a box always lie in one group: no per-step group test, accumulators local to the box.
+// XS (needs FAST, M <= 8, K % 128 == 0, M*K*2 <= GEMV_XS_MAX_BYTES): x is copied once per CTA into
+// shared memory in the order the MMA wants it, the odd k of every 8-block pre-divided by 16 so that
+// the high nibble of each byte can be used where it sits (w & 0x00F000F0 | 0x6400 = 1024 + 16 q, no
+// shift), and the per-128-row sums that take the 1024 / 64 offsets and the zero point out again are
+// tabulated once.  That removes the x permutes, half of the shifts and the all-ones MMA from the loop.
+template <int MT, bool FAST, bool XS>
+__global__ void __launch_bounds__(GEMV_STREAM_THREADS, 1)
+gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap,
+                   const __grid_constant__ CUtensorMap zmap, const GemvStreamParams sp) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const GemvParams& p = sp.g;
+  constexpr int RED_FLOATS = GEMV_CWARPS * MT * 8 * GEMV_TN;          // one buffer of warp partials
+  float* red = reinterpret_cast<float*>(smem + (size_t)GEMV_STAGES * GEMV_STAGE_BYTES);   // [2][16][MT*8][32]
+  uint64_t* full = reinterpret_cast<uint64_t*>(red + 2 * RED_FLOATS);
+  uint64_t* empty = full + GEMV_STAGES;
+  volatile int* flags = reinterpret_cast<volatile int*>(empty + GEMV_STAGES);   // [0] abort
+  // XS only: [16 B of zeros][chunk table: K/128 x 8 float2][x rows, MMA order]
+  unsigned char* xs_base = smem + gemv_stream_smem<MT>();
+  float2* ctab = reinterpret_cast<float2*>(xs_base + 16);
+  __half* xs_buf = reinterpret_cast<__half*>(xs_base + 16 + (size_t)(sp.g.K / 128) * 64);
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nb = sp.total_boxes, G = gridDim.x, bpt = sp.boxes_per_tile;
+  const int b0 = (int)((long long)blockIdx.x * nb / G), b1 = (int)((long long)(blockIdx.x + 1) * nb / G);
+  const int gs = p.groupsize;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < GEMV_STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 4); }
+    flags[0] = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&wmap); tma_prefetch_desc(&smap); tma_prefetch_desc(&zmap);
+  }
+  __syncthreads();
+  pdl_launch_dependents();
+
+  if (warp >= GEMV_CWARPS) {
+    // ---------------- producers: one thread per warp, each feeding every 4th box of the ring ------
+    // (issuing a TMA tile load costs a few hundred cycles; four issuers keep the ring ahead)
+    if (lane == 0) {
+      const int pw = warp - GEMV_CWARPS;
+      int tile = b0 / bpt, bx = b0 - tile * bpt;
+      for (int i = b0; i < b1; ++i, ++bx) {
+        if (bx == bpt) { bx = 0; ++tile; }
+        const int it = i - b0, st = it % GEMV_STAGES, use = it / GEMV_STAGES;
+        if ((it % GEMV_PWARPS) != pw) continue;
+        if (use > 0) {
+          bool ok = false;
+          const uint32_t lim = flags[0] ? 4u : 20000u;
+          for (uint32_t tr = 0; tr < lim && !ok; ++tr) ok = mbar_try_wait_sleep(&empty[st], (use - 1) & 1, 2000u);
+          if (!ok) { flags[0] = 1; atomicExch(sp.status, Q4_STATUS_WAIT_EXPIRED); }
+        }
+        trace_mark(sp.trace, 32 + it);
+        unsigned char* dst = smem + (size_t)st * GEMV_STAGE_BYTES;
+        const int grow0 = p.v1 ? 0 : (bx * GEMV_BOX_ROWS * 8) / gs;
+        mbar_arrive_expect_tx(&full[st], sp.stage_tx);
+        tma_load_2d(dst, &wmap, tile * GEMV_TN, bx * GEMV_BOX_ROWS, &full[st]);
+        tma_load_2d(dst + GEMV_BOX_BYTES, &smap, tile * GEMV_TN, grow0, &full[st]);
+        tma_load_2d(dst + GEMV_BOX_BYTES + GEMV_SC_BYTES, &zmap, p.v1 ? tile * GEMV_TN : tile * (GEMV_TN / 8), grow0, &full[st]);
+      }
+    }
+    return;
+  }
+
+  // ---------------- consumers: warp = (box phase, 16-row slot) ----------------
+  const int g = lane >> 2, t = lane & 3;
+  const int phase = warp >> 2, slot = warp & 3;
+  const int K = p.K;
+  const int steps_per_group = gs >> 5;
+  const bool xok0 = g < p.M, xok1 = (g + 8) < p.M;
+  const __half* xrow = p.x + (size_t)g * K + 8 * t;
+
+  float yacc[MT][2][4];                                   // scaled sums of the closed groups of a tile
 #pragma unroll
-  for (int mt = 0; mt < MT; ++mt) {
+  for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
     for (int j = 0; j < 2; ++j)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) { yacc[mt][j][i] = 0.f; c[mt][j][i] = 0.f; }
-#pragma unroll
-    for (int i = 0; i < 4; ++i) co[mt][i] = 0.f;
-  }
+      for (int i = 0; i < 4; ++i) yacc[mt][j][i] = 0.f;
 
-  const uint32_t* wp = p.qw + (size_t)t * N + c0 + 4 * g;          // + 4*step*N
-  const __half* xp0 = p.x + (size_t)g * K + 8 * t;                  // + 32*step
-  const bool xok0 = g < p.M, xok1 = (g + 8) < p.M;
-
-  int cur_grp = -1;
-  uint2 sc = make_uint2(0, 0), zh = make_uint2(0, 0);
-  uint32_t zw = 0;
-
-  auto flush = [&]() {
-    // columns 4g..4g+3: scales as 4 halves, zero points as nibbles 4(g&1).. of the qzeros word
-    const __half2 s01 = as_h2(sc.x), s23 = as_h2(sc.y);
-    const float s[4] = {__low2float(s01), __high2float(s01), __low2float(s23), __high2float(s23)};
+  // y += s * (acc - (1024 + z + 1) * xsum) for the group whose scales sit in row `grow` of the stage;
+  // c / co are the raw MMA sums, one set per k-step parity so consecutive MMAs never wait on each other
+  auto flush = [&](const unsigned char* stg, int grow, float (&c)[MT][2][2][4], float (&co)[MT][2][4], int chunk) {
+    const uint2 sc = *reinterpret_cast<const uint2*>(stg + GEMV_BOX_BYTES + grow * 64 + 8 * g);
+    const float2 s01 = __half22float2(as_h2(sc.x)), s23 = __half22float2(as_h2(sc.y));
+    const float s[4] = {s01.x, s01.y, s23.x, s23.y};
     float zz[4], zf[4];
     if (!p.v1) {
+      const uint32_t zw = *reinterpret_cast<const uint32_t*>(stg + GEMV_BOX_BYTES + GEMV_SC_BYTES + grow * 16 + 4 * (g >> 1));
+      const uint32_t zb = zw >> (16 * (g & 1));
+      // 1024 + z through the fp16 exponent trick: (z | 0x6400) is 1024 + z exactly
+      const float2 za = __half22float2(as_h2(((zb & 0xFu) | ((zb & 0xF0u) << 12)) | 0x64006400u));
+      const float2 zc = __half22float2(as_h2((((zb >> 8) & 0xFu) | ((zb & 0xF000u) << 4)) | 0x64006400u));
+      const float off = XS ? -1023.f : 1.f;              // XS: plain z + 1, the offsets are in the table
+      zz[0] = za.x + off; zz[1] = za.y + off; zz[2] = zc.x + off; zz[3] = zc.y + off;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) { zz[i] = 1025.f + (float)((zw >> (16 * (g & 1) + 4 * i)) & 0xF); zf[i] = 0.f; }
-    } else {          // W = s*q - zero: only the 1024 offset scales with s, the float zero does not
-      const __half2 z01 = as_h2(zh.x), z23 = as_h2(zh.y);
-      zf[0] = __low2float(z01); zf[1] = __high2float(z01); zf[2] = __low2float(z23); zf[3] = __high2float(z23);
+      for (int i = 0; i < 4; ++i) zf[i] = 0.f;
+    } else {          // W = s*q - zero: only the offsets scale with s, the float zero does not
+      const uint2 zh = *reinterpret_cast<const uint2*>(stg + GEMV_BOX_BYTES + GEMV_SC_BYTES + 8 * g);
+      const float2 z01 = __half22float2(as_h2(zh.x)), z23 = __half22float2(as_h2(zh.y));
+      zf[0] = z01.x; zf[1] = z01.y; zf[2] = z23.x; zf[3] = z23.y;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) zz[i] = 1024.f;
+      for (int i = 0; i < 4; ++i) zz[i] = XS ? 0.f : 1024.f;
     }
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt) {
+      float xs0, xs1, of0 = 0.f, of1 = 0.f;
+      if constexpr (XS) {
+        // table entry of batch column b: (1024*sum_even + 64*sum_odd, sum_even + sum_odd) of x over the chunk
+        const float4 e = *reinterpret_cast<const float4*>(ctab + (size_t)chunk * 8 + 2 * t);
+        of0 = e.x; xs0 = e.y; of1 = e.z; xs1 = e.w;
+      } else {
+        xs0 = co[mt][0][0] + co[mt][1][0]; xs1 = co[mt][0][1] + co[mt][1][1];
+      }
 #pragma unroll
       for (int j = 0; j < 2; ++j)
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int col = 2 * j + (i >> 1);
-          float v = fmaf(s[col], fmaf(-zz[col], co[mt][i & 1], c[mt][j][i]), yacc[mt][j][i]);
-          yacc[mt][j][i] = fmaf(-zf[col], co[mt][i & 1], v);
-          c[mt][j][i] = 0.f;
+          const float xs = (i & 1) ? xs1 : xs0, of = (i & 1) ? of1 : of0;
+          float v = fmaf(s[col], fmaf(-zz[col], xs, c[mt][j][0][i] + c[mt][j][1][i] - of), yacc[mt][j][i]);
+          yacc[mt][j][i] = p.v1 ? fmaf(-zf[col], xs, v) : v;
         }
-#pragma unroll
-      for (int i = 0; i < 4; ++i) co[mt][i] = 0.f;
     }
   };
 
-  for (int s0 = sb + 4 * warp; s0 < se; s0 += 4 * GEMV_WARPS) {
-    uint4 wv[4], xv[MT][4];
+  // End of this CTA's run of boxes [seg_first, seg_last] in column tile `tile`.  Every warp leaves
+  // its sums in red[buf]; only the last consumer warp waits for the others, adds the 16 partials
+  // in warp order and either stores y (the run covers the whole tile) or hands the tile's partial
+  // to the last CTA to arrive.  The other warps go straight on to the next tile.
+  //   named barrier 1+buf: "red[buf] is complete"   (15 warps arrive, the reducer syncs)
+  //   named barrier 3+buf: "red[buf] may be reused" (the reducer arrives, 15 warps sync two tiles later)
+  auto finish_tile = [&](int tile, int seq, int seg_first, int seg_last) {
+    const int buf = seq & 1;
+    float* mine = red + (size_t)buf * RED_FLOATS;
+    const bool reducer = warp == GEMV_CWARPS - 1;
+    if (!reducer && seq >= 2) named_bar_sync(3 + buf, GEMV_CONSUMERS);
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int step = s0 + i;
-      if (step < se) {
-        wv[i] = ldg_stream(wp + (size_t)(4 * step) * N);
+    for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-          const bool ok = mt ? xok1 : xok0;
-          xv[mt][i] = ok ? __ldg(reinterpret_cast<const uint4*>(xp0 + (size_t)(8 * mt) * K + 32 * step))
-                         : make_uint4(0, 0, 0, 0);
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int col = 4 * g + 2 * j + (i >> 1), b = mt * 8 + 2 * t + (i & 1);
+          mine[(warp * (MT * 8) + b) * GEMV_TN + col] = yacc[mt][j][i];
+          yacc[mt][j][i] = 0.f;
         }
-      } else {
-        wv[i] = make_uint4(0, 0, 0, 0);
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) xv[mt][i] = make_uint4(0, 0, 0, 0);
-      }
+    if (!reducer) {
+      __threadfence_block();
+      named_bar_arrive(1 + buf, GEMV_CONSUMERS);
+      return;
     }
+    named_bar_sync(1 + buf, GEMV_CONSUMERS);
+    const int tc0 = tile * GEMV_TN, col = lane;
+    const bool whole = seg_first == 0 && seg_last == bpt - 1;
+    const int c_first = box_owner((long long)tile * bpt, G, nb), c_last = box_owner((long long)tile * bpt + bpt - 1, G, nb);
+    // slot 0 of a CTA's partials: the run continues a tile begun by an earlier CTA; slot 1: it begins the tile
+    float* part = sp.cta_part + ((size_t)blockIdx.x * 2 + (seg_first == 0 ? 1 : 0)) * (MT * 8) * GEMV_TN;
+    for (int r = 0; r < p.M; ++r) {
+      float v = 0.f;
 #pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const int step = s0 + i;
-      if (step >= se) break;
-      const int grp = step / steps_per_group;
-      if (grp != cur_grp) {
-        if (cur_grp >= 0) flush();
-        cur_grp = grp;
-        sc = __ldg(reinterpret_cast<const uint2*>(p.scales + (size_t)grp * N + c0 + 4 * g));
-        if (!p.v1) zw = __ldg(p.qzeros + (size_t)grp * (N >> 3) + ((c0 + 4 * g) >> 3));
-        else zh = __ldg(reinterpret_cast<const uint2*>(reinterpret_cast<const __half*>(p.qzeros) + c0 + 4 * g));
-      }
-      const uint32_t w[4] = {wv[i].x, wv[i].y, wv[i].z, wv[i].w};
-      uint32_t pr[4][4];                      // pr[word][m] = (q_m, q_m+4) + 1024
+      for (int w = 0; w < GEMV_CWARPS; ++w) v += mine[(w * (MT * 8) + r) * GEMV_TN + col];
+      if (whole) store_y(p, r, tc0 + col, v);
+      else __stcg(part + r * GEMV_TN + col, v);
+    }
+    named_bar_arrive(3 + buf, GEMV_CONSUMERS);
+    if (whole) return;
+    __threadfence();
+    __syncwarp();
+    unsigned last = 0;
+    if (lane == 0) last = atomicAdd(p.counters + tile, 1u) == (unsigned)(c_last - c_first);
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (!last) return;
+    __threadfence();
+    for (int r = 0; r < p.M; ++r) {
+      float v = 0.f;
+      for (int cc = c_first; cc <= c_last; ++cc)
+        v += __ldcg(sp.cta_part + ((size_t)cc * 2 + (cc == c_first ? 1 : 0)) * (MT * 8) * GEMV_TN + r * GEMV_TN + col);
+      store_y(p, r, tc0 + col, v);
+    }
+    if (lane == 0) p.counters[tile] = 0u;                // ready for the next launch
+  };
+
+  if (threadIdx.x == 0) trace_mark(sp.trace, 0);
+  pdl_wait();                                            // x, y and the workspace belong to the stream order
+  if (threadIdx.x == 0) trace_mark(sp.trace, 1);
+  if constexpr (XS) {
+    const int blocks_per_row = K >> 3;                   // 8-element blocks per x row, 16 per 128-row chunk
+    if (threadIdx.x < 4) reinterpret_cast<uint32_t*>(xs_base)[threadIdx.x] = 0u;
+    for (int idx = threadIdx.x; idx < (K >> 7) * 8; idx += GEMV_CONSUMERS)
+      if ((idx & 7) >= p.M) ctab[idx] = make_float2(0.f, 0.f);
+    for (int idx = threadIdx.x; idx < p.M * blocks_per_row; idx += GEMV_CONSUMERS) {
+      const int m = idx / blocks_per_row, blk = idx - m * blocks_per_row;
+      const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)m * K + 8 * blk));
+      const __half2 h01 = as_h2(v.x), h23 = as_h2(v.y), h45 = as_h2(v.z), h67 = as_h2(v.w);
+      const __half2 sixteenth = as_h2(0x2C002C00u);
+      const __half2 e04 = __lows2half2(h01, h45), o15 = __hmul2(__highs2half2(h01, h45), sixteenth);
+      const __half2 e26 = __lows2half2(h23, h67), o37 = __hmul2(__highs2half2(h23, h67), sixteenth);
+      *reinterpret_cast<uint4*>(xs_buf + (size_t)m * K + 8 * blk) = make_uint4(as_u32(e04), as_u32(o15), as_u32(e26), as_u32(o37));
+      const float2 f01 = __half22float2(h01), f23 = __half22float2(h23), f45 = __half22float2(h45), f67 = __half22float2(h67);
+      float se = (f01.x + f23.x) + (f45.x + f67.x), so = (f01.y + f23.y) + (f45.y + f67.y);
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {
-        pr[q][0] = (w[q] & 0x000F000Fu) | 0x64006400u;
-        pr[q][1] = ((w[q] >> 4) & 0x000F000Fu) | 0x64006400u;
-        pr[q][2] = ((w[q] >> 8) & 0x000F000Fu) | 0x64006400u;
-        pr[q][3] = ((w[q] >> 12) & 0x000F000Fu) | 0x64006400u;
-      }
+      for (int d = 8; d >= 1; d >>= 1) { se += __shfl_xor_sync(0xffffffffu, se, d); so += __shfl_xor_sync(0xffffffffu, so, d); }
+      // the odd elements sit in x' as x/16, so their 1024 offset comes back as 64 * x
+      if ((lane & 15) == 0) ctab[(size_t)(blk >> 4) * 8 + m] = make_float2(1024.f * se + 64.f * so, se + so);
+    }
+    named_bar_sync(5, GEMV_CONSUMERS);
+  }
+  uint4 xn[MT][4];
+  auto load_x = [&](int bxt) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      const int stp = bxt * GEMV_BOX_STEPS + 4 * slot + u;
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
-        const uint4 xq = xv[mt][i];             // x[k..k+7] of batch row g (+8)
-        const uint32_t xb[4] = {prmt(xq.x, xq.z, 0x5410), prmt(xq.x, xq.z, 0x7632),    // (x0,x4) (x1,x5)
-                                prmt(xq.y, xq.w, 0x5410), prmt(xq.y, xq.w, 0x7632)};   // (x2,x6) (x3,x7)
-#pragma unroll
-        for (int ks = 0; ks < 2; ++ks) {
-          const uint32_t b0 = xb[2 * ks], b1 = xb[2 * ks + 1];
-          mma16816(c[mt][0], pr[0][2 * ks], pr[1][2 * ks], pr[0][2 * ks + 1], pr[1][2 * ks + 1], b0, b1);
-          mma16816(c[mt][1], pr[2][2 * ks], pr[3][2 * ks], pr[2][2 * ks + 1], pr[3][2 * ks + 1], b0, b1);
-          mma16816(co[mt], 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, b0, b1);
-        }
+        const bool ok = (mt ? xok1 : xok0) && stp < sp.steps_per_tile;
+        if constexpr (XS)
+          xn[mt][u] = ok ? *reinterpret_cast<const uint4*>(xs_buf + (size_t)g * K + 8 * t + 32 * stp)
+                         : *reinterpret_cast<const uint4*>(xs_base);
+        else
+          xn[mt][u] = ok ? __ldg(reinterpret_cast<const uint4*>(xrow + (size_t)(8 * mt) * K + 32 * stp))
+                         : make_uint4(0, 0, 0, 0);
       }
     }
+  };
+  // This warp owns the boxes b0 + phase, b0 + phase + 4, ...; walk them tile by tile.
+  int i = b0 + phase;                                    // next owned box (global index)
+  const int tile_first = b0 / bpt, tile_last = (b1 - 1) / bpt;
+  int bx = i - tile_first * bpt;                         // may run past bpt: brought back per tile below
+  if (i < b1) load_x(bx % bpt);
+  int nbox = 0;
+  for (int tile = tile_first; tile <= tile_last; ++tile, bx -= bpt) {
+    const int seg_b1 = min(b1, (tile + 1) * bpt);
+    for (; i < seg_b1; i += GEMV_PHASES, bx += GEMV_PHASES, ++nbox) {
+      const int it = i - b0, st = it % GEMV_STAGES, use = it / GEMV_STAGES;
+      // x of this warp's four steps (rows 16*slot .. 16*slot+15 of the box) was requested one owned
+      // box ago; request the next one now so that its latency hides behind this box's math
+      uint4 xv[MT][4];
+      int step[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        step[u] = bx * GEMV_BOX_STEPS + 4 * slot + u;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) xv[mt][u] = xn[mt][u];
+      }
+      if (i + GEMV_PHASES < b1) {
+        int bxn = bx + GEMV_PHASES;
+        while (bxn >= bpt) bxn -= bpt;
+        load_x(bxn);
+      }
+      if (!mbar_wait_warp(&full[st], use & 1, flags[0] ? 4u : 20000u)) {
+        flags[0] = 1; atomicExch(sp.status, Q4_STATUS_WAIT_EXPIRED);
+      }
+      if (threadIdx.x == 0) trace_mark(sp.trace, 2 + 2 * nbox);
+      const unsigned char* stg = smem + (size_t)st * GEMV_STAGE_BYTES;
+      const uint32_t* box = reinterpret_cast<const uint32_t*>(stg);
+      const int grp0 = p.v1 ? 0 : (sp.group_shift >= 0 ? ((bx * GEMV_BOX_STEPS) >> sp.group_shift) : (bx * GEMV_BOX_ROWS * 8) / gs);
+      uint4 wv[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        wv[u] = *reinterpret_cast<const uint4*>(box + (4 * (4 * slot + u) + t) * GEMV_TN + 4 * g);
+      float c[MT][2][2][4], co[MT][2][4];
+      int cur_grp = -1;
+      bool fresh = true;
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (step[u] >= sp.steps_per_tile) break;         // rows past K were zero-filled by TMA
+        if (!FAST) {
+          const int grp = sp.group_shift >= 0 ? (step[u] >> sp.group_shift) : step[u] / steps_per_group;
+          if (grp != cur_grp) {
+            if (cur_grp >= 0) flush(stg, cur_grp - grp0, c, co, 0);
+            cur_grp = grp; fresh = true;
+          }
+        }
+        const uint32_t w[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
+        uint32_t pr[4][4];                      // pr[word][m] = (q_m, q_m+4) + 1024  (XS, odd m: 16 q + 1024)
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          if constexpr (XS) {
+            const uint32_t w8 = w[q] >> 8;
+            pr[q][0] = (w[q] & 0x000F000Fu) | 0x64006400u;
+            pr[q][1] = (w[q] & 0x00F000F0u) | 0x64006400u;
+            pr[q][2] = (w8 & 0x000F000Fu) | 0x64006400u;
+            pr[q][3] = (w8 & 0x00F000F0u) | 0x64006400u;
+          } else {
+            pr[q][0] = (w[q] & 0x000F000Fu) | 0x64006400u;
+            pr[q][1] = ((w[q] >> 4) & 0x000F000Fu) | 0x64006400u;
+            pr[q][2] = ((w[q] >> 8) & 0x000F000Fu) | 0x64006400u;
+            pr[q][3] = ((w[q] >> 12) & 0x000F000Fu) | 0x64006400u;
+          }
+        }
+        const bool first = FAST ? (u == 0) : fresh;
+#pragma unroll
+        for (int mt = 0; mt < MT; ++mt) {
+          const uint4 xq = xv[mt][u];             // x[k..k+7] of batch row g (+8); XS: already in MMA order
+          uint32_t xb[4];
+          if constexpr (XS) {
+            xb[0] = xq.x; xb[1] = xq.y; xb[2] = xq.z; xb[3] = xq.w;
+          } else {
+            xb[0] = prmt(xq.x, xq.z, 0x5410); xb[1] = prmt(xq.x, xq.z, 0x7632);    // (x0,x4) (x1,x5)
+            xb[2] = prmt(xq.y, xq.w, 0x5410); xb[3] = prmt(xq.y, xq.w, 0x7632);    // (x2,x6) (x3,x7)
+          }
+#pragma unroll
+          for (int ks = 0; ks < 2; ++ks) {
+            const uint32_t bb0 = xb[2 * ks], bb1 = xb[2 * ks + 1];
+            if (first) {
+              mma16816_first(c[mt][0][ks], pr[0][2 * ks], pr[1][2 * ks], pr[0][2 * ks + 1], pr[1][2 * ks + 1], bb0, bb1);
+              mma16816_first(c[mt][1][ks], pr[2][2 * ks], pr[3][2 * ks], pr[2][2 * ks + 1], pr[3][2 * ks + 1], bb0, bb1);
+              if constexpr (!XS) mma16816_first(co[mt][ks], 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, bb0, bb1);
+            } else {
+              mma16816(c[mt][0][ks], pr[0][2 * ks], pr[1][2 * ks], pr[0][2 * ks + 1], pr[1][2 * ks + 1], bb0, bb1);
+              mma16816(c[mt][1][ks], pr[2][2 * ks], pr[3][2 * ks], pr[2][2 * ks + 1], pr[3][2 * ks + 1], bb0, bb1);
+              if constexpr (!XS) mma16816(co[mt][ks], 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, bb0, bb1);
+            }
+          }
+        }
+        fresh = false;
+      }
+      // scales live in this stage: settle the open group before the slot is released
+      if (FAST) {
+        if (step[0] < sp.steps_per_tile)
+          flush(stg, p.v1 ? 0 : ((sp.group_shift >= 0 ? (step[0] >> sp.group_shift) : step[0] / steps_per_group) - grp0), c, co, step[0] >> 2);
+      } else if (cur_grp >= 0) {
+        flush(stg, cur_grp - grp0, c, co, 0);
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[st]);
+      if (threadIdx.x == 0) trace_mark(sp.trace, 3 + 2 * nbox);
+    }
+    if (threadIdx.x == 0) trace_mark(sp.trace, 30);
+    finish_tile(tile, tile - tile_first, max(b0, tile * bpt) - tile * bpt, seg_b1 - 1 - tile * bpt);
+    if (threadIdx.x == 0) trace_mark(sp.trace, 31);
   }
-  if (cur_grp >= 0) flush();
-  gemv_reduce_store<MT>(p, red, yacc, c0, split);
 }
 
 // ---- act-order (group of row k = g_idx[k]) -------------------------------------------------------
@@ -331,15 +606,51 @@ static void gemv_plan(int K, int N, int& S, int& steps_per_split) {
   S = (steps + steps_per_split - 1) / steps_per_split;
 }
 
+static unsigned long long* g_trace = nullptr;                 // set by q4_gemv_set_trace
+
+constexpr size_t GEMV_STATUS_OFFSET = GEMV_WS_HEAD - 4;      // status word: last 4 bytes of the head
+constexpr int GEMV_MAX_CTAS = 512;                            // upper bound on SMs for workspace sizing
+
+template <int MT, bool FAST, bool XS>
+static int launch_stream(const CUtensorMap& map, const CUtensorMap& smap, const CUtensorMap& zmap,
+                         const GemvStreamParams& sp, int grid, cudaStream_t st) {
+  static bool attr_done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  // XS adds: 16 B of zeros, the chunk table (at most 16 KiB) and x itself; sized for the worst case so that the
+  // attribute is set once
+  const size_t smem = gemv_stream_smem<MT>() + (XS ? 16 + 16384 + GEMV_XS_MAX_BYTES : 0);
+  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+    if (int e = check_cuda(cudaFuncSetAttribute(gemv_stream_kernel<MT, FAST, XS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                           "gemv smem attribute")) return e;
+    attr_done[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(GEMV_STREAM_THREADS);
+  cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  return check_cuda(cudaLaunchKernelEx(&cfg, gemv_stream_kernel<MT, FAST, XS>, map, smap, zmap, sp), "gemv launch");
+}
+
 }  // namespace q4
 
 using namespace q4;
+
+extern "C" int q4_gemv_set_trace(void* device_buffer) {
+  g_trace = (unsigned long long*)device_buffer;
+  return Q4_OK;
+}
 
 extern "C" size_t q4_gemv_workspace_bytes(int M, int K, int N) {
   if (M <= 0 || K <= 0 || N <= 0 || K % 32 || N % 32) return 0;
   int S, sps;
   gemv_plan(K, N, S, sps);
-  return GEMV_WS_HEAD + (S > 1 ? (size_t)S * M * N * sizeof(float) : 0);
+  const size_t split = S > 1 ? (size_t)S * M * N * sizeof(float) : 0;           // act-order kernel
+  const size_t stream = (size_t)GEMV_MAX_CTAS * 2 * 16 * GEMV_TN * sizeof(float); // streaming kernel
+  return GEMV_WS_HEAD + (split > stream ? split : stream);
 }
 
 extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const void* scales,
@@ -363,6 +674,12 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
   if (!aligned16(x) || !aligned16(qweight) || !aligned16(scales) || (act && !aligned16(g_idx)))
     return fail(Q4_E_ALIGN, "gemv: x/qweight/scales/g_idx must be 16-byte aligned");
   if ((K * 2) % 16) return fail(Q4_E_ALIGN, "gemv: row pitch of x must be a multiple of 16 bytes");
+  const size_t need = q4_gemv_workspace_bytes(M, K, N);
+  if (!workspace || workspace_bytes < need)
+    return fail(Q4_E_WORKSPACE, "gemv: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
+  if (!aligned16(workspace)) return fail(Q4_E_ALIGN, "gemv: workspace must be 16-byte aligned");
+  if ((size_t)(N / GEMV_TN) * sizeof(unsigned) > GEMV_STATUS_OFFSET)
+    return fail(Q4_E_SHAPE, "gemv: N=%d has more column tiles than the workspace head holds", N);
   if (int e = check_device()) return e;
 
   GemvParams p;
@@ -372,34 +689,59 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
   p.steps_total = K / 32;
   gemv_plan(K, N, p.S, p.steps_per_split);
   p.y_f32 = (y_dtype == Q4_F32); p.accumulate = (flags & Q4_GEMV_ACCUMULATE) ? 1 : 0; p.v1 = v1 ? 1 : 0;
-  const size_t need = q4_gemv_workspace_bytes(M, K, N);
-  if (p.S > 1) {
-    if (!workspace || workspace_bytes < need)
-      return fail(Q4_E_WORKSPACE, "gemv: workspace of %zu bytes needed, %zu given", need, workspace_bytes);
-    if (!aligned16(workspace)) return fail(Q4_E_ALIGN, "gemv: workspace must be 16-byte aligned");
-    if ((size_t)(N / GEMV_TN) * sizeof(unsigned) > GEMV_WS_HEAD)
-      return fail(Q4_E_SHAPE, "gemv: N=%d has more column tiles than the workspace head holds", N);
-    p.counters = (unsigned*)workspace;
-    p.part = (float*)((char*)workspace + GEMV_WS_HEAD);
-  } else {
-    p.counters = nullptr; p.part = nullptr;
-  }
-  const dim3 grid(N / GEMV_TN, p.S), block(GEMV_THREADS);
+  p.counters = (unsigned*)workspace;
+  p.part = (float*)((char*)workspace + GEMV_WS_HEAD);
   cudaStream_t st = (cudaStream_t)stream;
+  const int MT = M <= 8 ? 1 : 2;
+
   if (!act) {
-    if (M <= 8) gemv_seq_kernel<1><<<grid, block, 0, st>>>(p);
-    else gemv_seq_kernel<2><<<grid, block, 0, st>>>(p);
-  } else {
-    const int MT = M <= 8 ? 1 : 2;
-    const size_t smem = sizeof(float) * GEMV_WARPS * MT * 8 * GEMV_TN + (size_t)G * GEMV_TN * sizeof(__half2);
-    if (smem > 200 * 1024) return fail(Q4_E_SHAPE, "gemv: act-order tables for G=%d groups do not fit shared memory", G);
-    if (MT == 1) {
-      if (int e = check_cuda(cudaFuncSetAttribute(gemv_act_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "gemv smem attr")) return e;
-      gemv_act_kernel<1><<<grid, block, smem, st>>>(p, G);
+    GemvStreamParams sp;
+    sp.g = p;
+    sp.steps_per_tile = K / 32;
+    sp.boxes_per_tile = (K / 8 + GEMV_BOX_ROWS - 1) / GEMV_BOX_ROWS;
+    sp.total_boxes = sp.boxes_per_tile * (N / GEMV_TN);
+    sp.cta_part = p.part;
+    sp.status = (unsigned*)((char*)workspace + GEMV_STATUS_OFFSET);
+    sp.trace = g_trace;
+    sp.group_shift = -1;
+    for (int sh = 0; sh < 20; ++sh) if ((groupsize >> 5) == (1 << sh)) sp.group_shift = sh;
+    int grid = sm_count();
+    if (grid > GEMV_MAX_CTAS) grid = GEMV_MAX_CTAS;
+    if (grid > sp.total_boxes) grid = sp.total_boxes;
+    // group rows one box (512 k-rows) can touch, counting a straddled group at either end
+    sp.meta_rows = v1 ? 1 : (GEMV_BOX_ROWS * 8 + groupsize - 1) / groupsize + ((GEMV_BOX_ROWS * 8) % groupsize ? 1 : 0);
+    if (sp.meta_rows > GEMV_META_ROWS) return fail(Q4_E_SHAPE, "gemv: groupsize=%d too small", groupsize);
+    if (!aligned16(qzeros)) return fail(Q4_E_ALIGN, "gemv: qzeros must be 16-byte aligned");
+    CUtensorMap map, smap, zmap;
+    if (int e = make_tmap_2d(&map, qweight, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, (uint64_t)N, (uint64_t)(K / 8),
+                             (uint64_t)N * 4, GEMV_TN, GEMV_BOX_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
+    if (int e = make_tmap_2d(&smap, scales, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (uint64_t)N, (uint64_t)G,
+                             (uint64_t)N * 2, GEMV_TN, sp.meta_rows, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
+    if (!v1) {
+      if (int e = make_tmap_2d(&zmap, qzeros, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, (uint64_t)(N / 8), (uint64_t)G,
+                               (uint64_t)(N / 8) * 4, GEMV_TN / 8, sp.meta_rows, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
+      sp.stage_tx = GEMV_BOX_BYTES + sp.meta_rows * (GEMV_TN * 2 + GEMV_TN / 2);
     } else {
-      if (int e = check_cuda(cudaFuncSetAttribute(gemv_act_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "gemv smem attr")) return e;
-      gemv_act_kernel<2><<<grid, block, smem, st>>>(p, G);
+      if (int e = make_tmap_2d(&zmap, qzeros, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (uint64_t)N, 1,
+                               (uint64_t)N * 2, GEMV_TN, 1, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
+      sp.stage_tx = GEMV_BOX_BYTES + 2 * GEMV_TN * 2;
     }
+    const bool fast = v1 || groupsize % 128 == 0;
+    const bool xs = fast && MT == 1 && K % 128 == 0 && (size_t)M * K * 2 <= (size_t)GEMV_XS_MAX_BYTES && K / 128 * 64 <= 16384;
+    if (xs) return launch_stream<1, true, true>(map, smap, zmap, sp, grid, st);
+    if (MT == 1) return fast ? launch_stream<1, true, false>(map, smap, zmap, sp, grid, st) : launch_stream<1, false, false>(map, smap, zmap, sp, grid, st);
+    return fast ? launch_stream<2, true, false>(map, smap, zmap, sp, grid, st) : launch_stream<2, false, false>(map, smap, zmap, sp, grid, st);
+  }
+
+  const dim3 grid(N / GEMV_TN, p.S), block(GEMV_THREADS);
+  const size_t smem = sizeof(float) * GEMV_WARPS * MT * 8 * GEMV_TN + (size_t)G * GEMV_TN * sizeof(__half2);
+  if (smem > 200 * 1024) return fail(Q4_E_SHAPE, "gemv: act-order tables for G=%d groups do not fit shared memory", G);
+  if (MT == 1) {
+    if (int e = check_cuda(cudaFuncSetAttribute(gemv_act_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "gemv smem attr")) return e;
+    gemv_act_kernel<1><<<grid, block, smem, st>>>(p, G);
+  } else {
+    if (int e = check_cuda(cudaFuncSetAttribute(gemv_act_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "gemv smem attr")) return e;
+    gemv_act_kernel<2><<<grid, block, smem, st>>>(p, G);
   }
   return check_cuda(cudaGetLastError(), "gemv launch");
 }

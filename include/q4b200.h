@@ -87,6 +87,11 @@ int q4_gemv(const void* x, const int32_t* qweight, void* y, const void* scales,
             int M, int K, int N, int G, int groupsize, int y_dtype, unsigned flags,
             void* workspace, size_t workspace_bytes, q4_stream_t stream);
 
+/* Profiling aid: when `device_buffer` is non-NULL, every CTA of the sequential-group decode kernel
+ * writes SM cycle counters at fixed points of its life into 64 uint64 slots (buffer of at least
+ * 64 * 8 * number-of-SMs bytes).  NULL switches the trace off (the default). */
+int q4_gemv_set_trace(void* device_buffer);
+
 #ifdef __cplusplus
 }
 #endif
