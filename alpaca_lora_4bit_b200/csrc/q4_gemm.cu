@@ -1,0 +1,378 @@
+// Large-M products over a packed int4 layer without materialising W in global memory:
+//   forward   y [M, N] = x  [M, K] * W        (AutogradMatmul4bit forward,  autograd_4bit.py:34-43)
+//   backward  dx[M, K] = dy [M, N] * W^T      (AutogradMatmul4bit backward, autograd_4bit.py:45-54)
+// The reference reconstructs W into a dense fp16 [K, N] buffer and calls cuBLAS
+// (matmul_utils_4bit.py:114-127).  Here each CTA dequantises the tiles of W it needs straight into
+// shared memory, bit-exactly as the reference reconstruct does (rn(rn(s*q) - rn(s*(z+1)))), in
+// the layout the 5th-generation tensor core reads, and tcgen05.mma accumulates in TMEM.
+//
+// One CTA computes a 128 x 128 output tile.  Roles (192 threads):
+//   warp 0      TMA producer: activation tiles [128 rows x 64 contraction] fp16, 128B-swizzled
+//   warp 1      owns TMEM (128 fp32 columns) and issues tcgen05.mma (one elected thread)
+//   warps 2-5   dequantise W into the stage's B buffer, then run the epilogue (one TMEM lane
+//               quarter each): tcgen05.ld -> (+bias) -> fp16 -> global
+// A stage holds 16 KiB of activations and 16 KiB of dequantised W:
+//   forward   B = W[k0:k0+64, n0:n0+128], two panels of [64 k-rows][64 n = 128 B], MN-major operand
+//   backward  B = W[k0:k0+128, n0:n0+64], one panel of [128 k-rows][64 n = 128 B], K-major operand
+// Both are the same bytes: rows of 64 consecutive n for one k, 16-byte chunks XOR-swizzled with
+// the row index (the 128B swizzle pattern), so one dequant routine serves both directions: a
+// thread takes 8 packed words (8 k-rows x 8 columns) and writes eight 16-byte chunks.
+// Scales and rn(s*(z+1)) come from shared-memory tables (forward: all groups x the CTA's 128
+// columns, built once) or, in the backward, from global memory per row with reuse while the group
+// stays the same.  Act-order is free in this scheme: the group of every row is read from g_idx.
+// Every mbarrier wait is bounded: on expiry the kernel records a status word and stops waiting.
+#include "q4_async.cuh"
+
+namespace q4 {
+
+__device__ unsigned g_gemm_status = 0;        // Q4_STATUS_WAIT_EXPIRED if any bounded wait gave up
+
+constexpr int GM_TILE_M = 128;
+constexpr int GM_TILE_N = 128;                // output columns per CTA
+constexpr int GM_TILE_C = 64;                 // contraction elements per stage
+constexpr int GM_STAGES = 4;
+constexpr int GM_A_BYTES = GM_TILE_M * GM_TILE_C * 2;     // 16 KiB
+constexpr int GM_B_BYTES = 128 * 64 * 2;                  // 16 KiB
+constexpr int GM_STAGE_BYTES = GM_A_BYTES + GM_B_BYTES;
+constexpr int GM_THREADS = 192;
+constexpr int GM_DEQ_THREADS = 128;
+constexpr uint32_t GM_WAIT_TRIES = 40000;     // x ~2 us sleeping tries
+
+struct GemmParams {
+  const uint32_t* qw;       // [K/8, N]
+  const __half* scales;     // [G, N]
+  const uint32_t* qzeros;   // [G, N/8]
+  const int* g_idx;         // [K]
+  const __half* bias;       // [N_out] or null (forward only)
+  __half* out;              // [M, N_out]
+  int M, K, N, G;
+  int n_contract_tiles;     // contraction length / 64
+};
+
+// ---- tcgen05 wrappers --------------------------------------------------------------------------
+__device__ __forceinline__ void tmem_alloc(uint32_t* smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+__device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrives on `bar` when all tcgen05.mma issued so far by this thread have completed.
+__device__ __forceinline__ void umma_commit(uint64_t* bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+// 32 lanes x 32 consecutive fp32 columns: thread i of the warp gets row (lane base + i).
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+      : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]),
+        "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]),
+        "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]),
+        "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+      : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Shared-memory matrix descriptor, 128B swizzle: start address, leading / stride byte offsets
+// (all in 16-byte units), descriptor version 1 (sm_100), layout type 2 (SWIZZLE_128B).
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr >> 4) & 0x3FFFu);
+  d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// Instruction descriptor for kind::f16: D fp32, A/B fp16, A K-major, B K-major or MN-major, M x N.
+__host__ __device__ constexpr uint32_t idesc_f16(int m, int n, bool b_mn_major) {
+  return (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | ((b_mn_major ? 1u : 0u) << 16) |
+         ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  const uint32_t lim = *abort_flag ? 4u : GM_WAIT_TRIES;
+  for (uint32_t i = 0; i < lim; ++i)
+    if (mbar_try_wait_sleep(bar, parity, 2000u)) return true;
+  *abort_flag = 1;
+  atomicExch(&g_gemm_status, Q4_STATUS_WAIT_EXPIRED);
+  return false;
+}
+
+// Dequantise 8 packed words (8 k-rows x 8 adjacent columns) and write the eight 16-byte chunks
+// into a [rows][128 B] panel with the 128B swizzle.  `s`/`zp` give scale and rn(s*(z+1)) of the 8
+// columns for each of the 8 rows (as four half2 each).
+template <int J, int BYTE, bool ODD>
+__device__ __forceinline__ void deq_row(unsigned char* panel_rows8, int chunk, const uint32_t (&w)[8],
+                                        const uint4& s, const uint4& zp) {
+  const uint32_t sv[4] = {s.x, s.y, s.z, s.w}, zv[4] = {zp.x, zp.y, zp.z, zp.w};
+  uint4 o;
+  uint32_t* ov = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    const __half2 q = nibble_pair<BYTE, ODD>(w[2 * c], w[2 * c + 1]);
+    ov[c] = as_u32(__hsub2_rn(__hmul2_rn(as_h2(sv[c]), q), as_h2(zv[c])));
+  }
+  *reinterpret_cast<uint4*>(panel_rows8 + J * 128 + ((chunk ^ J) << 4)) = o;
+}
+
+// rn(s * (z+1)) for 8 adjacent columns from their scales and the packed zero-point word.
+__device__ __forceinline__ uint4 zero_terms(const uint4& s, uint32_t zw) {
+  const uint32_t sv[4] = {s.x, s.y, s.z, s.w};
+  uint4 o;
+  uint32_t* ov = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+  for (int c = 0; c < 4; ++c) {
+    // (z | 0x6400) = 1024 + z exactly; minus 1023 gives z + 1 exactly
+    const uint32_t pair = (((zw >> (8 * c)) & 0xFu) | (((zw >> (8 * c + 4)) & 0xFu) << 16)) | 0x64006400u;
+    const __half2 z1 = __hsub2(as_h2(pair), as_h2(0x63FE63FEu) /* 1023 */);
+    ov[c] = as_u32(__hmul2_rn(as_h2(sv[c]), z1));
+  }
+  return o;
+}
+
+template <bool TRANSPOSE>
+__global__ void __launch_bounds__(GM_THREADS, 1)
+q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const GemmParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  // 1024-byte alignment for the swizzled tiles
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  unsigned char* stages = smem;
+  uint64_t* full_a = reinterpret_cast<uint64_t*>(smem + GM_STAGES * GM_STAGE_BYTES);
+  uint64_t* full_b = full_a + GM_STAGES;
+  uint64_t* empty = full_b + GM_STAGES;
+  uint64_t* acc_full = empty + GM_STAGES;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  __half* s_tab = reinterpret_cast<__half*>(smem + GM_STAGES * GM_STAGE_BYTES + 256);     // forward: [G][128]
+  __half* zp_tab = s_tab + (size_t)p.G * GM_TILE_N;
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int out0 = blockIdx.x * GM_TILE_N;            // first output column (n forward, k backward)
+  const int m0 = blockIdx.y * GM_TILE_M;
+  const int T = p.n_contract_tiles;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < GM_STAGES; ++i) { mbar_init(&full_a[i], 1); mbar_init(&full_b[i], GM_DEQ_THREADS / 32); mbar_init(&empty[i], 1); }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&amap);
+  }
+  if (warp == 1) { tmem_alloc(tmem_slot, 128); tmem_relinquish(); }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_acc = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------- TMA producer: activation tiles ----------------
+    if (lane == 0) {
+      for (int it = 0; it < T; ++it) {
+        const int st = it % GM_STAGES, use = it / GM_STAGES;
+        if (use > 0) wait_bar(&empty[st], (use - 1) & 1, abort_flag);
+        mbar_arrive_expect_tx(&full_a[st], GM_A_BYTES);
+        tma_load_2d(stages + (size_t)st * GM_STAGE_BYTES, &amap, it * GM_TILE_C, m0, &full_a[st]);
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer ----------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = idesc_f16(GM_TILE_M, GM_TILE_N, !TRANSPOSE);
+      for (int it = 0; it < T; ++it) {
+        const int st = it % GM_STAGES, use = it / GM_STAGES;
+        wait_bar(&full_a[st], use & 1, abort_flag);
+        wait_bar(&full_b[st], use & 1, abort_flag);
+        tc_fence_after();
+        const uint32_t a_addr = smem_u32(stages + (size_t)st * GM_STAGE_BYTES);
+        const uint32_t b_addr = a_addr + GM_A_BYTES;
+#pragma unroll
+        for (int ks = 0; ks < GM_TILE_C / 16; ++ks) {
+          // A: K-major, 128-byte rows, 8-row groups 1024 B apart; 16 contraction elements = 32 B
+          const uint64_t ad = smem_desc_sw128(a_addr + ks * 32, 16, 1024);
+          // forward  B: MN-major: 64 n contiguous (128 B) per k-row, next 64 n at +8192, next 8 k-rows at +1024
+          // backward B: K-major like A
+          const uint64_t bd = TRANSPOSE ? smem_desc_sw128(b_addr + ks * 32, 16, 1024)
+                                        : smem_desc_sw128(b_addr + ks * 2048, 8192, 1024);
+          umma_f16(tmem_acc, ad, bd, idesc, (it > 0 || ks > 0) ? 1u : 0u);
+        }
+        umma_commit(&empty[st]);                   // frees the stage when these MMAs have read it
+      }
+      umma_commit(acc_full);
+    }
+  } else {
+    // ---------------- dequantisers (then epilogue) ----------------
+    const int tid = threadIdx.x - 64;                              // 0..127
+    const int chunk16 = TRANSPOSE ? (tid & 7) : (tid & 15);        // 16-byte chunk (8 columns) within the stage's n-range
+    const int r = TRANSPOSE ? (tid >> 3) : (tid >> 4);             // packed row within the stage
+    const int N = p.N;
+    if (!TRANSPOSE) {
+      // tables for the CTA's 128 columns: scale and rn(s*(z+1)) of every group
+      for (int i = tid; i < p.G * (GM_TILE_N / 8); i += GM_DEQ_THREADS) {
+        const int g = i / (GM_TILE_N / 8), c8 = i % (GM_TILE_N / 8);
+        const uint4 s = __ldg(reinterpret_cast<const uint4*>(p.scales + (size_t)g * N + out0 + 8 * c8));
+        const uint32_t zw = __ldg(p.qzeros + (size_t)g * (N >> 3) + ((out0 + 8 * c8) >> 3));
+        *reinterpret_cast<uint4*>(s_tab + (size_t)g * GM_TILE_N + 8 * c8) = s;
+        *reinterpret_cast<uint4*>(zp_tab + (size_t)g * GM_TILE_N + 8 * c8) = zero_terms(s, zw);
+      }
+      named_bar_sync(1, GM_DEQ_THREADS);
+    }
+    // packed words of the stage: rows (k0/8 + r), columns ncol0 .. ncol0+7
+    auto word_ptr = [&](int it) -> const uint32_t* {
+      const int prow = TRANSPOSE ? (out0 >> 3) + r : it * (GM_TILE_C >> 3) + r;
+      const int ncol = TRANSPOSE ? it * GM_TILE_C + 8 * chunk16 : out0 + 8 * chunk16;
+      return p.qw + (size_t)prow * N + ncol;
+    };
+    uint4 wa = ldg_stream(word_ptr(0)), wb = ldg_stream(word_ptr(0) + 4);
+    int4 ga, gb;                                                   // groups of the task's 8 k-rows
+    {
+      const int k8 = TRANSPOSE ? out0 + 8 * r : 8 * r;
+      ga = __ldg(reinterpret_cast<const int4*>(p.g_idx + k8));
+      gb = __ldg(reinterpret_cast<const int4*>(p.g_idx + k8 + 4));
+    }
+    for (int it = 0; it < T; ++it) {
+      const int st = it % GM_STAGES, use = it / GM_STAGES;
+      const uint32_t w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+      const int gi[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+      if (it + 1 < T) {                                            // prefetch the next stage's words
+        wa = ldg_stream(word_ptr(it + 1)); wb = ldg_stream(word_ptr(it + 1) + 4);
+        if (!TRANSPOSE) {
+          const int k8 = (it + 1) * GM_TILE_C + 8 * r;
+          ga = __ldg(reinterpret_cast<const int4*>(p.g_idx + k8));
+          gb = __ldg(reinterpret_cast<const int4*>(p.g_idx + k8 + 4));
+        }
+      }
+      if (use > 0 && lane == 0) wait_bar(&empty[st], (use - 1) & 1, abort_flag);
+      __syncwarp();
+      unsigned char* bst = stages + (size_t)st * GM_STAGE_BYTES + GM_A_BYTES;
+      // forward: panel (chunk16 / 8) of [64 rows][128 B]; backward: one panel of [128 rows][128 B]
+      unsigned char* rows8 = TRANSPOSE ? bst + r * 1024 : bst + (chunk16 >> 3) * 8192 + r * 1024;
+      const int cc = chunk16 & 7;
+      uint4 s, zp;
+      int cur = -1;
+      const int ncol = TRANSPOSE ? it * GM_TILE_C + 8 * chunk16 : 8 * chunk16;    // backward: global column
+#define Q4_DEQ(J, BYTE, ODD)                                                                      \
+      if (gi[J] != cur) {                                                                         \
+        cur = gi[J];                                                                              \
+        if (TRANSPOSE) {                                                                          \
+          s = __ldg(reinterpret_cast<const uint4*>(p.scales + (size_t)cur * N + ncol));           \
+          zp = zero_terms(s, __ldg(p.qzeros + (size_t)cur * (N >> 3) + (ncol >> 3)));             \
+        } else {                                                                                  \
+          s = *reinterpret_cast<const uint4*>(s_tab + (size_t)cur * GM_TILE_N + ncol);            \
+          zp = *reinterpret_cast<const uint4*>(zp_tab + (size_t)cur * GM_TILE_N + ncol);          \
+        }                                                                                         \
+      }                                                                                           \
+      deq_row<J, BYTE, ODD>(rows8, cc, w, s, zp);
+      Q4_DEQ(0, 0, false) Q4_DEQ(1, 0, true) Q4_DEQ(2, 1, false) Q4_DEQ(3, 1, true)
+      Q4_DEQ(4, 2, false) Q4_DEQ(5, 2, true) Q4_DEQ(6, 3, false) Q4_DEQ(7, 3, true)
+#undef Q4_DEQ
+      fence_async_smem();                          // generic-proxy stores -> visible to the tensor core
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&full_b[st]);
+    }
+
+    // ---------------- epilogue: TMEM -> registers -> fp16 -> global ----------------
+    if (lane == 0) wait_bar(acc_full, 0, abort_flag);
+    __syncwarp();
+    tc_fence_after();
+    const int quarter = warp & 3;                                  // TMEM lanes 32*quarter .. +31
+    const int m = m0 + 32 * quarter + lane;
+    const int n_out_total = TRANSPOSE ? p.K : p.N;
+#pragma unroll 1
+    for (int cb = 0; cb < GM_TILE_N / 32; ++cb) {
+      uint32_t v[32];
+      tmem_ld32(tmem_acc + ((uint32_t)(32 * quarter) << 16) + cb * 32, v);
+      tmem_ld_wait();
+      if (m < p.M) {
+        __half* dst = p.out + (size_t)m * n_out_total + out0 + cb * 32;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint4 o;
+          uint32_t* ov = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float f0 = __uint_as_float(v[8 * q + 2 * e]), f1 = __uint_as_float(v[8 * q + 2 * e + 1]);
+            if (!TRANSPOSE && p.bias) {
+              f0 += __half2float(p.bias[out0 + cb * 32 + 8 * q + 2 * e]);
+              f1 += __half2float(p.bias[out0 + cb * 32 + 8 * q + 2 * e + 1]);
+            }
+            ov[e] = as_u32(__floats2half2_rn(f0, f1));
+          }
+          *reinterpret_cast<uint4*>(dst + 8 * q) = o;
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_acc, 128);
+}
+
+static size_t gemm_smem_bytes(bool transpose, int G) {
+  return 1024 + (size_t)GM_STAGES * GM_STAGE_BYTES + 256 + (transpose ? 0 : (size_t)2 * G * GM_TILE_N * sizeof(__half));
+}
+
+}  // namespace q4
+
+using namespace q4;
+
+static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, void* out, const void* scales,
+                       const int32_t* qzeros, const int32_t* g_idx, const void* bias, int M, int K, int N, int G,
+                       q4_stream_t stream) {
+  if (!act || !qweight || !out || !scales || !qzeros || !g_idx) return fail(Q4_E_BADARG, "gemm: null pointer");
+  if (M <= 0 || K <= 0 || N <= 0 || G <= 0) return fail(Q4_E_BADARG, "gemm: M=%d K=%d N=%d G=%d", M, K, N, G);
+  if (K % 128 || N % 128) return fail(Q4_E_SHAPE, "gemm: K=%d and N=%d must be multiples of 128", K, N);
+  if (!aligned16(act) || !aligned16(qweight) || !aligned16(out) || !aligned16(scales) || !aligned16(g_idx))
+    return fail(Q4_E_ALIGN, "gemm: pointers must be 16-byte aligned");
+  if (int e = check_device()) return e;
+  const size_t smem = gemm_smem_bytes(transpose, G);
+  if (smem > 227 * 1024) return fail(Q4_E_SHAPE, "gemm: scale tables for G=%d groups do not fit shared memory", G);
+
+  GemmParams p;
+  p.qw = (const uint32_t*)qweight; p.scales = (const __half*)scales; p.qzeros = (const uint32_t*)qzeros;
+  p.g_idx = g_idx; p.bias = (const __half*)bias; p.out = (__half*)out;
+  p.M = M; p.K = K; p.N = N; p.G = G;
+  const int contract = transpose ? N : K, nout = transpose ? K : N;
+  p.n_contract_tiles = contract / GM_TILE_C;
+  CUtensorMap amap;
+  if (int e = make_tmap_2d(&amap, act, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)contract, (uint64_t)M,
+                           (uint64_t)contract * 2, GM_TILE_C, GM_TILE_M, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
+  const dim3 grid(nout / GM_TILE_N, (M + GM_TILE_M - 1) / GM_TILE_M), block(GM_THREADS);
+  cudaStream_t st = (cudaStream_t)stream;
+  if (transpose) {
+    if (int e = check_cuda(cudaFuncSetAttribute(q4_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "gemm smem attribute")) return e;
+    q4_gemm_kernel<true><<<grid, block, smem, st>>>(amap, p);
+  } else {
+    if (int e = check_cuda(cudaFuncSetAttribute(q4_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "gemm smem attribute")) return e;
+    q4_gemm_kernel<false><<<grid, block, smem, st>>>(amap, p);
+  }
+  return check_cuda(cudaGetLastError(), "gemm launch");
+}
+
+extern "C" int q4_gemm_fwd(const void* x, const int32_t* qweight, void* y, const void* scales, const int32_t* qzeros,
+                           const int32_t* g_idx, const void* bias, int M, int K, int N, int G, q4_stream_t stream) {
+  return gemm_launch(false, x, qweight, y, scales, qzeros, g_idx, bias, M, K, N, G, stream);
+}
+
+extern "C" int q4_gemm_bwd(const void* dy, const int32_t* qweight, void* dx, const void* scales, const int32_t* qzeros,
+                           const int32_t* g_idx, int M, int K, int N, int G, q4_stream_t stream) {
+  return gemm_launch(true, dy, qweight, dx, scales, qzeros, g_idx, nullptr, M, K, N, G, stream);
+}
+
+extern "C" int q4_device_status(unsigned* out) {
+  if (!out) return fail(Q4_E_BADARG, "device_status: null pointer");
+  return check_cuda(cudaMemcpyFromSymbol(out, g_gemm_status, sizeof(unsigned)), "read device status");
+}

@@ -87,6 +87,24 @@ int q4_gemv(const void* x, const int32_t* qweight, void* y, const void* scales,
             int M, int K, int N, int G, int groupsize, int y_dtype, unsigned flags,
             void* workspace, size_t workspace_bytes, q4_stream_t stream);
 
+/* Large-M products straight from the packed layer (W is never written to global memory):
+ *   q4_gemm_fwd:  y  [M, N] = x  [M, K] * W (+ bias)      q4_gemm_bwd:  dx [M, K] = dy [M, N] * W^T
+ * Together they replace the reference's reconstruct + torch.matmul composition,
+ * matmul_utils_4bit._matmul4bit_v2_recons (matmul_utils_4bit.py:114-127), i.e. the forward and
+ * backward of AutogradMatmul4bitCuda (autograd_4bit.py:32-54).  x, dy, y, dx, scales, bias fp16;
+ * fp32 accumulation in tensor memory; the dequantised operand is bit-identical to q4_recons_v2.
+ * The group of every row is read from g_idx (act-order safe).  Needs K % 128 == 0, N % 128 == 0;
+ * any M >= 1.  The forward keeps per-group scale tables for 128 columns in shared memory and
+ * returns Q4_E_SHAPE when G is too large for that (about 180 groups). */
+int q4_gemm_fwd(const void* x, const int32_t* qweight, void* y, const void* scales, const int32_t* qzeros,
+                const int32_t* g_idx, const void* bias, int M, int K, int N, int G, q4_stream_t stream);
+int q4_gemm_bwd(const void* dy, const int32_t* qweight, void* dx, const void* scales, const int32_t* qzeros,
+                const int32_t* g_idx, int M, int K, int N, int G, q4_stream_t stream);
+
+/* Copies the device status word to *out (synchronises the device): 0, or 0xDEAD0001 if a bounded
+ * wait inside a q4_gemm_* kernel expired (its output is then invalid). */
+int q4_device_status(unsigned* out);
+
 /* Profiling aid: when `device_buffer` is non-NULL, every CTA of the sequential-group decode kernel
  * writes SM cycle counters at fixed points of its life into 64 uint64 slots (buffer of at least
  * 64 * 8 * number-of-SMs bytes).  NULL switches the trace off (the default). */
