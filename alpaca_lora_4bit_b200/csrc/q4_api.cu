@@ -70,6 +70,11 @@ int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int
   if (!fn) return fail(Q4_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   if (!aligned16(base) || row_pitch_bytes % 16 || (uint64_t)box_cols * elem_bytes % 16)
     return fail(Q4_E_ALIGN, "tensor map: base, row pitch and box width must be multiples of 16 bytes");
+  // The driver call needs this thread to have a current context; a thread that has only inherited
+  // the device setting (an autograd worker, say) binds the primary context with cudaSetDevice.
+  int dev = 0;
+  if (int e = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return e;
+  if (int e = check_cuda(cudaSetDevice(dev), "cudaSetDevice")) return e;
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {row_pitch_bytes};
   cuuint32_t box[2] = {box_cols, box_rows};

@@ -6,12 +6,15 @@
 // shared memory, bit-exactly as the reference reconstruct does (rn(rn(s*q) - rn(s*(z+1)))), in
 // the layout the 5th-generation tensor core reads, and tcgen05.mma accumulates in TMEM.
 //
-// One CTA computes a 128 x 128 output tile.  Roles (192 threads):
-//   warp 0      TMA producer: activation tiles [128 rows x 64 contraction] fp16, 128B-swizzled
-//   warp 1      owns TMEM (128 fp32 columns) and issues tcgen05.mma (one elected thread)
-//   warps 2-5   dequantise W into the stage's B buffer, then run the epilogue (one TMEM lane
-//               quarter each): tcgen05.ld -> (+bias) -> fp16 -> global
-// A stage holds 16 KiB of activations and 16 KiB of dequantised W:
+// One CTA computes a 256 x 128 output tile as two 128-row accumulators, so that every dequantised
+// tile of W feeds two MMAs.  Roles (320 threads):
+//   warp 0      TMA producer: activation tiles [256 rows x 64 contraction] fp16, 128B-swizzled
+//   warp 1      owns TMEM (256 fp32 columns) and issues tcgen05.mma (one elected thread)
+//   warps 2-9   two groups of four: group 0 dequantises W for the even stages, group 1 for the
+//               odd ones (packed words prefetched one own stage ahead); afterwards all eight run
+//               the epilogue, one TMEM lane quarter of one accumulator each:
+//               tcgen05.ld -> (+bias) -> fp16 -> global
+// A stage holds 32 KiB of activations and 16 KiB of dequantised W:
 //   forward   B = W[k0:k0+64, n0:n0+128], two panels of [64 k-rows][64 n = 128 B], MN-major operand
 //   backward  B = W[k0:k0+128, n0:n0+64], one panel of [128 k-rows][64 n = 128 B], K-major operand
 // Both are the same bytes: rows of 64 consecutive n for one k, 16-byte chunks XOR-swizzled with
@@ -27,15 +30,17 @@ namespace q4 {
 
 __device__ unsigned g_gemm_status = 0;        // Q4_STATUS_WAIT_EXPIRED if any bounded wait gave up
 
-constexpr int GM_TILE_M = 128;
+constexpr int GM_TILE_M = 256;                // two accumulators of 128 rows
 constexpr int GM_TILE_N = 128;                // output columns per CTA
 constexpr int GM_TILE_C = 64;                 // contraction elements per stage
-constexpr int GM_STAGES = 4;
-constexpr int GM_A_BYTES = GM_TILE_M * GM_TILE_C * 2;     // 16 KiB
+constexpr int GM_MAX_STAGES = 4;
+constexpr int GM_A_BYTES = GM_TILE_M * GM_TILE_C * 2;     // 32 KiB
 constexpr int GM_B_BYTES = 128 * 64 * 2;                  // 16 KiB
 constexpr int GM_STAGE_BYTES = GM_A_BYTES + GM_B_BYTES;
-constexpr int GM_THREADS = 192;
-constexpr int GM_DEQ_THREADS = 128;
+constexpr int GM_THREADS = 320;
+constexpr int GM_DEQ_THREADS = 128;           // per dequant group
+constexpr int GM_DEQ_GROUPS = 2;
+constexpr int GM_TMEM_COLS = 256;
 constexpr uint32_t GM_WAIT_TRIES = 40000;     // x ~2 us sleeping tries
 
 struct GemmParams {
@@ -47,6 +52,7 @@ struct GemmParams {
   __half* out;              // [M, N_out]
   int M, K, N, G;
   int n_contract_tiles;     // contraction length / 64
+  int stages;               // pipeline depth (3 or 4, what shared memory allows)
 };
 
 // ---- tcgen05 wrappers --------------------------------------------------------------------------
@@ -151,13 +157,14 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const GemmParams p) {
   // 1024-byte alignment for the swizzled tiles
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   unsigned char* stages = smem;
-  uint64_t* full_a = reinterpret_cast<uint64_t*>(smem + GM_STAGES * GM_STAGE_BYTES);
-  uint64_t* full_b = full_a + GM_STAGES;
-  uint64_t* empty = full_b + GM_STAGES;
-  uint64_t* acc_full = empty + GM_STAGES;
+  const int S = p.stages;
+  uint64_t* full_a = reinterpret_cast<uint64_t*>(smem + S * GM_STAGE_BYTES);
+  uint64_t* full_b = full_a + GM_MAX_STAGES;
+  uint64_t* empty = full_b + GM_MAX_STAGES;
+  uint64_t* acc_full = empty + GM_MAX_STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  __half* s_tab = reinterpret_cast<__half*>(smem + GM_STAGES * GM_STAGE_BYTES + 256);     // forward: [G][128]
+  __half* s_tab = reinterpret_cast<__half*>(smem + S * GM_STAGE_BYTES + 256);     // forward: [G][128]
   __half* zp_tab = s_tab + (size_t)p.G * GM_TILE_N;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -166,13 +173,13 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const GemmParams p) {
   const int T = p.n_contract_tiles;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < GM_STAGES; ++i) { mbar_init(&full_a[i], 1); mbar_init(&full_b[i], GM_DEQ_THREADS / 32); mbar_init(&empty[i], 1); }
+    for (int i = 0; i < S; ++i) { mbar_init(&full_a[i], 1); mbar_init(&full_b[i], GM_DEQ_THREADS / 32); mbar_init(&empty[i], 1); }
     mbar_init(acc_full, 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&amap);
   }
-  if (warp == 1) { tmem_alloc(tmem_slot, 128); tmem_relinquish(); }
+  if (warp == 1) { tmem_alloc(tmem_slot, GM_TMEM_COLS); tmem_relinquish(); }
   tc_fence_before();
   __syncthreads();
   tc_fence_after();
@@ -182,7 +189,7 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const GemmParams p) {
     // ---------------- TMA producer: activation tiles ----------------
     if (lane == 0) {
       for (int it = 0; it < T; ++it) {
-        const int st = it % GM_STAGES, use = it / GM_STAGES;
+        const int st = it % S, use = it / S;
         if (use > 0) wait_bar(&empty[st], (use - 1) & 1, abort_flag);
         mbar_arrive_expect_tx(&full_a[st], GM_A_BYTES);
         tma_load_2d(stages + (size_t)st * GM_STAGE_BYTES, &amap, it * GM_TILE_C, m0, &full_a[st]);
@@ -191,9 +198,9 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const GemmParams p) {
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
-      constexpr uint32_t idesc = idesc_f16(GM_TILE_M, GM_TILE_N, !TRANSPOSE);
+      constexpr uint32_t idesc = idesc_f16(128, GM_TILE_N, !TRANSPOSE);
       for (int it = 0; it < T; ++it) {
-        const int st = it % GM_STAGES, use = it / GM_STAGES;
+        const int st = it % S, use = it / S;
         wait_bar(&full_a[st], use & 1, abort_flag);
         wait_bar(&full_b[st], use & 1, abort_flag);
         tc_fence_after();
@@ -202,12 +209,14 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const GemmParams p) {
 #pragma unroll
         for (int ks = 0; ks < GM_TILE_C / 16; ++ks) {
           // A: K-major, 128-byte rows, 8-row groups 1024 B apart; 16 contraction elements = 32 B
-          const uint64_t ad = smem_desc_sw128(a_addr + ks * 32, 16, 1024);
+          const uint64_t ad0 = smem_desc_sw128(a_addr + ks * 32, 16, 1024);
+          const uint64_t ad1 = smem_desc_sw128(a_addr + GM_A_BYTES / 2 + ks * 32, 16, 1024);      // rows 128..255
           // forward  B: MN-major: 64 n contiguous (128 B) per k-row, next 64 n at +8192, next 8 k-rows at +1024
           // backward B: K-major like A
           const uint64_t bd = TRANSPOSE ? smem_desc_sw128(b_addr + ks * 32, 16, 1024)
                                         : smem_desc_sw128(b_addr + ks * 2048, 8192, 1024);
-          umma_f16(tmem_acc, ad, bd, idesc, (it > 0 || ks > 0) ? 1u : 0u);
+          umma_f16(tmem_acc, ad0, bd, idesc, (it > 0 || ks > 0) ? 1u : 0u);
+          umma_f16(tmem_acc + 128, ad1, bd, idesc, (it > 0 || ks > 0) ? 1u : 0u);
         }
         umma_commit(&empty[st]);                   // frees the stage when these MMAs have read it
       }
@@ -215,20 +224,21 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const GemmParams p) {
     }
   } else {
     // ---------------- dequantisers (then epilogue) ----------------
-    const int tid = threadIdx.x - 64;                              // 0..127
+    const int grp = (warp - 2) >> 2;                               // dequant group: stages it % 2 == grp
+    const int tid = (threadIdx.x - 64) & (GM_DEQ_THREADS - 1);     // 0..127 within the group
     const int chunk16 = TRANSPOSE ? (tid & 7) : (tid & 15);        // 16-byte chunk (8 columns) within the stage's n-range
     const int r = TRANSPOSE ? (tid >> 3) : (tid >> 4);             // packed row within the stage
     const int N = p.N;
     if (!TRANSPOSE) {
       // tables for the CTA's 128 columns: scale and rn(s*(z+1)) of every group
-      for (int i = tid; i < p.G * (GM_TILE_N / 8); i += GM_DEQ_THREADS) {
+      for (int i = threadIdx.x - 64; i < p.G * (GM_TILE_N / 8); i += GM_DEQ_THREADS * GM_DEQ_GROUPS) {
         const int g = i / (GM_TILE_N / 8), c8 = i % (GM_TILE_N / 8);
         const uint4 s = __ldg(reinterpret_cast<const uint4*>(p.scales + (size_t)g * N + out0 + 8 * c8));
         const uint32_t zw = __ldg(p.qzeros + (size_t)g * (N >> 3) + ((out0 + 8 * c8) >> 3));
         *reinterpret_cast<uint4*>(s_tab + (size_t)g * GM_TILE_N + 8 * c8) = s;
         *reinterpret_cast<uint4*>(zp_tab + (size_t)g * GM_TILE_N + 8 * c8) = zero_terms(s, zw);
       }
-      named_bar_sync(1, GM_DEQ_THREADS);
+      named_bar_sync(1, GM_DEQ_THREADS * GM_DEQ_GROUPS);
     }
     // packed words of the stage: rows (k0/8 + r), columns ncol0 .. ncol0+7
     auto word_ptr = [&](int it) -> const uint32_t* {
@@ -236,21 +246,22 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const GemmParams p) {
       const int ncol = TRANSPOSE ? it * GM_TILE_C + 8 * chunk16 : out0 + 8 * chunk16;
       return p.qw + (size_t)prow * N + ncol;
     };
-    uint4 wa = ldg_stream(word_ptr(0)), wb = ldg_stream(word_ptr(0) + 4);
-    int4 ga, gb;                                                   // groups of the task's 8 k-rows
-    {
-      const int k8 = TRANSPOSE ? out0 + 8 * r : 8 * r;
+    uint4 wa = make_uint4(0, 0, 0, 0), wb = wa;
+    int4 ga = make_int4(0, 0, 0, 0), gb = ga;                      // groups of the task's 8 k-rows
+    if (grp < T) {
+      wa = ldg_stream(word_ptr(grp)); wb = ldg_stream(word_ptr(grp) + 4);
+      const int k8 = TRANSPOSE ? out0 + 8 * r : grp * GM_TILE_C + 8 * r;
       ga = __ldg(reinterpret_cast<const int4*>(p.g_idx + k8));
       gb = __ldg(reinterpret_cast<const int4*>(p.g_idx + k8 + 4));
     }
-    for (int it = 0; it < T; ++it) {
-      const int st = it % GM_STAGES, use = it / GM_STAGES;
+    for (int it = grp; it < T; it += GM_DEQ_GROUPS) {
+      const int st = it % S, use = it / S;
       const uint32_t w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
       const int gi[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
-      if (it + 1 < T) {                                            // prefetch the next stage's words
-        wa = ldg_stream(word_ptr(it + 1)); wb = ldg_stream(word_ptr(it + 1) + 4);
+      if (it + GM_DEQ_GROUPS < T) {                                // prefetch this group's next stage
+        wa = ldg_stream(word_ptr(it + GM_DEQ_GROUPS)); wb = ldg_stream(word_ptr(it + GM_DEQ_GROUPS) + 4);
         if (!TRANSPOSE) {
-          const int k8 = (it + 1) * GM_TILE_C + 8 * r;
+          const int k8 = (it + GM_DEQ_GROUPS) * GM_TILE_C + 8 * r;
           ga = __ldg(reinterpret_cast<const int4*>(p.g_idx + k8));
           gb = __ldg(reinterpret_cast<const int4*>(p.g_idx + k8 + 4));
         }
@@ -289,12 +300,13 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const GemmParams p) {
     __syncwarp();
     tc_fence_after();
     const int quarter = warp & 3;                                  // TMEM lanes 32*quarter .. +31
-    const int m = m0 + 32 * quarter + lane;
+    const int half = grp;                                          // accumulator (rows 128*half ..)
+    const int m = m0 + 128 * half + 32 * quarter + lane;
     const int n_out_total = TRANSPOSE ? p.K : p.N;
 #pragma unroll 1
     for (int cb = 0; cb < GM_TILE_N / 32; ++cb) {
       uint32_t v[32];
-      tmem_ld32(tmem_acc + ((uint32_t)(32 * quarter) << 16) + cb * 32, v);
+      tmem_ld32(tmem_acc + ((uint32_t)(32 * quarter) << 16) + 128 * half + cb * 32, v);
       tmem_ld_wait();
       if (m < p.M) {
         __half* dst = p.out + (size_t)m * n_out_total + out0 + cb * 32;
@@ -318,11 +330,11 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const GemmParams p) {
   }
   tc_fence_before();
   __syncthreads();
-  if (warp == 1) tmem_dealloc(tmem_acc, 128);
+  if (warp == 1) tmem_dealloc(tmem_acc, GM_TMEM_COLS);
 }
 
-static size_t gemm_smem_bytes(bool transpose, int G) {
-  return 1024 + (size_t)GM_STAGES * GM_STAGE_BYTES + 256 + (transpose ? 0 : (size_t)2 * G * GM_TILE_N * sizeof(__half));
+static size_t gemm_smem_bytes(bool transpose, int G, int stages) {
+  return 1024 + (size_t)stages * GM_STAGE_BYTES + 256 + (transpose ? 0 : (size_t)2 * G * GM_TILE_N * sizeof(__half));
 }
 
 }  // namespace q4
@@ -338,7 +350,9 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
   if (!aligned16(act) || !aligned16(qweight) || !aligned16(out) || !aligned16(scales) || !aligned16(g_idx))
     return fail(Q4_E_ALIGN, "gemm: pointers must be 16-byte aligned");
   if (int e = check_device()) return e;
-  const size_t smem = gemm_smem_bytes(transpose, G);
+  int stages = GM_MAX_STAGES;
+  while (stages > 2 && gemm_smem_bytes(transpose, G, stages) > 227 * 1024) --stages;
+  const size_t smem = gemm_smem_bytes(transpose, G, stages);
   if (smem > 227 * 1024) return fail(Q4_E_SHAPE, "gemm: scale tables for G=%d groups do not fit shared memory", G);
 
   GemmParams p;
@@ -347,6 +361,7 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
   p.M = M; p.K = K; p.N = N; p.G = G;
   const int contract = transpose ? N : K, nout = transpose ? K : N;
   p.n_contract_tiles = contract / GM_TILE_C;
+  p.stages = stages;
   CUtensorMap amap;
   if (int e = make_tmap_2d(&amap, act, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)contract, (uint64_t)M,
                            (uint64_t)contract * 2, GM_TILE_C, GM_TILE_M, CU_TENSOR_MAP_SWIZZLE_128B)) return e;

@@ -12,6 +12,11 @@ anything smaller to the decode kernel.  Module-level switches keep their referen
                                           groups come from ``groupsize`` or from ``g_idx``
   act_order                               take the group of every row from ``g_idx``
   cache_buffer / buffer_mat_dic           cache of dense fp16 buffers used by the reconstruct path
+  fused_gemm (new)                        True: ``_matmul4bit_v2_recons`` runs the fused dequant-GEMM
+                                          kernels (W never written to global memory) whenever the
+                                          operands are fp16 and the shape is supported; False, or an
+                                          unsupported shape / dtype: reconstruct + ``torch.matmul`` as
+                                          in the reference
   debug                                   print which variant ran
 """
 from __future__ import annotations
@@ -31,6 +36,7 @@ faster_mode = 'old_faster'  # set disable to disable it
 valid_faster_mode = ('faster', 'old_faster')
 act_order = False
 cache_buffer = True
+fused_gemm = True          # large-M v2 products on the fused tcgen05 kernels instead of reconstruct + library GEMM
 
 
 def get_buffer(shape_of_qweight, dtype=torch.float16, device='cuda', bits=4):
@@ -115,6 +121,15 @@ def _matmul4bit_v2_recons(x, qweight, scales, zeros, g_idx, transpose=False):
     if debug:
         print('_matmul4bit_v2_recons')
     _check_inner(x, qweight, 8, transpose)
+    K, N = qweight.shape[0] * 8, qweight.shape[1]
+    if (fused_gemm and x.dtype == torch.float16 and scales.dtype == torch.float16
+            and quant_cuda.gemm_supported(K, N, scales.shape[0], transpose)):
+        x2 = x.reshape(-1, x.shape[-1])
+        if not x2.is_contiguous():
+            x2 = x2.contiguous()
+        out = torch.empty((x2.shape[0], K if transpose else N), dtype=torch.float16, device=x.device)
+        quant_cuda.gemm(x2, qweight, out, scales, zeros, g_idx, transpose=transpose)
+        return out.reshape(x.shape[:-1] + (out.shape[-1],))
     buffer = get_buffer(qweight.shape, dtype=scales.dtype, device=qweight.device)
     quant_cuda.vecquant4recons_v2(qweight, buffer, scales, zeros, g_idx)
     return _dense_matmul(x, buffer, transpose)

@@ -103,6 +103,46 @@ def gemv(x, qweight, y, scales, zeros, g_idx, groupsize, flags, bias=None) -> No
                                  m, K, N, G, groupsize, ydt, flags, ws.data_ptr(), ws.numel(), st), "gemv")
 
 
+def gemm(x, qweight, out, scales, zeros, g_idx, transpose=False, bias=None) -> None:
+    """Fused large-M product on the tensor cores: ``out = x @ W (+ bias)`` or, with ``transpose``,
+    ``out = x @ W.T``; ``x``, ``out``, ``scales`` fp16, W never leaves shared memory."""
+    dev = _lib.require_cuda(x, qweight, out, scales, zeros, g_idx, bias)
+    R, N = qweight.shape
+    K = R * 8
+    M = x.shape[0]
+    G = scales.shape[0]
+    inner, outer = (N, K) if transpose else (K, N)
+    if x.shape != (M, inner) or out.shape != (M, outer):
+        raise RuntimeError(f"quant_cuda: gemm shapes x{tuple(x.shape)} out{tuple(out.shape)} do not match the layer [{K},{N}]")
+    if x.dtype != torch.float16 or out.dtype != torch.float16 or scales.dtype != torch.float16:
+        raise RuntimeError("quant_cuda: gemm takes fp16 x, out and scales")
+    L = _lib.lib()
+    with torch.cuda.device(dev):
+        st = _lib.stream_of(x)
+        if transpose:
+            rc = L.q4_gemm_bwd(x.data_ptr(), qweight.data_ptr(), out.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
+                               g_idx.data_ptr(), M, K, N, G, st)
+        else:
+            rc = L.q4_gemm_fwd(x.data_ptr(), qweight.data_ptr(), out.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
+                               g_idx.data_ptr(), _lib.ptr(bias), M, K, N, G, st)
+    _lib.check(rc, "gemm")
+
+
+def gemm_supported(K: int, N: int, G: int, transpose: bool) -> bool:
+    """Shapes the fused kernels take: K, N multiples of 128; forward scale tables must fit shared memory."""
+    if K % 128 or N % 128:
+        return False
+    return transpose or (1024 + 2 * 49152 + 256 + 2 * G * 128 * 2) <= 227 * 1024
+
+
+def device_status() -> int:
+    """Status word of the fused kernels (synchronises): 0 unless a bounded device-side wait expired."""
+    import ctypes
+    v = ctypes.c_uint(0)
+    _lib.check(_lib.lib().q4_device_status(ctypes.byref(v)), "device_status")
+    return v.value
+
+
 def _half(t):
     return t if t.dtype == torch.float16 else t.half()
 

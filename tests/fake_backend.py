@@ -35,6 +35,18 @@ def gemv(x, qweight, y, scales, zeros, g_idx, groupsize, flags, bias=None):
     y.copy_((y.float() + out) if (flags & 1) else out)
 
 
+def gemm_supported(K, N, G, transpose):
+    return K % 128 == 0 and N % 128 == 0
+
+
+def gemm(x, qweight, out, scales, zeros, g_idx, transpose=False, bias=None):
+    w = orc.recons_v2(qweight, scales, zeros, g_idx).float()
+    y = x.float() @ (w.t() if transpose else w)
+    if bias is not None:
+        y = y + bias.float()
+    out.copy_(y)
+
+
 @contextlib.contextmanager
 def installed():
     """Route the dispatch layer to the oracle for the duration of the block."""

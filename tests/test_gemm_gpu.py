@@ -1,0 +1,140 @@
+"""Parity of the fused dequant-GEMM kernels (forward x*W, backward dy*W^T) through the C ABI, and of
+the autograd / module surface built on them."""
+import pytest
+import torch
+
+from alpaca_lora_4bit_b200 import autograd_4bit as a4, matmul_utils_4bit as mm4b, models, quant_cuda, synth
+from oracle import q4_oracle as orc
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+REL_TOL = 2e-3          # relative Frobenius error allowed on matmul outputs (fp16 output rounding ~2e-4)
+
+
+def rel_fro(got, want):
+    got, want = got.double().cpu(), want.double().cpu()
+    return float((got - want).norm() / want.norm())
+
+
+def run_gemm(layer, x, transpose, bias=None):
+    L = layer.to(DEV)
+    M = x.shape[0]
+    out = torch.full((M + 16, layer.K if transpose else layer.N), -777.0, dtype=torch.float16, device=DEV)
+    view = out[8:8 + M]
+    quant_cuda.gemm(x.to(DEV), L.qweight, view, L.scales, L.qzeros, L.g_idx, transpose=transpose,
+                    bias=None if bias is None else bias.to(DEV))
+    torch.cuda.synchronize()
+    assert quant_cuda.device_status() == 0
+    assert bool((out[:8] == -777.0).all()) and bool((out[8 + M:] == -777.0).all())    # canary rows intact
+    return view
+
+
+@pytest.mark.parametrize("transpose", [False, True])
+@pytest.mark.parametrize("M,K,N,g,act", [(128, 128, 128, 128, False), (1, 256, 128, 128, True), (17, 128, 384, 32, True),
+                                         (200, 512, 384, 64, True), (129, 1024, 256, -1, False), (300, 4096, 512, 128, True)])
+def test_gemm_vs_oracle(M, K, N, g, act, transpose):
+    layer = synth.make_layer(K, N, g, act, seed=M + K)
+    x = synth.make_acts(M, N if transpose else K, seed=M)
+    want = orc.matmul4bit_ref(x, layer.qweight, layer.scales, layer.qzeros, layer.g_idx, transpose=transpose)
+    assert rel_fro(run_gemm(layer, x, transpose), want) <= REL_TOL
+
+
+@pytest.mark.parametrize("transpose", [False, True])
+def test_gemm_selects_rows_of_w_bit_exactly(transpose):
+    """One-hot activations copy rows (columns) of W through the tensor core: the in-kernel dequant
+    must equal the reference reconstruct bit for bit."""
+    layer = synth.make_layer(256, 384, 128, True, seed=5)
+    w = orc.recons_v2(layer.qweight, layer.scales, layer.qzeros, layer.g_idx)
+    inner = 384 if transpose else 256
+    x = torch.zeros((inner, inner), dtype=torch.float16)
+    x[torch.arange(inner), torch.arange(inner)] = 1.0
+    got = run_gemm(layer, x, transpose).cpu()
+    want = w.t().contiguous() if transpose else w
+    assert torch.equal(got.view(torch.int16), want.contiguous().view(torch.int16))
+
+
+def test_gemm_bias_forward():
+    layer = synth.make_layer(512, 256, 128, False, seed=7)
+    x = synth.make_acts(64, 512, seed=8)
+    bias = torch.randn(256).half()
+    want = orc.matmul4bit_ref(x, layer.qweight, layer.scales, layer.qzeros, layer.g_idx) + bias.float()
+    assert rel_fro(run_gemm(layer, x, False, bias=bias), want) <= REL_TOL
+
+
+@pytest.mark.parametrize("K,N", [(5120, 5120), (5120, 13824), (13824, 5120)])
+def test_gemm_llama13b_shapes_act_order(K, N):
+    """C2 sizes (M=2048, act-order, g128): checked against fp32 matmul of the bit-exact reconstruct on the GPU."""
+    layer = synth.make_layer(K, N, 128, True, seed=K // 128 + N)
+    L = layer.to(DEV)
+    w = torch.empty((K, N), dtype=torch.float16, device=DEV)
+    quant_cuda.vecquant4recons_v2(L.qweight, w, L.scales, L.qzeros, L.g_idx)
+    torch.backends.cuda.matmul.allow_tf32 = False
+    for transpose in (False, True):
+        x = synth.make_acts(2048, N if transpose else K, seed=3).to(DEV)
+        want = x.float() @ (w.float().t() if transpose else w.float())
+        got = run_gemm(layer, x.cpu(), transpose)
+        assert rel_fro(got, want) <= REL_TOL
+
+
+def test_backward_is_transpose_of_forward():
+    """<dy, x W> = <dy W^T, x> for random x, dy at a full-size layer."""
+    layer = synth.make_layer(4096, 11008, 128, False, seed=11)
+    x = synth.make_acts(256, 4096, seed=12)
+    dy = synth.make_acts(256, 11008, seed=13)
+    y = run_gemm(layer, x, False).double()
+    dx = run_gemm(layer, dy, True).double()
+    lhs = float((dy.double().to(DEV) * y).sum())
+    rhs = float((dx * x.double().to(DEV)).sum())
+    assert abs(lhs - rhs) <= 2e-3 * max(abs(lhs), abs(rhs))
+
+
+def _module(K, N, g, act, seed, cls=a4.Autograd4bitQuantLinear, **kw):
+    layer = synth.make_layer(K, N, g, act, seed)
+    m = cls(K, N, groupsize=g, **kw) if cls is a4.Autograd4bitQuantLinear else cls("default", K, N, groupsize=g, **kw)
+    m.qweight, m.qzeros, m.scales, m.g_idx = layer.qweight, layer.qzeros, layer.scales, layer.g_idx
+    m.bias = torch.zeros(N, dtype=torch.float16)
+    return m.to(DEV), layer
+
+
+@pytest.mark.parametrize("fused", [True, False])
+def test_autograd_module_forward_backward(fused):
+    m, layer = _module(1024, 512, 128, True, 21)
+    w = orc.recons_v2(layer.qweight, layer.scales, layer.qzeros, layer.g_idx).float()
+    x = synth.make_acts(2 * 96, 1024, 22).reshape(2, 96, 1024).to(DEV).requires_grad_(True)
+    mm4b.fused_gemm = fused
+    try:
+        y = m(x)
+        dy = torch.randn_like(y)
+        y.backward(dy)
+    finally:
+        mm4b.fused_gemm = True
+    assert y.shape == (2, 96, 512) and y.dtype == torch.float16
+    assert rel_fro(y.reshape(-1, 512), x.detach().reshape(-1, 1024).float().cpu() @ w) <= REL_TOL
+    assert rel_fro(x.grad.reshape(-1, 1024), dy.reshape(-1, 512).float().cpu() @ w.t()) <= REL_TOL
+
+
+def test_module_routes_by_rows_and_grad_mode():
+    m, layer = _module(512, 256, 128, False, 31)
+    want = lambda x: orc.matmul4bit_ref(x, layer.qweight, layer.scales, layer.qzeros, layer.g_idx)
+    with torch.no_grad():
+        for rows in (1, 8, 9, 40):                              # decode kernel up to auto_switch_thd rows, fused GEMM above
+            x = synth.make_acts(rows, 512, rows)
+            assert rel_fro(m(x.to(DEV)), want(x)) <= REL_TOL
+
+
+def test_linear4bitlt_lora_training_step():
+    m, layer = _module(512, 256, 128, True, 41, cls=models.Linear4bitLt, r=8, lora_alpha=16, lora_dropout=0.0)
+    A, B = synth.make_lora(512, 256, 8, seed=42, dtype=torch.float32)
+    m.lora_A["default"].weight.data.copy_(A)
+    m.lora_B["default"].weight.data.copy_(B)
+    x = synth.make_acts(160, 512, 43).to(DEV).requires_grad_(True)
+    y = m(x)
+    dy = torch.randn_like(y)
+    y.backward(dy)
+    w = orc.recons_v2(layer.qweight, layer.scales, layer.qzeros, layer.g_idx).float()
+    xc, dyc = x.detach().cpu(), dy.cpu()
+    assert rel_fro(y, xc.float() @ w + orc.lora_forward(xc, A, B, 2.0)) <= REL_TOL
+    dx_l, dA, dB = orc.lora_backward(xc, dyc, A, B, 2.0)
+    assert rel_fro(x.grad, dyc.float() @ w.t() + dx_l) <= REL_TOL
+    assert rel_fro(m.lora_A["default"].weight.grad, dA) <= 5e-3
+    assert rel_fro(m.lora_B["default"].weight.grad, dB) <= 5e-3
