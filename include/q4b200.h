@@ -87,6 +87,24 @@ int q4_gemv(const void* x, const int32_t* qweight, void* y, const void* scales,
             int M, int K, int N, int G, int groupsize, int y_dtype, unsigned flags,
             void* workspace, size_t workspace_bytes, q4_stream_t stream);
 
+/* The same product as q4_gemv for callers that cannot allocate device memory (no counterpart in the
+ * reference; added for hosts such as a serving process that handed all of HBM to its own pools, a
+ * plugin that may not call the allocator of the process it lives in, or a latency path on which the
+ * device-synchronising cudaMalloc is not acceptable).  The scratch is a 2.0625 MiB device array built
+ * into the library (q4_gemv_static_max_bytes()), present on every GPU that loads the library until
+ * the process exits; the call allocates nothing and frees nothing.  That size serves every shape
+ * with sequential groups; shapes whose q4_gemv_workspace_bytes() exceeds it (16-row products over
+ * roughly 17k-19k columns) are refused with Q4_E_WORKSPACE.
+ * The first call on each device looks up the device address of the array; make that first call
+ * outside any stream capture.  All calls on a device share the one array, so calls that can overlap
+ * on the GPU (different streams without ordering) race; keep them on one stream or order them with
+ * events.  The head of the array is cleared on the stream before every launch. */
+size_t q4_gemv_static_max_bytes(void);
+int q4_gemv_static(const void* x, const int32_t* qweight, void* y, const void* scales,
+                   const int32_t* qzeros, const int32_t* g_idx, const void* bias,
+                   int M, int K, int N, int G, int groupsize, int y_dtype, unsigned flags,
+                   q4_stream_t stream);
+
 /* Large-M products straight from the packed layer (W is never written to global memory):
  *   q4_gemm_fwd:  y  [M, N] = x  [M, K] * W (+ bias)      q4_gemm_bwd:  dx [M, K] = dy [M, N] * W^T
  * Together they replace the reference's reconstruct + torch.matmul composition,
