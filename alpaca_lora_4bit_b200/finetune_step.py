@@ -1,0 +1,190 @@
+"""One LoRA finetune step over a 4-bit LLaMA, single GPU or data parallel.
+
+This is the caller whose step the benchmark times: what the reference's ``finetune.py`` sets up
+around the quant linears (finetune.py:36-188) without the HF Trainer: every ``nn.Linear`` but
+``lm_head`` becomes an ``Autograd4bitQuantLinear`` (autograd_4bit.py:266-272), the target
+projections get ``Linear4bitLt`` LoRA layers (models.py:13-76), every decoder layer runs under
+``torch.utils.checkpoint`` with the embedding output as a grad-requiring leaf
+(gradient_checkpointing.py:19-65), fp16 autocast with loss scaling, AdamW on the LoRA factors.
+Data parallelism follows the reference's DDP use (Finetune4bConfig.py:83-88, finetune.py:166):
+every rank holds the whole int4 base and its own micro-batch; the only exchange is one
+all-reduce of the LoRA gradients, here over a single flat fp32 buffer that all ``.grad`` fields
+alias, so one collective per step moves everything.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Iterable, List, Optional
+
+import torch
+import torch.nn as nn
+from torch.utils.checkpoint import checkpoint
+
+from .autograd_4bit import Autograd4bitQuantLinear, find_layers, make_quant_for_4bit_autograd
+from .models import Linear4bitLt, wrap_with_lora
+
+
+@dataclass
+class LlamaShape:
+    hidden_size: int = 4096
+    intermediate_size: int = 11008
+    num_hidden_layers: int = 32
+    num_attention_heads: int = 32
+    num_key_value_heads: int = 32
+    vocab_size: int = 32000
+    max_position_embeddings: int = 2048
+
+    @staticmethod
+    def llama_7b() -> "LlamaShape":
+        return LlamaShape()
+
+    @staticmethod
+    def llama2_70b() -> "LlamaShape":
+        return LlamaShape(8192, 28672, 80, 64, 8, 32000, 4096)
+
+
+def fill_random_quant(mod: Autograd4bitQuantLinear, gen: torch.Generator, act_order: bool, scale_mul: float = 1.0):
+    """Random GPTQ v2 contents on the module's device: uniform levels, zero points 0..14, fp16 scales
+    uniform in [0.002, 0.02] * scale_mul, sequential or permuted ``g_idx``."""
+    dev = mod.qweight.device
+    K, N, g = mod.in_features, mod.out_features, mod.groupsize
+    G = math.ceil(K / g)
+    mod.qweight = torch.randint(-2 ** 31, 2 ** 31 - 1, (K // 8, N), generator=gen, device=dev, dtype=torch.int64).to(torch.int32)
+    zl = torch.randint(0, 15, (G, N), generator=gen, device=dev, dtype=torch.int64)
+    sh = torch.arange(8, device=dev, dtype=torch.int64) * 4
+    zw = (zl.reshape(G, N // 8, 8) << sh).sum(-1)
+    mod.qzeros = torch.where(zw >= 2 ** 31, zw - 2 ** 32, zw).to(torch.int32)
+    mod.scales = ((torch.rand((G, N), generator=gen, device=dev) * 0.018 + 0.002) * scale_mul).half()
+    if act_order:
+        mod.g_idx = (torch.randperm(K, generator=gen, device=dev) // g).to(torch.int32)
+    else:
+        mod.g_idx = (torch.arange(K, device=dev) // g).to(torch.int32)
+    mod.bias = torch.zeros(N, dtype=torch.float16, device=dev)
+
+
+def build_quant_llama(shape: LlamaShape, device, groupsize: int = 128, act_order: bool = False, seed: int = 0,
+                      attn_implementation: str = "sdpa") -> nn.Module:
+    """Random-init LLaMA of the given shape with every linear but ``lm_head`` quantised (4-bit, v2).
+
+    Built on the meta device so the dense fp16 weights of the replaced linears never exist."""
+    from transformers import LlamaConfig, LlamaForCausalLM
+    cfg = LlamaConfig(hidden_size=shape.hidden_size, intermediate_size=shape.intermediate_size,
+                      num_hidden_layers=shape.num_hidden_layers, num_attention_heads=shape.num_attention_heads,
+                      num_key_value_heads=shape.num_key_value_heads, vocab_size=shape.vocab_size,
+                      max_position_embeddings=shape.max_position_embeddings, attn_implementation=attn_implementation)
+    with torch.device("meta"):
+        model = LlamaForCausalLM(cfg)
+    model = model.half()
+    layers = find_layers(model)
+    layers.pop("lm_head", None)
+    make_quant_for_4bit_autograd(model, layers, groupsize=groupsize)
+    model = model.to_empty(device=device)
+    gen = torch.Generator(device=device).manual_seed(seed)
+    # weight scale chosen so activations keep a sane magnitude through 32+ random layers
+    mul = 1.0 / math.sqrt(shape.hidden_size / 1024.0)
+    for name, mod in model.named_modules():
+        if isinstance(mod, Autograd4bitQuantLinear):
+            fill_random_quant(mod, gen, act_order, scale_mul=mul)
+    with torch.no_grad():
+        for name, prm in model.named_parameters():
+            if prm.dim() >= 2:
+                prm.copy_((torch.randn(prm.shape, generator=gen, device=device) * 0.02).to(prm.dtype))
+            else:
+                prm.fill_(1.0)                                     # RMSNorm weights
+    # non-persistent rotary buffers were created on the meta device: recompute them
+    for mod in model.modules():
+        if hasattr(mod, "inv_freq") and hasattr(mod, "compute_default_rope_parameters"):
+            inv, _ = mod.compute_default_rope_parameters(cfg, device)
+            mod.inv_freq = inv
+            if hasattr(mod, "original_inv_freq"):
+                mod.original_inv_freq = inv.clone()
+    model.config.use_cache = False
+    return model
+
+
+def add_lora(model: nn.Module, targets: Iterable[str], r: int, alpha: int, std_a: float = 0.02, std_b: float = 0.01,
+             seed: int = 1) -> nn.Module:
+    """LoRA on the named projections: fp32 factors (as fresh PEFT adapters are), A ~ N(0, std_a), B ~ N(0, std_b)."""
+    wrap_with_lora(model, list(targets), r=r, lora_alpha=alpha, lora_dropout=0.0)
+    dev = next(model.parameters()).device
+    gen = torch.Generator(device=dev).manual_seed(seed)
+    for mod in model.modules():
+        if isinstance(mod, Linear4bitLt):
+            for name in mod.lora_A.keys():
+                a, b = mod.lora_A[name].weight, mod.lora_B[name].weight
+                a.data = (torch.randn(a.shape, generator=gen, device=dev) * std_a).float()
+                b.data = (torch.randn(b.shape, generator=gen, device=dev) * std_b).float()
+    return model
+
+
+def apply_gradient_checkpointing(model: nn.Module) -> None:
+    """Recompute every decoder layer in the backward (gradient_checkpointing.py:47-65)."""
+    for layer in model.model.layers:
+        inner = layer.forward
+
+        def wrapped(*args, _inner=inner, **kwargs):
+            return checkpoint(_inner, *args, use_reentrant=False, **kwargs)
+
+        layer.forward = wrapped
+    # the embedding output must carry a gradient or the checkpointed segments have nothing to differentiate
+    model.get_input_embeddings().register_forward_hook(lambda m, i, o: o.requires_grad_(True))
+
+
+class FlatGrads:
+    """All trainable gradients as views of one contiguous fp32 buffer (one collective per step)."""
+
+    def __init__(self, params: List[nn.Parameter]):
+        self.params = params
+        total = sum(p.numel() for p in params)
+        self.buffer = torch.zeros(total, dtype=torch.float32, device=params[0].device)
+        off = 0
+        for p in params:
+            p.grad = self.buffer[off:off + p.numel()].view_as(p)
+            off += p.numel()
+
+    def zero(self):
+        self.buffer.zero_()
+
+    def all_reduce_mean(self, group=None):
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+            dist.all_reduce(self.buffer, op=dist.ReduceOp.SUM, group=group)
+            self.buffer.div_(dist.get_world_size(group))
+
+
+class LoraFinetuner:
+    """Owns the optimizer state and runs one step: forward, backward, gradient all-reduce, AdamW."""
+
+    def __init__(self, model: nn.Module, lr: float = 3e-4, loss_scale: float = 1024.0, autocast: bool = True,
+                 group=None):
+        self.model = model
+        self.params = [p for p in model.parameters() if p.requires_grad]
+        if not self.params:
+            raise ValueError("model has no trainable parameters (wrap it with add_lora first)")
+        self.flat = FlatGrads(self.params)
+        self.opt = torch.optim.AdamW(self.params, lr=lr, fused=self.params[0].is_cuda)
+        self.loss_scale = loss_scale
+        self.autocast = autocast
+        self.group = group
+
+    def step(self, input_ids: torch.Tensor) -> torch.Tensor:
+        """One optimisation step on a batch of token ids ``[B, T]`` (labels = inputs, shifted inside
+        the model).  Returns the detached loss (a device scalar)."""
+        self.flat.zero()
+        dev_type = input_ids.device.type
+        with torch.autocast(device_type=dev_type, dtype=torch.float16, enabled=self.autocast and dev_type == "cuda"):
+            loss = self.model(input_ids=input_ids, labels=input_ids, use_cache=False).loss
+        (loss.float() * self.loss_scale).backward()
+        self.flat.buffer.div_(self.loss_scale)
+        self.flat.all_reduce_mean(self.group)
+        self.opt.step()
+        return loss.detach()
+
+
+def lora_param_count(model: nn.Module) -> int:
+    return sum(p.numel() for p in model.parameters() if p.requires_grad)
+
+
+def quant_linear_params(model: nn.Module) -> int:
+    return sum(m.in_features * m.out_features for m in model.modules() if isinstance(m, Autograd4bitQuantLinear))

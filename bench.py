@@ -229,6 +229,66 @@ def run_ours(args, rank, world, local_rank):
                 per_shape=per_shape, h2d=h2d, d2h=d2h)
 
 
+def run_finetune(args, rank, world, local_rank):
+    """LLaMA-7B-shape LoRA finetune step (C3): 32 layers, g128 int4 base, LoRA r=8 alpha=16 on q_proj/v_proj,
+    micro-batch 4 x 256 uniform token ids per rank, fp16 autocast, gradient checkpointing, AdamW; data parallel
+    with one NCCL all-reduce of the flat LoRA-gradient buffer.  Token ids come from pinned host memory every
+    step and the loss is read back every step (inside the timed region)."""
+    from alpaca_lora_4bit_b200 import finetune_step as fs
+    dev = torch.device("cuda", local_rank)
+    shape = fs.LlamaShape.llama_7b()
+    if args.finetune_layers:
+        shape.num_hidden_layers = args.finetune_layers
+    model = fs.build_quant_llama(shape, dev, groupsize=128, act_order=False, seed=0)
+    fs.add_lora(model, ["q_proj", "v_proj"], r=8, alpha=16, std_a=0.02, std_b=0.01, seed=1)
+    fs.apply_gradient_checkpointing(model)
+    model.train()
+    ft = fs.LoraFinetuner(model, lr=3e-4)
+    B, T = 4, 256
+    gen = torch.Generator().manual_seed(1000 + rank)
+    steps, warm = args.finetune_steps, 3
+    ids_host = [torch.randint(0, shape.vocab_size, (B, T), generator=gen).pin_memory() for _ in range(steps + warm)]
+    loss_host = torch.zeros(1, dtype=torch.float32).pin_memory()
+
+    def one(i):
+        ids = ids_host[i].to(dev, non_blocking=True)
+        loss = ft.step(ids)
+        loss_host.copy_(loss.float().reshape(1), non_blocking=True)
+        torch.cuda.current_stream(dev).synchronize()
+        return float(loss_host[0])
+
+    for i in range(warm):
+        one(i)
+    if world > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize(dev)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    losses = [one(warm + i) for i in range(steps)]
+    e1.record()
+    torch.cuda.synchronize(dev)
+    if world > 1:
+        torch.distributed.barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=dev, dtype=torch.float64)
+        torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+        ms = float(t[0])
+    tokens = B * T * world * steps
+    p_lin = fs.quant_linear_params(model) + shape.vocab_size * shape.hidden_size
+    flops_per_token = 4 * p_lin                      # forward 2P + backward-dx 2P, recompute not counted
+    tps = tokens / (ms * 1e-3)
+    out = {"metric": "llama7b_lora_finetune_tokens_per_s", "value": round(tps, 1), "unit": "tokens/s", "n_gpus": world,
+           "steps": steps, "ms_per_step": round(ms / steps, 2), "layers": shape.num_hidden_layers,
+           "micro_batch": [B, T], "lora": "r=8 alpha=16 q_proj,v_proj, dropout 0 (as the reference forces under checkpointing)",
+           "lora_params": fs.lora_param_count(model), "allreduce_bytes_per_step": 4 * fs.lora_param_count(model) if world > 1 else 0,
+           "model_tflops_per_s": round(tps * flops_per_token / 1e12, 1), "loss_first_last": [round(losses[0], 4), round(losses[-1], 4)],
+           "h2d_bytes_per_step": B * T * 8, "d2h_bytes_per_step": 4}
+    del ft, model
+    torch.cuda.empty_cache()
+    return out
+
+
 def cpu_reference(sample_layers=1, reps=3, threads=None):
     """The reference composition on the host: reconstruct fp16 [K,N] + fp32 matmul, M=1."""
     from oracle import q4_oracle as orc
@@ -256,6 +316,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--copies", type=int, default=8, help="distinct copies of each layer shape per GPU")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--finetune-steps", type=int, default=5, help="timed LLaMA-7B LoRA finetune steps (0 = skip)")
+    ap.add_argument("--finetune-layers", type=int, default=0, help="override the number of decoder layers (0 = 32)")
     args = ap.parse_args()
 
     rank = int(os.environ.get("RANK", "0"))
@@ -285,6 +347,7 @@ def main():
     if world > 1:
         torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     r = run_ours(args, rank, world, local_rank)
+    ft = run_finetune(args, rank, world, local_rank) if args.finetune_steps > 0 else None
     if rank == 0:
         peak, peak_kind = load_peaks()
         bps = bytes_per_step(args.copies)
@@ -303,6 +366,8 @@ def main():
                 "e2e": {"value": round(e2e, 1), "unit": UNIT, "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": r["d2h"],
                         "api": "matmul_utils_4bit.matmul4bit, pinned host x in, pinned host y out, weights resident"},
                 "gpu_launches": args.steps * r["n_launch"], "clocks": r["clocks"]}
+        if ft is not None:
+            line["finetune"] = ft
         if world == 1 and not args.no_cpu:
             gbs, sec, threads = cpu_reference(reps=3)
             line["cpu_baseline"] = {"value": round(gbs, 4), "unit": UNIT, "cores": threads, "kind": "port",
