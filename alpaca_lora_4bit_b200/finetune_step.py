@@ -81,11 +81,12 @@ def build_quant_llama(shape: LlamaShape, device, groupsize: int = 128, act_order
     make_quant_for_4bit_autograd(model, layers, groupsize=groupsize)
     model = model.to_empty(device=device)
     gen = torch.Generator(device=device).manual_seed(seed)
-    # weight scale chosen so activations keep a sane magnitude through 32+ random layers
-    mul = 1.0 / math.sqrt(shape.hidden_size / 1024.0)
     for name, mod in model.named_modules():
         if isinstance(mod, Autograd4bitQuantLinear):
-            fill_random_quant(mod, gen, act_order, scale_mul=mul)
+            # random levels minus random zero points have a standard deviation of about 6.3 levels and the
+            # base scales average 0.011; shrink them so that every layer has unit gain (std(W) = 1/sqrt(K)),
+            # as trained checkpoints roughly do - otherwise 32 random layers overflow fp16
+            fill_random_quant(mod, gen, act_order, scale_mul=1.0 / (6.3 * 0.011 * math.sqrt(mod.in_features)))
     with torch.no_grad():
         for name, prm in model.named_parameters():
             if prm.dim() >= 2:
@@ -157,7 +158,7 @@ class LoraFinetuner:
     """Owns the optimizer state and runs one step: forward, backward, gradient all-reduce, AdamW."""
 
     def __init__(self, model: nn.Module, lr: float = 3e-4, loss_scale: float = 1024.0, autocast: bool = True,
-                 group=None):
+                 group=None, dynamic_scale: Optional[bool] = None):
         self.model = model
         self.params = [p for p in model.parameters() if p.requires_grad]
         if not self.params:
@@ -167,6 +168,10 @@ class LoraFinetuner:
         self.loss_scale = loss_scale
         self.autocast = autocast
         self.group = group
+        # fp16 training as the HF Trainer does it: dynamic loss scale, steps with non-finite gradients skipped
+        if dynamic_scale is None:
+            dynamic_scale = self.params[0].is_cuda and autocast
+        self.scaler = torch.amp.GradScaler("cuda", init_scale=loss_scale) if dynamic_scale else None
 
     def step(self, input_ids: torch.Tensor) -> torch.Tensor:
         """One optimisation step on a batch of token ids ``[B, T]`` (labels = inputs, shifted inside
@@ -175,10 +180,16 @@ class LoraFinetuner:
         dev_type = input_ids.device.type
         with torch.autocast(device_type=dev_type, dtype=torch.float16, enabled=self.autocast and dev_type == "cuda"):
             loss = self.model(input_ids=input_ids, labels=input_ids, use_cache=False).loss
-        (loss.float() * self.loss_scale).backward()
-        self.flat.buffer.div_(self.loss_scale)
-        self.flat.all_reduce_mean(self.group)
-        self.opt.step()
+        if self.scaler is not None:
+            self.scaler.scale(loss.float()).backward()
+            self.flat.all_reduce_mean(self.group)          # scaled gradients; an overflow on any rank reaches all
+            self.scaler.step(self.opt)                     # unscales, skips the update on inf/nan
+            self.scaler.update()
+        else:
+            (loss.float() * self.loss_scale).backward()
+            self.flat.buffer.div_(self.loss_scale)
+            self.flat.all_reduce_mean(self.group)
+            self.opt.step()
         return loss.detach()
 
 
