@@ -289,6 +289,60 @@ def run_finetune(args, rank, world, local_rank):
     return out
 
 
+def run_gemm(args, local_rank):
+    """C2: fused dequant-GEMM at M=2048 on LLaMA-13B layer shapes, act-order g128, forward and backward,
+    next to the reference's composition (reconstruct to a dense fp16 buffer + library GEMM) run with this
+    library's reconstruct kernel.  Tensor-core roofline: 2*M*K*N flop against the measured bf16 GEMM peak."""
+    from alpaca_lora_4bit_b200 import quant_cuda
+    dev = torch.device("cuda", local_rank)
+    gen = torch.Generator(device=dev).manual_seed(7)
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peak = float(json.load(f)["bf16_tflops"])
+        kind = "measured"
+    except Exception:
+        peak, kind = 1590.0, "fallback"
+
+    def timed(fn, reps=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize(dev)
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(reps):
+            fn()
+        b.record()
+        torch.cuda.synchronize(dev)
+        return a.elapsed_time(b) / reps
+
+    M, out = 2048, {"M": M, "peak_tflops": peak, "peak_kind": kind, "shapes": {}}
+    for K, N in [(5120, 5120), (5120, 13824), (13824, 5120)]:
+        G = K // 128
+        qw = torch.randint(-2 ** 31, 2 ** 31 - 1, (K // 8, N), device=dev, dtype=torch.int64, generator=gen).to(torch.int32)
+        zw = (torch.randint(0, 2 ** 31 - 1, (G, N // 8), device=dev, dtype=torch.int64, generator=gen) & 0x66666666).to(torch.int32)
+        sc = (torch.rand((G, N), device=dev, generator=gen) * 0.018 + 0.002).half()
+        gi = (torch.randperm(K, device=dev, generator=gen) // 128).int()
+        x = torch.randn((M, K), device=dev, generator=gen).half()
+        dy = torch.randn((M, N), device=dev, generator=gen).half()
+        y = torch.empty((M, N), device=dev, dtype=torch.float16)
+        dx = torch.empty((M, K), device=dev, dtype=torch.float16)
+        w = torch.empty((K, N), device=dev, dtype=torch.float16)
+        fl = 2.0 * M * K * N / 1e9
+        tf = timed(lambda: quant_cuda.gemm(x, qw, y, sc, zw, gi))
+        tb = timed(lambda: quant_cuda.gemm(dy, qw, dx, sc, zw, gi, transpose=True))
+        tr = timed(lambda: quant_cuda.vecquant4recons_v2(qw, w, sc, zw, gi))
+        tm = timed(lambda: torch.matmul(x, w, out=y))
+        tmb = timed(lambda: torch.matmul(dy, w.t(), out=dx))
+        out["shapes"][f"{K}x{N}"] = {
+            "fused_fwd_tflops": round(fl / tf, 1), "fused_bwd_tflops": round(fl / tb, 1),
+            "fused_fwd_frac": round(fl / tf / peak, 3), "fused_bwd_frac": round(fl / tb / peak, 3),
+            "recons_plus_library_gemm_fwd_tflops": round(fl / (tr + tm), 1),
+            "recons_plus_library_gemm_bwd_tflops": round(fl / (tr + tmb), 1), "recons_us": round(tr * 1e3, 1)}
+        del qw, zw, sc, gi, x, dy, y, dx, w
+    torch.cuda.empty_cache()
+    return out
+
+
 def cpu_reference(sample_layers=1, reps=3, threads=None):
     """The reference composition on the host: reconstruct fp16 [K,N] + fp32 matmul, M=1."""
     from oracle import q4_oracle as orc
@@ -316,6 +370,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--copies", type=int, default=8, help="distinct copies of each layer shape per GPU")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-gemm", action="store_true", help="skip the M=2048 fused GEMM leg")
     ap.add_argument("--finetune-steps", type=int, default=5, help="timed LLaMA-7B LoRA finetune steps (0 = skip)")
     ap.add_argument("--finetune-layers", type=int, default=0, help="override the number of decoder layers (0 = 32)")
     args = ap.parse_args()
@@ -347,6 +402,7 @@ def main():
     if world > 1:
         torch.distributed.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     r = run_ours(args, rank, world, local_rank)
+    gm = run_gemm(args, local_rank) if (rank == 0 and not args.no_gemm) else None
     ft = run_finetune(args, rank, world, local_rank) if args.finetune_steps > 0 else None
     if rank == 0:
         peak, peak_kind = load_peaks()
@@ -360,12 +416,14 @@ def main():
                 "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": config,
                 "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                              "frac": round(achieved / peak, 4), "traffic": None, "peak_kind": peak_kind,
-                             "kernel": "gemv_seq_kernel<1>", "avg_launch_us": round(per_launch_us, 3),
+                             "kernel": "gemv_stream_kernel<1,true,true>", "avg_launch_us": round(per_launch_us, 3),
                              "frac_of_nominal_8000": round(achieved / 8000.0, 4)},
                 "per_shape": r["per_shape"],
                 "e2e": {"value": round(e2e, 1), "unit": UNIT, "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": r["d2h"],
                         "api": "matmul_utils_4bit.matmul4bit, pinned host x in, pinned host y out, weights resident"},
                 "gpu_launches": args.steps * r["n_launch"], "clocks": r["clocks"]}
+        if gm is not None:
+            line["gemm"] = gm
         if ft is not None:
             line["finetune"] = ft
         if world == 1 and not args.no_cpu:
