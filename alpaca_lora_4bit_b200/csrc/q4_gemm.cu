@@ -53,6 +53,7 @@ struct GemmParams {
   int M, K, N, G;
   int n_contract_tiles;     // contraction length / 64
   int stages;               // pipeline depth (3 or 4, what shared memory allows)
+  unsigned long long* trace;  // optional per-CTA cycle trace (256 slots), else null
 };
 
 // ---- tcgen05 wrappers --------------------------------------------------------------------------
@@ -107,6 +108,10 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t saddr, uint32_t lbo
 __host__ __device__ constexpr uint32_t idesc_f16(int m, int n, bool b_mn_major) {
   return (1u << 4) | (0u << 7) | (0u << 10) | (0u << 15) | ((b_mn_major ? 1u : 0u) << 16) |
          ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+
+__device__ __forceinline__ void gm_mark(unsigned long long* tr, int slot) {
+  if (tr && slot < 256) tr[((size_t)blockIdx.y * gridDim.x + blockIdx.x) * 256 + slot] = clock64();
 }
 
 __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
@@ -201,8 +206,11 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const GemmParams p) {
       constexpr uint32_t idesc = idesc_f16(128, GM_TILE_N, !TRANSPOSE);
       for (int it = 0; it < T; ++it) {
         const int st = it % S, use = it / S;
+        if (it < 20) gm_mark(p.trace, 3 * it);
         wait_bar(&full_a[st], use & 1, abort_flag);
+        if (it < 20) gm_mark(p.trace, 3 * it + 1);
         wait_bar(&full_b[st], use & 1, abort_flag);
+        if (it < 20) gm_mark(p.trace, 3 * it + 2);
         tc_fence_after();
         const uint32_t a_addr = smem_u32(stages + (size_t)st * GM_STAGE_BYTES);
         const uint32_t b_addr = a_addr + GM_A_BYTES;
@@ -266,8 +274,10 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const GemmParams p) {
           gb = __ldg(reinterpret_cast<const int4*>(p.g_idx + k8 + 4));
         }
       }
+      if (threadIdx.x == 64 && it < 40) gm_mark(p.trace, 64 + 3 * (it / 2));
       if (use > 0 && lane == 0) wait_bar(&empty[st], (use - 1) & 1, abort_flag);
       __syncwarp();
+      if (threadIdx.x == 64 && it < 40) gm_mark(p.trace, 65 + 3 * (it / 2));
       unsigned char* bst = stages + (size_t)st * GM_STAGE_BYTES + GM_A_BYTES;
       // forward: panel (chunk16 / 8) of [64 rows][128 B]; backward: one panel of [128 rows][128 B]
       unsigned char* rows8 = TRANSPOSE ? bst + r * 1024 : bst + (chunk16 >> 3) * 8192 + r * 1024;
@@ -293,7 +303,9 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const GemmParams p) {
       fence_async_smem();                          // generic-proxy stores -> visible to the tensor core
       __syncwarp();
       if (lane == 0) mbar_arrive(&full_b[st]);
+      if (threadIdx.x == 64 && it < 40) gm_mark(p.trace, 66 + 3 * (it / 2));
     }
+    if (threadIdx.x == 64) gm_mark(p.trace, 200);
 
     // ---------------- epilogue: TMEM -> registers -> fp16 -> global ----------------
     if (lane == 0) wait_bar(acc_full, 0, abort_flag);
@@ -328,10 +340,13 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const GemmParams p) {
       }
     }
   }
+  if (threadIdx.x == 64) gm_mark(p.trace, 201);
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_acc, GM_TMEM_COLS);
 }
+
+static unsigned long long* g_gemm_trace = nullptr;
 
 static size_t gemm_smem_bytes(bool transpose, int G, int stages) {
   return 1024 + (size_t)stages * GM_STAGE_BYTES + 256 + (transpose ? 0 : (size_t)2 * G * GM_TILE_N * sizeof(__half));
@@ -362,6 +377,7 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
   const int contract = transpose ? N : K, nout = transpose ? K : N;
   p.n_contract_tiles = contract / GM_TILE_C;
   p.stages = stages;
+  p.trace = g_gemm_trace;
   CUtensorMap amap;
   if (int e = make_tmap_2d(&amap, act, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)contract, (uint64_t)M,
                            (uint64_t)contract * 2, GM_TILE_C, GM_TILE_M, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
@@ -385,6 +401,11 @@ extern "C" int q4_gemm_fwd(const void* x, const int32_t* qweight, void* y, const
 extern "C" int q4_gemm_bwd(const void* dy, const int32_t* qweight, void* dx, const void* scales, const int32_t* qzeros,
                            const int32_t* g_idx, int M, int K, int N, int G, q4_stream_t stream) {
   return gemm_launch(true, dy, qweight, dx, scales, qzeros, g_idx, nullptr, M, K, N, G, stream);
+}
+
+extern "C" int q4_gemm_set_trace(void* device_buffer) {
+  g_gemm_trace = (unsigned long long*)device_buffer;
+  return Q4_OK;
 }
 
 extern "C" int q4_device_status(unsigned* out) {

@@ -134,27 +134,22 @@ __device__ __forceinline__ void gemv_reduce_store(const GemvParams& p, float* re
 }
 
 // ---- sequential groups (group of row k = k / groupsize) and v1 layers: TMA streaming kernel --------
-constexpr int GEMV_BOX_ROWS = 64;                 // packed rows per box (512 k-rows, 16 steps)
-constexpr int GEMV_BOX_STEPS = GEMV_BOX_ROWS / 4;
-constexpr int GEMV_BOX_WORDS = GEMV_BOX_ROWS * GEMV_TN;
-constexpr int GEMV_BOX_BYTES = GEMV_BOX_WORDS * 4;
-constexpr int GEMV_META_ROWS = 17;                // groups one box can touch at groupsize 32, +1 straddle
-constexpr int GEMV_SC_BYTES = 1152;               // 17 rows x 32 halves, rounded up to 128
-constexpr int GEMV_ZP_BYTES = 1152;               // 17 rows x 16 B (v2) or x 64 B (v1 fp16 zeros)
-constexpr int GEMV_STAGE_BYTES = GEMV_BOX_BYTES + GEMV_SC_BYTES + GEMV_ZP_BYTES;
-constexpr int GEMV_STAGES = 11;
-constexpr int GEMV_CWARPS = 16;                   // consumer warps: 4 box phases x 4 row slots
-constexpr int GEMV_PHASES = GEMV_CWARPS / 4;
-constexpr int GEMV_CONSUMERS = GEMV_CWARPS * 32;
-constexpr int GEMV_PWARPS = 4;                    // producer warps, each feeding every 4th box
-constexpr int GEMV_STREAM_THREADS = GEMV_CONSUMERS + 32 * GEMV_PWARPS;
-constexpr uint32_t GEMV_WAIT_LIMIT = 1u << 22;    // polls before a wait is declared dead
-constexpr int GEMV_XS_MAX_BYTES = 49152;          // largest x kept in shared memory
+constexpr int GEMV_UNIT_ROWS = 32;                // packed rows per unit (256 k-rows, 8 steps)
+constexpr int GEMV_UNIT_STEPS = GEMV_UNIT_ROWS / 4;
+constexpr int GEMV_UNIT_BYTES = GEMV_UNIT_ROWS * GEMV_TN * 4;      // 4 KiB
+constexpr int GEMV_META_ROWS = 9;                 // groups one unit can touch at groupsize 32, +1 straddle
+constexpr int GEMV_SC_BYTES = 640;                // 9 rows x 32 halves, rounded up to 128
+constexpr int GEMV_ZP_BYTES = 256;                // 9 rows x 16 B (v2) or 64 B of fp16 zeros (v1)
+constexpr int GEMV_STAGE_BYTES = GEMV_UNIT_BYTES + GEMV_SC_BYTES + GEMV_ZP_BYTES;
+constexpr int GEMV_WSTAGES = 2;                   // stages per warp
+constexpr int GEMV_CWARPS = 16;
+constexpr int GEMV_STREAM_THREADS = GEMV_CWARPS * 32;
+constexpr int GEMV_XS_MAX_BYTES = 40960;          // largest x (+ its chunk table) kept in shared memory
 
 struct GemvStreamParams {
   GemvParams g;
-  int boxes_per_tile, total_boxes, steps_per_tile;
-  int meta_rows;                                  // group rows fetched with each box
+  int units_per_tile, total_units, steps_per_tile;
+  int meta_rows;                                  // group rows fetched with each unit
   uint32_t stage_tx;                              // bytes TMA delivers per stage
   float* cta_part;                                // [grid][2][MT*8][32]
   unsigned* status;
@@ -164,15 +159,16 @@ struct GemvStreamParams {
 
 template <int MT>
 __host__ __device__ constexpr size_t gemv_stream_smem() {
-  return (size_t)GEMV_STAGES * GEMV_STAGE_BYTES + sizeof(float) * 2 * GEMV_CWARPS * MT * 8 * GEMV_TN + 2 * GEMV_STAGES * 8 + 16;
+  return (size_t)GEMV_CWARPS * GEMV_WSTAGES * GEMV_STAGE_BYTES + sizeof(float) * GEMV_CWARPS * MT * 8 * GEMV_TN +
+         GEMV_CWARPS * GEMV_WSTAGES * 8 + 16;
 }
 
 __device__ __forceinline__ void trace_mark(unsigned long long* tr, int slot) {
   if (tr && slot < 64) tr[(size_t)blockIdx.x * 64 + slot] = clock64();
 }
 
-// CTA that owns box b when `nb` boxes are dealt to `G` CTAs as [c*nb/G, (c+1)*nb/G).
-__device__ __forceinline__ int box_owner(long long b, int G, int nb) { return (int)(((b + 1) * G + nb - 1) / nb) - 1; }
+// CTA that owns unit u when `nu` units are dealt to `G` CTAs as [c*nu/G, (c+1)*nu/G).
+__device__ __forceinline__ int unit_owner(long long u, int G, int nu) { return (int)(((u + 1) * G + nu - 1) / nu) - 1; }
 
 // MMA whose accumulator starts at zero (first k-step of a group).
 __device__ __forceinline__ void mma16816_first(float (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
@@ -185,11 +181,21 @@ __device__ __forceinline__ void named_bar_arrive(int id, int threads) {
   asm volatile("bar.arrive %0, %1;" ::"r"(id), "r"(threads) : "memory");
 }
 
-// FAST: the group size is a multiple of 128 rows (or the layer is v1), so the 128 rows a warp
-// takes from a box always lie in one group: no per-step group test, accumulators local to the box.
-// XS (needs FAST, M <= 8, K % 128 == 0, M*K*2 <= GEMV_XS_MAX_BYTES): x is copied once per CTA into
-// shared memory in the order the MMA wants it, the odd k of every 8-block pre-divided by 16 so that
-// the high nibble of each byte can be used where it sits (w & 0x00F000F0 | 0x6400 = 1024 + 16 q, no
+// One CTA per SM, 16 warps, every warp an independent stream processor:
+//   * qweight is cut into units of 32 packed rows x 32 columns (4 KiB = 256 k-rows x 32 outputs); the
+//     units, ordered column tile by column tile, are dealt to the CTAs in equal contiguous runs
+//     (stream-K) and inside a CTA round-robin to the warps.
+//   * A warp fetches its own units with TMA (weights + the scale / zero-point rows the unit touches)
+//     into a private two-stage ring and waits only on its own mbarriers, so in the steady state
+//     there is no synchronisation between warps at all; for the LLaMA-7B shapes nearly every unit of
+//     the launch is in flight within the first microsecond.
+//   * At the end of a column tile every warp leaves its partial sums in shared memory and one warp
+//     adds them (fixed order) and stores y, or hands a partial tile to the last CTA to arrive.
+// FAST: the group size is a multiple of 128 rows (or the layer is v1), so each 128-row half of a unit
+// lies in one group: no per-step group test.
+// XS (needs FAST, M <= 8, K % 128 == 0, x + its table <= GEMV_XS_MAX_BYTES): x is copied once per CTA
+// into shared memory in the order the MMA wants it, the odd k of every 8-block pre-divided by 16 so
+// that the high nibble of each byte can be used where it sits (w & 0x00F000F0 | 0x6400 = 1024 + 16 q, no
 // shift), and the per-128-row sums that take the 1024 / 64 offsets and the zero point out again are
 // tabulated once.  That removes the x permutes, half of the shifts and the all-ones MMA from the loop.
 template <int MT, bool FAST, bool XS>
@@ -198,23 +204,24 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
                    const __grid_constant__ CUtensorMap zmap, const GemvStreamParams sp) {
   extern __shared__ __align__(128) unsigned char smem[];
   const GemvParams& p = sp.g;
-  constexpr int RED_FLOATS = GEMV_CWARPS * MT * 8 * GEMV_TN;          // one buffer of warp partials
-  float* red = reinterpret_cast<float*>(smem + (size_t)GEMV_STAGES * GEMV_STAGE_BYTES);   // [2][16][MT*8][32]
-  uint64_t* full = reinterpret_cast<uint64_t*>(red + 2 * RED_FLOATS);
-  uint64_t* empty = full + GEMV_STAGES;
-  volatile int* flags = reinterpret_cast<volatile int*>(empty + GEMV_STAGES);   // [0] abort
+  constexpr int RED_FLOATS = GEMV_CWARPS * MT * 8 * GEMV_TN;
+  float* red = reinterpret_cast<float*>(smem + (size_t)GEMV_CWARPS * GEMV_WSTAGES * GEMV_STAGE_BYTES);   // [16][MT*8][32]
+  uint64_t* full = reinterpret_cast<uint64_t*>(red + RED_FLOATS);                                         // [16][2]
+  volatile int* flags = reinterpret_cast<volatile int*>(full + GEMV_CWARPS * GEMV_WSTAGES);              // [0] abort
   // XS only: [16 B of zeros][chunk table: K/128 x 8 float2][x rows, MMA order]
   unsigned char* xs_base = smem + gemv_stream_smem<MT>();
   float2* ctab = reinterpret_cast<float2*>(xs_base + 16);
   __half* xs_buf = reinterpret_cast<__half*>(xs_base + 16 + (size_t)(sp.g.K / 128) * 64);
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int nb = sp.total_boxes, G = gridDim.x, bpt = sp.boxes_per_tile;
-  const int b0 = (int)((long long)blockIdx.x * nb / G), b1 = (int)((long long)(blockIdx.x + 1) * nb / G);
+  const int nu = sp.total_units, G = gridDim.x, upt = sp.units_per_tile;
+  const int u0 = (int)((long long)blockIdx.x * nu / G), u1 = (int)((long long)(blockIdx.x + 1) * nu / G);
   const int gs = p.groupsize;
+  unsigned char* my_stages = smem + (size_t)warp * GEMV_WSTAGES * GEMV_STAGE_BYTES;
+  uint64_t* my_full = full + warp * GEMV_WSTAGES;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < GEMV_STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 4); }
+    for (int i = 0; i < GEMV_CWARPS * GEMV_WSTAGES; ++i) mbar_init(&full[i], 1);
     flags[0] = 0;
     mbar_fence_init();
     tma_prefetch_desc(&wmap); tma_prefetch_desc(&smap); tma_prefetch_desc(&zmap);
@@ -222,37 +229,27 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
   __syncthreads();
   pdl_launch_dependents();
 
-  if (warp >= GEMV_CWARPS) {
-    // ---------------- producers: one thread per warp, each feeding every 4th box of the ring ------
-    // (issuing a TMA tile load costs a few hundred cycles; four issuers keep the ring ahead)
+  // Fetch this warp's n-th unit (CTA-local unit warp + 16 n) into stage n % 2: lanes 0..2 issue one copy each.
+  auto issue = [&](int n) {
+    const int u = u0 + warp + GEMV_CWARPS * n;
+    if (u >= u1) return;
+    const int tile = u / upt, ux = u - tile * upt;
+    unsigned char* dst = my_stages + (size_t)(n % GEMV_WSTAGES) * GEMV_STAGE_BYTES;
+    uint64_t* bar = &my_full[n % GEMV_WSTAGES];
+    const int grow0 = p.v1 ? 0 : (ux * GEMV_UNIT_ROWS * 8) / gs;
     if (lane == 0) {
-      const int pw = warp - GEMV_CWARPS;
-      int tile = b0 / bpt, bx = b0 - tile * bpt;
-      for (int i = b0; i < b1; ++i, ++bx) {
-        if (bx == bpt) { bx = 0; ++tile; }
-        const int it = i - b0, st = it % GEMV_STAGES, use = it / GEMV_STAGES;
-        if ((it % GEMV_PWARPS) != pw) continue;
-        if (use > 0) {
-          bool ok = false;
-          const uint32_t lim = flags[0] ? 4u : 20000u;
-          for (uint32_t tr = 0; tr < lim && !ok; ++tr) ok = mbar_try_wait_sleep(&empty[st], (use - 1) & 1, 2000u);
-          if (!ok) { flags[0] = 1; atomicExch(sp.status, Q4_STATUS_WAIT_EXPIRED); }
-        }
-        trace_mark(sp.trace, 32 + it);
-        unsigned char* dst = smem + (size_t)st * GEMV_STAGE_BYTES;
-        const int grow0 = p.v1 ? 0 : (bx * GEMV_BOX_ROWS * 8) / gs;
-        mbar_arrive_expect_tx(&full[st], sp.stage_tx);
-        tma_load_2d(dst, &wmap, tile * GEMV_TN, bx * GEMV_BOX_ROWS, &full[st]);
-        tma_load_2d(dst + GEMV_BOX_BYTES, &smap, tile * GEMV_TN, grow0, &full[st]);
-        tma_load_2d(dst + GEMV_BOX_BYTES + GEMV_SC_BYTES, &zmap, p.v1 ? tile * GEMV_TN : tile * (GEMV_TN / 8), grow0, &full[st]);
-      }
+      mbar_arrive_expect_tx(bar, sp.stage_tx);
+      tma_load_2d(dst, &wmap, tile * GEMV_TN, ux * GEMV_UNIT_ROWS, bar);
+    } else if (lane == 1) {
+      tma_load_2d(dst + GEMV_UNIT_BYTES, &smap, tile * GEMV_TN, grow0, bar);
+    } else if (lane == 2) {
+      tma_load_2d(dst + GEMV_UNIT_BYTES + GEMV_SC_BYTES, &zmap, p.v1 ? tile * GEMV_TN : tile * (GEMV_TN / 8), grow0, bar);
     }
-    return;
-  }
+  };
+  issue(0);
+  issue(1);                                              // weights never depend on an earlier kernel
 
-  // ---------------- consumers: warp = (box phase, 16-row slot) ----------------
   const int g = lane >> 2, t = lane & 3;
-  const int phase = warp >> 2, slot = warp & 3;
   const int K = p.K;
   const int steps_per_group = gs >> 5;
   const bool xok0 = g < p.M, xok1 = (g + 8) < p.M;
@@ -269,12 +266,12 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
   // y += s * (acc - (1024 + z + 1) * xsum) for the group whose scales sit in row `grow` of the stage;
   // c / co are the raw MMA sums, one set per k-step parity so consecutive MMAs never wait on each other
   auto flush = [&](const unsigned char* stg, int grow, float (&c)[MT][2][2][4], float (&co)[MT][2][4], int chunk) {
-    const uint2 sc = *reinterpret_cast<const uint2*>(stg + GEMV_BOX_BYTES + grow * 64 + 8 * g);
+    const uint2 sc = *reinterpret_cast<const uint2*>(stg + GEMV_UNIT_BYTES + grow * 64 + 8 * g);
     const float2 s01 = __half22float2(as_h2(sc.x)), s23 = __half22float2(as_h2(sc.y));
     const float s[4] = {s01.x, s01.y, s23.x, s23.y};
     float zz[4], zf[4];
     if (!p.v1) {
-      const uint32_t zw = *reinterpret_cast<const uint32_t*>(stg + GEMV_BOX_BYTES + GEMV_SC_BYTES + grow * 16 + 4 * (g >> 1));
+      const uint32_t zw = *reinterpret_cast<const uint32_t*>(stg + GEMV_UNIT_BYTES + GEMV_SC_BYTES + grow * 16 + 4 * (g >> 1));
       const uint32_t zb = zw >> (16 * (g & 1));
       // 1024 + z through the fp16 exponent trick: (z | 0x6400) is 1024 + z exactly
       const float2 za = __half22float2(as_h2(((zb & 0xFu) | ((zb & 0xF0u) << 12)) | 0x64006400u));
@@ -284,7 +281,7 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
 #pragma unroll
       for (int i = 0; i < 4; ++i) zf[i] = 0.f;
     } else {          // W = s*q - zero: only the offsets scale with s, the float zero does not
-      const uint2 zh = *reinterpret_cast<const uint2*>(stg + GEMV_BOX_BYTES + GEMV_SC_BYTES + 8 * g);
+      const uint2 zh = *reinterpret_cast<const uint2*>(stg + GEMV_UNIT_BYTES + GEMV_SC_BYTES + 8 * g);
       const float2 z01 = __half22float2(as_h2(zh.x)), z23 = __half22float2(as_h2(zh.y));
       zf[0] = z01.x; zf[1] = z01.y; zf[2] = z23.x; zf[3] = z23.y;
 #pragma unroll
@@ -312,17 +309,14 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
     }
   };
 
-  // End of this CTA's run of boxes [seg_first, seg_last] in column tile `tile`.  Every warp leaves
-  // its sums in red[buf]; only the last consumer warp waits for the others, adds the 16 partials
-  // in warp order and either stores y (the run covers the whole tile) or hands the tile's partial
-  // to the last CTA to arrive.  The other warps go straight on to the next tile.
-  //   named barrier 1+buf: "red[buf] is complete"   (15 warps arrive, the reducer syncs)
-  //   named barrier 3+buf: "red[buf] may be reused" (the reducer arrives, 15 warps sync two tiles later)
+  // End of this CTA's run of units [seg_first, seg_last] in column tile `tile`.  Every warp leaves its
+  // sums in `red`; only the last warp waits for the others, adds the 16 partials in warp order and
+  // either stores y (the run covers the whole tile) or hands the tile's partial to the last CTA to arrive.
+  //   named barrier 1: "red is complete"   (15 warps arrive, the reducer syncs)
+  //   named barrier 2: "red may be reused" (the reducer arrives, 15 warps sync at the next tile)
   auto finish_tile = [&](int tile, int seq, int seg_first, int seg_last) {
-    const int buf = seq & 1;
-    float* mine = red + (size_t)buf * RED_FLOATS;
     const bool reducer = warp == GEMV_CWARPS - 1;
-    if (!reducer && seq >= 2) named_bar_sync(3 + buf, GEMV_CONSUMERS);
+    if (!reducer && seq >= 1) named_bar_sync(2, GEMV_STREAM_THREADS);
 #pragma unroll
     for (int mt = 0; mt < MT; ++mt)
 #pragma unroll
@@ -330,28 +324,28 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
           const int col = 4 * g + 2 * j + (i >> 1), b = mt * 8 + 2 * t + (i & 1);
-          mine[(warp * (MT * 8) + b) * GEMV_TN + col] = yacc[mt][j][i];
+          red[(warp * (MT * 8) + b) * GEMV_TN + col] = yacc[mt][j][i];
           yacc[mt][j][i] = 0.f;
         }
     if (!reducer) {
       __threadfence_block();
-      named_bar_arrive(1 + buf, GEMV_CONSUMERS);
+      named_bar_arrive(1, GEMV_STREAM_THREADS);
       return;
     }
-    named_bar_sync(1 + buf, GEMV_CONSUMERS);
+    named_bar_sync(1, GEMV_STREAM_THREADS);
     const int tc0 = tile * GEMV_TN, col = lane;
-    const bool whole = seg_first == 0 && seg_last == bpt - 1;
-    const int c_first = box_owner((long long)tile * bpt, G, nb), c_last = box_owner((long long)tile * bpt + bpt - 1, G, nb);
+    const bool whole = seg_first == 0 && seg_last == upt - 1;
+    const int c_first = unit_owner((long long)tile * upt, G, nu), c_last = unit_owner((long long)tile * upt + upt - 1, G, nu);
     // slot 0 of a CTA's partials: the run continues a tile begun by an earlier CTA; slot 1: it begins the tile
     float* part = sp.cta_part + ((size_t)blockIdx.x * 2 + (seg_first == 0 ? 1 : 0)) * (MT * 8) * GEMV_TN;
     for (int r = 0; r < p.M; ++r) {
       float v = 0.f;
 #pragma unroll
-      for (int w = 0; w < GEMV_CWARPS; ++w) v += mine[(w * (MT * 8) + r) * GEMV_TN + col];
+      for (int w = 0; w < GEMV_CWARPS; ++w) v += red[(w * (MT * 8) + r) * GEMV_TN + col];
       if (whole) store_y(p, r, tc0 + col, v);
       else __stcg(part + r * GEMV_TN + col, v);
     }
-    named_bar_arrive(3 + buf, GEMV_CONSUMERS);
+    named_bar_arrive(2, GEMV_STREAM_THREADS);
     if (whole) return;
     __threadfence();
     __syncwarp();
@@ -375,9 +369,9 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
   if constexpr (XS) {
     const int blocks_per_row = K >> 3;                   // 8-element blocks per x row, 16 per 128-row chunk
     if (threadIdx.x < 4) reinterpret_cast<uint32_t*>(xs_base)[threadIdx.x] = 0u;
-    for (int idx = threadIdx.x; idx < (K >> 7) * 8; idx += GEMV_CONSUMERS)
+    for (int idx = threadIdx.x; idx < (K >> 7) * 8; idx += GEMV_STREAM_THREADS)
       if ((idx & 7) >= p.M) ctab[idx] = make_float2(0.f, 0.f);
-    for (int idx = threadIdx.x; idx < p.M * blocks_per_row; idx += GEMV_CONSUMERS) {
+    for (int idx = threadIdx.x; idx < p.M * blocks_per_row; idx += GEMV_STREAM_THREADS) {
       const int m = idx / blocks_per_row, blk = idx - m * blocks_per_row;
       const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)m * K + 8 * blk));
       const __half2 h01 = as_h2(v.x), h23 = as_h2(v.y), h45 = as_h2(v.z), h67 = as_h2(v.w);
@@ -392,131 +386,384 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
       // the odd elements sit in x' as x/16, so their 1024 offset comes back as 64 * x
       if ((lane & 15) == 0) ctab[(size_t)(blk >> 4) * 8 + m] = make_float2(1024.f * se + 64.f * so, se + so);
     }
-    named_bar_sync(5, GEMV_CONSUMERS);
+    named_bar_sync(5, GEMV_STREAM_THREADS);
   }
-  uint4 xn[MT][4];
-  auto load_x = [&](int bxt) {
+  if (threadIdx.x == 0) trace_mark(sp.trace, 2);
+
+  // x of one 128-row half of a unit: four steps, rows 16*h .. 16*h+15 of the unit
+  auto load_x = [&](uint4 (&xv)[MT][4], int ux, int h) {
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
-      const int stp = bxt * GEMV_BOX_STEPS + 4 * slot + u;
+      const int stp = ux * GEMV_UNIT_STEPS + 4 * h + u;
 #pragma unroll
       for (int mt = 0; mt < MT; ++mt) {
         const bool ok = (mt ? xok1 : xok0) && stp < sp.steps_per_tile;
         if constexpr (XS)
-          xn[mt][u] = ok ? *reinterpret_cast<const uint4*>(xs_buf + (size_t)g * K + 8 * t + 32 * stp)
+          xv[mt][u] = ok ? *reinterpret_cast<const uint4*>(xs_buf + (size_t)g * K + 8 * t + 32 * stp)
                          : *reinterpret_cast<const uint4*>(xs_base);
         else
-          xn[mt][u] = ok ? __ldg(reinterpret_cast<const uint4*>(xrow + (size_t)(8 * mt) * K + 32 * stp))
+          xv[mt][u] = ok ? __ldg(reinterpret_cast<const uint4*>(xrow + (size_t)(8 * mt) * K + 32 * stp))
                          : make_uint4(0, 0, 0, 0);
       }
     }
   };
-  // This warp owns the boxes b0 + phase, b0 + phase + 4, ...; walk them tile by tile.
-  int i = b0 + phase;                                    // next owned box (global index)
-  const int tile_first = b0 / bpt, tile_last = (b1 - 1) / bpt;
-  int bx = i - tile_first * bpt;                         // may run past bpt: brought back per tile below
-  if (i < b1) load_x(bx % bpt);
-  int nbox = 0;
-  for (int tile = tile_first; tile <= tile_last; ++tile, bx -= bpt) {
-    const int seg_b1 = min(b1, (tile + 1) * bpt);
-    for (; i < seg_b1; i += GEMV_PHASES, bx += GEMV_PHASES, ++nbox) {
-      const int it = i - b0, st = it % GEMV_STAGES, use = it / GEMV_STAGES;
-      // x of this warp's four steps (rows 16*slot .. 16*slot+15 of the box) was requested one owned
-      // box ago; request the next one now so that its latency hides behind this box's math
+
+  const int tile_first = u0 / upt, tile_last = (u1 - 1) / upt;
+  int n = 0;                                             // index of this warp's next unit
+  for (int tile = tile_first; tile <= tile_last; ++tile) {
+    const int seg_u1 = min(u1, (tile + 1) * upt);
+    for (int u = u0 + warp + GEMV_CWARPS * n; u < seg_u1; ++n, u += GEMV_CWARPS) {
+      const int ux = u - tile * upt;
+      const int st = n % GEMV_WSTAGES, use = n / GEMV_WSTAGES;
       uint4 xv[MT][4];
-      int step[4];
-#pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        step[u] = bx * GEMV_BOX_STEPS + 4 * slot + u;
-#pragma unroll
-        for (int mt = 0; mt < MT; ++mt) xv[mt][u] = xn[mt][u];
-      }
-      if (i + GEMV_PHASES < b1) {
-        int bxn = bx + GEMV_PHASES;
-        while (bxn >= bpt) bxn -= bpt;
-        load_x(bxn);
-      }
-      if (!mbar_wait_warp(&full[st], use & 1, flags[0] ? 4u : 20000u)) {
+      load_x(xv, ux, 0);
+      if (!mbar_wait_warp(&my_full[st], use & 1, flags[0] ? 4u : 20000u)) {
         flags[0] = 1; atomicExch(sp.status, Q4_STATUS_WAIT_EXPIRED);
       }
-      if (threadIdx.x == 0) trace_mark(sp.trace, 2 + 2 * nbox);
-      const unsigned char* stg = smem + (size_t)st * GEMV_STAGE_BYTES;
+      if (warp == 0 && lane == 0) trace_mark(sp.trace, 3 + 2 * n);
+      const unsigned char* stg = my_stages + (size_t)st * GEMV_STAGE_BYTES;
       const uint32_t* box = reinterpret_cast<const uint32_t*>(stg);
-      const int grp0 = p.v1 ? 0 : (sp.group_shift >= 0 ? ((bx * GEMV_BOX_STEPS) >> sp.group_shift) : (bx * GEMV_BOX_ROWS * 8) / gs);
-      uint4 wv[4];
+      const int grp0 = p.v1 ? 0 : (sp.group_shift >= 0 ? ((ux * GEMV_UNIT_STEPS) >> sp.group_shift) : (ux * GEMV_UNIT_ROWS * 8) / gs);
+#pragma unroll 1
+      for (int h = 0; h < 2; ++h) {
+        if (h == 1) load_x(xv, ux, 1);
+        const int step0 = ux * GEMV_UNIT_STEPS + 4 * h;
+        if (step0 >= sp.steps_per_tile) break;           // rows past K were zero-filled by TMA
+        uint4 wv[4];
 #pragma unroll
-      for (int u = 0; u < 4; ++u)
-        wv[u] = *reinterpret_cast<const uint4*>(box + (4 * (4 * slot + u) + t) * GEMV_TN + 4 * g);
-      float c[MT][2][2][4], co[MT][2][4];
-      int cur_grp = -1;
-      bool fresh = true;
+        for (int uu = 0; uu < 4; ++uu)
+          wv[uu] = *reinterpret_cast<const uint4*>(box + (4 * (4 * h + uu) + t) * GEMV_TN + 4 * g);
+        float c[MT][2][2][4], co[MT][2][4];
+        int cur_grp = -1;
+        bool fresh = true;
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
-        if (step[u] >= sp.steps_per_tile) break;         // rows past K were zero-filled by TMA
-        if (!FAST) {
-          const int grp = sp.group_shift >= 0 ? (step[u] >> sp.group_shift) : step[u] / steps_per_group;
-          if (grp != cur_grp) {
-            if (cur_grp >= 0) flush(stg, cur_grp - grp0, c, co, 0);
-            cur_grp = grp; fresh = true;
+        for (int uu = 0; uu < 4; ++uu) {
+          const int step = step0 + uu;
+          if (step >= sp.steps_per_tile) break;
+          if (!FAST) {
+            const int grp = sp.group_shift >= 0 ? (step >> sp.group_shift) : step / steps_per_group;
+            if (grp != cur_grp) {
+              if (cur_grp >= 0) flush(stg, cur_grp - grp0, c, co, 0);
+              cur_grp = grp; fresh = true;
+            }
           }
-        }
-        const uint32_t w[4] = {wv[u].x, wv[u].y, wv[u].z, wv[u].w};
-        uint32_t pr[4][4];                      // pr[word][m] = (q_m, q_m+4) + 1024  (XS, odd m: 16 q + 1024)
+          const uint32_t w[4] = {wv[uu].x, wv[uu].y, wv[uu].z, wv[uu].w};
+          uint32_t pr[4][4];                      // pr[word][m] = (q_m, q_m+4) + 1024  (XS, odd m: 16 q + 1024)
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          if constexpr (XS) {
+          for (int q = 0; q < 4; ++q) {
+            if constexpr (XS) {
+              const uint32_t w8 = w[q] >> 8;
+              pr[q][0] = (w[q] & 0x000F000Fu) | 0x64006400u;
+              pr[q][1] = (w[q] & 0x00F000F0u) | 0x64006400u;
+              pr[q][2] = (w8 & 0x000F000Fu) | 0x64006400u;
+              pr[q][3] = (w8 & 0x00F000F0u) | 0x64006400u;
+            } else {
+              pr[q][0] = (w[q] & 0x000F000Fu) | 0x64006400u;
+              pr[q][1] = ((w[q] >> 4) & 0x000F000Fu) | 0x64006400u;
+              pr[q][2] = ((w[q] >> 8) & 0x000F000Fu) | 0x64006400u;
+              pr[q][3] = ((w[q] >> 12) & 0x000F000Fu) | 0x64006400u;
+            }
+          }
+          const bool first = FAST ? (uu == 0) : fresh;
+#pragma unroll
+          for (int mt = 0; mt < MT; ++mt) {
+            const uint4 xq = xv[mt][uu];            // x[k..k+7] of batch row g (+8); XS: already in MMA order
+            uint32_t xb[4];
+            if constexpr (XS) {
+              xb[0] = xq.x; xb[1] = xq.y; xb[2] = xq.z; xb[3] = xq.w;
+            } else {
+              xb[0] = prmt(xq.x, xq.z, 0x5410); xb[1] = prmt(xq.x, xq.z, 0x7632);    // (x0,x4) (x1,x5)
+              xb[2] = prmt(xq.y, xq.w, 0x5410); xb[3] = prmt(xq.y, xq.w, 0x7632);    // (x2,x6) (x3,x7)
+            }
+#pragma unroll
+            for (int ks = 0; ks < 2; ++ks) {
+              const uint32_t bb0 = xb[2 * ks], bb1 = xb[2 * ks + 1];
+              if (first) {
+                mma16816_first(c[mt][0][ks], pr[0][2 * ks], pr[1][2 * ks], pr[0][2 * ks + 1], pr[1][2 * ks + 1], bb0, bb1);
+                mma16816_first(c[mt][1][ks], pr[2][2 * ks], pr[3][2 * ks], pr[2][2 * ks + 1], pr[3][2 * ks + 1], bb0, bb1);
+                if constexpr (!XS) mma16816_first(co[mt][ks], 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, bb0, bb1);
+              } else {
+                mma16816(c[mt][0][ks], pr[0][2 * ks], pr[1][2 * ks], pr[0][2 * ks + 1], pr[1][2 * ks + 1], bb0, bb1);
+                mma16816(c[mt][1][ks], pr[2][2 * ks], pr[3][2 * ks], pr[2][2 * ks + 1], pr[3][2 * ks + 1], bb0, bb1);
+                if constexpr (!XS) mma16816(co[mt][ks], 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, bb0, bb1);
+              }
+            }
+          }
+          fresh = false;
+        }
+        // scales live in this stage: settle the open group before the stage is refilled
+        if (FAST) {
+          flush(stg, p.v1 ? 0 : ((sp.group_shift >= 0 ? (step0 >> sp.group_shift) : step0 / steps_per_group) - grp0), c, co, step0 >> 2);
+        } else if (cur_grp >= 0) {
+          flush(stg, cur_grp - grp0, c, co, 0);
+        }
+      }
+      __syncwarp();
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // our reads before the next TMA write
+      issue(n + GEMV_WSTAGES);
+      if (warp == 0 && lane == 0) trace_mark(sp.trace, 4 + 2 * n);
+    }
+    if (threadIdx.x == 0) trace_mark(sp.trace, 30);
+    finish_tile(tile, tile - tile_first, max(u0, tile * upt) - tile * upt, seg_u1 - 1 - tile * upt);
+    if (threadIdx.x == 0) trace_mark(sp.trace, 31);
+  }
+}
+
+// ---- M <= 2, sequential groups of a multiple of 128 rows: the lean decode kernel --------------------
+// Same decomposition as gemv_stream_kernel (independent per-warp TMA streams over 4 KiB units), with
+// everything per-step stripped to the minimum:
+//   * x of a unit (256 halves per batch row) arrives in the warp's stage with cp.async next to the
+//     weights and is rewritten in place into MMA order, odd elements divided by 16, so the B fragment of
+//     a step is one LDS.128 and the high nibbles of the packed words are used where they sit
+//     (w & 0x00F000F0 | 0x6400 = 1024 + 16 q): 5 integer instructions per 8 weights.
+//   * the +1024 / +64 offsets and the zero points are not handled per MMA fragment: one lane per
+//     column subtracts s * (offset_sum + (z+1) * x_sum) once per group, from sums of x computed once
+//     per unit with warp shuffles.
+constexpr int GF_WARPS = 16;
+constexpr int GF_THREADS = GF_WARPS * 32;
+constexpr int GF_STAGES = 2;
+constexpr int GF_META_OFF = GEMV_UNIT_BYTES;          // scales: 2 rows x 64 B
+constexpr int GF_ZP_OFF = GF_META_OFF + 128;          // zero points: 2 rows x 16 B
+constexpr int GF_X_OFF = GF_ZP_OFF + 128;             // x: MR rows x 512 B, then the sums: 2 chunks x MR x float2
+
+template <int MR>
+__host__ __device__ constexpr int gf_stage_bytes() { return (GF_X_OFF + MR * 512 + 64 + 127) / 128 * 128; }   // TMA needs 128 B
+template <int MR>
+__host__ __device__ constexpr size_t gf_smem_bytes() {
+  return (size_t)GF_WARPS * GF_STAGES * gf_stage_bytes<MR>() + sizeof(float) * GF_WARPS * MR * GEMV_TN + GF_WARPS * GF_STAGES * 8 + 64 + GF_WARPS * 512;
+}
+
+__device__ __forceinline__ void cp_async16_zfill(void* dst, const void* src, bool valid) {
+  const uint32_t n = valid ? 16u : 0u;
+  asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(n) : "memory");
+}
+__device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+template <int MR>
+__global__ void __launch_bounds__(GF_THREADS, 1)
+gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap,
+                 const __grid_constant__ CUtensorMap zmap, const GemvStreamParams sp) {
+  extern __shared__ __align__(128) unsigned char smem[];
+  const GemvParams& p = sp.g;
+  constexpr int STG = gf_stage_bytes<MR>();
+  float* red = reinterpret_cast<float*>(smem + (size_t)GF_WARPS * GF_STAGES * STG);            // [16][MR][32]
+  uint64_t* full = reinterpret_cast<uint64_t*>(red + GF_WARPS * MR * GEMV_TN);                  // [16][2]
+  volatile int* flags = reinterpret_cast<volatile int*>(full + GF_WARPS * GF_STAGES);          // [0] abort
+  unsigned char* zero_rows = reinterpret_cast<unsigned char*>(const_cast<int*>(flags)) + 64;   // [16 warps][512 B] of zeros
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nu = sp.total_units, G = gridDim.x, upt = sp.units_per_tile;
+  const int u0 = (int)((long long)blockIdx.x * nu / G), u1 = (int)((long long)(blockIdx.x + 1) * nu / G);
+  const int K = p.K, gs = p.groupsize;
+  unsigned char* my_stages = smem + (size_t)warp * GF_STAGES * STG;
+  uint64_t* my_full = full + warp * GF_STAGES;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < GF_WARPS * GF_STAGES; ++i) mbar_init(&full[i], 1 + 32);   // TMA arrive + 32 cp.async arrivals
+    flags[0] = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&wmap); tma_prefetch_desc(&smap); tma_prefetch_desc(&zmap);
+  }
+  for (int i = threadIdx.x; i < GF_WARPS * 128; i += GF_THREADS) reinterpret_cast<uint32_t*>(zero_rows)[i] = 0u;
+  __syncthreads();
+  pdl_launch_dependents();
+
+  // weights (+ scales, zero points) of this warp's n-th unit: lanes 0..2 issue one TMA copy each
+  auto issue_w = [&](int n) {
+    const int u = u0 + warp + GF_WARPS * n;
+    if (u >= u1) return;
+    const int tile = u / upt, ux = u - tile * upt;        // one division per unit, on three lanes only below
+    unsigned char* dst = my_stages + (size_t)(n % GF_STAGES) * STG;
+    uint64_t* bar = &my_full[n % GF_STAGES];
+    const int grow0 = sp.group_shift >= 0 ? ((ux * GEMV_UNIT_STEPS) >> sp.group_shift) : (ux * GEMV_UNIT_ROWS * 8) / gs;
+    if (lane == 0) {
+      mbar_arrive_expect_tx(bar, sp.stage_tx);
+      tma_load_2d(dst, &wmap, tile * GEMV_TN, ux * GEMV_UNIT_ROWS, bar);
+    } else if (lane == 1) {
+      tma_load_2d(dst + GF_META_OFF, &smap, tile * GEMV_TN, grow0, bar);
+    } else if (lane == 2) {
+      tma_load_2d(dst + GF_ZP_OFF, &zmap, tile * (GEMV_TN / 8), grow0, bar);
+    }
+  };
+  // x of the same unit: every lane copies its 8 elements of every batch row, then arrives on the barrier
+  auto issue_x = [&](int n) {
+    const int u = u0 + warp + GF_WARPS * n;
+    if (u >= u1) return;
+    const int ux = u % upt;
+    unsigned char* dst = my_stages + (size_t)(n % GF_STAGES) * STG + GF_X_OFF;
+    const int k = ux * 256 + 8 * lane;
+#pragma unroll
+    for (int r = 0; r < MR; ++r)
+      cp_async16_zfill(dst + r * 512 + 16 * lane, p.x + (size_t)(r < p.M ? r : 0) * K + (k < K ? k : 0), r < p.M && k < K);
+    cp_async_arrive_noinc(&my_full[n % GF_STAGES]);
+  };
+  issue_w(0);
+  issue_w(1);                                            // weights never depend on an earlier kernel
+  pdl_wait();                                            // x, y and the workspace belong to the stream order
+  issue_x(0);
+  issue_x(1);
+  if (threadIdx.x == 0) trace_mark(sp.trace, 0);
+
+  const int g = lane >> 2, t = lane & 3;
+  float yacc[2][4], ycorr[MR];
+#pragma unroll
+  for (int j = 0; j < 2; ++j)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) yacc[j][i] = 0.f;
+#pragma unroll
+  for (int r = 0; r < MR; ++r) ycorr[r] = 0.f;
+
+  auto finish_tile = [&](int tile, int seq, int seg_first, int seg_last) {
+    const bool reducer = warp == GF_WARPS - 1;
+    if (!reducer && seq >= 1) named_bar_sync(2, GF_THREADS);
+    float* mine = red + warp * MR * GEMV_TN;
+    if (t == 0) {                                        // batch columns 0 and 1 live in the t == 0 lanes
+#pragma unroll
+      for (int j = 0; j < 2; ++j)
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          if ((i & 1) < MR) mine[(i & 1) * GEMV_TN + 4 * g + 2 * j + (i >> 1)] = yacc[j][i];
+    }
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) yacc[j][i] = 0.f;
+    __syncwarp();
+#pragma unroll
+    for (int r = 0; r < MR; ++r) { mine[r * GEMV_TN + lane] -= ycorr[r]; ycorr[r] = 0.f; }
+    if (!reducer) {
+      __threadfence_block();
+      named_bar_arrive(1, GF_THREADS);
+      return;
+    }
+    named_bar_sync(1, GF_THREADS);
+    const int tc0 = tile * GEMV_TN, col = lane;
+    const bool whole = seg_first == 0 && seg_last == upt - 1;
+    const int c_first = unit_owner((long long)tile * upt, G, nu), c_last = unit_owner((long long)tile * upt + upt - 1, G, nu);
+    float* part = sp.cta_part + ((size_t)blockIdx.x * 2 + (seg_first == 0 ? 1 : 0)) * 16 * GEMV_TN;
+    for (int r = 0; r < p.M; ++r) {
+      float v = 0.f;
+#pragma unroll
+      for (int w = 0; w < GF_WARPS; ++w) v += red[(w * MR + r) * GEMV_TN + col];
+      if (whole) store_y(p, r, tc0 + col, v);
+      else __stcg(part + r * GEMV_TN + col, v);
+    }
+    named_bar_arrive(2, GF_THREADS);
+    if (whole) return;
+    __threadfence();
+    __syncwarp();
+    unsigned last = 0;
+    if (lane == 0) last = atomicAdd(p.counters + tile, 1u) == (unsigned)(c_last - c_first);
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (!last) return;
+    __threadfence();
+    for (int r = 0; r < p.M; ++r) {
+      float v = 0.f;
+      for (int cc = c_first; cc <= c_last; ++cc)
+        v += __ldcg(sp.cta_part + ((size_t)cc * 2 + (cc == c_first ? 1 : 0)) * 16 * GEMV_TN + r * GEMV_TN + col);
+      store_y(p, r, tc0 + col, v);
+    }
+    if (lane == 0) p.counters[tile] = 0u;
+  };
+
+  const int tile_first = u0 / upt, tile_last = (u1 - 1) / upt;
+  const int groups_shift_ok = 0; (void)groups_shift_ok;
+  int n = 0;
+  for (int tile = tile_first; tile <= tile_last; ++tile) {
+    const int seg_u1 = min(u1, (tile + 1) * upt);
+    for (int u = u0 + warp + GF_WARPS * n; u < seg_u1; ++n, u += GF_WARPS) {
+      const int ux = u - tile * upt;
+      const int st = n % GF_STAGES, use = n / GF_STAGES;
+      if (!mbar_wait_warp(&my_full[st], use & 1, flags[0] ? 4u : 20000u)) {
+        flags[0] = 1; atomicExch(sp.status, Q4_STATUS_WAIT_EXPIRED);
+      }
+      if (warp == 0 && lane == 0) trace_mark(sp.trace, 3 + 2 * n);
+      unsigned char* stg = my_stages + (size_t)st * STG;
+      // ---- x: rewrite this lane's 8 elements per batch row in MMA order, and the unit's sums of x ----
+      float2* sums = reinterpret_cast<float2*>(stg + GF_X_OFF + MR * 512);      // [2 chunks][MR]
+#pragma unroll
+      for (int r = 0; r < MR; ++r) {
+        uint4* px = reinterpret_cast<uint4*>(stg + GF_X_OFF + r * 512 + 16 * lane);
+        const uint4 v = *px;
+        const __half2 h01 = as_h2(v.x), h23 = as_h2(v.y), h45 = as_h2(v.z), h67 = as_h2(v.w);
+        const __half2 sixteenth = as_h2(0x2C002C00u);
+        const __half2 e04 = __lows2half2(h01, h45), o15 = __hmul2(__highs2half2(h01, h45), sixteenth);
+        const __half2 e26 = __lows2half2(h23, h67), o37 = __hmul2(__highs2half2(h23, h67), sixteenth);
+        *px = make_uint4(as_u32(e04), as_u32(o15), as_u32(e26), as_u32(o37));
+        const float2 f01 = __half22float2(h01), f23 = __half22float2(h23), f45 = __half22float2(h45), f67 = __half22float2(h67);
+        float se = (f01.x + f23.x) + (f45.x + f67.x), so = (f01.y + f23.y) + (f45.y + f67.y);
+#pragma unroll
+        for (int d = 8; d >= 1; d >>= 1) { se += __shfl_xor_sync(0xffffffffu, se, d); so += __shfl_xor_sync(0xffffffffu, so, d); }
+        // odd elements sit in x' as x/16: their 1024 offset comes back as 64 x
+        if ((lane & 15) == 0) sums[(lane >> 4) * MR + r] = make_float2(1024.f * se + 64.f * so, se + so);
+      }
+      __syncwarp();
+      const uint4* wq = reinterpret_cast<const uint4*>(stg) + t * 8 + g;                       // row t, columns 4g..4g+3
+      // lanes of batch rows that do not exist read a row of zeros with the same stride
+      const uint4* xq = (g < MR ? reinterpret_cast<const uint4*>(stg + GF_X_OFF + g * 512)
+                                : reinterpret_cast<const uint4*>(zero_rows + warp * 512)) + t;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        float c[2][2][4];
+#pragma unroll
+        for (int uu = 0; uu < 4; ++uu) {
+          const uint4 wv = wq[32 * (4 * h + uu)];
+          const uint4 xv = xq[4 * (4 * h + uu)];
+          const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};
+          uint32_t pr[4][4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
             const uint32_t w8 = w[q] >> 8;
             pr[q][0] = (w[q] & 0x000F000Fu) | 0x64006400u;
             pr[q][1] = (w[q] & 0x00F000F0u) | 0x64006400u;
             pr[q][2] = (w8 & 0x000F000Fu) | 0x64006400u;
             pr[q][3] = (w8 & 0x00F000F0u) | 0x64006400u;
+          }
+          if (uu == 0) {
+            mma16816_first(c[0][0], pr[0][0], pr[1][0], pr[0][1], pr[1][1], xv.x, xv.y);
+            mma16816_first(c[1][0], pr[2][0], pr[3][0], pr[2][1], pr[3][1], xv.x, xv.y);
+            mma16816_first(c[0][1], pr[0][2], pr[1][2], pr[0][3], pr[1][3], xv.z, xv.w);
+            mma16816_first(c[1][1], pr[2][2], pr[3][2], pr[2][3], pr[3][3], xv.z, xv.w);
           } else {
-            pr[q][0] = (w[q] & 0x000F000Fu) | 0x64006400u;
-            pr[q][1] = ((w[q] >> 4) & 0x000F000Fu) | 0x64006400u;
-            pr[q][2] = ((w[q] >> 8) & 0x000F000Fu) | 0x64006400u;
-            pr[q][3] = ((w[q] >> 12) & 0x000F000Fu) | 0x64006400u;
+            mma16816(c[0][0], pr[0][0], pr[1][0], pr[0][1], pr[1][1], xv.x, xv.y);
+            mma16816(c[1][0], pr[2][0], pr[3][0], pr[2][1], pr[3][1], xv.x, xv.y);
+            mma16816(c[0][1], pr[0][2], pr[1][2], pr[0][3], pr[1][3], xv.z, xv.w);
+            mma16816(c[1][1], pr[2][2], pr[3][2], pr[2][3], pr[3][3], xv.z, xv.w);
           }
         }
-        const bool first = FAST ? (u == 0) : fresh;
+        // close the group of this half: scale the raw sums, and (one lane per column) take the offsets
+        // and the zero point out: y -= s * (offset_sum + (z + 1) * x_sum)
+        const int grow = (h == 1 && gs == 128) ? 1 : 0;            // gs = 128: two groups per unit; else the second
+                                                                   // half only starts a new group at a unit boundary
+        const uint2 sc = *reinterpret_cast<const uint2*>(stg + GF_META_OFF + grow * 64 + 8 * g);
+        const float2 s01 = __half22float2(as_h2(sc.x)), s23 = __half22float2(as_h2(sc.y));
+        yacc[0][0] = fmaf(s01.x, c[0][0][0] + c[0][1][0], yacc[0][0]);
+        yacc[0][1] = fmaf(s01.x, c[0][0][1] + c[0][1][1], yacc[0][1]);
+        yacc[0][2] = fmaf(s01.y, c[0][0][2] + c[0][1][2], yacc[0][2]);
+        yacc[0][3] = fmaf(s01.y, c[0][0][3] + c[0][1][3], yacc[0][3]);
+        yacc[1][0] = fmaf(s23.x, c[1][0][0] + c[1][1][0], yacc[1][0]);
+        yacc[1][1] = fmaf(s23.x, c[1][0][1] + c[1][1][1], yacc[1][1]);
+        yacc[1][2] = fmaf(s23.y, c[1][0][2] + c[1][1][2], yacc[1][2]);
+        yacc[1][3] = fmaf(s23.y, c[1][0][3] + c[1][1][3], yacc[1][3]);
+        const float sl = __half2float(*reinterpret_cast<const __half*>(stg + GF_META_OFF + grow * 64 + 2 * lane));
+        const uint32_t zw = *reinterpret_cast<const uint32_t*>(stg + GF_ZP_OFF + grow * 16 + 4 * (lane >> 3));
+        const float z1 = (float)(((zw >> (4 * (lane & 7))) & 0xFu) + 1u);
 #pragma unroll
-        for (int mt = 0; mt < MT; ++mt) {
-          const uint4 xq = xv[mt][u];             // x[k..k+7] of batch row g (+8); XS: already in MMA order
-          uint32_t xb[4];
-          if constexpr (XS) {
-            xb[0] = xq.x; xb[1] = xq.y; xb[2] = xq.z; xb[3] = xq.w;
-          } else {
-            xb[0] = prmt(xq.x, xq.z, 0x5410); xb[1] = prmt(xq.x, xq.z, 0x7632);    // (x0,x4) (x1,x5)
-            xb[2] = prmt(xq.y, xq.w, 0x5410); xb[3] = prmt(xq.y, xq.w, 0x7632);    // (x2,x6) (x3,x7)
-          }
-#pragma unroll
-          for (int ks = 0; ks < 2; ++ks) {
-            const uint32_t bb0 = xb[2 * ks], bb1 = xb[2 * ks + 1];
-            if (first) {
-              mma16816_first(c[mt][0][ks], pr[0][2 * ks], pr[1][2 * ks], pr[0][2 * ks + 1], pr[1][2 * ks + 1], bb0, bb1);
-              mma16816_first(c[mt][1][ks], pr[2][2 * ks], pr[3][2 * ks], pr[2][2 * ks + 1], pr[3][2 * ks + 1], bb0, bb1);
-              if constexpr (!XS) mma16816_first(co[mt][ks], 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, bb0, bb1);
-            } else {
-              mma16816(c[mt][0][ks], pr[0][2 * ks], pr[1][2 * ks], pr[0][2 * ks + 1], pr[1][2 * ks + 1], bb0, bb1);
-              mma16816(c[mt][1][ks], pr[2][2 * ks], pr[3][2 * ks], pr[2][2 * ks + 1], pr[3][2 * ks + 1], bb0, bb1);
-              if constexpr (!XS) mma16816(co[mt][ks], 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, 0x3C003C00u, bb0, bb1);
-            }
-          }
+        for (int r = 0; r < MR; ++r) {
+          const float2 e = sums[h * MR + r];
+          ycorr[r] = fmaf(sl, fmaf(z1, e.y, e.x), ycorr[r]);
         }
-        fresh = false;
-      }
-      // scales live in this stage: settle the open group before the slot is released
-      if (FAST) {
-        if (step[0] < sp.steps_per_tile)
-          flush(stg, p.v1 ? 0 : ((sp.group_shift >= 0 ? (step[0] >> sp.group_shift) : step[0] / steps_per_group) - grp0), c, co, step[0] >> 2);
-      } else if (cur_grp >= 0) {
-        flush(stg, cur_grp - grp0, c, co, 0);
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(&empty[st]);
-      if (threadIdx.x == 0) trace_mark(sp.trace, 3 + 2 * nbox);
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // our reads before the next TMA write
+      issue_w(n + GF_STAGES);
+      issue_x(n + GF_STAGES);
+      if (warp == 0 && lane == 0) trace_mark(sp.trace, 4 + 2 * n);
     }
     if (threadIdx.x == 0) trace_mark(sp.trace, 30);
-    finish_tile(tile, tile - tile_first, max(b0, tile * bpt) - tile * bpt, seg_b1 - 1 - tile * bpt);
+    finish_tile(tile, tile - tile_first, max(u0, tile * upt) - tile * upt, seg_u1 - 1 - tile * upt);
     if (threadIdx.x == 0) trace_mark(sp.trace, 31);
   }
 }
@@ -619,7 +866,7 @@ static int launch_stream(const CUtensorMap& map, const CUtensorMap& smap, const 
   cudaGetDevice(&dev);
   // XS adds: 16 B of zeros, the chunk table (at most 16 KiB) and x itself; sized for the worst case so that the
   // attribute is set once
-  const size_t smem = gemv_stream_smem<MT>() + (XS ? 16 + 16384 + GEMV_XS_MAX_BYTES : 0);
+  const size_t smem = gemv_stream_smem<MT>() + (XS ? 16 + GEMV_XS_MAX_BYTES : 0);
   if (dev >= 0 && dev < 64 && !attr_done[dev]) {
     if (int e = check_cuda(cudaFuncSetAttribute(gemv_stream_kernel<MT, FAST, XS>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                            "gemv smem attribute")) return e;
@@ -633,6 +880,28 @@ static int launch_stream(const CUtensorMap& map, const CUtensorMap& smap, const 
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at; cfg.numAttrs = 1;
   return check_cuda(cudaLaunchKernelEx(&cfg, gemv_stream_kernel<MT, FAST, XS>, map, smap, zmap, sp), "gemv launch");
+}
+
+template <int MR>
+static int launch_fast(const CUtensorMap& map, const CUtensorMap& smap, const CUtensorMap& zmap,
+                       const GemvStreamParams& sp, int grid, cudaStream_t st) {
+  static bool attr_done[64] = {false};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const size_t smem = gf_smem_bytes<MR>();
+  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+    if (int e = check_cuda(cudaFuncSetAttribute(gemv_fast_kernel<MR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+                           "gemv smem attribute")) return e;
+    attr_done[dev] = true;
+  }
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(GF_THREADS);
+  cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  return check_cuda(cudaLaunchKernelEx(&cfg, gemv_fast_kernel<MR>, map, smap, zmap, sp), "gemv launch");
 }
 
 }  // namespace q4
@@ -698,8 +967,8 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
     GemvStreamParams sp;
     sp.g = p;
     sp.steps_per_tile = K / 32;
-    sp.boxes_per_tile = (K / 8 + GEMV_BOX_ROWS - 1) / GEMV_BOX_ROWS;
-    sp.total_boxes = sp.boxes_per_tile * (N / GEMV_TN);
+    sp.units_per_tile = (K / 8 + GEMV_UNIT_ROWS - 1) / GEMV_UNIT_ROWS;
+    sp.total_units = sp.units_per_tile * (N / GEMV_TN);
     sp.cta_part = p.part;
     sp.status = (unsigned*)((char*)workspace + GEMV_STATUS_OFFSET);
     sp.trace = g_trace;
@@ -707,27 +976,29 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
     for (int sh = 0; sh < 20; ++sh) if ((groupsize >> 5) == (1 << sh)) sp.group_shift = sh;
     int grid = sm_count();
     if (grid > GEMV_MAX_CTAS) grid = GEMV_MAX_CTAS;
-    if (grid > sp.total_boxes) grid = sp.total_boxes;
-    // group rows one box (512 k-rows) can touch, counting a straddled group at either end
-    sp.meta_rows = v1 ? 1 : (GEMV_BOX_ROWS * 8 + groupsize - 1) / groupsize + ((GEMV_BOX_ROWS * 8) % groupsize ? 1 : 0);
+    if (grid > sp.total_units) grid = sp.total_units;
+    // group rows one unit (256 k-rows) can touch, counting a straddled group at either end
+    sp.meta_rows = v1 ? 1 : (GEMV_UNIT_ROWS * 8 + groupsize - 1) / groupsize + ((GEMV_UNIT_ROWS * 8) % groupsize ? 1 : 0);
     if (sp.meta_rows > GEMV_META_ROWS) return fail(Q4_E_SHAPE, "gemv: groupsize=%d too small", groupsize);
     if (!aligned16(qzeros)) return fail(Q4_E_ALIGN, "gemv: qzeros must be 16-byte aligned");
     CUtensorMap map, smap, zmap;
     if (int e = make_tmap_2d(&map, qweight, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, (uint64_t)N, (uint64_t)(K / 8),
-                             (uint64_t)N * 4, GEMV_TN, GEMV_BOX_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
+                             (uint64_t)N * 4, GEMV_TN, GEMV_UNIT_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
     if (int e = make_tmap_2d(&smap, scales, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (uint64_t)N, (uint64_t)G,
                              (uint64_t)N * 2, GEMV_TN, sp.meta_rows, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
     if (!v1) {
       if (int e = make_tmap_2d(&zmap, qzeros, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, (uint64_t)(N / 8), (uint64_t)G,
                                (uint64_t)(N / 8) * 4, GEMV_TN / 8, sp.meta_rows, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
-      sp.stage_tx = GEMV_BOX_BYTES + sp.meta_rows * (GEMV_TN * 2 + GEMV_TN / 2);
+      sp.stage_tx = GEMV_UNIT_BYTES + sp.meta_rows * (GEMV_TN * 2 + GEMV_TN / 2);
     } else {
       if (int e = make_tmap_2d(&zmap, qzeros, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (uint64_t)N, 1,
                                (uint64_t)N * 2, GEMV_TN, 1, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
-      sp.stage_tx = GEMV_BOX_BYTES + 2 * GEMV_TN * 2;
+      sp.stage_tx = GEMV_UNIT_BYTES + 2 * GEMV_TN * 2;
     }
     const bool fast = v1 || groupsize % 128 == 0;
-    const bool xs = fast && MT == 1 && K % 128 == 0 && (size_t)M * K * 2 <= (size_t)GEMV_XS_MAX_BYTES && K / 128 * 64 <= 16384;
+    if (!v1 && M <= 2 && (groupsize == 128 || groupsize % 256 == 0) && K % 128 == 0)   // lean kernel: x travels with the weights
+      return M == 1 ? launch_fast<1>(map, smap, zmap, sp, grid, st) : launch_fast<2>(map, smap, zmap, sp, grid, st);
+    const bool xs = fast && MT == 1 && K % 128 == 0 && (size_t)M * K * 2 + (size_t)(K / 128) * 64 <= (size_t)GEMV_XS_MAX_BYTES;
     if (xs) return launch_stream<1, true, true>(map, smap, zmap, sp, grid, st);
     if (MT == 1) return fast ? launch_stream<1, true, false>(map, smap, zmap, sp, grid, st) : launch_stream<1, false, false>(map, smap, zmap, sp, grid, st);
     return fast ? launch_stream<2, true, false>(map, smap, zmap, sp, grid, st) : launch_stream<2, false, false>(map, smap, zmap, sp, grid, st);

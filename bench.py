@@ -416,7 +416,7 @@ def main():
                 "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": config,
                 "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
                              "frac": round(achieved / peak, 4), "traffic": None, "peak_kind": peak_kind,
-                             "kernel": "gemv_stream_kernel<1,true,true>", "avg_launch_us": round(per_launch_us, 3),
+                             "kernel": "gemv_fast_kernel<1>", "avg_launch_us": round(per_launch_us, 3),
                              "frac_of_nominal_8000": round(achieved / 8000.0, 4)},
                 "per_shape": r["per_shape"],
                 "e2e": {"value": round(e2e, 1), "unit": UNIT, "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": r["d2h"],

@@ -127,6 +127,8 @@ int q4_device_status(unsigned* out);
  * writes SM cycle counters at fixed points of its life into 64 uint64 slots (buffer of at least
  * 64 * 8 * number-of-SMs bytes).  NULL switches the trace off (the default). */
 int q4_gemv_set_trace(void* device_buffer);
+/* Same for the fused GEMM kernels: 256 uint64 slots per CTA (buffer of 256 * 8 * number-of-CTAs bytes). */
+int q4_gemm_set_trace(void* device_buffer);
 
 #ifdef __cplusplus
 }
