@@ -35,10 +35,10 @@ _SIGNATURES = {
     "q4_gemv_static_max_bytes": (c_size_t, []),
     "q4_gemv_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                c_int, c_int, c_int, c_int, c_int, c_int, c_uint, c_void_p]),
-    "q4_gemm_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                            c_int, c_int, c_int, c_int, c_void_p]),
-    "q4_gemm_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                            c_int, c_int, c_int, c_int, c_void_p]),
+    "q4_gemm_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                            c_int, c_int, c_int, c_int, c_int, c_void_p]),
+    "q4_gemm_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                            c_int, c_int, c_int, c_int, c_int, c_void_p]),
     "q4_device_status": (c_int, [ctypes.POINTER(c_uint)]),
     "q4_gemv": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                         c_int, c_int, c_int, c_int, c_int, c_int, c_uint, c_void_p, c_size_t, c_void_p]),

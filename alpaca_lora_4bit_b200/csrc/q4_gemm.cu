@@ -54,6 +54,11 @@ struct GemmParams {
   int n_contract_tiles;     // contraction length / 64
   int stages;               // pipeline depth (3 or 4, what shared memory allows)
   unsigned long long* trace;  // optional per-CTA cycle trace (256 slots), else null
+  // Optional low-rank term added through one extra pipeline stage (null / 0 = none):
+  //   forward   y  += U * lora_B^T,  U = scale * x  * lora_A^T  [M, 64] (zero-padded),  lora_w = lora_B [N, r]
+  //   backward  dx += V * lora_A,    V = scale * dy * lora_B    [M, 64] (zero-padded),  lora_w = lora_A [r, K]
+  const __half* lora_w;
+  int lora_r;
 };
 
 // ---- tcgen05 wrappers --------------------------------------------------------------------------
@@ -157,7 +162,7 @@ __device__ __forceinline__ uint4 zero_terms(const uint4& s, uint32_t zw) {
 
 template <bool TRANSPOSE>
 __global__ void __launch_bounds__(GM_THREADS, 1)
-q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const GemmParams p) {
+q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap umap, const GemmParams p) {
   extern __shared__ unsigned char smem_raw[];
   // 1024-byte alignment for the swizzled tiles
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -176,6 +181,8 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const GemmParams p) {
   const int out0 = blockIdx.x * GM_TILE_N;            // first output column (n forward, k backward)
   const int m0 = blockIdx.y * GM_TILE_M;
   const int T = p.n_contract_tiles;
+  const int TT = T + (p.lora_r > 0 ? 1 : 0);          // one more stage for the low-rank term
+  const int lora_ks = (p.lora_r + 15) >> 4;           // its 16-wide MMA steps
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; ++i) { mbar_init(&full_a[i], 1); mbar_init(&full_b[i], GM_DEQ_THREADS / 32); mbar_init(&empty[i], 1); }
@@ -193,19 +200,21 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const GemmParams p) {
   if (warp == 0) {
     // ---------------- TMA producer: activation tiles ----------------
     if (lane == 0) {
-      for (int it = 0; it < T; ++it) {
+      for (int it = 0; it < TT; ++it) {
         const int st = it % S, use = it / S;
         if (use > 0) wait_bar(&empty[st], (use - 1) & 1, abort_flag);
         mbar_arrive_expect_tx(&full_a[st], GM_A_BYTES);
-        tma_load_2d(stages + (size_t)st * GM_STAGE_BYTES, &amap, it * GM_TILE_C, m0, &full_a[st]);
+        if (it < T) tma_load_2d(stages + (size_t)st * GM_STAGE_BYTES, &amap, it * GM_TILE_C, m0, &full_a[st]);
+        else tma_load_2d(stages + (size_t)st * GM_STAGE_BYTES, &umap, 0, m0, &full_a[st]);
       }
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer ----------------
     if (lane == 0) {
       constexpr uint32_t idesc = idesc_f16(128, GM_TILE_N, !TRANSPOSE);
-      for (int it = 0; it < T; ++it) {
+      for (int it = 0; it < TT; ++it) {
         const int st = it % S, use = it / S;
+        const int nks = it < T ? GM_TILE_C / 16 : lora_ks;
         if (it < 20) gm_mark(p.trace, 3 * it);
         wait_bar(&full_a[st], use & 1, abort_flag);
         if (it < 20) gm_mark(p.trace, 3 * it + 1);
@@ -216,6 +225,7 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const GemmParams p) {
         const uint32_t b_addr = a_addr + GM_A_BYTES;
 #pragma unroll
         for (int ks = 0; ks < GM_TILE_C / 16; ++ks) {
+          if (ks >= nks) break;
           // A: K-major, 128-byte rows, 8-row groups 1024 B apart; 16 contraction elements = 32 B
           const uint64_t ad0 = smem_desc_sw128(a_addr + ks * 32, 16, 1024);
           const uint64_t ad1 = smem_desc_sw128(a_addr + GM_A_BYTES / 2 + ks * 32, 16, 1024);      // rows 128..255
@@ -262,8 +272,42 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const GemmParams p) {
       ga = __ldg(reinterpret_cast<const int4*>(p.g_idx + k8));
       gb = __ldg(reinterpret_cast<const int4*>(p.g_idx + k8 + 4));
     }
-    for (int it = grp; it < T; it += GM_DEQ_GROUPS) {
+    for (int it = grp; it < TT; it += GM_DEQ_GROUPS) {
       const int st = it % S, use = it / S;
+      if (it == T) {
+        // ---- low-rank stage: B operand from lora_w instead of dequantised weights ----
+        if (use > 0 && lane == 0) wait_bar(&empty[st], (use - 1) & 1, abort_flag);
+        __syncwarp();
+        unsigned char* bst = stages + (size_t)st * GM_STAGE_BYTES + GM_A_BYTES;
+        const int rr = p.lora_r, rows = 16 * lora_ks;
+        if (!TRANSPOSE) {
+          // column n = out0 + tid: element (j, n) = lora_B[n][j] into panel tid/64, row j, 128B-swizzled
+          const __half* src = p.lora_w + (size_t)(out0 + tid) * rr;
+          unsigned char* col = bst + (tid >> 6) * 8192 + ((tid & 7) << 1);
+          const int cc = (tid & 63) >> 3;
+          for (int j = 0; j < rows; ++j) {
+            const __half v = j < rr ? src[j] : __float2half(0.f);
+            *reinterpret_cast<__half*>(col + j * 128 + ((cc ^ (j & 7)) << 4)) = v;
+          }
+        } else {
+          // row k = out0 + tid: element (k, j) = lora_A[j][k], 8 j per 16-byte chunk
+          unsigned char* row = bst + tid * 128;
+          for (int c8 = 0; c8 < 2 * lora_ks; ++c8) {
+            uint4 o;
+            __half* oh = reinterpret_cast<__half*>(&o);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+              const int j = 8 * c8 + e;
+              oh[e] = j < rr ? p.lora_w[(size_t)j * p.K + out0 + tid] : __float2half(0.f);
+            }
+            *reinterpret_cast<uint4*>(row + ((c8 ^ (tid & 7)) << 4)) = o;
+          }
+        }
+        fence_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&full_b[st]);
+        continue;
+      }
       const uint32_t w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
       const int gi[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
       if (it + GM_DEQ_GROUPS < T) {                                // prefetch this group's next stage
@@ -357,13 +401,16 @@ static size_t gemm_smem_bytes(bool transpose, int G, int stages) {
 using namespace q4;
 
 static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, void* out, const void* scales,
-                       const int32_t* qzeros, const int32_t* g_idx, const void* bias, int M, int K, int N, int G,
-                       q4_stream_t stream) {
+                       const int32_t* qzeros, const int32_t* g_idx, const void* bias, const void* lora_u,
+                       const void* lora_w, int lora_r, int M, int K, int N, int G, q4_stream_t stream) {
   if (!act || !qweight || !out || !scales || !qzeros || !g_idx) return fail(Q4_E_BADARG, "gemm: null pointer");
   if (M <= 0 || K <= 0 || N <= 0 || G <= 0) return fail(Q4_E_BADARG, "gemm: M=%d K=%d N=%d G=%d", M, K, N, G);
   if (K % 128 || N % 128) return fail(Q4_E_SHAPE, "gemm: K=%d and N=%d must be multiples of 128", K, N);
   if (!aligned16(act) || !aligned16(qweight) || !aligned16(out) || !aligned16(scales) || !aligned16(g_idx))
     return fail(Q4_E_ALIGN, "gemm: pointers must be 16-byte aligned");
+  if (lora_r < 0 || lora_r > 64) return fail(Q4_E_SHAPE, "gemm: low-rank width %d outside 0..64", lora_r);
+  if (lora_r > 0 && (!lora_u || !lora_w || !aligned16(lora_u) || !aligned16(lora_w)))
+    return fail(Q4_E_BADARG, "gemm: the low-rank term needs 16-byte aligned lora_u [M,64] and lora_w");
   if (int e = check_device()) return e;
   int stages = GM_MAX_STAGES;
   while (stages > 2 && gemm_smem_bytes(transpose, G, stages) > 227 * 1024) --stages;
@@ -378,29 +425,37 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
   p.n_contract_tiles = contract / GM_TILE_C;
   p.stages = stages;
   p.trace = g_gemm_trace;
+  p.lora_w = lora_r > 0 ? (const __half*)lora_w : nullptr;
+  p.lora_r = lora_r;
   CUtensorMap amap;
   if (int e = make_tmap_2d(&amap, act, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)contract, (uint64_t)M,
                            (uint64_t)contract * 2, GM_TILE_C, GM_TILE_M, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
+  CUtensorMap umap = amap;
+  if (lora_r > 0)
+    if (int e = make_tmap_2d(&umap, lora_u, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, 64, (uint64_t)M, 128, GM_TILE_C, GM_TILE_M,
+                             CU_TENSOR_MAP_SWIZZLE_128B)) return e;
   const dim3 grid(nout / GM_TILE_N, (M + GM_TILE_M - 1) / GM_TILE_M), block(GM_THREADS);
   cudaStream_t st = (cudaStream_t)stream;
   if (transpose) {
     if (int e = check_cuda(cudaFuncSetAttribute(q4_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "gemm smem attribute")) return e;
-    q4_gemm_kernel<true><<<grid, block, smem, st>>>(amap, p);
+    q4_gemm_kernel<true><<<grid, block, smem, st>>>(amap, umap, p);
   } else {
     if (int e = check_cuda(cudaFuncSetAttribute(q4_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "gemm smem attribute")) return e;
-    q4_gemm_kernel<false><<<grid, block, smem, st>>>(amap, p);
+    q4_gemm_kernel<false><<<grid, block, smem, st>>>(amap, umap, p);
   }
   return check_cuda(cudaGetLastError(), "gemm launch");
 }
 
 extern "C" int q4_gemm_fwd(const void* x, const int32_t* qweight, void* y, const void* scales, const int32_t* qzeros,
-                           const int32_t* g_idx, const void* bias, int M, int K, int N, int G, q4_stream_t stream) {
-  return gemm_launch(false, x, qweight, y, scales, qzeros, g_idx, bias, M, K, N, G, stream);
+                           const int32_t* g_idx, const void* bias, const void* lora_u, const void* lora_b, int lora_r,
+                           int M, int K, int N, int G, q4_stream_t stream) {
+  return gemm_launch(false, x, qweight, y, scales, qzeros, g_idx, bias, lora_u, lora_b, lora_r, M, K, N, G, stream);
 }
 
 extern "C" int q4_gemm_bwd(const void* dy, const int32_t* qweight, void* dx, const void* scales, const int32_t* qzeros,
-                           const int32_t* g_idx, int M, int K, int N, int G, q4_stream_t stream) {
-  return gemm_launch(true, dy, qweight, dx, scales, qzeros, g_idx, nullptr, M, K, N, G, stream);
+                           const int32_t* g_idx, const void* lora_v, const void* lora_a, int lora_r,
+                           int M, int K, int N, int G, q4_stream_t stream) {
+  return gemm_launch(true, dy, qweight, dx, scales, qzeros, g_idx, nullptr, lora_v, lora_a, lora_r, M, K, N, G, stream);
 }
 
 extern "C" int q4_gemm_set_trace(void* device_buffer) {

@@ -16,8 +16,14 @@ import math
 
 import torch
 import torch.nn as nn
+import torch.nn.functional as F
+from torch.amp import custom_bwd, custom_fwd
 
+from . import matmul_utils_4bit as mm4b
+from . import quant_cuda
 from .autograd_4bit import Autograd4bitQuantLinear
+
+fused_lora = True      # base product and LoRA term in one kernel when the layer and input allow it
 
 try:  # PEFT is optional
     from peft.tuners.lora import LoraLayer as _PeftLoraLayer  # type: ignore
@@ -85,6 +91,52 @@ class LoraLayerTwin:
 _LoraBase = _PeftLoraLayer if _HAVE_PEFT else LoraLayerTwin
 
 
+class LoraMatmul4bit(torch.autograd.Function):
+    """``y = x @ W + bias + scaling * (x @ A^T) @ B^T`` over a 4-bit v2 layer in one fused kernel, with
+    the matching backward ``dx = dy @ W^T + scaling * (dy @ B) @ A`` (also one kernel) and the LoRA
+    gradients ``dA = (scaling * dy @ B)^T @ x``, ``dB = dy^T @ (scaling * x @ A^T)``.
+
+    Same mathematics as ``Autograd4bitQuantLinear.forward`` followed by the adapter update of
+    ``Linear4bitLt.forward`` (models.py:51-69); the two skinny products that form the rank-r
+    activations are library GEMMs, everything N- or K-wide runs inside the dequant-GEMM kernels."""
+
+    @staticmethod
+    @custom_fwd(device_type="cuda", cast_inputs=torch.float16)
+    def forward(ctx, x, lora_a, lora_b, scaling, qweight, scales, qzeros, g_idx, bias):
+        K, N = qweight.shape[0] * 8, qweight.shape[1]
+        x2 = x.reshape(-1, K).half().contiguous()
+        a_h, b_h = lora_a.half().contiguous(), lora_b.half().contiguous()
+        r = a_h.shape[0]
+        u = F.pad(torch.matmul(x2, a_h.t()) * scaling, (0, 64 - r))              # [M, 64], scaling folded in
+        y = torch.empty((x2.shape[0], N), dtype=torch.float16, device=x.device)
+        quant_cuda.gemm(x2, qweight, y, scales.half(), qzeros, g_idx, bias=None if bias is None else bias.half(),
+                        lora_u=u, lora_w=b_h)
+        ctx.save_for_backward(x2, u, a_h, b_h, qweight, scales, qzeros, g_idx)
+        ctx.scaling = scaling
+        ctx.x_shape = x.shape
+        return y.reshape(x.shape[:-1] + (N,))
+
+    @staticmethod
+    @custom_bwd(device_type="cuda")
+    def backward(ctx, grad_output):
+        x2, u, a_h, b_h, qweight, scales, qzeros, g_idx = ctx.saved_tensors
+        K, N = qweight.shape[0] * 8, qweight.shape[1]
+        r = a_h.shape[0]
+        dy = grad_output.reshape(-1, N).half().contiguous()
+        v = torch.matmul(dy, b_h) * ctx.scaling                                   # [M, r]
+        dx = d_a = d_b = None
+        if ctx.needs_input_grad[0]:
+            dx = torch.empty((dy.shape[0], K), dtype=torch.float16, device=dy.device)
+            quant_cuda.gemm(dy, qweight, dx, scales.half(), qzeros, g_idx, transpose=True,
+                            lora_u=F.pad(v, (0, 64 - r)), lora_w=a_h)
+            dx = dx.reshape(ctx.x_shape)
+        if ctx.needs_input_grad[1]:
+            d_a = torch.matmul(v.t(), x2)                                         # [r, K]
+        if ctx.needs_input_grad[2]:
+            d_b = torch.matmul(dy.t(), u[:, :r])                                  # [N, r]
+        return dx, d_a, d_b, None, None, None, None, None, None
+
+
 class Linear4bitLt(Autograd4bitQuantLinear, _LoraBase):
     """LoRA implemented on a 4-bit quantised dense layer (models.py:13-76)."""
 
@@ -104,7 +156,30 @@ class Linear4bitLt(Autograd4bitQuantLinear, _LoraBase):
         self.update_layer(adapter_name, r, lora_alpha, lora_dropout, init_lora_weights)
         self.set_adapter([adapter_name])
 
+    def _fused_adapter(self, x: torch.Tensor):
+        """Name of the one adapter the fused kernel can serve for this call, else None."""
+        if not (fused_lora and mm4b.fused_gemm) or self.disable_adapters or self.is_v1_model or self.bits != 4:
+            return None
+        active = [n for n in self.active_adapters if n in self.lora_A.keys()]
+        if len(active) != 1 or not x.is_cuda or not torch.is_grad_enabled():
+            return None
+        name = active[0]
+        drop = self.lora_dropout[name]
+        if isinstance(drop, nn.Dropout) and drop.p > 0 and self.training:
+            return None                                   # the LoRA branch would see a different x
+        rows = x.numel() // x.shape[-1]
+        if rows <= mm4b.auto_switch_thd or self.r[name] > 64:
+            return None
+        if not quant_cuda.gemm_supported(self.in_features, self.out_features, self.scales.shape[0], False):
+            return None
+        return name
+
     def forward(self, x: torch.Tensor):
+        name = self._fused_adapter(x)
+        if name is not None:
+            bias = None if (self.disable_bias or self.bias is None) else self.bias
+            return LoraMatmul4bit.apply(x, self.lora_A[name].weight, self.lora_B[name].weight, self.scaling[name],
+                                        self.qweight, self.scales, self.qzeros, self.g_idx, bias)
         result = Autograd4bitQuantLinear.forward(self, x)
         if self.disable_adapters:
             return result

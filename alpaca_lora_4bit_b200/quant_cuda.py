@@ -103,10 +103,14 @@ def gemv(x, qweight, y, scales, zeros, g_idx, groupsize, flags, bias=None) -> No
                                  m, K, N, G, groupsize, ydt, flags, ws.data_ptr(), ws.numel(), st), "gemv")
 
 
-def gemm(x, qweight, out, scales, zeros, g_idx, transpose=False, bias=None) -> None:
+def gemm(x, qweight, out, scales, zeros, g_idx, transpose=False, bias=None, lora_u=None, lora_w=None) -> None:
     """Fused large-M product on the tensor cores: ``out = x @ W (+ bias)`` or, with ``transpose``,
-    ``out = x @ W.T``; ``x``, ``out``, ``scales`` fp16, W never leaves shared memory."""
-    dev = _lib.require_cuda(x, qweight, out, scales, zeros, g_idx, bias)
+    ``out = x @ W.T``; ``x``, ``out``, ``scales`` fp16, W never leaves shared memory.
+
+    ``lora_u`` fp16 ``[M, 64]`` (columns beyond the rank zero) with ``lora_w`` adds the low-rank term in
+    the same kernel: forward ``+ lora_u[:, :r] @ lora_w.T`` with ``lora_w = lora_B [N, r]``; transpose
+    ``+ lora_u[:, :r] @ lora_w`` with ``lora_w = lora_A [r, K]``."""
+    dev = _lib.require_cuda(x, qweight, out, scales, zeros, g_idx, bias, lora_u, lora_w)
     R, N = qweight.shape
     K = R * 8
     M = x.shape[0]
@@ -116,15 +120,21 @@ def gemm(x, qweight, out, scales, zeros, g_idx, transpose=False, bias=None) -> N
         raise RuntimeError(f"quant_cuda: gemm shapes x{tuple(x.shape)} out{tuple(out.shape)} do not match the layer [{K},{N}]")
     if x.dtype != torch.float16 or out.dtype != torch.float16 or scales.dtype != torch.float16:
         raise RuntimeError("quant_cuda: gemm takes fp16 x, out and scales")
+    r = 0
+    if lora_u is not None:
+        r = lora_w.shape[0] if transpose else lora_w.shape[1]
+        want_w = (r, K) if transpose else (N, r)
+        if lora_u.shape != (M, 64) or lora_w.shape != want_w or lora_u.dtype != torch.float16 or lora_w.dtype != torch.float16:
+            raise RuntimeError(f"quant_cuda: gemm low-rank term needs lora_u [M,64] and lora_w {want_w}, both fp16")
     L = _lib.lib()
     with torch.cuda.device(dev):
         st = _lib.stream_of(x)
         if transpose:
             rc = L.q4_gemm_bwd(x.data_ptr(), qweight.data_ptr(), out.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
-                               g_idx.data_ptr(), M, K, N, G, st)
+                               g_idx.data_ptr(), _lib.ptr(lora_u), _lib.ptr(lora_w), r, M, K, N, G, st)
         else:
             rc = L.q4_gemm_fwd(x.data_ptr(), qweight.data_ptr(), out.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
-                               g_idx.data_ptr(), _lib.ptr(bias), M, K, N, G, st)
+                               g_idx.data_ptr(), _lib.ptr(bias), _lib.ptr(lora_u), _lib.ptr(lora_w), r, M, K, N, G, st)
     _lib.check(rc, "gemm")
 
 

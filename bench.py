@@ -328,17 +328,25 @@ def run_gemm(args, local_rank):
         dx = torch.empty((M, K), device=dev, dtype=torch.float16)
         w = torch.empty((K, N), device=dev, dtype=torch.float16)
         fl = 2.0 * M * K * N / 1e9
+        r = 16                                             # LoRA r=16, alpha=32: A ~ N(0, 0.02) [16, K], B ~ N(0, 0.02) [N, 16]
+        la = (torch.randn((r, K), device=dev, generator=gen) * 0.02).half()
+        lb = (torch.randn((N, r), device=dev, generator=gen) * 0.02).half()
+        u = torch.nn.functional.pad((x @ la.t()) * 2.0, (0, 64 - r)).contiguous()
+        v = torch.nn.functional.pad((dy @ lb) * 2.0, (0, 64 - r)).contiguous()
         tf = timed(lambda: quant_cuda.gemm(x, qw, y, sc, zw, gi))
         tb = timed(lambda: quant_cuda.gemm(dy, qw, dx, sc, zw, gi, transpose=True))
+        tfl = timed(lambda: quant_cuda.gemm(x, qw, y, sc, zw, gi, lora_u=u, lora_w=lb))
+        tbl = timed(lambda: quant_cuda.gemm(dy, qw, dx, sc, zw, gi, transpose=True, lora_u=v, lora_w=la))
         tr = timed(lambda: quant_cuda.vecquant4recons_v2(qw, w, sc, zw, gi))
         tm = timed(lambda: torch.matmul(x, w, out=y))
         tmb = timed(lambda: torch.matmul(dy, w.t(), out=dx))
         out["shapes"][f"{K}x{N}"] = {
             "fused_fwd_tflops": round(fl / tf, 1), "fused_bwd_tflops": round(fl / tb, 1),
             "fused_fwd_frac": round(fl / tf / peak, 3), "fused_bwd_frac": round(fl / tb / peak, 3),
+            "fused_fwd_with_lora_r16_tflops": round(fl / tfl, 1), "fused_bwd_with_lora_r16_tflops": round(fl / tbl, 1),
             "recons_plus_library_gemm_fwd_tflops": round(fl / (tr + tm), 1),
             "recons_plus_library_gemm_bwd_tflops": round(fl / (tr + tmb), 1), "recons_us": round(tr * 1e3, 1)}
-        del qw, zw, sc, gi, x, dy, y, dx, w
+        del qw, zw, sc, gi, x, dy, y, dx, w, la, lb, u, v
     torch.cuda.empty_cache()
     return out
 

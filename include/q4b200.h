@@ -113,11 +113,18 @@ int q4_gemv_static(const void* x, const int32_t* qweight, void* y, const void* s
  * fp32 accumulation in tensor memory; the dequantised operand is bit-identical to q4_recons_v2.
  * The group of every row is read from g_idx (act-order safe).  Needs K % 128 == 0, N % 128 == 0;
  * any M >= 1.  The forward keeps per-group scale tables for 128 columns in shared memory and
- * returns Q4_E_SHAPE when G is too large for that (about 180 groups). */
+ * returns Q4_E_SHAPE when G is too large for that (about 250 groups).
+ * LoRA term, fused as one more pipeline stage of the same kernel (lora_r = 0 switches it off):
+ *   forward   y  += U * lora_b^T   U      fp16 [M, 64] = (alpha/r) * x  * lora_A^T, columns >= r zero; lora_b fp16 [N, r]
+ *   backward  dx += V * lora_a     lora_v fp16 [M, 64] = (alpha/r) * dy * lora_B,   columns >= r zero; lora_a fp16 [r, K]
+ * which is the `lora_B(lora_A(x)) * scaling` of Linear4bitLt.forward (models.py:61-66) and its
+ * gradient with respect to x.  1 <= lora_r <= 64. */
 int q4_gemm_fwd(const void* x, const int32_t* qweight, void* y, const void* scales, const int32_t* qzeros,
-                const int32_t* g_idx, const void* bias, int M, int K, int N, int G, q4_stream_t stream);
+                const int32_t* g_idx, const void* bias, const void* lora_u, const void* lora_b, int lora_r,
+                int M, int K, int N, int G, q4_stream_t stream);
 int q4_gemm_bwd(const void* dy, const int32_t* qweight, void* dx, const void* scales, const int32_t* qzeros,
-                const int32_t* g_idx, int M, int K, int N, int G, q4_stream_t stream);
+                const int32_t* g_idx, const void* lora_v, const void* lora_a, int lora_r,
+                int M, int K, int N, int G, q4_stream_t stream);
 
 /* Copies the device status word to *out (synchronises the device): 0, or 0xDEAD0001 if a bounded
  * wait inside a q4_gemm_* kernel expired (its output is then invalid). */

@@ -122,15 +122,48 @@ def test_module_routes_by_rows_and_grad_mode():
             assert rel_fro(m(x.to(DEV)), want(x)) <= REL_TOL
 
 
-def test_linear4bitlt_lora_training_step():
+@pytest.mark.parametrize("r", [8, 16, 40])
+@pytest.mark.parametrize("transpose", [False, True])
+def test_gemm_fused_lora_term(r, transpose):
+    """C2: the LoRA update fused into the GEMM as an extra pipeline stage (r=16, alpha=32 -> scale 2)."""
+    K, N, M = 1024, 640 if not transpose else 512, 300
+    layer = synth.make_layer(K, N, 128, True, seed=r)
+    A, B = synth.make_lora(K, N, r, seed=r + 1)
+    inner = N if transpose else K
+    x = synth.make_acts(M, inner, seed=r + 2)
+    w = orc.recons_v2(layer.qweight, layer.scales, layer.qzeros, layer.g_idx).float()
+    if transpose:                                           # dx = dy W^T + 2 (dy B) A
+        u = ((x.float() @ B.float()) * 2.0).half()
+        want = x.float() @ w.t() + u.float() @ A.float()
+        lw = A
+    else:                                                   # y = x W + 2 (x A^T) B^T
+        u = ((x.float() @ A.float().t()) * 2.0).half()
+        want = x.float() @ w + u.float() @ B.float().t()
+        lw = B
+    L = layer.to(DEV)
+    out = torch.empty((M, K if transpose else N), dtype=torch.float16, device=DEV)
+    u_pad = torch.nn.functional.pad(u, (0, 64 - r)).to(DEV)
+    quant_cuda.gemm(x.to(DEV), L.qweight, out, L.scales, L.qzeros, L.g_idx, transpose=transpose, lora_u=u_pad,
+                    lora_w=lw.contiguous().to(DEV))
+    torch.cuda.synchronize()
+    assert quant_cuda.device_status() == 0
+    assert rel_fro(out, want) <= REL_TOL
+
+
+@pytest.mark.parametrize("fused", [True, False])
+def test_linear4bitlt_lora_training_step(fused):
+    models.fused_lora = fused
     m, layer = _module(512, 256, 128, True, 41, cls=models.Linear4bitLt, r=8, lora_alpha=16, lora_dropout=0.0)
     A, B = synth.make_lora(512, 256, 8, seed=42, dtype=torch.float32)
     m.lora_A["default"].weight.data.copy_(A)
     m.lora_B["default"].weight.data.copy_(B)
     x = synth.make_acts(160, 512, 43).to(DEV).requires_grad_(True)
-    y = m(x)
-    dy = torch.randn_like(y)
-    y.backward(dy)
+    try:
+        y = m(x)
+        dy = torch.randn_like(y)
+        y.backward(dy)
+    finally:
+        models.fused_lora = True
     w = orc.recons_v2(layer.qweight, layer.scales, layer.qzeros, layer.g_idx).float()
     xc, dyc = x.detach().cpu(), dy.cpu()
     assert rel_fro(y, xc.float() @ w + orc.lora_forward(xc, A, B, 2.0)) <= REL_TOL
