@@ -315,7 +315,8 @@ def run_gemm(args, local_rank):
         torch.cuda.synchronize(dev)
         return a.elapsed_time(b) / reps
 
-    M, out = 2048, {"M": M, "peak_tflops": peak, "peak_kind": kind, "shapes": {}}
+    M = 2048
+    out = {"M": M, "peak_tflops": peak, "peak_kind": kind, "shapes": {}}
     for K, N in [(5120, 5120), (5120, 13824), (13824, 5120)]:
         G = K // 128
         qw = torch.randint(-2 ** 31, 2 ** 31 - 1, (K // 8, N), device=dev, dtype=torch.int64, generator=gen).to(torch.int32)
