@@ -99,6 +99,27 @@ def require_cuda(*tensors) -> torch.device:
     return dev
 
 
+class on_device:
+    """Make ``dev`` the current CUDA device for the duration of a call; free when it already is."""
+    __slots__ = ("dev", "prev")
+
+    def __init__(self, dev: torch.device):
+        self.dev = dev.index if dev.index is not None else torch.cuda.current_device()
+        self.prev = -1
+
+    def __enter__(self):
+        cur = torch.cuda.current_device()
+        if cur != self.dev:
+            self.prev = cur
+            torch.cuda.set_device(self.dev)
+        return self
+
+    def __exit__(self, *exc):
+        if self.prev >= 0:
+            torch.cuda.set_device(self.prev)
+        return False
+
+
 def dtype_code(dt: torch.dtype) -> int:
     if dt == torch.float16:
         return Q4_F16

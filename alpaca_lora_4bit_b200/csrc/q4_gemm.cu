@@ -436,13 +436,20 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
                              CU_TENSOR_MAP_SWIZZLE_128B)) return e;
   const dim3 grid(nout / GM_TILE_N, (M + GM_TILE_M - 1) / GM_TILE_M), block(GM_THREADS);
   cudaStream_t st = (cudaStream_t)stream;
-  if (transpose) {
-    if (int e = check_cuda(cudaFuncSetAttribute(q4_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "gemm smem attribute")) return e;
-    q4_gemm_kernel<true><<<grid, block, smem, st>>>(amap, umap, p);
-  } else {
-    if (int e = check_cuda(cudaFuncSetAttribute(q4_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "gemm smem attribute")) return e;
-    q4_gemm_kernel<false><<<grid, block, smem, st>>>(amap, umap, p);
+  // raise the dynamic shared memory limit once per device and direction (the largest this kernel can ask for)
+  static bool attr_done[2][64] = {{false}};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64) dev = 0;
+  if (!attr_done[transpose ? 1 : 0][dev]) {
+    const int cap = 227 * 1024;
+    if (int e = check_cuda(transpose ? cudaFuncSetAttribute(q4_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap)
+                                     : cudaFuncSetAttribute(q4_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap),
+                           "gemm smem attribute")) return e;
+    attr_done[transpose ? 1 : 0][dev] = true;
   }
+  if (transpose) q4_gemm_kernel<true><<<grid, block, smem, st>>>(amap, umap, p);
+  else q4_gemm_kernel<false><<<grid, block, smem, st>>>(amap, umap, p);
   return check_cuda(cudaGetLastError(), "gemm launch");
 }
 

@@ -125,7 +125,8 @@ def apply_gradient_checkpointing(model: nn.Module) -> None:
         inner = layer.forward
 
         def wrapped(*args, _inner=inner, **kwargs):
-            return checkpoint(_inner, *args, use_reentrant=False, **kwargs)
+            # no dropout anywhere in the step, so there is no RNG state to save and restore
+            return checkpoint(_inner, *args, use_reentrant=False, preserve_rng_state=False, **kwargs)
 
         layer.forward = wrapped
     # the embedding output must carry a gradient or the checkpointed segments have nothing to differentiate
@@ -164,7 +165,11 @@ class LoraFinetuner:
         if not self.params:
             raise ValueError("model has no trainable parameters (wrap it with add_lora first)")
         self.flat = FlatGrads(self.params)
-        self.opt = torch.optim.AdamW(self.params, lr=lr, fused=self.params[0].is_cuda)
+        on_gpu = self.params[0].is_cuda
+        self.opt = torch.optim.AdamW(self.params, lr=lr, fused=on_gpu, capturable=on_gpu)
+        self._graph = None
+        self._static_ids = None
+        self._static_loss = None
         self.loss_scale = loss_scale
         self.autocast = autocast
         self.group = group
@@ -173,9 +178,44 @@ class LoraFinetuner:
             dynamic_scale = self.params[0].is_cuda and autocast
         self.scaler = torch.amp.GradScaler("cuda", init_scale=loss_scale) if dynamic_scale else None
 
+    def capture(self, example_ids: torch.Tensor, warmup: int = 3) -> bool:
+        """Record the whole step (forward, backward, gradient all-reduce, AdamW) as one CUDA graph for
+        batches shaped like ``example_ids``; later ``step`` calls of that shape replay it.  The ~700
+        kernel launches of the quant linears and the thousands of small framework kernels around them
+        are otherwise issued one by one from Python, which is what bounds the step time.  Returns False
+        (and stays on the eager path) if the step cannot be captured."""
+        if not example_ids.is_cuda:
+            return False
+        try:
+            self._static_ids = example_ids.clone()
+            side = torch.cuda.Stream(device=example_ids.device)
+            side.wait_stream(torch.cuda.current_stream(example_ids.device))
+            with torch.cuda.stream(side):
+                for _ in range(warmup):
+                    self._eager_step(self._static_ids)
+            torch.cuda.current_stream(example_ids.device).wait_stream(side)
+            torch.cuda.synchronize(example_ids.device)
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self._static_loss = self._eager_step(self._static_ids)
+            self._graph = graph
+            return True
+        except Exception as exc:                                   # capture is an optimisation, never a requirement
+            print(f"finetune_step: CUDA-graph capture not possible ({type(exc).__name__}: {exc}); running eagerly")
+            self._graph = None
+            torch.cuda.synchronize(example_ids.device)
+            return False
+
     def step(self, input_ids: torch.Tensor) -> torch.Tensor:
         """One optimisation step on a batch of token ids ``[B, T]`` (labels = inputs, shifted inside
         the model).  Returns the detached loss (a device scalar)."""
+        if self._graph is not None and input_ids.shape == self._static_ids.shape:
+            self._static_ids.copy_(input_ids, non_blocking=True)
+            self._graph.replay()
+            return self._static_loss
+        return self._eager_step(input_ids)
+
+    def _eager_step(self, input_ids: torch.Tensor) -> torch.Tensor:
         self.flat.zero()
         dev_type = input_ids.device.type
         with torch.autocast(device_type=dev_type, dtype=torch.float16, enabled=self.autocast and dev_type == "cuda"):

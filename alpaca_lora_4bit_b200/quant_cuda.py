@@ -39,7 +39,7 @@ def vecquant4recons_v2(mat, res, scales, zeros, g_idx) -> None:
     G = scales.shape[0]
     if scales.shape != (G, N) or zeros.shape != (G, N // 8) or g_idx.numel() < K:
         raise RuntimeError("quant_cuda: scales/zeros/g_idx shapes do not match mat")
-    with torch.cuda.device(dev):
+    with _lib.on_device(dev):
         _lib.check(_lib.lib().q4_recons_v2(mat.data_ptr(), res.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
                                            g_idx.data_ptr(), K, N, G, _lib.dtype_code(scales.dtype),
                                            _lib.stream_of(mat)), "recons_v2")
@@ -55,7 +55,7 @@ def vecquant4recons_v1(mat, res, scales, zeros) -> None:
         raise RuntimeError(f"quant_cuda: res must be [{K},{N}] and share the dtype of scales and zeros")
     if scales.numel() != N or zeros.numel() != N:
         raise RuntimeError("quant_cuda: v1 scales and zeros hold one value per column")
-    with torch.cuda.device(dev):
+    with _lib.on_device(dev):
         _lib.check(_lib.lib().q4_recons_v1(mat.data_ptr(), res.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
                                            K, N, _lib.dtype_code(scales.dtype), _lib.stream_of(mat)), "recons_v1")
 
@@ -71,7 +71,7 @@ def vecquant2recons_v2(mat, res, scales, zeros, g_idx) -> None:
         raise RuntimeError(f"quant_cuda: res must be [{K},{N}] of {scales.dtype}")
     if scales.shape != (G, N) or zeros.shape != (G, N // 16) or g_idx.numel() < K:
         raise RuntimeError("quant_cuda: scales/zeros/g_idx shapes do not match mat")
-    with torch.cuda.device(dev):
+    with _lib.on_device(dev):
         _lib.check(_lib.lib().q2_recons_v2(mat.data_ptr(), res.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
                                            g_idx.data_ptr(), K, N, G, _lib.dtype_code(scales.dtype),
                                            _lib.stream_of(mat)), "recons2_v2")
@@ -92,7 +92,7 @@ def gemv(x, qweight, y, scales, zeros, g_idx, groupsize, flags, bias=None) -> No
             raise RuntimeError("quant_cuda: scales/zeros shapes do not match mat")
     L = _lib.lib()
     ydt = _lib.dtype_code(y.dtype)
-    with torch.cuda.device(dev):
+    with _lib.on_device(dev):
         st = _lib.stream_of(x)
         for m0 in range(0, M, 16):
             m = min(16, M - m0)
@@ -127,7 +127,7 @@ def gemm(x, qweight, out, scales, zeros, g_idx, transpose=False, bias=None, lora
         if lora_u.shape != (M, 64) or lora_w.shape != want_w or lora_u.dtype != torch.float16 or lora_w.dtype != torch.float16:
             raise RuntimeError(f"quant_cuda: gemm low-rank term needs lora_u [M,64] and lora_w {want_w}, both fp16")
     L = _lib.lib()
-    with torch.cuda.device(dev):
+    with _lib.on_device(dev):
         st = _lib.stream_of(x)
         if transpose:
             rc = L.q4_gemm_bwd(x.data_ptr(), qweight.data_ptr(), out.data_ptr(), scales.data_ptr(), zeros.data_ptr(),

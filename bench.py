@@ -259,6 +259,16 @@ def run_finetune(args, rank, world, local_rank):
 
     for i in range(warm):
         one(i)
+    graphed = False
+    if not args.finetune_eager:
+        graphed = ft.capture(ids_host[0].to(dev))
+        if world > 1:                                   # all ranks must take the same path
+            flag = torch.tensor([1 if graphed else 0], device=dev)
+            torch.distributed.all_reduce(flag, op=torch.distributed.ReduceOp.MIN)
+            if int(flag[0]) == 0:
+                ft._graph, graphed = None, False
+        for i in range(warm):
+            one(i)
     if world > 1:
         torch.distributed.barrier()
     torch.cuda.synchronize(dev)
@@ -282,7 +292,7 @@ def run_finetune(args, rank, world, local_rank):
            "steps": steps, "ms_per_step": round(ms / steps, 2), "layers": shape.num_hidden_layers,
            "micro_batch": [B, T], "lora": "r=8 alpha=16 q_proj,v_proj, dropout 0 (as the reference forces under checkpointing)",
            "lora_params": fs.lora_param_count(model), "allreduce_bytes_per_step": 4 * fs.lora_param_count(model) if world > 1 else 0,
-           "model_tflops_per_s": round(tps * flops_per_token / 1e12, 1), "loss_first_last": [round(losses[0], 4), round(losses[-1], 4)],
+           "model_tflops_per_s": round(tps * flops_per_token / 1e12, 1), "loss_first_last": [round(losses[0], 4), round(losses[-1], 4)], "launch": "cuda_graph" if graphed else "eager",
            "h2d_bytes_per_step": B * T * 8, "d2h_bytes_per_step": 4}
     del ft, model
     torch.cuda.empty_cache()
@@ -381,6 +391,7 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-gemm", action="store_true", help="skip the M=2048 fused GEMM leg")
     ap.add_argument("--finetune-steps", type=int, default=5, help="timed LLaMA-7B LoRA finetune steps (0 = skip)")
+    ap.add_argument("--finetune-eager", action="store_true", help="do not capture the finetune step as a CUDA graph")
     ap.add_argument("--finetune-layers", type=int, default=0, help="override the number of decoder layers (0 = 32)")
     args = ap.parse_args()
 
