@@ -129,6 +129,17 @@ def dtype_code(dt: torch.dtype) -> int:
 
 
 _workspaces: dict = {}
+_WS_BYTES = 4 << 20          # covers q4_gemv_workspace_bytes() of every shape the decode kernels accept
+
+
+def workspace_for(device: torch.device, stream_handle: int) -> torch.Tensor:
+    """The decode workspace of one (device, stream): allocated zeroed on first use, then reused."""
+    key = (device.index, stream_handle)
+    ws = _workspaces.get(key)
+    if ws is None:
+        ws = torch.zeros(_WS_BYTES, dtype=torch.uint8, device=device)
+        _workspaces[key] = ws
+    return ws
 
 
 def workspace(device: torch.device, nbytes: int) -> torch.Tensor:

@@ -21,6 +21,8 @@ anything smaller to the decode kernel.  Module-level switches keep their referen
 """
 from __future__ import annotations
 
+import math
+
 import numpy as np
 import torch
 
@@ -52,17 +54,18 @@ def get_buffer(shape_of_qweight, dtype=torch.float16, device='cuda', bits=4):
 
 
 def _decode(x, qweight, scales, zeros, g_idx, groupsize, flags):
-    outshape = x.shape[:-1] + (qweight.shape[1],)
-    x2 = x.reshape(-1, x.shape[-1])
-    dtype = x2.dtype
-    xh = x2 if dtype == torch.float16 else x2.half()
-    y = torch.empty((x2.shape[0], qweight.shape[-1]), dtype=torch.float16 if dtype == torch.float16 else torch.float32,
+    dtype = x.dtype
+    x2 = x if x.dim() == 2 else x.reshape(-1, x.shape[-1])
+    if dtype != torch.float16:
+        x2 = x2.half()
+    if not x2.is_contiguous():
+        x2 = x2.contiguous()
+    y = torch.empty((x2.shape[0], qweight.shape[1]), dtype=torch.float16 if dtype == torch.float16 else torch.float32,
                     device=x.device)
-    sh = scales if scales.dtype == torch.float16 else scales.half()
-    quant_cuda.gemv(xh.contiguous(), qweight, y, sh, zeros, g_idx, groupsize, flags)
+    quant_cuda.gemv(x2, qweight, y, scales if scales.dtype == torch.float16 else scales.half(), zeros, g_idx, groupsize, flags)
     if y.dtype != dtype:
         y = y.to(dtype)
-    return y.reshape(outshape)
+    return y if x.dim() == 2 else y.reshape(x.shape[:-1] + (qweight.shape[1],))
 
 
 def _matmul4bit_v1(x, qweight, scales, zeros):
@@ -147,7 +150,7 @@ def _matmul2bit_v2_recons(x, qweight, scales, zeros, g_idx, transpose=False):
 
 def matmul4bit(x, qweight, scales, zeros, g_idx=None, groupsize=None):
     """No-grad entry (matmul_utils_4bit.py:146-170): format from ``zeros.dtype``, kernel from M."""
-    rows = int(np.prod(x.shape[:-1]))
+    rows = math.prod(x.shape[:-1])
     large = use_new and auto_switch and rows > auto_switch_thd
     if zeros.dtype != torch.int32:            # v1: float zeros
         if large:

@@ -78,29 +78,39 @@ def vecquant2recons_v2(mat, res, scales, zeros, g_idx) -> None:
 
 
 def gemv(x, qweight, y, scales, zeros, g_idx, groupsize, flags, bias=None) -> None:
-    """``y (+)= x @ W`` through ``q4_gemv`` in slabs of at most 16 rows; x, scales fp16."""
-    dev = _lib.require_cuda(x, qweight, y, scales, zeros, g_idx, bias)
+    """``y (+)= x @ W`` through ``q4_gemv`` in slabs of at most 16 rows; x, scales fp16.
+
+    This is the per-token path of decode, so the host side is kept short: one stream lookup, one
+    cached workspace, one foreign call (shape and pointer checks happen inside the library)."""
+    if not (x.is_cuda and x.is_contiguous() and y.is_contiguous() and qweight.is_cuda and scales.is_contiguous()):
+        _lib.require_cuda(x, qweight, y, scales, zeros, g_idx, bias)
+        raise RuntimeError("quant_cuda: gemv tensors must be contiguous CUDA tensors")
     M, K = x.shape
-    R, N = qweight.shape
-    if R * 8 != K or y.shape != (M, N):
-        raise RuntimeError(f"quant_cuda: shapes x{tuple(x.shape)} mat{tuple(qweight.shape)} mul{tuple(y.shape)} disagree")
-    if flags & _lib.GEMV_V1:
-        G = 1
-    else:
-        G = scales.shape[0]
-        if scales.shape != (G, N) or zeros.shape != (G, N // 8):
-            raise RuntimeError("quant_cuda: scales/zeros shapes do not match mat")
-    L = _lib.lib()
-    ydt = _lib.dtype_code(y.dtype)
+    N = qweight.shape[1]
+    if qweight.shape[0] * 8 != K or y.shape[0] != M or y.shape[1] != N or x.dtype != torch.float16 or scales.dtype != torch.float16:
+        raise RuntimeError(f"quant_cuda: shapes x{tuple(x.shape)} mat{tuple(qweight.shape)} mul{tuple(y.shape)} disagree "
+                           f"or x / scales are not fp16")
+    G = 1 if (flags & _lib.GEMV_V1) else scales.shape[0]
+    dev = x.device
+    st = torch.cuda.current_stream(dev).cuda_stream
+    ws = _lib.workspace_for(dev, st)
+    ydt = _lib.Q4_F16 if y.dtype == torch.float16 else _lib.Q4_F32 if y.dtype == torch.float32 else _lib.dtype_code(y.dtype)
+    fn = _lib.lib().q4_gemv
+    gp = None if g_idx is None else g_idx.data_ptr()
+    bp = None if bias is None else bias.data_ptr()
     with _lib.on_device(dev):
-        st = _lib.stream_of(x)
+        if M <= 16:
+            rc = fn(x.data_ptr(), qweight.data_ptr(), y.data_ptr(), scales.data_ptr(), zeros.data_ptr(), gp, bp,
+                    M, K, N, G, groupsize, ydt, flags, ws.data_ptr(), ws.numel(), st)
+            if rc:
+                _lib.check(rc, "gemv")
+            return
+        row_x, row_y = K * x.element_size(), N * y.element_size()
         for m0 in range(0, M, 16):
-            m = min(16, M - m0)
-            need = L.q4_gemv_workspace_bytes(m, K, N)
-            ws = _lib.workspace(dev, need)
-            _lib.check(L.q4_gemv(x[m0:m0 + m].data_ptr(), qweight.data_ptr(), y[m0:m0 + m].data_ptr(),
-                                 scales.data_ptr(), zeros.data_ptr(), _lib.ptr(g_idx), _lib.ptr(bias),
-                                 m, K, N, G, groupsize, ydt, flags, ws.data_ptr(), ws.numel(), st), "gemv")
+            rc = fn(x.data_ptr() + m0 * row_x, qweight.data_ptr(), y.data_ptr() + m0 * row_y, scales.data_ptr(),
+                    zeros.data_ptr(), gp, bp, min(16, M - m0), K, N, G, groupsize, ydt, flags, ws.data_ptr(), ws.numel(), st)
+            if rc:
+                _lib.check(rc, "gemv")
 
 
 def gemm(x, qweight, out, scales, zeros, g_idx, transpose=False, bias=None, lora_u=None, lora_w=None) -> None:

@@ -362,6 +362,57 @@ def run_gemm(args, local_rank):
     return out
 
 
+def reference_gpu(args):
+    """The reference's own decode path on this GPU: its compiled ``quant_cuda`` kernels (oracle/_ref, built
+    unmodified from the reference sources) driven exactly as ``matmul_utils_4bit._matmul4bit_v2`` drives them
+    in its default ``faster_mode='old_faster'`` (matmul_utils_4bit.py:84-87,94): zero-filled fp32 y, x.half(),
+    scales.float() per call, the kernel on the legacy default stream, y.to(dtype).  Returns None when the
+    extension is not there or there is no GPU."""
+    from oracle import build_ref
+    if not torch.cuda.is_available():
+        return None
+    ref = build_ref.load()
+    if ref is None:
+        return None
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    pool = make_pool(args.copies, dev, 1234)
+    gen = torch.Generator(device=dev).manual_seed(99)
+    xs = {K: torch.randn((1, K), generator=gen, device=dev).half() for K in (4096, 11008)}
+
+    def matmul4bit_v2(x, l):
+        y = torch.zeros((x.shape[0], l.N), dtype=torch.float32, device=x.device)
+        ref.vecquant4matmul_old_faster(x.half(), l.qweight, y, l.scales.float(), l.qzeros, GROUPSIZE, x.shape[-1] // 2)
+        return y.to(x.dtype)
+
+    def step():
+        return [matmul4bit_v2(xs[l.K], l) for l in pool]
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize(dev)
+    steps = max(1, min(args.steps, 50))
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize(dev)
+    ms = e0.elapsed_time(e1) / steps
+    xh = {K: torch.randn((1, K)).half().pin_memory() for K in (4096, 11008)}
+    yh = [torch.empty((1, l.N), dtype=torch.float16).pin_memory() for l in pool]
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        outs = [matmul4bit_v2(xh[l.K].to(dev, non_blocking=True), l) for l in pool]
+        for o, h in zip(outs, yh):
+            h.copy_(o, non_blocking=True)
+        torch.cuda.synchronize(dev)
+    e2e_ms = (time.perf_counter() - t0) * 1e3 / steps
+    bps = bytes_per_step(args.copies)
+    return {"gbs": bps / (ms * 1e-3) / 1e9, "ms": ms, "e2e_gbs": bps / (e2e_ms * 1e-3) / 1e9, "launches": len(pool),
+            "h2d": sum(xh[l.K].numel() * 2 for l in pool), "d2h": sum(y.numel() * 2 for y in yh)}
+
+
 def cpu_reference(sample_layers=1, reps=3, threads=None):
     """The reference composition on the host: reconstruct fp16 [K,N] + fp32 matmul, M=1."""
     from oracle import q4_oracle as orc
@@ -404,6 +455,22 @@ def main():
 
     if args.impl == "reference":
         if rank != 0:
+            return
+        rg = reference_gpu(args)
+        if rg is not None:
+            line = {"impl": "reference", "metric": METRIC, "value": round(rg["gbs"], 1), "unit": UNIT, "n_gpus": 1,
+                    "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(rg["ms"], 5), "higher_is_better": True,
+                    "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+                    "config": dict(config, launch="eager, legacy default stream (as the reference launches)",
+                                   parallelism="one GPU (the reference arm does not replicate)"),
+                    "reference_path": "the reference's quant_cuda kernels, built unmodified for sm_100a (oracle/_ref), driven as "
+                                      "matmul_utils_4bit._matmul4bit_v2 does with faster_mode='old_faster'",
+                    "cpu_baseline": {"value": round(rg["gbs"], 1), "unit": UNIT, "cores": 0, "kind": "reference",
+                                     "sample": "the whole workload, on the GPU: the reference has no CPU implementation of this path"},
+                    "e2e": {"value": round(rg["e2e_gbs"], 1), "unit": UNIT, "h2d_bytes_per_step": rg["h2d"],
+                            "d2h_bytes_per_step": rg["d2h"]},
+                    "gpu_launches": 0}
+            print(json.dumps(line))
             return
         steps = max(1, min(args.steps, 5))
         gbs, sec, threads = cpu_reference(reps=max(1, min(args.warmup, 2)) + steps)

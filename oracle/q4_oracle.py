@@ -5,13 +5,16 @@ This file restates, on the CPU with torch tensors, the arithmetic of the referen
 ``__graft_entry__.smoke()`` and ``bench.py``'s CPU-baseline / ``--impl reference`` legs may
 import it; the shipped package never does.
 
-Parity status: **parity unpinned by the reference's own tests.**  The reference has no CPU
+Parity status: **pinned against the reference's own kernels.**  The reference has no CPU
 implementation of this path and its only tests are whole-model runs that need a checkpoint
-download (tests/test_cuda_generation.py:56-73, tests/test_cuda_finetune.py:87), so no golden
-vector of the reference pins these functions at the operator boundary.  The pins that do exist
-are (1) an independent scalar re-derivation from the kernel source, element by element
-(``tests/golden/make_golden.py``), and (2) where ``oracle/_ref`` has been built, the reference's
-own kernels run on the GPU and compared bit for bit (``tests/test_reference_kernels.py``).
+download (tests/test_cuda_generation.py:56-73, tests/test_cuda_finetune.py:87), so none of its
+test vectors reaches the operator boundary.  Instead its ``quant_cuda`` extension is compiled
+unmodified for sm_100a (``oracle/build_ref.py`` -> ``oracle/_ref/``) and
+``tests/test_reference_kernels.py`` runs those kernels on the GPU next to this oracle: the
+reconstruct kernels (4-bit v2 with fp16 and fp32 scales, v1, 2-bit) agree with the functions below
+bit for bit, the decode kernels within the tolerance.  On a machine without a GPU the oracle is
+additionally held to an independent scalar re-derivation of the kernel source, element by
+element (``tests/golden/make_golden.py``).
 
 Arithmetic notes.  The reference kernels are templated on ``scalar_t``; for ``c10::Half`` every
 binary operator converts to float, computes, and rounds back to half, so
