@@ -66,6 +66,7 @@ __device__ __forceinline__ void gm_mark(unsigned long long* tr, int slot) {
 }
 
 __device__ __forceinline__ bool wait_bar(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait(bar, parity)) return true;        // the common case once the pipeline is full
   const uint32_t lim = *abort_flag ? 4u : GM_WAIT_TRIES;
   for (uint32_t i = 0; i < lim; ++i)
     if (mbar_try_wait_sleep(bar, parity, 2000u)) return true;
@@ -88,8 +89,8 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__
   uint64_t* acc_full = empty + GM_MAX_STAGES;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  __half* s_tab = reinterpret_cast<__half*>(smem + S * GM_STAGE_BYTES + 256);     // forward: [G][128]
-  __half* zp_tab = s_tab + (size_t)p.G * GM_TILE_N;
+  // forward: [G][128 scales | 128 rn(s*(z+1))], 512 bytes per group
+  const uint32_t tab = smem_u32(smem + S * GM_STAGE_BYTES + 256);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int out0 = blockIdx.x * GM_TILE_N;            // first output column (n forward, k backward)
@@ -167,8 +168,9 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__
         const int g = i / (GM_TILE_N / 8), c8 = i % (GM_TILE_N / 8);
         const uint4 s = __ldg(reinterpret_cast<const uint4*>(p.scales + (size_t)g * N + out0 + 8 * c8));
         const uint32_t zw = __ldg(p.qzeros + (size_t)g * (N >> 3) + ((out0 + 8 * c8) >> 3));
-        *reinterpret_cast<uint4*>(s_tab + (size_t)g * GM_TILE_N + 8 * c8) = s;
-        *reinterpret_cast<uint4*>(zp_tab + (size_t)g * GM_TILE_N + 8 * c8) = zero_terms(s, zw);
+        const uint4 z = zero_terms(s, zw);
+        sts_v4(tab + g * 512 + 16 * c8, s.x, s.y, s.z, s.w);
+        sts_v4(tab + g * 512 + 256 + 16 * c8, z.x, z.y, z.z, z.w);
       }
       named_bar_sync(1, GM_DEQ_THREADS * GM_DEQ_GROUPS);
     }
@@ -238,26 +240,14 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__
       if (threadIdx.x == 64 && it < 40) gm_mark(p.trace, 65 + 3 * (it / 2));
       unsigned char* bst = stages + (size_t)st * GM_STAGE_BYTES + GM_A_BYTES;
       // forward: panel (chunk16 / 8) of [64 rows][128 B]; backward: one panel of [128 rows][128 B]
-      unsigned char* rows8 = TRANSPOSE ? bst + r * 1024 : bst + (chunk16 >> 3) * 8192 + r * 1024;
-      const int cc = chunk16 & 7;
-      uint4 s, zp;
-      int cur = -1;
-      const int ncol = TRANSPOSE ? it * GM_TILE_C + 8 * chunk16 : 8 * chunk16;    // backward: global column
-#define Q4_DEQ(J, BYTE, ODD)                                                                      \
-      if (gi[J] != cur) {                                                                         \
-        cur = gi[J];                                                                              \
-        if (TRANSPOSE) {                                                                          \
-          s = __ldg(reinterpret_cast<const uint4*>(p.scales + (size_t)cur * N + ncol));           \
-          zp = zero_terms(s, __ldg(p.qzeros + (size_t)cur * (N >> 3) + (ncol >> 3)));             \
-        } else {                                                                                  \
-          s = *reinterpret_cast<const uint4*>(s_tab + (size_t)cur * GM_TILE_N + ncol);            \
-          zp = *reinterpret_cast<const uint4*>(zp_tab + (size_t)cur * GM_TILE_N + ncol);          \
-        }                                                                                         \
-      }                                                                                           \
-      deq_row<J, BYTE, ODD>(rows8, cc, w, s, zp);
-      Q4_DEQ(0, 0, false) Q4_DEQ(1, 0, true) Q4_DEQ(2, 1, false) Q4_DEQ(3, 1, true)
-      Q4_DEQ(4, 2, false) Q4_DEQ(5, 2, true) Q4_DEQ(6, 3, false) Q4_DEQ(7, 3, true)
-#undef Q4_DEQ
+      const uint32_t rows8 = smem_u32(bst) + (TRANSPOSE ? r * 1024 : (chunk16 >> 3) * 8192 + r * 1024);
+      const int4 ga_now = make_int4(gi[0], gi[1], gi[2], gi[3]), gb_now = make_int4(gi[4], gi[5], gi[6], gi[7]);
+      if (TRANSPOSE) {
+        const int ncol = it * GM_TILE_C + 8 * chunk16;             // global column of the task
+        deq_task_global(rows8, chunk16 & 7, w, ga_now, gb_now, p.scales + ncol, p.qzeros + (ncol >> 3), N);
+      } else {
+        deq_task_tables(rows8, chunk16 & 7, w, ga_now, gb_now, tab + 16 * chunk16);
+      }
       fence_async_smem();                          // generic-proxy stores -> visible to the tensor core
       __syncwarp();
       if (lane == 0) mbar_arrive(&full_b[st]);
@@ -306,11 +296,15 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__
 
 static unsigned long long* g_gemm_trace = nullptr;
 
+static int g_gemm_variant = 0;                // 0 = choose per shape, 1 = single-CTA kernel, 2 = CTA-pair kernel
+
 static size_t gemm_smem_bytes(bool transpose, int G, int stages) {
   return 1024 + (size_t)stages * GM_STAGE_BYTES + 256 + (transpose ? 0 : (size_t)2 * G * GM_TILE_N * sizeof(__half));
 }
 
 }  // namespace q4
+
+#include "q4_gemm2.cuh"
 
 using namespace q4;
 
@@ -326,44 +320,73 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
   if (lora_r > 0 && (!lora_u || !lora_w || !aligned16(lora_u) || !aligned16(lora_w)))
     return fail(Q4_E_BADARG, "gemm: the low-rank term needs 16-byte aligned lora_u [M,64] and lora_w");
   if (int e = check_device()) return e;
+  const int contract = transpose ? N : K, nout = transpose ? K : N;
+  const int stages2 = gemm2_stages(transpose, G);
+  const bool pair_ok = nout % G2_TILE_N == 0 && stages2 > 0;
+  if (g_gemm_variant == 2 && !pair_ok)
+    return fail(Q4_E_SHAPE, "gemm: the CTA-pair kernel needs %d output columns to be a multiple of 256 and G=%d tables to fit", nout, G);
+  const bool use_pair = pair_ok && g_gemm_variant != 1;
   int stages = GM_MAX_STAGES;
   while (stages > 2 && gemm_smem_bytes(transpose, G, stages) > 227 * 1024) --stages;
-  const size_t smem = gemm_smem_bytes(transpose, G, stages);
+  if (use_pair) stages = stages2;
+  const size_t smem = use_pair ? gemm2_smem_bytes(transpose, G, stages) : gemm_smem_bytes(transpose, G, stages);
   if (smem > 227 * 1024) return fail(Q4_E_SHAPE, "gemm: scale tables for G=%d groups do not fit shared memory", G);
 
   GemmParams p;
   p.qw = (const uint32_t*)qweight; p.scales = (const __half*)scales; p.qzeros = (const uint32_t*)qzeros;
   p.g_idx = g_idx; p.bias = (const __half*)bias; p.out = (__half*)out;
   p.M = M; p.K = K; p.N = N; p.G = G;
-  const int contract = transpose ? N : K, nout = transpose ? K : N;
   p.n_contract_tiles = contract / GM_TILE_C;
   p.stages = stages;
   p.trace = g_gemm_trace;
   p.lora_w = lora_r > 0 ? (const __half*)lora_w : nullptr;
   p.lora_r = lora_r;
+  const int box_rows = use_pair ? 128 : GM_TILE_M;    // activation rows one TMA copy brings
   CUtensorMap amap;
   if (int e = make_tmap_2d(&amap, act, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)contract, (uint64_t)M,
-                           (uint64_t)contract * 2, GM_TILE_C, GM_TILE_M, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
+                           (uint64_t)contract * 2, GM_TILE_C, box_rows, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
   CUtensorMap umap = amap;
   if (lora_r > 0)
-    if (int e = make_tmap_2d(&umap, lora_u, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, 64, (uint64_t)M, 128, GM_TILE_C, GM_TILE_M,
+    if (int e = make_tmap_2d(&umap, lora_u, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, 64, (uint64_t)M, 128, GM_TILE_C, box_rows,
                              CU_TENSOR_MAP_SWIZZLE_128B)) return e;
-  const dim3 grid(nout / GM_TILE_N, (M + GM_TILE_M - 1) / GM_TILE_M), block(GM_THREADS);
   cudaStream_t st = (cudaStream_t)stream;
-  // raise the dynamic shared memory limit once per device and direction (the largest this kernel can ask for)
-  static bool attr_done[2][64] = {{false}};
+  // once per device, direction and kernel: raise the dynamic shared memory limit to the largest the
+  // kernel can ask for and, for the pair kernel, ask how many pairs can be resident at once
+  static bool attr_done[2][2][64] = {{{false}}};
+  static int max_pairs[2][64] = {{0}};
   int dev = 0;
   cudaGetDevice(&dev);
   if (dev < 0 || dev >= 64) dev = 0;
-  if (!attr_done[transpose ? 1 : 0][dev]) {
+  const int tr = transpose ? 1 : 0;
+  if (!attr_done[use_pair ? 1 : 0][tr][dev]) {
     const int cap = 227 * 1024;
-    if (int e = check_cuda(transpose ? cudaFuncSetAttribute(q4_gemm_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap)
-                                     : cudaFuncSetAttribute(q4_gemm_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, cap),
-                           "gemm smem attribute")) return e;
-    attr_done[transpose ? 1 : 0][dev] = true;
+    const void* fn = use_pair ? (transpose ? (const void*)q4_gemm2_kernel<true> : (const void*)q4_gemm2_kernel<false>)
+                              : (transpose ? (const void*)q4_gemm_kernel<true> : (const void*)q4_gemm_kernel<false>);
+    if (int e = check_cuda(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, cap), "gemm smem attribute")) return e;
+    if (use_pair) {
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(2 * sm_count(), 1, 1); cfg.blockDim = dim3(G2_THREADS, 1, 1); cfg.dynamicSmemBytes = cap;
+      cudaLaunchAttribute at[1];
+      at[0].id = cudaLaunchAttributeClusterDimension;
+      at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+      cfg.attrs = at; cfg.numAttrs = 1;
+      int nc = 0;
+      if (cudaOccupancyMaxActiveClusters(&nc, fn, &cfg) != cudaSuccess || nc <= 0) { cudaGetLastError(); nc = sm_count() / 2; }
+      max_pairs[tr][dev] = nc;
+    }
+    attr_done[use_pair ? 1 : 0][tr][dev] = true;
   }
-  if (transpose) q4_gemm_kernel<true><<<grid, block, smem, st>>>(amap, umap, p);
-  else q4_gemm_kernel<false><<<grid, block, smem, st>>>(amap, umap, p);
+  if (use_pair) {
+    const int n_tiles = (nout / G2_TILE_N) * ((M + G2_TILE_M - 1) / G2_TILE_M);
+    const int pairs = n_tiles < max_pairs[tr][dev] ? n_tiles : max_pairs[tr][dev];
+    const dim3 grid(2 * pairs), block(G2_THREADS);
+    if (transpose) q4_gemm2_kernel<true><<<grid, block, smem, st>>>(amap, umap, p);
+    else q4_gemm2_kernel<false><<<grid, block, smem, st>>>(amap, umap, p);
+  } else {
+    const dim3 grid(nout / GM_TILE_N, (M + GM_TILE_M - 1) / GM_TILE_M), block(GM_THREADS);
+    if (transpose) q4_gemm_kernel<true><<<grid, block, smem, st>>>(amap, umap, p);
+    else q4_gemm_kernel<false><<<grid, block, smem, st>>>(amap, umap, p);
+  }
   return check_cuda(cudaGetLastError(), "gemm launch");
 }
 
@@ -377,6 +400,12 @@ extern "C" int q4_gemm_bwd(const void* dy, const int32_t* qweight, void* dx, con
                            const int32_t* g_idx, const void* lora_v, const void* lora_a, int lora_r,
                            int M, int K, int N, int G, q4_stream_t stream) {
   return gemm_launch(true, dy, qweight, dx, scales, qzeros, g_idx, nullptr, lora_v, lora_a, lora_r, M, K, N, G, stream);
+}
+
+extern "C" int q4_gemm_set_variant(int variant) {
+  if (variant < 0 || variant > 2) return fail(Q4_E_BADARG, "gemm_set_variant: %d is not 0 (choose per shape), 1 (single CTA) or 2 (CTA pair)", variant);
+  g_gemm_variant = variant;
+  return Q4_OK;
 }
 
 extern "C" int q4_gemm_set_trace(void* device_buffer) {

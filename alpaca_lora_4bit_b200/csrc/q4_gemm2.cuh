@@ -1,0 +1,334 @@
+// The fused dequant-GEMM on CTA pairs (tcgen05 cta_group::2), persistent over output tiles.
+// Included by q4_gemm.cu after GemmParams / wait_bar / g_gemm_status are defined.
+//
+// A pair of CTAs (a cluster of two, on the two SMs of one TPC) computes 256 x 256 output tiles:
+// CTA r of the pair holds activation rows 128r..128r+127 and dequantises the tile's output columns
+// 128r..128r+127; one tcgen05.mma issued by the even CTA multiplies all 256 rows by all 256 columns
+// and leaves rows 128r.. of the product in CTA r's TMEM.  Per 16 contraction elements each SM
+// reads 8 KiB of operands for 128 x 256 x 16 multiply-adds - half the shared-memory traffic per
+// flop of a single-CTA 128 x 128 instruction, which is what bounds that form.
+//
+// The grid is one pair per pair of SMs; every pair walks the tile list with a stride of the number
+// of pairs.  TMEM holds two accumulators (2 x 256 columns), so the epilogue of a tile overlaps the
+// MMAs of the next.  Roles (512 threads per CTA):
+//   warp 0        TMA producer for this CTA's activation rows; completion bytes of both CTAs are
+//                 counted on the even CTA's barrier
+//   warp 1        owns TMEM; in the even CTA one elected thread issues the MMAs and the commits
+//   warps 2-4, 6-8, 10-11   two groups of four dequantise W for alternate pipeline stages (as in
+//                 the single-CTA kernel) and arrive on the even CTA's barrier
+//   warps 12-15   epilogue: tcgen05.ld -> (+bias) -> fp16 -> global, one TMEM lane quarter each
+// Every wait is bounded; on expiry a status word is set and the kernel runs on without waiting.
+#pragma once
+
+namespace q4 {
+
+constexpr int G2_TILE_N = 256;                // output columns per pair (128 dequantised per CTA)
+constexpr int G2_TILE_M = 256;                // output rows per pair (128 per CTA)
+constexpr int G2_A_BYTES = 128 * GM_TILE_C * 2;           // 16 KiB: this CTA's rows of the stage
+constexpr int G2_B_BYTES = 128 * 64 * 2;                  // 16 KiB: this CTA's columns of the stage
+constexpr int G2_STAGE_BYTES = G2_A_BYTES + G2_B_BYTES;
+constexpr int G2_MAX_STAGES = 6;
+constexpr int G2_THREADS = 512;
+constexpr int G2_TMEM_COLS = 512;             // two accumulators of 256 fp32 columns
+constexpr int G2_BAR_BYTES = 512;
+
+__device__ __forceinline__ bool wait_bar_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  const uint32_t lim = *abort_flag ? 4u : GM_WAIT_TRIES;
+  for (uint32_t i = 0; i < lim; ++i)
+    if (mbar_try_wait_sleep_cluster(bar, parity, 2000u)) return true;
+  *abort_flag = 1;
+  atomicExch(&g_gemm_status, Q4_STATUS_WAIT_EXPIRED);
+  return false;
+}
+
+// Wait of a warp that has nothing else to do for a long time (the epilogue between tiles, the TMA
+// producer ahead of the MMAs): sleeps between tries so that its polling does not take issue slots
+// from the dequant warps on the same scheduler.
+__device__ __forceinline__ bool wait_bar_idle(uint64_t* bar, uint32_t parity, volatile int* abort_flag, uint32_t sleep_ns) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const uint32_t lim = *abort_flag ? 4u : 200000u;
+  for (uint32_t i = 0; i < lim; ++i) {
+    __nanosleep(sleep_ns);
+    if (mbar_try_wait(bar, parity)) return true;
+  }
+  *abort_flag = 1;
+  atomicExch(&g_gemm_status, Q4_STATUS_WAIT_EXPIRED);
+  return false;
+}
+
+template <bool TRANSPOSE>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
+q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap umap, const GemmParams p) {
+  extern __shared__ unsigned char smem_raw[];
+  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  unsigned char* stages = smem;
+  const int S = p.stages;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + S * G2_STAGE_BYTES);     // even CTA: activation bytes + 4 dequant warps, of both CTAs
+  uint64_t* empty = full + 8;                                                   // both CTAs: stage read by the MMAs
+  uint64_t* acc_full = empty + 8;                                               // [2] both CTAs: accumulator complete
+  uint64_t* acc_empty = acc_full + 2;                                           // [2] even CTA: 4 epilogue warps x 2 CTAs
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  // forward: [G][128 scales | 128 rn(s*(z+1))], 512 bytes per group
+  const uint32_t tab = smem_u32(smem + S * G2_STAGE_BYTES + G2_BAR_BYTES);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const uint32_t rank = cluster_ctarank();
+  const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+  const int T = p.n_contract_tiles;
+  const int TT = T + (p.lora_r > 0 ? 1 : 0);          // one more stage for the low-rank term
+  const int lora_ks = (p.lora_r + 15) >> 4;           // its 16-wide MMA steps
+  const int n_out_total = TRANSPOSE ? p.K : p.N;
+  const int m_tiles = (p.M + G2_TILE_M - 1) / G2_TILE_M;
+  const int n_tiles = m_tiles * (n_out_total / G2_TILE_N);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < S; ++i) { mbar_init(&full[i], 1 + 8); mbar_init(&empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 8); }
+    *abort_flag = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&amap);
+  }
+  if (warp == 1) { tmem_alloc_pair(tmem_slot, G2_TMEM_COLS); tmem_relinquish_pair(); }
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();                                 // the peer's barriers exist before anything arrives on them
+  tc_fence_after();
+  const uint32_t tmem_acc = *tmem_slot;
+
+  // Warp w issues on scheduler w % 4.  The MMA warp (1) shares its scheduler with no dequant warp:
+  // its short instruction stream is the pacemaker of the whole pipeline and must not queue behind
+  // long arithmetic sequences.  Warps 5 and 9 therefore stay idle.
+  const int dw = (warp >= 2 && warp <= 11 && warp != 5 && warp != 9) ? warp - 2 - (warp > 5) - (warp > 9) : -1;
+
+  if (warp == 0) {
+    // ---------------- TMA producer: this CTA's 128 activation rows of every stage ----------------
+    if (lane == 0) {
+      int st = 0, use = 0;                             // stage and how often it has been used, over all tiles
+      const uint32_t full0 = mapa_u32(smem_u32(full), 0);
+      for (int tile = pair; tile < n_tiles; tile += n_pairs) {
+        const int m0 = (tile % m_tiles) * G2_TILE_M + 128 * (int)rank;
+        for (int it = 0; it < TT; ++it) {
+          if (use > 0) wait_bar_idle(&empty[st], (use - 1) & 1, abort_flag, 200);
+          if (rank == 0) mbar_arrive_expect_tx(&full[st], 2 * G2_A_BYTES);
+          unsigned char* dst = stages + (size_t)st * G2_STAGE_BYTES;
+          if (it < T) tma_load_2d_pair(dst, &amap, it * GM_TILE_C, m0, full0 + 8 * st);
+          else tma_load_2d_pair(dst, &umap, 0, m0, full0 + 8 * st);
+          if (++st == S) { st = 0; ++use; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------- MMA issuer (even CTA only) ----------------
+    if (rank == 0 && lane == 0) {
+      constexpr uint32_t idesc = idesc_f16(256, 256, !TRANSPOSE);
+      // descriptors of stage 0; the same descriptors address the same offsets in both CTAs' shared memory.
+      // A: K-major, 128-byte rows, 8-row groups 1024 B apart, 16 contraction elements = 32 B.
+      // forward  B: MN-major: 64 n contiguous (128 B) per k-row, next 64 n at +8192, 16 k-rows = 2048 B
+      // backward B: K-major like A
+      const uint64_t ad0 = smem_desc_sw128(smem_u32(stages), 16, 1024);
+      const uint64_t bd0 = TRANSPOSE ? smem_desc_sw128(smem_u32(stages) + G2_A_BYTES, 16, 1024)
+                                     : smem_desc_sw128(smem_u32(stages) + G2_A_BYTES, 8192, 1024);
+      constexpr uint64_t A_STEP = 32 >> 4, B_STEP = (TRANSPOSE ? 32 : 2048) >> 4, ST_STEP = G2_STAGE_BYTES >> 4;
+      int st = 0, use = 0, tl = 0;
+      uint64_t ad = ad0, bd = bd0;
+      for (int tile = pair; tile < n_tiles; tile += n_pairs, ++tl) {
+        const int acc = tl & 1, acc_use = tl >> 1;
+        if (acc_use > 0) wait_bar_cluster(&acc_empty[acc], (acc_use - 1) & 1, abort_flag);
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_acc + acc * 256;
+        const bool tron = p.trace != nullptr && tl == 1;
+        for (int it = 0; it < TT; ++it) {
+          if (tron && it < 12) gm_mark(p.trace, 5 * it);
+          wait_bar_cluster(&full[st], use & 1, abort_flag);
+          if (tron && it < 12) gm_mark(p.trace, 5 * it + 2);
+          tc_fence_after();
+          if (it < T) {
+            umma_f16_pair(d_tmem, ad, bd, idesc, it > 0 ? 1u : 0u);
+            umma_f16_pair(d_tmem, ad + A_STEP, bd + B_STEP, idesc, 1u);
+            umma_f16_pair(d_tmem, ad + 2 * A_STEP, bd + 2 * B_STEP, idesc, 1u);
+            umma_f16_pair(d_tmem, ad + 3 * A_STEP, bd + 3 * B_STEP, idesc, 1u);
+          } else {
+            for (int ks = 0; ks < lora_ks; ++ks) umma_f16_pair(d_tmem, ad + ks * A_STEP, bd + ks * B_STEP, idesc, 1u);
+          }
+          if (tron && it < 12) gm_mark(p.trace, 5 * it + 3);
+          umma_commit_pair(&empty[st]);                // frees the stage in both CTAs
+          if (tron && it < 12) gm_mark(p.trace, 5 * it + 4);
+          ad += ST_STEP; bd += ST_STEP;
+          if (++st == S) { st = 0; ++use; ad = ad0; bd = bd0; }
+        }
+        umma_commit_pair(&acc_full[acc]);
+      }
+    }
+  } else if (dw >= 0) {
+    // ---------------- dequantisers: this CTA's 128 output columns of every stage ----------------
+    const int grp = dw >> 2;                                       // takes the stage uses g with g % 2 == grp
+    const int tid = ((dw & 3) << 5) | lane;                        // 0..127 within the group
+    const int chunk16 = TRANSPOSE ? (tid & 7) : (tid & 15);        // 16-byte chunk (8 columns) within the stage's n-range
+    const int r = TRANSPOSE ? (tid >> 3) : (tid >> 4);             // packed row within the stage
+    const int N = p.N;
+    const uint32_t full0 = mapa_u32(smem_u32(full), 0);            // the even CTA's full[0]
+    int tl = 0, tab_out0 = -1;
+    int st = grp, use = 0;                                         // of this group's next stage use (g = grp, grp + 2, ...)
+    for (int tile = pair; tile < n_tiles; tile += n_pairs, ++tl) {
+      const int out0 = (tile / m_tiles) * G2_TILE_N + 128 * (int)rank;   // first output column (n forward, k backward)
+      const int gbase = tl * TT;
+      if (!TRANSPOSE && out0 != tab_out0) {
+        // tables for the CTA's 128 columns: scale and rn(s*(z+1)) of every group
+        if (tab_out0 >= 0) named_bar_sync(1, GM_DEQ_THREADS * GM_DEQ_GROUPS);      // all readers of the old tables are done
+        for (int i = (dw << 5) | lane; i < p.G * 16; i += GM_DEQ_THREADS * GM_DEQ_GROUPS) {
+          const int g = i >> 4, c8 = i & 15;
+          const uint4 s = __ldg(reinterpret_cast<const uint4*>(p.scales + (size_t)g * N + out0 + 8 * c8));
+          const uint32_t zw = __ldg(p.qzeros + (size_t)g * (N >> 3) + ((out0 + 8 * c8) >> 3));
+          const uint4 z = zero_terms(s, zw);
+          sts_v4(tab + g * 512 + 16 * c8, s.x, s.y, s.z, s.w);
+          sts_v4(tab + g * 512 + 256 + 16 * c8, z.x, z.y, z.z, z.w);
+        }
+        named_bar_sync(1, GM_DEQ_THREADS * GM_DEQ_GROUPS);
+        tab_out0 = out0;
+      }
+      // packed words of the stage: rows (k0/8 + r), columns ncol0 .. ncol0+7
+      auto word_ptr = [&](int it) -> const uint32_t* {
+        const int prow = TRANSPOSE ? (out0 >> 3) + r : it * (GM_TILE_C >> 3) + r;
+        const int ncol = TRANSPOSE ? it * GM_TILE_C + 8 * chunk16 : out0 + 8 * chunk16;
+        return p.qw + (size_t)prow * N + ncol;
+      };
+      const int it0 = (grp ^ gbase) & 1;
+      uint4 wa = make_uint4(0, 0, 0, 0), wb = wa;
+      int4 ga = make_int4(0, 0, 0, 0), gb = ga;                      // groups of the task's 8 k-rows
+      if (it0 < T) {
+        wa = ldg_stream(word_ptr(it0)); wb = ldg_stream(word_ptr(it0) + 4);
+        const int k8 = TRANSPOSE ? out0 + 8 * r : it0 * GM_TILE_C + 8 * r;
+        ga = __ldg(reinterpret_cast<const int4*>(p.g_idx + k8));
+        gb = __ldg(reinterpret_cast<const int4*>(p.g_idx + k8 + 4));
+      }
+      for (int it = it0; it < TT; it += GM_DEQ_GROUPS, st += GM_DEQ_GROUPS) {
+        if (st >= S) { st -= S; ++use; }
+        unsigned char* bst = stages + (size_t)st * G2_STAGE_BYTES + G2_A_BYTES;
+        if (it == T) {
+          // ---- low-rank stage: B operand from lora_w instead of dequantised weights ----
+          if (use > 0 && lane == 0) wait_bar(&empty[st], (use - 1) & 1, abort_flag);
+          __syncwarp();
+          const int rr = p.lora_r, rows = 16 * lora_ks;
+          if (!TRANSPOSE) {
+            // column n = out0 + tid: element (j, n) = lora_B[n][j] into panel tid/64, row j, 128B-swizzled
+            const __half* src = p.lora_w + (size_t)(out0 + tid) * rr;
+            unsigned char* col = bst + (tid >> 6) * 8192 + ((tid & 7) << 1);
+            const int cc = (tid & 63) >> 3;
+            for (int j = 0; j < rows; ++j) {
+              const __half v = j < rr ? src[j] : __float2half(0.f);
+              *reinterpret_cast<__half*>(col + j * 128 + ((cc ^ (j & 7)) << 4)) = v;
+            }
+          } else {
+            // row k = out0 + tid: element (k, j) = lora_A[j][k], 8 j per 16-byte chunk
+            unsigned char* row = bst + tid * 128;
+            for (int c8 = 0; c8 < 2 * lora_ks; ++c8) {
+              uint4 o;
+              __half* oh = reinterpret_cast<__half*>(&o);
+#pragma unroll
+              for (int e = 0; e < 8; ++e) {
+                const int j = 8 * c8 + e;
+                oh[e] = j < rr ? p.lora_w[(size_t)j * p.K + out0 + tid] : __float2half(0.f);
+              }
+              *reinterpret_cast<uint4*>(row + ((c8 ^ (tid & 7)) << 4)) = o;
+            }
+          }
+          fence_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive_cluster(full0 + 8 * st);
+          continue;
+        }
+        const uint32_t w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
+        const int gi[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+        if (it + GM_DEQ_GROUPS < T) {                                // prefetch this group's next stage
+          wa = ldg_stream(word_ptr(it + GM_DEQ_GROUPS)); wb = ldg_stream(word_ptr(it + GM_DEQ_GROUPS) + 4);
+          if (!TRANSPOSE) {
+            const int k8 = (it + GM_DEQ_GROUPS) * GM_TILE_C + 8 * r;
+            ga = __ldg(reinterpret_cast<const int4*>(p.g_idx + k8));
+            gb = __ldg(reinterpret_cast<const int4*>(p.g_idx + k8 + 4));
+          }
+        }
+        const bool tr_on = p.trace && tl == 1 && dw == 0 && lane == 0 && it < 40;
+        if (tr_on) gm_mark(p.trace, 64 + 3 * (it >> 1));
+        if (use > 0 && lane == 0) wait_bar(&empty[st], (use - 1) & 1, abort_flag);
+        __syncwarp();
+        if (tr_on) gm_mark(p.trace, 65 + 3 * (it >> 1));
+        // forward: panel (chunk16 / 8) of [64 rows][128 B]; backward: one panel of [128 rows][128 B]
+        const uint32_t rows8 = smem_u32(bst) + (TRANSPOSE ? r * 1024 : (chunk16 >> 3) * 8192 + r * 1024);
+        const int4 ga_now = make_int4(gi[0], gi[1], gi[2], gi[3]), gb_now = make_int4(gi[4], gi[5], gi[6], gi[7]);
+        if (TRANSPOSE) {
+          const int ncol = it * GM_TILE_C + 8 * chunk16;             // global column of the task
+          deq_task_global(rows8, chunk16 & 7, w, ga_now, gb_now, p.scales + ncol, p.qzeros + (ncol >> 3), N);
+        } else {
+          deq_task_tables(rows8, chunk16 & 7, w, ga_now, gb_now, tab + 16 * chunk16);
+        }
+        fence_async_smem();                          // generic-proxy stores -> visible to the tensor core
+        __syncwarp();
+        if (lane == 0) mbar_arrive_cluster(full0 + 8 * st);
+        if (tr_on) gm_mark(p.trace, 66 + 3 * (it >> 1));
+      }
+    }
+  } else if (warp >= 12) {
+    // ---------------- epilogue: TMEM -> registers -> (+bias) -> fp16 -> global ----------------
+    const int quarter = warp & 3;                                  // TMEM lanes 32*quarter .. +31
+    const uint32_t acc_empty0 = mapa_u32(smem_u32(acc_empty), 0);  // the even CTA's acc_empty[0]
+    int tl = 0;
+    for (int tile = pair; tile < n_tiles; tile += n_pairs, ++tl) {
+      const int acc = tl & 1, acc_use = tl >> 1;
+      const int col0 = (tile / m_tiles) * G2_TILE_N;
+      const int m = (tile % m_tiles) * G2_TILE_M + 128 * (int)rank + 32 * quarter + lane;
+      if (threadIdx.x == 384 && tl < 8) gm_mark(p.trace, 200 + 3 * tl);
+      if (lane == 0) wait_bar_idle(&acc_full[acc], acc_use & 1, abort_flag, 1000);
+      __syncwarp();
+      tc_fence_after();
+      if (threadIdx.x == 384 && tl < 8) gm_mark(p.trace, 201 + 3 * tl);
+#pragma unroll 1
+      for (int cb = 0; cb < G2_TILE_N / 32; ++cb) {
+        uint32_t v[32];
+        tmem_ld32(tmem_acc + ((uint32_t)(32 * quarter) << 16) + acc * 256 + cb * 32, v);
+        tmem_ld_wait();
+        if (m < p.M) {
+          __half* dst = p.out + (size_t)m * n_out_total + col0 + cb * 32;
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            uint4 o;
+            uint32_t* ov = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              float f0 = __uint_as_float(v[8 * q + 2 * e]), f1 = __uint_as_float(v[8 * q + 2 * e + 1]);
+              if (!TRANSPOSE && p.bias) {
+                f0 += __half2float(p.bias[col0 + cb * 32 + 8 * q + 2 * e]);
+                f1 += __half2float(p.bias[col0 + cb * 32 + 8 * q + 2 * e + 1]);
+              }
+              ov[e] = as_u32(__floats2half2_rn(f0, f1));
+            }
+            *reinterpret_cast<uint4*>(dst + 8 * q) = o;
+          }
+        }
+      }
+      // this warp has read its part of the accumulator: the even CTA may overwrite it
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acc_empty0 + 8 * acc);
+      if (threadIdx.x == 384 && tl < 8) gm_mark(p.trace, 202 + 3 * tl);
+    }
+  }
+  // neither CTA may leave (or free TMEM) while its peer can still signal its barriers or read its tiles
+  tc_fence_before();
+  __syncthreads();
+  cluster_sync_all();
+  if (warp == 1) tmem_dealloc_pair(tmem_acc, G2_TMEM_COLS);
+}
+
+static size_t gemm2_smem_bytes(bool transpose, int G, int stages) {
+  return 1024 + (size_t)stages * G2_STAGE_BYTES + G2_BAR_BYTES + (transpose ? 0 : (size_t)2 * G * 128 * sizeof(__half));
+}
+
+// Pipeline depth the pair kernel gets for this layer (0 = its tables do not leave room for three stages).
+static int gemm2_stages(bool transpose, int G) {
+  int stages = G2_MAX_STAGES;
+  while (stages > 2 && gemm2_smem_bytes(transpose, G, stages) > 227 * 1024) --stages;
+  return stages >= 3 ? stages : 0;
+}
+
+}  // namespace q4

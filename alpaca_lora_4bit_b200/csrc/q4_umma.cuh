@@ -30,6 +30,33 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t adesc, uint64
 __device__ __forceinline__ void umma_commit(uint64_t* bar) {
   asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
+// ---- the same for a CTA pair (cta_group::2): the even CTA of the pair issues the MMA, which reads
+// 128 rows of A and half of B's columns from each CTA's shared memory and writes 128 accumulator
+// rows x all N columns into each CTA's TMEM.  Allocation, release and free are issued by the same
+// warp index in both CTAs.
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t* smem_dst, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_dst)), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// Arrives on the mbarrier at this shared-memory offset in BOTH CTAs of the pair when all
+// tcgen05.mma issued so far by this thread have completed.
+__device__ __forceinline__ void umma_commit_pair(uint64_t* bar) {
+  const uint16_t both = 3;
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+               ::"r"(smem_u32(bar)), "h"(both) : "memory");
+}
+
 // 32 lanes x 32 consecutive fp32 columns: thread i of the warp gets row (lane base + i).
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&v)[32]) {
   asm volatile(
@@ -60,21 +87,42 @@ __host__ __device__ constexpr uint32_t idesc_f16(int m, int n, bool b_mn_major) 
          ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
-// Dequantise 8 packed words (8 k-rows x 8 adjacent columns) and write the eight 16-byte chunks
-// into a [rows][128 B] panel with the 128B swizzle.  `s`/`zp` give scale and rn(s*(z+1)) of the 8
-// columns for each of the 8 rows (as four half2 each).
+// ---- shared memory through 32-bit shared-space addresses (no generic-pointer arithmetic) --------
+__device__ __forceinline__ void sts_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
+  uint4 v;
+  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+  return v;
+}
+
+// Dequantise row J (nibble J of each word) of 8 packed words (8 k-rows x 8 adjacent columns) and
+// write its 16-byte chunk into a [rows][128 B] panel with the 128B swizzle.  `rows8` is the
+// shared-space address of the task's first row, `chunk` the 16-byte column chunk, `s`/`zp` scale and
+// rn(s*(z+1)) of the 8 columns (four half2 each).
 template <int J, int BYTE, bool ODD>
-__device__ __forceinline__ void deq_row(unsigned char* panel_rows8, int chunk, const uint32_t (&w)[8],
-                                        const uint4& s, const uint4& zp) {
+__device__ __forceinline__ void deq_row(uint32_t rows8, int chunk, const uint32_t (&w)[8], const uint4& s, const uint4& zp) {
   const uint32_t sv[4] = {s.x, s.y, s.z, s.w}, zv[4] = {zp.x, zp.y, zp.z, zp.w};
-  uint4 o;
-  uint32_t* ov = reinterpret_cast<uint32_t*>(&o);
+  uint32_t ov[4];
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
     const __half2 q = nibble_pair<BYTE, ODD>(w[2 * c], w[2 * c + 1]);
     ov[c] = as_u32(__hsub2_rn(__hmul2_rn(as_h2(sv[c]), q), as_h2(zv[c])));
   }
-  *reinterpret_cast<uint4*>(panel_rows8 + J * 128 + ((chunk ^ J) << 4)) = o;
+  sts_v4(rows8 + J * 128 + ((chunk ^ J) << 4), ov[0], ov[1], ov[2], ov[3]);
+}
+
+// All 8 rows with one scale / zero-term set (the rows share a quantisation group).
+__device__ __forceinline__ void deq_task_uniform(uint32_t rows8, int chunk, const uint32_t (&w)[8], const uint4& s, const uint4& zp) {
+  deq_row<0, 0, false>(rows8, chunk, w, s, zp); deq_row<1, 0, true>(rows8, chunk, w, s, zp);
+  deq_row<2, 1, false>(rows8, chunk, w, s, zp); deq_row<3, 1, true>(rows8, chunk, w, s, zp);
+  deq_row<4, 2, false>(rows8, chunk, w, s, zp); deq_row<5, 2, true>(rows8, chunk, w, s, zp);
+  deq_row<6, 3, false>(rows8, chunk, w, s, zp); deq_row<7, 3, true>(rows8, chunk, w, s, zp);
+}
+
+__device__ __forceinline__ bool all_equal8(const int4& a, const int4& b) {
+  return (((a.x ^ a.y) | (a.x ^ a.z) | (a.x ^ a.w) | (a.x ^ b.x) | (a.x ^ b.y) | (a.x ^ b.z) | (a.x ^ b.w)) == 0);
 }
 
 // rn(s * (z+1)) for 8 adjacent columns from their scales and the packed zero-point word.
@@ -92,5 +140,49 @@ __device__ __forceinline__ uint4 zero_terms(const uint4& s, uint32_t zw) {
   return o;
 }
 
+
+// One dequant task (8 k-rows x 8 columns) with scales and zero terms from shared-memory tables laid
+// out [group][ 128 scales | 128 rn(s*(z+1)) ] (512 bytes per group); `tab` already points at the
+// task's 8 columns.  Rows of one group (always, without act-order) take the short path.
+__device__ __forceinline__ void deq_task_tables(uint32_t rows8, int chunk, const uint32_t (&w)[8], const int4& ga, const int4& gb, uint32_t tab) {
+  if (all_equal8(ga, gb)) {
+    const uint32_t t = tab + ga.x * 512;
+    deq_task_uniform(rows8, chunk, w, lds_v4(t), lds_v4(t + 256));
+  } else {
+    uint32_t t;
+    t = tab + ga.x * 512; deq_row<0, 0, false>(rows8, chunk, w, lds_v4(t), lds_v4(t + 256));
+    t = tab + ga.y * 512; deq_row<1, 0, true>(rows8, chunk, w, lds_v4(t), lds_v4(t + 256));
+    t = tab + ga.z * 512; deq_row<2, 1, false>(rows8, chunk, w, lds_v4(t), lds_v4(t + 256));
+    t = tab + ga.w * 512; deq_row<3, 1, true>(rows8, chunk, w, lds_v4(t), lds_v4(t + 256));
+    t = tab + gb.x * 512; deq_row<4, 2, false>(rows8, chunk, w, lds_v4(t), lds_v4(t + 256));
+    t = tab + gb.y * 512; deq_row<5, 2, true>(rows8, chunk, w, lds_v4(t), lds_v4(t + 256));
+    t = tab + gb.z * 512; deq_row<6, 3, false>(rows8, chunk, w, lds_v4(t), lds_v4(t + 256));
+    t = tab + gb.w * 512; deq_row<7, 3, true>(rows8, chunk, w, lds_v4(t), lds_v4(t + 256));
+  }
+}
+
+// The same with scales and packed zero points read from global memory: `sc` / `qz` point at the
+// task's 8 columns in group 0, `N` is the row length of the scales.
+__device__ __forceinline__ void deq_task_global(uint32_t rows8, int chunk, const uint32_t (&w)[8], const int4& ga, const int4& gb,
+                                                const __half* sc, const uint32_t* qz, int N) {
+  const int N8 = N >> 3;
+  if (all_equal8(ga, gb)) {
+    const uint4 s = __ldg(reinterpret_cast<const uint4*>(sc + (size_t)ga.x * N));
+    deq_task_uniform(rows8, chunk, w, s, zero_terms(s, __ldg(qz + (size_t)ga.x * N8)));
+  } else {
+    const int gi[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
+    uint4 s[8];
+    uint32_t z[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      s[j] = __ldg(reinterpret_cast<const uint4*>(sc + (size_t)gi[j] * N));
+      z[j] = __ldg(qz + (size_t)gi[j] * N8);
+    }
+    deq_row<0, 0, false>(rows8, chunk, w, s[0], zero_terms(s[0], z[0])); deq_row<1, 0, true>(rows8, chunk, w, s[1], zero_terms(s[1], z[1]));
+    deq_row<2, 1, false>(rows8, chunk, w, s[2], zero_terms(s[2], z[2])); deq_row<3, 1, true>(rows8, chunk, w, s[3], zero_terms(s[3], z[3]));
+    deq_row<4, 2, false>(rows8, chunk, w, s[4], zero_terms(s[4], z[4])); deq_row<5, 2, true>(rows8, chunk, w, s[5], zero_terms(s[5], z[5]));
+    deq_row<6, 3, false>(rows8, chunk, w, s[6], zero_terms(s[6], z[6])); deq_row<7, 3, true>(rows8, chunk, w, s[7], zero_terms(s[7], z[7]));
+  }
+}
 
 }  // namespace q4

@@ -155,6 +155,12 @@ def gemm_supported(K: int, N: int, G: int, transpose: bool) -> bool:
     return transpose or (1024 + 2 * 49152 + 256 + 2 * G * 128 * 2) <= 227 * 1024
 
 
+def gemm_set_variant(variant: int) -> None:
+    """Which fused GEMM kernel ``gemm`` launches: 0 = chosen per shape (default), 1 = single-CTA kernel,
+    2 = CTA-pair kernel (needs the number of output columns to be a multiple of 256)."""
+    _lib.check(_lib.lib().q4_gemm_set_variant(int(variant)), "gemm_set_variant")
+
+
 def device_status() -> int:
     """Status word of the fused kernels (synchronises): 0 unless a bounded device-side wait expired."""
     import ctypes

@@ -150,6 +150,61 @@ def test_gemm_fused_lora_term(r, transpose):
     assert rel_fro(out, want) <= REL_TOL
 
 
+@pytest.fixture
+def gemm_variant():
+    yield quant_cuda.gemm_set_variant
+    quant_cuda.gemm_set_variant(0)
+
+
+@pytest.mark.parametrize("transpose", [False, True])
+@pytest.mark.parametrize("M,K,N,g,act", [(700, 1024, 768, 128, True), (256, 256, 256, 64, False), (5, 512, 1280, 128, True)])
+def test_both_gemm_kernels_against_oracle(gemm_variant, M, K, N, g, act, transpose):
+    """The single-CTA kernel and the CTA-pair kernel on the same inputs (shapes both can serve)."""
+    layer = synth.make_layer(K, N, g, act, seed=M + N)
+    x = synth.make_acts(M, N if transpose else K, seed=M + 1)
+    want = orc.matmul4bit_ref(x, layer.qweight, layer.scales, layer.qzeros, layer.g_idx, transpose=transpose)
+    outs = []
+    for variant in (1, 2):
+        gemm_variant(variant)
+        outs.append(run_gemm(layer, x, transpose).clone())
+        assert rel_fro(outs[-1], want) <= REL_TOL
+    assert rel_fro(outs[0], outs[1]) <= 5e-4               # same products, different accumulation grouping at most
+
+
+@pytest.mark.parametrize("transpose", [False, True])
+def test_pair_kernel_many_tiles_per_pair(gemm_variant, transpose):
+    """More than five 256 x 256 tiles per CTA pair: both accumulators and every pipeline stage are
+    reused several times (the barrier phases wrap), with the low-rank stage making the stage count odd."""
+    K, N, M, r = (256, 12288, 2048, 16) if not transpose else (12288, 256, 2048, 16)
+    layer = synth.make_layer(K, N, 128, True, seed=11)
+    A, B = synth.make_lora(K, N, r, seed=12)
+    x = synth.make_acts(M, N if transpose else K, seed=13)
+    w = orc.recons_v2(layer.qweight, layer.scales, layer.qzeros, layer.g_idx).float()
+    if transpose:
+        u = ((x.float() @ B.float()) * 2.0).half()
+        want, lw = x.float() @ w.t() + u.float() @ A.float(), A
+    else:
+        u = ((x.float() @ A.float().t()) * 2.0).half()
+        want, lw = x.float() @ w + u.float() @ B.float().t(), B
+    L = layer.to(DEV)
+    gemm_variant(2)
+    out = torch.empty((M, K if transpose else N), dtype=torch.float16, device=DEV)
+    quant_cuda.gemm(x.to(DEV), L.qweight, out, L.scales, L.qzeros, L.g_idx, transpose=transpose,
+                    lora_u=torch.nn.functional.pad(u, (0, 64 - r)).to(DEV), lora_w=lw.contiguous().to(DEV))
+    torch.cuda.synchronize()
+    assert quant_cuda.device_status() == 0
+    assert rel_fro(out, want) <= REL_TOL
+
+
+def test_pair_kernel_rejects_shapes_it_cannot_serve(gemm_variant):
+    layer = synth.make_layer(256, 384, 128, False, seed=3).to(DEV)
+    x = synth.make_acts(16, 256, seed=4).to(DEV)
+    out = torch.empty((16, 384), dtype=torch.float16, device=DEV)
+    gemm_variant(2)
+    with pytest.raises(RuntimeError):
+        quant_cuda.gemm(x, layer.qweight, out, layer.scales, layer.qzeros, layer.g_idx)
+
+
 @pytest.mark.parametrize("fused", [True, False])
 def test_linear4bitlt_lora_training_step(fused):
     models.fused_lora = fused
