@@ -44,6 +44,30 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
   return ok != 0;
 }
 
+// Non-blocking test of the phase.  (mbarrier.try_wait is compiled into a polling loop of its own -
+// try, short sleep, retry until an internal time limit - whose instructions compete for issue
+// slots with working warps on the same scheduler; test_wait is a single instruction, so the
+// caller decides how often a waiting thread polls.)
+__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// The same on a barrier that CTAs of the whole cluster arrive on (acquire at cluster scope).
+__device__ __forceinline__ bool mbar_test_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+
 // Bounded wait.  Returns false if the phase did not complete within `limit` polls; the caller
 // then records Q4_STATUS_WAIT_EXPIRED and carries on without waiting (results are garbage but
 // every thread still reaches the end of the kernel, so nothing can hang).
@@ -107,6 +131,16 @@ __device__ __forceinline__ void cluster_sync_all() {
 // would add a device-wide memory barrier to every arrive.
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// one try on an own mbarrier that CTAs of the whole cluster arrive on (acquire at cluster scope)
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
 }
 // sleeping try on an own mbarrier that CTAs of the whole cluster arrive on (acquire at cluster scope)
 __device__ __forceinline__ bool mbar_try_wait_sleep_cluster(uint64_t* bar, uint32_t parity, uint32_t ns) {

@@ -80,7 +80,7 @@ __global__ void __launch_bounds__(GM_THREADS, 1)
 q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap umap, const GemmParams p) {
   extern __shared__ unsigned char smem_raw[];
   // 1024-byte alignment for the swizzled tiles
-  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);      // 1024-byte aligned, still a shared-space pointer
   unsigned char* stages = smem;
   const int S = p.stages;
   uint64_t* full_a = reinterpret_cast<uint64_t*>(smem + S * GM_STAGE_BYTES);
@@ -90,7 +90,7 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   // forward: [G][128 scales | 128 rn(s*(z+1))], 512 bytes per group
-  const uint32_t tab = smem_u32(smem + S * GM_STAGE_BYTES + 256);
+  unsigned char* tab = smem + S * GM_STAGE_BYTES + 256;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int out0 = blockIdx.x * GM_TILE_N;            // first output column (n forward, k backward)
@@ -162,6 +162,8 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__
     const int chunk16 = TRANSPOSE ? (tid & 7) : (tid & 15);        // 16-byte chunk (8 columns) within the stage's n-range
     const int r = TRANSPOSE ? (tid >> 3) : (tid >> 4);             // packed row within the stage
     const int N = p.N;
+    uint32_t off[8];
+    deq_offsets(chunk16 & 7, off);
     if (!TRANSPOSE) {
       // tables for the CTA's 128 columns: scale and rn(s*(z+1)) of every group
       for (int i = threadIdx.x - 64; i < p.G * (GM_TILE_N / 8); i += GM_DEQ_THREADS * GM_DEQ_GROUPS) {
@@ -169,8 +171,8 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__
         const uint4 s = __ldg(reinterpret_cast<const uint4*>(p.scales + (size_t)g * N + out0 + 8 * c8));
         const uint32_t zw = __ldg(p.qzeros + (size_t)g * (N >> 3) + ((out0 + 8 * c8) >> 3));
         const uint4 z = zero_terms(s, zw);
-        sts_v4(tab + g * 512 + 16 * c8, s.x, s.y, s.z, s.w);
-        sts_v4(tab + g * 512 + 256 + 16 * c8, z.x, z.y, z.z, z.w);
+        *reinterpret_cast<uint4*>(tab + g * 512 + 16 * c8) = s;
+        *reinterpret_cast<uint4*>(tab + g * 512 + 256 + 16 * c8) = z;
       }
       named_bar_sync(1, GM_DEQ_THREADS * GM_DEQ_GROUPS);
     }
@@ -240,13 +242,13 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__
       if (threadIdx.x == 64 && it < 40) gm_mark(p.trace, 65 + 3 * (it / 2));
       unsigned char* bst = stages + (size_t)st * GM_STAGE_BYTES + GM_A_BYTES;
       // forward: panel (chunk16 / 8) of [64 rows][128 B]; backward: one panel of [128 rows][128 B]
-      const uint32_t rows8 = smem_u32(bst) + (TRANSPOSE ? r * 1024 : (chunk16 >> 3) * 8192 + r * 1024);
+      unsigned char* rows8 = bst + (TRANSPOSE ? r * 1024 : (chunk16 >> 3) * 8192 + r * 1024);
       const int4 ga_now = make_int4(gi[0], gi[1], gi[2], gi[3]), gb_now = make_int4(gi[4], gi[5], gi[6], gi[7]);
       if (TRANSPOSE) {
         const int ncol = it * GM_TILE_C + 8 * chunk16;             // global column of the task
-        deq_task_global(rows8, chunk16 & 7, w, ga_now, gb_now, p.scales + ncol, p.qzeros + (ncol >> 3), N);
+        deq_task_global(rows8, off, w, ga_now, gb_now, p.scales + ncol, p.qzeros + (ncol >> 3), N);
       } else {
-        deq_task_tables(rows8, chunk16 & 7, w, ga_now, gb_now, tab + 16 * chunk16);
+        deq_task_tables(rows8, off, w, ga_now, gb_now, tab + 16 * chunk16);
       }
       fence_async_smem();                          // generic-proxy stores -> visible to the tensor core
       __syncwarp();

@@ -32,24 +32,29 @@ constexpr int G2_THREADS = 512;
 constexpr int G2_TMEM_COLS = 512;             // two accumulators of 256 fp32 columns
 constexpr int G2_BAR_BYTES = 512;
 
-__device__ __forceinline__ bool wait_bar_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-  const uint32_t lim = *abort_flag ? 4u : GM_WAIT_TRIES;
-  for (uint32_t i = 0; i < lim; ++i)
-    if (mbar_try_wait_sleep_cluster(bar, parity, 2000u)) return true;
+// Wait of the MMA thread, the pacemaker of the pipeline: single-instruction tests back to back.
+__device__ __forceinline__ bool wait_bar_cluster(uint64_t* bar, uint32_t parity, volatile int* abort_flag, unsigned* polls = nullptr) {
+  if (mbar_test_wait_cluster(bar, parity)) return true;
+  const uint32_t lim = *abort_flag ? 4u : 40000000u;
+  for (uint32_t i = 0; i < lim; ++i) {
+    if (polls) ++*polls;
+    if (mbar_test_wait_cluster(bar, parity)) return true;
+  }
   *abort_flag = 1;
   atomicExch(&g_gemm_status, Q4_STATUS_WAIT_EXPIRED);
   return false;
 }
 
-// Wait of a warp that has nothing else to do for a long time (the epilogue between tiles, the TMA
-// producer ahead of the MMAs): sleeps between tries so that its polling does not take issue slots
-// from the dequant warps on the same scheduler.
-__device__ __forceinline__ bool wait_bar_idle(uint64_t* bar, uint32_t parity, volatile int* abort_flag, uint32_t sleep_ns) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const uint32_t lim = *abort_flag ? 4u : 200000u;
+// Wait of a warp that has nothing else to do for a while (the epilogue between tiles, the TMA
+// producer ahead of the MMAs, a dequant warp ahead of the MMAs): sleeps between tests so that its
+// polling takes no issue slots from the working warps on the same scheduler.
+__device__ __forceinline__ bool wait_bar_idle(uint64_t* bar, uint32_t parity, volatile int* abort_flag, uint32_t sleep_ns, unsigned* polls = nullptr) {
+  if (mbar_test_wait(bar, parity)) return true;
+  const uint32_t lim = *abort_flag ? 4u : 100000000u / sleep_ns;     // about 0.1 s
   for (uint32_t i = 0; i < lim; ++i) {
+    if (polls) ++*polls;
     __nanosleep(sleep_ns);
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_test_wait(bar, parity)) return true;
   }
   *abort_flag = 1;
   atomicExch(&g_gemm_status, Q4_STATUS_WAIT_EXPIRED);
@@ -60,7 +65,7 @@ template <bool TRANSPOSE>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
 q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap umap, const GemmParams p) {
   extern __shared__ unsigned char smem_raw[];
-  unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);      // 1024-byte aligned, still a shared-space pointer
   unsigned char* stages = smem;
   const int S = p.stages;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + S * G2_STAGE_BYTES);     // even CTA: activation bytes + 4 dequant warps, of both CTAs
@@ -70,7 +75,7 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   // forward: [G][128 scales | 128 rn(s*(z+1))], 512 bytes per group
-  const uint32_t tab = smem_u32(smem + S * G2_STAGE_BYTES + G2_BAR_BYTES);
+  unsigned char* tab = smem + S * G2_STAGE_BYTES + G2_BAR_BYTES;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();
@@ -105,11 +110,12 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
     // ---------------- TMA producer: this CTA's 128 activation rows of every stage ----------------
     if (lane == 0) {
       int st = 0, use = 0;                             // stage and how often it has been used, over all tiles
+      unsigned polls = 0;
       const uint32_t full0 = mapa_u32(smem_u32(full), 0);
       for (int tile = pair; tile < n_tiles; tile += n_pairs) {
         const int m0 = (tile % m_tiles) * G2_TILE_M + 128 * (int)rank;
         for (int it = 0; it < TT; ++it) {
-          if (use > 0) wait_bar_idle(&empty[st], (use - 1) & 1, abort_flag, 200);
+          if (use > 0) wait_bar_idle(&empty[st], (use - 1) & 1, abort_flag, 200, &polls);
           if (rank == 0) mbar_arrive_expect_tx(&full[st], 2 * G2_A_BYTES);
           unsigned char* dst = stages + (size_t)st * G2_STAGE_BYTES;
           if (it < T) tma_load_2d_pair(dst, &amap, it * GM_TILE_C, m0, full0 + 8 * st);
@@ -117,6 +123,7 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
           if (++st == S) { st = 0; ++use; }
         }
       }
+      if (p.trace) p.trace[(size_t)blockIdx.x * 256 + 240] = polls;
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer (even CTA only) ----------------
@@ -131,6 +138,7 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
                                      : smem_desc_sw128(smem_u32(stages) + G2_A_BYTES, 8192, 1024);
       constexpr uint64_t A_STEP = 32 >> 4, B_STEP = (TRANSPOSE ? 32 : 2048) >> 4, ST_STEP = G2_STAGE_BYTES >> 4;
       int st = 0, use = 0, tl = 0;
+      unsigned polls = 0;
       uint64_t ad = ad0, bd = bd0;
       for (int tile = pair; tile < n_tiles; tile += n_pairs, ++tl) {
         const int acc = tl & 1, acc_use = tl >> 1;
@@ -140,7 +148,7 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         const bool tron = p.trace != nullptr && tl == 1;
         for (int it = 0; it < TT; ++it) {
           if (tron && it < 12) gm_mark(p.trace, 5 * it);
-          wait_bar_cluster(&full[st], use & 1, abort_flag);
+          wait_bar_cluster(&full[st], use & 1, abort_flag, &polls);
           if (tron && it < 12) gm_mark(p.trace, 5 * it + 2);
           tc_fence_after();
           if (it < T) {
@@ -159,6 +167,7 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         }
         umma_commit_pair(&acc_full[acc]);
       }
+      if (p.trace) p.trace[(size_t)blockIdx.x * 256 + 241] = polls;
     }
   } else if (dw >= 0) {
     // ---------------- dequantisers: this CTA's 128 output columns of every stage ----------------
@@ -167,9 +176,12 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
     const int chunk16 = TRANSPOSE ? (tid & 7) : (tid & 15);        // 16-byte chunk (8 columns) within the stage's n-range
     const int r = TRANSPOSE ? (tid >> 3) : (tid >> 4);             // packed row within the stage
     const int N = p.N;
+    uint32_t off[8];
+    deq_offsets(chunk16 & 7, off);
     const uint32_t full0 = mapa_u32(smem_u32(full), 0);            // the even CTA's full[0]
     int tl = 0, tab_out0 = -1;
     int st = grp, use = 0;                                         // of this group's next stage use (g = grp, grp + 2, ...)
+    unsigned polls = 0;
     for (int tile = pair; tile < n_tiles; tile += n_pairs, ++tl) {
       const int out0 = (tile / m_tiles) * G2_TILE_N + 128 * (int)rank;   // first output column (n forward, k backward)
       const int gbase = tl * TT;
@@ -181,8 +193,8 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
           const uint4 s = __ldg(reinterpret_cast<const uint4*>(p.scales + (size_t)g * N + out0 + 8 * c8));
           const uint32_t zw = __ldg(p.qzeros + (size_t)g * (N >> 3) + ((out0 + 8 * c8) >> 3));
           const uint4 z = zero_terms(s, zw);
-          sts_v4(tab + g * 512 + 16 * c8, s.x, s.y, s.z, s.w);
-          sts_v4(tab + g * 512 + 256 + 16 * c8, z.x, z.y, z.z, z.w);
+          *reinterpret_cast<uint4*>(tab + g * 512 + 16 * c8) = s;
+          *reinterpret_cast<uint4*>(tab + g * 512 + 256 + 16 * c8) = z;
         }
         named_bar_sync(1, GM_DEQ_THREADS * GM_DEQ_GROUPS);
         tab_out0 = out0;
@@ -194,20 +206,29 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         return p.qw + (size_t)prow * N + ncol;
       };
       const int it0 = (grp ^ gbase) & 1;
-      uint4 wa = make_uint4(0, 0, 0, 0), wb = wa;
-      int4 ga = make_int4(0, 0, 0, 0), gb = ga;                      // groups of the task's 8 k-rows
-      if (it0 < T) {
-        wa = ldg_stream(word_ptr(it0)); wb = ldg_stream(word_ptr(it0) + 4);
-        const int k8 = TRANSPOSE ? out0 + 8 * r : it0 * GM_TILE_C + 8 * r;
-        ga = __ldg(reinterpret_cast<const int4*>(p.g_idx + k8));
-        gb = __ldg(reinterpret_cast<const int4*>(p.g_idx + k8 + 4));
+      // Packed words (and, forward, the groups of their 8 k-rows) of one task.  Two sets: the loads of
+      // the group's next task are in flight into one while the other is being dequantised.
+      struct TaskRegs { uint4 wa, wb; int4 ga, gb; };
+      TaskRegs R0, R1;
+      int4 tga = make_int4(0, 0, 0, 0), tgb = tga;                   // backward: the task's k-rows are the same in every stage
+      if (TRANSPOSE) {
+        tga = __ldg(reinterpret_cast<const int4*>(p.g_idx + out0 + 8 * r));
+        tgb = __ldg(reinterpret_cast<const int4*>(p.g_idx + out0 + 8 * r + 4));
       }
-      for (int it = it0; it < TT; it += GM_DEQ_GROUPS, st += GM_DEQ_GROUPS) {
+      auto prefetch = [&](int it, TaskRegs& R) {
+        if (it >= T) return;
+        R.wa = ldg_stream(word_ptr(it)); R.wb = ldg_stream(word_ptr(it) + 4);
+        if (!TRANSPOSE) {
+          R.ga = __ldg(reinterpret_cast<const int4*>(p.g_idx + it * GM_TILE_C + 8 * r));
+          R.gb = __ldg(reinterpret_cast<const int4*>(p.g_idx + it * GM_TILE_C + 8 * r + 4));
+        }
+      };
+      auto task = [&](int it, const TaskRegs& C) {
         if (st >= S) { st -= S; ++use; }
         unsigned char* bst = stages + (size_t)st * G2_STAGE_BYTES + G2_A_BYTES;
         if (it == T) {
           // ---- low-rank stage: B operand from lora_w instead of dequantised weights ----
-          if (use > 0 && lane == 0) wait_bar(&empty[st], (use - 1) & 1, abort_flag);
+          if (use > 0 && lane == 0) wait_bar_idle(&empty[st], (use - 1) & 1, abort_flag, 100, &polls);
           __syncwarp();
           const int rr = p.lora_r, rows = 16 * lora_ks;
           if (!TRANSPOSE) {
@@ -236,49 +257,52 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
           fence_async_smem();
           __syncwarp();
           if (lane == 0) mbar_arrive_cluster(full0 + 8 * st);
-          continue;
+          st += GM_DEQ_GROUPS;
+          return;
         }
-        const uint32_t w[8] = {wa.x, wa.y, wa.z, wa.w, wb.x, wb.y, wb.z, wb.w};
-        const int gi[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
-        if (it + GM_DEQ_GROUPS < T) {                                // prefetch this group's next stage
-          wa = ldg_stream(word_ptr(it + GM_DEQ_GROUPS)); wb = ldg_stream(word_ptr(it + GM_DEQ_GROUPS) + 4);
-          if (!TRANSPOSE) {
-            const int k8 = (it + GM_DEQ_GROUPS) * GM_TILE_C + 8 * r;
-            ga = __ldg(reinterpret_cast<const int4*>(p.g_idx + k8));
-            gb = __ldg(reinterpret_cast<const int4*>(p.g_idx + k8 + 4));
-          }
-        }
+        const uint32_t w[8] = {C.wa.x, C.wa.y, C.wa.z, C.wa.w, C.wb.x, C.wb.y, C.wb.z, C.wb.w};
         const bool tr_on = p.trace && tl == 1 && dw == 0 && lane == 0 && it < 40;
         if (tr_on) gm_mark(p.trace, 64 + 3 * (it >> 1));
-        if (use > 0 && lane == 0) wait_bar(&empty[st], (use - 1) & 1, abort_flag);
+        if (use > 0 && lane == 0) wait_bar_idle(&empty[st], (use - 1) & 1, abort_flag, 100, &polls);
         __syncwarp();
         if (tr_on) gm_mark(p.trace, 65 + 3 * (it >> 1));
         // forward: panel (chunk16 / 8) of [64 rows][128 B]; backward: one panel of [128 rows][128 B]
-        const uint32_t rows8 = smem_u32(bst) + (TRANSPOSE ? r * 1024 : (chunk16 >> 3) * 8192 + r * 1024);
-        const int4 ga_now = make_int4(gi[0], gi[1], gi[2], gi[3]), gb_now = make_int4(gi[4], gi[5], gi[6], gi[7]);
+        unsigned char* rows8 = bst + (TRANSPOSE ? r * 1024 : (chunk16 >> 3) * 8192 + r * 1024);
         if (TRANSPOSE) {
           const int ncol = it * GM_TILE_C + 8 * chunk16;             // global column of the task
-          deq_task_global(rows8, chunk16 & 7, w, ga_now, gb_now, p.scales + ncol, p.qzeros + (ncol >> 3), N);
+          deq_task_global(rows8, off, w, tga, tgb, p.scales + ncol, p.qzeros + (ncol >> 3), N);
         } else {
-          deq_task_tables(rows8, chunk16 & 7, w, ga_now, gb_now, tab + 16 * chunk16);
+          deq_task_tables(rows8, off, w, C.ga, C.gb, tab + 16 * chunk16);
         }
         fence_async_smem();                          // generic-proxy stores -> visible to the tensor core
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(full0 + 8 * st);
         if (tr_on) gm_mark(p.trace, 66 + 3 * (it >> 1));
+        st += GM_DEQ_GROUPS;
+      };
+      prefetch(it0, R0);
+      for (int it = it0; it < TT; it += 2 * GM_DEQ_GROUPS) {
+        prefetch(it + GM_DEQ_GROUPS, R1);
+        task(it, R0);
+        if (it + GM_DEQ_GROUPS < TT) {
+          prefetch(it + 2 * GM_DEQ_GROUPS, R0);
+          task(it + GM_DEQ_GROUPS, R1);
+        }
       }
     }
+    if (p.trace && lane == 0) p.trace[(size_t)blockIdx.x * 256 + 246 + dw] = polls;
   } else if (warp >= 12) {
     // ---------------- epilogue: TMEM -> registers -> (+bias) -> fp16 -> global ----------------
     const int quarter = warp & 3;                                  // TMEM lanes 32*quarter .. +31
     const uint32_t acc_empty0 = mapa_u32(smem_u32(acc_empty), 0);  // the even CTA's acc_empty[0]
     int tl = 0;
+    unsigned polls = 0;
     for (int tile = pair; tile < n_tiles; tile += n_pairs, ++tl) {
       const int acc = tl & 1, acc_use = tl >> 1;
       const int col0 = (tile / m_tiles) * G2_TILE_N;
       const int m = (tile % m_tiles) * G2_TILE_M + 128 * (int)rank + 32 * quarter + lane;
       if (threadIdx.x == 384 && tl < 8) gm_mark(p.trace, 200 + 3 * tl);
-      if (lane == 0) wait_bar_idle(&acc_full[acc], acc_use & 1, abort_flag, 1000);
+      if (lane == 0) wait_bar_idle(&acc_full[acc], acc_use & 1, abort_flag, 1000, &polls);
       __syncwarp();
       tc_fence_after();
       if (threadIdx.x == 384 && tl < 8) gm_mark(p.trace, 201 + 3 * tl);
@@ -312,6 +336,7 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
       if (lane == 0) mbar_arrive_cluster(acc_empty0 + 8 * acc);
       if (threadIdx.x == 384 && tl < 8) gm_mark(p.trace, 202 + 3 * tl);
     }
+    if (p.trace && lane == 0) p.trace[(size_t)blockIdx.x * 256 + 242 + (warp & 3)] = polls;
   }
   // neither CTA may leave (or free TMEM) while its peer can still signal its barriers or read its tiles
   tc_fence_before();

@@ -87,38 +87,40 @@ __host__ __device__ constexpr uint32_t idesc_f16(int m, int n, bool b_mn_major) 
          ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
 
-// ---- shared memory through 32-bit shared-space addresses (no generic-pointer arithmetic) --------
-__device__ __forceinline__ void sts_v4(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
-  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
-}
-__device__ __forceinline__ uint4 lds_v4(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-  return v;
+// ---- dequantisation into the swizzled operand panels ---------------------------------------------
+// Pointers into shared memory stay derived from the kernel's `extern __shared__` array by plain
+// pointer arithmetic, so that the compiler keeps them in the shared address space (32-bit
+// addresses, STS.128 straight from the result registers).
+
+// Byte offsets of a task's 8 rows inside its 8-row group of a [rows][128 B] panel with the 128B
+// swizzle: row J at J * 128, its 16-byte chunk `chunk` at position chunk ^ J.  Constant per thread.
+__device__ __forceinline__ void deq_offsets(int chunk, uint32_t (&off)[8]) {
+#pragma unroll
+  for (int j = 0; j < 8; ++j) off[j] = j * 128 + ((chunk ^ j) << 4);
 }
 
 // Dequantise row J (nibble J of each word) of 8 packed words (8 k-rows x 8 adjacent columns) and
-// write its 16-byte chunk into a [rows][128 B] panel with the 128B swizzle.  `rows8` is the
-// shared-space address of the task's first row, `chunk` the 16-byte column chunk, `s`/`zp` scale and
+// write its 16-byte chunk.  `rows8` points at the task's first row, `s`/`zp` are scale and
 // rn(s*(z+1)) of the 8 columns (four half2 each).
 template <int J, int BYTE, bool ODD>
-__device__ __forceinline__ void deq_row(uint32_t rows8, int chunk, const uint32_t (&w)[8], const uint4& s, const uint4& zp) {
+__device__ __forceinline__ void deq_row(unsigned char* rows8, const uint32_t (&off)[8], const uint32_t (&w)[8], const uint4& s, const uint4& zp) {
   const uint32_t sv[4] = {s.x, s.y, s.z, s.w}, zv[4] = {zp.x, zp.y, zp.z, zp.w};
-  uint32_t ov[4];
+  uint4 o;
+  uint32_t* ov = reinterpret_cast<uint32_t*>(&o);
 #pragma unroll
   for (int c = 0; c < 4; ++c) {
     const __half2 q = nibble_pair<BYTE, ODD>(w[2 * c], w[2 * c + 1]);
     ov[c] = as_u32(__hsub2_rn(__hmul2_rn(as_h2(sv[c]), q), as_h2(zv[c])));
   }
-  sts_v4(rows8 + J * 128 + ((chunk ^ J) << 4), ov[0], ov[1], ov[2], ov[3]);
+  *reinterpret_cast<uint4*>(rows8 + off[J]) = o;
 }
 
 // All 8 rows with one scale / zero-term set (the rows share a quantisation group).
-__device__ __forceinline__ void deq_task_uniform(uint32_t rows8, int chunk, const uint32_t (&w)[8], const uint4& s, const uint4& zp) {
-  deq_row<0, 0, false>(rows8, chunk, w, s, zp); deq_row<1, 0, true>(rows8, chunk, w, s, zp);
-  deq_row<2, 1, false>(rows8, chunk, w, s, zp); deq_row<3, 1, true>(rows8, chunk, w, s, zp);
-  deq_row<4, 2, false>(rows8, chunk, w, s, zp); deq_row<5, 2, true>(rows8, chunk, w, s, zp);
-  deq_row<6, 3, false>(rows8, chunk, w, s, zp); deq_row<7, 3, true>(rows8, chunk, w, s, zp);
+__device__ __forceinline__ void deq_task_uniform(unsigned char* rows8, const uint32_t (&off)[8], const uint32_t (&w)[8], const uint4& s, const uint4& zp) {
+  deq_row<0, 0, false>(rows8, off, w, s, zp); deq_row<1, 0, true>(rows8, off, w, s, zp);
+  deq_row<2, 1, false>(rows8, off, w, s, zp); deq_row<3, 1, true>(rows8, off, w, s, zp);
+  deq_row<4, 2, false>(rows8, off, w, s, zp); deq_row<5, 2, true>(rows8, off, w, s, zp);
+  deq_row<6, 3, false>(rows8, off, w, s, zp); deq_row<7, 3, true>(rows8, off, w, s, zp);
 }
 
 __device__ __forceinline__ bool all_equal8(const int4& a, const int4& b) {
@@ -144,31 +146,39 @@ __device__ __forceinline__ uint4 zero_terms(const uint4& s, uint32_t zw) {
 // One dequant task (8 k-rows x 8 columns) with scales and zero terms from shared-memory tables laid
 // out [group][ 128 scales | 128 rn(s*(z+1)) ] (512 bytes per group); `tab` already points at the
 // task's 8 columns.  Rows of one group (always, without act-order) take the short path.
-__device__ __forceinline__ void deq_task_tables(uint32_t rows8, int chunk, const uint32_t (&w)[8], const int4& ga, const int4& gb, uint32_t tab) {
+__device__ __forceinline__ void deq_task_tables(unsigned char* rows8, const uint32_t (&off)[8], const uint32_t (&w)[8], const int4& ga, const int4& gb,
+                                                const unsigned char* tab) {
+#define Q4_TAB(g, o) (*reinterpret_cast<const uint4*>(tab + (g) * 512 + (o)))
+  // table entries are copied into registers before any row is stored: a reference into shared
+  // memory would have to be re-read after every store (the compiler cannot rule out an overlap)
   if (all_equal8(ga, gb)) {
-    const uint32_t t = tab + ga.x * 512;
-    deq_task_uniform(rows8, chunk, w, lds_v4(t), lds_v4(t + 256));
+    const uint4 s = Q4_TAB(ga.x, 0), z = Q4_TAB(ga.x, 256);
+    deq_task_uniform(rows8, off, w, s, z);
   } else {
-    uint32_t t;
-    t = tab + ga.x * 512; deq_row<0, 0, false>(rows8, chunk, w, lds_v4(t), lds_v4(t + 256));
-    t = tab + ga.y * 512; deq_row<1, 0, true>(rows8, chunk, w, lds_v4(t), lds_v4(t + 256));
-    t = tab + ga.z * 512; deq_row<2, 1, false>(rows8, chunk, w, lds_v4(t), lds_v4(t + 256));
-    t = tab + ga.w * 512; deq_row<3, 1, true>(rows8, chunk, w, lds_v4(t), lds_v4(t + 256));
-    t = tab + gb.x * 512; deq_row<4, 2, false>(rows8, chunk, w, lds_v4(t), lds_v4(t + 256));
-    t = tab + gb.y * 512; deq_row<5, 2, true>(rows8, chunk, w, lds_v4(t), lds_v4(t + 256));
-    t = tab + gb.z * 512; deq_row<6, 3, false>(rows8, chunk, w, lds_v4(t), lds_v4(t + 256));
-    t = tab + gb.w * 512; deq_row<7, 3, true>(rows8, chunk, w, lds_v4(t), lds_v4(t + 256));
+    {
+      const uint4 s0 = Q4_TAB(ga.x, 0), z0 = Q4_TAB(ga.x, 256), s1 = Q4_TAB(ga.y, 0), z1 = Q4_TAB(ga.y, 256);
+      const uint4 s2 = Q4_TAB(ga.z, 0), z2 = Q4_TAB(ga.z, 256), s3 = Q4_TAB(ga.w, 0), z3 = Q4_TAB(ga.w, 256);
+      deq_row<0, 0, false>(rows8, off, w, s0, z0); deq_row<1, 0, true>(rows8, off, w, s1, z1);
+      deq_row<2, 1, false>(rows8, off, w, s2, z2); deq_row<3, 1, true>(rows8, off, w, s3, z3);
+    }
+    {
+      const uint4 s0 = Q4_TAB(gb.x, 0), z0 = Q4_TAB(gb.x, 256), s1 = Q4_TAB(gb.y, 0), z1 = Q4_TAB(gb.y, 256);
+      const uint4 s2 = Q4_TAB(gb.z, 0), z2 = Q4_TAB(gb.z, 256), s3 = Q4_TAB(gb.w, 0), z3 = Q4_TAB(gb.w, 256);
+      deq_row<4, 2, false>(rows8, off, w, s0, z0); deq_row<5, 2, true>(rows8, off, w, s1, z1);
+      deq_row<6, 3, false>(rows8, off, w, s2, z2); deq_row<7, 3, true>(rows8, off, w, s3, z3);
+    }
   }
+#undef Q4_TAB
 }
 
 // The same with scales and packed zero points read from global memory: `sc` / `qz` point at the
 // task's 8 columns in group 0, `N` is the row length of the scales.
-__device__ __forceinline__ void deq_task_global(uint32_t rows8, int chunk, const uint32_t (&w)[8], const int4& ga, const int4& gb,
+__device__ __forceinline__ void deq_task_global(unsigned char* rows8, const uint32_t (&off)[8], const uint32_t (&w)[8], const int4& ga, const int4& gb,
                                                 const __half* sc, const uint32_t* qz, int N) {
   const int N8 = N >> 3;
   if (all_equal8(ga, gb)) {
     const uint4 s = __ldg(reinterpret_cast<const uint4*>(sc + (size_t)ga.x * N));
-    deq_task_uniform(rows8, chunk, w, s, zero_terms(s, __ldg(qz + (size_t)ga.x * N8)));
+    deq_task_uniform(rows8, off, w, s, zero_terms(s, __ldg(qz + (size_t)ga.x * N8)));
   } else {
     const int gi[8] = {ga.x, ga.y, ga.z, ga.w, gb.x, gb.y, gb.z, gb.w};
     uint4 s[8];
@@ -178,10 +188,10 @@ __device__ __forceinline__ void deq_task_global(uint32_t rows8, int chunk, const
       s[j] = __ldg(reinterpret_cast<const uint4*>(sc + (size_t)gi[j] * N));
       z[j] = __ldg(qz + (size_t)gi[j] * N8);
     }
-    deq_row<0, 0, false>(rows8, chunk, w, s[0], zero_terms(s[0], z[0])); deq_row<1, 0, true>(rows8, chunk, w, s[1], zero_terms(s[1], z[1]));
-    deq_row<2, 1, false>(rows8, chunk, w, s[2], zero_terms(s[2], z[2])); deq_row<3, 1, true>(rows8, chunk, w, s[3], zero_terms(s[3], z[3]));
-    deq_row<4, 2, false>(rows8, chunk, w, s[4], zero_terms(s[4], z[4])); deq_row<5, 2, true>(rows8, chunk, w, s[5], zero_terms(s[5], z[5]));
-    deq_row<6, 3, false>(rows8, chunk, w, s[6], zero_terms(s[6], z[6])); deq_row<7, 3, true>(rows8, chunk, w, s[7], zero_terms(s[7], z[7]));
+    deq_row<0, 0, false>(rows8, off, w, s[0], zero_terms(s[0], z[0])); deq_row<1, 0, true>(rows8, off, w, s[1], zero_terms(s[1], z[1]));
+    deq_row<2, 1, false>(rows8, off, w, s[2], zero_terms(s[2], z[2])); deq_row<3, 1, true>(rows8, off, w, s[3], zero_terms(s[3], z[3]));
+    deq_row<4, 2, false>(rows8, off, w, s[4], zero_terms(s[4], z[4])); deq_row<5, 2, true>(rows8, off, w, s[5], zero_terms(s[5], z[5]));
+    deq_row<6, 3, false>(rows8, off, w, s[6], zero_terms(s[6], z[6])); deq_row<7, 3, true>(rows8, off, w, s[7], zero_terms(s[7], z[7]));
   }
 }
 
