@@ -37,9 +37,10 @@ _SIGNATURES = {
     "q4_gemv_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                c_int, c_int, c_int, c_int, c_int, c_int, c_uint, c_void_p]),
     "q4_gemm_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                            c_int, c_int, c_int, c_int, c_int, c_void_p]),
+                            c_int, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "q4_gemm_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                            c_int, c_int, c_int, c_int, c_int, c_void_p]),
+                            c_int, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+    "q4_gemm_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "q4_device_status": (c_int, [ctypes.POINTER(c_uint)]),
     "q4_gemv": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                         c_int, c_int, c_int, c_int, c_int, c_int, c_uint, c_void_p, c_size_t, c_void_p]),
@@ -140,6 +141,20 @@ def workspace_for(device: torch.device, stream_handle: int) -> torch.Tensor:
     if ws is None:
         ws = torch.zeros(_WS_BYTES, dtype=torch.uint8, device=device)
         _workspaces[key] = ws
+    return ws
+
+
+_gemm_workspaces: dict = {}
+
+
+def gemm_workspace_for(device: torch.device, stream_handle: int, nbytes: int) -> torch.Tensor:
+    """Scratch of the fused GEMM for one (device, stream): zeroed when (re)allocated, only ever grows.
+    The kernels leave its counter head zero, so calls ordered on the stream can share it."""
+    key = (device.index, stream_handle)
+    ws = _gemm_workspaces.get(key)
+    if ws is None or ws.numel() < nbytes:
+        ws = torch.zeros(max(nbytes, 24 << 20), dtype=torch.uint8, device=device)
+        _gemm_workspaces[key] = ws
     return ws
 
 

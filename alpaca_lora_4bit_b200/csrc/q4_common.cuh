@@ -42,6 +42,14 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
   return v;
 }
 
+// 128-bit read-only load that the compiler may not move: used where a load is issued early on
+// purpose (a prefetch) and must not sink down to its first use.
+__device__ __forceinline__ int4 ldg_pinned_int4(const void* p) {
+  int4 v;
+  asm volatile("ld.global.nc.v4.s32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+  return v;
+}
+
 // Two exact small integers as a half2, taken from the same byte lane of two packed words.
 //   byte b (0..3) of `lo` and of `hi` each hold two 4-bit levels; `odd` selects the high nibble.
 // The byte pair is gathered with one PRMT; the low nibble is turned into 1024+q by OR-ing the

@@ -42,6 +42,8 @@ constexpr int GM_DEQ_THREADS = 128;           // per dequant group
 constexpr int GM_DEQ_GROUPS = 2;
 constexpr int GM_TMEM_COLS = 256;
 constexpr uint32_t GM_WAIT_TRIES = 40000;     // x ~2 us sleeping tries
+constexpr size_t Q4_GEMM_WS_COUNTER_BYTES = 65536;          // head of the workspace: arrival counters
+constexpr size_t Q4_GEMM_WS_SLICE_BYTES = 256 * 256 * 4;    // fp32 partial sums of one slice of one 256 x 256 tile
 
 struct GemmParams {
   const uint32_t* qw;       // [K/8, N]
@@ -59,6 +61,14 @@ struct GemmParams {
   //   backward  dx += V * lora_A,    V = scale * dy * lora_B    [M, 64] (zero-padded),  lora_w = lora_A [r, K]
   const __half* lora_w;
   int lora_r;
+  // CTA-pair kernel only.  Work items 0 .. n_whole-1 are whole output tiles; each remaining ("tail")
+  // tile is cut into split_f slices of split_sps contraction stages whose fp32 partial sums meet in
+  // ws_partials (split_f = 1: no cut).  ws_counters: one arrival counter per 32 rows of a tail tile,
+  // zero between launches.
+  int n_whole, split_f, split_sps, split_inv;   // split_inv = ceil(65536 / split_f)
+  float* ws_partials;
+  unsigned* ws_counters;
+  const __half* zp_table;   // backward: rn(s * (z+1)) for every [group, column], or null
 };
 
 __device__ __forceinline__ void gm_mark(unsigned long long* tr, int slot) {
@@ -298,6 +308,15 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__
 
 static unsigned long long* g_gemm_trace = nullptr;
 
+// rn(s * (z+1)) of every [group, column]: what the backward would otherwise recompute for every
+// row of every task when the rows of a task belong to different groups (act-order).
+__global__ void zp_table_kernel(const __half* __restrict__ scales, const uint32_t* __restrict__ qzeros, __half* __restrict__ out, int total8) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= total8) return;
+  const uint4 s = __ldg(reinterpret_cast<const uint4*>(scales) + i);
+  reinterpret_cast<uint4*>(out)[i] = zero_terms(s, __ldg(qzeros + i));
+}
+
 static int g_gemm_variant = 0;                // 0 = choose per shape, 1 = single-CTA kernel, 2 = CTA-pair kernel
 
 static size_t gemm_smem_bytes(bool transpose, int G, int stages) {
@@ -312,7 +331,8 @@ using namespace q4;
 
 static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, void* out, const void* scales,
                        const int32_t* qzeros, const int32_t* g_idx, const void* bias, const void* lora_u,
-                       const void* lora_w, int lora_r, int M, int K, int N, int G, q4_stream_t stream) {
+                       const void* lora_w, int lora_r, int M, int K, int N, int G, void* workspace, size_t workspace_bytes,
+                       q4_stream_t stream) {
   if (!act || !qweight || !out || !scales || !qzeros || !g_idx) return fail(Q4_E_BADARG, "gemm: null pointer");
   if (M <= 0 || K <= 0 || N <= 0 || G <= 0) return fail(Q4_E_BADARG, "gemm: M=%d K=%d N=%d G=%d", M, K, N, G);
   if (K % 128 || N % 128) return fail(Q4_E_SHAPE, "gemm: K=%d and N=%d must be multiples of 128", K, N);
@@ -321,6 +341,7 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
   if (lora_r < 0 || lora_r > 64) return fail(Q4_E_SHAPE, "gemm: low-rank width %d outside 0..64", lora_r);
   if (lora_r > 0 && (!lora_u || !lora_w || !aligned16(lora_u) || !aligned16(lora_w)))
     return fail(Q4_E_BADARG, "gemm: the low-rank term needs 16-byte aligned lora_u [M,64] and lora_w");
+  if (workspace && !aligned16(workspace)) return fail(Q4_E_ALIGN, "gemm: the workspace must be 16-byte aligned");
   if (int e = check_device()) return e;
   const int contract = transpose ? N : K, nout = transpose ? K : N;
   const int stages2 = gemm2_stages(transpose, G);
@@ -343,6 +364,7 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
   p.trace = g_gemm_trace;
   p.lora_w = lora_r > 0 ? (const __half*)lora_w : nullptr;
   p.lora_r = lora_r;
+  p.n_whole = 0; p.split_f = 1; p.split_sps = 0; p.split_inv = 65536; p.ws_partials = nullptr; p.ws_counters = nullptr; p.zp_table = nullptr;
   const int box_rows = use_pair ? 128 : GM_TILE_M;    // activation rows one TMA copy brings
   CUtensorMap amap;
   if (int e = make_tmap_2d(&amap, act, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)contract, (uint64_t)M,
@@ -362,9 +384,13 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
   const int tr = transpose ? 1 : 0;
   if (!attr_done[use_pair ? 1 : 0][tr][dev]) {
     const int cap = 227 * 1024;
-    const void* fn = use_pair ? (transpose ? (const void*)q4_gemm2_kernel<true> : (const void*)q4_gemm2_kernel<false>)
+    const void* fn = use_pair ? (transpose ? (const void*)q4_gemm2_kernel<true, false> : (const void*)q4_gemm2_kernel<false, false>)
                               : (transpose ? (const void*)q4_gemm_kernel<true> : (const void*)q4_gemm_kernel<false>);
     if (int e = check_cuda(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, cap), "gemm smem attribute")) return e;
+    if (use_pair) {
+      const void* fn_split = transpose ? (const void*)q4_gemm2_kernel<true, true> : (const void*)q4_gemm2_kernel<false, true>;
+      if (int e = check_cuda(cudaFuncSetAttribute(fn_split, cudaFuncAttributeMaxDynamicSharedMemorySize, cap), "gemm smem attribute")) return e;
+    }
     if (use_pair) {
       cudaLaunchConfig_t cfg = {};
       cfg.gridDim = dim3(2 * sm_count(), 1, 1); cfg.blockDim = dim3(G2_THREADS, 1, 1); cfg.dynamicSmemBytes = cap;
@@ -380,10 +406,43 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
   }
   if (use_pair) {
     const int n_tiles = (nout / G2_TILE_N) * ((M + G2_TILE_M - 1) / G2_TILE_M);
-    const int pairs = n_tiles < max_pairs[tr][dev] ? n_tiles : max_pairs[tr][dev];
+    const int P = max_pairs[tr][dev], T = p.n_contract_tiles;
+    unsigned char* ws = (unsigned char*)workspace;
+    size_t ws_off = Q4_GEMM_WS_COUNTER_BYTES;
+    // backward: table of zero terms in the workspace, filled by a small kernel ahead of the GEMM
+    p.zp_table = nullptr;
+    const size_t zp_bytes = ((size_t)G * N * sizeof(__half) + 255) & ~(size_t)255;
+    if (transpose && ws && workspace_bytes >= ws_off + zp_bytes) {
+      p.zp_table = (const __half*)(ws + ws_off);
+      const int total8 = G * (N / 8);
+      zp_table_kernel<<<(total8 + 255) / 256, 256, 0, st>>>((const __half*)scales, (const uint32_t*)qzeros, (__half*)(ws + ws_off), total8);
+      ws_off += zp_bytes;
+    }
+    // tiles left over after the last full round of all pairs are cut along the contraction
+    const int rem = n_tiles % P;
+    int f = 1, sps = T;
+    if (rem > 0 && ws && P / rem >= 2 && T >= 8) {
+      f = P / rem;
+      if (f > 8) f = 8;
+      if (f > T / 4) f = T / 4;
+      sps = (T + f - 1) / f;
+      f = (T + sps - 1) / sps;                       // no empty slice
+      if (f < 2 || workspace_bytes < ws_off + (size_t)rem * f * Q4_GEMM_WS_SLICE_BYTES) { f = 1; sps = T; }
+    }
+    p.split_f = f; p.split_sps = sps; p.split_inv = (65536 + f - 1) / f;
+    p.n_whole = f > 1 ? n_tiles - rem : n_tiles;
+    p.ws_partials = (float*)(ws + ws_off);
+    p.ws_counters = (unsigned*)ws;
+    const int n_items = p.n_whole + (n_tiles - p.n_whole) * f;
+    const int pairs = n_items < P ? n_items : P;
     const dim3 grid(2 * pairs), block(G2_THREADS);
-    if (transpose) q4_gemm2_kernel<true><<<grid, block, smem, st>>>(amap, umap, p);
-    else q4_gemm2_kernel<false><<<grid, block, smem, st>>>(amap, umap, p);
+    if (f > 1) {
+      if (transpose) q4_gemm2_kernel<true, true><<<grid, block, smem, st>>>(amap, umap, p);
+      else q4_gemm2_kernel<false, true><<<grid, block, smem, st>>>(amap, umap, p);
+    } else {
+      if (transpose) q4_gemm2_kernel<true, false><<<grid, block, smem, st>>>(amap, umap, p);
+      else q4_gemm2_kernel<false, false><<<grid, block, smem, st>>>(amap, umap, p);
+    }
   } else {
     const dim3 grid(nout / GM_TILE_N, (M + GM_TILE_M - 1) / GM_TILE_M), block(GM_THREADS);
     if (transpose) q4_gemm_kernel<true><<<grid, block, smem, st>>>(amap, umap, p);
@@ -392,16 +451,22 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
   return check_cuda(cudaGetLastError(), "gemm launch");
 }
 
+extern "C" size_t q4_gemm_workspace_bytes(int K, int N, int G) {
+  if (K <= 0 || N <= 0 || G <= 0) return 0;
+  const size_t zp_bytes = ((size_t)G * N * sizeof(__half) + 255) & ~(size_t)255;
+  return Q4_GEMM_WS_COUNTER_BYTES + zp_bytes + (size_t)80 * Q4_GEMM_WS_SLICE_BYTES;
+}
+
 extern "C" int q4_gemm_fwd(const void* x, const int32_t* qweight, void* y, const void* scales, const int32_t* qzeros,
                            const int32_t* g_idx, const void* bias, const void* lora_u, const void* lora_b, int lora_r,
-                           int M, int K, int N, int G, q4_stream_t stream) {
-  return gemm_launch(false, x, qweight, y, scales, qzeros, g_idx, bias, lora_u, lora_b, lora_r, M, K, N, G, stream);
+                           int M, int K, int N, int G, void* workspace, size_t workspace_bytes, q4_stream_t stream) {
+  return gemm_launch(false, x, qweight, y, scales, qzeros, g_idx, bias, lora_u, lora_b, lora_r, M, K, N, G, workspace, workspace_bytes, stream);
 }
 
 extern "C" int q4_gemm_bwd(const void* dy, const int32_t* qweight, void* dx, const void* scales, const int32_t* qzeros,
                            const int32_t* g_idx, const void* lora_v, const void* lora_a, int lora_r,
-                           int M, int K, int N, int G, q4_stream_t stream) {
-  return gemm_launch(true, dy, qweight, dx, scales, qzeros, g_idx, nullptr, lora_v, lora_a, lora_r, M, K, N, G, stream);
+                           int M, int K, int N, int G, void* workspace, size_t workspace_bytes, q4_stream_t stream) {
+  return gemm_launch(true, dy, qweight, dx, scales, qzeros, g_idx, nullptr, lora_v, lora_a, lora_r, M, K, N, G, workspace, workspace_bytes, stream);
 }
 
 extern "C" int q4_gemm_set_variant(int variant) {

@@ -61,7 +61,36 @@ __device__ __forceinline__ bool wait_bar_idle(uint64_t* bar, uint32_t parity, vo
   return false;
 }
 
-template <bool TRANSPOSE>
+// A work item: a whole output tile, or one slice of the contraction of a tail tile (the tiles left
+// over after the last full round of all pairs are cut along the contraction so that every pair
+// still has work; their fp32 partial sums meet in global memory, see the epilogue).
+struct WorkItem {
+  int tile;      // output tile
+  int kb, ke;    // contraction stages [kb, ke)
+  int tail;      // index among the tail tiles (split items only)
+  int slice;     // slice of the tail tile
+  bool split;    // partial sum: goes to the workspace instead of the output
+  bool lora;     // the low-rank stage follows the contraction stages
+};
+template <bool SPLIT>
+__device__ __forceinline__ WorkItem work_item(const GemmParams& p, int i, int T) {
+  WorkItem w;
+  if (!SPLIT || i < p.n_whole) {
+    w.tile = i; w.kb = 0; w.ke = T; w.tail = 0; w.slice = 0; w.split = false; w.lora = p.lora_r > 0;
+  } else {
+    const int j = i - p.n_whole;
+    w.tail = (j * p.split_inv) >> 16;               // j / split_f without a division (j < 128, split_f <= 8)
+    w.slice = j - w.tail * p.split_f; w.tile = p.n_whole + w.tail;
+    w.kb = w.slice * p.split_sps; w.ke = min(T, w.kb + p.split_sps);
+    w.split = true; w.lora = p.lora_r > 0 && w.slice == p.split_f - 1;
+  }
+  return w;
+}
+
+// SPLIT = false: every work item is a whole tile and the item decode folds away (the loop bounds of
+// the dequant loop are then kernel-wide constants, which the register allocation of that loop is
+// sensitive to); SPLIT = true: the launch has tail tiles cut along the contraction.
+template <bool TRANSPOSE, bool SPLIT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
 q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap umap, const GemmParams p) {
   extern __shared__ unsigned char smem_raw[];
@@ -81,11 +110,11 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
   const uint32_t rank = cluster_ctarank();
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const int T = p.n_contract_tiles;
-  const int TT = T + (p.lora_r > 0 ? 1 : 0);          // one more stage for the low-rank term
   const int lora_ks = (p.lora_r + 15) >> 4;           // its 16-wide MMA steps
   const int n_out_total = TRANSPOSE ? p.K : p.N;
   const int m_tiles = (p.M + G2_TILE_M - 1) / G2_TILE_M;
   const int n_tiles = m_tiles * (n_out_total / G2_TILE_N);
+  const int n_items = SPLIT ? p.n_whole + (n_tiles - p.n_whole) * p.split_f : n_tiles;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; ++i) { mbar_init(&full[i], 1 + 8); mbar_init(&empty[i], 1); }
@@ -112,13 +141,16 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
       int st = 0, use = 0;                             // stage and how often it has been used, over all tiles
       unsigned polls = 0;
       const uint32_t full0 = mapa_u32(smem_u32(full), 0);
-      for (int tile = pair; tile < n_tiles; tile += n_pairs) {
-        const int m0 = (tile % m_tiles) * G2_TILE_M + 128 * (int)rank;
-        for (int it = 0; it < TT; ++it) {
+      for (int item = pair; item < n_items; item += n_pairs) {
+        const WorkItem wi = work_item<SPLIT>(p, item, T);
+        const int m0 = (wi.tile % m_tiles) * G2_TILE_M + 128 * (int)rank;
+        const int nst = wi.ke - wi.kb + (wi.lora ? 1 : 0);
+        for (int j = 0; j < nst; ++j) {
+          const int it = wi.kb + j;
           if (use > 0) wait_bar_idle(&empty[st], (use - 1) & 1, abort_flag, 200, &polls);
           if (rank == 0) mbar_arrive_expect_tx(&full[st], 2 * G2_A_BYTES);
           unsigned char* dst = stages + (size_t)st * G2_STAGE_BYTES;
-          if (it < T) tma_load_2d_pair(dst, &amap, it * GM_TILE_C, m0, full0 + 8 * st);
+          if (it < wi.ke) tma_load_2d_pair(dst, &amap, it * GM_TILE_C, m0, full0 + 8 * st);
           else tma_load_2d_pair(dst, &umap, 0, m0, full0 + 8 * st);
           if (++st == S) { st = 0; ++use; }
         }
@@ -140,18 +172,20 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
       int st = 0, use = 0, tl = 0;
       unsigned polls = 0;
       uint64_t ad = ad0, bd = bd0;
-      for (int tile = pair; tile < n_tiles; tile += n_pairs, ++tl) {
+      for (int item = pair; item < n_items; item += n_pairs, ++tl) {
+        const WorkItem wi = work_item<SPLIT>(p, item, T);
+        const int nst = wi.ke - wi.kb + (wi.lora ? 1 : 0), ncon = wi.ke - wi.kb;
         const int acc = tl & 1, acc_use = tl >> 1;
         if (acc_use > 0) wait_bar_cluster(&acc_empty[acc], (acc_use - 1) & 1, abort_flag);
         tc_fence_after();
         const uint32_t d_tmem = tmem_acc + acc * 256;
         const bool tron = p.trace != nullptr && tl == 1;
-        for (int it = 0; it < TT; ++it) {
+        for (int it = 0; it < nst; ++it) {
           if (tron && it < 12) gm_mark(p.trace, 5 * it);
           wait_bar_cluster(&full[st], use & 1, abort_flag, &polls);
           if (tron && it < 12) gm_mark(p.trace, 5 * it + 2);
           tc_fence_after();
-          if (it < T) {
+          if (it < ncon) {
             umma_f16_pair(d_tmem, ad, bd, idesc, it > 0 ? 1u : 0u);
             umma_f16_pair(d_tmem, ad + A_STEP, bd + B_STEP, idesc, 1u);
             umma_f16_pair(d_tmem, ad + 2 * A_STEP, bd + 2 * B_STEP, idesc, 1u);
@@ -182,9 +216,11 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
     int tl = 0, tab_out0 = -1;
     int st = grp, use = 0;                                         // of this group's next stage use (g = grp, grp + 2, ...)
     unsigned polls = 0;
-    for (int tile = pair; tile < n_tiles; tile += n_pairs, ++tl) {
-      const int out0 = (tile / m_tiles) * G2_TILE_N + 128 * (int)rank;   // first output column (n forward, k backward)
-      const int gbase = tl * TT;
+    int gbase = 0;                                                 // stage uses of all earlier items
+    for (int item = pair; item < n_items; item += n_pairs, ++tl) {
+      const WorkItem wi = work_item<SPLIT>(p, item, T);
+      const int ncon = wi.ke - wi.kb, nst = ncon + (wi.lora ? 1 : 0);    // stages of this item: j = 0 .. nst-1, contraction stage kb + j
+      const int out0 = (wi.tile / m_tiles) * G2_TILE_N + 128 * (int)rank;   // first output column (n forward, k backward)
       if (!TRANSPOSE && out0 != tab_out0) {
         // tables for the CTA's 128 columns: scale and rn(s*(z+1)) of every group
         if (tab_out0 >= 0) named_bar_sync(1, GM_DEQ_THREADS * GM_DEQ_GROUPS);      // all readers of the old tables are done
@@ -205,7 +241,7 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         const int ncol = TRANSPOSE ? it * GM_TILE_C + 8 * chunk16 : out0 + 8 * chunk16;
         return p.qw + (size_t)prow * N + ncol;
       };
-      const int it0 = (grp ^ gbase) & 1;
+      const int j0 = (grp ^ gbase) & 1;                              // this group's first stage of the item
       // Packed words (and, forward, the groups of their 8 k-rows) of one task.  Two sets: the loads of
       // the group's next task are in flight into one while the other is being dequantised.
       struct TaskRegs { uint4 wa, wb; int4 ga, gb; };
@@ -215,18 +251,20 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         tga = __ldg(reinterpret_cast<const int4*>(p.g_idx + out0 + 8 * r));
         tgb = __ldg(reinterpret_cast<const int4*>(p.g_idx + out0 + 8 * r + 4));
       }
-      auto prefetch = [&](int it, TaskRegs& R) {
-        if (it >= T) return;
+      auto prefetch = [&](int j, TaskRegs& R) {
+        if (j >= ncon) return;
+        const int it = wi.kb + j;
         R.wa = ldg_stream(word_ptr(it)); R.wb = ldg_stream(word_ptr(it) + 4);
         if (!TRANSPOSE) {
-          R.ga = __ldg(reinterpret_cast<const int4*>(p.g_idx + it * GM_TILE_C + 8 * r));
-          R.gb = __ldg(reinterpret_cast<const int4*>(p.g_idx + it * GM_TILE_C + 8 * r + 4));
+          R.ga = ldg_pinned_int4(p.g_idx + it * GM_TILE_C + 8 * r);
+          R.gb = ldg_pinned_int4(p.g_idx + it * GM_TILE_C + 8 * r + 4);
         }
       };
-      auto task = [&](int it, const TaskRegs& C) {
+      auto task = [&](int j, const TaskRegs& C) {
         if (st >= S) { st -= S; ++use; }
         unsigned char* bst = stages + (size_t)st * G2_STAGE_BYTES + G2_A_BYTES;
-        if (it == T) {
+        const int it = wi.kb + j;
+        if (j == ncon) {
           // ---- low-rank stage: B operand from lora_w instead of dequantised weights ----
           if (use > 0 && lane == 0) wait_bar_idle(&empty[st], (use - 1) & 1, abort_flag, 100, &polls);
           __syncwarp();
@@ -261,34 +299,36 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
           return;
         }
         const uint32_t w[8] = {C.wa.x, C.wa.y, C.wa.z, C.wa.w, C.wb.x, C.wb.y, C.wb.z, C.wb.w};
-        const bool tr_on = p.trace && tl == 1 && dw == 0 && lane == 0 && it < 40;
-        if (tr_on) gm_mark(p.trace, 64 + 3 * (it >> 1));
+        const bool tr_on = p.trace && tl == 1 && dw == 0 && lane == 0 && j < 40;
+        if (tr_on) gm_mark(p.trace, 64 + 3 * (j >> 1));
         if (use > 0 && lane == 0) wait_bar_idle(&empty[st], (use - 1) & 1, abort_flag, 100, &polls);
         __syncwarp();
-        if (tr_on) gm_mark(p.trace, 65 + 3 * (it >> 1));
+        if (tr_on) gm_mark(p.trace, 65 + 3 * (j >> 1));
         // forward: panel (chunk16 / 8) of [64 rows][128 B]; backward: one panel of [128 rows][128 B]
         unsigned char* rows8 = bst + (TRANSPOSE ? r * 1024 : (chunk16 >> 3) * 8192 + r * 1024);
         if (TRANSPOSE) {
           const int ncol = it * GM_TILE_C + 8 * chunk16;             // global column of the task
-          deq_task_global(rows8, off, w, tga, tgb, p.scales + ncol, p.qzeros + (ncol >> 3), N);
+          if (p.zp_table) deq_task_global_zp(rows8, off, w, tga, tgb, p.scales + ncol, p.zp_table + ncol, N);
+          else deq_task_global(rows8, off, w, tga, tgb, p.scales + ncol, p.qzeros + (ncol >> 3), N);
         } else {
           deq_task_tables(rows8, off, w, C.ga, C.gb, tab + 16 * chunk16);
         }
         fence_async_smem();                          // generic-proxy stores -> visible to the tensor core
         __syncwarp();
         if (lane == 0) mbar_arrive_cluster(full0 + 8 * st);
-        if (tr_on) gm_mark(p.trace, 66 + 3 * (it >> 1));
+        if (tr_on) gm_mark(p.trace, 66 + 3 * (j >> 1));
         st += GM_DEQ_GROUPS;
       };
-      prefetch(it0, R0);
-      for (int it = it0; it < TT; it += 2 * GM_DEQ_GROUPS) {
-        prefetch(it + GM_DEQ_GROUPS, R1);
-        task(it, R0);
-        if (it + GM_DEQ_GROUPS < TT) {
-          prefetch(it + 2 * GM_DEQ_GROUPS, R0);
-          task(it + GM_DEQ_GROUPS, R1);
+      prefetch(j0, R0);
+      for (int j = j0; j < nst; j += 2 * GM_DEQ_GROUPS) {
+        prefetch(j + GM_DEQ_GROUPS, R1);
+        task(j, R0);
+        if (j + GM_DEQ_GROUPS < nst) {
+          prefetch(j + 2 * GM_DEQ_GROUPS, R0);
+          task(j + GM_DEQ_GROUPS, R1);
         }
       }
+      gbase += nst;
     }
     if (p.trace && lane == 0) p.trace[(size_t)blockIdx.x * 256 + 246 + dw] = polls;
   } else if (warp >= 12) {
@@ -297,43 +337,90 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
     const uint32_t acc_empty0 = mapa_u32(smem_u32(acc_empty), 0);  // the even CTA's acc_empty[0]
     int tl = 0;
     unsigned polls = 0;
-    for (int tile = pair; tile < n_tiles; tile += n_pairs, ++tl) {
+    for (int item = pair; item < n_items; item += n_pairs, ++tl) {
+      const WorkItem wi = work_item<SPLIT>(p, item, T);
       const int acc = tl & 1, acc_use = tl >> 1;
-      const int col0 = (tile / m_tiles) * G2_TILE_N;
-      const int m = (tile % m_tiles) * G2_TILE_M + 128 * (int)rank + 32 * quarter + lane;
+      const int col0 = (wi.tile / m_tiles) * G2_TILE_N;
+      const int m = (wi.tile % m_tiles) * G2_TILE_M + 128 * (int)rank + 32 * quarter + lane;
+      // 32 fp32 sums of row m, columns col0 + 32 cb ..: (+bias) -> fp16 -> global
+      auto emit = [&](int cb, const uint32_t (&v)[32]) {
+        if (m >= p.M) return;
+        __half* dst = p.out + (size_t)m * n_out_total + col0 + cb * 32;
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint4 o;
+          uint32_t* ov = reinterpret_cast<uint32_t*>(&o);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            float f0 = __uint_as_float(v[8 * q + 2 * e]), f1 = __uint_as_float(v[8 * q + 2 * e + 1]);
+            if (!TRANSPOSE && p.bias) {
+              f0 += __half2float(p.bias[col0 + cb * 32 + 8 * q + 2 * e]);
+              f1 += __half2float(p.bias[col0 + cb * 32 + 8 * q + 2 * e + 1]);
+            }
+            ov[e] = as_u32(__floats2half2_rn(f0, f1));
+          }
+          *reinterpret_cast<uint4*>(dst + 8 * q) = o;
+        }
+      };
       if (threadIdx.x == 384 && tl < 8) gm_mark(p.trace, 200 + 3 * tl);
       if (lane == 0) wait_bar_idle(&acc_full[acc], acc_use & 1, abort_flag, 1000, &polls);
       __syncwarp();
       tc_fence_after();
       if (threadIdx.x == 384 && tl < 8) gm_mark(p.trace, 201 + 3 * tl);
+      // Partial sums of a slice: this warp's 32 rows x 256 columns as [cb][j][lane][4 floats], so that
+      // every 16-byte access of the warp is one contiguous 512 bytes.
+      const size_t part_floats = 8 * 8 * 32 * 4;
+      float* part = wi.split ? p.ws_partials + ((((size_t)wi.tail * p.split_f + wi.slice) * 2 + rank) * 4 + quarter) * part_floats : nullptr;
 #pragma unroll 1
       for (int cb = 0; cb < G2_TILE_N / 32; ++cb) {
         uint32_t v[32];
         tmem_ld32(tmem_acc + ((uint32_t)(32 * quarter) << 16) + acc * 256 + cb * 32, v);
         tmem_ld_wait();
-        if (m < p.M) {
-          __half* dst = p.out + (size_t)m * n_out_total + col0 + cb * 32;
+        if (!wi.split) {
+          emit(cb, v);
+        } else {
 #pragma unroll
-          for (int q = 0; q < 4; ++q) {
-            uint4 o;
-            uint32_t* ov = reinterpret_cast<uint32_t*>(&o);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-              float f0 = __uint_as_float(v[8 * q + 2 * e]), f1 = __uint_as_float(v[8 * q + 2 * e + 1]);
-              if (!TRANSPOSE && p.bias) {
-                f0 += __half2float(p.bias[col0 + cb * 32 + 8 * q + 2 * e]);
-                f1 += __half2float(p.bias[col0 + cb * 32 + 8 * q + 2 * e + 1]);
-              }
-              ov[e] = as_u32(__floats2half2_rn(f0, f1));
-            }
-            *reinterpret_cast<uint4*>(dst + 8 * q) = o;
-          }
+          for (int j = 0; j < 8; ++j)
+            *reinterpret_cast<uint4*>(part + ((cb * 8 + j) * 32 + lane) * 4) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
         }
       }
       // this warp has read its part of the accumulator: the even CTA may overwrite it
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc_empty0 + 8 * acc);
+      if (wi.split) {
+        // The warp that arrives last at the counter of these 32 rows adds the slices up in slice
+        // order (the same order whoever it is), writes the rows and leaves the counter at zero.
+        unsigned* cnt = p.ws_counters + ((size_t)wi.tail * 2 + rank) * 4 + quarter;
+        __threadfence();
+        __syncwarp();
+        unsigned last = 0;
+        if (lane == 0) last = atomicAdd(cnt, 1u) == (unsigned)(p.split_f - 1) ? 1u : 0u;
+        last = __shfl_sync(0xffffffffu, last, 0);
+        if (last) {
+          __threadfence();
+          const float* base = p.ws_partials + (((size_t)wi.tail * p.split_f * 2 + rank) * 4 + quarter) * part_floats;
+#pragma unroll 1
+          for (int cb = 0; cb < G2_TILE_N / 32; ++cb) {
+            float sum[32];
+#pragma unroll
+            for (int e = 0; e < 32; ++e) sum[e] = 0.f;
+            for (int sl = 0; sl < p.split_f; ++sl) {
+              const float* src = base + (size_t)sl * 2 * 4 * part_floats;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                const float4 t = __ldcg(reinterpret_cast<const float4*>(src + ((cb * 8 + j) * 32 + lane) * 4));
+                sum[4 * j] += t.x; sum[4 * j + 1] += t.y; sum[4 * j + 2] += t.z; sum[4 * j + 3] += t.w;
+              }
+            }
+            uint32_t v[32];
+#pragma unroll
+            for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(sum[e]);
+            emit(cb, v);
+          }
+          if (lane == 0) *cnt = 0;
+        }
+      }
       if (threadIdx.x == 384 && tl < 8) gm_mark(p.trace, 202 + 3 * tl);
     }
     if (p.trace && lane == 0) p.trace[(size_t)blockIdx.x * 256 + 242 + (warp & 3)] = polls;

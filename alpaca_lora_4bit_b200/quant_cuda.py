@@ -113,6 +113,9 @@ def gemv(x, qweight, y, scales, zeros, g_idx, groupsize, flags, bias=None) -> No
                 _lib.check(rc, "gemv")
 
 
+_gemm_ws_bytes: dict = {}
+
+
 def gemm(x, qweight, out, scales, zeros, g_idx, transpose=False, bias=None, lora_u=None, lora_w=None) -> None:
     """Fused large-M product on the tensor cores: ``out = x @ W (+ bias)`` or, with ``transpose``,
     ``out = x @ W.T``; ``x``, ``out``, ``scales`` fp16, W never leaves shared memory.
@@ -139,12 +142,17 @@ def gemm(x, qweight, out, scales, zeros, g_idx, transpose=False, bias=None, lora
     L = _lib.lib()
     with _lib.on_device(dev):
         st = _lib.stream_of(x)
+        need = _gemm_ws_bytes.get((K, N, G))
+        if need is None:
+            need = _gemm_ws_bytes[(K, N, G)] = int(L.q4_gemm_workspace_bytes(K, N, G))
+        ws = _lib.gemm_workspace_for(dev, st, need)
         if transpose:
             rc = L.q4_gemm_bwd(x.data_ptr(), qweight.data_ptr(), out.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
-                               g_idx.data_ptr(), _lib.ptr(lora_u), _lib.ptr(lora_w), r, M, K, N, G, st)
+                               g_idx.data_ptr(), _lib.ptr(lora_u), _lib.ptr(lora_w), r, M, K, N, G, ws.data_ptr(), ws.numel(), st)
         else:
             rc = L.q4_gemm_fwd(x.data_ptr(), qweight.data_ptr(), out.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
-                               g_idx.data_ptr(), _lib.ptr(bias), _lib.ptr(lora_u), _lib.ptr(lora_w), r, M, K, N, G, st)
+                               g_idx.data_ptr(), _lib.ptr(bias), _lib.ptr(lora_u), _lib.ptr(lora_w), r, M, K, N, G,
+                               ws.data_ptr(), ws.numel(), st)
     _lib.check(rc, "gemm")
 
 

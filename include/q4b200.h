@@ -121,10 +121,20 @@ int q4_gemv_static(const void* x, const int32_t* qweight, void* y, const void* s
  * gradient with respect to x.  1 <= lora_r <= 64. */
 int q4_gemm_fwd(const void* x, const int32_t* qweight, void* y, const void* scales, const int32_t* qzeros,
                 const int32_t* g_idx, const void* bias, const void* lora_u, const void* lora_b, int lora_r,
-                int M, int K, int N, int G, q4_stream_t stream);
+                int M, int K, int N, int G, void* workspace, size_t workspace_bytes, q4_stream_t stream);
 int q4_gemm_bwd(const void* dy, const int32_t* qweight, void* dx, const void* scales, const int32_t* qzeros,
                 const int32_t* g_idx, const void* lora_v, const void* lora_a, int lora_r,
-                int M, int K, int N, int G, q4_stream_t stream);
+                int M, int K, int N, int G, void* workspace, size_t workspace_bytes, q4_stream_t stream);
+/* Optional scratch for the two calls above (no reference counterpart: the reference's scratch is
+ * the dense fp16 copy of W it reconstructs).  `workspace` may be NULL; with at least
+ * q4_gemm_workspace_bytes(K, N, G) bytes of device memory, 16-byte aligned, whose first 64 KiB are
+ * zero before the first call (the kernels leave them zero), the CTA-pair kernel
+ *   - cuts the output tiles left over after the last full round of all SM pairs along the
+ *     contraction, so that no SM pair idles through that round (fp32 partial sums meet in the
+ *     workspace and are added in a fixed order: results do not depend on timing), and
+ *   - in the backward reads rn(s*(z+1)) from a [G, N] table a small kernel fills first.
+ * One workspace serves calls that are ordered on one stream; calls that may overlap need one each. */
+size_t q4_gemm_workspace_bytes(int K, int N, int G);
 
 /* Copies the device status word to *out (synchronises the device): 0, or 0xDEAD0001 if a bounded
  * wait inside a q4_gemm_* kernel expired (its output is then invalid). */

@@ -196,6 +196,56 @@ def test_pair_kernel_many_tiles_per_pair(gemm_variant, transpose):
     assert rel_fro(out, want) <= REL_TOL
 
 
+@pytest.mark.parametrize("transpose", [False, True])
+@pytest.mark.parametrize("act", [False, True])
+def test_tail_tiles_split_along_the_contraction(gemm_variant, transpose, act):
+    """20 output tiles on 74 SM pairs: with a workspace every tile is cut into slices whose partial
+    sums are added in a fixed order (bit-identical from call to call, workspace left clean); without
+    one the tiles are computed whole.  Both against the oracle, bias and low-rank term included."""
+    from alpaca_lora_4bit_b200 import _lib
+    K, N, M, r = (2048, 1280, 1024, 16) if not transpose else (1280, 2048, 1024, 16)
+    layer = synth.make_layer(K, N, 128, act, seed=21)
+    A, B = synth.make_lora(K, N, r, seed=22)
+    x = synth.make_acts(M, N if transpose else K, seed=23)
+    bias = None if transpose else torch.randn(N).half()
+    w = orc.recons_v2(layer.qweight, layer.scales, layer.qzeros, layer.g_idx).float()
+    if transpose:
+        u = ((x.float() @ B.float()) * 2.0).half()
+        want, lw = x.float() @ w.t() + u.float() @ A.float(), A
+    else:
+        u = ((x.float() @ A.float().t()) * 2.0).half()
+        want, lw = x.float() @ w + u.float() @ B.float().t() + bias.float(), B
+    L = layer.to(DEV)
+    xd, ud, lwd = x.to(DEV), torch.nn.functional.pad(u, (0, 64 - r)).to(DEV), lw.contiguous().to(DEV)
+    bd = None if bias is None else bias.to(DEV)
+    gemm_variant(2)
+    outs = []
+    for _ in range(2):
+        out = torch.empty((M, K if transpose else N), dtype=torch.float16, device=DEV)
+        quant_cuda.gemm(xd, L.qweight, out, L.scales, L.qzeros, L.g_idx, transpose=transpose, bias=bd, lora_u=ud, lora_w=lwd)
+        torch.cuda.synchronize()
+        outs.append(out)
+    assert quant_cuda.device_status() == 0
+    assert rel_fro(outs[0], want) <= REL_TOL
+    assert torch.equal(outs[0], outs[1])
+    ws = _lib.gemm_workspace_for(torch.device(DEV), torch.cuda.current_stream().cuda_stream, 0)
+    assert int(ws[:65536].view(torch.int32).abs().max()) == 0          # arrival counters back at zero
+    # the same call without a workspace
+    lib = _lib.lib()
+    whole = torch.empty_like(outs[0])
+    G, st = L.scales.shape[0], torch.cuda.current_stream().cuda_stream
+    if transpose:
+        rc = lib.q4_gemm_bwd(xd.data_ptr(), L.qweight.data_ptr(), whole.data_ptr(), L.scales.data_ptr(), L.qzeros.data_ptr(),
+                             L.g_idx.data_ptr(), ud.data_ptr(), lwd.data_ptr(), r, M, K, N, G, None, 0, st)
+    else:
+        rc = lib.q4_gemm_fwd(xd.data_ptr(), L.qweight.data_ptr(), whole.data_ptr(), L.scales.data_ptr(), L.qzeros.data_ptr(),
+                             L.g_idx.data_ptr(), bd.data_ptr(), ud.data_ptr(), lwd.data_ptr(), r, M, K, N, G, None, 0, st)
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert rel_fro(whole, want) <= REL_TOL
+    assert rel_fro(whole, outs[0]) <= 5e-4
+
+
 def test_pair_kernel_rejects_shapes_it_cannot_serve(gemm_variant):
     layer = synth.make_layer(256, 384, 128, False, seed=3).to(DEV)
     x = synth.make_acts(16, 256, seed=4).to(DEV)
