@@ -42,6 +42,15 @@ __device__ __forceinline__ uint4 ldg_stream(const void* p) {
   return v;
 }
 
+// (a & mask) | bits as ONE three-input logic instruction.  Written in C++ with two literal constants
+// the expression compiles to two instructions (the instruction has room for a single immediate);
+// here both constants are register operands, loaded once outside the loops that use them.
+__device__ __forceinline__ uint32_t and_or(uint32_t a, uint32_t mask, uint32_t bits) {
+  uint32_t d;
+  asm("lop3.b32 %0, %1, %2, %3, 0xEA;" : "=r"(d) : "r"(a), "r"(mask), "r"(bits));
+  return d;
+}
+
 // 128-bit read-only load that the compiler may not move: used where a load is issued early on
 // purpose (a prefetch) and must not sink down to its first use.
 __device__ __forceinline__ int4 ldg_pinned_int4(const void* p) {
@@ -63,10 +72,10 @@ __device__ __forceinline__ __half2 nibble_pair(uint32_t lo, uint32_t hi) {
   constexpr uint32_t sel = BYTE | ((BYTE + 4) << 8);
   uint32_t u = prmt(lo, hi, sel);
   if (!ODD) {
-    uint32_t v = (u & 0x000F000Fu) | 0x64006400u;
+    uint32_t v = and_or(u, 0x000F000Fu, 0x64006400u);
     return __hsub2(as_h2(v), as_h2(0x64006400u));
   } else {
-    uint32_t v = (u & 0x00F000F0u) | 0x64006400u;
+    uint32_t v = and_or(u, 0x00F000F0u, 0x64006400u);
     return __hfma2(as_h2(v), as_h2(0x2C002C00u) /* 1/16 */, as_h2(0xD400D400u) /* -64 */);
   }
 }

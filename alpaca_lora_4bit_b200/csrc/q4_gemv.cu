@@ -155,6 +155,8 @@ struct GemvStreamParams {
   unsigned* status;
   int group_shift;                                // log2(steps per group), or -1 if not a power of two
   unsigned long long* trace;                      // optional timing trace (64 slots per CTA), else null
+  int whole_tiles;                                // lean kernel: CTAs get whole column tiles (no sums meet across CTAs)
+  int n_groups;                                   // rows of scales / qzeros
 };
 
 template <int MT>
@@ -165,6 +167,14 @@ __host__ __device__ constexpr size_t gemv_stream_smem() {
 
 __device__ __forceinline__ void trace_mark(unsigned long long* tr, int slot) {
   if (tr && slot < 64) tr[(size_t)blockIdx.x * 64 + slot] = clock64();
+}
+// the same with the device-wide nanosecond timer, to line up CTAs of different SMs and launches
+__device__ __forceinline__ void trace_mark_ns(unsigned long long* tr, int slot) {
+  if (tr && slot < 64) {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    tr[(size_t)blockIdx.x * 64 + slot] = t;
+  }
 }
 
 // CTA that owns unit u when `nu` units are dealt to `G` CTAs as [c*nu/G, (c+1)*nu/G).
@@ -453,15 +463,15 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
           for (int q = 0; q < 4; ++q) {
             if constexpr (XS) {
               const uint32_t w8 = w[q] >> 8;
-              pr[q][0] = (w[q] & 0x000F000Fu) | 0x64006400u;
-              pr[q][1] = (w[q] & 0x00F000F0u) | 0x64006400u;
-              pr[q][2] = (w8 & 0x000F000Fu) | 0x64006400u;
-              pr[q][3] = (w8 & 0x00F000F0u) | 0x64006400u;
+              pr[q][0] = and_or(w[q], 0x000F000Fu, 0x64006400u);
+              pr[q][1] = and_or(w[q], 0x00F000F0u, 0x64006400u);
+              pr[q][2] = and_or(w8, 0x000F000Fu, 0x64006400u);
+              pr[q][3] = and_or(w8, 0x00F000F0u, 0x64006400u);
             } else {
-              pr[q][0] = (w[q] & 0x000F000Fu) | 0x64006400u;
-              pr[q][1] = ((w[q] >> 4) & 0x000F000Fu) | 0x64006400u;
-              pr[q][2] = ((w[q] >> 8) & 0x000F000Fu) | 0x64006400u;
-              pr[q][3] = ((w[q] >> 12) & 0x000F000Fu) | 0x64006400u;
+              pr[q][0] = and_or(w[q], 0x000F000Fu, 0x64006400u);
+              pr[q][1] = and_or(w[q] >> 4, 0x000F000Fu, 0x64006400u);
+              pr[q][2] = and_or(w[q] >> 8, 0x000F000Fu, 0x64006400u);
+              pr[q][3] = and_or(w[q] >> 12, 0x000F000Fu, 0x64006400u);
             }
           }
           const bool first = FAST ? (uu == 0) : fresh;
@@ -554,54 +564,79 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
   unsigned char* zero_rows = reinterpret_cast<unsigned char*>(const_cast<int*>(flags)) + 64;   // [16 warps][512 B] of zeros
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) trace_mark_ns(sp.trace, 40);
   const int nu = sp.total_units, G = gridDim.x, upt = sp.units_per_tile;
-  const int u0 = (int)((long long)blockIdx.x * nu / G), u1 = (int)((long long)(blockIdx.x + 1) * nu / G);
+  // this CTA's units [u0, u1): an even share of all units, or (whole_tiles) of all column tiles
+  // (the host keeps nu * G below 2^32, so 32-bit arithmetic is exact)
+  const unsigned share = sp.whole_tiles ? (unsigned)(nu / upt) : (unsigned)nu, per = sp.whole_tiles ? (unsigned)upt : 1u;
+  const int u0 = (int)((unsigned)blockIdx.x * share / (unsigned)G * per), u1 = (int)(((unsigned)blockIdx.x + 1u) * share / (unsigned)G * per);
   const int K = p.K, gs = p.groupsize;
   unsigned char* my_stages = smem + (size_t)warp * GF_STAGES * STG;
   uint64_t* my_full = full + warp * GF_STAGES;
 
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < GF_WARPS * GF_STAGES; ++i) mbar_init(&full[i], 1 + 32);   // TMA arrive + 32 cp.async arrivals
-    flags[0] = 0;
+  if (lane < GF_STAGES) {                                 // every warp sets up its own barriers
+    mbar_init(&my_full[lane], 1 + 32);                    // TMA arrive + 32 cp.async arrivals
     mbar_fence_init();
+  }
+  if (threadIdx.x == 0) {
+    flags[0] = 0;
     tma_prefetch_desc(&wmap); tma_prefetch_desc(&smap); tma_prefetch_desc(&zmap);
   }
   for (int i = threadIdx.x; i < GF_WARPS * 128; i += GF_THREADS) reinterpret_cast<uint32_t*>(zero_rows)[i] = 0u;
+  if (threadIdx.x == 0) trace_mark_ns(sp.trace, 46);
   __syncthreads();
+  if (threadIdx.x == 0) trace_mark_ns(sp.trace, 47);
   pdl_launch_dependents();
 
-  // weights (+ scales, zero points) of this warp's n-th unit: lanes 0..2 issue one TMA copy each
-  auto issue_w = [&](int n) {
-    const int u = u0 + warp + GF_WARPS * n;
-    if (u >= u1) return;
-    const int tile = u / upt, ux = u - tile * upt;        // one division per unit, on three lanes only below
-    unsigned char* dst = my_stages + (size_t)(n % GF_STAGES) * STG;
-    uint64_t* bar = &my_full[n % GF_STAGES];
-    const int grow0 = sp.group_shift >= 0 ? ((ux * GEMV_UNIT_STEPS) >> sp.group_shift) : (ux * GEMV_UNIT_ROWS * 8) / gs;
-    if (lane == 0) {
-      mbar_arrive_expect_tx(bar, sp.stage_tx);
-      tma_load_2d(dst, &wmap, tile * GEMV_TN, ux * GEMV_UNIT_ROWS, bar);
-    } else if (lane == 1) {
-      tma_load_2d(dst + GF_META_OFF, &smap, tile * GEMV_TN, grow0, bar);
-    } else if (lane == 2) {
-      tma_load_2d(dst + GF_ZP_OFF, &zmap, tile * (GEMV_TN / 8), grow0, bar);
-    }
+  // The warp's units are u0 + warp + 16 n, n = 0, 1, ...; both issue streams below walk them in
+  // order and keep (tile, unit within tile) by stepping, so that no unit costs an integer division.
+  struct Cursor { int u, tile, ux; };
+  auto cursor_step = [&](Cursor& c) {
+    c.u += GF_WARPS; c.ux += GF_WARPS;
+    while (c.ux >= upt) { c.ux -= upt; ++c.tile; }
   };
-  // x of the same unit: every lane copies its 8 elements of every batch row, then arrives on the barrier
+  Cursor cw, cx;
+  cw.u = u0 + warp; cw.tile = cw.u / upt; cw.ux = cw.u - cw.tile * upt;
+  cx = cw;
+  // packed weights of this warp's n-th unit: one TMA copy, issued by lane 0
+  auto issue_w = [&](int n) {
+    if (cw.u >= u1) return;
+    if (lane == 0) {
+      uint64_t* bar = &my_full[n % GF_STAGES];
+      mbar_arrive_expect_tx(bar, GEMV_UNIT_BYTES);
+      tma_load_2d(my_stages + (size_t)(n % GF_STAGES) * STG, &wmap, cw.tile * GEMV_TN, cw.ux * GEMV_UNIT_ROWS, bar);
+    }
+    cursor_step(cw);
+  };
+  // x of the same unit (every lane copies its 8 elements of every batch row) and, on lanes 0..9, the
+  // unit's two group rows of scales (4 x 16 bytes each) and of packed zero points (16 bytes each);
+  // then every lane arrives on the barrier.  One TMA copy per unit instead of three: issuing a
+  // TMA copy occupies the issuing thread for some 200 cycles, an asynchronous 16-byte copy does not.
   auto issue_x = [&](int n) {
-    const int u = u0 + warp + GF_WARPS * n;
-    if (u >= u1) return;
-    const int ux = u % upt;
-    unsigned char* dst = my_stages + (size_t)(n % GF_STAGES) * STG + GF_X_OFF;
-    const int k = ux * 256 + 8 * lane;
+    if (cx.u >= u1) return;
+    unsigned char* stg = my_stages + (size_t)(n % GF_STAGES) * STG;
+    unsigned char* dst = stg + GF_X_OFF;
+    const int k = cx.ux * 256 + 8 * lane;
 #pragma unroll
     for (int r = 0; r < MR; ++r)
       cp_async16_zfill(dst + r * 512 + 16 * lane, p.x + (size_t)(r < p.M ? r : 0) * K + (k < K ? k : 0), r < p.M && k < K);
+    if (lane < 10) {
+      const int grow0 = sp.group_shift >= 0 ? ((cx.ux * GEMV_UNIT_STEPS) >> sp.group_shift) : (cx.ux * GEMV_UNIT_ROWS * 8) / gs;
+      const int row = grow0 + (lane < 8 ? (lane >> 2) : (lane - 8));
+      const bool ok = row < sp.n_groups;
+      const int rr = ok ? row : 0;
+      if (lane < 8) cp_async16_zfill(stg + GF_META_OFF + 16 * lane, p.scales + (size_t)rr * p.N + cx.tile * GEMV_TN + 8 * (lane & 3), ok);
+      else cp_async16_zfill(stg + GF_ZP_OFF + 16 * (lane - 8), p.qzeros + (size_t)rr * (p.N >> 3) + cx.tile * (GEMV_TN / 8), ok);
+    }
     cp_async_arrive_noinc(&my_full[n % GF_STAGES]);
+    cursor_step(cx);
   };
+  if (threadIdx.x == 0) trace_mark_ns(sp.trace, 48);
   issue_w(0);
   issue_w(1);                                            // weights never depend on an earlier kernel
+  if (threadIdx.x == 0) trace_mark_ns(sp.trace, 41);
   pdl_wait();                                            // x, y and the workspace belong to the stream order
+  if (threadIdx.x == 0) trace_mark_ns(sp.trace, 42);
   issue_x(0);
   issue_x(1);
   if (threadIdx.x == 0) trace_mark(sp.trace, 0);
@@ -641,7 +676,6 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
     named_bar_sync(1, GF_THREADS);
     const int tc0 = tile * GEMV_TN, col = lane;
     const bool whole = seg_first == 0 && seg_last == upt - 1;
-    const int c_first = unit_owner((long long)tile * upt, G, nu), c_last = unit_owner((long long)tile * upt + upt - 1, G, nu);
     float* part = sp.cta_part + ((size_t)blockIdx.x * 2 + (seg_first == 0 ? 1 : 0)) * 16 * GEMV_TN;
     for (int r = 0; r < p.M; ++r) {
       float v = 0.f;
@@ -652,6 +686,7 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
     }
     named_bar_arrive(2, GF_THREADS);
     if (whole) return;
+    const int c_first = unit_owner((long long)tile * upt, G, nu), c_last = unit_owner((long long)tile * upt + upt - 1, G, nu);
     __threadfence();
     __syncwarp();
     unsigned last = 0;
@@ -680,6 +715,7 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
         flags[0] = 1; atomicExch(sp.status, Q4_STATUS_WAIT_EXPIRED);
       }
       if (warp == 0 && lane == 0) trace_mark(sp.trace, 3 + 2 * n);
+      if (warp == 0 && lane == 0 && n == 0) trace_mark_ns(sp.trace, 43);
       unsigned char* stg = my_stages + (size_t)st * STG;
       // ---- x: rewrite this lane's 8 elements per batch row in MMA order, and the unit's sums of x ----
       float2* sums = reinterpret_cast<float2*>(stg + GF_X_OFF + MR * 512);      // [2 chunks][MR]
@@ -716,10 +752,10 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
             const uint32_t w8 = w[q] >> 8;
-            pr[q][0] = (w[q] & 0x000F000Fu) | 0x64006400u;
-            pr[q][1] = (w[q] & 0x00F000F0u) | 0x64006400u;
-            pr[q][2] = (w8 & 0x000F000Fu) | 0x64006400u;
-            pr[q][3] = (w8 & 0x00F000F0u) | 0x64006400u;
+            pr[q][0] = and_or(w[q], 0x000F000Fu, 0x64006400u);
+            pr[q][1] = and_or(w[q], 0x00F000F0u, 0x64006400u);
+            pr[q][2] = and_or(w8, 0x000F000Fu, 0x64006400u);
+            pr[q][3] = and_or(w8, 0x00F000F0u, 0x64006400u);
           }
           if (uu == 0) {
             mma16816_first(c[0][0], pr[0][0], pr[1][0], pr[0][1], pr[1][1], xv.x, xv.y);
@@ -763,8 +799,10 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
       if (warp == 0 && lane == 0) trace_mark(sp.trace, 4 + 2 * n);
     }
     if (threadIdx.x == 0) trace_mark(sp.trace, 30);
+    if (warp == GF_WARPS - 1 && lane == 0 && tile == tile_last) trace_mark_ns(sp.trace, 44);
     finish_tile(tile, tile - tile_first, max(u0, tile * upt) - tile * upt, seg_u1 - 1 - tile * upt);
     if (threadIdx.x == 0) trace_mark(sp.trace, 31);
+    if (warp == GF_WARPS - 1 && lane == 0 && tile == tile_last) trace_mark_ns(sp.trace, 45);
   }
 }
 
@@ -817,7 +855,7 @@ gemv_act_kernel(const GemvParams p, int G) {
     for (int q = 0; q < 4; ++q) {
 #pragma unroll
       for (int m = 0; m < 4; ++m) {
-        const uint32_t raw = ((w[q] >> (4 * m)) & 0x000F000Fu) | 0x64006400u;
+        const uint32_t raw = and_or(w[q] >> (4 * m), 0x000F000Fu, 0x64006400u);
         const __half2 qq = __hsub2(as_h2(raw), as_h2(0x64006400u));              // (q_m, q_m+4)
         const __half2 ta = tab[gi[m] * GEMV_TN + 4 * g + q], tb = tab[gi[m + 4] * GEMV_TN + 4 * g + q];
         const __half2 sv = __lows2half2(ta, tb), zv = __highs2half2(ta, tb);
@@ -977,6 +1015,20 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
     int grid = sm_count();
     if (grid > GEMV_MAX_CTAS) grid = GEMV_MAX_CTAS;
     if (grid > sp.total_units) grid = sp.total_units;
+    // Lean kernel: an even share of all units per CTA makes column tiles straddle CTAs, and the sums
+    // of a straddled tile meet through global memory (a fence, an atomic and a read back to back at
+    // the end of the CTA, about as long as six units take).  Dealing whole tiles avoids that at the
+    // price of an uneven load; take whichever ends sooner.
+    sp.whole_tiles = 0;
+    sp.n_groups = G;
+    {
+      const int tiles = N / GEMV_TN;
+      const long long cost_split = (sp.total_units + grid - 1) / grid + 12;
+      const int g2 = grid < tiles ? grid : tiles;
+      const long long cost_whole = (long long)((tiles + g2 - 1) / g2) * sp.units_per_tile;
+      if (cost_whole <= cost_split) sp.whole_tiles = 1;
+    }
+    const bool lean_ok = (long long)sp.total_units * grid < (1ll << 32);
     // group rows one unit (256 k-rows) can touch, counting a straddled group at either end
     sp.meta_rows = v1 ? 1 : (GEMV_UNIT_ROWS * 8 + groupsize - 1) / groupsize + ((GEMV_UNIT_ROWS * 8) % groupsize ? 1 : 0);
     if (sp.meta_rows > GEMV_META_ROWS) return fail(Q4_E_SHAPE, "gemv: groupsize=%d too small", groupsize);
@@ -996,8 +1048,11 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
       sp.stage_tx = GEMV_UNIT_BYTES + 2 * GEMV_TN * 2;
     }
     const bool fast = v1 || groupsize % 128 == 0;
-    if (!v1 && M <= 2 && (groupsize == 128 || groupsize % 256 == 0) && K % 128 == 0)   // lean kernel: x travels with the weights
+    if (lean_ok && !v1 && M <= 2 && (groupsize == 128 || groupsize % 256 == 0) && K % 128 == 0) {  // lean kernel: x travels with the weights
+      if (sp.whole_tiles && grid > N / GEMV_TN) grid = N / GEMV_TN;
       return M == 1 ? launch_fast<1>(map, smap, zmap, sp, grid, st) : launch_fast<2>(map, smap, zmap, sp, grid, st);
+    }
+    sp.whole_tiles = 0;
     const bool xs = fast && MT == 1 && K % 128 == 0 && (size_t)M * K * 2 + (size_t)(K / 128) * 64 <= (size_t)GEMV_XS_MAX_BYTES;
     if (xs) return launch_stream<1, true, true>(map, smap, zmap, sp, grid, st);
     if (MT == 1) return fast ? launch_stream<1, true, false>(map, smap, zmap, sp, grid, st) : launch_stream<1, false, false>(map, smap, zmap, sp, grid, st);
