@@ -96,6 +96,12 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
+# DRAM bytes (read + write) of one launch of the decode kernel, averaged over the three layer shapes:
+# dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture per shape (8,758,016 / 23,466,496 /
+# 23,480,064 bytes against 8,749,056 / 23,471,616 / 23,499,264 algorithmic; summary under profiles/).
+NCU_DRAM_BYTES_PER_LAUNCH = round((8758016 + 23466496 + 23480064) / 3)
+
+
 def make_pool(copies, device, seed):
     """``copies`` x 3 layers generated on the device (same distributions as synth.make_layer)."""
     gen = torch.Generator(device=device).manual_seed(seed)
@@ -327,7 +333,10 @@ def run_gemm(args, local_rank):
 
     M = 2048
     out = {"M": M, "peak_tflops": peak, "peak_kind": kind, "shapes": {}}
-    for K, N in [(5120, 5120), (5120, 13824), (13824, 5120)]:
+    shapes = [(5120, 5120), (5120, 13824), (13824, 5120)]
+    if getattr(args, "gemm_shape", ""):
+        shapes = [tuple(int(v) for v in args.gemm_shape.lower().split("x"))]
+    for K, N in shapes:
         G = K // 128
         qw = torch.randint(-2 ** 31, 2 ** 31 - 1, (K // 8, N), device=dev, dtype=torch.int64, generator=gen).to(torch.int32)
         zw = (torch.randint(0, 2 ** 31 - 1, (G, N // 8), device=dev, dtype=torch.int64, generator=gen) & 0x66666666).to(torch.int32)
@@ -441,6 +450,7 @@ def main():
     ap.add_argument("--copies", type=int, default=8, help="distinct copies of each layer shape per GPU")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-gemm", action="store_true", help="skip the M=2048 fused GEMM leg")
+    ap.add_argument("--gemm-shape", default="", help="restrict the GEMM leg to one KxN shape, e.g. 5120x13824 (for profiler captures)")
     ap.add_argument("--finetune-steps", type=int, default=5, help="timed LLaMA-7B LoRA finetune steps (0 = skip)")
     ap.add_argument("--finetune-eager", action="store_true", help="do not capture the finetune step as a CUDA graph")
     ap.add_argument("--finetune-layers", type=int, default=0, help="override the number of decoder layers (0 = 32)")
@@ -502,7 +512,8 @@ def main():
                 "warmup": args.warmup, "ms_per_step": round(r["ms"] / args.steps, 5), "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": config,
                 "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                             "frac": round(achieved / peak, 4), "traffic": None, "peak_kind": peak_kind,
+                             "frac": round(achieved / peak, 4), "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
+                             "algorithmic_bytes_per_launch": round(bps / r["n_launch"]), "peak_kind": peak_kind,
                              "kernel": "gemv_fast_kernel<1>", "avg_launch_us": round(per_launch_us, 3),
                              "frac_of_nominal_8000": round(achieved / 8000.0, 4)},
                 "per_shape": r["per_shape"],
