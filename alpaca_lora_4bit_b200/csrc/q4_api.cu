@@ -70,11 +70,24 @@ int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int
   if (!fn) return fail(Q4_E_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
   if (!aligned16(base) || row_pitch_bytes % 16 || (uint64_t)box_cols * elem_bytes % 16)
     return fail(Q4_E_ALIGN, "tensor map: base, row pitch and box width must be multiples of 16 bytes");
-  // The driver call needs this thread to have a current context; a thread that has only inherited
-  // the device setting (an autograd worker, say) binds the primary context with cudaSetDevice.
   int dev = 0;
   if (int e = check_cuda(cudaGetDevice(&dev), "cudaGetDevice")) return e;
-  if (int e = check_cuda(cudaSetDevice(dev), "cudaSetDevice")) return e;
+  // A descriptor depends only on the address and the geometry, not on the bytes behind it, and a
+  // decode step asks for the same few hundred descriptors token after token: keep the last ones
+  // of this thread (direct-mapped, keyed by everything that goes into the descriptor).
+  struct Entry { const void* base; uint64_t cols, rows, pitch; uint32_t box_cols, box_rows; int dt, swizzle, dev, valid; CUtensorMap map; };
+  constexpr int SLOTS = 512;
+  static thread_local Entry cache[SLOTS];
+  const size_t h = ((reinterpret_cast<uintptr_t>(base) >> 8) * 0x9E3779B97F4A7C15ull + cols * 31 + rows * 17 + box_rows) % SLOTS;
+  Entry& e = cache[h];
+  if (e.valid && e.base == base && e.cols == cols && e.rows == rows && e.pitch == row_pitch_bytes && e.box_cols == box_cols &&
+      e.box_rows == box_rows && e.dt == (int)dt && e.swizzle == (int)swizzle && e.dev == dev) {
+    *out = e.map;
+    return Q4_OK;
+  }
+  // The driver call needs this thread to have a current context; a thread that has only inherited
+  // the device setting (an autograd worker, say) binds the primary context with cudaSetDevice.
+  if (int err = check_cuda(cudaSetDevice(dev), "cudaSetDevice")) return err;
   cuuint64_t dims[2] = {cols, rows};
   cuuint64_t strides[1] = {row_pitch_bytes};
   cuuint32_t box[2] = {box_cols, box_rows};
@@ -82,6 +95,8 @@ int make_tmap_2d(CUtensorMap* out, const void* base, CUtensorMapDataType dt, int
   CUresult r = fn(out, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(Q4_E_CUDA, "cuTensorMapEncodeTiled failed with CUresult %d", (int)r);
+  e.base = base; e.cols = cols; e.rows = rows; e.pitch = row_pitch_bytes; e.box_cols = box_cols; e.box_rows = box_rows;
+  e.dt = (int)dt; e.swizzle = (int)swizzle; e.dev = dev; e.map = *out; e.valid = 1;
   return Q4_OK;
 }
 

@@ -1036,6 +1036,13 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
     CUtensorMap map, smap, zmap;
     if (int e = make_tmap_2d(&map, qweight, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, (uint64_t)N, (uint64_t)(K / 8),
                              (uint64_t)N * 4, GEMV_TN, GEMV_UNIT_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
+    if (lean_ok && !v1 && M <= 2 && (groupsize == 128 || groupsize % 256 == 0) && K % 128 == 0) {
+      // lean kernel: x, scales and zero points travel with the weights by 16-byte asynchronous copies,
+      // so the weights are the only tensor map it uses
+      if (sp.whole_tiles && grid > N / GEMV_TN) grid = N / GEMV_TN;
+      return M == 1 ? launch_fast<1>(map, map, map, sp, grid, st) : launch_fast<2>(map, map, map, sp, grid, st);
+    }
+    sp.whole_tiles = 0;
     if (int e = make_tmap_2d(&smap, scales, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (uint64_t)N, (uint64_t)G,
                              (uint64_t)N * 2, GEMV_TN, sp.meta_rows, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
     if (!v1) {
@@ -1048,11 +1055,6 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
       sp.stage_tx = GEMV_UNIT_BYTES + 2 * GEMV_TN * 2;
     }
     const bool fast = v1 || groupsize % 128 == 0;
-    if (lean_ok && !v1 && M <= 2 && (groupsize == 128 || groupsize % 256 == 0) && K % 128 == 0) {  // lean kernel: x travels with the weights
-      if (sp.whole_tiles && grid > N / GEMV_TN) grid = N / GEMV_TN;
-      return M == 1 ? launch_fast<1>(map, smap, zmap, sp, grid, st) : launch_fast<2>(map, smap, zmap, sp, grid, st);
-    }
-    sp.whole_tiles = 0;
     const bool xs = fast && MT == 1 && K % 128 == 0 && (size_t)M * K * 2 + (size_t)(K / 128) * 64 <= (size_t)GEMV_XS_MAX_BYTES;
     if (xs) return launch_stream<1, true, true>(map, smap, zmap, sp, grid, st);
     if (MT == 1) return fast ? launch_stream<1, true, false>(map, smap, zmap, sp, grid, st) : launch_stream<1, false, false>(map, smap, zmap, sp, grid, st);

@@ -113,6 +113,40 @@ def gemv(x, qweight, y, scales, zeros, g_idx, groupsize, flags, bias=None) -> No
                 _lib.check(rc, "gemv")
 
 
+_decode_ws: dict = {}          # (device index, stream handle) -> (pointer, bytes, tensor)
+
+
+def decode_v2(x, qweight, scales, zeros, groupsize):
+    """``x @ W`` for at most 16 rows on a v2 layer with sequential groups, result in a new fp16 tensor.
+
+    The per-token call of generation: the caller (``matmul_utils_4bit.matmul4bit``) has already
+    established that ``x`` is a contiguous 2-D fp16 CUDA tensor and ``scales`` fp16, so what is left
+    here is what protects memory - the shapes must describe one layer - and the foreign call."""
+    M, K = x.shape
+    R, N = qweight.shape
+    G = scales.shape[0]
+    if R * 8 != K or scales.shape[1] != N or zeros.shape[0] != G or zeros.shape[1] * 8 != N or M > 16:
+        raise RuntimeError(f"quant_cuda: shapes x{tuple(x.shape)} mat{tuple(qweight.shape)} scales{tuple(scales.shape)} "
+                           f"zeros{tuple(zeros.shape)} do not describe one layer")
+    dev = x.device
+    idx = dev.index
+    if idx != torch.cuda.current_device() or not (qweight.is_contiguous() and scales.is_contiguous() and zeros.is_contiguous()):
+        y = torch.empty((M, N), dtype=torch.float16, device=dev)
+        gemv(x, qweight.contiguous(), y, scales.contiguous(), zeros.contiguous(), None, groupsize, 0)
+        return y
+    y = torch.empty((M, N), dtype=torch.float16, device=dev)
+    st = torch.cuda.current_stream(dev).cuda_stream
+    w = _decode_ws.get((idx, st))
+    if w is None:
+        t = _lib.workspace_for(dev, st)
+        w = _decode_ws[(idx, st)] = (t.data_ptr(), t.numel(), t)
+    rc = _lib.lib().q4_gemv(x.data_ptr(), qweight.data_ptr(), y.data_ptr(), scales.data_ptr(), zeros.data_ptr(), None, None,
+                            M, K, N, G, groupsize, _lib.Q4_F16, 0, w[0], w[1], st)
+    if rc:
+        _lib.check(rc, "gemv")
+    return y
+
+
 _gemm_ws_bytes: dict = {}
 
 
