@@ -237,6 +237,23 @@ def test_facade_matmul_variants_add_into_mul():
     assert rel_fro(y, want) <= REL_TOL
 
 
+@pytest.mark.parametrize("M", [1, 2])
+@pytest.mark.parametrize("K,N", [(4096, 5120), (1024, 5120), (2048, 9600), (512, 4768)])
+def test_gemv_work_dealing_modes(K, N, M):
+    """Column-tile counts just above the SM count (160, 300 and 149 tiles on a 148-SM part), where the
+    lean kernel chooses between whole tiles per CTA and an even split of all units whose straddled
+    tiles meet in the workspace.  Twice on the same workspace: the counters must come back to zero."""
+    layer = synth.make_layer(K, N, 128, False, seed=K + N)
+    x = synth.make_acts(M, K, seed=M + 5)
+    want = orc.gemv_fp32(x, layer.qweight, layer.scales, layer.qzeros, layer.g_idx)
+    first = gemv_gpu(layer, x, torch.float32)
+    again = gemv_gpu(layer, x, torch.float32)
+    assert rel_fro(first, want) <= REL_TOL
+    assert torch.equal(first, again)
+    for ws in _lib._workspaces.values():
+        assert int(ws[:65536].view(torch.int32).abs().sum()) == 0
+
+
 def test_workspace_counters_return_to_zero():
     layer = synth.make_layer(4096, 4096, 128, False, seed=3)
     gemv_gpu(layer, synth.make_acts(1, 4096), torch.float16)
