@@ -317,7 +317,8 @@ __global__ void zp_table_kernel(const __half* __restrict__ scales, const uint32_
   reinterpret_cast<uint4*>(out)[i] = zero_terms(s, __ldg(qzeros + i));
 }
 
-static int g_gemm_variant = 0;                // 0 = choose per shape, 1 = single-CTA kernel, 2 = CTA-pair kernel
+static int g_gemm_variant = 0;                // 0 = choose per shape, 1 = single-CTA kernel, 2 = CTA-pair kernel with 256-row tiles,
+                                              // 3 = CTA-pair kernel with 512-row tiles
 
 static size_t gemm_smem_bytes(bool transpose, int G, int stages) {
   return 1024 + (size_t)stages * GM_STAGE_BYTES + 256 + (transpose ? 0 : (size_t)2 * G * GM_TILE_N * sizeof(__half));
@@ -344,15 +345,19 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
   if (workspace && !aligned16(workspace)) return fail(Q4_E_ALIGN, "gemm: the workspace must be 16-byte aligned");
   if (int e = check_device()) return e;
   const int contract = transpose ? N : K, nout = transpose ? K : N;
-  const int stages2 = gemm2_stages(transpose, G);
+  const int stages2 = gemm2_stages(transpose, G, 1), stages2w = gemm2_stages(transpose, G, 2);
   const bool pair_ok = nout % G2_TILE_N == 0 && stages2 > 0;
-  if (g_gemm_variant == 2 && !pair_ok)
+  const bool wide_ok = nout % G2_TILE_N == 0 && stages2w > 0;
+  if ((g_gemm_variant == 2 && !pair_ok) || (g_gemm_variant == 3 && !wide_ok))
     return fail(Q4_E_SHAPE, "gemm: the CTA-pair kernel needs %d output columns to be a multiple of 256 and G=%d tables to fit", nout, G);
-  const bool use_pair = pair_ok && g_gemm_variant != 1;
+  const bool use_pair = (pair_ok && g_gemm_variant != 1) || g_gemm_variant == 3;
+  // 512-row tiles halve the dequant work per flop; they pay off as soon as there is more than one
+  // 256-row tile of rows
+  const int mh = use_pair && ((g_gemm_variant == 0 && wide_ok && M > 256) || g_gemm_variant == 3) ? 2 : 1;
   int stages = GM_MAX_STAGES;
   while (stages > 2 && gemm_smem_bytes(transpose, G, stages) > 227 * 1024) --stages;
-  if (use_pair) stages = stages2;
-  const size_t smem = use_pair ? gemm2_smem_bytes(transpose, G, stages) : gemm_smem_bytes(transpose, G, stages);
+  if (use_pair) stages = mh == 2 ? stages2w : stages2;
+  const size_t smem = use_pair ? gemm2_smem_bytes(transpose, G, stages, mh) : gemm_smem_bytes(transpose, G, stages);
   if (smem > 227 * 1024) return fail(Q4_E_SHAPE, "gemm: scale tables for G=%d groups do not fit shared memory", G);
 
   GemmParams p;
@@ -365,7 +370,7 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
   p.lora_w = lora_r > 0 ? (const __half*)lora_w : nullptr;
   p.lora_r = lora_r;
   p.n_whole = 0; p.split_f = 1; p.split_sps = 0; p.split_inv = 65536; p.ws_partials = nullptr; p.ws_counters = nullptr; p.zp_table = nullptr;
-  const int box_rows = use_pair ? 128 : GM_TILE_M;    // activation rows one TMA copy brings
+  const int box_rows = use_pair ? 128 * mh : GM_TILE_M;    // activation rows one TMA copy brings
   CUtensorMap amap;
   if (int e = make_tmap_2d(&amap, act, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)contract, (uint64_t)M,
                            (uint64_t)contract * 2, GM_TILE_C, box_rows, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
@@ -384,12 +389,15 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
   const int tr = transpose ? 1 : 0;
   if (!attr_done[use_pair ? 1 : 0][tr][dev]) {
     const int cap = 227 * 1024;
-    const void* fn = use_pair ? (transpose ? (const void*)q4_gemm2_kernel<true, false> : (const void*)q4_gemm2_kernel<false, false>)
+    const void* fn = use_pair ? (transpose ? (const void*)q4_gemm2_kernel<true, false, 1> : (const void*)q4_gemm2_kernel<false, false, 1>)
                               : (transpose ? (const void*)q4_gemm_kernel<true> : (const void*)q4_gemm_kernel<false>);
     if (int e = check_cuda(cudaFuncSetAttribute(fn, cudaFuncAttributeMaxDynamicSharedMemorySize, cap), "gemm smem attribute")) return e;
     if (use_pair) {
-      const void* fn_split = transpose ? (const void*)q4_gemm2_kernel<true, true> : (const void*)q4_gemm2_kernel<false, true>;
-      if (int e = check_cuda(cudaFuncSetAttribute(fn_split, cudaFuncAttributeMaxDynamicSharedMemorySize, cap), "gemm smem attribute")) return e;
+      const void* more[3] = {transpose ? (const void*)q4_gemm2_kernel<true, true, 1> : (const void*)q4_gemm2_kernel<false, true, 1>,
+                             transpose ? (const void*)q4_gemm2_kernel<true, false, 2> : (const void*)q4_gemm2_kernel<false, false, 2>,
+                             transpose ? (const void*)q4_gemm2_kernel<true, true, 2> : (const void*)q4_gemm2_kernel<false, true, 2>};
+      for (const void* f2 : more)
+        if (int e = check_cuda(cudaFuncSetAttribute(f2, cudaFuncAttributeMaxDynamicSharedMemorySize, cap), "gemm smem attribute")) return e;
     }
     if (use_pair) {
       cudaLaunchConfig_t cfg = {};
@@ -405,7 +413,8 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
     attr_done[use_pair ? 1 : 0][tr][dev] = true;
   }
   if (use_pair) {
-    const int n_tiles = (nout / G2_TILE_N) * ((M + G2_TILE_M - 1) / G2_TILE_M);
+    const int tile_m = 256 * mh;
+    const int n_tiles = (nout / G2_TILE_N) * ((M + tile_m - 1) / tile_m);
     const int P = max_pairs[tr][dev], T = p.n_contract_tiles;
     unsigned char* ws = (unsigned char*)workspace;
     size_t ws_off = Q4_GEMM_WS_COUNTER_BYTES;
@@ -427,7 +436,7 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
       if (f > T / 4) f = T / 4;
       sps = (T + f - 1) / f;
       f = (T + sps - 1) / sps;                       // no empty slice
-      if (f < 2 || workspace_bytes < ws_off + (size_t)rem * f * Q4_GEMM_WS_SLICE_BYTES) { f = 1; sps = T; }
+      if (f < 2 || workspace_bytes < ws_off + (size_t)rem * f * mh * Q4_GEMM_WS_SLICE_BYTES) { f = 1; sps = T; }
     }
     p.split_f = f; p.split_sps = sps; p.split_inv = (65536 + f - 1) / f;
     p.n_whole = f > 1 ? n_tiles - rem : n_tiles;
@@ -436,13 +445,15 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
     const int n_items = p.n_whole + (n_tiles - p.n_whole) * f;
     const int pairs = n_items < P ? n_items : P;
     const dim3 grid(2 * pairs), block(G2_THREADS);
-    if (f > 1) {
-      if (transpose) q4_gemm2_kernel<true, true><<<grid, block, smem, st>>>(amap, umap, p);
-      else q4_gemm2_kernel<false, true><<<grid, block, smem, st>>>(amap, umap, p);
+#define Q4_LAUNCH2(TR, SP, MHV) q4_gemm2_kernel<TR, SP, MHV><<<grid, block, smem, st>>>(amap, umap, p)
+    if (mh == 2) {
+      if (f > 1) { if (transpose) Q4_LAUNCH2(true, true, 2); else Q4_LAUNCH2(false, true, 2); }
+      else { if (transpose) Q4_LAUNCH2(true, false, 2); else Q4_LAUNCH2(false, false, 2); }
     } else {
-      if (transpose) q4_gemm2_kernel<true, false><<<grid, block, smem, st>>>(amap, umap, p);
-      else q4_gemm2_kernel<false, false><<<grid, block, smem, st>>>(amap, umap, p);
+      if (f > 1) { if (transpose) Q4_LAUNCH2(true, true, 1); else Q4_LAUNCH2(false, true, 1); }
+      else { if (transpose) Q4_LAUNCH2(true, false, 1); else Q4_LAUNCH2(false, false, 1); }
     }
+#undef Q4_LAUNCH2
   } else {
     const dim3 grid(nout / GM_TILE_N, (M + GM_TILE_M - 1) / GM_TILE_M), block(GM_THREADS);
     if (transpose) q4_gemm_kernel<true><<<grid, block, smem, st>>>(amap, umap, p);
@@ -454,7 +465,7 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
 extern "C" size_t q4_gemm_workspace_bytes(int K, int N, int G) {
   if (K <= 0 || N <= 0 || G <= 0) return 0;
   const size_t zp_bytes = ((size_t)G * N * sizeof(__half) + 255) & ~(size_t)255;
-  return Q4_GEMM_WS_COUNTER_BYTES + zp_bytes + (size_t)80 * Q4_GEMM_WS_SLICE_BYTES;
+  return Q4_GEMM_WS_COUNTER_BYTES + zp_bytes + (size_t)80 * 2 * Q4_GEMM_WS_SLICE_BYTES;
 }
 
 extern "C" int q4_gemm_fwd(const void* x, const int32_t* qweight, void* y, const void* scales, const int32_t* qzeros,
@@ -470,7 +481,7 @@ extern "C" int q4_gemm_bwd(const void* dy, const int32_t* qweight, void* dx, con
 }
 
 extern "C" int q4_gemm_set_variant(int variant) {
-  if (variant < 0 || variant > 2) return fail(Q4_E_BADARG, "gemm_set_variant: %d is not 0 (choose per shape), 1 (single CTA) or 2 (CTA pair)", variant);
+  if (variant < 0 || variant > 3) return fail(Q4_E_BADARG, "gemm_set_variant: %d is not 0 (choose per shape), 1 (single CTA), 2 (CTA pair, 256-row tiles) or 3 (CTA pair, 512-row tiles)", variant);
   g_gemm_variant = variant;
   return Q4_OK;
 }

@@ -23,10 +23,8 @@
 namespace q4 {
 
 constexpr int G2_TILE_N = 256;                // output columns per pair (128 dequantised per CTA)
-constexpr int G2_TILE_M = 256;                // output rows per pair (128 per CTA)
-constexpr int G2_A_BYTES = 128 * GM_TILE_C * 2;           // 16 KiB: this CTA's rows of the stage
+constexpr int G2_HALF_BYTES = 128 * GM_TILE_C * 2;        // 16 KiB: 128 activation rows of one stage
 constexpr int G2_B_BYTES = 128 * 64 * 2;                  // 16 KiB: this CTA's columns of the stage
-constexpr int G2_STAGE_BYTES = G2_A_BYTES + G2_B_BYTES;
 constexpr int G2_MAX_STAGES = 6;
 constexpr int G2_THREADS = 512;
 constexpr int G2_TMEM_COLS = 512;             // two accumulators of 256 fp32 columns
@@ -90,12 +88,19 @@ __device__ __forceinline__ WorkItem work_item(const GemmParams& p, int i, int T)
 // SPLIT = false: every work item is a whole tile and the item decode folds away (the loop bounds of
 // the dequant loop are then kernel-wide constants, which the register allocation of that loop is
 // sensitive to); SPLIT = true: the launch has tail tiles cut along the contraction.
-template <bool TRANSPOSE, bool SPLIT>
+// MH = 1: 256-row tiles (128 rows per CTA) and two TMEM accumulators, so that the epilogue of a tile
+// overlaps the MMAs of the next.  MH = 2: 512-row tiles (256 rows per CTA, two MMAs per 16
+// contraction elements on the same dequantised operand): half the dequant work per flop, which is
+// what bounds the MH = 1 form; both accumulators belong to the one tile in flight.
+template <bool TRANSPOSE, bool SPLIT, int MH>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
 q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap umap, const GemmParams p) {
   extern __shared__ unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);      // 1024-byte aligned, still a shared-space pointer
   unsigned char* stages = smem;
+  constexpr int G2_A_BYTES = MH * G2_HALF_BYTES;       // this CTA's activation rows of a stage
+  constexpr int G2_STAGE_BYTES = G2_A_BYTES + G2_B_BYTES;
+  constexpr int G2_TILE_M = 256 * MH;                  // output rows per pair
   const int S = p.stages;
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + S * G2_STAGE_BYTES);     // even CTA: activation bytes + 4 dequant warps, of both CTAs
   uint64_t* empty = full + 8;                                                   // both CTAs: stage read by the MMAs
@@ -143,7 +148,7 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
       const uint32_t full0 = mapa_u32(smem_u32(full), 0);
       for (int item = pair; item < n_items; item += n_pairs) {
         const WorkItem wi = work_item<SPLIT>(p, item, T);
-        const int m0 = (wi.tile % m_tiles) * G2_TILE_M + 128 * (int)rank;
+        const int m0 = (wi.tile % m_tiles) * G2_TILE_M + 128 * MH * (int)rank;
         const int nst = wi.ke - wi.kb + (wi.lora ? 1 : 0);
         for (int j = 0; j < nst; ++j) {
           const int it = wi.kb + j;
@@ -175,10 +180,11 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
       for (int item = pair; item < n_items; item += n_pairs, ++tl) {
         const WorkItem wi = work_item<SPLIT>(p, item, T);
         const int nst = wi.ke - wi.kb + (wi.lora ? 1 : 0), ncon = wi.ke - wi.kb;
-        const int acc = tl & 1, acc_use = tl >> 1;
+        const int acc = MH == 1 ? (tl & 1) : 0, acc_use = MH == 1 ? (tl >> 1) : tl;
         if (acc_use > 0) wait_bar_cluster(&acc_empty[acc], (acc_use - 1) & 1, abort_flag);
         tc_fence_after();
         const uint32_t d_tmem = tmem_acc + acc * 256;
+        constexpr uint64_t H_STEP = G2_HALF_BYTES >> 4;   // next 128 activation rows of the stage
         const bool tron = p.trace != nullptr && tl == 1;
         for (int it = 0; it < nst; ++it) {
           if (tron && it < 12) gm_mark(p.trace, 5 * it);
@@ -186,12 +192,16 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
           if (tron && it < 12) gm_mark(p.trace, 5 * it + 2);
           tc_fence_after();
           if (it < ncon) {
-            umma_f16_pair(d_tmem, ad, bd, idesc, it > 0 ? 1u : 0u);
-            umma_f16_pair(d_tmem, ad + A_STEP, bd + B_STEP, idesc, 1u);
-            umma_f16_pair(d_tmem, ad + 2 * A_STEP, bd + 2 * B_STEP, idesc, 1u);
-            umma_f16_pair(d_tmem, ad + 3 * A_STEP, bd + 3 * B_STEP, idesc, 1u);
+#pragma unroll
+            for (int ks = 0; ks < 4; ++ks)
+#pragma unroll
+              for (int h = 0; h < MH; ++h)
+                umma_f16_pair(d_tmem + h * 256, ad + ks * A_STEP + h * H_STEP, bd + ks * B_STEP, idesc, (it > 0 || ks > 0) ? 1u : 0u);
           } else {
-            for (int ks = 0; ks < lora_ks; ++ks) umma_f16_pair(d_tmem, ad + ks * A_STEP, bd + ks * B_STEP, idesc, 1u);
+            for (int ks = 0; ks < lora_ks; ++ks)
+#pragma unroll
+              for (int h = 0; h < MH; ++h)
+                umma_f16_pair(d_tmem + h * 256, ad + ks * A_STEP + h * H_STEP, bd + ks * B_STEP, idesc, 1u);
           }
           if (tron && it < 12) gm_mark(p.trace, 5 * it + 3);
           umma_commit_pair(&empty[st]);                // frees the stage in both CTAs
@@ -339,9 +349,9 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
     unsigned polls = 0;
     for (int item = pair; item < n_items; item += n_pairs, ++tl) {
       const WorkItem wi = work_item<SPLIT>(p, item, T);
-      const int acc = tl & 1, acc_use = tl >> 1;
+      const int acc = MH == 1 ? (tl & 1) : 0, acc_use = MH == 1 ? (tl >> 1) : tl;
       const int col0 = (wi.tile / m_tiles) * G2_TILE_N;
-      const int m = (wi.tile % m_tiles) * G2_TILE_M + 128 * (int)rank + 32 * quarter + lane;
+      int m = 0;                                                     // output row of this thread, set per accumulator below
       // 32 fp32 sums of row m, columns col0 + 32 cb ..: (+bias) -> fp16 -> global
       auto emit = [&](int cb, const uint32_t (&v)[32]) {
         if (m >= p.M) return;
@@ -367,30 +377,38 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
       __syncwarp();
       tc_fence_after();
       if (threadIdx.x == 384 && tl < 8) gm_mark(p.trace, 201 + 3 * tl);
-      // Partial sums of a slice: this warp's 32 rows x 256 columns as [cb][j][lane][4 floats], so that
-      // every 16-byte access of the warp is one contiguous 512 bytes.
+      // Partial sums of a slice: this warp's 32 rows x 256 columns of accumulator h as
+      // [cb][j][lane][4 floats], so that every 16-byte access of the warp is one contiguous 512 bytes.
+      // Blocks are indexed [tail tile][slice][CTA of the pair][accumulator][lane quarter].
       const size_t part_floats = 8 * 8 * 32 * 4;
-      float* part = wi.split ? p.ws_partials + ((((size_t)wi.tail * p.split_f + wi.slice) * 2 + rank) * 4 + quarter) * part_floats : nullptr;
+      auto part_of = [&](int slice, int h) -> float* {
+        return p.ws_partials + (((((size_t)wi.tail * p.split_f + slice) * 2 + rank) * MH + h) * 4 + quarter) * part_floats;
+      };
 #pragma unroll 1
-      for (int cb = 0; cb < G2_TILE_N / 32; ++cb) {
-        uint32_t v[32];
-        tmem_ld32(tmem_acc + ((uint32_t)(32 * quarter) << 16) + acc * 256 + cb * 32, v);
-        tmem_ld_wait();
-        if (!wi.split) {
-          emit(cb, v);
-        } else {
+      for (int h = 0; h < MH; ++h) {
+        m = (wi.tile % m_tiles) * G2_TILE_M + 128 * MH * (int)rank + 128 * h + 32 * quarter + lane;
+        float* part = wi.split ? part_of(wi.slice, h) : nullptr;
+#pragma unroll 1
+        for (int cb = 0; cb < G2_TILE_N / 32; ++cb) {
+          uint32_t v[32];
+          tmem_ld32(tmem_acc + ((uint32_t)(32 * quarter) << 16) + (acc + h) * 256 + cb * 32, v);
+          tmem_ld_wait();
+          if (!wi.split) {
+            emit(cb, v);
+          } else {
 #pragma unroll
-          for (int j = 0; j < 8; ++j)
-            *reinterpret_cast<uint4*>(part + ((cb * 8 + j) * 32 + lane) * 4) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            for (int j = 0; j < 8; ++j)
+              *reinterpret_cast<uint4*>(part + ((cb * 8 + j) * 32 + lane) * 4) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          }
         }
       }
-      // this warp has read its part of the accumulator: the even CTA may overwrite it
+      // this warp has read its part of the accumulator(s): the even CTA may overwrite them
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc_empty0 + 8 * acc);
       if (wi.split) {
-        // The warp that arrives last at the counter of these 32 rows adds the slices up in slice
-        // order (the same order whoever it is), writes the rows and leaves the counter at zero.
+        // The warp that arrives last at the counter of these rows adds the slices up in slice order
+        // (the same order whoever it is), writes the rows and leaves the counter at zero.
         unsigned* cnt = p.ws_counters + ((size_t)wi.tail * 2 + rank) * 4 + quarter;
         __threadfence();
         __syncwarp();
@@ -399,24 +417,27 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         last = __shfl_sync(0xffffffffu, last, 0);
         if (last) {
           __threadfence();
-          const float* base = p.ws_partials + (((size_t)wi.tail * p.split_f * 2 + rank) * 4 + quarter) * part_floats;
 #pragma unroll 1
-          for (int cb = 0; cb < G2_TILE_N / 32; ++cb) {
-            float sum[32];
+          for (int h = 0; h < MH; ++h) {
+            m = (wi.tile % m_tiles) * G2_TILE_M + 128 * MH * (int)rank + 128 * h + 32 * quarter + lane;
+#pragma unroll 1
+            for (int cb = 0; cb < G2_TILE_N / 32; ++cb) {
+              float sum[32];
 #pragma unroll
-            for (int e = 0; e < 32; ++e) sum[e] = 0.f;
-            for (int sl = 0; sl < p.split_f; ++sl) {
-              const float* src = base + (size_t)sl * 2 * 4 * part_floats;
+              for (int e = 0; e < 32; ++e) sum[e] = 0.f;
+              for (int sl = 0; sl < p.split_f; ++sl) {
+                const float* src = part_of(sl, h);
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const float4 t = __ldcg(reinterpret_cast<const float4*>(src + ((cb * 8 + j) * 32 + lane) * 4));
-                sum[4 * j] += t.x; sum[4 * j + 1] += t.y; sum[4 * j + 2] += t.z; sum[4 * j + 3] += t.w;
+                for (int j = 0; j < 8; ++j) {
+                  const float4 t = __ldcg(reinterpret_cast<const float4*>(src + ((cb * 8 + j) * 32 + lane) * 4));
+                  sum[4 * j] += t.x; sum[4 * j + 1] += t.y; sum[4 * j + 2] += t.z; sum[4 * j + 3] += t.w;
+                }
               }
-            }
-            uint32_t v[32];
+              uint32_t v[32];
 #pragma unroll
-            for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(sum[e]);
-            emit(cb, v);
+              for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(sum[e]);
+              emit(cb, v);
+            }
           }
           if (lane == 0) *cnt = 0;
         }
@@ -432,14 +453,14 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
   if (warp == 1) tmem_dealloc_pair(tmem_acc, G2_TMEM_COLS);
 }
 
-static size_t gemm2_smem_bytes(bool transpose, int G, int stages) {
-  return 1024 + (size_t)stages * G2_STAGE_BYTES + G2_BAR_BYTES + (transpose ? 0 : (size_t)2 * G * 128 * sizeof(__half));
+static size_t gemm2_smem_bytes(bool transpose, int G, int stages, int mh) {
+  return 1024 + (size_t)stages * (mh * G2_HALF_BYTES + G2_B_BYTES) + G2_BAR_BYTES + (transpose ? 0 : (size_t)2 * G * 128 * sizeof(__half));
 }
 
 // Pipeline depth the pair kernel gets for this layer (0 = its tables do not leave room for three stages).
-static int gemm2_stages(bool transpose, int G) {
+static int gemm2_stages(bool transpose, int G, int mh) {
   int stages = G2_MAX_STAGES;
-  while (stages > 2 && gemm2_smem_bytes(transpose, G, stages) > 227 * 1024) --stages;
+  while (stages > 2 && gemm2_smem_bytes(transpose, G, stages, mh) > 227 * 1024) --stages;
   return stages >= 3 ? stages : 0;
 }
 

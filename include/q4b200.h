@@ -148,8 +148,9 @@ int q4_gemv_set_trace(void* device_buffer);
 int q4_gemm_set_trace(void* device_buffer);
 /* Which fused GEMM kernel q4_gemm_fwd / q4_gemm_bwd launch (process-wide; no reference counterpart):
  * 0 = choose per shape (the default: the CTA-pair kernel when the number of output columns is a
- * multiple of 256, else the single-CTA kernel), 1 = always the single-CTA kernel, 2 = always the
- * CTA-pair kernel (calls it cannot serve then fail with Q4_E_SHAPE).  For tests and measurements. */
+ * multiple of 256 - with 512-row tiles when M > 256, else 256-row tiles - and the single-CTA kernel
+ * otherwise), 1 = always the single-CTA kernel, 2 / 3 = always the CTA-pair kernel with 256- /
+ * 512-row tiles (calls it cannot serve then fail with Q4_E_SHAPE).  For tests and measurements. */
 int q4_gemm_set_variant(int variant);
 
 #ifdef __cplusplus

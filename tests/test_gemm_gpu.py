@@ -159,20 +159,22 @@ def gemm_variant():
 @pytest.mark.parametrize("transpose", [False, True])
 @pytest.mark.parametrize("M,K,N,g,act", [(700, 1024, 768, 128, True), (256, 256, 256, 64, False), (5, 512, 1280, 128, True)])
 def test_both_gemm_kernels_against_oracle(gemm_variant, M, K, N, g, act, transpose):
-    """The single-CTA kernel and the CTA-pair kernel on the same inputs (shapes both can serve)."""
+    """The single-CTA kernel and the CTA-pair kernel (256- and 512-row tiles) on the same inputs."""
     layer = synth.make_layer(K, N, g, act, seed=M + N)
     x = synth.make_acts(M, N if transpose else K, seed=M + 1)
     want = orc.matmul4bit_ref(x, layer.qweight, layer.scales, layer.qzeros, layer.g_idx, transpose=transpose)
     outs = []
-    for variant in (1, 2):
+    for variant in (1, 2, 3):
         gemm_variant(variant)
         outs.append(run_gemm(layer, x, transpose).clone())
         assert rel_fro(outs[-1], want) <= REL_TOL
     assert rel_fro(outs[0], outs[1]) <= 5e-4               # same products, different accumulation grouping at most
+    assert rel_fro(outs[0], outs[2]) <= 5e-4
 
 
+@pytest.mark.parametrize("variant", [2, 3])
 @pytest.mark.parametrize("transpose", [False, True])
-def test_pair_kernel_many_tiles_per_pair(gemm_variant, transpose):
+def test_pair_kernel_many_tiles_per_pair(gemm_variant, transpose, variant):
     """More than five 256 x 256 tiles per CTA pair: both accumulators and every pipeline stage are
     reused several times (the barrier phases wrap), with the low-rank stage making the stage count odd."""
     K, N, M, r = (256, 12288, 2048, 16) if not transpose else (12288, 256, 2048, 16)
@@ -187,7 +189,7 @@ def test_pair_kernel_many_tiles_per_pair(gemm_variant, transpose):
         u = ((x.float() @ A.float().t()) * 2.0).half()
         want, lw = x.float() @ w + u.float() @ B.float().t(), B
     L = layer.to(DEV)
-    gemm_variant(2)
+    gemm_variant(variant)
     out = torch.empty((M, K if transpose else N), dtype=torch.float16, device=DEV)
     quant_cuda.gemm(x.to(DEV), L.qweight, out, L.scales, L.qzeros, L.g_idx, transpose=transpose,
                     lora_u=torch.nn.functional.pad(u, (0, 64 - r)).to(DEV), lora_w=lw.contiguous().to(DEV))
@@ -196,9 +198,10 @@ def test_pair_kernel_many_tiles_per_pair(gemm_variant, transpose):
     assert rel_fro(out, want) <= REL_TOL
 
 
+@pytest.mark.parametrize("variant", [2, 3])
 @pytest.mark.parametrize("transpose", [False, True])
 @pytest.mark.parametrize("act", [False, True])
-def test_tail_tiles_split_along_the_contraction(gemm_variant, transpose, act):
+def test_tail_tiles_split_along_the_contraction(gemm_variant, transpose, act, variant):
     """20 output tiles on 74 SM pairs: with a workspace every tile is cut into slices whose partial
     sums are added in a fixed order (bit-identical from call to call, workspace left clean); without
     one the tiles are computed whole.  Both against the oracle, bias and low-rank term included."""
@@ -218,7 +221,7 @@ def test_tail_tiles_split_along_the_contraction(gemm_variant, transpose, act):
     L = layer.to(DEV)
     xd, ud, lwd = x.to(DEV), torch.nn.functional.pad(u, (0, 64 - r)).to(DEV), lw.contiguous().to(DEV)
     bd = None if bias is None else bias.to(DEV)
-    gemm_variant(2)
+    gemm_variant(variant)
     outs = []
     for _ in range(2):
         out = torch.empty((M, K if transpose else N), dtype=torch.float16, device=DEV)
