@@ -61,11 +61,9 @@ struct GemmParams {
   //   backward  dx += V * lora_A,    V = scale * dy * lora_B    [M, 64] (zero-padded),  lora_w = lora_A [r, K]
   const __half* lora_w;
   int lora_r;
-  // CTA-pair kernel only.  Work items 0 .. n_whole-1 are whole output tiles; each remaining ("tail")
-  // tile is cut into split_f slices of split_sps contraction stages whose fp32 partial sums meet in
-  // ws_partials (split_f = 1: no cut).  ws_counters: one arrival counter per 32 rows of a tail tile,
-  // zero between launches.
-  int n_whole, split_f, split_sps, split_inv;   // split_inv = ceil(65536 / split_f)
+  // CTA-pair kernel, when tiles x contraction stages are dealt to the pairs as one sequence: fp32
+  // partial sums of shared tiles ([pair][256 or 512 x 256]) and one arrival counter per 32 rows of a
+  // shared tile (indexed by the first contributing pair), zero between launches.
   float* ws_partials;
   unsigned* ws_counters;
   const __half* zp_table;   // backward: rn(s * (z+1)) for every [group, column], or null
@@ -369,7 +367,7 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
   p.trace = g_gemm_trace;
   p.lora_w = lora_r > 0 ? (const __half*)lora_w : nullptr;
   p.lora_r = lora_r;
-  p.n_whole = 0; p.split_f = 1; p.split_sps = 0; p.split_inv = 65536; p.ws_partials = nullptr; p.ws_counters = nullptr; p.zp_table = nullptr;
+  p.ws_partials = nullptr; p.ws_counters = nullptr; p.zp_table = nullptr;
   const int box_rows = use_pair ? 128 * mh : GM_TILE_M;    // activation rows one TMA copy brings
   CUtensorMap amap;
   if (int e = make_tmap_2d(&amap, act, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)contract, (uint64_t)M,
@@ -427,23 +425,23 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
       zp_table_kernel<<<(total8 + 255) / 256, 256, 0, st>>>((const __half*)scales, (const uint32_t*)qzeros, (__half*)(ws + ws_off), total8);
       ws_off += zp_bytes;
     }
-    // tiles left over after the last full round of all pairs are cut along the contraction
-    const int rem = n_tiles % P;
-    int f = 1, sps = T;
-    if (rem > 0 && ws && P / rem >= 2 && T >= 8) {
-      f = P / rem;
-      if (f > 8) f = 8;
-      if (f > T / 4) f = T / 4;
-      sps = (T + f - 1) / f;
-      f = (T + sps - 1) / sps;                       // no empty slice
-      if (f < 2 || workspace_bytes < ws_off + (size_t)rem * f * mh * Q4_GEMM_WS_SLICE_BYTES) { f = 1; sps = T; }
+    // Whole tiles per pair, round after round - or, when the last round would leave pairs idle for
+    // longer than the exchange of partial sums costs (about a dozen stages), all tiles x stages as one
+    // sequence cut into equal runs.
+    bool stream = false;
+    int pairs = n_tiles < P ? n_tiles : P;
+    if (ws && T >= 8 && n_tiles % P != 0) {
+      const long long total = (long long)n_tiles * T;
+      const long long whole_cost = (long long)((n_tiles + P - 1) / P) * T, stream_cost = (total + P - 1) / P + 12;
+      const size_t need = ws_off + (size_t)P * mh * Q4_GEMM_WS_SLICE_BYTES;
+      if (stream_cost < whole_cost && total >= (long long)P * 4 && total * P < (1ll << 32) && workspace_bytes >= need) {
+        stream = true;
+        pairs = P;
+      }
     }
-    p.split_f = f; p.split_sps = sps; p.split_inv = (65536 + f - 1) / f;
-    p.n_whole = f > 1 ? n_tiles - rem : n_tiles;
+    const int f = stream ? 2 : 1;
     p.ws_partials = (float*)(ws + ws_off);
     p.ws_counters = (unsigned*)ws;
-    const int n_items = p.n_whole + (n_tiles - p.n_whole) * f;
-    const int pairs = n_items < P ? n_items : P;
     const dim3 grid(2 * pairs), block(G2_THREADS);
 #define Q4_LAUNCH2(TR, SP, MHV) q4_gemm2_kernel<TR, SP, MHV><<<grid, block, smem, st>>>(amap, umap, p)
     if (mh == 2) {

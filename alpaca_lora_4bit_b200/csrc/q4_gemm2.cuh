@@ -59,35 +59,52 @@ __device__ __forceinline__ bool wait_bar_idle(uint64_t* bar, uint32_t parity, vo
   return false;
 }
 
-// A work item: a whole output tile, or one slice of the contraction of a tail tile (the tiles left
-// over after the last full round of all pairs are cut along the contraction so that every pair
-// still has work; their fp32 partial sums meet in global memory, see the epilogue).
+// A work item: an output tile, or a run of contraction stages of one.
+// SPLIT = false: pair q takes the tiles q, q + pairs, ... whole.
+// SPLIT = true ("stream-K"): all tiles x contraction stages, tile by tile, are one sequence that is
+// cut into equal runs, one per pair; a run covers the end of one tile, some whole tiles and the
+// start of another.  A tile that several pairs contribute to is added up in global memory: every
+// contributor writes its fp32 partial sums, the one that arrives last at the tile's counter adds
+// them in pair order (the same order whoever is last) and writes the output.
 struct WorkItem {
   int tile;      // output tile
   int kb, ke;    // contraction stages [kb, ke)
-  int tail;      // index among the tail tiles (split items only)
-  int slice;     // slice of the tail tile
   bool split;    // partial sum: goes to the workspace instead of the output
-  bool lora;     // the low-rank stage follows the contraction stages
+  bool lora;     // the low-rank stage follows the contraction stages (the run reaches the end of the tile)
 };
+struct WorkRange { int first_tile, n_items; unsigned s0, s1; };   // SPLIT: this pair's run [s0, s1) of the stage sequence
+
 template <bool SPLIT>
-__device__ __forceinline__ WorkItem work_item(const GemmParams& p, int i, int T) {
-  WorkItem w;
-  if (!SPLIT || i < p.n_whole) {
-    w.tile = i; w.kb = 0; w.ke = T; w.tail = 0; w.slice = 0; w.split = false; w.lora = p.lora_r > 0;
+__device__ __forceinline__ WorkRange work_range(int pair, int n_pairs, int n_tiles, int T) {
+  WorkRange r;
+  if (!SPLIT) {
+    r.first_tile = pair; r.n_items = pair < n_tiles ? (n_tiles - pair + n_pairs - 1) / n_pairs : 0; r.s0 = r.s1 = 0;
   } else {
-    const int j = i - p.n_whole;
-    w.tail = (j * p.split_inv) >> 16;               // j / split_f without a division (j < 128, split_f <= 8)
-    w.slice = j - w.tail * p.split_f; w.tile = p.n_whole + w.tail;
-    w.kb = w.slice * p.split_sps; w.ke = min(T, w.kb + p.split_sps);
-    w.split = true; w.lora = p.lora_r > 0 && w.slice == p.split_f - 1;
+    const unsigned total = (unsigned)n_tiles * (unsigned)T;        // the host keeps total * pairs below 2^32
+    r.s0 = (unsigned)pair * total / (unsigned)n_pairs; r.s1 = ((unsigned)pair + 1u) * total / (unsigned)n_pairs;
+    r.first_tile = (int)(r.s0 / (unsigned)T);
+    r.n_items = r.s1 > r.s0 ? (int)((r.s1 - 1u) / (unsigned)T) - r.first_tile + 1 : 0;
+  }
+  return r;
+}
+template <bool SPLIT>
+__device__ __forceinline__ WorkItem work_item(const GemmParams& p, const WorkRange& r, int i, int n_pairs, int T) {
+  WorkItem w;
+  if (!SPLIT) {
+    w.tile = r.first_tile + i * n_pairs; w.kb = 0; w.ke = T; w.split = false; w.lora = p.lora_r > 0;
+  } else {
+    w.tile = r.first_tile + i;
+    const int t0 = w.tile * T;
+    w.kb = i == 0 ? (int)r.s0 - t0 : 0;
+    w.ke = min(T, (int)r.s1 - t0);
+    w.split = w.kb > 0 || w.ke < T;
+    w.lora = p.lora_r > 0 && w.ke == T;
   }
   return w;
 }
+// Pair that owns stage u of the sequence when `total` stages are dealt to `n` pairs as [q total / n, (q + 1) total / n).
+__device__ __forceinline__ int stage_owner(long long u, int n, long long total) { return (int)(((u + 1) * n + total - 1) / total) - 1; }
 
-// SPLIT = false: every work item is a whole tile and the item decode folds away (the loop bounds of
-// the dequant loop are then kernel-wide constants, which the register allocation of that loop is
-// sensitive to); SPLIT = true: the launch has tail tiles cut along the contraction.
 // MH = 1: 256-row tiles (128 rows per CTA) and two TMEM accumulators, so that the epilogue of a tile
 // overlaps the MMAs of the next.  MH = 2: 512-row tiles (256 rows per CTA, two MMAs per 16
 // contraction elements on the same dequantised operand): half the dequant work per flop, which is
@@ -119,7 +136,7 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
   const int n_out_total = TRANSPOSE ? p.K : p.N;
   const int m_tiles = (p.M + G2_TILE_M - 1) / G2_TILE_M;
   const int n_tiles = m_tiles * (n_out_total / G2_TILE_N);
-  const int n_items = SPLIT ? p.n_whole + (n_tiles - p.n_whole) * p.split_f : n_tiles;
+  const WorkRange wr = work_range<SPLIT>(pair, n_pairs, n_tiles, T);
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < S; ++i) { mbar_init(&full[i], 1 + 8); mbar_init(&empty[i], 1); }
@@ -146,8 +163,8 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
       int st = 0, use = 0;                             // stage and how often it has been used, over all tiles
       unsigned polls = 0;
       const uint32_t full0 = mapa_u32(smem_u32(full), 0);
-      for (int item = pair; item < n_items; item += n_pairs) {
-        const WorkItem wi = work_item<SPLIT>(p, item, T);
+      for (int item = 0; item < wr.n_items; ++item) {
+        const WorkItem wi = work_item<SPLIT>(p, wr, item, n_pairs, T);
         const int m0 = (wi.tile % m_tiles) * G2_TILE_M + 128 * MH * (int)rank;
         const int nst = wi.ke - wi.kb + (wi.lora ? 1 : 0);
         for (int j = 0; j < nst; ++j) {
@@ -177,8 +194,8 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
       int st = 0, use = 0, tl = 0;
       unsigned polls = 0;
       uint64_t ad = ad0, bd = bd0;
-      for (int item = pair; item < n_items; item += n_pairs, ++tl) {
-        const WorkItem wi = work_item<SPLIT>(p, item, T);
+      for (int item = 0; item < wr.n_items; ++item, ++tl) {
+        const WorkItem wi = work_item<SPLIT>(p, wr, item, n_pairs, T);
         const int nst = wi.ke - wi.kb + (wi.lora ? 1 : 0), ncon = wi.ke - wi.kb;
         const int acc = MH == 1 ? (tl & 1) : 0, acc_use = MH == 1 ? (tl >> 1) : tl;
         if (acc_use > 0) wait_bar_cluster(&acc_empty[acc], (acc_use - 1) & 1, abort_flag);
@@ -227,8 +244,8 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
     int st = grp, use = 0;                                         // of this group's next stage use (g = grp, grp + 2, ...)
     unsigned polls = 0;
     int gbase = 0;                                                 // stage uses of all earlier items
-    for (int item = pair; item < n_items; item += n_pairs, ++tl) {
-      const WorkItem wi = work_item<SPLIT>(p, item, T);
+    for (int item = 0; item < wr.n_items; ++item, ++tl) {
+      const WorkItem wi = work_item<SPLIT>(p, wr, item, n_pairs, T);
       const int ncon = wi.ke - wi.kb, nst = ncon + (wi.lora ? 1 : 0);    // stages of this item: j = 0 .. nst-1, contraction stage kb + j
       const int out0 = (wi.tile / m_tiles) * G2_TILE_N + 128 * (int)rank;   // first output column (n forward, k backward)
       if (!TRANSPOSE && out0 != tab_out0) {
@@ -347,8 +364,8 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
     const uint32_t acc_empty0 = mapa_u32(smem_u32(acc_empty), 0);  // the even CTA's acc_empty[0]
     int tl = 0;
     unsigned polls = 0;
-    for (int item = pair; item < n_items; item += n_pairs, ++tl) {
-      const WorkItem wi = work_item<SPLIT>(p, item, T);
+    for (int item = 0; item < wr.n_items; ++item, ++tl) {
+      const WorkItem wi = work_item<SPLIT>(p, wr, item, n_pairs, T);
       const int acc = MH == 1 ? (tl & 1) : 0, acc_use = MH == 1 ? (tl >> 1) : tl;
       const int col0 = (wi.tile / m_tiles) * G2_TILE_N;
       int m = 0;                                                     // output row of this thread, set per accumulator below
@@ -377,28 +394,72 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
       __syncwarp();
       tc_fence_after();
       if (threadIdx.x == 384 && tl < 8) gm_mark(p.trace, 201 + 3 * tl);
-      // Partial sums of a slice: this warp's 32 rows x 256 columns of accumulator h as
+      // Partial sums of a run: this warp's 32 rows x 256 columns of accumulator h as
       // [cb][j][lane][4 floats], so that every 16-byte access of the warp is one contiguous 512 bytes.
-      // Blocks are indexed [tail tile][slice][CTA of the pair][accumulator][lane quarter].
+      // Blocks are indexed [contributing pair][CTA of the pair][accumulator][lane quarter].
+      // The pair whose run STARTS a shared tile adds the tile up: that piece is the last item of its
+      // run, so the other contributors (for whom the tile comes earlier in their runs) have as a rule
+      // long published their sums; it adds them to its own accumulator in pair order.
       const size_t part_floats = 8 * 8 * 32 * 4;
-      auto part_of = [&](int slice, int h) -> float* {
-        return p.ws_partials + (((((size_t)wi.tail * p.split_f + slice) * 2 + rank) * MH + h) * 4 + quarter) * part_floats;
+      auto part_of = [&](int cpair, int h) -> float* {
+        return p.ws_partials + ((((size_t)cpair * 2 + rank) * MH + h) * 4 + quarter) * part_floats;
       };
+      const bool shared_tile = SPLIT && wi.split;
+      const bool reducer = shared_tile && wi.kb == 0;
+      int c_first = 0, c_last = 0;
+      unsigned* cnt = nullptr;
+      if (shared_tile) {
+        const long long total = (long long)n_tiles * T;
+        c_first = stage_owner((long long)wi.tile * T, n_pairs, total);
+        c_last = stage_owner((long long)wi.tile * T + T - 1, n_pairs, total);
+        cnt = p.ws_counters + ((size_t)c_first * 2 + rank) * 4 + quarter;     // a pair starts at most one shared tile
+      }
+      if (reducer) {
+        if (lane == 0) {
+          const unsigned want = (unsigned)(c_last - c_first);
+          bool ok = false;
+          const uint32_t lim = *abort_flag ? 4u : 500000u;                    // x 200 ns
+          for (uint32_t i = 0; i < lim && !ok; ++i) {
+            unsigned have;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(have) : "l"(cnt) : "memory");
+            ok = have >= want;
+            if (!ok) __nanosleep(200);
+          }
+          if (!ok) { *abort_flag = 1; atomicExch(&g_gemm_status, Q4_STATUS_WAIT_EXPIRED); }
+        }
+        __syncwarp();
+        __threadfence();
+      }
 #pragma unroll 1
       for (int h = 0; h < MH; ++h) {
         m = (wi.tile % m_tiles) * G2_TILE_M + 128 * MH * (int)rank + 128 * h + 32 * quarter + lane;
-        float* part = wi.split ? part_of(wi.slice, h) : nullptr;
+        float* part = shared_tile && !reducer ? part_of(pair, h) : nullptr;
 #pragma unroll 1
         for (int cb = 0; cb < G2_TILE_N / 32; ++cb) {
           uint32_t v[32];
           tmem_ld32(tmem_acc + ((uint32_t)(32 * quarter) << 16) + (acc + h) * 256 + cb * 32, v);
           tmem_ld_wait();
-          if (!wi.split) {
+          if (!shared_tile) {
             emit(cb, v);
-          } else {
+          } else if (!reducer) {
 #pragma unroll
             for (int j = 0; j < 8; ++j)
               *reinterpret_cast<uint4*>(part + ((cb * 8 + j) * 32 + lane) * 4) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+          } else {
+            for (int cc = c_first + 1; cc <= c_last; ++cc) {
+              const float* src = part_of(cc, h);
+              float4 t[8];
+#pragma unroll
+              for (int j = 0; j < 8; ++j) t[j] = __ldcg(reinterpret_cast<const float4*>(src + ((cb * 8 + j) * 32 + lane) * 4));
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                v[4 * j] = __float_as_uint(__uint_as_float(v[4 * j]) + t[j].x);
+                v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + t[j].y);
+                v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + t[j].z);
+                v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + t[j].w);
+              }
+            }
+            emit(cb, v);
           }
         }
       }
@@ -406,42 +467,12 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc_empty0 + 8 * acc);
-      if (wi.split) {
-        // The warp that arrives last at the counter of these rows adds the slices up in slice order
-        // (the same order whoever it is), writes the rows and leaves the counter at zero.
-        unsigned* cnt = p.ws_counters + ((size_t)wi.tail * 2 + rank) * 4 + quarter;
+      if (shared_tile && !reducer) {                       // publish: sums, then the count
         __threadfence();
         __syncwarp();
-        unsigned last = 0;
-        if (lane == 0) last = atomicAdd(cnt, 1u) == (unsigned)(p.split_f - 1) ? 1u : 0u;
-        last = __shfl_sync(0xffffffffu, last, 0);
-        if (last) {
-          __threadfence();
-#pragma unroll 1
-          for (int h = 0; h < MH; ++h) {
-            m = (wi.tile % m_tiles) * G2_TILE_M + 128 * MH * (int)rank + 128 * h + 32 * quarter + lane;
-#pragma unroll 1
-            for (int cb = 0; cb < G2_TILE_N / 32; ++cb) {
-              float sum[32];
-#pragma unroll
-              for (int e = 0; e < 32; ++e) sum[e] = 0.f;
-              for (int sl = 0; sl < p.split_f; ++sl) {
-                const float* src = part_of(sl, h);
-#pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                  const float4 t = __ldcg(reinterpret_cast<const float4*>(src + ((cb * 8 + j) * 32 + lane) * 4));
-                  sum[4 * j] += t.x; sum[4 * j + 1] += t.y; sum[4 * j + 2] += t.z; sum[4 * j + 3] += t.w;
-                }
-              }
-              uint32_t v[32];
-#pragma unroll
-              for (int e = 0; e < 32; ++e) v[e] = __float_as_uint(sum[e]);
-              emit(cb, v);
-            }
-          }
-          if (lane == 0) *cnt = 0;
-        }
+        if (lane == 0) atomicAdd(cnt, 1u);
       }
+      if (reducer && lane == 0) *cnt = 0;                  // every contributor has been counted: ready for the next launch
       if (threadIdx.x == 384 && tl < 8) gm_mark(p.trace, 202 + 3 * tl);
     }
     if (p.trace && lane == 0) p.trace[(size_t)blockIdx.x * 256 + 242 + (warp & 3)] = polls;
