@@ -328,6 +328,24 @@ static size_t gemm_smem_bytes(bool transpose, int G, int stages) {
 
 using namespace q4;
 
+// Estimated duration (SM cycles) of the pair kernel with tiles of 256 * mh rows, and whether that
+// assumes whole tiles per pair (round after round) or all tiles x stages dealt as one sequence.
+// Per contraction stage a pair takes about 700 cycles with 256-row tiles (bounded by the dequant
+// warps) and 1100 with 512-row tiles (bounded by the MMAs: twice the flops per stage); exchanging
+// the partial sums of a shared tile costs about as much as 12 resp. 16 stages.
+static long long gemm2_estimate(int M, int nout, int T, int P, int mh, bool ws_ok, bool* stream) {
+  const int tile_m = 256 * mh;
+  const long long n_tiles = (long long)(nout / G2_TILE_N) * ((M + tile_m - 1) / tile_m);
+  const long long per_stage = mh == 2 ? 1100 : 700, exchange = mh == 2 ? 16 : 12;
+  long long best = (n_tiles + P - 1) / P * T;
+  *stream = false;
+  if (ws_ok && T >= 8 && n_tiles % P != 0) {
+    const long long total = n_tiles * T, dealt = (total + P - 1) / P + exchange;
+    if (dealt < best && total >= (long long)P * 4 && total * P < (1ll << 32)) { best = dealt; *stream = true; }
+  }
+  return best * per_stage;
+}
+
 static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, void* out, const void* scales,
                        const int32_t* qzeros, const int32_t* g_idx, const void* bias, const void* lora_u,
                        const void* lora_w, int lora_r, int M, int K, int N, int G, void* workspace, size_t workspace_bytes,
@@ -349,9 +367,19 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
   if ((g_gemm_variant == 2 && !pair_ok) || (g_gemm_variant == 3 && !wide_ok))
     return fail(Q4_E_SHAPE, "gemm: the CTA-pair kernel needs %d output columns to be a multiple of 256 and G=%d tables to fit", nout, G);
   const bool use_pair = (pair_ok && g_gemm_variant != 1) || g_gemm_variant == 3;
-  // 512-row tiles halve the dequant work per flop; they pay off as soon as there is more than one
-  // 256-row tile of rows
-  const int mh = use_pair && ((g_gemm_variant == 0 && wide_ok && M > 256) || g_gemm_variant == 3) ? 2 : 1;
+  // 512-row tiles halve the dequant work per flop but leave fewer, larger tiles to deal: take the
+  // form the estimate favours
+  const int P_est = sm_count() / 2 > 0 ? sm_count() / 2 : 1;
+  const size_t zp_need = transpose ? (((size_t)G * N * sizeof(__half) + 255) & ~(size_t)255) : 0;
+  auto ws_ok_for = [&](int m) { return workspace && workspace_bytes >= Q4_GEMM_WS_COUNTER_BYTES + zp_need + (size_t)P_est * m * Q4_GEMM_WS_SLICE_BYTES; };
+  int mh = 1;
+  if (use_pair && g_gemm_variant == 3) mh = 2;
+  else if (use_pair && g_gemm_variant == 0 && wide_ok && M > 256) {
+    bool s1, s2;
+    const long long e1 = gemm2_estimate(M, nout, contract / GM_TILE_C, P_est, 1, ws_ok_for(1), &s1);
+    const long long e2 = gemm2_estimate(M, nout, contract / GM_TILE_C, P_est, 2, ws_ok_for(2), &s2);
+    if (e2 < e1) mh = 2;
+  }
   int stages = GM_MAX_STAGES;
   while (stages > 2 && gemm_smem_bytes(transpose, G, stages) > 227 * 1024) --stages;
   if (use_pair) stages = mh == 2 ? stages2w : stages2;
@@ -430,15 +458,8 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
     // sequence cut into equal runs.
     bool stream = false;
     int pairs = n_tiles < P ? n_tiles : P;
-    if (ws && T >= 8 && n_tiles % P != 0) {
-      const long long total = (long long)n_tiles * T;
-      const long long whole_cost = (long long)((n_tiles + P - 1) / P) * T, stream_cost = (total + P - 1) / P + 12;
-      const size_t need = ws_off + (size_t)P * mh * Q4_GEMM_WS_SLICE_BYTES;
-      if (stream_cost < whole_cost && total >= (long long)P * 4 && total * P < (1ll << 32) && workspace_bytes >= need) {
-        stream = true;
-        pairs = P;
-      }
-    }
+    gemm2_estimate(M, nout, T, P, mh, ws && workspace_bytes >= ws_off + (size_t)P * mh * Q4_GEMM_WS_SLICE_BYTES, &stream);
+    if (stream) pairs = P;
     const int f = stream ? 2 : 1;
     p.ws_partials = (float*)(ws + ws_off);
     p.ws_counters = (unsigned*)ws;
