@@ -362,6 +362,7 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
     // ---------------- epilogue: TMEM -> registers -> (+bias) -> fp16 -> global ----------------
     const int quarter = warp & 3;                                  // TMEM lanes 32*quarter .. +31
     const uint32_t acc_empty0 = mapa_u32(smem_u32(acc_empty), 0);  // the even CTA's acc_empty[0]
+    const bool out_aligned32 = (reinterpret_cast<uintptr_t>(p.out) & 31) == 0;   // rows are multiples of 512 bytes apart
     int tl = 0;
     unsigned polls = 0;
     for (int item = 0; item < wr.n_items; ++item, ++tl) {
@@ -373,20 +374,24 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
       auto emit = [&](int cb, const uint32_t (&v)[32]) {
         if (m >= p.M) return;
         __half* dst = p.out + (size_t)m * n_out_total + col0 + cb * 32;
+        uint32_t o[16];
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          uint4 o;
-          uint32_t* ov = reinterpret_cast<uint32_t*>(&o);
-#pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            float f0 = __uint_as_float(v[8 * q + 2 * e]), f1 = __uint_as_float(v[8 * q + 2 * e + 1]);
-            if (!TRANSPOSE && p.bias) {
-              f0 += __half2float(p.bias[col0 + cb * 32 + 8 * q + 2 * e]);
-              f1 += __half2float(p.bias[col0 + cb * 32 + 8 * q + 2 * e + 1]);
-            }
-            ov[e] = as_u32(__floats2half2_rn(f0, f1));
+        for (int e = 0; e < 16; ++e) {
+          float f0 = __uint_as_float(v[2 * e]), f1 = __uint_as_float(v[2 * e + 1]);
+          if (!TRANSPOSE && p.bias) {
+            f0 += __half2float(p.bias[col0 + cb * 32 + 2 * e]);
+            f1 += __half2float(p.bias[col0 + cb * 32 + 2 * e + 1]);
           }
-          *reinterpret_cast<uint4*>(dst + 8 * q) = o;
+          o[e] = as_u32(__floats2half2_rn(f0, f1));
+        }
+        if (out_aligned32) {                               // whole 32-byte sectors per store instruction
+          asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]),
+                       "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
+          asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst + 16), "r"(o[8]), "r"(o[9]), "r"(o[10]), "r"(o[11]),
+                       "r"(o[12]), "r"(o[13]), "r"(o[14]), "r"(o[15]) : "memory");
+        } else {
+#pragma unroll
+          for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(dst + 8 * q) = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
         }
       };
       if (threadIdx.x == 384 && tl < 8) gm_mark(p.trace, 200 + 3 * tl);
