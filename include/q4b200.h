@@ -129,9 +129,10 @@ int q4_gemm_bwd(const void* dy, const int32_t* qweight, void* dx, const void* sc
  * the dense fp16 copy of W it reconstructs).  `workspace` may be NULL; with at least
  * q4_gemm_workspace_bytes(K, N, G) bytes of device memory, 16-byte aligned, whose first 64 KiB are
  * zero before the first call (the kernels leave them zero), the CTA-pair kernel
- *   - cuts the output tiles left over after the last full round of all SM pairs along the
- *     contraction, so that no SM pair idles through that round (fp32 partial sums meet in the
- *     workspace and are added in a fixed order: results do not depend on timing), and
+ *   - may deal all output tiles x contraction stages to the SM pairs as one sequence of equal runs
+ *     instead of whole tiles, when whole tiles would leave pairs idle (fp32 partial sums of a tile
+ *     that two or more pairs share meet in the workspace and are added in a fixed order: results do
+ *     not depend on timing), and
  *   - in the backward reads rn(s*(z+1)) from a [G, N] table a small kernel fills first.
  * One workspace serves calls that are ordered on one stream; calls that may overlap need one each. */
 size_t q4_gemm_workspace_bytes(int K, int N, int G);
