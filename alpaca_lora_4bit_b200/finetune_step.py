@@ -64,10 +64,11 @@ def fill_random_quant(mod: Autograd4bitQuantLinear, gen: torch.Generator, act_or
 
 
 def build_quant_llama(shape: LlamaShape, device, groupsize: int = 128, act_order: bool = False, seed: int = 0,
-                      attn_implementation: str = "sdpa") -> nn.Module:
+                      attn_implementation: str = "sdpa", gain: float = 1.0) -> nn.Module:
     """Random-init LLaMA of the given shape with every linear but ``lm_head`` quantised (4-bit, v2).
 
-    Built on the meta device so the dense fp16 weights of the replaced linears never exist."""
+    Built on the meta device so the dense fp16 weights of the replaced linears never exist.  ``gain`` scales
+    every quantised layer (1.0 = unit gain); deep stacks of random layers want less."""
     from transformers import LlamaConfig, LlamaForCausalLM
     cfg = LlamaConfig(hidden_size=shape.hidden_size, intermediate_size=shape.intermediate_size,
                       num_hidden_layers=shape.num_hidden_layers, num_attention_heads=shape.num_attention_heads,
@@ -86,7 +87,7 @@ def build_quant_llama(shape: LlamaShape, device, groupsize: int = 128, act_order
             # random levels minus random zero points have a standard deviation of about 6.3 levels and the
             # base scales average 0.011; shrink them so that every layer has unit gain (std(W) = 1/sqrt(K)),
             # as trained checkpoints roughly do - otherwise 32 random layers overflow fp16
-            fill_random_quant(mod, gen, act_order, scale_mul=1.0 / (6.3 * 0.011 * math.sqrt(mod.in_features)))
+            fill_random_quant(mod, gen, act_order, scale_mul=gain / (6.3 * 0.011 * math.sqrt(mod.in_features)))
     with torch.no_grad():
         for name, prm in model.named_parameters():
             if prm.dim() >= 2:
@@ -159,7 +160,7 @@ class LoraFinetuner:
     """Owns the optimizer state and runs one step: forward, backward, gradient all-reduce, AdamW."""
 
     def __init__(self, model: nn.Module, lr: float = 3e-4, loss_scale: float = 1024.0, autocast: bool = True,
-                 group=None, dynamic_scale: Optional[bool] = None):
+                 group=None, dynamic_scale: Optional[bool] = None, autocast_dtype: torch.dtype = torch.float16):
         self.model = model
         self.params = [p for p in model.parameters() if p.requires_grad]
         if not self.params:
@@ -172,10 +173,11 @@ class LoraFinetuner:
         self._static_loss = None
         self.loss_scale = loss_scale
         self.autocast = autocast
+        self.autocast_dtype = autocast_dtype
         self.group = group
         # fp16 training as the HF Trainer does it: dynamic loss scale, steps with non-finite gradients skipped
         if dynamic_scale is None:
-            dynamic_scale = self.params[0].is_cuda and autocast
+            dynamic_scale = self.params[0].is_cuda and autocast and autocast_dtype == torch.float16
         self.scaler = torch.amp.GradScaler("cuda", init_scale=loss_scale) if dynamic_scale else None
 
     def capture(self, example_ids: torch.Tensor, warmup: int = 3) -> bool:
@@ -218,7 +220,7 @@ class LoraFinetuner:
     def _eager_step(self, input_ids: torch.Tensor) -> torch.Tensor:
         self.flat.zero()
         dev_type = input_ids.device.type
-        with torch.autocast(device_type=dev_type, dtype=torch.float16, enabled=self.autocast and dev_type == "cuda"):
+        with torch.autocast(device_type=dev_type, dtype=self.autocast_dtype, enabled=self.autocast and dev_type == "cuda"):
             loss = self.model(input_ids=input_ids, labels=input_ids, use_cache=False).loss
         if self.scaler is not None:
             self.scaler.scale(loss.float()).backward()
@@ -226,8 +228,9 @@ class LoraFinetuner:
             self.scaler.step(self.opt)                     # unscales, skips the update on inf/nan
             self.scaler.update()
         else:
-            (loss.float() * self.loss_scale).backward()
-            self.flat.buffer.div_(self.loss_scale)
+            scale = self.loss_scale if self.autocast_dtype == torch.float16 else 1.0     # bf16 needs no loss scaling
+            (loss.float() * scale).backward()
+            self.flat.buffer.div_(scale)
             self.flat.all_reduce_mean(self.group)
             self.opt.step()
         return loss.detach()

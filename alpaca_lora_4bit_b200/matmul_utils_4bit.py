@@ -56,6 +56,8 @@ def get_buffer(shape_of_qweight, dtype=torch.float16, device='cuda', bits=4):
 def _decode(x, qweight, scales, zeros, g_idx, groupsize, flags):
     dtype = x.dtype
     x2 = x if x.dim() == 2 else x.reshape(-1, x.shape[-1])
+    if x2.shape[0] == 0:                      # no rows: nothing to launch
+        return x.new_zeros(x.shape[:-1] + (qweight.shape[1],))
     if dtype != torch.float16:
         x2 = x2.half()
     if not x2.is_contiguous():
@@ -131,7 +133,8 @@ def _matmul4bit_v2_recons(x, qweight, scales, zeros, g_idx, transpose=False):
         if not x2.is_contiguous():
             x2 = x2.contiguous()
         out = torch.empty((x2.shape[0], K if transpose else N), dtype=torch.float16, device=x.device)
-        quant_cuda.gemm(x2, qweight, out, scales, zeros, g_idx, transpose=transpose)
+        if x2.shape[0] > 0:                   # no rows: nothing to launch
+            quant_cuda.gemm(x2, qweight, out, scales, zeros, g_idx, transpose=transpose)
         return out.reshape(x.shape[:-1] + (out.shape[-1],))
     buffer = get_buffer(qweight.shape, dtype=scales.dtype, device=qweight.device)
     quant_cuda.vecquant4recons_v2(qweight, buffer, scales, zeros, g_idx)
@@ -150,7 +153,7 @@ def _matmul2bit_v2_recons(x, qweight, scales, zeros, g_idx, transpose=False):
 
 def matmul4bit(x, qweight, scales, zeros, g_idx=None, groupsize=None):
     """No-grad entry (matmul_utils_4bit.py:146-170): format from ``zeros.dtype``, kernel from M."""
-    if (x.dim() == 2 and x.shape[0] <= 16 and not (use_new and auto_switch and x.shape[0] > auto_switch_thd)
+    if (x.dim() == 2 and 1 <= x.shape[0] <= 16 and not (use_new and auto_switch and x.shape[0] > auto_switch_thd)
             and g_idx is not None and zeros.dtype == torch.int32 and x.dtype == torch.float16 and scales.dtype == torch.float16
             and not act_order and not debug and x.is_cuda and x.is_contiguous()):
         # the per-token call: sequential groups, fp16 in and out - straight to the decode kernel

@@ -242,15 +242,21 @@ def run_finetune(args, rank, world, local_rank):
     step and the loss is read back every step (inside the timed region)."""
     from alpaca_lora_4bit_b200 import finetune_step as fs
     dev = torch.device("cuda", local_rank)
-    shape = fs.LlamaShape.llama_7b()
+    big = args.finetune_config == "70b"
+    shape = fs.LlamaShape.llama2_70b() if big else fs.LlamaShape.llama_7b()
     if args.finetune_layers:
         shape.num_hidden_layers = args.finetune_layers
-    model = fs.build_quant_llama(shape, dev, groupsize=128, act_order=False, seed=0)
-    fs.add_lora(model, ["q_proj", "v_proj"], r=8, alpha=16, std_a=0.02, std_b=0.01, seed=1)
+    # 80 random layers at unit gain overflow bf16 attention around layer 64: the deep model is built at gain 0.5
+    model = fs.build_quant_llama(shape, dev, groupsize=128, act_order=big, seed=0, gain=0.5 if big else 1.0)
+    if big:
+        fs.add_lora(model, ["q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj"], r=16, alpha=32,
+                    std_a=0.02, std_b=0.01, seed=1)
+    else:
+        fs.add_lora(model, ["q_proj", "v_proj"], r=8, alpha=16, std_a=0.02, std_b=0.01, seed=1)
     fs.apply_gradient_checkpointing(model)
     model.train()
-    ft = fs.LoraFinetuner(model, lr=3e-4)
-    B, T = 4, 256
+    ft = fs.LoraFinetuner(model, lr=3e-4, autocast_dtype=torch.bfloat16 if big else torch.float16)
+    B, T = (1, 2048) if big else (4, 256)
     gen = torch.Generator().manual_seed(1000 + rank)
     steps, warm = args.finetune_steps, 3
     ids_host = [torch.randint(0, shape.vocab_size, (B, T), generator=gen).pin_memory() for _ in range(steps + warm)]
@@ -294,9 +300,10 @@ def run_finetune(args, rank, world, local_rank):
     p_lin = fs.quant_linear_params(model) + shape.vocab_size * shape.hidden_size
     flops_per_token = 4 * p_lin                      # forward 2P + backward-dx 2P, recompute not counted
     tps = tokens / (ms * 1e-3)
-    out = {"metric": "llama7b_lora_finetune_tokens_per_s", "value": round(tps, 1), "unit": "tokens/s", "n_gpus": world,
+    out = {"metric": "llama2_70b_lora_finetune_tokens_per_s" if big else "llama7b_lora_finetune_tokens_per_s", "value": round(tps, 1), "unit": "tokens/s", "n_gpus": world,
            "steps": steps, "ms_per_step": round(ms / steps, 2), "layers": shape.num_hidden_layers,
-           "micro_batch": [B, T], "lora": "r=8 alpha=16 q_proj,v_proj, dropout 0 (as the reference forces under checkpointing)",
+           "micro_batch": [B, T], "lora": ("r=16 alpha=32 on q,k,v,o,gate,up,down; act-order g_idx; bf16 autocast" if big else
+                                             "r=8 alpha=16 q_proj,v_proj, dropout 0 (as the reference forces under checkpointing)"),
            "lora_params": fs.lora_param_count(model), "allreduce_bytes_per_step": 4 * fs.lora_param_count(model) if world > 1 else 0,
            "model_tflops_per_s": round(tps * flops_per_token / 1e12, 1), "loss_first_last": [round(losses[0], 4), round(losses[-1], 4)], "launch": "cuda_graph" if graphed else "eager",
            "h2d_bytes_per_step": B * T * 8, "d2h_bytes_per_step": 4}
@@ -453,6 +460,9 @@ def main():
     ap.add_argument("--no-gemm", action="store_true", help="skip the M=2048 fused GEMM leg")
     ap.add_argument("--gemm-shape", default="", help="restrict the GEMM leg to one KxN shape, e.g. 5120x13824 (for profiler captures)")
     ap.add_argument("--finetune-steps", type=int, default=5, help="timed LLaMA-7B LoRA finetune steps (0 = skip)")
+    ap.add_argument("--finetune-config", default="7b", choices=["7b", "70b"],
+                    help="7b: LLaMA-7B, r=8 LoRA on q/v, 4 x 256 tokens, fp16 (C3); 70b: LLaMA-2-70B GQA, act-order, r=16 LoRA on "
+                         "all seven projections, 1 x 2048 tokens, bf16 autocast (C4; 35 GB of int4 weights per GPU)")
     ap.add_argument("--finetune-eager", action="store_true", help="do not capture the finetune step as a CUDA graph")
     ap.add_argument("--finetune-layers", type=int, default=0, help="override the number of decoder layers (0 = 32)")
     args = ap.parse_args()

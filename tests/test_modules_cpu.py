@@ -54,6 +54,25 @@ def test_dispatch_threshold_and_formats():
     assert y_big.shape == (20, 64) and y_small.dtype == torch.float16
 
 
+def test_empty_inputs_launch_nothing():
+    """Zero rows in, zero rows out (as ``torch.matmul`` on the reference's dense buffer gives), without a kernel call."""
+    layer = synth.make_layer(256, 64, 64, False, 1)
+    calls = []
+    with fake_backend.installed():
+        real_gemv, real_gemm = fake_backend.gemv, fake_backend.gemm
+        try:
+            fake_backend.gemv = lambda *a, **k: calls.append("gemv")
+            fake_backend.gemm = lambda *a, **k: calls.append("gemm")
+            y = mm4b.matmul4bit(torch.empty((0, 256), dtype=torch.float16), layer.qweight, layer.scales, layer.qzeros, layer.g_idx, 64)
+            y3 = mm4b.matmul4bit(torch.empty((2, 0, 256), dtype=torch.float16), layer.qweight, layer.scales, layer.qzeros, layer.g_idx, 64)
+            dx = mm4b._matmul4bit_v2_recons(torch.empty((0, 64), dtype=torch.float16), layer.qweight, layer.scales, layer.qzeros,
+                                            layer.g_idx, transpose=True)
+        finally:
+            fake_backend.gemv, fake_backend.gemm = real_gemv, real_gemm
+    assert calls == []
+    assert y.shape == (0, 64) and y3.shape == (2, 0, 64) and dx.shape == (0, 256)
+
+
 def test_autograd_forward_backward_matches_dense():
     m, layer = make_module(256, 128, 64, act=True, seed=3)
     w = orc.recons_v2(layer.qweight, layer.scales, layer.qzeros, layer.g_idx).float()
