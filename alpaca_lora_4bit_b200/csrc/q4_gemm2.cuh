@@ -447,10 +447,12 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
           if (!shared_tile) {
             emit(cb, v);
           } else if (!reducer) {
+            if (m < p.M) {                                 // rows beyond M are padding: nobody reads their sums
 #pragma unroll
-            for (int j = 0; j < 8; ++j)
-              *reinterpret_cast<uint4*>(part + ((cb * 8 + j) * 32 + lane) * 4) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-          } else {
+              for (int j = 0; j < 8; ++j)
+                *reinterpret_cast<uint4*>(part + ((cb * 8 + j) * 32 + lane) * 4) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+            }
+          } else if (m < p.M) {
             for (int cc = c_first + 1; cc <= c_last; ++cc) {
               const float* src = part_of(cc, h);
               float4 t[8];

@@ -519,7 +519,7 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
   }
 }
 
-// ---- M <= 2, sequential groups of a multiple of 128 rows: the lean decode kernel --------------------
+// ---- M <= 4, sequential groups of a multiple of 128 rows: the lean decode kernel --------------------
 // Same decomposition as gemv_stream_kernel (independent per-warp TMA streams over 4 KiB units), with
 // everything per-step stripped to the minimum:
 //   * x of a unit (256 halves per batch row) arrives in the warp's stage with cp.async next to the
@@ -654,12 +654,12 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
     const bool reducer = warp == GF_WARPS - 1;
     if (!reducer && seq >= 1) named_bar_sync(2, GF_THREADS);
     float* mine = red + warp * MR * GEMV_TN;
-    if (t == 0) {                                        // batch columns 0 and 1 live in the t == 0 lanes
+    if (2 * t < MR) {                                    // batch rows 2t and 2t + 1 live in the lanes with this t
 #pragma unroll
       for (int j = 0; j < 2; ++j)
 #pragma unroll
         for (int i = 0; i < 4; ++i)
-          if ((i & 1) < MR) mine[(i & 1) * GEMV_TN + 4 * g + 2 * j + (i >> 1)] = yacc[j][i];
+          if (2 * t + (i & 1) < MR) mine[(2 * t + (i & 1)) * GEMV_TN + 4 * g + 2 * j + (i >> 1)] = yacc[j][i];
     }
 #pragma unroll
     for (int j = 0; j < 2; ++j)
@@ -1036,11 +1036,12 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
     CUtensorMap map, smap, zmap;
     if (int e = make_tmap_2d(&map, qweight, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, (uint64_t)N, (uint64_t)(K / 8),
                              (uint64_t)N * 4, GEMV_TN, GEMV_UNIT_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
-    if (lean_ok && !v1 && M <= 2 && (groupsize == 128 || groupsize % 256 == 0) && K % 128 == 0) {
+    if (lean_ok && !v1 && M <= 4 && (groupsize == 128 || groupsize % 256 == 0) && K % 128 == 0) {
       // lean kernel: x, scales and zero points travel with the weights by 16-byte asynchronous copies,
       // so the weights are the only tensor map it uses
       if (sp.whole_tiles && grid > N / GEMV_TN) grid = N / GEMV_TN;
-      return M == 1 ? launch_fast<1>(map, map, map, sp, grid, st) : launch_fast<2>(map, map, map, sp, grid, st);
+      return M == 1 ? launch_fast<1>(map, map, map, sp, grid, st) : M == 2 ? launch_fast<2>(map, map, map, sp, grid, st)
+                                                                  : launch_fast<4>(map, map, map, sp, grid, st);
     }
     sp.whole_tiles = 0;
     if (int e = make_tmap_2d(&smap, scales, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (uint64_t)N, (uint64_t)G,
