@@ -18,6 +18,7 @@ the installed torch.
 from __future__ import annotations
 
 import argparse
+import contextlib
 import json
 import os
 import statistics
@@ -197,6 +198,37 @@ def run_ours(args, rank, world, local_rank):
                 per_shape[f"{K}x{N}"] = {"us_per_launch": round(us, 3),
                                          "gbs": round(synth.gemv_bytes(1, K, N, GROUPSIZE) / us / 1e3, 1)}
 
+        # the same pool at the other batch sizes of the decode sweep (C1: M in {1, 4, 8, 16}), rank 0 only
+        m_sweep = {}
+        if rank == 0:
+            wsm = _lib.workspace(dev, max(L.q4_gemv_workspace_bytes(16, K, N) for K, N in SHAPES))
+            for M in (4, 8, 16):
+                xm = {K: torch.randn((M, K), generator=gen, device=dev).half() for K in (4096, 11008)}
+                ym = [torch.empty((M, l.N), dtype=torch.float16, device=dev) for l in pool]
+                gm = torch.cuda.CUDAGraph()
+                with torch.cuda.stream(stream):
+                    for capture in (False, True):
+                        ctx = torch.cuda.graph(gm, stream=stream) if capture else contextlib.nullcontext()
+                        with ctx:
+                            st = torch.cuda.current_stream(dev).cuda_stream
+                            for l, y in zip(pool, ym):
+                                L.q4_gemv(xm[l.K].data_ptr(), l.qweight.data_ptr(), y.data_ptr(), l.scales.data_ptr(),
+                                          l.qzeros.data_ptr(), None, None, M, l.K, l.N, l.K // GROUPSIZE, GROUPSIZE,
+                                          _lib.Q4_F16, 0, wsm.data_ptr(), wsm.numel(), st)
+                        stream.synchronize()
+                    for _ in range(3):
+                        gm.replay()
+                    a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    a.record(stream)
+                    for _ in range(10):
+                        gm.replay()
+                    b.record(stream)
+                    stream.synchronize()
+                us = a.elapsed_time(b) / 10 / len(pool) * 1e3
+                byt = sum(synth.gemv_bytes(M, l.K, l.N, GROUPSIZE) for l in pool) / len(pool)
+                m_sweep[str(M)] = {"us_per_launch": round(us, 3), "gbs": round(byt / us / 1e3, 1)}
+                del xm, ym, gm
+
     # ---- end to end through the Python operator surface, host buffers in, host buffers out
     for l in pool:
         l.g_idx = (torch.arange(l.K, device=dev) // GROUPSIZE).to(torch.int32)
@@ -232,7 +264,7 @@ def run_ours(args, rank, world, local_rank):
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
         ms, e2e_ms = float(t[0]), float(t[1])
     return dict(ms=ms, e2e_ms=e2e_ms, e2e_steps=e2e_steps, n_launch=n_launch, clocks=clk.summary(),
-                per_shape=per_shape, h2d=h2d, d2h=d2h)
+                per_shape=per_shape, m_sweep=m_sweep, h2d=h2d, d2h=d2h)
 
 
 def run_finetune(args, rank, world, local_rank):
@@ -527,7 +559,7 @@ def main():
                              "algorithmic_bytes_per_launch": round(bps / r["n_launch"]), "peak_kind": peak_kind,
                              "kernel": "gemv_fast_kernel<1>", "avg_launch_us": round(per_launch_us, 3),
                              "frac_of_nominal_8000": round(achieved / 8000.0, 4)},
-                "per_shape": r["per_shape"],
+                "per_shape": r["per_shape"], "m_sweep": r["m_sweep"],
                 "e2e": {"value": round(e2e, 1), "unit": UNIT, "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": r["d2h"],
                         "api": "matmul_utils_4bit.matmul4bit per layer; per step the activation vectors come from pinned host memory and all outputs go back in one copy; weights resident"},
                 "gpu_launches": args.steps * r["n_launch"], "clocks": r["clocks"]}
