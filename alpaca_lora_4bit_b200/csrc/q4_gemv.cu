@@ -540,7 +540,7 @@ template <int MR>
 __host__ __device__ constexpr int gf_stage_bytes() { return (GF_X_OFF + MR * 512 + 64 + 127) / 128 * 128; }   // TMA needs 128 B
 template <int MR>
 __host__ __device__ constexpr size_t gf_smem_bytes() {
-  return (size_t)GF_WARPS * GF_STAGES * gf_stage_bytes<MR>() + sizeof(float) * GF_WARPS * MR * GEMV_TN + GF_WARPS * GF_STAGES * 8 + 64 + GF_WARPS * 512;
+  return (size_t)GF_WARPS * GF_STAGES * gf_stage_bytes<MR>() + sizeof(float) * GF_WARPS * MR * GEMV_TN + GF_WARPS * GF_STAGES * 8 + 64;
 }
 
 __device__ __forceinline__ void cp_async16_zfill(void* dst, const void* src, bool valid) {
@@ -561,7 +561,6 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
   float* red = reinterpret_cast<float*>(smem + (size_t)GF_WARPS * GF_STAGES * STG);            // [16][MR][32]
   uint64_t* full = reinterpret_cast<uint64_t*>(red + GF_WARPS * MR * GEMV_TN);                  // [16][2]
   volatile int* flags = reinterpret_cast<volatile int*>(full + GF_WARPS * GF_STAGES);          // [0] abort
-  unsigned char* zero_rows = reinterpret_cast<unsigned char*>(const_cast<int*>(flags)) + 64;   // [16 warps][512 B] of zeros
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (threadIdx.x == 0) trace_mark_ns(sp.trace, 40);
@@ -582,7 +581,6 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
     flags[0] = 0;
     tma_prefetch_desc(&wmap); tma_prefetch_desc(&smap); tma_prefetch_desc(&zmap);
   }
-  for (int i = threadIdx.x; i < GF_WARPS * 128; i += GF_THREADS) reinterpret_cast<uint32_t*>(zero_rows)[i] = 0u;
   if (threadIdx.x == 0) trace_mark_ns(sp.trace, 46);
   __syncthreads();
   if (threadIdx.x == 0) trace_mark_ns(sp.trace, 47);
@@ -612,6 +610,14 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
   // unit's two group rows of scales (4 x 16 bytes each) and of packed zero points (16 bytes each);
   // then every lane arrives on the barrier.  One TMA copy per unit instead of three: issuing a
   // TMA copy occupies the issuing thread for some 200 cycles, an asynchronous 16-byte copy does not.
+  // lanes 0..7 copy 16 bytes of one of the unit's two scale rows, lanes 8 and 9 one of its two zero-point rows
+  const bool meta_lane = lane < 10;
+  const int meta_sel = lane < 8 ? (lane >> 2) : (lane - 8);
+  const unsigned char* meta_src = lane < 8 ? reinterpret_cast<const unsigned char*>(p.scales + 8 * (lane & 3))
+                                           : reinterpret_cast<const unsigned char*>(p.qzeros);
+  const size_t meta_pitch = lane < 8 ? (size_t)p.N * 2 : (size_t)(p.N >> 3) * 4;        // bytes per group row
+  const int meta_tile = lane < 8 ? GEMV_TN * 2 : (GEMV_TN / 8) * 4;                      // bytes per column tile
+  const int meta_dst = lane < 8 ? GF_META_OFF + 16 * lane : GF_ZP_OFF + 16 * (lane - 8);
   auto issue_x = [&](int n) {
     if (cx.u >= u1) return;
     unsigned char* stg = my_stages + (size_t)(n % GF_STAGES) * STG;
@@ -620,13 +626,11 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
 #pragma unroll
     for (int r = 0; r < MR; ++r)
       cp_async16_zfill(dst + r * 512 + 16 * lane, p.x + (size_t)(r < p.M ? r : 0) * K + (k < K ? k : 0), r < p.M && k < K);
-    if (lane < 10) {
+    if (meta_lane) {
       const int grow0 = sp.group_shift >= 0 ? ((cx.ux * GEMV_UNIT_STEPS) >> sp.group_shift) : (cx.ux * GEMV_UNIT_ROWS * 8) / gs;
-      const int row = grow0 + (lane < 8 ? (lane >> 2) : (lane - 8));
+      const int row = grow0 + meta_sel;
       const bool ok = row < sp.n_groups;
-      const int rr = ok ? row : 0;
-      if (lane < 8) cp_async16_zfill(stg + GF_META_OFF + 16 * lane, p.scales + (size_t)rr * p.N + cx.tile * GEMV_TN + 8 * (lane & 3), ok);
-      else cp_async16_zfill(stg + GF_ZP_OFF + 16 * (lane - 8), p.qzeros + (size_t)rr * (p.N >> 3) + cx.tile * (GEMV_TN / 8), ok);
+      cp_async16_zfill(stg + meta_dst, meta_src + (size_t)(ok ? row : 0) * meta_pitch + cx.tile * meta_tile, ok);
     }
     cp_async_arrive_noinc(&my_full[n % GF_STAGES]);
     cursor_step(cx);
@@ -711,8 +715,12 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
     for (int u = u0 + warp + GF_WARPS * n; u < seg_u1; ++n, u += GF_WARPS) {
       const int ux = u - tile * upt;
       const int st = n % GF_STAGES, use = n / GF_STAGES;
-      if (!mbar_wait_warp(&my_full[st], use & 1, flags[0] ? 4u : 20000u)) {
-        flags[0] = 1; atomicExch(sp.status, Q4_STATUS_WAIT_EXPIRED);
+      {
+        // every lane tests the barrier itself (one instruction per try, no vote or shuffle afterwards)
+        uint32_t tries = 0;
+        const uint32_t lim = flags[0] ? 64u : 20000000u;
+        while (!mbar_test_wait(&my_full[st], use & 1) && ++tries < lim) {}
+        if (tries >= lim) { flags[0] = 1; atomicExch(sp.status, Q4_STATUS_WAIT_EXPIRED); }
       }
       if (warp == 0 && lane == 0) trace_mark(sp.trace, 3 + 2 * n);
       if (warp == 0 && lane == 0 && n == 0) trace_mark_ns(sp.trace, 43);
@@ -737,9 +745,9 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
       }
       __syncwarp();
       const uint4* wq = reinterpret_cast<const uint4*>(stg) + t * 8 + g;                       // row t, columns 4g..4g+3
-      // lanes of batch rows that do not exist read a row of zeros with the same stride
-      const uint4* xq = (g < MR ? reinterpret_cast<const uint4*>(stg + GF_X_OFF + g * 512)
-                                : reinterpret_cast<const uint4*>(zero_rows + warp * 512)) + t;
+      // lanes of batch rows that do not exist feed row 0 again: an MMA output column depends on its own
+      // input column only, and the columns beyond MR are never stored
+      const uint4* xq = reinterpret_cast<const uint4*>(stg + GF_X_OFF + (g < MR ? g : 0) * 512) + t;
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         float c[2][2][4];
