@@ -519,7 +519,7 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
   }
 }
 
-// ---- M <= 4, sequential groups of a multiple of 128 rows: the lean decode kernel --------------------
+// ---- M <= 8, sequential groups of a multiple of 128 rows: the lean decode kernel --------------------
 // Same decomposition as gemv_stream_kernel (independent per-warp TMA streams over 4 KiB units), with
 // everything per-step stripped to the minimum:
 //   * x of a unit (256 halves per batch row) arrives in the warp's stage with cp.async next to the
@@ -529,8 +529,9 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
 //   * the +1024 / +64 offsets and the zero points are not handled per MMA fragment: one lane per
 //     column subtracts s * (offset_sum + (z+1) * x_sum) once per group, from sums of x computed once
 //     per unit with warp shuffles.
-constexpr int GF_WARPS = 16;
-constexpr int GF_THREADS = GF_WARPS * 32;
+// warps per CTA: 16, or 12 where the stages of 16 (4 KiB of weights + MR x 512 B of x each) do not fit
+template <int MR>
+__host__ __device__ constexpr int gf_warps() { return MR <= 4 ? 16 : 12; }
 constexpr int GF_STAGES = 2;
 constexpr int GF_META_OFF = GEMV_UNIT_BYTES;          // scales: 2 rows x 64 B
 constexpr int GF_ZP_OFF = GF_META_OFF + 128;          // zero points: 2 rows x 16 B
@@ -540,7 +541,7 @@ template <int MR>
 __host__ __device__ constexpr int gf_stage_bytes() { return (GF_X_OFF + MR * 512 + 64 + 127) / 128 * 128; }   // TMA needs 128 B
 template <int MR>
 __host__ __device__ constexpr size_t gf_smem_bytes() {
-  return (size_t)GF_WARPS * GF_STAGES * gf_stage_bytes<MR>() + sizeof(float) * GF_WARPS * MR * GEMV_TN + GF_WARPS * GF_STAGES * 8 + 64;
+  return (size_t)gf_warps<MR>() * GF_STAGES * gf_stage_bytes<MR>() + sizeof(float) * gf_warps<MR>() * MR * GEMV_TN + gf_warps<MR>() * GF_STAGES * 8 + 64;
 }
 
 __device__ __forceinline__ void cp_async16_zfill(void* dst, const void* src, bool valid) {
@@ -552,12 +553,13 @@ __device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
 }
 
 template <int MR>
-__global__ void __launch_bounds__(GF_THREADS, 1)
+__global__ void __launch_bounds__(gf_warps<MR>() * 32, 1)
 gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap,
                  const __grid_constant__ CUtensorMap zmap, const GemvStreamParams sp) {
   extern __shared__ __align__(128) unsigned char smem[];
   const GemvParams& p = sp.g;
   constexpr int STG = gf_stage_bytes<MR>();
+  constexpr int GF_WARPS = gf_warps<MR>(), GF_THREADS = GF_WARPS * 32;
   float* red = reinterpret_cast<float*>(smem + (size_t)GF_WARPS * GF_STAGES * STG);            // [16][MR][32]
   uint64_t* full = reinterpret_cast<uint64_t*>(red + GF_WARPS * MR * GEMV_TN);                  // [16][2]
   volatile int* flags = reinterpret_cast<volatile int*>(full + GF_WARPS * GF_STAGES);          // [0] abort
@@ -941,7 +943,7 @@ static int launch_fast(const CUtensorMap& map, const CUtensorMap& smap, const CU
     attr_done[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(GF_THREADS);
+  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(gf_warps<MR>() * 32);
   cfg.dynamicSmemBytes = smem; cfg.stream = st;
   cudaLaunchAttribute at[1];
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -997,6 +999,16 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
     return fail(Q4_E_SHAPE, "gemv: N=%d has more column tiles than the workspace head holds", N);
   if (int e = check_device()) return e;
 
+  // 9..16 rows on a layer the lean kernel takes: two launches of it (8 rows, then the rest) end sooner
+  // than one launch of the general streaming kernel
+  if (M > 8 && !act && !v1 && (groupsize == 128 || groupsize % 256 == 0) && K % 128 == 0) {
+    if (int e = q4_gemv(x, qweight, y, scales, qzeros, g_idx, bias, 8, K, N, G, groupsize, y_dtype, flags, workspace, workspace_bytes, stream))
+      return e;
+    const size_t ybytes = (size_t)N * (y_dtype == Q4_F32 ? 4 : 2);
+    return q4_gemv((const char*)x + (size_t)8 * K * 2, qweight, (char*)y + 8 * ybytes, scales, qzeros, g_idx, bias, M - 8, K, N, G,
+                   groupsize, y_dtype, flags, workspace, workspace_bytes, stream);
+  }
+
   GemvParams p;
   p.x = (const __half*)x; p.qw = (const uint32_t*)qweight; p.y = y; p.scales = (const __half*)scales;
   p.qzeros = (const uint32_t*)qzeros; p.g_idx = g_idx; p.bias = (const __half*)bias;
@@ -1044,12 +1056,12 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
     CUtensorMap map, smap, zmap;
     if (int e = make_tmap_2d(&map, qweight, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, (uint64_t)N, (uint64_t)(K / 8),
                              (uint64_t)N * 4, GEMV_TN, GEMV_UNIT_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
-    if (lean_ok && !v1 && M <= 4 && (groupsize == 128 || groupsize % 256 == 0) && K % 128 == 0) {
+    if (lean_ok && !v1 && M <= 8 && (groupsize == 128 || groupsize % 256 == 0) && K % 128 == 0) {
       // lean kernel: x, scales and zero points travel with the weights by 16-byte asynchronous copies,
       // so the weights are the only tensor map it uses
       if (sp.whole_tiles && grid > N / GEMV_TN) grid = N / GEMV_TN;
       return M == 1 ? launch_fast<1>(map, map, map, sp, grid, st) : M == 2 ? launch_fast<2>(map, map, map, sp, grid, st)
-                                                                  : launch_fast<4>(map, map, map, sp, grid, st);
+           : M <= 4 ? launch_fast<4>(map, map, map, sp, grid, st) : launch_fast<8>(map, map, map, sp, grid, st);
     }
     sp.whole_tiles = 0;
     if (int e = make_tmap_2d(&smap, scales, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (uint64_t)N, (uint64_t)G,
