@@ -115,6 +115,12 @@ def gemv(x, qweight, y, scales, zeros, g_idx, groupsize, flags, bias=None) -> No
 
 _decode_ws: dict = {}          # (device index, stream handle) -> (pointer, bytes, tensor)
 
+try:                                                      # the handle of the current stream without building a Stream object
+    _raw_stream = torch._C._cuda_getCurrentRawStream
+except AttributeError:                                    # pragma: no cover - older / newer torch without the private hook
+    def _raw_stream(idx):
+        return torch.cuda.current_stream(idx).cuda_stream
+
 
 def decode_v2(x, qweight, scales, zeros, groupsize):
     """``x @ W`` for at most 16 rows on a v2 layer with sequential groups, result in a new fp16 tensor.
@@ -135,7 +141,7 @@ def decode_v2(x, qweight, scales, zeros, groupsize):
         gemv(x, qweight.contiguous(), y, scales.contiguous(), zeros.contiguous(), None, groupsize, 0)
         return y
     y = torch.empty((M, N), dtype=torch.float16, device=dev)
-    st = torch.cuda.current_stream(dev).cuda_stream
+    st = _raw_stream(idx)
     w = _decode_ws.get((idx, st))
     if w is None:
         t = _lib.workspace_for(dev, st)
