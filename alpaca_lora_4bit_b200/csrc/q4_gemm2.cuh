@@ -439,11 +439,8 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
       for (int h = 0; h < MH; ++h) {
         m = (wi.tile % m_tiles) * G2_TILE_M + 128 * MH * (int)rank + 128 * h + 32 * quarter + lane;
         float* part = shared_tile && !reducer ? part_of(pair, h) : nullptr;
-#pragma unroll 1
-        for (int cb = 0; cb < G2_TILE_N / 32; ++cb) {
-          uint32_t v[32];
-          tmem_ld32(tmem_acc + ((uint32_t)(32 * quarter) << 16) + (acc + h) * 256 + cb * 32, v);
-          tmem_ld_wait();
+        // what happens to 32 sums of this thread's row: output, partial sums, or output of the sum over all contributors
+        auto consume = [&](int cb, uint32_t (&v)[32]) {
           if (!shared_tile) {
             emit(cb, v);
           } else if (!reducer) {
@@ -468,6 +465,19 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
             }
             emit(cb, v);
           }
+        };
+        // two register buffers: the TMEM load of the next 32 columns is in flight while these are consumed
+        const uint32_t tsrc = tmem_acc + ((uint32_t)(32 * quarter) << 16) + (acc + h) * 256;
+        uint32_t va[32], vb[32];
+        tmem_ld32(tsrc, va);
+#pragma unroll 1
+        for (int cb = 0; cb < G2_TILE_N / 32; cb += 2) {
+          tmem_ld_wait();
+          tmem_ld32(tsrc + (cb + 1) * 32, vb);
+          consume(cb, va);
+          tmem_ld_wait();
+          if (cb + 2 < G2_TILE_N / 32) tmem_ld32(tsrc + (cb + 2) * 32, va);
+          consume(cb + 1, vb);
         }
       }
       // this warp has read its part of the accumulator(s): the even CTA may overwrite them
