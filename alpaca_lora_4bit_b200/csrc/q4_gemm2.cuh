@@ -449,35 +449,59 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
               for (int j = 0; j < 8; ++j)
                 *reinterpret_cast<uint4*>(part + ((cb * 8 + j) * 32 + lane) * 4) = make_uint4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
             }
-          } else if (m < p.M) {
-            for (int cc = c_first + 1; cc <= c_last; ++cc) {
-              const float* src = part_of(cc, h);
-              float4 t[8];
+          }
+        };
+        const uint32_t tsrc = tmem_acc + ((uint32_t)(32 * quarter) << 16) + (acc + h) * 256;
+        if (!(reducer && m < p.M)) {
+          // two register buffers: the TMEM load of the next 32 columns is in flight while these are consumed
+          uint32_t va[32], vb[32];
+          tmem_ld32(tsrc, va);
+#pragma unroll 1
+          for (int cb = 0; cb < G2_TILE_N / 32; cb += 2) {
+            tmem_ld_wait();
+            tmem_ld32(tsrc + (cb + 1) * 32, vb);
+            consume(cb, va);
+            tmem_ld_wait();
+            if (cb + 2 < G2_TILE_N / 32) tmem_ld32(tsrc + (cb + 2) * 32, va);
+            consume(cb + 1, vb);
+          }
+        } else {
+          // adding up a shared tile: what takes long is the first other contributor's sums coming from L2, so
+          // the loads of the next block of 32 columns are issued before this block is converted and stored;
+          // further contributors (rare) are read on the spot
+          const float* src = part_of(c_first + 1, h);
+          float4 t[8];
 #pragma unroll
-              for (int j = 0; j < 8; ++j) t[j] = __ldcg(reinterpret_cast<const float4*>(src + ((cb * 8 + j) * 32 + lane) * 4));
+          for (int j = 0; j < 8; ++j) t[j] = __ldcg(reinterpret_cast<const float4*>(src + (j * 32 + lane) * 4));
+#pragma unroll 1
+          for (int cb = 0; cb < G2_TILE_N / 32; ++cb) {
+            uint32_t v[32];
+            tmem_ld32(tsrc + cb * 32, v);
+            tmem_ld_wait();
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              v[4 * j] = __float_as_uint(__uint_as_float(v[4 * j]) + t[j].x);
+              v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + t[j].y);
+              v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + t[j].z);
+              v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + t[j].w);
+            }
+            if (cb + 1 < G2_TILE_N / 32) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) t[j] = __ldcg(reinterpret_cast<const float4*>(src + (((cb + 1) * 8 + j) * 32 + lane) * 4));
+            }
+            for (int cc = c_first + 2; cc <= c_last; ++cc) {
+              const float* s2 = part_of(cc, h);
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
-                v[4 * j] = __float_as_uint(__uint_as_float(v[4 * j]) + t[j].x);
-                v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + t[j].y);
-                v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + t[j].z);
-                v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + t[j].w);
+                const float4 u = __ldcg(reinterpret_cast<const float4*>(s2 + ((cb * 8 + j) * 32 + lane) * 4));
+                v[4 * j] = __float_as_uint(__uint_as_float(v[4 * j]) + u.x);
+                v[4 * j + 1] = __float_as_uint(__uint_as_float(v[4 * j + 1]) + u.y);
+                v[4 * j + 2] = __float_as_uint(__uint_as_float(v[4 * j + 2]) + u.z);
+                v[4 * j + 3] = __float_as_uint(__uint_as_float(v[4 * j + 3]) + u.w);
               }
             }
             emit(cb, v);
           }
-        };
-        // two register buffers: the TMEM load of the next 32 columns is in flight while these are consumed
-        const uint32_t tsrc = tmem_acc + ((uint32_t)(32 * quarter) << 16) + (acc + h) * 256;
-        uint32_t va[32], vb[32];
-        tmem_ld32(tsrc, va);
-#pragma unroll 1
-        for (int cb = 0; cb < G2_TILE_N / 32; cb += 2) {
-          tmem_ld_wait();
-          tmem_ld32(tsrc + (cb + 1) * 32, vb);
-          consume(cb, va);
-          tmem_ld_wait();
-          if (cb + 2 < G2_TILE_N / 32) tmem_ld32(tsrc + (cb + 2) * 32, va);
-          consume(cb + 1, vb);
         }
       }
       // this warp has read its part of the accumulator(s): the even CTA may overwrite them

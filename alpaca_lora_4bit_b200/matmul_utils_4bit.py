@@ -127,6 +127,12 @@ def _matmul4bit_v2_recons(x, qweight, scales, zeros, g_idx, transpose=False):
         print('_matmul4bit_v2_recons')
     _check_inner(x, qweight, 8, transpose)
     K, N = qweight.shape[0] * 8, qweight.shape[1]
+    rows = math.prod(x.shape[:-1])
+    if (not transpose and 0 < rows <= 16 and not act_order and x.is_cuda and x.dtype == torch.float16
+            and scales.dtype == torch.float16 and (K // scales.shape[0]) % 32 == 0 and K % scales.shape[0] == 0):
+        # a handful of rows above the switch threshold: the streaming decode kernel still ends sooner than a
+        # tensor-core launch whose tiles would be almost all padding
+        return _decode(x, qweight, scales, zeros, None, K // scales.shape[0], 0)
     if (fused_gemm and x.dtype == torch.float16 and scales.dtype == torch.float16
             and quant_cuda.gemm_supported(K, N, scales.shape[0], transpose)):
         x2 = x.reshape(-1, x.shape[-1])
