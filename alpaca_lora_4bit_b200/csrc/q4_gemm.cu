@@ -6,8 +6,11 @@
 // shared memory, bit-exactly as the reference reconstruct does (rn(rn(s*q) - rn(s*(z+1)))), in
 // the layout the 5th-generation tensor core reads, and tcgen05.mma accumulates in TMEM.
 //
-// One CTA computes a 256 x 128 output tile as two 128-row accumulators, so that every dequantised
-// tile of W feeds two MMAs.  Roles (320 threads):
+// Two kernels share the dequant routine and the operand layout.  The CTA-pair kernel (q4_gemm2.cuh)
+// serves layers whose number of output columns is a multiple of 256; the single-CTA kernel in this
+// file serves the rest (multiples of 128).  In the single-CTA kernel one CTA computes a 256 x 128
+// output tile as two 128-row accumulators, so that every dequantised tile of W feeds two MMAs.
+// Roles (320 threads):
 //   warp 0      TMA producer: activation tiles [256 rows x 64 contraction] fp16, 128B-swizzled
 //   warp 1      owns TMEM (256 fp32 columns) and issues tcgen05.mma (one elected thread)
 //   warps 2-9   two groups of four: group 0 dequantises W for the even stages, group 1 for the

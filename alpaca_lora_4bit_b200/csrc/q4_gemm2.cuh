@@ -1,16 +1,20 @@
 // The fused dequant-GEMM on CTA pairs (tcgen05 cta_group::2), persistent over output tiles.
 // Included by q4_gemm.cu after GemmParams / wait_bar / g_gemm_status are defined.
 //
-// A pair of CTAs (a cluster of two, on the two SMs of one TPC) computes 256 x 256 output tiles:
-// CTA r of the pair holds activation rows 128r..128r+127 and dequantises the tile's output columns
-// 128r..128r+127; one tcgen05.mma issued by the even CTA multiplies all 256 rows by all 256 columns
-// and leaves rows 128r.. of the product in CTA r's TMEM.  Per 16 contraction elements each SM
-// reads 8 KiB of operands for 128 x 256 x 16 multiply-adds - half the shared-memory traffic per
-// flop of a single-CTA 128 x 128 instruction, which is what bounds that form.
+// A pair of CTAs (a cluster of two, on the two SMs of one TPC) computes output tiles of 256 columns
+// and 256 or 512 rows: CTA r of the pair holds half of the tile's activation rows and dequantises
+// the tile's output columns 128r..128r+127; one tcgen05.mma (M 256 x N 256 x K 16) issued by the even
+// CTA multiplies 128 rows of each CTA by all 256 columns and leaves the products in the TMEM of the
+// CTA that holds the rows.  Per 16 contraction elements each SM reads 8 KiB of operands for
+// 128 x 256 x 16 multiply-adds - half the shared-memory traffic per flop of a single-CTA 128 x 128
+// instruction, which is what bounds that form.
 //
-// The grid is one pair per pair of SMs; every pair walks the tile list with a stride of the number
-// of pairs.  TMEM holds two accumulators (2 x 256 columns), so the epilogue of a tile overlaps the
-// MMAs of the next.  Roles (512 threads per CTA):
+// The grid is one pair per pair of SMs.  Work is dealt either as whole tiles (pair q takes tiles q,
+// q + pairs, ...) or, when that would leave pairs idle in the last round, as equal runs of the
+// sequence of all tiles x contraction stages (see WorkItem below).  With 256-row tiles TMEM holds two
+// accumulators, so the epilogue of a tile overlaps the MMAs of the next; with 512-row tiles both
+// accumulators belong to the tile in flight and every dequantised operand feeds two MMAs.
+// Roles (512 threads per CTA):
 //   warp 0        TMA producer for this CTA's activation rows; completion bytes of both CTAs are
 //                 counted on the even CTA's barrier
 //   warp 1        owns TMEM; in the even CTA one elected thread issues the MMAs and the commits
