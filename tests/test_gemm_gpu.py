@@ -249,6 +249,36 @@ def test_tail_tiles_split_along_the_contraction(gemm_variant, transpose, act, va
     assert rel_fro(whole, outs[0]) <= 5e-4
 
 
+@pytest.mark.parametrize("variant", [1, 2, 3])
+@pytest.mark.parametrize("M,r", [(1, 64), (513, 1), (2000, 64)])
+def test_gemm_edge_rows_and_ranks(gemm_variant, variant, M, r):
+    """One row, one row past a tile boundary and a ragged large M; rank 1 and the largest rank the
+    low-rank stage takes (64); forward with bias and backward, on every kernel."""
+    K, N = 768, 512
+    layer = synth.make_layer(K, N, 128, True, seed=31)
+    A, B = synth.make_lora(K, N, r, seed=32)
+    w = orc.recons_v2(layer.qweight, layer.scales, layer.qzeros, layer.g_idx).float()
+    L = layer.to(DEV)
+    gemm_variant(variant)
+    for transpose in (False, True):
+        x = synth.make_acts(M, N if transpose else K, seed=33 + transpose)
+        bias = None if transpose else torch.randn(N).half()
+        if transpose:
+            u = ((x.float() @ B.float()) * 0.5).half()
+            want, lw = x.float() @ w.t() + u.float() @ A.float(), A
+        else:
+            u = ((x.float() @ A.float().t()) * 0.5).half()
+            want, lw = x.float() @ w + u.float() @ B.float().t() + bias.float(), B
+        out = torch.full((M + 2, K if transpose else N), 7.0, dtype=torch.float16, device=DEV)
+        quant_cuda.gemm(x.to(DEV), L.qweight, out[1:M + 1], L.scales, L.qzeros, L.g_idx, transpose=transpose,
+                        bias=None if bias is None else bias.to(DEV),
+                        lora_u=torch.nn.functional.pad(u, (0, 64 - r)).to(DEV), lora_w=lw.contiguous().to(DEV))
+        torch.cuda.synchronize()
+        assert quant_cuda.device_status() == 0
+        assert bool((out[0] == 7.0).all()) and bool((out[M + 1] == 7.0).all())         # rows around the view untouched
+        assert rel_fro(out[1:M + 1], want) <= REL_TOL
+
+
 def test_pair_kernel_rejects_shapes_it_cannot_serve(gemm_variant):
     layer = synth.make_layer(256, 384, 128, False, seed=3).to(DEV)
     x = synth.make_acts(16, 256, seed=4).to(DEV)
