@@ -30,6 +30,9 @@ _SIGNATURES = {
     "q4_recons_v1": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "q2_recons_v2": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p]),
     "q4_gemv_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
+    "q4_layer_create": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int]),
+    "q4_layer_gemv": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_size_t, c_void_p]),
+    "q4_layer_destroy": (None, [c_void_p]),
     "q4_gemv_set_trace": (c_int, [c_void_p]),
     "q4_gemm_set_trace": (c_int, [c_void_p]),
     "q4_gemm_set_variant": (c_int, [c_int]),

@@ -29,6 +29,7 @@
 // The act-order variant (group from g_idx per row) cannot factor the scale out of the
 // contraction; it dequantises per element from shared-memory scale tables instead.
 #include "q4_async.cuh"
+#include <new>
 
 
 namespace q4 {
@@ -956,6 +957,29 @@ static int launch_fast(const CUtensorMap& map, const CUtensorMap& smap, const CU
 
 using namespace q4;
 
+// ---- layer handle: the arguments of q4_gemv that do not change from token to token ------------
+struct q4_layer {
+  const int32_t* qweight;
+  const void* scales;
+  const int32_t* qzeros;
+  int K, N, G, groupsize;
+};
+
+extern "C" int q4_layer_create(q4_layer_t** out, const int32_t* qweight, const void* scales, const int32_t* qzeros,
+                               int K, int N, int G, int groupsize) {
+  if (!out) return fail(Q4_E_BADARG, "layer: null handle pointer");
+  *out = nullptr;
+  if (!qweight || !scales || !qzeros) return fail(Q4_E_BADARG, "layer: null pointer");
+  if (K <= 0 || N <= 0 || G <= 0 || groupsize <= 0) return fail(Q4_E_BADARG, "layer: K=%d N=%d G=%d groupsize=%d", K, N, G, groupsize);
+  if (K % 32 || N % 32) return fail(Q4_E_SHAPE, "layer: K=%d and N=%d must be multiples of 32", K, N);
+  q4_layer* l = new (std::nothrow) q4_layer{qweight, scales, qzeros, K, N, G, groupsize};
+  if (!l) return fail(Q4_E_BADARG, "layer: out of host memory");
+  *out = l;
+  return Q4_OK;
+}
+
+extern "C" void q4_layer_destroy(q4_layer_t* layer) { delete layer; }
+
 extern "C" int q4_gemv_set_trace(void* device_buffer) {
   g_trace = (unsigned long long*)device_buffer;
   return Q4_OK;
@@ -1093,4 +1117,12 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
     gemv_act_kernel<2><<<grid, block, smem, st>>>(p, G);
   }
   return check_cuda(cudaGetLastError(), "gemv launch");
+}
+
+
+extern "C" int q4_layer_gemv(const q4_layer_t* l, const void* x, void* y, int M,
+                             void* workspace, size_t workspace_bytes, q4_stream_t stream) {
+  if (!l) return fail(Q4_E_BADARG, "layer: null handle");
+  return q4_gemv(x, l->qweight, y, l->scales, l->qzeros, nullptr, nullptr, M, l->K, l->N, l->G, l->groupsize, Q4_F16, 0u,
+                 workspace, workspace_bytes, stream);
 }

@@ -159,13 +159,19 @@ def _matmul2bit_v2_recons(x, qweight, scales, zeros, g_idx, transpose=False):
 
 def matmul4bit(x, qweight, scales, zeros, g_idx=None, groupsize=None):
     """No-grad entry (matmul_utils_4bit.py:146-170): format from ``zeros.dtype``, kernel from M."""
+    if g_idx is not None and not act_order and not debug and (faster_mode in valid_faster_mode or faster_mode == 'disable'):
+        # a layer the per-token path has served before: its recorded plan, if this call fits it
+        y = quant_cuda.decode_planned(x, qweight, scales, zeros, -1 if groupsize is None else groupsize,
+                                      min(16, auto_switch_thd) if use_new and auto_switch else 16)
+        if y is not None:
+            return y
     if (x.dim() == 2 and 1 <= x.shape[0] <= 16 and not (use_new and auto_switch and x.shape[0] > auto_switch_thd)
             and g_idx is not None and zeros.dtype == torch.int32 and x.dtype == torch.float16 and scales.dtype == torch.float16
             and not act_order and not debug and x.is_cuda and x.is_contiguous()):
         # the per-token call: sequential groups, fp16 in and out - straight to the decode kernel
         gs = groupsize if groupsize is not None and groupsize > 0 else x.shape[1] // scales.shape[0]
         if gs % 32 == 0 and (faster_mode in valid_faster_mode or faster_mode == 'disable'):
-            return quant_cuda.decode_v2(x, qweight, scales, zeros, gs)
+            return quant_cuda.decode_v2(x, qweight, scales, zeros, gs, plan_key=-1 if groupsize is None else groupsize)
     rows = math.prod(x.shape[:-1])
     large = use_new and auto_switch and rows > auto_switch_thd
     if zeros.dtype != torch.int32:            # v1: float zeros

@@ -122,12 +122,82 @@ except AttributeError:                                    # pragma: no cover - o
         return torch.cuda.current_stream(idx).cuda_stream
 
 
-def decode_v2(x, qweight, scales, zeros, groupsize):
+class _LayerPlan:
+    """What the per-token call needs of one layer, looked up by the identity of its ``qweight``."""
+    __slots__ = ("handle", "qref", "scales", "zeros", "qptr", "sptr", "zptr", "K", "N", "index", "device", "gs_arg")
+
+
+_plans: dict = {}              # id(qweight) -> _LayerPlan; the entry dies with the qweight tensor
+_F16 = torch.float16
+try:
+    _current_device = torch._C._cuda_getDevice
+except AttributeError:                                    # pragma: no cover
+    _current_device = torch.cuda.current_device
+
+
+def _drop_plan(key):
+    p = _plans.pop(key, None)
+    if p is not None and p.handle:
+        _lib.lib().q4_layer_destroy(p.handle)
+        p.handle = None
+
+
+def _make_plan(qweight, scales, zeros, K, N, G, groupsize, gs_arg):
+    import ctypes
+    import weakref
+    h = ctypes.c_void_p()
+    _lib.check(_lib.lib().q4_layer_create(ctypes.byref(h), qweight.data_ptr(), scales.data_ptr(), zeros.data_ptr(), K, N, G, groupsize),
+               "layer_create")
+    p = _LayerPlan()
+    key = id(qweight)
+    p.handle = h.value
+    p.qref = weakref.ref(qweight, lambda _r, key=key: _drop_plan(key))
+    p.scales, p.zeros = scales, zeros
+    p.qptr, p.sptr, p.zptr = qweight.data_ptr(), scales.data_ptr(), zeros.data_ptr()
+    p.K, p.N, p.index, p.device, p.gs_arg = K, N, qweight.device.index, qweight.device, gs_arg
+    _drop_plan(key)
+    _plans[key] = p
+
+
+def decode_planned(x, qweight, scales, zeros, groupsize, max_rows):
+    """The per-token call for a layer ``decode_v2`` has seen before: ``x @ W`` in a new fp16 tensor, or
+    ``None`` when this call is not one the recorded plan covers (the caller then takes the general path).
+
+    A plan is valid for exactly the tensors it was made from: same objects, same storage addresses.
+    What is checked per call is what can differ between calls - ``x``, the current device, the
+    stream - so that a repeated call costs a dictionary lookup, one allocation and one foreign call
+    with seven arguments."""
+    p = _plans.get(id(qweight))
+    if p is None or p.scales is not scales or p.zeros is not zeros or p.gs_arg != groupsize or p.qref() is not qweight:
+        return None
+    if x.dtype is not _F16 or x.dim() != 2 or not x.is_contiguous() or x.device != p.device or _current_device() != p.index:
+        return None
+    M, K = x.shape
+    if K != p.K or M < 1 or M > max_rows:
+        return None
+    if qweight.data_ptr() != p.qptr or scales.data_ptr() != p.sptr or zeros.data_ptr() != p.zptr:
+        _drop_plan(id(qweight))                              # storage moved under the same tensor objects
+        return None
+    y = x.new_empty((M, p.N))
+    st = _raw_stream(p.index)
+    w = _decode_ws.get((p.index, st))
+    if w is None:
+        t = _lib.workspace_for(p.device, st)
+        w = _decode_ws[(p.index, st)] = (t.data_ptr(), t.numel(), t)
+    rc = _lib.lib().q4_layer_gemv(p.handle, x.data_ptr(), y.data_ptr(), M, w[0], w[1], st)
+    if rc:
+        _lib.check(rc, "layer_gemv")
+    return y
+
+
+def decode_v2(x, qweight, scales, zeros, groupsize, plan_key=None):
     """``x @ W`` for at most 16 rows on a v2 layer with sequential groups, result in a new fp16 tensor.
 
     The per-token call of generation: the caller (``matmul_utils_4bit.matmul4bit``) has already
     established that ``x`` is a contiguous 2-D fp16 CUDA tensor and ``scales`` fp16, so what is left
-    here is what protects memory - the shapes must describe one layer - and the foreign call."""
+    here is what protects memory - the shapes must describe one layer - and the foreign call.
+    With ``plan_key`` (the caller's own ``groupsize`` argument) the validated layer is recorded for
+    ``decode_planned``."""
     M, K = x.shape
     R, N = qweight.shape
     G = scales.shape[0]
@@ -150,6 +220,8 @@ def decode_v2(x, qweight, scales, zeros, groupsize):
                             M, K, N, G, groupsize, _lib.Q4_F16, 0, w[0], w[1], st)
     if rc:
         _lib.check(rc, "gemv")
+    if plan_key is not None and qweight.device == dev and scales.device == dev and zeros.device == dev and zeros.dtype == torch.int32:
+        _make_plan(qweight, scales, zeros, K, N, G, groupsize, plan_key)
     return y
 
 

@@ -87,6 +87,20 @@ int q4_gemv(const void* x, const int32_t* qweight, void* y, const void* scales,
             int M, int K, int N, int G, int groupsize, int y_dtype, unsigned flags,
             void* workspace, size_t workspace_bytes, q4_stream_t stream);
 
+/* A layer handle for the per-token call (no counterpart in the reference): a host that calls
+ * q4_gemv through a foreign-function interface once per layer and token pays for marshalling its 17
+ * arguments every time.  q4_layer_create records the layer's tensors and geometry once (v2 layout,
+ * sequential groups, no bias); q4_layer_gemv is q4_gemv(x, <layer>, y, M, ..., Q4_F16, flags 0, ...)
+ * with the arguments that change from call to call.  The handle owns no device memory and keeps no
+ * reference to the tensors: destroy it before they are freed or moved.  Handles are immutable and
+ * may be used from any thread. */
+typedef struct q4_layer q4_layer_t;
+int q4_layer_create(q4_layer_t** out, const int32_t* qweight, const void* scales, const int32_t* qzeros,
+                    int K, int N, int G, int groupsize);
+int q4_layer_gemv(const q4_layer_t* layer, const void* x, void* y, int M,
+                  void* workspace, size_t workspace_bytes, q4_stream_t stream);
+void q4_layer_destroy(q4_layer_t* layer);
+
 /* The same product as q4_gemv for callers that cannot allocate device memory (no counterpart in the
  * reference; added for hosts such as a serving process that handed all of HBM to its own pools, a
  * plugin that may not call the allocator of the process it lives in, or a latency path on which the

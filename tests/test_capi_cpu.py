@@ -52,6 +52,16 @@ def test_bad_arguments_are_rejected_without_a_device():
     assert L.q4_gemv(*args, 1, 128, 128, 1, 48, 0, 0, None, 0, None) == -2
     assert L.q4_gemv_workspace_bytes(1, 100, 128) == 0
     assert L.q4_gemv_workspace_bytes(16, 11008, 4096) > 0
+    # layer handle: made and destroyed on the host; bad geometry and null pointers give no handle
+    h = ctypes.c_void_p()
+    assert L.q4_layer_create(ctypes.byref(h), fake, fake, None, 128, 128, 1, 128) == -1 and not h.value
+    assert L.q4_layer_create(ctypes.byref(h), fake, fake, fake, 100, 128, 1, 128) == -2 and not h.value
+    assert L.q4_layer_create(None, fake, fake, fake, 128, 128, 1, 128) == -1
+    assert L.q4_layer_create(ctypes.byref(h), fake, fake, fake, 128, 128, 1, 128) == 0 and h.value
+    assert L.q4_layer_gemv(h, fake, fake, 17, None, 0, None) == -2            # the checks of q4_gemv apply
+    assert L.q4_layer_gemv(None, fake, fake, 1, None, 0, None) == -1
+    L.q4_layer_destroy(h)
+    L.q4_layer_destroy(None)
 
 
 def test_facade_refuses_cpu_tensors():

@@ -259,3 +259,43 @@ def test_workspace_counters_return_to_zero():
     gemv_gpu(layer, synth.make_acts(1, 4096), torch.float16)
     for ws in _lib._workspaces.values():
         assert int(ws[:65536].view(torch.int32).abs().sum()) == 0      # the counter head of the workspace
+
+
+def test_recorded_layer_plan_serves_repeated_calls_and_expires():
+    """``matmul4bit`` records a layer on its first per-token call and serves the next calls from the
+    record: same results as the oracle for 1..8 rows, a new output tensor per call, the general path
+    again for calls the record does not cover (other tensors, more rows than the switch threshold),
+    and no record left once the layer's tensors are gone."""
+    from alpaca_lora_4bit_b200 import matmul_utils_4bit as mm4b
+    layer = synth.make_layer(1024, 2048, 128, False, seed=11)
+    L = layer.to(DEV)
+    before = len(quant_cuda._plans)
+    outs = []
+    for M in (1, 1, 3, 8, 1):
+        x = synth.make_acts(M, 1024, seed=20 + M)
+        y = mm4b.matmul4bit(x.to(DEV), L.qweight, L.scales, L.qzeros, L.g_idx, 128)
+        assert y.shape == (M, 2048) and y.dtype == torch.float16
+        assert rel_fro(y, orc.matmul4bit_ref(x, layer.qweight, layer.scales, layer.qzeros, layer.g_idx)) <= REL_TOL
+        outs.append(y)
+    assert len(quant_cuda._plans) == before + 1 and id(L.qweight) in quant_cuda._plans
+    assert outs[0].data_ptr() != outs[1].data_ptr() and torch.equal(outs[0], outs[1]) and torch.equal(outs[0], outs[4])
+    # 12 rows are above the switch threshold: reconstruct + GEMM path, not the record
+    x12 = synth.make_acts(12, 1024, seed=4)
+    y12 = mm4b.matmul4bit(x12.to(DEV), L.qweight, L.scales, L.qzeros, L.g_idx, 128)
+    assert rel_fro(y12, orc.matmul4bit_ref(x12, layer.qweight, layer.scales, layer.qzeros, layer.g_idx)) <= REL_TOL
+    # other scales with the same qweight: the record does not apply, the result follows the new scales
+    s2 = (L.scales * 2).contiguous()
+    x = synth.make_acts(1, 1024, seed=21)
+    y2 = mm4b.matmul4bit(x.to(DEV), L.qweight, s2, L.qzeros, L.g_idx, 128)
+    assert rel_fro(y2, 2 * outs[0].float()) <= REL_TOL
+    assert quant_cuda._plans[id(L.qweight)].scales is s2          # re-recorded for the tensors last seen
+    # a CPU x is refused by the general path, not handed to the kernel
+    with pytest.raises(RuntimeError):
+        mm4b.matmul4bit(x, L.qweight, s2, L.qzeros, L.g_idx, 128)
+    key = id(L.qweight)
+    del L, y, y2, s2
+    import gc
+    gc.collect()
+    assert key not in quant_cuda._plans
+    torch.cuda.synchronize()
+    assert quant_cuda.device_status() == 0
