@@ -576,18 +576,18 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
   unsigned char* my_stages = smem + (size_t)warp * GF_STAGES * STG;
   uint64_t* my_full = full + warp * GF_STAGES;
 
-  if (lane < GF_STAGES) {                                 // every warp sets up its own barriers
-    mbar_init(&my_full[lane], 1 + 32);                    // TMA arrive + 32 cp.async arrivals
+  // Every warp sets up its own barriers, and the lane that does it is the lane that issues the warp's
+  // TMA copies: the first copies leave without waiting for any other warp.  The CTA-wide barrier
+  // that publishes flags[0] comes after them.
+  pdl_launch_dependents();
+  if (threadIdx.x == 0) tma_prefetch_desc(&wmap);
+  if (lane == 0) {
+#pragma unroll
+    for (int i = 0; i < GF_STAGES; ++i) mbar_init(&my_full[i], 1 + 32);   // TMA arrive + 32 cp.async arrivals
     mbar_fence_init();
   }
-  if (threadIdx.x == 0) {
-    flags[0] = 0;
-    tma_prefetch_desc(&wmap); tma_prefetch_desc(&smap); tma_prefetch_desc(&zmap);
-  }
+  if (threadIdx.x == 0) flags[0] = 0;
   if (threadIdx.x == 0) trace_mark_ns(sp.trace, 46);
-  __syncthreads();
-  if (threadIdx.x == 0) trace_mark_ns(sp.trace, 47);
-  pdl_launch_dependents();
 
   // The warp's units are u0 + warp + 16 n, n = 0, 1, ...; both issue streams below walk them in
   // order and keep (tile, unit within tile) by stepping, so that no unit costs an integer division.
@@ -642,6 +642,8 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
   issue_w(0);
   issue_w(1);                                            // weights never depend on an earlier kernel
   if (threadIdx.x == 0) trace_mark_ns(sp.trace, 41);
+  __syncthreads();                                       // barriers and flags[0] of every warp are set up
+  if (threadIdx.x == 0) trace_mark_ns(sp.trace, 47);
   pdl_wait();                                            // x, y and the workspace belong to the stream order
   if (threadIdx.x == 0) trace_mark_ns(sp.trace, 42);
   issue_x(0);

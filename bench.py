@@ -51,18 +51,22 @@ def load_peaks():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU with nvidia-smi while a region runs."""
+    """Samples SM clock and throttle reasons of one GPU with nvidia-smi, every sample stamped with the host
+    time it arrived.  The sampler is started ahead of the load (nvidia-smi needs up to a few seconds before
+    its first line on a box with many GPUs); ``summary(t0, t1)`` keeps the samples of that window."""
     Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
          "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
 
-    def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+    def __init__(self, index, enabled=True):
+        self.index, self.rows, self.proc, self.enabled = index, [], None, enabled
 
     def __enter__(self):
+        if not self.enabled:
+            return self
         try:
             self.proc = subprocess.Popen(
                 ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
-                 "-lms", "100"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+                 "-lms", "50"], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
             self.thread = threading.Thread(target=self._read, daemon=True)
             self.thread.start()
         except Exception:
@@ -71,21 +75,28 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([c.strip() for c in line.split(",")])
+            self.rows.append((time.time(), [c.strip() for c in line.split(",")]))
+
+    def wait_ready(self, timeout=10.0):
+        """Blocks until the first sample has arrived (or ``timeout`` seconds have passed)."""
+        t0 = time.time()
+        while self.proc is not None and not self.rows and time.time() - t0 < timeout and self.proc.poll() is None:
+            time.sleep(0.01)
 
     def __exit__(self, *a):
         if self.proc is not None:
-            time.sleep(0.15)
             self.proc.terminate()
             try:
                 self.proc.wait(timeout=2)
             except Exception:
                 self.proc.kill()
 
-    def summary(self):
+    def summary(self, t0=None, t1=None):
         sm, mx, reasons = [], 0, set()
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
+        for t, r in self.rows:
+            if (t0 is not None and t < t0) or (t1 is not None and t > t1):
+                continue
             try:
                 sm.append(float(r[0])); mx = max(mx, float(r[1]))
             except Exception:
@@ -157,18 +168,32 @@ def run_ours(args, rank, world, local_rank):
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph, stream=stream):
             step()
-        for _ in range(max(args.warmup, 3)):
-            graph.replay()
-        stream.synchronize()
-        barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        with ClockSampler(local_rank) as clk:
+        # The timed region of the default run lasts a few milliseconds, nvidia-smi delivers a sample every
+        # 50 ms: the warm-up replays of the same graph therefore run for at least 0.4 s right up to the timed
+        # region, and the clock record is the samples from the start of that load to the end of the timed
+        # region (rank 0 samples its own GPU; every rank runs the same load).
+        with ClockSampler(local_rank, enabled=(rank == 0)) as clk:
+            clk.wait_ready()
+            barrier()
+            t_load = time.time()
+            n_warm = 0
+            while n_warm < max(args.warmup, 3) or time.time() - t_load < 0.4:
+                graph.replay()
+                n_warm += 1
+                if n_warm % 64 == 0:
+                    stream.synchronize()
+            stream.synchronize()
+            barrier()
             torch.cuda.synchronize(dev)
             e0.record(stream)
             for _ in range(args.steps):
                 graph.replay()
             e1.record(stream)
             stream.synchronize()
+            t_end = time.time()
+            time.sleep(0.06)                     # the sample that covers the end of the region
+        clocks = clk.summary(t_load + 0.05, t_end + 0.06)
         torch.cuda.synchronize(dev)
         barrier()
         ms = e0.elapsed_time(e1)
@@ -263,7 +288,7 @@ def run_ours(args, rank, world, local_rank):
         t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
         ms, e2e_ms = float(t[0]), float(t[1])
-    return dict(ms=ms, e2e_ms=e2e_ms, e2e_steps=e2e_steps, n_launch=n_launch, clocks=clk.summary(),
+    return dict(ms=ms, e2e_ms=e2e_ms, e2e_steps=e2e_steps, n_launch=n_launch, clocks=clocks,
                 per_shape=per_shape, m_sweep=m_sweep, h2d=h2d, d2h=d2h)
 
 
