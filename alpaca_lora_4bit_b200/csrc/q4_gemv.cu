@@ -534,15 +534,20 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
 template <int MR>
 __host__ __device__ constexpr int gf_warps() { return MR <= 4 ? 16 : 12; }
 constexpr int GF_STAGES = 2;
-constexpr int GF_META_OFF = GEMV_UNIT_BYTES;          // scales: 2 rows x 64 B
+// A stage is two blocks.  The packed words (4 KiB, TMA with the 128-byte swizzle: the 16-byte chunk c of
+// row r lies at chunk c ^ (r & 7), which needs the block on a 1 KiB boundary) and, in a ring of its own,
+// the small operands of the unit:
+constexpr int GF_META_OFF = 0;                        // scales: 2 rows x 64 B
 constexpr int GF_ZP_OFF = GF_META_OFF + 128;          // zero points: 2 rows x 16 B
-constexpr int GF_X_OFF = GF_ZP_OFF + 128;             // x: MR rows x 512 B, then the sums: 2 chunks x MR x float2
+constexpr int GF_X_OFF = GF_ZP_OFF + 128;             // x: MR rows of 512 B at a pitch of 528 B, then the sums: 2 chunks x MR x float2
+constexpr int GF_X_PITCH = 528;                       // odd multiple of 16 B: the rows of a quarter-warp's loads fall on different banks
 
 template <int MR>
-__host__ __device__ constexpr int gf_stage_bytes() { return (GF_X_OFF + MR * 512 + 64 + 127) / 128 * 128; }   // TMA needs 128 B
+__host__ __device__ constexpr int gf_aux_bytes() { return (GF_X_OFF + MR * GF_X_PITCH + 64 + 127) / 128 * 128; }
 template <int MR>
 __host__ __device__ constexpr size_t gf_smem_bytes() {
-  return (size_t)gf_warps<MR>() * GF_STAGES * gf_stage_bytes<MR>() + sizeof(float) * gf_warps<MR>() * MR * GEMV_TN + gf_warps<MR>() * GF_STAGES * 8 + 64;
+  return 1024 + (size_t)gf_warps<MR>() * GF_STAGES * (GEMV_UNIT_BYTES + gf_aux_bytes<MR>()) + sizeof(float) * gf_warps<MR>() * MR * GEMV_TN +
+         gf_warps<MR>() * GF_STAGES * 8 + 64;
 }
 
 __device__ __forceinline__ void cp_async16_zfill(void* dst, const void* src, bool valid) {
@@ -557,11 +562,13 @@ template <int MR>
 __global__ void __launch_bounds__(gf_warps<MR>() * 32, 1)
 gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap,
                  const __grid_constant__ CUtensorMap zmap, const GemvStreamParams sp) {
-  extern __shared__ __align__(128) unsigned char smem[];
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);            // the swizzle works on address bits
   const GemvParams& p = sp.g;
-  constexpr int STG = gf_stage_bytes<MR>();
+  constexpr int STG = GEMV_UNIT_BYTES, AUX = gf_aux_bytes<MR>();
   constexpr int GF_WARPS = gf_warps<MR>(), GF_THREADS = GF_WARPS * 32;
-  float* red = reinterpret_cast<float*>(smem + (size_t)GF_WARPS * GF_STAGES * STG);            // [16][MR][32]
+  unsigned char* aux_ring = smem + (size_t)GF_WARPS * GF_STAGES * STG;
+  float* red = reinterpret_cast<float*>(aux_ring + (size_t)GF_WARPS * GF_STAGES * AUX);        // [16][MR][32]
   uint64_t* full = reinterpret_cast<uint64_t*>(red + GF_WARPS * MR * GEMV_TN);                  // [16][2]
   volatile int* flags = reinterpret_cast<volatile int*>(full + GF_WARPS * GF_STAGES);          // [0] abort
 
@@ -574,20 +581,21 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
   const int u0 = (int)((unsigned)blockIdx.x * share / (unsigned)G * per), u1 = (int)(((unsigned)blockIdx.x + 1u) * share / (unsigned)G * per);
   const int K = p.K, gs = p.groupsize;
   unsigned char* my_stages = smem + (size_t)warp * GF_STAGES * STG;
+  unsigned char* my_aux = aux_ring + (size_t)warp * GF_STAGES * AUX;
   uint64_t* my_full = full + warp * GF_STAGES;
 
-  // Every warp sets up its own barriers, and the lane that does it is the lane that issues the warp's
-  // TMA copies: the first copies leave without waiting for any other warp.  The CTA-wide barrier
-  // that publishes flags[0] comes after them.
-  pdl_launch_dependents();
-  if (threadIdx.x == 0) tma_prefetch_desc(&wmap);
-  if (lane == 0) {
-#pragma unroll
-    for (int i = 0; i < GF_STAGES; ++i) mbar_init(&my_full[i], 1 + 32);   // TMA arrive + 32 cp.async arrivals
+  if (lane < GF_STAGES) {                                 // every warp sets up its own barriers
+    mbar_init(&my_full[lane], 1 + 32);                    // TMA arrive + 32 cp.async arrivals
     mbar_fence_init();
   }
-  if (threadIdx.x == 0) flags[0] = 0;
+  if (threadIdx.x == 0) {
+    flags[0] = 0;
+    tma_prefetch_desc(&wmap); tma_prefetch_desc(&smap); tma_prefetch_desc(&zmap);
+  }
   if (threadIdx.x == 0) trace_mark_ns(sp.trace, 46);
+  __syncthreads();
+  if (threadIdx.x == 0) trace_mark_ns(sp.trace, 47);
+  pdl_launch_dependents();
 
   // The warp's units are u0 + warp + 16 n, n = 0, 1, ...; both issue streams below walk them in
   // order and keep (tile, unit within tile) by stepping, so that no unit costs an integer division.
@@ -623,12 +631,12 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
   const int meta_dst = lane < 8 ? GF_META_OFF + 16 * lane : GF_ZP_OFF + 16 * (lane - 8);
   auto issue_x = [&](int n) {
     if (cx.u >= u1) return;
-    unsigned char* stg = my_stages + (size_t)(n % GF_STAGES) * STG;
+    unsigned char* stg = my_aux + (size_t)(n % GF_STAGES) * AUX;
     unsigned char* dst = stg + GF_X_OFF;
     const int k = cx.ux * 256 + 8 * lane;
 #pragma unroll
     for (int r = 0; r < MR; ++r)
-      cp_async16_zfill(dst + r * 512 + 16 * lane, p.x + (size_t)(r < p.M ? r : 0) * K + (k < K ? k : 0), r < p.M && k < K);
+      cp_async16_zfill(dst + r * GF_X_PITCH + 16 * lane, p.x + (size_t)(r < p.M ? r : 0) * K + (k < K ? k : 0), r < p.M && k < K);
     if (meta_lane) {
       const int grow0 = sp.group_shift >= 0 ? ((cx.ux * GEMV_UNIT_STEPS) >> sp.group_shift) : (cx.ux * GEMV_UNIT_ROWS * 8) / gs;
       const int row = grow0 + meta_sel;
@@ -642,8 +650,6 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
   issue_w(0);
   issue_w(1);                                            // weights never depend on an earlier kernel
   if (threadIdx.x == 0) trace_mark_ns(sp.trace, 41);
-  __syncthreads();                                       // barriers and flags[0] of every warp are set up
-  if (threadIdx.x == 0) trace_mark_ns(sp.trace, 47);
   pdl_wait();                                            // x, y and the workspace belong to the stream order
   if (threadIdx.x == 0) trace_mark_ns(sp.trace, 42);
   issue_x(0);
@@ -651,6 +657,10 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
   if (threadIdx.x == 0) trace_mark(sp.trace, 0);
 
   const int g = lane >> 2, t = lane & 3;
+  // Packed words: lane (g, t) takes columns 4g..4g+3 of rows 2t (+1) of every block of eight rows.  With
+  // the rows a quarter-warp reads two apart, the swizzle puts its eight 16-byte chunks on eight different
+  // bank groups (rows t, t+1, ... at chunk g would put them on two).
+  const uint32_t woff0 = 128u * (2 * t) + 16u * (g ^ (2 * t)), woff1 = 128u * (2 * t + 1) + 16u * (g ^ (2 * t + 1));
   float yacc[2][4], ycorr[MR];
 #pragma unroll
   for (int j = 0; j < 2; ++j)
@@ -729,12 +739,13 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
       }
       if (warp == 0 && lane == 0) trace_mark(sp.trace, 3 + 2 * n);
       if (warp == 0 && lane == 0 && n == 0) trace_mark_ns(sp.trace, 43);
-      unsigned char* stg = my_stages + (size_t)st * STG;
+      const unsigned char* wst = my_stages + (size_t)st * STG;
+      unsigned char* stg = my_aux + (size_t)st * AUX;
       // ---- x: rewrite this lane's 8 elements per batch row in MMA order, and the unit's sums of x ----
-      float2* sums = reinterpret_cast<float2*>(stg + GF_X_OFF + MR * 512);      // [2 chunks][MR]
+      float2* sums = reinterpret_cast<float2*>(stg + GF_X_OFF + MR * GF_X_PITCH);      // [2 chunks][MR]
 #pragma unroll
       for (int r = 0; r < MR; ++r) {
-        uint4* px = reinterpret_cast<uint4*>(stg + GF_X_OFF + r * 512 + 16 * lane);
+        uint4* px = reinterpret_cast<uint4*>(stg + GF_X_OFF + r * GF_X_PITCH + 16 * lane);
         const uint4 v = *px;
         const __half2 h01 = as_h2(v.x), h23 = as_h2(v.y), h45 = as_h2(v.z), h67 = as_h2(v.w);
         const __half2 sixteenth = as_h2(0x2C002C00u);
@@ -749,17 +760,17 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
         if ((lane & 15) == 0) sums[(lane >> 4) * MR + r] = make_float2(1024.f * se + 64.f * so, se + so);
       }
       __syncwarp();
-      const uint4* wq = reinterpret_cast<const uint4*>(stg) + t * 8 + g;                       // row t, columns 4g..4g+3
       // lanes of batch rows that do not exist feed row 0 again: an MMA output column depends on its own
       // input column only, and the columns beyond MR are never stored
-      const uint4* xq = reinterpret_cast<const uint4*>(stg + GF_X_OFF + (g < MR ? g : 0) * 512) + t;
+      const uint4* xq = reinterpret_cast<const uint4*>(stg + GF_X_OFF + (g < MR ? g : 0) * GF_X_PITCH) + 2 * t;
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         float c[2][2][4];
 #pragma unroll
         for (int uu = 0; uu < 4; ++uu) {
-          const uint4 wv = wq[32 * (4 * h + uu)];
-          const uint4 xv = xq[4 * (4 * h + uu)];
+          // step (h, uu) takes packed rows 8 j + 2 t + pp of the unit, j = 2 h + uu / 2, pp = uu & 1
+          const uint4 wv = *reinterpret_cast<const uint4*>(wst + ((uu & 1) ? woff1 : woff0) + 1024 * (2 * h + (uu >> 1)));
+          const uint4 xv = xq[8 * (2 * h + (uu >> 1)) + (uu & 1)];
           const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};
           uint32_t pr[4][4];
 #pragma unroll
@@ -1086,8 +1097,11 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
       // lean kernel: x, scales and zero points travel with the weights by 16-byte asynchronous copies,
       // so the weights are the only tensor map it uses
       if (sp.whole_tiles && grid > N / GEMV_TN) grid = N / GEMV_TN;
-      return M == 1 ? launch_fast<1>(map, map, map, sp, grid, st) : M == 2 ? launch_fast<2>(map, map, map, sp, grid, st)
-           : M <= 4 ? launch_fast<4>(map, map, map, sp, grid, st) : launch_fast<8>(map, map, map, sp, grid, st);
+      CUtensorMap wsw;                                    // the same boxes, chunks swizzled by the row on their way in
+      if (int e = make_tmap_2d(&wsw, qweight, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, (uint64_t)N, (uint64_t)(K / 8),
+                               (uint64_t)N * 4, GEMV_TN, GEMV_UNIT_ROWS, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
+      return M == 1 ? launch_fast<1>(wsw, wsw, wsw, sp, grid, st) : M == 2 ? launch_fast<2>(wsw, wsw, wsw, sp, grid, st)
+           : M <= 4 ? launch_fast<4>(wsw, wsw, wsw, sp, grid, st) : launch_fast<8>(wsw, wsw, wsw, sp, grid, st);
     }
     sp.whole_tiles = 0;
     if (int e = make_tmap_2d(&smap, scales, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (uint64_t)N, (uint64_t)G,

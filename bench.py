@@ -142,7 +142,7 @@ def run_ours(args, rank, world, local_rank):
     L = _lib.lib()
     pool = make_pool(args.copies, dev, 1234 + rank)
     gen = torch.Generator(device=dev).manual_seed(99 + rank)
-    xs = {K: torch.randn((1, K), generator=gen, device=dev).half() for K in (4096, 11008)}
+    xs = {K: torch.randn((1, K), generator=gen, device=dev).half() for K in sorted({k for k, _ in SHAPES})}
     ys = [torch.empty((1, l.N), dtype=torch.float16, device=dev) for l in pool]
     ws = _lib.workspace(dev, max(L.q4_gemv_workspace_bytes(1, K, N) for K, N in SHAPES))
     stream = torch.cuda.Stream(dev)
@@ -228,7 +228,7 @@ def run_ours(args, rank, world, local_rank):
         if rank == 0:
             wsm = _lib.workspace(dev, max(L.q4_gemv_workspace_bytes(16, K, N) for K, N in SHAPES))
             for M in (4, 8, 16):
-                xm = {K: torch.randn((M, K), generator=gen, device=dev).half() for K in (4096, 11008)}
+                xm = {K: torch.randn((M, K), generator=gen, device=dev).half() for K in sorted({k for k, _ in SHAPES})}
                 ym = [torch.empty((M, l.N), dtype=torch.float16, device=dev) for l in pool]
                 gm = torch.cuda.CUDAGraph()
                 with torch.cuda.stream(stream):
@@ -260,7 +260,7 @@ def run_ours(args, rank, world, local_rank):
     # One step = one pass over the pool: the step's inputs (one activation vector per layer width) go
     # host -> device from pinned memory, every layer runs through the public no-grad entry point, and
     # the step's result (all output vectors, gathered on the device) comes back in one device -> host copy.
-    xh = {K: torch.randn((1, K)).half().pin_memory() for K in (4096, 11008)}
+    xh = {K: torch.randn((1, K)).half().pin_memory() for K in sorted({k for k, _ in SHAPES})}
     yh = torch.empty((1, sum(l.N for l in pool)), dtype=torch.float16).pin_memory()
     h2d = sum(v.numel() * 2 for v in xh.values())
     d2h = yh.numel() * 2
@@ -451,7 +451,7 @@ def reference_gpu(args):
     torch.cuda.set_device(dev)
     pool = make_pool(args.copies, dev, 1234)
     gen = torch.Generator(device=dev).manual_seed(99)
-    xs = {K: torch.randn((1, K), generator=gen, device=dev).half() for K in (4096, 11008)}
+    xs = {K: torch.randn((1, K), generator=gen, device=dev).half() for K in sorted({k for k, _ in SHAPES})}
 
     def matmul4bit_v2(x, l):
         y = torch.zeros((x.shape[0], l.N), dtype=torch.float32, device=x.device)
@@ -473,7 +473,7 @@ def reference_gpu(args):
     torch.cuda.synchronize(dev)
     ms = e0.elapsed_time(e1) / steps
     # the same end-to-end step as this library's arm: inputs in from pinned memory, all outputs back in one copy
-    xh = {K: torch.randn((1, K)).half().pin_memory() for K in (4096, 11008)}
+    xh = {K: torch.randn((1, K)).half().pin_memory() for K in sorted({k for k, _ in SHAPES})}
     yh = torch.empty((1, sum(l.N for l in pool)), dtype=torch.float16).pin_memory()
     t0 = time.perf_counter()
     for _ in range(steps):
@@ -516,6 +516,8 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-gemm", action="store_true", help="skip the M=2048 fused GEMM leg")
     ap.add_argument("--gemm-shape", default="", help="restrict the GEMM leg to one KxN shape, e.g. 5120x13824 (for profiler captures)")
+    ap.add_argument("--decode-shape", default="", help="decode pool of one KxN layer shape instead of the three LLaMA-7B shapes, "
+                                                       "e.g. 8192x28672 (for profiler captures; not the headline workload)")
     ap.add_argument("--finetune-steps", type=int, default=5, help="timed LLaMA-7B LoRA finetune steps (0 = skip)")
     ap.add_argument("--finetune-config", default="7b", choices=["7b", "70b"],
                     help="7b: LLaMA-7B, r=8 LoRA on q/v, 4 x 256 tokens, fp16 (C3); 70b: LLaMA-2-70B GQA, act-order, r=16 LoRA on "
@@ -523,6 +525,8 @@ def main():
     ap.add_argument("--finetune-eager", action="store_true", help="do not capture the finetune step as a CUDA graph")
     ap.add_argument("--finetune-layers", type=int, default=0, help="override the number of decoder layers (0 = 32)")
     args = ap.parse_args()
+    if args.decode_shape:
+        SHAPES[:] = [tuple(int(v) for v in args.decode_shape.lower().split("x"))]
 
     # The one JSON line must be alone on stdout: libraries that write to file descriptor 1 on their own
     # (NCCL prints its version there) are sent to stderr until the line is printed.
@@ -537,7 +541,8 @@ def main():
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    config = {"workload": "C1 decode GEMV M=1, LLaMA-7B shapes 4096x4096+4096x11008+11008x4096, g128, "
+    shapes_txt = "LLaMA-7B shapes 4096x4096+4096x11008+11008x4096" if not args.decode_shape else f"one shape {args.decode_shape} (not the headline workload)"
+    config = {"workload": f"C1 decode GEMV M=1, {shapes_txt}, g128, "
                           f"{args.copies} copies each per GPU (pool > 2x L2, no flush needed)",
               "l2_policy": "inputs larger than L2", "launch": "cuda_graph", "parallelism": f"replicas x{world}"}
 
@@ -592,7 +597,7 @@ def main():
                 "warmup": args.warmup, "ms_per_step": round(r["ms"] / args.steps, 5), "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": config,
                 "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                             "frac": round(achieved / peak, 4), "traffic": NCU_DRAM_BYTES_PER_LAUNCH,
+                             "frac": round(achieved / peak, 4), "traffic": None if args.decode_shape else NCU_DRAM_BYTES_PER_LAUNCH,
                              "algorithmic_bytes_per_launch": round(bps / r["n_launch"]), "peak_kind": peak_kind,
                              "kernel": "gemv_fast_kernel<1>", "avg_launch_us": round(per_launch_us, 3),
                              "frac_of_nominal_8000": round(achieved / 8000.0, 4)},
