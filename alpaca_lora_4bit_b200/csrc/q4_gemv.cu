@@ -558,13 +558,15 @@ __device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
-template <int MR>
+// TRACE: the instance that records timestamps (q4_gemv_set_trace); the other carries no trace code at all
+template <int MR, bool TRACE>
 __global__ void __launch_bounds__(gf_warps<MR>() * 32, 1)
 gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap,
                  const __grid_constant__ CUtensorMap zmap, const GemvStreamParams sp) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);            // the swizzle works on address bits
   const GemvParams& p = sp.g;
+  unsigned long long* const trc = TRACE ? sp.trace : nullptr;
   constexpr int STG = GEMV_UNIT_BYTES, AUX = gf_aux_bytes<MR>();
   constexpr int GF_WARPS = gf_warps<MR>(), GF_THREADS = GF_WARPS * 32;
   unsigned char* aux_ring = smem + (size_t)GF_WARPS * GF_STAGES * STG;
@@ -573,7 +575,7 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
   volatile int* flags = reinterpret_cast<volatile int*>(full + GF_WARPS * GF_STAGES);          // [0] abort
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  if (threadIdx.x == 0) trace_mark_ns(sp.trace, 40);
+  if (threadIdx.x == 0) trace_mark_ns(trc, 40);
   const int nu = sp.total_units, G = gridDim.x, upt = sp.units_per_tile;
   // this CTA's units [u0, u1): an even share of all units, or (whole_tiles) of all column tiles
   // (the host keeps nu * G below 2^32, so 32-bit arithmetic is exact)
@@ -592,9 +594,9 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
     flags[0] = 0;
     tma_prefetch_desc(&wmap); tma_prefetch_desc(&smap); tma_prefetch_desc(&zmap);
   }
-  if (threadIdx.x == 0) trace_mark_ns(sp.trace, 46);
+  if (threadIdx.x == 0) trace_mark_ns(trc, 46);
   __syncthreads();
-  if (threadIdx.x == 0) trace_mark_ns(sp.trace, 47);
+  if (threadIdx.x == 0) trace_mark_ns(trc, 47);
   pdl_launch_dependents();
 
   // The warp's units are u0 + warp + 16 n, n = 0, 1, ...; both issue streams below walk them in
@@ -646,15 +648,22 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
     cp_async_arrive_noinc(&my_full[n % GF_STAGES]);
     cursor_step(cx);
   };
-  if (threadIdx.x == 0) trace_mark_ns(sp.trace, 48);
+  // inside the unit loop both copies of a unit are issued together and one cursor serves both
+  auto issue_wx = [&](int n) {
+    if (cw.u >= u1) return;
+    cx = cw;
+    issue_w(n);
+    issue_x(n);
+  };
+  if (threadIdx.x == 0) trace_mark_ns(trc, 48);
   issue_w(0);
   issue_w(1);                                            // weights never depend on an earlier kernel
-  if (threadIdx.x == 0) trace_mark_ns(sp.trace, 41);
+  if (threadIdx.x == 0) trace_mark_ns(trc, 41);
   pdl_wait();                                            // x, y and the workspace belong to the stream order
-  if (threadIdx.x == 0) trace_mark_ns(sp.trace, 42);
+  if (threadIdx.x == 0) trace_mark_ns(trc, 42);
   issue_x(0);
   issue_x(1);
-  if (threadIdx.x == 0) trace_mark(sp.trace, 0);
+  if (threadIdx.x == 0) trace_mark(trc, 0);
 
   const int g = lane >> 2, t = lane & 3;
   // Packed words: lane (g, t) takes columns 4g..4g+3 of rows 2t (+1) of every block of eight rows.  With
@@ -730,15 +739,16 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
     for (int u = u0 + warp + GF_WARPS * n; u < seg_u1; ++n, u += GF_WARPS) {
       const int ux = u - tile * upt;
       const int st = n % GF_STAGES, use = n / GF_STAGES;
-      {
-        // every lane tests the barrier itself (one instruction per try, no vote or shuffle afterwards)
+      if (!mbar_test_wait(&my_full[st], use & 1)) {
+        // not there yet: every lane tests the barrier itself (one instruction per try, no vote or shuffle
+        // afterwards), up to a limit that shrinks once any wait of the CTA has expired
         uint32_t tries = 0;
         const uint32_t lim = flags[0] ? 64u : 20000000u;
         while (!mbar_test_wait(&my_full[st], use & 1) && ++tries < lim) {}
         if (tries >= lim) { flags[0] = 1; atomicExch(sp.status, Q4_STATUS_WAIT_EXPIRED); }
       }
-      if (warp == 0 && lane == 0) trace_mark(sp.trace, 3 + 2 * n);
-      if (warp == 0 && lane == 0 && n == 0) trace_mark_ns(sp.trace, 43);
+      if (warp == 0 && lane == 0) trace_mark(trc, 3 + 2 * n);
+      if (warp == 0 && lane == 0 && n == 0) trace_mark_ns(trc, 43);
       const unsigned char* wst = my_stages + (size_t)st * STG;
       unsigned char* stg = my_aux + (size_t)st * AUX;
       // ---- x: rewrite this lane's 8 elements per batch row in MMA order, and the unit's sums of x ----
@@ -818,27 +828,31 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
       }
       __syncwarp();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // our reads before the next TMA write
-      issue_w(n + GF_STAGES);
-      issue_x(n + GF_STAGES);
-      if (warp == 0 && lane == 0) trace_mark(sp.trace, 4 + 2 * n);
+      issue_wx(n + GF_STAGES);
+      if (warp == 0 && lane == 0) trace_mark(trc, 4 + 2 * n);
     }
-    if (threadIdx.x == 0) trace_mark(sp.trace, 30);
-    if (warp == GF_WARPS - 1 && lane == 0 && tile == tile_last) trace_mark_ns(sp.trace, 44);
+    if (threadIdx.x == 0) trace_mark(trc, 30);
+    if (warp == GF_WARPS - 1 && lane == 0 && tile == tile_last) trace_mark_ns(trc, 44);
     finish_tile(tile, tile - tile_first, max(u0, tile * upt) - tile * upt, seg_u1 - 1 - tile * upt);
-    if (threadIdx.x == 0) trace_mark(sp.trace, 31);
-    if (warp == GF_WARPS - 1 && lane == 0 && tile == tile_last) trace_mark_ns(sp.trace, 45);
+    if (threadIdx.x == 0) trace_mark(trc, 31);
+    if (warp == GF_WARPS - 1 && lane == 0 && tile == tile_last) trace_mark_ns(trc, 45);
   }
 }
 
 // ---- act-order (group of row k = g_idx[k]) -------------------------------------------------------
 // Scale and (z+1) of the CTA's 32 columns for every group live in shared memory as half2
 // (s, z+1); every element is dequantised as s*(q - (z+1)) in fp16 pairs before the MMA.
+// The four lanes that share the columns 4g..4g+3 (t = 0..3) hold different k-rows, hence different
+// groups: reading one table they would meet on the same bank in different rows.  The table is
+// therefore kept four times, copy t with the columns of every quad rotated by t, so that the 32
+// lanes of a lookup fall on 32 different banks whatever their groups are (copies = 4; layers with so
+// many groups that four copies do not fit keep one, copies = 1).
 template <int MT>
 __global__ void __launch_bounds__(GEMV_THREADS)
-gemv_act_kernel(const GemvParams p, int G) {
+gemv_act_kernel(const GemvParams p, int G, int copies) {
   extern __shared__ __align__(16) unsigned char smem_raw[];
   float* red = reinterpret_cast<float*>(smem_raw);                              // [8][MT*8][32]
-  __half2* tab = reinterpret_cast<__half2*>(smem_raw + sizeof(float) * GEMV_WARPS * MT * 8 * GEMV_TN);  // [G][32]
+  __half2* tab = reinterpret_cast<__half2*>(smem_raw + sizeof(float) * GEMV_WARPS * MT * 8 * GEMV_TN);  // [G][4 copies][32]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int g = lane >> 2, t = lane & 3;
   const int c0 = blockIdx.x * GEMV_TN;
@@ -851,7 +865,10 @@ gemv_act_kernel(const GemvParams p, int G) {
     const int grp = i >> 5, col = i & 31;
     const uint32_t zw = p.qzeros[(size_t)grp * (N >> 3) + ((c0 + col) >> 3)];
     const unsigned z1 = ((zw >> (4 * (col & 7))) & 0xF) + 1;
-    tab[i] = __halves2half2(p.scales[(size_t)grp * N + c0 + col], __ushort2half_rn((unsigned short)z1));
+    const __half2 e = __halves2half2(p.scales[(size_t)grp * N + c0 + col], __ushort2half_rn((unsigned short)z1));
+#pragma unroll
+    for (int tt = 0; tt < 4; ++tt)
+      if (tt < copies) tab[(grp * copies + tt) * GEMV_TN + (col & ~3) + ((col + tt) & 3)] = e;
   }
   __syncthreads();
 
@@ -866,6 +883,9 @@ gemv_act_kernel(const GemvParams p, int G) {
   const uint32_t* wp = p.qw + (size_t)t * N + c0 + 4 * g;
   const __half* xp0 = p.x + (size_t)g * K + 8 * t;
   const bool xok0 = g < p.M, xok1 = (g + 8) < p.M;
+  const int tc = copies == 4 ? t : 0, tstride = copies * GEMV_TN;
+  const __half2* tabt = tab + tc * GEMV_TN + 4 * g;               // this lane's copy, its quad of columns
+  const int qpos[4] = {tc & 3, (tc + 1) & 3, (tc + 2) & 3, (tc + 3) & 3};   // where column 4g + q sits in that copy
 
   for (int step = sb + warp; step < se; step += GEMV_WARPS) {
     const uint4 wv = ldg_stream(wp + (size_t)(4 * step) * N);
@@ -881,7 +901,7 @@ gemv_act_kernel(const GemvParams p, int G) {
       for (int m = 0; m < 4; ++m) {
         const uint32_t raw = and_or(w[q] >> (4 * m), 0x000F000Fu, 0x64006400u);
         const __half2 qq = __hsub2(as_h2(raw), as_h2(0x64006400u));              // (q_m, q_m+4)
-        const __half2 ta = tab[gi[m] * GEMV_TN + 4 * g + q], tb = tab[gi[m + 4] * GEMV_TN + 4 * g + q];
+        const __half2 ta = tabt[gi[m] * tstride + qpos[q]], tb = tabt[gi[m + 4] * tstride + qpos[q]];
         const __half2 sv = __lows2half2(ta, tb), zv = __highs2half2(ta, tb);
         pr[q][m] = as_u32(__hmul2(sv, __hsub2(qq, zv)));
       }
@@ -944,7 +964,7 @@ static int launch_stream(const CUtensorMap& map, const CUtensorMap& smap, const 
   return check_cuda(cudaLaunchKernelEx(&cfg, gemv_stream_kernel<MT, FAST, XS>, map, smap, zmap, sp), "gemv launch");
 }
 
-template <int MR>
+template <int MR, bool TRACE>
 static int launch_fast(const CUtensorMap& map, const CUtensorMap& smap, const CUtensorMap& zmap,
                        const GemvStreamParams& sp, int grid, cudaStream_t st) {
   static bool attr_done[64] = {false};
@@ -952,7 +972,7 @@ static int launch_fast(const CUtensorMap& map, const CUtensorMap& smap, const CU
   cudaGetDevice(&dev);
   const size_t smem = gf_smem_bytes<MR>();
   if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    if (int e = check_cuda(cudaFuncSetAttribute(gemv_fast_kernel<MR>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+    if (int e = check_cuda(cudaFuncSetAttribute(gemv_fast_kernel<MR, TRACE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
                            "gemv smem attribute")) return e;
     attr_done[dev] = true;
   }
@@ -963,7 +983,7 @@ static int launch_fast(const CUtensorMap& map, const CUtensorMap& smap, const CU
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at; cfg.numAttrs = 1;
-  return check_cuda(cudaLaunchKernelEx(&cfg, gemv_fast_kernel<MR>, map, smap, zmap, sp), "gemv launch");
+  return check_cuda(cudaLaunchKernelEx(&cfg, gemv_fast_kernel<MR, TRACE>, map, smap, zmap, sp), "gemv launch");
 }
 
 }  // namespace q4
@@ -1100,8 +1120,9 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
       CUtensorMap wsw;                                    // the same boxes, chunks swizzled by the row on their way in
       if (int e = make_tmap_2d(&wsw, qweight, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, (uint64_t)N, (uint64_t)(K / 8),
                                (uint64_t)N * 4, GEMV_TN, GEMV_UNIT_ROWS, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
-      return M == 1 ? launch_fast<1>(wsw, wsw, wsw, sp, grid, st) : M == 2 ? launch_fast<2>(wsw, wsw, wsw, sp, grid, st)
-           : M <= 4 ? launch_fast<4>(wsw, wsw, wsw, sp, grid, st) : launch_fast<8>(wsw, wsw, wsw, sp, grid, st);
+      if (g_trace && M == 1) return launch_fast<1, true>(wsw, wsw, wsw, sp, grid, st);
+      return M == 1 ? launch_fast<1, false>(wsw, wsw, wsw, sp, grid, st) : M == 2 ? launch_fast<2, false>(wsw, wsw, wsw, sp, grid, st)
+           : M <= 4 ? launch_fast<4, false>(wsw, wsw, wsw, sp, grid, st) : launch_fast<8, false>(wsw, wsw, wsw, sp, grid, st);
     }
     sp.whole_tiles = 0;
     if (int e = make_tmap_2d(&smap, scales, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (uint64_t)N, (uint64_t)G,
@@ -1123,14 +1144,16 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
   }
 
   const dim3 grid(N / GEMV_TN, p.S), block(GEMV_THREADS);
-  const size_t smem = sizeof(float) * GEMV_WARPS * MT * 8 * GEMV_TN + (size_t)G * GEMV_TN * sizeof(__half2);
+  const size_t red_bytes = sizeof(float) * GEMV_WARPS * MT * 8 * GEMV_TN;
+  const int copies = red_bytes + (size_t)G * 4 * GEMV_TN * sizeof(__half2) <= 100 * 1024 ? 4 : 1;   // two CTAs per SM at least
+  const size_t smem = red_bytes + (size_t)G * copies * GEMV_TN * sizeof(__half2);
   if (smem > 200 * 1024) return fail(Q4_E_SHAPE, "gemv: act-order tables for G=%d groups do not fit shared memory", G);
   if (MT == 1) {
     if (int e = check_cuda(cudaFuncSetAttribute(gemv_act_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "gemv smem attr")) return e;
-    gemv_act_kernel<1><<<grid, block, smem, st>>>(p, G);
+    gemv_act_kernel<1><<<grid, block, smem, st>>>(p, G, copies);
   } else {
     if (int e = check_cuda(cudaFuncSetAttribute(gemv_act_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem), "gemv smem attr")) return e;
-    gemv_act_kernel<2><<<grid, block, smem, st>>>(p, G);
+    gemv_act_kernel<2><<<grid, block, smem, st>>>(p, G, copies);
   }
   return check_cuda(cudaGetLastError(), "gemv launch");
 }
