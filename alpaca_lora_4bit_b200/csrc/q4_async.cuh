@@ -109,6 +109,18 @@ __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, i
       "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
       ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar)) : "memory");
 }
+// expect_tx + 2-D tile load as one predicated pair: the lanes with `pred` false issue nothing, and no
+// divergent region (with its reconvergence bookkeeping) is opened around the two instructions
+__device__ __forceinline__ void tma_expect_load_2d_if(bool pred, void* dst, const CUtensorMap* map, int c0, int c1,
+                                                      uint64_t* bar, uint32_t bytes) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.u32 p, %6, 0;\n\t"
+      "@p mbarrier.arrive.expect_tx.shared::cta.b64 _, [%4], %5;\n\t"
+      "@p cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n\t"
+      "}"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_u32(bar)), "r"(bytes), "r"((uint32_t)pred) : "memory");
+}
 // ---- thread-block cluster helpers (CTA pairs) ---------------------------------------------------
 __device__ __forceinline__ uint32_t cluster_ctarank() {
   uint32_t r;

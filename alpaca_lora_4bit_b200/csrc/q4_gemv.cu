@@ -554,6 +554,11 @@ __device__ __forceinline__ void cp_async16_zfill(void* dst, const void* src, boo
   const uint32_t n = valid ? 16u : 0u;
   asm volatile("cp.async.ca.shared.global [%0], [%1], 16, %2;" ::"r"(smem_u32(dst)), "l"(src), "r"(n) : "memory");
 }
+__device__ __forceinline__ void cp_async16_zfill_if(bool pred, void* dst, const void* src, bool valid) {
+  const uint32_t n = valid ? 16u : 0u;
+  asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.u32 p, %3, 0;\n\t@p cp.async.ca.shared.global [%0], [%1], 16, %2;\n\t}"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(n), "r"((uint32_t)pred) : "memory");
+}
 __device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
   asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
@@ -612,11 +617,8 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
   // packed weights of this warp's n-th unit: one TMA copy, issued by lane 0
   auto issue_w = [&](int n) {
     if (cw.u >= u1) return;
-    if (lane == 0) {
-      uint64_t* bar = &my_full[n % GF_STAGES];
-      mbar_arrive_expect_tx(bar, GEMV_UNIT_BYTES);
-      tma_load_2d(my_stages + (size_t)(n % GF_STAGES) * STG, &wmap, cw.tile * GEMV_TN, cw.ux * GEMV_UNIT_ROWS, bar);
-    }
+    tma_expect_load_2d_if(lane == 0, my_stages + (size_t)(n % GF_STAGES) * STG, &wmap, cw.tile * GEMV_TN, cw.ux * GEMV_UNIT_ROWS,
+                          &my_full[n % GF_STAGES], GEMV_UNIT_BYTES);
     cursor_step(cw);
   };
   // x of the same unit (every lane copies its 8 elements of every batch row) and, on lanes 0..9, the
@@ -639,11 +641,12 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
 #pragma unroll
     for (int r = 0; r < MR; ++r)
       cp_async16_zfill(dst + r * GF_X_PITCH + 16 * lane, p.x + (size_t)(r < p.M ? r : 0) * K + (k < K ? k : 0), r < p.M && k < K);
-    if (meta_lane) {
+    {
+      // lanes 10..31 run the same address arithmetic and copy nothing (a predicated copy, not a branch)
       const int grow0 = sp.group_shift >= 0 ? ((cx.ux * GEMV_UNIT_STEPS) >> sp.group_shift) : (cx.ux * GEMV_UNIT_ROWS * 8) / gs;
       const int row = grow0 + meta_sel;
       const bool ok = row < sp.n_groups;
-      cp_async16_zfill(stg + meta_dst, meta_src + (size_t)(ok ? row : 0) * meta_pitch + cx.tile * meta_tile, ok);
+      cp_async16_zfill_if(meta_lane, stg + meta_dst, meta_src + (size_t)(ok ? row : 0) * meta_pitch + cx.tile * meta_tile, ok);
     }
     cp_async_arrive_noinc(&my_full[n % GF_STAGES]);
     cursor_step(cx);
@@ -775,7 +778,7 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
       const uint4* xq = reinterpret_cast<const uint4*>(stg + GF_X_OFF + (g < MR ? g : 0) * GF_X_PITCH) + 2 * t;
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
-        float c[2][2][4];
+        float c[2][4];                                  // raw sums of the half: columns 4g, 4g+1 | 4g+2, 4g+3
 #pragma unroll
         for (int uu = 0; uu < 4; ++uu) {
           // step (h, uu) takes packed rows 8 j + 2 t + pp of the unit, j = 2 h + uu / 2, pp = uu & 1
@@ -792,16 +795,14 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
             pr[q][3] = and_or(w8, 0x00F000F0u, 0x64006400u);
           }
           if (uu == 0) {
-            mma16816_first(c[0][0], pr[0][0], pr[1][0], pr[0][1], pr[1][1], xv.x, xv.y);
-            mma16816_first(c[1][0], pr[2][0], pr[3][0], pr[2][1], pr[3][1], xv.x, xv.y);
-            mma16816_first(c[0][1], pr[0][2], pr[1][2], pr[0][3], pr[1][3], xv.z, xv.w);
-            mma16816_first(c[1][1], pr[2][2], pr[3][2], pr[2][3], pr[3][3], xv.z, xv.w);
+            mma16816_first(c[0], pr[0][0], pr[1][0], pr[0][1], pr[1][1], xv.x, xv.y);
+            mma16816_first(c[1], pr[2][0], pr[3][0], pr[2][1], pr[3][1], xv.x, xv.y);
           } else {
-            mma16816(c[0][0], pr[0][0], pr[1][0], pr[0][1], pr[1][1], xv.x, xv.y);
-            mma16816(c[1][0], pr[2][0], pr[3][0], pr[2][1], pr[3][1], xv.x, xv.y);
-            mma16816(c[0][1], pr[0][2], pr[1][2], pr[0][3], pr[1][3], xv.z, xv.w);
-            mma16816(c[1][1], pr[2][2], pr[3][2], pr[2][3], pr[3][3], xv.z, xv.w);
+            mma16816(c[0], pr[0][0], pr[1][0], pr[0][1], pr[1][1], xv.x, xv.y);
+            mma16816(c[1], pr[2][0], pr[3][0], pr[2][1], pr[3][1], xv.x, xv.y);
           }
+          mma16816(c[0], pr[0][2], pr[1][2], pr[0][3], pr[1][3], xv.z, xv.w);
+          mma16816(c[1], pr[2][2], pr[3][2], pr[2][3], pr[3][3], xv.z, xv.w);
         }
         // close the group of this half: scale the raw sums, and (one lane per column) take the offsets
         // and the zero point out: y -= s * (offset_sum + (z + 1) * x_sum)
@@ -809,14 +810,14 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
                                                                    // half only starts a new group at a unit boundary
         const uint2 sc = *reinterpret_cast<const uint2*>(stg + GF_META_OFF + grow * 64 + 8 * g);
         const float2 s01 = __half22float2(as_h2(sc.x)), s23 = __half22float2(as_h2(sc.y));
-        yacc[0][0] = fmaf(s01.x, c[0][0][0] + c[0][1][0], yacc[0][0]);
-        yacc[0][1] = fmaf(s01.x, c[0][0][1] + c[0][1][1], yacc[0][1]);
-        yacc[0][2] = fmaf(s01.y, c[0][0][2] + c[0][1][2], yacc[0][2]);
-        yacc[0][3] = fmaf(s01.y, c[0][0][3] + c[0][1][3], yacc[0][3]);
-        yacc[1][0] = fmaf(s23.x, c[1][0][0] + c[1][1][0], yacc[1][0]);
-        yacc[1][1] = fmaf(s23.x, c[1][0][1] + c[1][1][1], yacc[1][1]);
-        yacc[1][2] = fmaf(s23.y, c[1][0][2] + c[1][1][2], yacc[1][2]);
-        yacc[1][3] = fmaf(s23.y, c[1][0][3] + c[1][1][3], yacc[1][3]);
+        yacc[0][0] = fmaf(s01.x, c[0][0], yacc[0][0]);
+        yacc[0][1] = fmaf(s01.x, c[0][1], yacc[0][1]);
+        yacc[0][2] = fmaf(s01.y, c[0][2], yacc[0][2]);
+        yacc[0][3] = fmaf(s01.y, c[0][3], yacc[0][3]);
+        yacc[1][0] = fmaf(s23.x, c[1][0], yacc[1][0]);
+        yacc[1][1] = fmaf(s23.x, c[1][1], yacc[1][1]);
+        yacc[1][2] = fmaf(s23.y, c[1][2], yacc[1][2]);
+        yacc[1][3] = fmaf(s23.y, c[1][3], yacc[1][3]);
         const float sl = __half2float(*reinterpret_cast<const __half*>(stg + GF_META_OFF + grow * 64 + 2 * lane));
         const uint32_t zw = *reinterpret_cast<const uint32_t*>(stg + GF_ZP_OFF + grow * 16 + 4 * (lane >> 3));
         const float z1 = (float)(((zw >> (4 * (lane & 7))) & 0xFu) + 1u);
