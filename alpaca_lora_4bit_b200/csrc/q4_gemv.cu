@@ -158,6 +158,10 @@ struct GemvStreamParams {
   unsigned long long* trace;                      // optional timing trace (64 slots per CTA), else null
   int whole_tiles;                                // lean kernel: CTAs get whole column tiles (no sums meet across CTAs)
   int n_groups;                                   // rows of scales / qzeros
+  // lean kernel: what is dealt to the CTAs (`share` items of `per` units each) and the multipliers
+  // ceil(2^32 / d) that turn its divisions by the grid size and by units_per_tile into one multiply
+  // (exact while dividend * d < 2^32, which the host checks)
+  unsigned share, per, magic_grid, magic_upt;
 };
 
 template <int MT>
@@ -584,8 +588,9 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
   const int nu = sp.total_units, G = gridDim.x, upt = sp.units_per_tile;
   // this CTA's units [u0, u1): an even share of all units, or (whole_tiles) of all column tiles
   // (the host keeps nu * G below 2^32, so 32-bit arithmetic is exact)
-  const unsigned share = sp.whole_tiles ? (unsigned)(nu / upt) : (unsigned)nu, per = sp.whole_tiles ? (unsigned)upt : 1u;
-  const int u0 = (int)((unsigned)blockIdx.x * share / (unsigned)G * per), u1 = (int)(((unsigned)blockIdx.x + 1u) * share / (unsigned)G * per);
+  const unsigned share = sp.share, per = sp.per;
+  const int u0 = (int)(__umulhi((unsigned)blockIdx.x * share, sp.magic_grid) * per);
+  const int u1 = (int)(__umulhi(((unsigned)blockIdx.x + 1u) * share, sp.magic_grid) * per);
   const int K = p.K, gs = p.groupsize;
   unsigned char* my_stages = smem + (size_t)warp * GF_STAGES * STG;
   unsigned char* my_aux = aux_ring + (size_t)warp * GF_STAGES * AUX;
@@ -612,7 +617,7 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
     while (c.ux >= upt) { c.ux -= upt; ++c.tile; }
   };
   Cursor cw, cx;
-  cw.u = u0 + warp; cw.tile = cw.u / upt; cw.ux = cw.u - cw.tile * upt;
+  cw.u = u0 + warp; cw.tile = (int)__umulhi((unsigned)cw.u, sp.magic_upt); cw.ux = cw.u - cw.tile * upt;
   cx = cw;
   // packed weights of this warp's n-th unit: one TMA copy, issued by lane 0
   auto issue_w = [&](int n) {
@@ -734,8 +739,7 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
     if (lane == 0) p.counters[tile] = 0u;
   };
 
-  const int tile_first = u0 / upt, tile_last = (u1 - 1) / upt;
-  const int groups_shift_ok = 0; (void)groups_shift_ok;
+  const int tile_first = (int)__umulhi((unsigned)u0, sp.magic_upt), tile_last = (int)__umulhi((unsigned)(u1 - 1), sp.magic_upt);
   int n = 0;
   for (int tile = tile_first; tile <= tile_last; ++tile) {
     const int seg_u1 = min(u1, (tile + 1) * upt);
@@ -1106,7 +1110,7 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
       const long long cost_whole = (long long)((tiles + g2 - 1) / g2) * sp.units_per_tile;
       if (cost_whole <= cost_split) sp.whole_tiles = 1;
     }
-    const bool lean_ok = (long long)sp.total_units * grid < (1ll << 32);
+    bool lean_ok = (long long)sp.total_units * grid < (1ll << 32);
     // group rows one unit (256 k-rows) can touch, counting a straddled group at either end
     sp.meta_rows = v1 ? 1 : (GEMV_UNIT_ROWS * 8 + groupsize - 1) / groupsize + ((GEMV_UNIT_ROWS * 8) % groupsize ? 1 : 0);
     if (sp.meta_rows > GEMV_META_ROWS) return fail(Q4_E_SHAPE, "gemv: groupsize=%d too small", groupsize);
@@ -1114,10 +1118,20 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
     CUtensorMap map, smap, zmap;
     if (int e = make_tmap_2d(&map, qweight, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, (uint64_t)N, (uint64_t)(K / 8),
                              (uint64_t)N * 4, GEMV_TN, GEMV_UNIT_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
+    // the lean kernel divides by the grid size and by the units per tile with 32-bit multipliers: both
+    // divisors at least 2 and the dividends small enough for the multiply to be exact
+    const int lean_grid = sp.whole_tiles && grid > N / GEMV_TN ? N / GEMV_TN : grid;
+    sp.share = sp.whole_tiles ? (unsigned)(N / GEMV_TN) : (unsigned)sp.total_units;
+    sp.per = sp.whole_tiles ? (unsigned)sp.units_per_tile : 1u;
+    lean_ok = lean_ok && lean_grid >= 2 && sp.units_per_tile >= 2 &&
+              (unsigned long long)sp.share * lean_grid * lean_grid < (1ull << 32) &&
+              ((unsigned long long)sp.total_units + 64) * sp.units_per_tile < (1ull << 32);
     if (lean_ok && !v1 && M <= 8 && (groupsize == 128 || groupsize % 256 == 0) && K % 128 == 0) {
       // lean kernel: x, scales and zero points travel with the weights by 16-byte asynchronous copies,
       // so the weights are the only tensor map it uses
-      if (sp.whole_tiles && grid > N / GEMV_TN) grid = N / GEMV_TN;
+      grid = lean_grid;
+      sp.magic_grid = (unsigned)(((1ull << 32) + grid - 1) / grid);
+      sp.magic_upt = (unsigned)(((1ull << 32) + sp.units_per_tile - 1) / sp.units_per_tile);
       CUtensorMap wsw;                                    // the same boxes, chunks swizzled by the row on their way in
       if (int e = make_tmap_2d(&wsw, qweight, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, (uint64_t)N, (uint64_t)(K / 8),
                                (uint64_t)N * 4, GEMV_TN, GEMV_UNIT_ROWS, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
