@@ -109,9 +109,9 @@ class ClockSampler:
 
 
 # DRAM bytes (read + write) of one launch of the decode kernel, averaged over the three layer shapes:
-# dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture per shape (8,758,016 / 23,466,496 /
-# 23,480,064 bytes against 8,749,056 / 23,471,616 / 23,499,264 algorithmic; summary under profiles/).
-NCU_DRAM_BYTES_PER_LAUNCH = round((8758016 + 23466496 + 23480064) / 3)
+# dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture per shape (8,754,432 / 23,463,168 /
+# 23,476,736 bytes against 8,749,056 / 23,471,616 / 23,499,264 algorithmic; summary under profiles/).
+NCU_DRAM_BYTES_PER_LAUNCH = round((8754432 + 23463168 + 23476736) / 3)
 
 
 def make_pool(copies, device, seed):
