@@ -36,6 +36,7 @@ _SIGNATURES = {
     "q4_gemv_set_trace": (c_int, [c_void_p]),
     "q4_gemm_set_trace": (c_int, [c_void_p]),
     "q4_gemm_set_variant": (c_int, [c_int]),
+    "q4_gemv_set_variant": (c_int, [c_int]),
     "q4_gemv_static_max_bytes": (c_size_t, []),
     "q4_gemv_static": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                c_int, c_int, c_int, c_int, c_int, c_int, c_uint, c_void_p]),

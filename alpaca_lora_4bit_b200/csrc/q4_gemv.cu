@@ -547,10 +547,14 @@ constexpr int GF_X_OFF = GF_ZP_OFF + 128;             // x: MR rows of 512 B at 
 constexpr int GF_X_PITCH = 528;                       // odd multiple of 16 B: the rows of a quarter-warp's loads fall on different banks
 
 template <int MR>
-__host__ __device__ constexpr int gf_aux_bytes() { return (GF_X_OFF + MR * GF_X_PITCH + 64 + 127) / 128 * 128; }
+__host__ __device__ constexpr int gf_aux_bytes(bool xc) { return xc ? GF_X_OFF : (GF_X_OFF + MR * GF_X_PITCH + 64 + 127) / 128 * 128; }
+// With XC the whole of x is re-laid out once per CTA instead of per unit: x' rows of `xc_pitch` bytes
+// (k padded to whole units, plus 16 so that neighbouring rows start on different banks) and one
+// (offset sum, plain sum) pair per 128 k and row.
+__host__ __device__ inline size_t gf_xc_bytes(int mr, int upt) { return (size_t)mr * (upt * 512 + 16) + (size_t)upt * 2 * mr * 8; }
 template <int MR>
-__host__ __device__ constexpr size_t gf_smem_bytes() {
-  return 1024 + (size_t)gf_warps<MR>() * GF_STAGES * (GEMV_UNIT_BYTES + gf_aux_bytes<MR>()) + sizeof(float) * gf_warps<MR>() * MR * GEMV_TN +
+__host__ __device__ constexpr size_t gf_smem_bytes(bool xc) {
+  return 1024 + (size_t)gf_warps<MR>() * GF_STAGES * (GEMV_UNIT_BYTES + gf_aux_bytes<MR>(xc)) + sizeof(float) * gf_warps<MR>() * MR * GEMV_TN +
          gf_warps<MR>() * GF_STAGES * 8 + 64;
 }
 
@@ -568,7 +572,7 @@ __device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
 }
 
 // TRACE: the instance that records timestamps (q4_gemv_set_trace); the other carries no trace code at all
-template <int MR, bool TRACE>
+template <int MR, bool TRACE, bool XC>
 __global__ void __launch_bounds__(gf_warps<MR>() * 32, 1)
 gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap,
                  const __grid_constant__ CUtensorMap zmap, const GemvStreamParams sp) {
@@ -576,10 +580,13 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);            // the swizzle works on address bits
   const GemvParams& p = sp.g;
   unsigned long long* const trc = TRACE ? sp.trace : nullptr;
-  constexpr int STG = GEMV_UNIT_BYTES, AUX = gf_aux_bytes<MR>();
+  constexpr int STG = GEMV_UNIT_BYTES, AUX = gf_aux_bytes<MR>(XC);
   constexpr int GF_WARPS = gf_warps<MR>(), GF_THREADS = GF_WARPS * 32;
   unsigned char* aux_ring = smem + (size_t)GF_WARPS * GF_STAGES * STG;
-  float* red = reinterpret_cast<float*>(aux_ring + (size_t)GF_WARPS * GF_STAGES * AUX);        // [16][MR][32]
+  unsigned char* xc = aux_ring + (size_t)GF_WARPS * GF_STAGES * AUX;                            // XC: x' of the whole layer
+  const int xc_pitch = sp.units_per_tile * 512 + 16;
+  float2* xc_sums = reinterpret_cast<float2*>(xc + (size_t)MR * xc_pitch);                       // XC: [K / 128][MR]
+  float* red = reinterpret_cast<float*>(xc + (XC ? gf_xc_bytes(MR, sp.units_per_tile) : 0));    // [16][MR][32]
   uint64_t* full = reinterpret_cast<uint64_t*>(red + GF_WARPS * MR * GEMV_TN);                  // [16][2]
   volatile int* flags = reinterpret_cast<volatile int*>(full + GF_WARPS * GF_STAGES);          // [0] abort
 
@@ -642,10 +649,12 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
     if (cx.u >= u1) return;
     unsigned char* stg = my_aux + (size_t)(n % GF_STAGES) * AUX;
     unsigned char* dst = stg + GF_X_OFF;
-    const int k = cx.ux * 256 + 8 * lane;
+    if constexpr (!XC) {
+      const int k = cx.ux * 256 + 8 * lane;
 #pragma unroll
-    for (int r = 0; r < MR; ++r)
-      cp_async16_zfill(dst + r * GF_X_PITCH + 16 * lane, p.x + (size_t)(r < p.M ? r : 0) * K + (k < K ? k : 0), r < p.M && k < K);
+      for (int r = 0; r < MR; ++r)
+        cp_async16_zfill(dst + r * GF_X_PITCH + 16 * lane, p.x + (size_t)(r < p.M ? r : 0) * K + (k < K ? k : 0), r < p.M && k < K);
+    }
     {
       // lanes 10..31 run the same address arithmetic and copy nothing (a predicated copy, not a branch)
       const int grow0 = sp.group_shift >= 0 ? ((cx.ux * GEMV_UNIT_STEPS) >> sp.group_shift) : (cx.ux * GEMV_UNIT_ROWS * 8) / gs;
@@ -671,6 +680,26 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
   if (threadIdx.x == 0) trace_mark_ns(trc, 42);
   issue_x(0);
   issue_x(1);
+  if constexpr (XC) {
+    // x' of all rows and the sums of every 128 k, once for the CTA: 16 lanes share one 128-k chunk
+    const int blocks = sp.units_per_tile * 32;           // 8-element blocks per padded row (a multiple of 16)
+    for (int idx = threadIdx.x; idx < MR * blocks; idx += GF_THREADS) {
+      const int m = idx / blocks, blk = idx - m * blocks;
+      const bool ok = m < p.M && 8 * blk < K;
+      const uint4 v = ok ? __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)m * K + 8 * blk)) : make_uint4(0u, 0u, 0u, 0u);
+      const __half2 h01 = as_h2(v.x), h23 = as_h2(v.y), h45 = as_h2(v.z), h67 = as_h2(v.w);
+      const __half2 sixteenth = as_h2(0x2C002C00u);
+      const __half2 e04 = __lows2half2(h01, h45), o15 = __hmul2(__highs2half2(h01, h45), sixteenth);
+      const __half2 e26 = __lows2half2(h23, h67), o37 = __hmul2(__highs2half2(h23, h67), sixteenth);
+      *reinterpret_cast<uint4*>(xc + (size_t)m * xc_pitch + 16 * blk) = make_uint4(as_u32(e04), as_u32(o15), as_u32(e26), as_u32(o37));
+      const float2 f01 = __half22float2(h01), f23 = __half22float2(h23), f45 = __half22float2(h45), f67 = __half22float2(h67);
+      float se = (f01.x + f23.x) + (f45.x + f67.x), so = (f01.y + f23.y) + (f45.y + f67.y);
+#pragma unroll
+      for (int d = 8; d >= 1; d >>= 1) { se += __shfl_xor_sync(0xffffffffu, se, d); so += __shfl_xor_sync(0xffffffffu, so, d); }
+      if ((lane & 15) == 0) xc_sums[(blk >> 4) * MR + m] = make_float2(1024.f * se + 64.f * so, se + so);
+    }
+    __syncthreads();
+  }
   if (threadIdx.x == 0) trace_mark(trc, 0);
 
   const int g = lane >> 2, t = lane & 3;
@@ -759,9 +788,10 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
       const unsigned char* wst = my_stages + (size_t)st * STG;
       unsigned char* stg = my_aux + (size_t)st * AUX;
       // ---- x: rewrite this lane's 8 elements per batch row in MMA order, and the unit's sums of x ----
-      float2* sums = reinterpret_cast<float2*>(stg + GF_X_OFF + MR * GF_X_PITCH);      // [2 chunks][MR]
+      // (XC: both are in the CTA's x' already)
+      float2* sums = XC ? xc_sums + 2 * ux * MR : reinterpret_cast<float2*>(stg + GF_X_OFF + MR * GF_X_PITCH);      // [2 chunks][MR]
 #pragma unroll
-      for (int r = 0; r < MR; ++r) {
+      for (int r = 0; r < (XC ? 0 : MR); ++r) {
         uint4* px = reinterpret_cast<uint4*>(stg + GF_X_OFF + r * GF_X_PITCH + 16 * lane);
         const uint4 v = *px;
         const __half2 h01 = as_h2(v.x), h23 = as_h2(v.y), h45 = as_h2(v.z), h67 = as_h2(v.w);
@@ -776,10 +806,11 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
         // odd elements sit in x' as x/16: their 1024 offset comes back as 64 x
         if ((lane & 15) == 0) sums[(lane >> 4) * MR + r] = make_float2(1024.f * se + 64.f * so, se + so);
       }
-      __syncwarp();
+      if constexpr (!XC) __syncwarp();
       // lanes of batch rows that do not exist feed row 0 again: an MMA output column depends on its own
       // input column only, and the columns beyond MR are never stored
-      const uint4* xq = reinterpret_cast<const uint4*>(stg + GF_X_OFF + (g < MR ? g : 0) * GF_X_PITCH) + 2 * t;
+      const uint4* xq = XC ? reinterpret_cast<const uint4*>(xc + (size_t)(g < MR ? g : 0) * xc_pitch + 512 * ux) + 2 * t
+                           : reinterpret_cast<const uint4*>(stg + GF_X_OFF + (g < MR ? g : 0) * GF_X_PITCH) + 2 * t;
 #pragma unroll
       for (int h = 0; h < 2; ++h) {
         float c[2][4];                                  // raw sums of the half: columns 4g, 4g+1 | 4g+2, 4g+3
@@ -855,7 +886,7 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
 template <int MT>
 __global__ void __launch_bounds__(GEMV_THREADS)
 gemv_act_kernel(const GemvParams p, int G, int copies) {
-  extern __shared__ __align__(16) unsigned char smem_raw[];
+  extern __shared__ __align__(128) unsigned char smem_raw[];
   float* red = reinterpret_cast<float*>(smem_raw);                              // [8][MT*8][32]
   __half2* tab = reinterpret_cast<__half2*>(smem_raw + sizeof(float) * GEMV_WARPS * MT * 8 * GEMV_TN);  // [G][4 copies][32]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -941,6 +972,7 @@ static void gemv_plan(int K, int N, int& S, int& steps_per_split) {
 }
 
 static unsigned long long* g_trace = nullptr;                 // set by q4_gemv_set_trace
+static int g_gemv_variant = 0;                                // set by q4_gemv_set_variant
 
 constexpr size_t GEMV_STATUS_OFFSET = GEMV_WS_HEAD - 4;      // status word: last 4 bytes of the head
 constexpr int GEMV_MAX_CTAS = 512;                            // upper bound on SMs for workspace sizing
@@ -969,15 +1001,17 @@ static int launch_stream(const CUtensorMap& map, const CUtensorMap& smap, const 
   return check_cuda(cudaLaunchKernelEx(&cfg, gemv_stream_kernel<MT, FAST, XS>, map, smap, zmap, sp), "gemv launch");
 }
 
-template <int MR, bool TRACE>
-static int launch_fast(const CUtensorMap& map, const CUtensorMap& smap, const CUtensorMap& zmap,
-                       const GemvStreamParams& sp, int grid, cudaStream_t st) {
+constexpr size_t GF_SMEM_LIMIT = 227 * 1024;
+
+template <int MR, bool TRACE, bool XC>
+static int launch_fast_xc(const CUtensorMap& map, const GemvStreamParams& sp, int grid, cudaStream_t st) {
   static bool attr_done[64] = {false};
   int dev = 0;
   cudaGetDevice(&dev);
-  const size_t smem = gf_smem_bytes<MR>();
+  const size_t smem = gf_smem_bytes<MR>(XC) + (XC ? gf_xc_bytes(MR, sp.units_per_tile) : 0);
   if (dev >= 0 && dev < 64 && !attr_done[dev]) {
-    if (int e = check_cuda(cudaFuncSetAttribute(gemv_fast_kernel<MR, TRACE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem),
+    const size_t most = XC ? GF_SMEM_LIMIT : smem;       // XC: the size follows K, the attribute is set once
+    if (int e = check_cuda(cudaFuncSetAttribute(gemv_fast_kernel<MR, TRACE, XC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most),
                            "gemv smem attribute")) return e;
     attr_done[dev] = true;
   }
@@ -988,7 +1022,21 @@ static int launch_fast(const CUtensorMap& map, const CUtensorMap& smap, const CU
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at; cfg.numAttrs = 1;
-  return check_cuda(cudaLaunchKernelEx(&cfg, gemv_fast_kernel<MR, TRACE>, map, smap, zmap, sp), "gemv launch");
+  return check_cuda(cudaLaunchKernelEx(&cfg, gemv_fast_kernel<MR, TRACE, XC>, map, map, map, sp), "gemv launch");
+}
+
+// x' of the whole layer per CTA when it fits beside the rings and the CTA has more than one column
+// tile's worth of units to amortise it over; else every unit brings and re-lays its own slice
+template <int MR, bool TRACE>
+static int launch_fast(const CUtensorMap& map, const GemvStreamParams& sp, int grid, cudaStream_t st) {
+  const bool fits = gf_smem_bytes<MR>(true) + gf_xc_bytes(MR, sp.units_per_tile) <= GF_SMEM_LIMIT;
+  const bool pays = (long long)sp.total_units > (long long)grid * sp.units_per_tile;
+  // (measured: with one row the per-unit slice is as fast or faster at every shape tried - the re-layout
+  //  is 10 % of a unit's instructions and the per-CTA pass delays the first unit; from two rows on the
+  //  per-CTA pass wins 5-15 % wherever a CTA has more than one tile)
+  const bool xc = g_gemv_variant == 2 || (g_gemv_variant == 0 && pays && MR >= 2);
+  if (fits && xc) return launch_fast_xc<MR, TRACE, true>(map, sp, grid, st);
+  return launch_fast_xc<MR, TRACE, false>(map, sp, grid, st);
 }
 
 }  // namespace q4
@@ -1020,6 +1068,12 @@ extern "C" void q4_layer_destroy(q4_layer_t* layer) { delete layer; }
 
 extern "C" int q4_gemv_set_trace(void* device_buffer) {
   g_trace = (unsigned long long*)device_buffer;
+  return Q4_OK;
+}
+
+extern "C" int q4_gemv_set_variant(int variant) {
+  if (variant < 0 || variant > 2) return fail(Q4_E_BADARG, "gemv: variant %d outside 0..2", variant);
+  g_gemv_variant = variant;
   return Q4_OK;
 }
 
@@ -1135,9 +1189,9 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
       CUtensorMap wsw;                                    // the same boxes, chunks swizzled by the row on their way in
       if (int e = make_tmap_2d(&wsw, qweight, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, (uint64_t)N, (uint64_t)(K / 8),
                                (uint64_t)N * 4, GEMV_TN, GEMV_UNIT_ROWS, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
-      if (g_trace && M == 1) return launch_fast<1, true>(wsw, wsw, wsw, sp, grid, st);
-      return M == 1 ? launch_fast<1, false>(wsw, wsw, wsw, sp, grid, st) : M == 2 ? launch_fast<2, false>(wsw, wsw, wsw, sp, grid, st)
-           : M <= 4 ? launch_fast<4, false>(wsw, wsw, wsw, sp, grid, st) : launch_fast<8, false>(wsw, wsw, wsw, sp, grid, st);
+      if (g_trace && M == 1) return launch_fast<1, true>(wsw, sp, grid, st);
+      return M == 1 ? launch_fast<1, false>(wsw, sp, grid, st) : M == 2 ? launch_fast<2, false>(wsw, sp, grid, st)
+           : M <= 4 ? launch_fast<4, false>(wsw, sp, grid, st) : launch_fast<8, false>(wsw, sp, grid, st);
     }
     sp.whole_tiles = 0;
     if (int e = make_tmap_2d(&smap, scales, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (uint64_t)N, (uint64_t)G,

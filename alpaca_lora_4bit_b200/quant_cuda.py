@@ -281,6 +281,12 @@ def gemm_set_variant(variant: int) -> None:
     _lib.check(_lib.lib().q4_gemm_set_variant(int(variant)), "gemm_set_variant")
 
 
+def gemv_set_variant(variant: int) -> None:
+    """How the sequential-group decode kernel gets x: 0 = chosen per shape (default), 1 = every unit brings its
+    own slice, 2 = every CTA re-lays the whole of x out once (where it fits shared memory)."""
+    _lib.check(_lib.lib().q4_gemv_set_variant(int(variant)), "gemv_set_variant")
+
+
 def device_status() -> int:
     """Status word of the fused kernels (synchronises): 0 unless a bounded device-side wait expired."""
     import ctypes

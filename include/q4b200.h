@@ -167,6 +167,11 @@ int q4_gemm_set_trace(void* device_buffer);
  * otherwise), 1 = always the single-CTA kernel, 2 / 3 = always the CTA-pair kernel with 256- /
  * 512-row tiles (calls it cannot serve then fail with Q4_E_SHAPE).  For tests and measurements. */
 int q4_gemm_set_variant(int variant);
+/* How the sequential-group decode kernel gets x (process-wide; no reference counterpart): 0 = choose
+ * per shape (the default: with two or more rows every CTA re-lays the whole of x out once when it has more
+ * than one column tile's worth of units and x fits its shared memory; else every 4 KiB unit brings its own slice),
+ * 1 = always per unit, 2 = per CTA wherever it fits.  For tests and measurements. */
+int q4_gemv_set_variant(int variant);
 
 #ifdef __cplusplus
 }

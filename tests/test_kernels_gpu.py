@@ -254,6 +254,28 @@ def test_gemv_work_dealing_modes(K, N, M):
         assert int(ws[:65536].view(torch.int32).abs().sum()) == 0
 
 
+@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("K,N", [(4096, 4096), (1024, 5120), (11008, 4096), (4224, 9600), (8192, 8192)])
+def test_gemv_x_per_unit_and_per_cta_agree(K, N, M):
+    """The lean decode kernel with x brought and re-laid per 4 KiB unit (variant 1) and with the whole of x
+    re-laid once per CTA (variant 2; K = 4224 has a half-filled last unit whose padding must read as zero):
+    both within tolerance of the oracle, and the automatic choice equal to one of them bit for bit."""
+    layer = synth.make_layer(K, N, 128, False, seed=K // 7 + N)
+    x = synth.make_acts(M, K, seed=3 + M)
+    want = orc.gemv_fp32(x, layer.qweight, layer.scales, layer.qzeros, layer.g_idx)
+    got = {}
+    try:
+        for v in (1, 2, 0):
+            quant_cuda.gemv_set_variant(v)
+            got[v] = gemv_gpu(layer, x, torch.float32)
+            assert rel_fro(got[v], want) <= REL_TOL, v
+    finally:
+        quant_cuda.gemv_set_variant(0)
+    assert torch.equal(got[0], got[1]) or torch.equal(got[0], got[2])
+    torch.cuda.synchronize()
+    assert quant_cuda.device_status() == 0
+
+
 def test_workspace_counters_return_to_zero():
     layer = synth.make_layer(4096, 4096, 128, False, seed=3)
     gemv_gpu(layer, synth.make_acts(1, 4096), torch.float16)
