@@ -1170,10 +1170,10 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
     if (sp.meta_rows > GEMV_META_ROWS) return fail(Q4_E_SHAPE, "gemv: groupsize=%d too small", groupsize);
     if (!aligned16(qzeros)) return fail(Q4_E_ALIGN, "gemv: qzeros must be 16-byte aligned");
     CUtensorMap map, smap, zmap;
-    if (int e = make_tmap_2d(&map, qweight, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, (uint64_t)N, (uint64_t)(K / 8),
-                             (uint64_t)N * 4, GEMV_TN, GEMV_UNIT_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
     // the lean kernel divides by the grid size and by the units per tile with 32-bit multipliers: both
     // divisors at least 2 and the dividends small enough for the multiply to be exact
+    // (a layer with so many units that an even split would overflow them is dealt by whole tiles)
+    if (!sp.whole_tiles && (unsigned long long)sp.total_units * grid * grid >= (1ull << 32) && N / GEMV_TN >= grid) sp.whole_tiles = 1;
     const int lean_grid = sp.whole_tiles && grid > N / GEMV_TN ? N / GEMV_TN : grid;
     sp.share = sp.whole_tiles ? (unsigned)(N / GEMV_TN) : (unsigned)sp.total_units;
     sp.per = sp.whole_tiles ? (unsigned)sp.units_per_tile : 1u;
@@ -1194,6 +1194,8 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
            : M <= 4 ? launch_fast<4, false>(wsw, sp, grid, st) : launch_fast<8, false>(wsw, sp, grid, st);
     }
     sp.whole_tiles = 0;
+    if (int e = make_tmap_2d(&map, qweight, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, (uint64_t)N, (uint64_t)(K / 8),
+                             (uint64_t)N * 4, GEMV_TN, GEMV_UNIT_ROWS, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
     if (int e = make_tmap_2d(&smap, scales, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (uint64_t)N, (uint64_t)G,
                              (uint64_t)N * 2, GEMV_TN, sp.meta_rows, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
     if (!v1) {
