@@ -74,6 +74,27 @@ def lib() -> ctypes.CDLL:
     return _lib
 
 
+_layer_gemv_call = None
+
+
+def layer_gemv_call():
+    """``q4_layer_gemv`` as a callable of seven Python ints that returns the C return code: the ``_q4call``
+    extension module (built in-tree with the C compiler on first use), bound to the loaded library.  It
+    makes the same foreign call as the ctypes binding without ctypes' per-argument conversion."""
+    global _layer_gemv_call
+    if _layer_gemv_call is not None:
+        return _layer_gemv_call
+    handle = lib()
+    with _lock:
+        if _layer_gemv_call is None:
+            from . import build as _build
+            _build.build_call()
+            from . import _q4call
+            _q4call.bind(ctypes.cast(handle.q4_layer_gemv, c_void_p).value)
+            _layer_gemv_call = _q4call.layer_gemv
+    return _layer_gemv_call
+
+
 def check(code: int, what: str) -> None:
     if code != 0:
         msg = lib().q4_last_error_string().decode("utf-8", "replace")

@@ -68,5 +68,24 @@ def build(force: bool = False, verbose: bool = False) -> str:
     return LIB
 
 
+CALL_SRC = os.path.join(CSRC, "host", "q4call.c")
+CALL_LIB = os.path.join(PKG, "_q4call.so")
+
+
+def build_call(force: bool = False) -> str:
+    """Builds ``_q4call.so`` (the CPython module that makes the per-token foreign call) with the C compiler."""
+    if not force and os.path.exists(CALL_LIB) and os.path.getmtime(CALL_LIB) >= os.path.getmtime(CALL_SRC):
+        return CALL_LIB
+    import sysconfig
+    cc = shutil.which("gcc") or shutil.which("cc")
+    if cc is None:
+        raise RuntimeError("no C compiler; _q4call.so cannot be built")
+    tmp = CALL_LIB + ".tmp"
+    subprocess.check_call([cc, "-O2", "-shared", "-fPIC", "-I", sysconfig.get_paths()["include"], CALL_SRC, "-o", tmp])
+    os.replace(tmp, CALL_LIB)
+    return CALL_LIB
+
+
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    print(build_call(force="--force" in sys.argv))

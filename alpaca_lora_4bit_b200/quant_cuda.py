@@ -135,6 +135,15 @@ except AttributeError:                                    # pragma: no cover
     _current_device = torch.cuda.current_device
 
 
+_layer_gemv = None             # the per-token foreign call, resolved on first use
+
+
+def _bind_layer_gemv():
+    global _layer_gemv
+    _layer_gemv = _lib.layer_gemv_call()
+    return _layer_gemv
+
+
 def _drop_plan(key):
     p = _plans.pop(key, None)
     if p is not None and p.handle:
@@ -184,7 +193,7 @@ def decode_planned(x, qweight, scales, zeros, groupsize, max_rows):
     if w is None:
         t = _lib.workspace_for(p.device, st)
         w = _decode_ws[(p.index, st)] = (t.data_ptr(), t.numel(), t)
-    rc = _lib.lib().q4_layer_gemv(p.handle, x.data_ptr(), y.data_ptr(), M, w[0], w[1], st)
+    rc = (_layer_gemv or _bind_layer_gemv())(p.handle, x.data_ptr(), y.data_ptr(), M, w[0], w[1], st)
     if rc:
         _lib.check(rc, "layer_gemv")
     return y

@@ -73,3 +73,21 @@ def test_facade_refuses_cpu_tensors():
                                       torch.zeros((1, 16), dtype=torch.int32), torch.zeros(128, dtype=torch.int32))
     with pytest.raises(NotImplementedError):
         quant_cuda.vecquant3matmul()
+
+
+def test_call_module_makes_the_same_foreign_call():
+    """The `_q4call` extension is bound to the loaded library and returns its codes: a null handle is
+    refused on the host (no device involved), the wrong number of arguments raises."""
+    call = _lib.layer_gemv_call()
+    assert call(0, 0x1000, 0x1000, 1, 0, 0, 0) == -1
+    assert b"null handle" in _lib.lib().q4_last_error_string()
+    L = _lib.lib()
+    h = ctypes.c_void_p()
+    fake = ctypes.c_void_p(0x1000)
+    assert L.q4_layer_create(ctypes.byref(h), fake, fake, fake, 128, 128, 1, 128) == 0
+    assert call(h.value, 0x1000, 0x1000, 17, 0, 0, 0) == -2            # M out of range: q4_gemv's own check
+    L.q4_layer_destroy(h)
+    with pytest.raises(TypeError):
+        call(0, 0, 0)
+    with pytest.raises(ValueError):
+        call(0, 0, 0, -5, 0, 0, 0)
