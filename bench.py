@@ -178,7 +178,7 @@ def run_ours(args, rank, world, local_rank):
             barrier()
             t_load = time.time()
             n_warm = 0
-            while n_warm < max(args.warmup, 3) or time.time() - t_load < 0.4:
+            while n_warm < max(args.warmup, 3) or time.time() - t_load < args.load_seconds:
                 graph.replay()
                 n_warm += 1
                 if n_warm % 64 == 0:
@@ -516,6 +516,9 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-gemm", action="store_true", help="skip the M=2048 fused GEMM leg")
     ap.add_argument("--gemm-shape", default="", help="restrict the GEMM leg to one KxN shape, e.g. 5120x13824 (for profiler captures)")
+    ap.add_argument("--load-seconds", type=float, default=0.4,
+                    help="keep replaying the decode graph for at least this long before the timed region, so that the clock "
+                         "sampler sees the GPU under this load (0 for profiler captures: warm-up replays only)")
     ap.add_argument("--decode-shape", default="", help="decode pool of one KxN layer shape instead of the three LLaMA-7B shapes, "
                                                        "e.g. 8192x28672 (for profiler captures; not the headline workload)")
     ap.add_argument("--finetune-steps", type=int, default=5, help="timed LLaMA-7B LoRA finetune steps (0 = skip)")
