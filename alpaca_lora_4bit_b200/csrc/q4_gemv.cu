@@ -1153,13 +1153,13 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
     if (grid > sp.total_units) grid = sp.total_units;
     // Lean kernel: an even share of all units per CTA makes column tiles straddle CTAs, and the sums
     // of a straddled tile meet through global memory (a fence, an atomic and a read back to back at
-    // the end of the CTA, about as long as six units take).  Dealing whole tiles avoids that at the
-    // price of an uneven load; take whichever ends sooner.
+    // the end of the CTA: measured 3 to 4 us per launch, as long as a CTA takes for 40 units).  Dealing
+    // whole tiles avoids that at the price of an uneven load; take whichever ends sooner.
     sp.whole_tiles = 0;
     sp.n_groups = G;
     {
       const int tiles = N / GEMV_TN;
-      const long long cost_split = (sp.total_units + grid - 1) / grid + 12;
+      const long long cost_split = (sp.total_units + grid - 1) / grid + 40;
       const int g2 = grid < tiles ? grid : tiles;
       const long long cost_whole = (long long)((tiles + g2 - 1) / g2) * sp.units_per_tile;
       if (cost_whole <= cost_split) sp.whole_tiles = 1;
