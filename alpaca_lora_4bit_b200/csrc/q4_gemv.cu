@@ -371,8 +371,15 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
     __threadfence();
     for (int r = 0; r < p.M; ++r) {
       float v = 0.f;
-      for (int cc = c_first; cc <= c_last; ++cc)
-        v += __ldcg(sp.cta_part + ((size_t)cc * 2 + (cc == c_first ? 1 : 0)) * (MT * 8) * GEMV_TN + r * GEMV_TN + col);
+      // four contributors' partials in flight at a time, added in CTA order (an absent one adds +0)
+      for (int cc = c_first; cc <= c_last; cc += 4) {
+        float t4[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          t4[i] = cc + i <= c_last ? __ldcg(sp.cta_part + ((size_t)(cc + i) * 2 + (cc + i == c_first ? 1 : 0)) * (MT * 8) * GEMV_TN + r * GEMV_TN + col) : 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v += t4[i];
+      }
       store_y(p, r, tc0 + col, v);
     }
     if (lane == 0) p.counters[tile] = 0u;                // ready for the next launch
@@ -761,8 +768,15 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
     __threadfence();
     for (int r = 0; r < p.M; ++r) {
       float v = 0.f;
-      for (int cc = c_first; cc <= c_last; ++cc)
-        v += __ldcg(sp.cta_part + ((size_t)cc * 2 + (cc == c_first ? 1 : 0)) * 16 * GEMV_TN + r * GEMV_TN + col);
+      // four contributors' partials in flight at a time, added in CTA order (an absent one adds +0)
+      for (int cc = c_first; cc <= c_last; cc += 4) {
+        float t4[4];
+#pragma unroll
+        for (int i = 0; i < 4; ++i)
+          t4[i] = cc + i <= c_last ? __ldcg(sp.cta_part + ((size_t)(cc + i) * 2 + (cc + i == c_first ? 1 : 0)) * 16 * GEMV_TN + r * GEMV_TN + col) : 0.f;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) v += t4[i];
+      }
       store_y(p, r, tc0 + col, v);
     }
     if (lane == 0) p.counters[tile] = 0u;
