@@ -44,7 +44,8 @@ extern "C" {
 #define Q4_GEMV_ACCUMULATE 1u  /* y += x*W instead of y = x*W (the reference kernels add into `mul`) */
 #define Q4_GEMV_ACT_ORDER  2u  /* take the group of every row from g_idx (else k / groupsize)      */
 #define Q4_GEMV_V1         4u  /* v1 layer: scales fp16 [N]; `qzeros` points at fp16 zeros [N];
-                                  W = scales[n]*q - zeros[n]; G, groupsize and g_idx are ignored */
+                                  W = scales[n]*q - zeros[n]; G, groupsize and g_idx are ignored;
+                                  K must be a multiple of 256 (Q4_E_SHAPE otherwise) */
 
 typedef void* q4_stream_t;     /* a cudaStream_t */
 

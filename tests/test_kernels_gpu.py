@@ -182,6 +182,19 @@ def test_gemv_ragged_sizes(K, N, g, M):
     assert rel_fro(gemv_gpu(layer, x, torch.float32), want) <= REL_TOL
 
 
+@pytest.mark.parametrize("K,N,g,M", [(1056, 64, 32, 1), (4160, 2048, 128, 1), (4160, 2048, 128, 12), (4224, 2048, 384, 1),
+                                     (4224, 2048, 384, 5), (4224, 1024, 128, 13), (1152, 512, 128, 3)])
+def test_gemv_half_filled_last_unit(K, N, g, M):
+    """Layers whose last 256-row unit is partly out of bounds, with groups of 128-row multiples: the lean
+    kernel where it applies (K a multiple of 128, groups of 128), the general streaming instance elsewhere."""
+    layer = synth.make_layer(K, N, g, False, seed=K + N + M)
+    x = synth.make_acts(M, K, seed=3)
+    want = orc.gemv_fp32(x, layer.qweight, layer.scales, layer.qzeros, layer.g_idx)
+    assert rel_fro(gemv_gpu(layer, x, torch.float32), want) <= REL_TOL
+    torch.cuda.synchronize()
+    assert quant_cuda.device_status() == 0
+
+
 def test_gemv_accumulates_bias_and_is_reproducible():
     layer = synth.make_layer(4096, 4096, 128, False, seed=77)
     x = synth.make_acts(4, 4096, seed=8)
