@@ -579,7 +579,8 @@ __device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
 }
 
 // TRACE: the instance that records timestamps (q4_gemv_set_trace); the other carries no trace code at all
-template <int MR, bool TRACE, bool XC>
+// V1: the first layer format - one scale and one fp16 zero term per column (W = s q - zero), no groups
+template <int MR, bool TRACE, bool XC, bool V1>
 __global__ void __launch_bounds__(gf_warps<MR>() * 32, 1)
 gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap,
                  const __grid_constant__ CUtensorMap zmap, const GemvStreamParams sp) {
@@ -645,12 +646,14 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
   // then every lane arrives on the barrier.  One TMA copy per unit instead of three: issuing a
   // TMA copy occupies the issuing thread for some 200 cycles, an asynchronous 16-byte copy does not.
   // lanes 0..7 copy 16 bytes of one of the unit's two scale rows, lanes 8 and 9 one of its two zero-point rows
-  const bool meta_lane = lane < 10;
-  const int meta_sel = lane < 8 ? (lane >> 2) : (lane - 8);
+  // (V1: lanes 0..3 the one scale row, lanes 8..11 the 64 bytes of fp16 zero terms of the tile's 32 columns)
+  const bool meta_lane = lane < (V1 ? 12 : 10);
+  const int meta_sel = lane < 8 ? (lane >> 2) : (V1 ? 0 : lane - 8);
   const unsigned char* meta_src = lane < 8 ? reinterpret_cast<const unsigned char*>(p.scales + 8 * (lane & 3))
+                                : V1       ? reinterpret_cast<const unsigned char*>(p.qzeros) + 16 * (lane - 8)
                                            : reinterpret_cast<const unsigned char*>(p.qzeros);
   const size_t meta_pitch = lane < 8 ? (size_t)p.N * 2 : (size_t)(p.N >> 3) * 4;        // bytes per group row
-  const int meta_tile = lane < 8 ? GEMV_TN * 2 : (GEMV_TN / 8) * 4;                      // bytes per column tile
+  const int meta_tile = (lane < 8 || V1) ? GEMV_TN * 2 : (GEMV_TN / 8) * 4;              // bytes per column tile
   const int meta_dst = lane < 8 ? GF_META_OFF + 16 * lane : GF_ZP_OFF + 16 * (lane - 8);
   auto issue_x = [&](int n) {
     if (cx.u >= u1) return;
@@ -868,12 +871,21 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
         yacc[1][2] = fmaf(s23.y, c[1][2], yacc[1][2]);
         yacc[1][3] = fmaf(s23.y, c[1][3], yacc[1][3]);
         const float sl = __half2float(*reinterpret_cast<const __half*>(stg + GF_META_OFF + grow * 64 + 2 * lane));
-        const uint32_t zw = *reinterpret_cast<const uint32_t*>(stg + GF_ZP_OFF + grow * 16 + 4 * (lane >> 3));
-        const float z1 = (float)(((zw >> (4 * (lane & 7))) & 0xFu) + 1u);
+        if constexpr (V1) {
+          const float zf = __half2float(*reinterpret_cast<const __half*>(stg + GF_ZP_OFF + 2 * lane));
 #pragma unroll
-        for (int r = 0; r < MR; ++r) {
-          const float2 e = sums[h * MR + r];
-          ycorr[r] = fmaf(sl, fmaf(z1, e.y, e.x), ycorr[r]);
+          for (int r = 0; r < MR; ++r) {
+            const float2 e = sums[h * MR + r];
+            ycorr[r] = fmaf(zf, e.y, fmaf(sl, e.x, ycorr[r]));       // y -= s * offset_sum + zero * x_sum
+          }
+        } else {
+          const uint32_t zw = *reinterpret_cast<const uint32_t*>(stg + GF_ZP_OFF + grow * 16 + 4 * (lane >> 3));
+          const float z1 = (float)(((zw >> (4 * (lane & 7))) & 0xFu) + 1u);
+#pragma unroll
+          for (int r = 0; r < MR; ++r) {
+            const float2 e = sums[h * MR + r];
+            ycorr[r] = fmaf(sl, fmaf(z1, e.y, e.x), ycorr[r]);
+          }
         }
       }
       __syncwarp();
@@ -1017,7 +1029,7 @@ static int launch_stream(const CUtensorMap& map, const CUtensorMap& smap, const 
 
 constexpr size_t GF_SMEM_LIMIT = 227 * 1024;
 
-template <int MR, bool TRACE, bool XC>
+template <int MR, bool TRACE, bool XC, bool V1>
 static int launch_fast_xc(const CUtensorMap& map, const GemvStreamParams& sp, int grid, cudaStream_t st) {
   static bool attr_done[64] = {false};
   int dev = 0;
@@ -1025,7 +1037,7 @@ static int launch_fast_xc(const CUtensorMap& map, const GemvStreamParams& sp, in
   const size_t smem = gf_smem_bytes<MR>(XC) + (XC ? gf_xc_bytes(MR, sp.units_per_tile) : 0);
   if (dev >= 0 && dev < 64 && !attr_done[dev]) {
     const size_t most = XC ? GF_SMEM_LIMIT : smem;       // XC: the size follows K, the attribute is set once
-    if (int e = check_cuda(cudaFuncSetAttribute(gemv_fast_kernel<MR, TRACE, XC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most),
+    if (int e = check_cuda(cudaFuncSetAttribute(gemv_fast_kernel<MR, TRACE, XC, V1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most),
                            "gemv smem attribute")) return e;
     attr_done[dev] = true;
   }
@@ -1036,7 +1048,7 @@ static int launch_fast_xc(const CUtensorMap& map, const GemvStreamParams& sp, in
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at; cfg.numAttrs = 1;
-  return check_cuda(cudaLaunchKernelEx(&cfg, gemv_fast_kernel<MR, TRACE, XC>, map, map, map, sp), "gemv launch");
+  return check_cuda(cudaLaunchKernelEx(&cfg, gemv_fast_kernel<MR, TRACE, XC, V1>, map, map, map, sp), "gemv launch");
 }
 
 // x' of the whole layer per CTA when it fits beside the rings and the CTA has more than one column
@@ -1049,8 +1061,14 @@ static int launch_fast(const CUtensorMap& map, const GemvStreamParams& sp, int g
   //  is 10 % of a unit's instructions and the per-CTA pass delays the first unit; from two rows on the
   //  per-CTA pass wins 5-15 % wherever a CTA has more than one tile)
   const bool xc = g_gemv_variant == 2 || (g_gemv_variant == 0 && pays && MR >= 2);
-  if (fits && xc) return launch_fast_xc<MR, TRACE, true>(map, sp, grid, st);
-  return launch_fast_xc<MR, TRACE, false>(map, sp, grid, st);
+  if (sp.g.v1) {
+    if constexpr (!TRACE) {
+      if (fits && xc) return launch_fast_xc<MR, false, true, true>(map, sp, grid, st);
+      return launch_fast_xc<MR, false, false, true>(map, sp, grid, st);
+    }
+  }
+  if (fits && xc) return launch_fast_xc<MR, TRACE, true, false>(map, sp, grid, st);
+  return launch_fast_xc<MR, TRACE, false, false>(map, sp, grid, st);
 }
 
 }  // namespace q4
@@ -1134,7 +1152,7 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
 
   // 9..16 rows on a layer the lean kernel takes: two launches of it (8 rows, then the rest) end sooner
   // than one launch of the general streaming kernel
-  if (M > 8 && !act && !v1 && (groupsize == 128 || groupsize % 256 == 0) && K % 128 == 0) {
+  if (M > 8 && !act && (groupsize == 128 || groupsize % 256 == 0) && K % 128 == 0) {
     if (int e = q4_gemv(x, qweight, y, scales, qzeros, g_idx, bias, 8, K, N, G, groupsize, y_dtype, flags, workspace, workspace_bytes, stream))
       return e;
     const size_t ybytes = (size_t)N * (y_dtype == Q4_F32 ? 4 : 2);
@@ -1197,7 +1215,7 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
     lean_ok = lean_ok && lean_grid >= 2 && sp.units_per_tile >= 2 &&
               (unsigned long long)sp.share * lean_grid * lean_grid < (1ull << 32) &&
               ((unsigned long long)sp.total_units + 64) * sp.units_per_tile < (1ull << 32);
-    if (lean_ok && !v1 && M <= 8 && (groupsize == 128 || groupsize % 256 == 0) && K % 128 == 0) {
+    if (lean_ok && M <= 8 && (groupsize == 128 || groupsize % 256 == 0) && K % 128 == 0) {
       // lean kernel: x, scales and zero points travel with the weights by 16-byte asynchronous copies,
       // so the weights are the only tensor map it uses
       grid = lean_grid;
@@ -1206,7 +1224,7 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
       CUtensorMap wsw;                                    // the same boxes, chunks swizzled by the row on their way in
       if (int e = make_tmap_2d(&wsw, qweight, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, (uint64_t)N, (uint64_t)(K / 8),
                                (uint64_t)N * 4, GEMV_TN, GEMV_UNIT_ROWS, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
-      if (g_trace && M == 1) return launch_fast<1, true>(wsw, sp, grid, st);
+      if (g_trace && M == 1 && !v1) return launch_fast<1, true>(wsw, sp, grid, st);
       return M == 1 ? launch_fast<1, false>(wsw, sp, grid, st) : M == 2 ? launch_fast<2, false>(wsw, sp, grid, st)
            : M <= 4 ? launch_fast<4, false>(wsw, sp, grid, st) : launch_fast<8, false>(wsw, sp, grid, st);
     }

@@ -234,6 +234,29 @@ def test_gemv_v1_facade():
     assert rel_fro(y, want) <= REL_TOL
 
 
+@pytest.mark.parametrize("M", [1, 4, 8, 13])
+@pytest.mark.parametrize("K,N", [(4096, 4096), (11008, 1024), (1024, 5120), (512, 4768)])
+def test_gemv_v1_shapes(K, N, M):
+    """First-format layers (one scale and one fp16 zero term per column) through the C ABI, against the
+    oracle's reconstruct + matmul; output rows beyond M untouched."""
+    gen = torch.Generator().manual_seed(K + N + M)
+    layer = synth.make_layer(K, N, K, False, seed=K + N)
+    sc = (torch.rand(N, generator=gen) * 0.018 + 0.002).half()
+    ze = (sc.float() * torch.randint(1, 16, (N,), generator=gen)).half()
+    x = synth.make_acts(M, K, seed=M)
+    full, y = guarded((M, N), torch.float16)
+    L = _lib.lib()
+    ws = _lib.workspace(torch.device(DEV), L.q4_gemv_workspace_bytes(M, K, N))
+    xd, qd, sd, zd = x.to(DEV), layer.qweight.to(DEV), sc.to(DEV), ze.to(DEV)
+    _lib.check(L.q4_gemv(xd.data_ptr(), qd.data_ptr(), y.data_ptr(), sd.data_ptr(), zd.data_ptr(), None, None, M, K, N, 1, K,
+                         _lib.Q4_F16, _lib.GEMV_V1, ws.data_ptr(), ws.numel(), torch.cuda.current_stream().cuda_stream), "v1")
+    torch.cuda.synchronize()
+    assert canaries_intact(full, M)
+    want = orc.matmul_recons(x, orc.recons_v1(layer.qweight, sc, ze))
+    assert rel_fro(y, want) <= REL_TOL
+    assert quant_cuda.device_status() == 0
+
+
 def test_facade_matmul_variants_add_into_mul():
     layer = synth.make_layer(4096, 4096, 128, False, seed=41)
     L = layer.to(DEV)
