@@ -1131,8 +1131,8 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
   const bool v1 = flags & Q4_GEMV_V1;
   if (v1) {
     if (act) return fail(Q4_E_BADARG, "gemv: v1 layers have no g_idx");
-    // a v1 layer whose last 256-row unit is half filled (K = 4224) ran into waits that expire only
-    // after minutes in the streaming kernel; until the cause is found such layers are refused
+    // v1 layers are served by the lean kernel and by the streaming instance for groups of whole 128-row
+    // halves; both want K in whole 256-row units (the general streaming instance has never run a v1 layer)
     if (K % 256) return fail(Q4_E_SHAPE, "gemv: v1 layers need K to be a multiple of 256 (K=%d)", K);
     groupsize = K; G = 1;
   }
@@ -1242,8 +1242,10 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
                                (uint64_t)N * 2, GEMV_TN, 1, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
       sp.stage_tx = GEMV_UNIT_BYTES + 2 * GEMV_TN * 2;
     }
-    // the instance specialised for groups of whole 128-row halves is kept to layers made of whole
-    // 256-row units (see the v1 note above: a half-filled last unit is where it was seen waiting)
+    // The instance specialised for groups of whole 128-row halves is kept to layers made of whole
+    // 256-row units: its per-CTA pass over x sums 16-lane groups with full-mask shuffles in a loop over
+    // M * K / 8 blocks, and with K = 128 mod 256 the last trip of that loop is taken by half a warp -
+    // the other half has left the loop and the shuffle never completes.
     const bool fast = (v1 || groupsize % 128 == 0) && K % 256 == 0;
     const bool xs = fast && MT == 1 && K % 128 == 0 && (size_t)M * K * 2 + (size_t)(K / 128) * 64 <= (size_t)GEMV_XS_MAX_BYTES;
     if (xs) return launch_stream<1, true, true>(map, smap, zmap, sp, grid, st);
