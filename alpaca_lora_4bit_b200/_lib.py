@@ -46,6 +46,8 @@ _SIGNATURES = {
                             c_int, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "q4_gemm_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "q4_device_status": (c_int, [ctypes.POINTER(c_uint)]),
+    "q4_gemv_status": (c_int, [c_void_p, c_size_t, ctypes.POINTER(c_uint)]),
+    "q4_gemv_static_status": (c_int, [ctypes.POINTER(c_uint)]),
     "q4_gemv": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                         c_int, c_int, c_int, c_int, c_int, c_int, c_uint, c_void_p, c_size_t, c_void_p]),
 }

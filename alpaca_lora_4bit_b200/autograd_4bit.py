@@ -206,58 +206,128 @@ def find_layers(module, layers=(nn.Conv2d, nn.Linear), name=''):
     return res
 
 
-def _load_state(model, model_path):
-    """Fill the quant buffers by name from a ``.safetensors`` / torch checkpoint, without accelerate."""
+def _read_checkpoint(model_path):
     if str(model_path).endswith('.safetensors'):
         from safetensors.torch import load_file
-        state = load_file(model_path)
-    else:
-        state = torch.load(model_path, map_location='cpu')
+        return load_file(str(model_path))
+    return torch.load(model_path, map_location='cpu')
+
+
+def _load_state(model, model_path):
+    """Fill parameters and quant buffers by name from a ``.safetensors`` / torch checkpoint, without
+    accelerate.  Like ``accelerate.load_checkpoint_and_dispatch`` with no dtype given (what the reference
+    calls, autograd_4bit.py:273-278), a floating-point entry is cast to the dtype the module holds for it
+    (so fp16 ``scales`` of a checkpoint become fp32 until ``model_to_half``); integer entries are taken as
+    they are.  Every value lands on the device of the tensor it replaces."""
+    state = _read_checkpoint(model_path)
     own = dict(model.named_parameters())
     own.update(dict(model.named_buffers()))
-    missing = [k for k in own if k not in state and not k.endswith('rotary_emb.inv_freq')]
+    missing = [k for k in own if k not in state and 'rotary_emb' not in k]
+    unexpected = [k for k in state if k not in own]
     for key, value in state.items():
         if key not in own:
             continue
         mod_name, _, leaf = key.rpartition('.')
         mod = model.get_submodule(mod_name) if mod_name else model
         cur = getattr(mod, leaf)
+        if tuple(value.shape) != tuple(cur.shape):
+            raise ValueError(f'checkpoint entry {key} has shape {tuple(value.shape)}, the model expects {tuple(cur.shape)}')
+        if cur.is_floating_point() and value.is_floating_point():
+            value = value.to(cur.dtype)
+        value = value.to(cur.device)
         if isinstance(cur, nn.Parameter):
-            setattr(mod, leaf, nn.Parameter(value.to(cur.dtype), requires_grad=False))
+            setattr(mod, leaf, nn.Parameter(value, requires_grad=False))
         else:
             setattr(mod, leaf, value)
     if missing:
         logging.warning('checkpoint has no entry for: %s', ', '.join(missing[:8]))
+    if unexpected:
+        logging.warning('checkpoint entries without a place in the model: %s', ', '.join(unexpected[:8]))
     return model
+
+
+def reset_rotary_buffers(model, config, device):
+    """The rotary embedding's ``inv_freq`` / ``original_inv_freq`` are non-persistent buffers: no checkpoint
+    holds them, and a model materialised from the meta device has uninitialised memory there.  Recompute
+    them from the configuration."""
+    for mod in model.modules():
+        if hasattr(mod, 'inv_freq') and hasattr(mod, 'compute_default_rope_parameters'):
+            inv, scaling = mod.compute_default_rope_parameters(config, device)
+            mod.inv_freq = inv
+            if hasattr(mod, 'original_inv_freq'):
+                mod.original_inv_freq = inv.clone()
+            if hasattr(mod, 'attention_scaling'):
+                mod.attention_scaling = scaling
+
+
+def _target_device(device_map):
+    if isinstance(device_map, dict):
+        return torch.device(device_map.get('', 'cuda'))
+    if isinstance(device_map, (str, torch.device)) and str(device_map) not in ('auto', 'balanced', 'sequential'):
+        return torch.device(device_map)
+    return torch.device('cuda', torch.cuda.current_device()) if torch.cuda.is_available() else torch.device('cpu')
 
 
 def load_llama_model_4bit_low_ram(config_path, model_path, groupsize=-1, half=False, device_map="auto", seqlen=2048,
                                   is_v1_model=False, bits=4):
     """Build an HF LLaMA, swap every linear but ``lm_head`` for a quant linear and load a GPTQ
     checkpoint into it (autograd_4bit.py:258-294).  The reference places weights with accelerate;
-    this loader reads the checkpoint directly and moves the model to one device (``device_map`` of the
-    form ``{'': device}`` or ``"auto"`` = current CUDA device)."""
-    from transformers import AutoTokenizer, LlamaConfig, LlamaForCausalLM
+    this loader reads the checkpoint directly onto one device (``device_map`` of the form
+    ``{'': device}``, a device, or ``"auto"`` = the current CUDA device).  The model is built on the
+    meta device and its linears are swapped there, so the dense weights of the quantised layers never
+    exist anywhere.  Returns ``(model, tokenizer)``; the tokenizer is ``None`` when ``config_path``
+    holds no tokenizer files."""
+    from transformers import LlamaConfig, LlamaForCausalLM
     t0 = time.time()
     config = LlamaConfig.from_pretrained(config_path)
-    saved = torch.get_default_dtype()
-    torch.set_default_dtype(torch.float16)
-    try:
-        with torch.device('meta'):
-            model = LlamaForCausalLM(config)
-    finally:
-        torch.set_default_dtype(saved)
-    model = model.to_empty(device='cpu')
-    layers = find_layers(model)
-    layers.pop('lm_head', None)
-    make_quant_for_4bit_autograd(model, layers, groupsize=groupsize, is_v1_model=is_v1_model, bits=bits)
+    with torch.device('meta'):
+        model = LlamaForCausalLM(config)
+        model = model.eval()
+        layers = find_layers(model)
+        layers.pop('lm_head', None)
+        make_quant_for_4bit_autograd(model, layers, groupsize=groupsize, is_v1_model=is_v1_model, bits=bits)
+    device = _target_device(device_map)
+    model = model.to_empty(device=device)
+    for m in model.modules():                       # buffers the constructor computes and no checkpoint carries
+        if isinstance(m, Autograd4bitQuantLinear):
+            m.bias = torch.zeros(m.out_features, device=device)
+            if not m.is_v1_model:
+                m.g_idx = (torch.arange(m.in_features, device=device) // m.groupsize).to(torch.int32)
     _load_state(model, model_path)
-    device = device_map.get('', 'cuda') if isinstance(device_map, dict) else 'cuda'
-    model = model.to(device)
+    reset_rotary_buffers(model, config, device)
+    if getattr(config, 'tie_word_embeddings', False):
+        model.tie_weights()
     model.seqlen = seqlen
     if half:
         model_to_half(model)
-    tokenizer = AutoTokenizer.from_pretrained(config_path)
-    tokenizer.truncation_side = 'left'
+    tokenizer = None
+    try:
+        from transformers import AutoTokenizer
+        tokenizer = AutoTokenizer.from_pretrained(config_path)
+        tokenizer.truncation_side = 'left'
+    except (OSError, ValueError, KeyError, TypeError) as exc:
+        logging.warning('no tokenizer loaded from %s (%s)', config_path, type(exc).__name__)
     print(f"Loaded the model in {(time.time() - t0):.2f} seconds.")
     return model, tokenizer
+
+
+def load_llama_model_4bit_low_ram_and_offload(config_path, model_path, lora_path=None, groupsize=-1, seqlen=2048,
+                                              max_memory=None, is_v1_model=False, bits=4):
+    """The reference's variant for GPUs that cannot hold the model spreads layers over GPU and host
+    memory with accelerate (autograd_4bit.py:296-362).  A B200 holds every LLaMA this format exists for
+    (a 70B int4 checkpoint is 35 GB of 180), so the whole model goes to the current device, in half
+    precision as the reference leaves it; ``max_memory`` is accepted and ignored.  With ``lora_path`` the
+    PEFT adapter there is applied through the int4 LoRA layers (needs ``peft``)."""
+    model, tokenizer = load_llama_model_4bit_low_ram(config_path, model_path, groupsize=groupsize, half=False,
+                                                     seqlen=seqlen, is_v1_model=is_v1_model, bits=bits)
+    if lora_path is not None:
+        from .monkeypatch.peft_tuners_lora_monkey_patch import replace_peft_model_with_int4_lora_model
+        replace_peft_model_with_int4_lora_model()
+        from peft import PeftModel
+        model = PeftModel.from_pretrained(model, lora_path, torch_dtype=torch.float32, is_trainable=True)
+        print('{} Lora Applied.'.format(lora_path))
+    _cast_quant_buffers(model, torch.float16)
+    return model, tokenizer
+
+
+load_llama_model_4bit_low_ram_and_offload_to_cpu = load_llama_model_4bit_low_ram_and_offload

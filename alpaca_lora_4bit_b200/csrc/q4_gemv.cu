@@ -29,6 +29,7 @@
 // The act-order variant (group from g_idx per row) cannot factor the scale out of the
 // contraction; it dequantises per element from shared-memory scale tables instead.
 #include "q4_async.cuh"
+#include <atomic>
 #include <new>
 
 
@@ -162,6 +163,8 @@ struct GemvStreamParams {
   // ceil(2^32 / d) that turn its divisions by the grid size and by units_per_tile into one multiply
   // (exact while dividend * d < 2^32, which the host checks)
   unsigned share, per, magic_grid, magic_upt;
+  // warp-specialised kernel: CTAs that have work (the grid may be larger: see launch_ws)
+  int work_ctas;
 };
 
 template <int MT>
@@ -393,20 +396,26 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
     if (threadIdx.x < 4) reinterpret_cast<uint32_t*>(xs_base)[threadIdx.x] = 0u;
     for (int idx = threadIdx.x; idx < (K >> 7) * 8; idx += GEMV_STREAM_THREADS)
       if ((idx & 7) >= p.M) ctab[idx] = make_float2(0.f, 0.f);
-    for (int idx = threadIdx.x; idx < p.M * blocks_per_row; idx += GEMV_STREAM_THREADS) {
-      const int m = idx / blocks_per_row, blk = idx - m * blocks_per_row;
-      const uint4 v = __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)m * K + 8 * blk));
+    // The trip count is the same for every lane of a warp (the sums below are full-warp shuffles): the
+    // bound is rounded up to whole CTA strides and the lanes past the end carry zeros.  Rows are a
+    // multiple of 16 blocks long, so the 16 lanes that share a sum always sit in one row and chunk.
+    const int total = p.M * blocks_per_row;
+    for (int base = 0; base < total; base += GEMV_STREAM_THREADS) {
+      const int idx = base + threadIdx.x;
+      const bool ok = idx < total;
+      const int m = ok ? idx / blocks_per_row : 0, blk = ok ? idx - m * blocks_per_row : 0;
+      const uint4 v = ok ? __ldg(reinterpret_cast<const uint4*>(p.x + (size_t)m * K + 8 * blk)) : make_uint4(0u, 0u, 0u, 0u);
       const __half2 h01 = as_h2(v.x), h23 = as_h2(v.y), h45 = as_h2(v.z), h67 = as_h2(v.w);
       const __half2 sixteenth = as_h2(0x2C002C00u);
       const __half2 e04 = __lows2half2(h01, h45), o15 = __hmul2(__highs2half2(h01, h45), sixteenth);
       const __half2 e26 = __lows2half2(h23, h67), o37 = __hmul2(__highs2half2(h23, h67), sixteenth);
-      *reinterpret_cast<uint4*>(xs_buf + (size_t)m * K + 8 * blk) = make_uint4(as_u32(e04), as_u32(o15), as_u32(e26), as_u32(o37));
+      if (ok) *reinterpret_cast<uint4*>(xs_buf + (size_t)m * K + 8 * blk) = make_uint4(as_u32(e04), as_u32(o15), as_u32(e26), as_u32(o37));
       const float2 f01 = __half22float2(h01), f23 = __half22float2(h23), f45 = __half22float2(h45), f67 = __half22float2(h67);
       float se = (f01.x + f23.x) + (f45.x + f67.x), so = (f01.y + f23.y) + (f45.y + f67.y);
 #pragma unroll
       for (int d = 8; d >= 1; d >>= 1) { se += __shfl_xor_sync(0xffffffffu, se, d); so += __shfl_xor_sync(0xffffffffu, so, d); }
       // the odd elements sit in x' as x/16, so their 1024 offset comes back as 64 * x
-      if ((lane & 15) == 0) ctab[(size_t)(blk >> 4) * 8 + m] = make_float2(1024.f * se + 64.f * so, se + so);
+      if (ok && (lane & 15) == 0) ctab[(size_t)(blk >> 4) * 8 + m] = make_float2(1024.f * se + 64.f * so, se + so);
     }
     named_bar_sync(5, GEMV_STREAM_THREADS);
   }
@@ -541,9 +550,12 @@ gemv_stream_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_consta
 //   * the +1024 / +64 offsets and the zero points are not handled per MMA fragment: one lane per
 //     column subtracts s * (offset_sum + (z+1) * x_sum) once per group, from sums of x computed once
 //     per unit with warp shuffles.
-// warps per CTA: 16, or 12 where the stages of 16 (4 KiB of weights + MR x 512 B of x each) do not fit
-template <int MR>
-__host__ __device__ constexpr int gf_warps() { return MR <= 4 ? 16 : 12; }
+// Warps per CTA (W) and CTAs per SM (OCC) are parameters of the kernel.  With one CTA per SM (W = 16, or 12
+// where the stages of 16 - 4 KiB of weights + MR x 512 B of x each - do not fit) the CTAs of the next launch
+// in the stream cannot become resident before this launch's CTAs exit, so its prologue and its first weight
+// copies start only then.  The two-per-SM form (fewer warps, at most half of the SM's shared memory and
+// registers per CTA) leaves room for them: the next launch's CTAs start, issue their first weight copies and
+// park in griddepcontrol.wait while this launch is still streaming.
 constexpr int GF_STAGES = 2;
 // A stage is two blocks.  The packed words (4 KiB, TMA with the 128-byte swizzle: the 16-byte chunk c of
 // row r lies at chunk c ^ (r & 7), which needs the block on a 1 KiB boundary) and, in a ring of its own,
@@ -559,10 +571,10 @@ __host__ __device__ constexpr int gf_aux_bytes(bool xc) { return xc ? GF_X_OFF :
 // (k padded to whole units, plus 16 so that neighbouring rows start on different banks) and one
 // (offset sum, plain sum) pair per 128 k and row.
 __host__ __device__ inline size_t gf_xc_bytes(int mr, int upt) { return (size_t)mr * (upt * 512 + 16) + (size_t)upt * 2 * mr * 8; }
-template <int MR>
+template <int MR, int W>
 __host__ __device__ constexpr size_t gf_smem_bytes(bool xc) {
-  return 1024 + (size_t)gf_warps<MR>() * GF_STAGES * (GEMV_UNIT_BYTES + gf_aux_bytes<MR>(xc)) + sizeof(float) * gf_warps<MR>() * MR * GEMV_TN +
-         gf_warps<MR>() * GF_STAGES * 8 + 64;
+  return 1024 + (size_t)W * GF_STAGES * (GEMV_UNIT_BYTES + gf_aux_bytes<MR>(xc)) + sizeof(float) * W * MR * GEMV_TN +
+         W * GF_STAGES * 8 + 64;
 }
 
 __device__ __forceinline__ void cp_async16_zfill(void* dst, const void* src, bool valid) {
@@ -580,8 +592,8 @@ __device__ __forceinline__ void cp_async_arrive_noinc(uint64_t* bar) {
 
 // TRACE: the instance that records timestamps (q4_gemv_set_trace); the other carries no trace code at all
 // V1: the first layer format - one scale and one fp16 zero term per column (W = s q - zero), no groups
-template <int MR, bool TRACE, bool XC, bool V1>
-__global__ void __launch_bounds__(gf_warps<MR>() * 32, 1)
+template <int MR, bool TRACE, bool XC, bool V1, int W, int OCC>
+__global__ void __launch_bounds__(W * 32, OCC)
 gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap,
                  const __grid_constant__ CUtensorMap zmap, const GemvStreamParams sp) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -589,7 +601,7 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
   const GemvParams& p = sp.g;
   unsigned long long* const trc = TRACE ? sp.trace : nullptr;
   constexpr int STG = GEMV_UNIT_BYTES, AUX = gf_aux_bytes<MR>(XC);
-  constexpr int GF_WARPS = gf_warps<MR>(), GF_THREADS = GF_WARPS * 32;
+  constexpr int GF_WARPS = W, GF_THREADS = GF_WARPS * 32;
   unsigned char* aux_ring = smem + (size_t)GF_WARPS * GF_STAGES * STG;
   unsigned char* xc = aux_ring + (size_t)GF_WARPS * GF_STAGES * AUX;                            // XC: x' of the whole layer
   const int xc_pitch = sp.units_per_tile * 512 + 16;
@@ -824,6 +836,7 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
         if ((lane & 15) == 0) sums[(lane >> 4) * MR + r] = make_float2(1024.f * se + 64.f * so, se + so);
       }
       if constexpr (!XC) __syncwarp();
+      if (warp == 0 && lane == 0 && n < 2) trace_mark(trc, 50 + 5 * n);
       // lanes of batch rows that do not exist feed row 0 again: an MMA output column depends on its own
       // input column only, and the columns beyond MR are never stored
       const uint4* xq = XC ? reinterpret_cast<const uint4*>(xc + (size_t)(g < MR ? g : 0) * xc_pitch + 512 * ux) + 2 * t
@@ -887,9 +900,11 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
             ycorr[r] = fmaf(sl, fmaf(z1, e.y, e.x), ycorr[r]);
           }
         }
+        if (warp == 0 && lane == 0 && n < 2) trace_mark(trc, 51 + 5 * n + h);
       }
       __syncwarp();
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // our reads before the next TMA write
+      if (warp == 0 && lane == 0 && n < 2) trace_mark(trc, 53 + 5 * n);
       issue_wx(n + GF_STAGES);
       if (warp == 0 && lane == 0) trace_mark(trc, 4 + 2 * n);
     }
@@ -898,6 +913,318 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
     finish_tile(tile, tile - tile_first, max(u0, tile * upt) - tile * upt, seg_u1 - 1 - tile * upt);
     if (threadIdx.x == 0) trace_mark(trc, 31);
     if (warp == GF_WARPS - 1 && lane == 0 && tile == tile_last) trace_mark_ns(trc, 45);
+  }
+}
+
+// ---- one row, groups of 128: the warp-specialised decode kernel ------------------------------------
+// A cycle trace of the lean kernel above showed what a warp spends per 4 KiB unit: 420-590 cycles re-laying
+// its slice of x out, 1400-1700 on unpack + MMA + closing the two groups, 520-750 issuing the next copies
+// (one TMA copy, a handful of 16-byte asynchronous copies, the barrier arrive) - and that the time per unit
+// hardly moves with the number of warps: every warp is bound by the latency of its own instruction stream,
+// not by issue slots.  Here the two side jobs leave the consumers' stream:
+//   * warp W issues every TMA copy of the CTA (lane c those of consumer c): the 4 KiB units of all consumer rings, in the
+//     order they are consumed, and per column tile one box each of the tile's scales and packed zero points
+//     (all groups).  None of that depends on an earlier kernel, so it starts before griddepcontrol.wait.
+//   * warps 0..W-1 wait for the earlier kernels of the stream and write, together and once, x' (MMA order, odd
+//     elements / 16) and the per-128-row sums of x for the whole of K into shared memory; then they
+//     consume: wait for the unit (and, once per tile, for the tile's metadata), unpack, MMA, close the two
+//     groups, release the stage.  The sums of a column tile meet exactly as in the lean kernel.
+// Stage ring per consumer: S units of 4 KiB (TMA, 128-byte swizzle).  With W = 8 and S = 2 a CTA takes less
+// than half of the SM's shared memory and registers: the next decode launch of the stream becomes resident
+// beside it, fills its rings and parks in griddepcontrol.wait while this one is still computing.
+constexpr int WS_MAX_UNITS_PER_TILE = 256;             // K <= 65536
+
+struct WsLayout {                                      // byte offsets from the 1 KiB-aligned base
+  int stages, meta, meta_slot, meta_zp, xp, sums, red, bars, total;
+};
+__host__ __device__ inline WsLayout ws_layout(int W, int S, int G, int upt) {
+  WsLayout l;
+  l.stages = 0;
+  l.meta = W * S * GEMV_UNIT_BYTES;
+  l.meta_zp = (G * 64 + 127) / 128 * 128;              // scales [G][32] fp16, then zero points [G][4] words
+  l.meta_slot = l.meta_zp + (G * 16 + 127) / 128 * 128;
+  l.xp = l.meta + 2 * l.meta_slot;
+  l.sums = l.xp + upt * 512;
+  l.red = l.sums + upt * 16;
+  l.bars = (l.red + W * GEMV_TN * 4 + 15) / 16 * 16;
+  l.total = l.bars + 8 * (2 * W * S + 4) + 16;
+  return l;
+}
+
+__device__ __forceinline__ bool mbar_wait_sleep_bounded(uint64_t* bar, uint32_t parity, uint32_t tries) {
+  for (uint32_t i = 0; i < tries; ++i)
+    if (mbar_try_wait_sleep(bar, parity, 1000u)) return true;
+  return false;
+}
+// every lane polls (one instruction per try); returns false when the limit ran out
+__device__ __forceinline__ bool mbar_spin_bounded(uint64_t* bar, uint32_t parity, uint32_t tries) {
+  if (mbar_test_wait(bar, parity)) return true;
+  for (uint32_t i = 0; i < tries; ++i)
+    if (mbar_test_wait(bar, parity)) return true;
+  return false;
+}
+
+template <int W, int S, int OCC, bool TRACE>
+__global__ void __launch_bounds__((W + 1) * 32, OCC)
+gemv_ws_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap,
+               const __grid_constant__ CUtensorMap zmap, const GemvStreamParams sp) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  const GemvParams& p = sp.g;
+  unsigned long long* const trc = TRACE ? sp.trace : nullptr;
+  const int upt = sp.units_per_tile, G = sp.n_groups;
+  const WsLayout L = ws_layout(W, S, G, upt);
+  unsigned char* xp = smem + L.xp;                                   // x' of the whole row: 16 bytes per 8 k
+  float2* sums = reinterpret_cast<float2*>(smem + L.sums);           // [K / 128]: (offset sum, plain sum)
+  float* red = reinterpret_cast<float*>(smem + L.red);               // [W][32]
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.bars);       // [W][S]  unit has landed
+  uint64_t* empty = full + W * S;                                    // [W][S]  unit has been consumed
+  uint64_t* mfull = empty + W * S;                                   // [2]     metadata of a tile has landed
+  uint64_t* mempty = mfull + 2;                                      // [2]     every consumer is done with it
+  volatile int* flags = reinterpret_cast<volatile int*>(mempty + 2);
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  if (threadIdx.x == 0) trace_mark_ns(trc, 40);
+  const int nu = sp.total_units, Gd = sp.work_ctas;
+  if ((int)blockIdx.x >= Gd) {
+    // A CTA without work.  The two-per-SM form always launches one CTA per SM, so that every SM holds exactly
+    // one CTA of this launch and one of the next (CTAs of one launch that share an SM halve each other's
+    // speed); the spare ones stay resident until the earlier kernels of the stream are done, then leave.
+    pdl_launch_dependents();
+    pdl_wait();
+    return;
+  }
+  const unsigned share = sp.share, per = sp.per;
+  const int u0 = (int)(__umulhi((unsigned)blockIdx.x * share, sp.magic_grid) * per);
+  const int u1 = (int)(__umulhi(((unsigned)blockIdx.x + 1u) * share, sp.magic_grid) * per);
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < W * S; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+    mbar_init(&mfull[0], 1); mbar_init(&mfull[1], 1);
+    mbar_init(&mempty[0], W); mbar_init(&mempty[1], W);
+    flags[0] = 0;
+    mbar_fence_init();
+    tma_prefetch_desc(&wmap); tma_prefetch_desc(&smap); tma_prefetch_desc(&zmap);
+  }
+  __syncthreads();
+  pdl_launch_dependents();
+  const uint32_t meta_tx = (uint32_t)G * 80u;
+
+  if (warp == W) {
+    // ---- copy issuer ---------------------------------------------------------------------------------
+    // Lane c feeds consumer c: one instruction of the warp issues the copies of a whole round of W units
+    // (a single thread issuing them one after the other needs some 300 cycles per copy, more than a
+    // consumer needs per unit).  The lane whose unit opens a column tile brings the tile's metadata first.
+    if (lane < W) {
+      const int tile_first = (int)__umulhi((unsigned)u0, sp.magic_upt);
+      int u = u0 + lane;
+      int tile = (int)__umulhi((unsigned)u, sp.magic_upt), ux = u - tile * upt;
+      for (int n = 0; u0 + W * n < u1; ++n) {
+        const bool act = u < u1;
+        if (act && (ux == 0 || u == u0)) {       // scales and zero points of all groups of this column tile
+          const int seq = tile - tile_first, slot = seq & 1;
+          if (seq >= 2 && !mbar_wait_sleep_bounded(&mempty[slot], ((seq >> 1) & 1) ^ 1, 200000u)) {
+            flags[0] = 1; atomicExch(sp.status, Q4_STATUS_WAIT_EXPIRED);
+          }
+          unsigned char* m = smem + L.meta + slot * L.meta_slot;
+          mbar_arrive_expect_tx(&mfull[slot], meta_tx);
+          tma_load_2d(m, &smap, tile * GEMV_TN, 0, &mfull[slot]);
+          tma_load_2d(m + L.meta_zp, &zmap, tile * (GEMV_TN / 8), 0, &mfull[slot]);
+        }
+        const int st = n % S;
+        if (act && n >= S && !mbar_wait_sleep_bounded(&empty[lane * S + st], ((n / S) & 1) ^ 1, flags[0] ? 4u : 200000u)) {
+          flags[0] = 1; atomicExch(sp.status, Q4_STATUS_WAIT_EXPIRED);
+        }
+        __syncwarp((1u << W) - 1u);
+        if (TRACE && lane == 0 && n < 8) trace_mark(trc, 8 + n);
+        tma_expect_load_2d_if(act, smem + (size_t)(lane * S + st) * GEMV_UNIT_BYTES, &wmap, tile * GEMV_TN, ux * GEMV_UNIT_ROWS,
+                              &full[lane * S + st], GEMV_UNIT_BYTES);
+        u += W; ux += W;
+        while (ux >= upt) { ux -= upt; ++tile; }
+      }
+      if (TRACE && lane == 0) trace_mark(trc, 16);
+    }
+    return;
+  }
+  // ---- consumers ---------------------------------------------------------------------------------------
+  if (TRACE && threadIdx.x == 0 && trc) {
+    unsigned smid;
+    asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+    trc[(size_t)blockIdx.x * 64 + 47] = smid + 1;
+  }
+  constexpr int CT = W * 32;                                         // consumer threads (named barriers)
+  // x' (MMA order, odd elements / 16) and the sums of every 128 rows of x, for the whole of K, by all
+  // consumers together: until x is there they have nothing else to do.  CT is a multiple of 16, so the 16
+  // lanes that share a 128-row chunk always hold the 16 blocks of one chunk.
+  pdl_wait();                                  // x belongs to the stream order
+  if (threadIdx.x == 0) trace_mark_ns(trc, 42);
+  {
+    const int K = p.K, n_blocks = upt * 32;
+    const uint4* xg = reinterpret_cast<const uint4*>(p.x);
+    for (int base = 0; base < n_blocks; base += 4 * CT) {
+      uint4 v[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int blk = base + i * CT + (int)threadIdx.x;
+        v[i] = 8 * blk < K ? __ldg(xg + blk) : make_uint4(0u, 0u, 0u, 0u);
+      }
+      float se[4], so[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int blk = base + i * CT + (int)threadIdx.x;
+        const __half2 h01 = as_h2(v[i].x), h23 = as_h2(v[i].y), h45 = as_h2(v[i].z), h67 = as_h2(v[i].w);
+        const __half2 sixteenth = as_h2(0x2C002C00u);
+        const __half2 e04 = __lows2half2(h01, h45), o15 = __hmul2(__highs2half2(h01, h45), sixteenth);
+        const __half2 e26 = __lows2half2(h23, h67), o37 = __hmul2(__highs2half2(h23, h67), sixteenth);
+        if (blk < n_blocks) *reinterpret_cast<uint4*>(xp + (size_t)blk * 16) = make_uint4(as_u32(e04), as_u32(o15), as_u32(e26), as_u32(o37));
+        const float2 f01 = __half22float2(h01), f23 = __half22float2(h23), f45 = __half22float2(h45), f67 = __half22float2(h67);
+        se[i] = (f01.x + f23.x) + (f45.x + f67.x);
+        so[i] = (f01.y + f23.y) + (f45.y + f67.y);
+      }
+#pragma unroll
+      for (int d = 8; d >= 1; d >>= 1)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) { se[i] += __shfl_xor_sync(0xffffffffu, se[i], d); so[i] += __shfl_xor_sync(0xffffffffu, so[i], d); }
+      if ((lane & 15) == 0) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const int blk = base + i * CT + (int)threadIdx.x;
+          // the odd elements sit in x' as x / 16: their 1024 offset comes back as 64 x
+          if (blk < n_blocks) sums[blk >> 4] = make_float2(1024.f * se[i] + 64.f * so[i], se[i] + so[i]);
+        }
+      }
+    }
+  }
+  named_bar_sync(3, CT);
+  if (threadIdx.x == 0) trace_mark_ns(trc, 43);
+  const int g = lane >> 2, t = lane & 3;
+  const uint32_t woff0 = 128u * (2 * t) + 16u * (g ^ (2 * t)), woff1 = 128u * (2 * t + 1) + 16u * (g ^ (2 * t + 1));
+  float yacc[4] = {0.f, 0.f, 0.f, 0.f};                              // lanes t = 0: columns 4g .. 4g+3 of the row
+  float ycorr = 0.f;                                                 // lane = column: offsets and zero points
+  const unsigned char* my_stages = smem + (size_t)warp * S * GEMV_UNIT_BYTES;
+
+  auto finish_tile = [&](int tile, int seq, int seg_first, int seg_last) {
+    const bool reducer = warp == W - 1;
+    if (!reducer && seq >= 1) named_bar_sync(2, CT);
+    float* mine = red + warp * GEMV_TN;
+    if (t == 0) *reinterpret_cast<float4*>(mine + 4 * g) = make_float4(yacc[0], yacc[1], yacc[2], yacc[3]);
+    yacc[0] = yacc[1] = yacc[2] = yacc[3] = 0.f;
+    __syncwarp();
+    mine[lane] -= ycorr;
+    ycorr = 0.f;
+    if (!reducer) {
+      __threadfence_block();
+      named_bar_arrive(1, CT);
+      return;
+    }
+    named_bar_sync(1, CT);
+    const int tc0 = tile * GEMV_TN, col = lane;
+    const bool whole = seg_first == 0 && seg_last == upt - 1;
+    float v = 0.f;
+#pragma unroll
+    for (int w = 0; w < W; ++w) v += red[w * GEMV_TN + col];
+    named_bar_arrive(2, CT);
+    pdl_wait();                                  // y and the workspace belong to the stream order
+    if (whole) { store_y(p, 0, tc0 + col, v); return; }
+    float* part = sp.cta_part + ((size_t)blockIdx.x * 2 + (seg_first == 0 ? 1 : 0)) * 16 * GEMV_TN;
+    __stcg(part + col, v);
+    const int c_first = unit_owner((long long)tile * upt, Gd, nu), c_last = unit_owner((long long)tile * upt + upt - 1, Gd, nu);
+    __threadfence();
+    __syncwarp();
+    unsigned last = 0;
+    if (lane == 0) last = atomicAdd(p.counters + tile, 1u) == (unsigned)(c_last - c_first);
+    last = __shfl_sync(0xffffffffu, last, 0);
+    if (!last) return;
+    __threadfence();
+    float s = 0.f;
+    for (int cc = c_first; cc <= c_last; cc += 4) {
+      float t4[4];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        t4[i] = cc + i <= c_last ? __ldcg(sp.cta_part + ((size_t)(cc + i) * 2 + (cc + i == c_first ? 1 : 0)) * 16 * GEMV_TN + col) : 0.f;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) s += t4[i];
+    }
+    store_y(p, 0, tc0 + col, s);
+    if (lane == 0) p.counters[tile] = 0u;
+  };
+
+  const int tile_first = (int)__umulhi((unsigned)u0, sp.magic_upt), tile_last = (int)__umulhi((unsigned)(u1 - 1), sp.magic_upt);
+  int n = 0;
+  for (int tile = tile_first; tile <= tile_last; ++tile) {
+    const int seq = tile - tile_first, slot = seq & 1;
+    const int seg_u1 = min(u1, (tile + 1) * upt);
+    const unsigned char* meta = smem + L.meta + slot * L.meta_slot;
+    bool meta_ready = false;
+    for (int u = u0 + warp + W * n; u < seg_u1; ++n, u += W) {
+      const int ux = u - tile * upt;
+      const int st = n % S;
+      const uint32_t lim = flags[0] ? 64u : 20000000u;
+      if ((!meta_ready && !mbar_spin_bounded(&mfull[slot], (seq >> 1) & 1, lim)) || !mbar_spin_bounded(&full[warp * S + st], (n / S) & 1, lim)) {
+        flags[0] = 1; atomicExch(sp.status, Q4_STATUS_WAIT_EXPIRED);
+      }
+      meta_ready = true;
+      if (warp == 0 && lane == 0 && n < 8) trace_mark(trc, 20 + 2 * n);
+      const unsigned char* wst = my_stages + (size_t)st * GEMV_UNIT_BYTES;
+      const uint4* xq = reinterpret_cast<const uint4*>(xp + 512 * ux) + 2 * t;
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint4 wv[4], xv[4];
+#pragma unroll
+        for (int uu = 0; uu < 4; ++uu) {
+          // step (h, uu) takes packed rows 8 j + 2 t + pp of the unit, j = 2 h + uu / 2, pp = uu & 1
+          wv[uu] = *reinterpret_cast<const uint4*>(wst + ((uu & 1) ? woff1 : woff0) + 1024 * (2 * h + (uu >> 1)));
+          xv[uu] = xq[8 * (2 * h + (uu >> 1)) + (uu & 1)];
+        }
+        float c[2][2][4];                              // [chain][column pair][fragment]: two chains per column pair
+#pragma unroll
+        for (int uu = 0; uu < 4; ++uu) {
+          const uint32_t w[4] = {wv[uu].x, wv[uu].y, wv[uu].z, wv[uu].w};
+          uint32_t pr[4][4];
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const uint32_t w8 = w[q] >> 8;
+            pr[q][0] = and_or(w[q], 0x000F000Fu, 0x64006400u);
+            pr[q][1] = and_or(w[q], 0x00F000F0u, 0x64006400u);
+            pr[q][2] = and_or(w8, 0x000F000Fu, 0x64006400u);
+            pr[q][3] = and_or(w8, 0x00F000F0u, 0x64006400u);
+          }
+          const int ch = uu & 1;
+          if (uu < 2) {
+            mma16816_first(c[ch][0], pr[0][0], pr[1][0], pr[0][1], pr[1][1], xv[uu].x, xv[uu].y);
+            mma16816_first(c[ch][1], pr[2][0], pr[3][0], pr[2][1], pr[3][1], xv[uu].x, xv[uu].y);
+          } else {
+            mma16816(c[ch][0], pr[0][0], pr[1][0], pr[0][1], pr[1][1], xv[uu].x, xv[uu].y);
+            mma16816(c[ch][1], pr[2][0], pr[3][0], pr[2][1], pr[3][1], xv[uu].x, xv[uu].y);
+          }
+          mma16816(c[ch][0], pr[0][2], pr[1][2], pr[0][3], pr[1][3], xv[uu].z, xv[uu].w);
+          mma16816(c[ch][1], pr[2][2], pr[3][2], pr[2][3], pr[3][3], xv[uu].z, xv[uu].w);
+        }
+        // close the group of this half: scale the raw sums; one lane per column takes the offsets and the
+        // zero point out: y -= s * (offset_sum + (z + 1) * x_sum)
+        const int grp = 2 * ux + h;
+        const uint2 sc = *reinterpret_cast<const uint2*>(meta + grp * 64 + 8 * g);
+        const float2 s01 = __half22float2(as_h2(sc.x)), s23 = __half22float2(as_h2(sc.y));
+        yacc[0] = fmaf(s01.x, c[0][0][0] + c[1][0][0], yacc[0]);
+        yacc[1] = fmaf(s01.y, c[0][0][2] + c[1][0][2], yacc[1]);
+        yacc[2] = fmaf(s23.x, c[0][1][0] + c[1][1][0], yacc[2]);
+        yacc[3] = fmaf(s23.y, c[0][1][2] + c[1][1][2], yacc[3]);
+        const float sl = __half2float(*reinterpret_cast<const __half*>(meta + grp * 64 + 2 * lane));
+        const uint32_t zw = *reinterpret_cast<const uint32_t*>(meta + L.meta_zp + grp * 16 + 4 * (lane >> 3));
+        const float z1 = (float)(((zw >> (4 * (lane & 7))) & 0xFu) + 1u);
+        const float2 e = sums[grp];
+        ycorr = fmaf(sl, fmaf(z1, e.y, e.x), ycorr);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // our reads before the next TMA write
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty[warp * S + st]);
+      if (warp == 0 && lane == 0 && n < 8) trace_mark(trc, 21 + 2 * n);
+    }
+    // done with this tile's metadata (whether or not this warp had a unit in it)
+    if (lane == 0) mbar_arrive(&mempty[slot]);
+    if (warp == W - 1 && lane == 0 && tile == tile_last) trace_mark_ns(trc, 44);
+    finish_tile(tile, seq, max(u0, tile * upt) - tile * upt, seg_u1 - 1 - tile * upt);
+    if (warp == W - 1 && lane == 0 && tile == tile_last) trace_mark_ns(trc, 45);
   }
 }
 
@@ -1028,47 +1355,95 @@ static int launch_stream(const CUtensorMap& map, const CUtensorMap& smap, const 
 }
 
 constexpr size_t GF_SMEM_LIMIT = 227 * 1024;
+// two CTAs per SM: the SM has 228 KiB of shared memory and every resident CTA reserves 1 KiB of it
+constexpr size_t GF_SMEM_LIMIT2 = (228 * 1024 - 2 * 1024) / 2;
 
-template <int MR, bool TRACE, bool XC, bool V1>
+template <int MR, bool TRACE, bool XC, bool V1, int W, int OCC>
 static int launch_fast_xc(const CUtensorMap& map, const GemvStreamParams& sp, int grid, cudaStream_t st) {
-  static bool attr_done[64] = {false};
+  static std::atomic<bool> attr_done[64];
   int dev = 0;
   cudaGetDevice(&dev);
-  const size_t smem = gf_smem_bytes<MR>(XC) + (XC ? gf_xc_bytes(MR, sp.units_per_tile) : 0);
-  if (dev >= 0 && dev < 64 && !attr_done[dev]) {
+  static_assert(OCC == 1 || (!XC && gf_smem_bytes<MR, W>(false) <= GF_SMEM_LIMIT2 && W * 32 * OCC <= 2048), "two CTAs must fit one SM");
+  const size_t smem = gf_smem_bytes<MR, W>(XC) + (XC ? gf_xc_bytes(MR, sp.units_per_tile) : 0);
+  if (dev < 0 || dev >= 64 || !attr_done[dev].load(std::memory_order_acquire)) {
     const size_t most = XC ? GF_SMEM_LIMIT : smem;       // XC: the size follows K, the attribute is set once
-    if (int e = check_cuda(cudaFuncSetAttribute(gemv_fast_kernel<MR, TRACE, XC, V1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most),
+    if (int e = check_cuda(cudaFuncSetAttribute(gemv_fast_kernel<MR, TRACE, XC, V1, W, OCC>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)most),
                            "gemv smem attribute")) return e;
-    attr_done[dev] = true;
+    // all of the SM's configurable memory as shared memory, so that OCC CTAs of this size are resident together
+    if (int e = check_cuda(cudaFuncSetAttribute(gemv_fast_kernel<MR, TRACE, XC, V1, W, OCC>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                                (int)cudaSharedmemCarveoutMaxShared), "gemv carveout attribute")) return e;
+    if (dev >= 0 && dev < 64) attr_done[dev].store(true, std::memory_order_release);
   }
   cudaLaunchConfig_t cfg = {};
-  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(gf_warps<MR>() * 32);
+  cfg.gridDim = dim3(grid); cfg.blockDim = dim3(W * 32);
   cfg.dynamicSmemBytes = smem; cfg.stream = st;
   cudaLaunchAttribute at[1];
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at; cfg.numAttrs = 1;
-  return check_cuda(cudaLaunchKernelEx(&cfg, gemv_fast_kernel<MR, TRACE, XC, V1>, map, map, map, sp), "gemv launch");
+  return check_cuda(cudaLaunchKernelEx(&cfg, gemv_fast_kernel<MR, TRACE, XC, V1, W, OCC>, map, map, map, sp), "gemv launch");
 }
+
+template <int W, int S, int OCC, bool TRACE>
+static int launch_ws(const CUtensorMap& wmap, const CUtensorMap& smap, const CUtensorMap& zmap, const GemvStreamParams& sp, int grid,
+                     cudaStream_t st) {
+  static std::atomic<bool> attr_done[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  const size_t smem = 1024 + (size_t)ws_layout(W, S, sp.n_groups, sp.units_per_tile).total;
+  if (dev < 0 || dev >= 64 || !attr_done[dev].load(std::memory_order_acquire)) {
+    if (int e = check_cuda(cudaFuncSetAttribute(gemv_ws_kernel<W, S, OCC, TRACE>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                (int)(OCC == 1 ? GF_SMEM_LIMIT : GF_SMEM_LIMIT2)), "gemv smem attribute")) return e;
+    if (int e = check_cuda(cudaFuncSetAttribute(gemv_ws_kernel<W, S, OCC, TRACE>, cudaFuncAttributePreferredSharedMemoryCarveout,
+                                                (int)cudaSharedmemCarveoutMaxShared), "gemv carveout attribute")) return e;
+    if (dev >= 0 && dev < 64) attr_done[dev].store(true, std::memory_order_release);
+  }
+  cudaLaunchConfig_t cfg = {};
+  if (OCC == 2 && grid < sm_count()) grid = sm_count();       // one CTA per SM, spare ones without work (see the kernel)
+  cfg.gridDim = dim3(grid); cfg.blockDim = dim3((W + 1) * 32);
+  cfg.dynamicSmemBytes = smem; cfg.stream = st;
+  cudaLaunchAttribute at[1];
+  at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  at[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = at; cfg.numAttrs = 1;
+  return check_cuda(cudaLaunchKernelEx(&cfg, gemv_ws_kernel<W, S, OCC, TRACE>, wmap, smap, zmap, sp), "gemv launch");
+}
+
+// warps of the one-CTA-per-SM form: 16, or 12 where the stages of 16 do not fit
+template <int MR>
+constexpr int gf_warps1() { return MR <= 4 ? 16 : 12; }
 
 // x' of the whole layer per CTA when it fits beside the rings and the CTA has more than one column
 // tile's worth of units to amortise it over; else every unit brings and re-lays its own slice
 template <int MR, bool TRACE>
 static int launch_fast(const CUtensorMap& map, const GemvStreamParams& sp, int grid, cudaStream_t st) {
-  const bool fits = gf_smem_bytes<MR>(true) + gf_xc_bytes(MR, sp.units_per_tile) <= GF_SMEM_LIMIT;
+  constexpr int W1 = gf_warps1<MR>();
+  const int xmode = g_gemv_variant & 3;
+  const bool fits = gf_smem_bytes<MR, W1>(true) + gf_xc_bytes(MR, sp.units_per_tile) <= GF_SMEM_LIMIT;
   const bool pays = (long long)sp.total_units > (long long)grid * sp.units_per_tile;
   // (measured: with one row the per-unit slice is as fast or faster at every shape tried - the re-layout
   //  is 10 % of a unit's instructions and the per-CTA pass delays the first unit; from two rows on the
   //  per-CTA pass wins 5-15 % wherever a CTA has more than one tile)
-  const bool xc = g_gemv_variant == 2 || (g_gemv_variant == 0 && pays && MR >= 2);
+  const bool xc = xmode == 2 || (xmode == 0 && pays && MR >= 2);
   if (sp.g.v1) {
     if constexpr (!TRACE) {
-      if (fits && xc) return launch_fast_xc<MR, false, true, true>(map, sp, grid, st);
-      return launch_fast_xc<MR, false, false, true>(map, sp, grid, st);
+      if (fits && xc) return launch_fast_xc<MR, false, true, true, W1, 1>(map, sp, grid, st);
+      return launch_fast_xc<MR, false, false, true, W1, 1>(map, sp, grid, st);
     }
   }
-  if (fits && xc) return launch_fast_xc<MR, TRACE, true, false>(map, sp, grid, st);
-  return launch_fast_xc<MR, TRACE, false, false>(map, sp, grid, st);
+  if (fits && xc) return launch_fast_xc<MR, TRACE, true, false, W1, 1>(map, sp, grid, st);
+  if constexpr (MR == 1) {
+    // one row, x per unit: the two-per-SM form, so that consecutive decode launches overlap
+    if (!(g_gemv_variant & 8)) {
+      const int wsel = (g_gemv_variant >> 5) & 3;
+      if constexpr (!TRACE) {
+        if (wsel == 1) return launch_fast_xc<1, false, false, false, 10, 2>(map, sp, grid, st);
+        if (wsel == 2) return launch_fast_xc<1, false, false, false, 8, 2>(map, sp, grid, st);
+      }
+      return launch_fast_xc<1, TRACE, false, false, 11, 2>(map, sp, grid, st);
+    }
+  }
+  return launch_fast_xc<MR, TRACE, false, false, W1, 1>(map, sp, grid, st);
 }
 
 }  // namespace q4
@@ -1104,7 +1479,7 @@ extern "C" int q4_gemv_set_trace(void* device_buffer) {
 }
 
 extern "C" int q4_gemv_set_variant(int variant) {
-  if (variant < 0 || variant > 2) return fail(Q4_E_BADARG, "gemv: variant %d outside 0..2", variant);
+  if (variant < 0 || variant > 127 || (variant & 3) == 3) return fail(Q4_E_BADARG, "gemv: variant %d is not a valid combination", variant);
   g_gemv_variant = variant;
   return Q4_OK;
 }
@@ -1131,9 +1506,9 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
   const bool v1 = flags & Q4_GEMV_V1;
   if (v1) {
     if (act) return fail(Q4_E_BADARG, "gemv: v1 layers have no g_idx");
-    // v1 layers are served by the lean kernel and by the streaming instance for groups of whole 128-row
-    // halves; both want K in whole 256-row units (the general streaming instance has never run a v1 layer)
-    if (K % 256) return fail(Q4_E_SHAPE, "gemv: v1 layers need K to be a multiple of 256 (K=%d)", K);
+    // v1 layers are served by the lean kernel (K in whole 256-row units) and by the streaming instance for
+    // groups of whole 128-row halves; the reference's kernel takes K in multiples of 128 as well
+    if (K % 128) return fail(Q4_E_SHAPE, "gemv: v1 layers need K to be a multiple of 128 (K=%d)", K);
     groupsize = K; G = 1;
   }
   if (act && !g_idx) return fail(Q4_E_BADARG, "gemv: act-order needs g_idx");
@@ -1198,6 +1573,7 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
       const int g2 = grid < tiles ? grid : tiles;
       const long long cost_whole = (long long)((tiles + g2 - 1) / g2) * sp.units_per_tile;
       if (cost_whole <= cost_split) sp.whole_tiles = 1;
+      if (g_gemv_variant & 4) sp.whole_tiles = 0;         // tests and measurements: always the even split
     }
     bool lean_ok = (long long)sp.total_units * grid < (1ll << 32);
     // group rows one unit (256 k-rows) can touch, counting a straddled group at either end
@@ -1224,6 +1600,21 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
       CUtensorMap wsw;                                    // the same boxes, chunks swizzled by the row on their way in
       if (int e = make_tmap_2d(&wsw, qweight, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, (uint64_t)N, (uint64_t)(K / 8),
                                (uint64_t)N * 4, GEMV_TN, GEMV_UNIT_ROWS, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
+      // one row, groups of 128, whole 256-row units: the warp-specialised kernel where its tables fit
+      if (M == 1 && !v1 && groupsize == 128 && K % 256 == 0 && G == K / 128 && G <= 256 && sp.units_per_tile <= WS_MAX_UNITS_PER_TILE &&
+          !(g_gemv_variant & 16)) {
+        sp.work_ctas = grid;
+        CUtensorMap sm2, zm2;                             // all groups of a column tile in one box each
+        if (int e = make_tmap_2d(&sm2, scales, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (uint64_t)N, (uint64_t)G, (uint64_t)N * 2,
+                                 GEMV_TN, G, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
+        if (int e = make_tmap_2d(&zm2, qzeros, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, (uint64_t)(N / 8), (uint64_t)G, (uint64_t)(N / 8) * 4,
+                                 GEMV_TN / 8, G, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
+        const bool one_per_sm = g_gemv_variant & 8;
+        if (!one_per_sm && 1024 + (size_t)ws_layout(8, 2, G, sp.units_per_tile).total <= GF_SMEM_LIMIT2)
+          return g_trace ? launch_ws<8, 2, 2, true>(wsw, sm2, zm2, sp, grid, st) : launch_ws<8, 2, 2, false>(wsw, sm2, zm2, sp, grid, st);
+        if (1024 + (size_t)ws_layout(16, 2, G, sp.units_per_tile).total <= GF_SMEM_LIMIT)
+          return g_trace ? launch_ws<16, 2, 1, true>(wsw, sm2, zm2, sp, grid, st) : launch_ws<16, 2, 1, false>(wsw, sm2, zm2, sp, grid, st);
+      }
       if (g_trace && M == 1 && !v1) return launch_fast<1, true>(wsw, sp, grid, st);
       return M == 1 ? launch_fast<1, false>(wsw, sp, grid, st) : M == 2 ? launch_fast<2, false>(wsw, sp, grid, st)
            : M <= 4 ? launch_fast<4, false>(wsw, sp, grid, st) : launch_fast<8, false>(wsw, sp, grid, st);
@@ -1242,11 +1633,8 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
                                (uint64_t)N * 2, GEMV_TN, 1, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
       sp.stage_tx = GEMV_UNIT_BYTES + 2 * GEMV_TN * 2;
     }
-    // The instance specialised for groups of whole 128-row halves is kept to layers made of whole
-    // 256-row units: its per-CTA pass over x sums 16-lane groups with full-mask shuffles in a loop over
-    // M * K / 8 blocks, and with K = 128 mod 256 the last trip of that loop is taken by half a warp -
-    // the other half has left the loop and the shuffle never completes.
-    const bool fast = (v1 || groupsize % 128 == 0) && K % 256 == 0;
+    // the instance specialised for groups of whole 128-row halves (a half-filled last unit ends after its first half)
+    const bool fast = (v1 || groupsize % 128 == 0) && K % 128 == 0;
     const bool xs = fast && MT == 1 && K % 128 == 0 && (size_t)M * K * 2 + (size_t)(K / 128) * 64 <= (size_t)GEMV_XS_MAX_BYTES;
     if (xs) return launch_stream<1, true, true>(map, smap, zmap, sp, grid, st);
     if (MT == 1) return fast ? launch_stream<1, true, false>(map, smap, zmap, sp, grid, st) : launch_stream<1, false, false>(map, smap, zmap, sp, grid, st);
@@ -1268,6 +1656,15 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
   return check_cuda(cudaGetLastError(), "gemv launch");
 }
 
+
+// The decode kernels record an expired bounded wait in the last word of the workspace head (there is one
+// workspace per stream, so the word lives with it and not in a device global).
+extern "C" int q4_gemv_status(const void* workspace, size_t workspace_bytes, unsigned* out) {
+  if (!workspace || !out) return fail(Q4_E_BADARG, "gemv_status: null pointer");
+  if (workspace_bytes < GEMV_WS_HEAD) return fail(Q4_E_WORKSPACE, "gemv_status: a decode workspace has at least %zu bytes", GEMV_WS_HEAD);
+  if (int e = check_cuda(cudaDeviceSynchronize(), "gemv_status: synchronize")) return e;
+  return check_cuda(cudaMemcpy(out, (const char*)workspace + GEMV_STATUS_OFFSET, sizeof(unsigned), cudaMemcpyDeviceToHost), "read decode status");
+}
 
 extern "C" int q4_layer_gemv(const q4_layer_t* l, const void* x, void* y, int M,
                              void* workspace, size_t workspace_bytes, q4_stream_t stream) {

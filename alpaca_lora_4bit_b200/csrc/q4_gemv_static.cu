@@ -52,9 +52,19 @@ extern "C" int q4_gemv_static(const void* x, const int32_t* qweight, void* y, co
                 "use q4_gemv with a caller-provided workspace", need, (size_t)GEMV_STATIC_SCRATCH_BYTES);
   void* scratch = nullptr;
   if (int e = static_scratch(&scratch)) return e;
-  // The array keeps whatever the previous call left.  The kernels need the arrival counters and the
-  // status word at its head to start at zero; a normal call leaves them so, an aborted one may not.
-  if (int e = check_cuda(cudaMemsetAsync(scratch, 0, 65536, (cudaStream_t)stream), "clear scratch head")) return e;
+  // The array keeps whatever the previous call left.  The kernels need the arrival counters at its head to
+  // start at zero; a normal call leaves them so, one whose bounded wait expired may not.  The status word
+  // (the last word of the head) is left alone: it stays set until q4_gemv_static_status has reported it.
+  if (int e = check_cuda(cudaMemsetAsync(scratch, 0, 65536 - 4, (cudaStream_t)stream), "clear scratch head")) return e;
   return q4_gemv(x, qweight, y, scales, qzeros, g_idx, bias, M, K, N, G, groupsize, y_dtype, flags,
                  scratch, GEMV_STATIC_SCRATCH_BYTES, stream);
+}
+
+extern "C" int q4_gemv_static_status(unsigned* out) {
+  if (!out) return fail(Q4_E_BADARG, "gemv_static_status: null pointer");
+  void* scratch = nullptr;
+  if (int e = static_scratch(&scratch)) return e;
+  if (int e = q4_gemv_status(scratch, GEMV_STATIC_SCRATCH_BYTES, out)) return e;
+  if (*out) return check_cuda(cudaMemset((char*)scratch + 65536 - 4, 0, 4), "clear decode status");
+  return Q4_OK;
 }

@@ -21,7 +21,7 @@ import torch
 import torch.nn as nn
 from torch.utils.checkpoint import checkpoint
 
-from .autograd_4bit import Autograd4bitQuantLinear, find_layers, make_quant_for_4bit_autograd
+from .autograd_4bit import Autograd4bitQuantLinear, find_layers, make_quant_for_4bit_autograd, reset_rotary_buffers
 from .models import Linear4bitLt, wrap_with_lora
 
 
@@ -94,13 +94,7 @@ def build_quant_llama(shape: LlamaShape, device, groupsize: int = 128, act_order
                 prm.copy_((torch.randn(prm.shape, generator=gen, device=device) * 0.02).to(prm.dtype))
             else:
                 prm.fill_(1.0)                                     # RMSNorm weights
-    # non-persistent rotary buffers were created on the meta device: recompute them
-    for mod in model.modules():
-        if hasattr(mod, "inv_freq") and hasattr(mod, "compute_default_rope_parameters"):
-            inv, _ = mod.compute_default_rope_parameters(cfg, device)
-            mod.inv_freq = inv
-            if hasattr(mod, "original_inv_freq"):
-                mod.original_inv_freq = inv.clone()
+    reset_rotary_buffers(model, cfg, device)       # non-persistent buffers, created on the meta device
     model.config.use_cache = False
     return model
 
@@ -228,7 +222,10 @@ class LoraFinetuner:
             self.scaler.step(self.opt)                     # unscales, skips the update on inf/nan
             self.scaler.update()
         else:
-            scale = self.loss_scale if self.autocast_dtype == torch.float16 else 1.0     # bf16 needs no loss scaling
+            # The quant linears and the LoRA products compute in fp16 whatever the autocast dtype is (their
+            # autograd functions cast their inputs to fp16, as the reference's do), so the gradients that
+            # flow back through them want the static loss scale under bf16 autocast as well.
+            scale = self.loss_scale
             (loss.float() * scale).backward()
             self.flat.buffer.div_(scale)
             self.flat.all_reduce_mean(self.group)

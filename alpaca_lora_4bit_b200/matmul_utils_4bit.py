@@ -53,6 +53,27 @@ def get_buffer(shape_of_qweight, dtype=torch.float16, device='cuda', bits=4):
     return buf
 
 
+_seq_cache: dict = {}        # id(g_idx) -> (weak reference, storage address, version counter, answer)
+
+
+def _groups_are_sequential(g_idx, groups: int) -> bool:
+    """True when ``g_idx[k] == k // (K / groups)`` for every row, i.e. the layer was quantised without
+    act-order and its groups can be derived from the row index.  One comparison per tensor (it synchronises the
+    device), remembered for as long as the tensor lives and is not written to."""
+    import weakref
+    key = id(g_idx)
+    hit = _seq_cache.get(key)
+    if hit is not None and hit[0]() is g_idx and hit[1] == g_idx.data_ptr() and hit[2] == g_idx._version:
+        return hit[3]
+    K = g_idx.numel()
+    ok = groups > 0 and K % groups == 0
+    if ok:
+        want = torch.arange(K, device=g_idx.device, dtype=torch.int64) // (K // groups)
+        ok = bool(torch.equal(g_idx.reshape(-1).to(torch.int64), want))
+    _seq_cache[key] = (weakref.ref(g_idx, lambda _r, key=key: _seq_cache.pop(key, None)), g_idx.data_ptr(), g_idx._version, ok)
+    return ok
+
+
 def _decode(x, qweight, scales, zeros, g_idx, groupsize, flags):
     dtype = x.dtype
     x2 = x if x.dim() == 2 else x.reshape(-1, x.shape[-1])
@@ -91,9 +112,12 @@ def _matmul4bit_v2(x, qweight, scales, zeros, g_idx, groupsize=None):
     if groupsize is None or groupsize <= 0:
         groupsize = K // scales.shape[0]
     # 'old_faster' derives the group from the row index (quant_cuda_kernel.cu:1023); the other
-    # reference variants read g_idx.  With sequential g_idx both agree, so only act_order (or a
-    # group size the sequential kernel cannot take) selects the per-row lookup.
+    # reference variants read g_idx (matmul_utils_4bit.py:75-83,90-93).  With sequential g_idx both
+    # agree, so the per-row lookup is taken for act_order, for a group size the sequential kernel
+    # cannot take, and - outside 'old_faster' - for a g_idx that is not sequential.
     by_index = act_order or (groupsize % 32 != 0)
+    if not by_index and faster_mode != 'old_faster' and g_idx is not None:
+        by_index = not _groups_are_sequential(g_idx, scales.shape[0])
     if by_index and g_idx is None:
         raise ValueError('act_order decode needs g_idx')
     return _decode(x, qweight, scales, zeros, g_idx if by_index else None, groupsize,
@@ -128,11 +152,15 @@ def _matmul4bit_v2_recons(x, qweight, scales, zeros, g_idx, transpose=False):
     _check_inner(x, qweight, 8, transpose)
     K, N = qweight.shape[0] * 8, qweight.shape[1]
     rows = math.prod(x.shape[:-1])
-    if (not transpose and 0 < rows <= 16 and not act_order and x.is_cuda and x.dtype == torch.float16
-            and scales.dtype == torch.float16 and (K // scales.shape[0]) % 32 == 0 and K % scales.shape[0] == 0):
+    if (not transpose and 0 < rows <= 16 and x.is_cuda and x.dtype == torch.float16 and scales.dtype == torch.float16):
         # a handful of rows above the switch threshold: the streaming decode kernel still ends sooner than a
-        # tensor-core launch whose tiles would be almost all padding
-        return _decode(x, qweight, scales, zeros, None, K // scales.shape[0], 0)
+        # tensor-core launch whose tiles would be almost all padding.  The reconstruct path always honours
+        # g_idx (matmul_utils_4bit.py:121), so the sequential-group kernel is taken only for a g_idx that is
+        # sequential; any other goes to the decode kernel that looks the group of every row up.
+        G = scales.shape[0]
+        if not act_order and K % G == 0 and (K // G) % 32 == 0 and _groups_are_sequential(g_idx, G):
+            return _decode(x, qweight, scales, zeros, None, K // G, 0)
+        return _decode(x, qweight, scales, zeros, g_idx, max(K // G, 1), _lib.GEMV_ACT_ORDER)
     if (fused_gemm and x.dtype == torch.float16 and scales.dtype == torch.float16
             and quant_cuda.gemm_supported(K, N, scales.shape[0], transpose)):
         x2 = x.reshape(-1, x.shape[-1])
@@ -159,18 +187,23 @@ def _matmul2bit_v2_recons(x, qweight, scales, zeros, g_idx, transpose=False):
 
 def matmul4bit(x, qweight, scales, zeros, g_idx=None, groupsize=None):
     """No-grad entry (matmul_utils_4bit.py:146-170): format from ``zeros.dtype``, kernel from M."""
-    if g_idx is not None and not act_order and not debug and (faster_mode in valid_faster_mode or faster_mode == 'disable'):
+    # the sequential-group kernel serves the default 'old_faster' mode, which derives groups from the row index
+    # as the reference's kernel does, and the modes that read g_idx when that g_idx is sequential
+    seq_ok = (g_idx is not None and not act_order and not debug and
+              (faster_mode == 'old_faster' or ((faster_mode == 'faster' or faster_mode == 'disable') and zeros.dtype == torch.int32
+                                               and _groups_are_sequential(g_idx, scales.shape[0]))))
+    if seq_ok:
         # a layer the per-token path has served before: its recorded plan, if this call fits it
         y = quant_cuda.decode_planned(x, qweight, scales, zeros, -1 if groupsize is None else groupsize,
                                       min(16, auto_switch_thd) if use_new and auto_switch else 16)
         if y is not None:
             return y
-    if (x.dim() == 2 and 1 <= x.shape[0] <= 16 and not (use_new and auto_switch and x.shape[0] > auto_switch_thd)
-            and g_idx is not None and zeros.dtype == torch.int32 and x.dtype == torch.float16 and scales.dtype == torch.float16
-            and not act_order and not debug and x.is_cuda and x.is_contiguous()):
+    if (seq_ok and x.dim() == 2 and 1 <= x.shape[0] <= 16 and not (use_new and auto_switch and x.shape[0] > auto_switch_thd)
+            and zeros.dtype == torch.int32 and x.dtype == torch.float16 and scales.dtype == torch.float16
+            and x.is_cuda and x.is_contiguous()):
         # the per-token call: sequential groups, fp16 in and out - straight to the decode kernel
         gs = groupsize if groupsize is not None and groupsize > 0 else x.shape[1] // scales.shape[0]
-        if gs % 32 == 0 and (faster_mode in valid_faster_mode or faster_mode == 'disable'):
+        if gs % 32 == 0:
             return quant_cuda.decode_v2(x, qweight, scales, zeros, gs, plan_key=-1 if groupsize is None else groupsize)
     rows = math.prod(x.shape[:-1])
     large = use_new and auto_switch and rows > auto_switch_thd

@@ -8,7 +8,7 @@
   do not share ``g_idx`` (act-order checkpoints), because one fused layer has one ``g_idx``.
 * ``make_fused_mlp`` does the same for gate/up (``QuantLlamaMLP``, model_attn_mlp_patch.py:165-247).
 * ``inject_lora_layers`` adds a merged q/v LoRA on top of the fused qkv output
-  (model_attn_mlp_patch.py:250-335).
+  (model_attn_mlp_patch.py:250-335); q and v updates may have different widths (grouped-query attention).
 """
 from __future__ import annotations
 
@@ -148,27 +148,46 @@ def make_fused_mlp(m, parent_name='', is_v1_model=False):
 
 
 class CustomLoraLayerMerged(torch.nn.Module):
-    """q and v LoRA factors of one layer stacked: ``lora_A [2, r, K]`` (pre-scaled), ``lora_B [2, N, r]``
-    (model_attn_mlp_patch.py:250-259)."""
+    """q and v LoRA factors of one layer: ``lora_A [2, r, K]`` (pre-scaled by alpha / r) and ``lora_B``,
+    stacked as ``[2, N, r]`` when q and v have the same width (model_attn_mlp_patch.py:250-259).  Under
+    grouped-query attention the v projection is narrower than q: ``lora_B`` is then the pair
+    ``(B_q [N_q, r], B_v [N_v, r])`` and the two products run separately.  ``forward`` returns the pair
+    of updates ``(q update, v update)`` either way."""
 
     def __init__(self, lora_A, lora_B):
         super().__init__()
         self.lora_A = torch.nn.Parameter(lora_A, requires_grad=False)
-        self.lora_B = torch.nn.Parameter(lora_B, requires_grad=False)
+        self.stacked = torch.is_tensor(lora_B)
+        if self.stacked:
+            self.lora_B = torch.nn.Parameter(lora_B, requires_grad=False)
+        else:
+            self.lora_B_q = torch.nn.Parameter(lora_B[0], requires_grad=False)
+            self.lora_B_v = torch.nn.Parameter(lora_B[1], requires_grad=False)
+
+    @property
+    def widths(self):
+        """(q width, v width) of the update."""
+        return (self.lora_B.shape[1], self.lora_B.shape[1]) if self.stacked else (self.lora_B_q.shape[0], self.lora_B_v.shape[0])
 
     def forward(self, x):
-        return torch.einsum('bjm,ndm,nkd->nbjk', x, self.lora_A, self.lora_B)
+        if self.stacked:
+            return torch.einsum('bjm,ndm,nkd->nbjk', x, self.lora_A, self.lora_B)
+        u = torch.einsum('bjm,ndm->nbjd', x, self.lora_A)
+        return u[0] @ self.lora_B_q.t(), u[1] @ self.lora_B_v.t()
 
 
 class LoraInjectionWrapper:
-    """Adds the merged q/v LoRA onto the first and last slice of a fused qkv output
-    (model_attn_mlp_patch.py:262-280); ``q_size``/``v_size`` default to a third of the width (MHA)."""
+    """Adds the merged q/v LoRA onto the q slice (the first ``q_size`` columns) and the v slice (the last
+    ``v_size`` columns) of a fused qkv output (model_attn_mlp_patch.py:262-280).  The slice widths default
+    to the widths of the LoRA update itself, which is a third of the output each for multi-head attention
+    and follows the narrower k/v projections under grouped-query attention."""
 
     def __init__(self, module, lora_layer, q_size=None, v_size=None):
         self.module = module
         self.lora_layer = lora_layer
-        self.q_size = q_size if q_size is not None else module.out_features // 3
-        self.v_size = v_size if v_size is not None else module.out_features // 3
+        widths = lora_layer.widths if hasattr(lora_layer, 'widths') else (module.out_features // 3,) * 2
+        self.q_size = q_size if q_size is not None else widths[0]
+        self.v_size = v_size if v_size is not None else widths[1]
 
     def apply(self):
         self.module.forward_before_lora = self.module.forward
@@ -183,6 +202,16 @@ class LoraInjectionWrapper:
         return result
 
 
+def _read_adapter_weights(lora_path):
+    """``adapter_model.bin`` (PEFT <= 0.6, what the reference reads) or ``adapter_model.safetensors``."""
+    import os
+    bin_path = os.path.join(lora_path, 'adapter_model.bin')
+    if os.path.exists(bin_path):
+        return torch.load(bin_path, map_location='cpu')
+    from safetensors.torch import load_file
+    return load_file(os.path.join(lora_path, 'adapter_model.safetensors'))
+
+
 def inject_lora_layers(model, lora_path, device='cuda', dtype=torch.float16):
     """Load a PEFT adapter (``adapter_config.json`` + ``adapter_model.bin``) and inject its q/v LoRA
     into every fused ``qkv_proj`` (model_attn_mlp_patch.py:283-335)."""
@@ -191,14 +220,16 @@ def inject_lora_layers(model, lora_path, device='cuda', dtype=torch.float16):
         lora_config = json.load(file)
     scaling = lora_config['lora_alpha'] / lora_config['r']
     per_layer = {}
-    for key, value in torch.load(lora_path + '/adapter_model.bin', map_location='cpu').items():
-        key = key.replace('base_model.model.', '')
+    for key, value in _read_adapter_weights(lora_path).items():
+        key = key.replace('base_model.model.', '').replace('.default.weight', '.weight')
         prefix = re.findall(r'^model\.layers\.\d+\.', key)[0]
         per_layer.setdefault(prefix, {})[key.replace(prefix, '')] = value
     lora_layers = {}
     for prefix, w in per_layer.items():
         a = torch.stack([w['self_attn.q_proj.lora_A.weight'], w['self_attn.v_proj.lora_A.weight']]).to(device=device, dtype=dtype)
-        b = torch.stack([w['self_attn.q_proj.lora_B.weight'], w['self_attn.v_proj.lora_B.weight']]).to(device=device, dtype=dtype)
+        bq = w['self_attn.q_proj.lora_B.weight'].to(device=device, dtype=dtype)
+        bv = w['self_attn.v_proj.lora_B.weight'].to(device=device, dtype=dtype)
+        b = torch.stack([bq, bv]) if bq.shape == bv.shape else (bq, bv)       # unequal under grouped-query attention
         lora_layers[prefix] = CustomLoraLayerMerged(a * scaling, b).to(device=device, dtype=dtype)
     wrappers = []
     for n, m in model.named_modules():
@@ -206,7 +237,8 @@ def inject_lora_layers(model, lora_path, device='cuda', dtype=torch.float16):
             if getattr(m, 'is_lora_injected', False):
                 m.forward = m.forward_before_lora
             prefix = re.findall(r'^model\.layers\.\d+\.', n)[0]
-            wrapper = LoraInjectionWrapper(m, lora_layers[prefix])
+            q_size, v_size = lora_layers[prefix].widths
+            wrapper = LoraInjectionWrapper(m, lora_layers[prefix], q_size=q_size, v_size=v_size)
             wrapper.apply()
             wrappers.append(wrapper)
     print('Lora Injected.')

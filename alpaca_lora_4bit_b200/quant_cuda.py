@@ -291,17 +291,35 @@ def gemm_set_variant(variant: int) -> None:
 
 
 def gemv_set_variant(variant: int) -> None:
-    """How the sequential-group decode kernel gets x: 0 = chosen per shape (default), 1 = every unit brings its
-    own slice, 2 = every CTA re-lays the whole of x out once (where it fits shared memory)."""
+    """Form of the sequential-group decode kernel, a sum of: bits 0-1 how it gets x (0 = chosen per shape,
+    the default; 1 = every unit brings its own slice; 2 = every CTA re-lays the whole of x out once where it
+    fits shared memory); 4 = always deal an even share of all units (straddled column tiles meet in the
+    workspace); 8 = one-row products in the one-CTA-per-SM form; 32 / 64 = one-row products with 10 / 8 warps
+    per CTA in the two-per-SM form."""
     _lib.check(_lib.lib().q4_gemv_set_variant(int(variant)), "gemv_set_variant")
 
 
 def device_status() -> int:
-    """Status word of the fused kernels (synchronises): 0 unless a bounded device-side wait expired."""
+    """Status of every kernel family on the current device (synchronises): 0 unless a bounded device-side
+    wait expired in a fused GEMM kernel (one word per device) or in a decode kernel (one word per decode
+    workspace, i.e. per stream that has run a decode product, plus the built-in scratch of
+    ``q4_gemv_static``).  A non-zero decode word means the workspace head must be cleared before reuse;
+    this function does that for the workspaces this module owns."""
     import ctypes
+    L = _lib.lib()
     v = ctypes.c_uint(0)
-    _lib.check(_lib.lib().q4_device_status(ctypes.byref(v)), "device_status")
-    return v.value
+    _lib.check(L.q4_device_status(ctypes.byref(v)), "device_status")
+    status = v.value
+    cur = torch.cuda.current_device()
+    for (index, _stream), ws in list(_lib._workspaces.items()):
+        if index != cur:
+            continue
+        _lib.check(L.q4_gemv_status(ws.data_ptr(), ws.numel(), ctypes.byref(v)), "gemv_status")
+        if v.value:
+            ws[:65536].zero_()
+            status = status or v.value
+    _lib.check(L.q4_gemv_static_status(ctypes.byref(v)), "gemv_static_status")
+    return status or v.value
 
 
 def _half(t):

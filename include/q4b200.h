@@ -7,6 +7,11 @@
  * success or a negative Q4_E_* code; q4_last_error_string() then gives a human-readable
  * reason (thread-local).  Launches are asynchronous on `stream`.
  *
+ * Threads: q4_gemv, q4_gemm_*, q4_recons_* and q4_layer_* may be called from several threads at
+ * once as long as calls that share a workspace are ordered on one stream.  The q4_*_set_variant
+ * and q4_*_set_trace switches are process-wide and unsynchronised: set them while no other thread
+ * is inside the library (they exist for tests and measurements).
+ *
  * Tensor conventions (GPTQ v2, as stored by Autograd4bitQuantLinear, autograd_4bit.py:176-189):
  *   qweight int32 [K/8, N]   nibble j of word (r, n) is level q of row k = 8r + j, column n
  *   qzeros  int32 [G, N/8]   nibble n%8 of word (g, n/8) is the stored zero point z (kernel adds 1)
@@ -45,7 +50,8 @@ extern "C" {
 #define Q4_GEMV_ACT_ORDER  2u  /* take the group of every row from g_idx (else k / groupsize)      */
 #define Q4_GEMV_V1         4u  /* v1 layer: scales fp16 [N]; `qzeros` points at fp16 zeros [N];
                                   W = scales[n]*q - zeros[n]; G, groupsize and g_idx are ignored;
-                                  K must be a multiple of 256 (Q4_E_SHAPE otherwise) */
+                                  K must be a multiple of 128 (Q4_E_SHAPE otherwise), as for the
+                                  reference's v1 kernel */
 
 typedef void* q4_stream_t;     /* a cudaStream_t */
 
@@ -155,6 +161,17 @@ size_t q4_gemm_workspace_bytes(int K, int N, int G);
 /* Copies the device status word to *out (synchronises the device): 0, or 0xDEAD0001 if a bounded
  * wait inside a q4_gemm_* kernel expired (its output is then invalid). */
 int q4_device_status(unsigned* out);
+/* The same for the decode kernels, which keep their status word with the workspace they were given
+ * (its head's last word) instead of in a device global: synchronises the device and copies the word
+ * of `workspace` to *out - 0, or 0xDEAD0001 if a bounded wait inside a q4_gemv kernel that used
+ * this workspace expired.  The output of that call is invalid and arrival counters in the head may
+ * be left non-zero: clear the first 64 KiB of the workspace (which also clears the word) before it
+ * is used again.  No counterpart in the reference, whose kernels wait on nothing. */
+int q4_gemv_status(const void* workspace, size_t workspace_bytes, unsigned* out);
+/* The status word of the built-in scratch of q4_gemv_static on the current device; a non-zero word
+ * is cleared once it has been reported (q4_gemv_static itself re-zeroes the counters before every
+ * launch but leaves the word for this call to find). */
+int q4_gemv_static_status(unsigned* out);
 
 /* Profiling aid: when `device_buffer` is non-NULL, every CTA of the sequential-group decode kernel
  * writes SM cycle counters at fixed points of its life into 64 uint64 slots (buffer of at least
@@ -168,10 +185,17 @@ int q4_gemm_set_trace(void* device_buffer);
  * otherwise), 1 = always the single-CTA kernel, 2 / 3 = always the CTA-pair kernel with 256- /
  * 512-row tiles (calls it cannot serve then fail with Q4_E_SHAPE).  For tests and measurements. */
 int q4_gemm_set_variant(int variant);
-/* How the sequential-group decode kernel gets x (process-wide; no reference counterpart): 0 = choose
- * per shape (the default: with two or more rows every CTA re-lays the whole of x out once when it has more
- * than one column tile's worth of units and x fits its shared memory; else every 4 KiB unit brings its own slice),
- * 1 = always per unit, 2 = per CTA wherever it fits.  For tests and measurements. */
+/* Forms of the sequential-group decode kernel, for tests and measurements (process-wide; no
+ * reference counterpart).  `variant` is a sum of:
+ *   bits 0-1  how the kernel gets x: 0 = choose per shape (the default: with two or more rows every CTA
+ *             re-lays the whole of x out once when it has more than one column tile's worth of units and x
+ *             fits its shared memory; else every 4 KiB unit brings its own slice), 1 = always per unit,
+ *             2 = per CTA wherever it fits
+ *   4         deal an even share of all units to every CTA even where whole column tiles per CTA would
+ *             end sooner (column tiles that straddle CTAs then meet in the workspace)
+ *   8         one-row products: the one-CTA-per-SM form instead of the two-per-SM form
+ *   32, 64    one-row products, two-per-SM form: 10 resp. 8 warps per CTA instead of 11
+ * Values outside these combinations are refused with Q4_E_BADARG. */
 int q4_gemv_set_variant(int variant);
 
 #ifdef __cplusplus

@@ -50,7 +50,14 @@ def test_bad_arguments_are_rejected_without_a_device():
     assert L.q4_gemv(*args, 1, 100, 128, 1, 128, 0, 0, None, 0, None) == -2
     assert L.q4_gemv(*args, 1, 128, 128, 1, 128, 0, 2, None, 0, None) == -1
     assert L.q4_gemv(*args, 1, 128, 128, 1, 48, 0, 0, None, 0, None) == -2
-    assert L.q4_gemv(*args, 1, 4224, 128, 1, 4224, 0, 4, None, 0, None) == -2       # v1 layer, K not a multiple of 256
+    assert L.q4_gemv(*args, 1, 4192, 128, 1, 4192, 0, 4, None, 0, None) == -2       # v1 layer, K not a multiple of 128
+    # decode status: null pointers and a size no decode workspace has are refused before any device call
+    v = ctypes.c_uint(0)
+    assert L.q4_gemv_status(None, 1 << 20, ctypes.byref(v)) == -1
+    assert L.q4_gemv_status(fake, 100, ctypes.byref(v)) == -4
+    assert L.q4_gemv_static_status(None) == -1
+    assert L.q4_gemv_set_variant(3) == -1 and L.q4_gemv_set_variant(128) == -1 and L.q4_gemv_set_variant(4 + 8 + 1) == 0
+    assert L.q4_gemv_set_variant(0) == 0
     assert L.q4_gemv_workspace_bytes(1, 100, 128) == 0
     assert L.q4_gemv_workspace_bytes(16, 11008, 4096) > 0
     # layer handle: made and destroyed on the host; bad geometry and null pointers give no handle

@@ -235,10 +235,11 @@ def test_gemv_v1_facade():
 
 
 @pytest.mark.parametrize("M", [1, 4, 8, 13])
-@pytest.mark.parametrize("K,N", [(4096, 4096), (11008, 1024), (1024, 5120), (512, 4768)])
+@pytest.mark.parametrize("K,N", [(4096, 4096), (11008, 1024), (1024, 5120), (512, 4768), (4224, 2048), (384, 512)])
 def test_gemv_v1_shapes(K, N, M):
     """First-format layers (one scale and one fp16 zero term per column) through the C ABI, against the
-    oracle's reconstruct + matmul; output rows beyond M untouched."""
+    oracle's reconstruct + matmul; output rows beyond M untouched.  K = 4224 and 384 end in a half-filled
+    256-row unit (the reference's kernel takes K in multiples of 128)."""
     gen = torch.Generator().manual_seed(K + N + M)
     layer = synth.make_layer(K, N, K, False, seed=K + N)
     sc = (torch.rand(N, generator=gen) * 0.018 + 0.002).half()
@@ -310,6 +311,83 @@ def test_gemv_x_per_unit_and_per_cta_agree(K, N, M):
     assert torch.equal(got[0], got[1]) or torch.equal(got[0], got[2])
     torch.cuda.synchronize()
     assert quant_cuda.device_status() == 0
+
+
+def _head_is_zero():
+    return all(int(ws[:65536].view(torch.int32).abs().sum()) == 0 for ws in _lib._workspaces.values())
+
+
+@pytest.mark.parametrize("M", [1, 3, 8])
+@pytest.mark.parametrize("K,N,forced", [(32768, 1024, False), (28672, 512, False), (4096, 4096, True), (4096, 11008, True),
+                                        (11008, 4096, True), (4224, 2048, True)])
+def test_gemv_even_split_meets_in_workspace(K, N, forced, M):
+    """The lean kernel dealing an even share of all units to every CTA: column tiles straddle CTAs, their
+    partial sums go through the workspace (partial, fence, counter, the last CTA to arrive adds them in CTA
+    order).  Long-K, few-column layers take this dealing by the host's own choice; on the LLaMA-7B shapes
+    (and one with a half-filled last unit) it is forced with variant bit 4, in the one- and the two-CTA-per-SM
+    form.  Twice on one workspace: same bits, counters back to zero, no expired wait."""
+    layer = synth.make_layer(K, N, 128, False, seed=K // 5 + N + M)
+    x = synth.make_acts(M, K, seed=M + 9)
+    want = orc.gemv_fp32(x, layer.qweight, layer.scales, layer.qzeros, layer.g_idx)
+    try:
+        for variant in ((4, 12) if forced else (0, 8)):
+            quant_cuda.gemv_set_variant(variant)
+            first = gemv_gpu(layer, x, torch.float32)
+            again = gemv_gpu(layer, x, torch.float32)
+            assert rel_fro(first, want) <= REL_TOL, variant
+            assert torch.equal(first, again), variant
+            assert _head_is_zero(), variant
+    finally:
+        quant_cuda.gemv_set_variant(0)
+    assert quant_cuda.device_status() == 0
+
+
+@pytest.mark.parametrize("K,N", [(4096, 4096), (4096, 11008), (11008, 4096), (4224, 1024), (512, 4768)])
+def test_gemv_one_row_forms_agree(K, N):
+    """One-row products through every form of the lean kernel (two CTAs per SM with 11, 10 and 8 warps, one
+    CTA per SM with 16): each within tolerance of the oracle; forms differ only in which warp adds which
+    units, so they agree to the rounding of fp32 sums of a few thousand terms."""
+    layer = synth.make_layer(K, N, 128, False, seed=K + 3 * N)
+    x = synth.make_acts(1, K, seed=17)
+    want = orc.gemv_fp32(x, layer.qweight, layer.scales, layer.qzeros, layer.g_idx)
+    got = {}
+    try:
+        for variant in (0, 32, 64, 8):
+            quant_cuda.gemv_set_variant(variant)
+            got[variant] = gemv_gpu(layer, x, torch.float32)
+            assert rel_fro(got[variant], want) <= REL_TOL, variant
+    finally:
+        quant_cuda.gemv_set_variant(0)
+    for variant in (32, 64, 8):
+        assert rel_fro(got[variant], got[0]) <= 2e-4
+    assert quant_cuda.device_status() == 0
+
+
+def test_decode_status_word_is_reported_and_cleared():
+    """An expired bounded wait in a decode kernel is recorded in the last word of the workspace head.  Nothing
+    here makes a wait expire on the GPU: the word is written from the host, then ``q4_gemv_status`` must return
+    it, ``quant_cuda.device_status`` must report it and hand back a clean workspace, and the next product on
+    that workspace must be right."""
+    import ctypes
+    layer = synth.make_layer(1024, 2048, 128, False, seed=5)
+    x = synth.make_acts(2, 1024, seed=6)
+    want = orc.gemv_fp32(x, layer.qweight, layer.scales, layer.qzeros, layer.g_idx)
+    assert rel_fro(gemv_gpu(layer, x, torch.float32), want) <= REL_TOL
+    assert quant_cuda.device_status() == 0
+    dev = torch.device(DEV)
+    ws = _lib.workspace_for(dev, torch.cuda.current_stream(dev).cuda_stream)
+    word = ws[65536 - 4:65536].view(torch.int32)
+    word.fill_(0xDEAD0001 - (1 << 32))
+    ws[:8].view(torch.int32).fill_(3)                      # counters an aborted launch could leave behind
+    v = ctypes.c_uint(0)
+    with torch.cuda.device(dev):
+        _lib.check(_lib.lib().q4_gemv_status(ws.data_ptr(), ws.numel(), ctypes.byref(v)), "status")
+        assert v.value == 0xDEAD0001
+        assert _lib.lib().q4_gemv_status(ws.data_ptr(), 100, ctypes.byref(v)) == -4
+        assert quant_cuda.device_status() == 0xDEAD0001
+        assert quant_cuda.device_status() == 0
+    assert _head_is_zero()
+    assert rel_fro(gemv_gpu(layer, x, torch.float32), want) <= REL_TOL
 
 
 def test_workspace_counters_return_to_zero():
