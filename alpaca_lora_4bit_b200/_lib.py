@@ -33,6 +33,7 @@ _SIGNATURES = {
     "q4_layer_create": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int]),
     "q4_layer_gemv": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_size_t, c_void_p]),
     "q4_layer_destroy": (None, [c_void_p]),
+    "q4_layer_set_next": (c_int, [c_void_p, c_void_p]),
     "q4_gemv_set_trace": (c_int, [c_void_p]),
     "q4_gemm_set_trace": (c_int, [c_void_p]),
     "q4_gemm_set_variant": (c_int, [c_int]),

@@ -163,8 +163,14 @@ struct GemvStreamParams {
   // ceil(2^32 / d) that turn its divisions by the grid size and by units_per_tile into one multiply
   // (exact while dividend * d < 2^32, which the host checks)
   unsigned share, per, magic_grid, magic_upt;
-  // warp-specialised kernel: CTAs that have work (the grid may be larger: see launch_ws)
+  // warp-specialised kernel: CTAs that have work (the grid may be larger: see launch_ws) and the word in the
+  // workspace (after the head) through which they tell the spare CTAs that the launch is about to end
   int work_ctas;
+  unsigned* leave_signal;
+  int prefetch_rows;                              // packed rows per L2 prefetch box (0: no prefetch)
+  // the layer the caller will run next (q4_layer_set_next): its packed weights are asked into L2 while this
+  // one computes; column tiles, boxes per tile and packed rows per box of that layer (0 rows: none)
+  int next_tiles, next_bpt, next_rows, next_late;
 };
 
 template <int MT>
@@ -917,25 +923,34 @@ gemv_fast_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
 }
 
 // ---- one row, groups of 128: the warp-specialised decode kernel ------------------------------------
-// A cycle trace of the lean kernel above showed what a warp spends per 4 KiB unit: 420-590 cycles re-laying
-// its slice of x out, 1400-1700 on unpack + MMA + closing the two groups, 520-750 issuing the next copies
-// (one TMA copy, a handful of 16-byte asynchronous copies, the barrier arrive) - and that the time per unit
-// hardly moves with the number of warps: every warp is bound by the latency of its own instruction stream,
-// not by issue slots.  Here the two side jobs leave the consumers' stream:
-//   * warp W issues every TMA copy of the CTA (lane c those of consumer c): the 4 KiB units of all consumer rings, in the
-//     order they are consumed, and per column tile one box each of the tile's scales and packed zero points
-//     (all groups).  None of that depends on an earlier kernel, so it starts before griddepcontrol.wait.
-//   * warps 0..W-1 wait for the earlier kernels of the stream and write, together and once, x' (MMA order, odd
-//     elements / 16) and the per-128-row sums of x for the whole of K into shared memory; then they
-//     consume: wait for the unit (and, once per tile, for the tile's metadata), unpack, MMA, close the two
-//     groups, release the stage.  The sums of a column tile meet exactly as in the lean kernel.
-// Stage ring per consumer: S units of 4 KiB (TMA, 128-byte swizzle).  With W = 8 and S = 2 a CTA takes less
-// than half of the SM's shared memory and registers: the next decode launch of the stream becomes resident
-// beside it, fills its rings and parks in griddepcontrol.wait while this one is still computing.
+// What the measurements on a B200 said about the lean kernel above, and what this kernel does about it:
+//   * With every weight byte already in L2 a launch is hardly faster than from HBM: the one-row product is
+//     bound by instruction issue and by the latency chain of a launch, not by memory.  The non-tensor pipes
+//     issue one warp instruction per two cycles per scheduler (LOP3, SHF, PRMT, IMAD, HFMA2 alike), the legacy
+//     mma.sync path one m16n8k16 per 8 cycles; unpacking to fp16 costs 5 integer instructions per 8 weights.
+//     Here the packed words are split into bytes, not halves: w & 0x0F0F0F0F and (w >> 4) & 0x0F0F0F0F are the
+//     eight levels of a word as two u8x4 operands of mma.sync.m16n8k32 (3 instructions per 8 weights, and half
+//     as many MMAs per weight).  x is converted once per CTA to 16-bit block fixed point - per group of 128
+//     rows x_int = rn(x * 2^(14 - E)), 2^E <= max |x| of the group - and enters as two byte digits
+//     (x_int = 256 hi + lo, hi signed, lo unsigned).  Products and sums are exact integers; the zero point
+//     leaves through the exact integer sum of the group's x_int; the only rounding of the whole product is
+//     that of x itself: none for elements within a factor 16 of their group's largest, an absolute error of at
+//     most 2^(E-15) for the smaller ones.
+//   * A warp of the lean kernel spent a fifth of its time per unit re-laying x out and a fifth issuing its
+//     next copies.  Here the consumers convert x once, together, while the first weights are still on their
+//     way, and refills are issued by a warp of their own (lane c for consumer c: issued one after the other
+//     by one thread a copy costs 300 cycles, issued side by side by the lanes of one instruction under 100).
+//   * Every consumer sets up its own two barriers and issues its own first copies, so that the launch's
+//     copies are all under way a few hundred cycles after the CTA starts.
+// Roles: warps 0..W-1 consume; warp W issues the metadata boxes (scales and packed zero points of all groups
+// of a column tile, one TMA box each), the L2 prefetches and the refills.  Stage ring per consumer: S units
+// of 4 KiB (TMA, 128-byte swizzle).  Two shapes of the kernel: W = 16, one CTA per SM; W = 8 at less than half
+// of the SM's shared memory and registers, so that the next decode launch of the stream becomes resident
+// beside this one and fills its rings while this one computes.
 constexpr int WS_MAX_UNITS_PER_TILE = 256;             // K <= 65536
 
 struct WsLayout {                                      // byte offsets from the 1 KiB-aligned base
-  int stages, meta, meta_slot, meta_zp, xp, sums, red, bars, total;
+  int stages, meta, meta_slot, meta_zp, xp, xinfo, red, bars, total;
 };
 __host__ __device__ inline WsLayout ws_layout(int W, int S, int G, int upt) {
   WsLayout l;
@@ -944,8 +959,8 @@ __host__ __device__ inline WsLayout ws_layout(int W, int S, int G, int upt) {
   l.meta_zp = (G * 64 + 127) / 128 * 128;              // scales [G][32] fp16, then zero points [G][4] words
   l.meta_slot = l.meta_zp + (G * 16 + 127) / 128 * 128;
   l.xp = l.meta + 2 * l.meta_slot;
-  l.sums = l.xp + upt * 512;
-  l.red = l.sums + upt * 16;
+  l.xinfo = l.xp + upt * 512;                          // x digits: 16 bytes per 8 k
+  l.red = l.xinfo + upt * 16;                          // per 128 k: (2^(E-14), sum of x_int)
   l.bars = (l.red + W * GEMV_TN * 4 + 15) / 16 * 16;
   l.total = l.bars + 8 * (2 * W * S + 4) + 16;
   return l;
@@ -963,144 +978,262 @@ __device__ __forceinline__ bool mbar_spin_bounded(uint64_t* bar, uint32_t parity
     if (mbar_test_wait(bar, parity)) return true;
   return false;
 }
+__device__ __forceinline__ void named_bar_sync_all(int id, int threads) {
+  asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(threads) : "memory");
+}
+// D += A (u8, 16 x 32) * B (s8 or u8, 32 x 8), s32 accumulators
+__device__ __forceinline__ void imma_u8s8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void imma_u8u8(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+r"(c[0]), "+r"(c[1]), "+r"(c[2]), "+r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+
+// the same with the accumulators starting at zero (first step of a group)
+__device__ __forceinline__ void imma_u8s8_first(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+               : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
+__device__ __forceinline__ void imma_u8u8_first(int (&c)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+  asm volatile("mma.sync.aligned.m16n8k32.row.col.s32.u8.u8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%10,%10,%10,%10};"
+               : "=r"(c[0]), "=r"(c[1]), "=r"(c[2]), "=r"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1), "r"(0));
+}
 
 template <int W, int S, int OCC, bool TRACE>
 __global__ void __launch_bounds__((W + 1) * 32, OCC)
 gemv_ws_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap,
-               const __grid_constant__ CUtensorMap zmap, const GemvStreamParams sp) {
+               const __grid_constant__ CUtensorMap zmap, const __grid_constant__ CUtensorMap pmap,
+               const __grid_constant__ CUtensorMap nmap, const GemvStreamParams sp) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
   const GemvParams& p = sp.g;
   unsigned long long* const trc = TRACE ? sp.trace : nullptr;
   const int upt = sp.units_per_tile, G = sp.n_groups;
   const WsLayout L = ws_layout(W, S, G, upt);
-  unsigned char* xp = smem + L.xp;                                   // x' of the whole row: 16 bytes per 8 k
-  float2* sums = reinterpret_cast<float2*>(smem + L.sums);           // [K / 128]: (offset sum, plain sum)
+  unsigned char* xp = smem + L.xp;                                   // digits of x_int: 16 bytes per 8 k
+  float2* xinfo = reinterpret_cast<float2*>(smem + L.xinfo);         // [K / 128]: (2^(E-14), sum of x_int)
   float* red = reinterpret_cast<float*>(smem + L.red);               // [W][32]
   uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.bars);       // [W][S]  unit has landed
   uint64_t* empty = full + W * S;                                    // [W][S]  unit has been consumed
   uint64_t* mfull = empty + W * S;                                   // [2]     metadata of a tile has landed
   uint64_t* mempty = mfull + 2;                                      // [2]     every consumer is done with it
   volatile int* flags = reinterpret_cast<volatile int*>(mempty + 2);
+  constexpr int ALL = (W + 1) * 32, CT = W * 32;
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (threadIdx.x == 0) trace_mark_ns(trc, 40);
   const int nu = sp.total_units, Gd = sp.work_ctas;
   if ((int)blockIdx.x >= Gd) {
     // A CTA without work.  The two-per-SM form always launches one CTA per SM, so that every SM holds exactly
-    // one CTA of this launch and one of the next (CTAs of one launch that share an SM halve each other's
-    // speed); the spare ones stay resident until the earlier kernels of the stream are done, then leave.
+    // one CTA of this launch and one of the next (two CTAs of one launch on an SM halve each other's speed,
+    // and the launch ends with the slower ones).  A spare CTA therefore keeps its place for about as long as
+    // the working ones: until the first of them says that it has begun its last round of units.  The word
+    // they count up is never reset (what matters is that it changes), and the wait is bounded.
     pdl_launch_dependents();
-    pdl_wait();
-    return;
-  }
-  const unsigned share = sp.share, per = sp.per;
-  const int u0 = (int)(__umulhi((unsigned)blockIdx.x * share, sp.magic_grid) * per);
-  const int u1 = (int)(__umulhi(((unsigned)blockIdx.x + 1u) * share, sp.magic_grid) * per);
-
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < W * S; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
-    mbar_init(&mfull[0], 1); mbar_init(&mfull[1], 1);
-    mbar_init(&mempty[0], W); mbar_init(&mempty[1], W);
-    flags[0] = 0;
-    mbar_fence_init();
-    tma_prefetch_desc(&wmap); tma_prefetch_desc(&smap); tma_prefetch_desc(&zmap);
-  }
-  __syncthreads();
-  pdl_launch_dependents();
-  const uint32_t meta_tx = (uint32_t)G * 80u;
-
-  if (warp == W) {
-    // ---- copy issuer ---------------------------------------------------------------------------------
-    // Lane c feeds consumer c: one instruction of the warp issues the copies of a whole round of W units
-    // (a single thread issuing them one after the other needs some 300 cycles per copy, more than a
-    // consumer needs per unit).  The lane whose unit opens a column tile brings the tile's metadata first.
-    if (lane < W) {
-      const int tile_first = (int)__umulhi((unsigned)u0, sp.magic_upt);
-      int u = u0 + lane;
-      int tile = (int)__umulhi((unsigned)u, sp.magic_upt), ux = u - tile * upt;
-      for (int n = 0; u0 + W * n < u1; ++n) {
-        const bool act = u < u1;
-        if (act && (ux == 0 || u == u0)) {       // scales and zero points of all groups of this column tile
-          const int seq = tile - tile_first, slot = seq & 1;
-          if (seq >= 2 && !mbar_wait_sleep_bounded(&mempty[slot], ((seq >> 1) & 1) ^ 1, 200000u)) {
-            flags[0] = 1; atomicExch(sp.status, Q4_STATUS_WAIT_EXPIRED);
-          }
-          unsigned char* m = smem + L.meta + slot * L.meta_slot;
-          mbar_arrive_expect_tx(&mfull[slot], meta_tx);
-          tma_load_2d(m, &smap, tile * GEMV_TN, 0, &mfull[slot]);
-          tma_load_2d(m + L.meta_zp, &zmap, tile * (GEMV_TN / 8), 0, &mfull[slot]);
-        }
-        const int st = n % S;
-        if (act && n >= S && !mbar_wait_sleep_bounded(&empty[lane * S + st], ((n / S) & 1) ^ 1, flags[0] ? 4u : 200000u)) {
-          flags[0] = 1; atomicExch(sp.status, Q4_STATUS_WAIT_EXPIRED);
-        }
-        __syncwarp((1u << W) - 1u);
-        if (TRACE && lane == 0 && n < 8) trace_mark(trc, 8 + n);
-        tma_expect_load_2d_if(act, smem + (size_t)(lane * S + st) * GEMV_UNIT_BYTES, &wmap, tile * GEMV_TN, ux * GEMV_UNIT_ROWS,
-                              &full[lane * S + st], GEMV_UNIT_BYTES);
-        u += W; ux += W;
-        while (ux >= upt) { ux -= upt; ++tile; }
-      }
-      if (TRACE && lane == 0) trace_mark(trc, 16);
+    if (threadIdx.x != 0) return;
+    pdl_wait();                                  // the earlier launch is complete: its count is final
+    const unsigned before = *reinterpret_cast<volatile unsigned*>(sp.leave_signal);
+    for (int i = 0; i < 20000; ++i) {
+      __nanosleep(100);
+      if (*reinterpret_cast<volatile unsigned*>(sp.leave_signal) != before) break;
     }
     return;
   }
+  pdl_launch_dependents();
+  const unsigned share = sp.share, per = sp.per;
+  const int u0 = (int)(__umulhi((unsigned)blockIdx.x * share, sp.magic_grid) * per);
+  const int u1 = (int)(__umulhi(((unsigned)blockIdx.x + 1u) * share, sp.magic_grid) * per);
+  const int tile_first = (int)__umulhi((unsigned)u0, sp.magic_upt), tile_last = (int)__umulhi((unsigned)(u1 - 1), sp.magic_upt);
+  const uint32_t meta_tx = (uint32_t)G * 80u;
+
+  if (warp == W) {
+    // ---- metadata, prefetches, refills -----------------------------------------------------------------
+    if (lane < 2) mbar_init(&mfull[lane], 1);
+    else if (lane < 4) mbar_init(&mempty[lane - 2], W);
+    if (lane == 4) {
+      flags[0] = 0;
+      tma_prefetch_desc(&smap); tma_prefetch_desc(&zmap); tma_prefetch_desc(&pmap);
+      if (sp.next_rows > 0) tma_prefetch_desc(&nmap);
+    }
+    if (lane < 4) mbar_fence_init();
+    __syncwarp();
+    // scales and zero points of all groups of a column tile: one box each into slot (tile - tile_first) & 1
+    auto issue_meta = [&](int tile) {
+      const int seq = tile - tile_first, slot = seq & 1;
+      if (seq >= 2 && !mbar_wait_sleep_bounded(&mempty[slot], ((seq >> 1) & 1) ^ 1, 200000u)) {
+        flags[0] = 1; atomicExch(sp.status, Q4_STATUS_WAIT_EXPIRED);
+      }
+      unsigned char* m = smem + L.meta + slot * L.meta_slot;
+      mbar_arrive_expect_tx(&mfull[slot], meta_tx);
+      tma_load_2d(m, &smap, tile * GEMV_TN, 0, &mfull[slot]);
+      tma_load_2d(m + L.meta_zp, &zmap, tile * (GEMV_TN / 8), 0, &mfull[slot]);
+    };
+    if (lane < 2 && tile_first + lane <= tile_last) issue_meta(tile_first + lane);     // the first two tiles: no waiting
+    __syncwarp();
+    if (OCC == 1) { pdl_wait(); __nanosleep(300); }  // (see the consumers: x and the metadata first)
+    if (lane < W) {
+      constexpr unsigned MASK = (1u << W) - 1u;
+      if (sp.prefetch_rows > 0) {
+        // Ask for the rest of this CTA's share of the layer (what the rings do not hold yet) to be brought into
+        // L2 now, in boxes of `prefetch_rows` packed rows: HBM then streams at its own pace, whatever the
+        // consumers do, and the refills find their bytes a short way off instead of a DRAM round trip away.
+        const int upb = sp.prefetch_rows / GEMV_UNIT_ROWS;                 // units per prefetch box
+        const int bpt = (upt + upb - 1) / upb;                             // boxes per column tile
+        for (int item = lane; item < (tile_last - tile_first + 1) * bpt; item += W) {
+          const int tl = tile_first + item / bpt, bx = item - (item / bpt) * bpt;
+          const int first_u = tl * upt + bx * upb, last_u = min(tl * upt + upt, first_u + upb) - 1;
+          if (last_u >= u0 + W * S && first_u < u1) tma_prefetch_l2_2d(&pmap, tl * GEMV_TN, bx * sp.prefetch_rows);
+        }
+      }
+      if (sp.next_rows > 0) {
+        // The layer that runs after this one (q4_layer_set_next): every CTA asks for its share of that layer's
+        // packed weights.  Nothing here depends on an earlier kernel: weights are never written.
+        const int total = sp.next_tiles * sp.next_bpt;
+        for (int item = (int)blockIdx.x * W + lane; item < total; item += Gd * W) {
+          const int tl = item / sp.next_bpt, bx = item - tl * sp.next_bpt;
+          tma_prefetch_l2_2d(&nmap, tl * GEMV_TN, bx * sp.next_rows);
+        }
+      }
+    }
+    // the consumers' barriers exist from here on (they set them up and fill their rings themselves)
+    named_bar_sync_all(4, ALL);
+    if (lane < W) {
+      constexpr unsigned MASK = (1u << W) - 1u;
+      // lane c follows consumer c: its units are u0 + c + W n; the first S of them are under way already
+      int n = 0, u = u0 + lane;
+      int tile = (int)__umulhi((unsigned)u, sp.magic_upt), ux = u - tile * upt;
+      auto advance = [&]() { u += W; ux += W; ++n; while (ux >= upt) { ux -= upt; ++tile; } };
+      for (int r = 0; r < S; ++r)
+        if (u < u1) {
+          if (ux == 0 && tile - tile_first >= 2) issue_meta(tile);   // a short tile that opens inside the first rounds
+          advance();
+        }
+      bool more = u < u1;
+      if (TRACE && lane == 0) trace_mark(trc, 16);
+      // a stage is refilled as soon as it is released, whatever the other consumers are doing (the polls do
+      // not block); the lane whose unit opens a column tile brings that tile's metadata first
+      uint32_t idle = 0;
+      while (__any_sync(MASK, more)) {
+        const bool ready = more && mbar_test_wait(&empty[lane * S + n % S], ((n / S) & 1) ^ 1);
+        if (ready) {
+          if (ux == 0 && tile - tile_first >= 2) issue_meta(tile);
+          const int st = n % S;
+          mbar_arrive_expect_tx(&full[lane * S + st], GEMV_UNIT_BYTES);
+          tma_load_2d(smem + (size_t)(lane * S + st) * GEMV_UNIT_BYTES, &wmap, tile * GEMV_TN, ux * GEMV_UNIT_ROWS, &full[lane * S + st]);
+          advance();
+          more = u < u1;
+        }
+        if (__any_sync(MASK, ready)) { idle = 0; continue; }
+        __nanosleep(40);
+        if (++idle > (flags[0] ? 64u : 4000000u)) {
+          if (lane == 0) { flags[0] = 1; atomicExch(sp.status, Q4_STATUS_WAIT_EXPIRED); }
+          break;
+        }
+      }
+    }
+    return;
+  }
+
   // ---- consumers ---------------------------------------------------------------------------------------
   if (TRACE && threadIdx.x == 0 && trc) {
     unsigned smid;
     asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
     trc[(size_t)blockIdx.x * 64 + 47] = smid + 1;
   }
-  constexpr int CT = W * 32;                                         // consumer threads (named barriers)
-  // x' (MMA order, odd elements / 16) and the sums of every 128 rows of x, for the whole of K, by all
-  // consumers together: until x is there they have nothing else to do.  CT is a multiple of 16, so the 16
-  // lanes that share a 128-row chunk always hold the 16 blocks of one chunk.
+  // own barriers, then the copies that fill the own ring: weights never depend on an earlier kernel
+  if (lane < S) { mbar_init(&full[warp * S + lane], 1); mbar_init(&empty[warp * S + lane], 1); }
+  if (lane < S) mbar_fence_init();
+  if (warp == 0 && lane == 0) tma_prefetch_desc(&wmap);
+  __syncwarp();
+  auto fill_ring = [&]() {
+    if (lane == 0) {
+      int u = u0 + warp;
+      int tile = (int)__umulhi((unsigned)u, sp.magic_upt), ux = u - tile * upt;
+#pragma unroll 1
+      for (int r = 0; r < S && u < u1; ++r) {
+        mbar_arrive_expect_tx(&full[warp * S + r], GEMV_UNIT_BYTES);
+        tma_load_2d(smem + (size_t)(warp * S + r) * GEMV_UNIT_BYTES, &wmap, tile * GEMV_TN, ux * GEMV_UNIT_ROWS, &full[warp * S + r]);
+        u += W; ux += W;
+        while (ux >= upt) { ux -= upt; ++tile; }
+      }
+    }
+  };
+  // Two per SM: the copies go out at once, long before the earlier launch is done.  One per SM: this CTA
+  // started when the earlier launch was all but over, and what matters is that the few kilobytes of x (and
+  // of metadata) are asked for ahead of the megabytes of weights - behind them they wait microseconds.
+  if (OCC == 2) fill_ring();
+  if (threadIdx.x == 0) trace_mark_ns(trc, 41);
+  // x as 16-bit block fixed point, for the whole of K, by all consumers together.  CT is a multiple of 16, so
+  // the 16 lanes that share a group of 128 rows always hold the 16 blocks (of 8 rows) of one group.
   pdl_wait();                                  // x belongs to the stream order
   if (threadIdx.x == 0) trace_mark_ns(trc, 42);
   {
     const int K = p.K, n_blocks = upt * 32;
     const uint4* xg = reinterpret_cast<const uint4*>(p.x);
+    // (every CTA of the launch reads the same few kilobytes at the same moment: each starts at a different
+    //  place, a whole number of groups in, and wraps around)
+    const int rot = (int)(((unsigned)blockIdx.x * 2654435761u) >> 8) % (n_blocks >> 4) * 16;
+    // a thread converts up to four blocks per pass; the passes' loads are issued together
     for (int base = 0; base < n_blocks; base += 4 * CT) {
       uint4 v[4];
+      int blk[4];
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int blk = base + i * CT + (int)threadIdx.x;
-        v[i] = 8 * blk < K ? __ldg(xg + blk) : make_uint4(0u, 0u, 0u, 0u);
+        const int idx = base + i * CT + (int)threadIdx.x;
+        int b = idx + rot;
+        if (b >= n_blocks) b -= n_blocks;
+        blk[i] = idx < n_blocks ? b : n_blocks;
+        if (base + i * CT < n_blocks) v[i] = 8 * blk[i] < K ? __ldg(xg + blk[i]) : make_uint4(0u, 0u, 0u, 0u);
       }
-      float se[4], so[4];
+      if (OCC == 1 && base == 0) fill_ring();            // x is on its way: now the weights
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
-        const int blk = base + i * CT + (int)threadIdx.x;
+        if (base + i * CT >= n_blocks) break;            // the same for the whole CTA
         const __half2 h01 = as_h2(v[i].x), h23 = as_h2(v[i].y), h45 = as_h2(v[i].z), h67 = as_h2(v[i].w);
-        const __half2 sixteenth = as_h2(0x2C002C00u);
-        const __half2 e04 = __lows2half2(h01, h45), o15 = __hmul2(__highs2half2(h01, h45), sixteenth);
-        const __half2 e26 = __lows2half2(h23, h67), o37 = __hmul2(__highs2half2(h23, h67), sixteenth);
-        if (blk < n_blocks) *reinterpret_cast<uint4*>(xp + (size_t)blk * 16) = make_uint4(as_u32(e04), as_u32(o15), as_u32(e26), as_u32(o37));
+        // largest magnitude of the group (16 lanes x 8 rows), kept as a pair of halves until the end
+        __half2 m2 = __hmax2(__hmax2(__habs2(h01), __habs2(h23)), __hmax2(__habs2(h45), __habs2(h67)));
+#pragma unroll
+        for (int d = 8; d >= 1; d >>= 1) m2 = __hmax2(m2, as_h2(__shfl_xor_sync(0xffffffffu, as_u32(m2), d)));
+        const uint32_t mb = as_u32(m2);
+        uint32_t ef = max(mb & 0x7FFFu, mb >> 16) >> 10;   // exponent field of the largest: 2^(ef-15) <= amax < 2^(ef-14)
+        // to_int = 2^(29 - ef) makes |x_int| < 2^15; a group of subnormals and zeros (field 0) converts like
+        // field 1; an infinity or a NaN (field 31) poisons the group's scale, hence its products
+        const bool bad = ef == 31u;
+        ef = ef ? ef : 1u;
+        const float to_int = __uint_as_float((156u - ef) << 23);
+        const float from_int = bad ? __uint_as_float(0x7FC00000u) : __uint_as_float((98u + ef) << 23);
         const float2 f01 = __half22float2(h01), f23 = __half22float2(h23), f45 = __half22float2(h45), f67 = __half22float2(h67);
-        se[i] = (f01.x + f23.x) + (f45.x + f67.x);
-        so[i] = (f01.y + f23.y) + (f45.y + f67.y);
-      }
+        // x * to_int + 1.5 * 2^23: the float's low 16 bits are x_int in two's complement (round to nearest even)
+        const float magic = 12582912.f;
+        const uint32_t x0 = __float_as_uint(fmaf(f01.x, to_int, magic)), x1 = __float_as_uint(fmaf(f01.y, to_int, magic));
+        const uint32_t x2 = __float_as_uint(fmaf(f23.x, to_int, magic)), x3 = __float_as_uint(fmaf(f23.y, to_int, magic));
+        const uint32_t x4 = __float_as_uint(fmaf(f45.x, to_int, magic)), x5 = __float_as_uint(fmaf(f45.y, to_int, magic));
+        const uint32_t x6 = __float_as_uint(fmaf(f67.x, to_int, magic)), x7 = __float_as_uint(fmaf(f67.y, to_int, magic));
+        // digits: bytes (lo, hi) of the 16-bit two's complement x_int; even rows and odd rows apart
+        const uint32_t e02 = prmt(x0, x2, 0x5140), e46 = prmt(x4, x6, 0x5140);   // lo0 lo2 hi0 hi2
+        const uint32_t o13 = prmt(x1, x3, 0x5140), o57 = prmt(x5, x7, 0x5140);
+        const uint4 dg = make_uint4(prmt(e02, e46, 0x7632), prmt(o13, o57, 0x7632),      // hi even, hi odd
+                                    prmt(e02, e46, 0x5410), prmt(o13, o57, 0x5410));     // lo even, lo odd
+        if (blk[i] < n_blocks) *reinterpret_cast<uint4*>(xp + (size_t)blk[i] * 16) = dg;
+        // sum of the eight x_int: the float patterns minus eight times the pattern of the magic number
+        int xs = (int)(((x0 + x1) + (x2 + x3)) + ((x4 + x5) + (x6 + x7)) - 8u * 0x4B400000u);
 #pragma unroll
-      for (int d = 8; d >= 1; d >>= 1)
-#pragma unroll
-        for (int i = 0; i < 4; ++i) { se[i] += __shfl_xor_sync(0xffffffffu, se[i], d); so[i] += __shfl_xor_sync(0xffffffffu, so[i], d); }
-      if ((lane & 15) == 0) {
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int blk = base + i * CT + (int)threadIdx.x;
-          // the odd elements sit in x' as x / 16: their 1024 offset comes back as 64 x
-          if (blk < n_blocks) sums[blk >> 4] = make_float2(1024.f * se[i] + 64.f * so[i], se[i] + so[i]);
-        }
+        for (int d = 8; d >= 1; d >>= 1) xs += __shfl_xor_sync(0xffffffffu, xs, d);
+        if ((lane & 15) == 0 && blk[i] < n_blocks) xinfo[blk[i] >> 4] = make_float2(from_int, (float)xs);
       }
     }
   }
-  named_bar_sync(3, CT);
+  named_bar_sync(3, CT);                          // x is converted
+  named_bar_sync_all(4, ALL);                     // the metadata barriers exist
   if (threadIdx.x == 0) trace_mark_ns(trc, 43);
   const int g = lane >> 2, t = lane & 3;
+  // Packed words: lane (g, t) takes columns 4g..4g+3 of rows 2t (+1) of every block of eight rows.  With the
+  // rows a quarter-warp reads two apart, the swizzle puts its eight 16-byte chunks on eight different bank groups.
   const uint32_t woff0 = 128u * (2 * t) + 16u * (g ^ (2 * t)), woff1 = 128u * (2 * t + 1) + 16u * (g ^ (2 * t + 1));
   float yacc[4] = {0.f, 0.f, 0.f, 0.f};                              // lanes t = 0: columns 4g .. 4g+3 of the row
-  float ycorr = 0.f;                                                 // lane = column: offsets and zero points
+  float ycorr = 0.f;                                                 // lane = column: zero points
   const unsigned char* my_stages = smem + (size_t)warp * S * GEMV_UNIT_BYTES;
 
   auto finish_tile = [&](int tile, int seq, int seg_first, int seg_last) {
@@ -1124,7 +1257,6 @@ gemv_ws_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
 #pragma unroll
     for (int w = 0; w < W; ++w) v += red[w * GEMV_TN + col];
     named_bar_arrive(2, CT);
-    pdl_wait();                                  // y and the workspace belong to the stream order
     if (whole) { store_y(p, 0, tc0 + col, v); return; }
     float* part = sp.cta_part + ((size_t)blockIdx.x * 2 + (seg_first == 0 ? 1 : 0)) * 16 * GEMV_TN;
     __stcg(part + col, v);
@@ -1149,7 +1281,6 @@ gemv_ws_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     if (lane == 0) p.counters[tile] = 0u;
   };
 
-  const int tile_first = (int)__umulhi((unsigned)u0, sp.magic_upt), tile_last = (int)__umulhi((unsigned)(u1 - 1), sp.magic_upt);
   int n = 0;
   for (int tile = tile_first; tile <= tile_last; ++tile) {
     const int seq = tile - tile_first, slot = seq & 1;
@@ -1164,6 +1295,8 @@ gemv_ws_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         flags[0] = 1; atomicExch(sp.status, Q4_STATUS_WAIT_EXPIRED);
       }
       meta_ready = true;
+      if (tile == tile_last && u + W >= seg_u1 && warp == 0 && lane == 0 && Gd < (int)gridDim.x)
+        atomicAdd(sp.leave_signal, 1u);          // last round of this CTA: the spare CTAs may go (see the top)
       if (warp == 0 && lane == 0 && n < 8) trace_mark(trc, 20 + 2 * n);
       const unsigned char* wst = my_stages + (size_t)st * GEMV_UNIT_BYTES;
       const uint4* xq = reinterpret_cast<const uint4*>(xp + 512 * ux) + 2 * t;
@@ -1176,44 +1309,43 @@ gemv_ws_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
           wv[uu] = *reinterpret_cast<const uint4*>(wst + ((uu & 1) ? woff1 : woff0) + 1024 * (2 * h + (uu >> 1)));
           xv[uu] = xq[8 * (2 * h + (uu >> 1)) + (uu & 1)];
         }
-        float c[2][2][4];                              // [chain][column pair][fragment]: two chains per column pair
+        int chi[2][4], clo[2][4];                      // [column pair][fragment]
 #pragma unroll
         for (int uu = 0; uu < 4; ++uu) {
           const uint32_t w[4] = {wv[uu].x, wv[uu].y, wv[uu].z, wv[uu].w};
-          uint32_t pr[4][4];
+          uint32_t ev[4], od[4];                       // levels 0,2,4,6 and 1,3,5,7 of a word's eight rows, one per byte
 #pragma unroll
           for (int q = 0; q < 4; ++q) {
-            const uint32_t w8 = w[q] >> 8;
-            pr[q][0] = and_or(w[q], 0x000F000Fu, 0x64006400u);
-            pr[q][1] = and_or(w[q], 0x00F000F0u, 0x64006400u);
-            pr[q][2] = and_or(w8, 0x000F000Fu, 0x64006400u);
-            pr[q][3] = and_or(w8, 0x00F000F0u, 0x64006400u);
+            ev[q] = w[q] & 0x0F0F0F0Fu;
+            od[q] = (w[q] >> 4) & 0x0F0F0F0Fu;
           }
-          const int ch = uu & 1;
-          if (uu < 2) {
-            mma16816_first(c[ch][0], pr[0][0], pr[1][0], pr[0][1], pr[1][1], xv[uu].x, xv[uu].y);
-            mma16816_first(c[ch][1], pr[2][0], pr[3][0], pr[2][1], pr[3][1], xv[uu].x, xv[uu].y);
+          if (uu == 0) {
+            imma_u8s8_first(chi[0], ev[0], ev[1], od[0], od[1], xv[uu].x, xv[uu].y);
+            imma_u8u8_first(clo[0], ev[0], ev[1], od[0], od[1], xv[uu].z, xv[uu].w);
+            imma_u8s8_first(chi[1], ev[2], ev[3], od[2], od[3], xv[uu].x, xv[uu].y);
+            imma_u8u8_first(clo[1], ev[2], ev[3], od[2], od[3], xv[uu].z, xv[uu].w);
           } else {
-            mma16816(c[ch][0], pr[0][0], pr[1][0], pr[0][1], pr[1][1], xv[uu].x, xv[uu].y);
-            mma16816(c[ch][1], pr[2][0], pr[3][0], pr[2][1], pr[3][1], xv[uu].x, xv[uu].y);
+            imma_u8s8(chi[0], ev[0], ev[1], od[0], od[1], xv[uu].x, xv[uu].y);
+            imma_u8u8(clo[0], ev[0], ev[1], od[0], od[1], xv[uu].z, xv[uu].w);
+            imma_u8s8(chi[1], ev[2], ev[3], od[2], od[3], xv[uu].x, xv[uu].y);
+            imma_u8u8(clo[1], ev[2], ev[3], od[2], od[3], xv[uu].z, xv[uu].w);
           }
-          mma16816(c[ch][0], pr[0][2], pr[1][2], pr[0][3], pr[1][3], xv[uu].z, xv[uu].w);
-          mma16816(c[ch][1], pr[2][2], pr[3][2], pr[2][3], pr[3][3], xv[uu].z, xv[uu].w);
         }
-        // close the group of this half: scale the raw sums; one lane per column takes the offsets and the
-        // zero point out: y -= s * (offset_sum + (z + 1) * x_sum)
+        // close the group of this half: the integer sums of the row (fragments 0 and 2: output columns of
+        // the pair, batch row 0) times scale and 2^(E-14); one lane per column takes the zero point out:
+        // y -= s * (z + 1) * 2^(E-14) * sum of x_int
         const int grp = 2 * ux + h;
+        const float2 xi = xinfo[grp];
         const uint2 sc = *reinterpret_cast<const uint2*>(meta + grp * 64 + 8 * g);
         const float2 s01 = __half22float2(as_h2(sc.x)), s23 = __half22float2(as_h2(sc.y));
-        yacc[0] = fmaf(s01.x, c[0][0][0] + c[1][0][0], yacc[0]);
-        yacc[1] = fmaf(s01.y, c[0][0][2] + c[1][0][2], yacc[1]);
-        yacc[2] = fmaf(s23.x, c[0][1][0] + c[1][1][0], yacc[2]);
-        yacc[3] = fmaf(s23.y, c[0][1][2] + c[1][1][2], yacc[3]);
+        yacc[0] = fmaf(s01.x * xi.x, (float)(chi[0][0] * 256 + clo[0][0]), yacc[0]);
+        yacc[1] = fmaf(s01.y * xi.x, (float)(chi[0][2] * 256 + clo[0][2]), yacc[1]);
+        yacc[2] = fmaf(s23.x * xi.x, (float)(chi[1][0] * 256 + clo[1][0]), yacc[2]);
+        yacc[3] = fmaf(s23.y * xi.x, (float)(chi[1][2] * 256 + clo[1][2]), yacc[3]);
         const float sl = __half2float(*reinterpret_cast<const __half*>(meta + grp * 64 + 2 * lane));
         const uint32_t zw = *reinterpret_cast<const uint32_t*>(meta + L.meta_zp + grp * 16 + 4 * (lane >> 3));
         const float z1 = (float)(((zw >> (4 * (lane & 7))) & 0xFu) + 1u);
-        const float2 e = sums[grp];
-        ycorr = fmaf(sl, fmaf(z1, e.y, e.x), ycorr);
+        ycorr = fmaf(sl * xi.x, z1 * xi.y, ycorr);
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // our reads before the next TMA write
       __syncwarp();
@@ -1324,11 +1456,16 @@ static void gemv_plan(int K, int N, int& S, int& steps_per_split) {
   S = (steps + steps_per_split - 1) / steps_per_split;
 }
 
+// What q4_layer_gemv knows about the layer that follows (set around its call of q4_gemv, on the calling thread)
+struct NextLayer { const int32_t* qweight; int K, N; };
+static thread_local const NextLayer* t_next_layer = nullptr;
+
 static unsigned long long* g_trace = nullptr;                 // set by q4_gemv_set_trace
 static int g_gemv_variant = 0;                                // set by q4_gemv_set_variant
 
 constexpr size_t GEMV_STATUS_OFFSET = GEMV_WS_HEAD - 4;      // status word: last 4 bytes of the head
-constexpr int GEMV_MAX_CTAS = 512;                            // upper bound on SMs for workspace sizing
+constexpr int GEMV_MAX_CTAS = 508;                            // upper bound on SMs for workspace sizing (4 slots' worth of
+                                                              // room is kept for the 256 bytes ahead of the partial sums)
 
 template <int MT, bool FAST, bool XS>
 static int launch_stream(const CUtensorMap& map, const CUtensorMap& smap, const CUtensorMap& zmap,
@@ -1385,8 +1522,8 @@ static int launch_fast_xc(const CUtensorMap& map, const GemvStreamParams& sp, in
 }
 
 template <int W, int S, int OCC, bool TRACE>
-static int launch_ws(const CUtensorMap& wmap, const CUtensorMap& smap, const CUtensorMap& zmap, const GemvStreamParams& sp, int grid,
-                     cudaStream_t st) {
+static int launch_ws(const CUtensorMap& wmap, const CUtensorMap& smap, const CUtensorMap& zmap, const CUtensorMap& pmap,
+                     const CUtensorMap& nmap, const GemvStreamParams& sp, int grid, cudaStream_t st) {
   static std::atomic<bool> attr_done[64];
   int dev = 0;
   cudaGetDevice(&dev);
@@ -1406,7 +1543,7 @@ static int launch_ws(const CUtensorMap& wmap, const CUtensorMap& smap, const CUt
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   at[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = at; cfg.numAttrs = 1;
-  return check_cuda(cudaLaunchKernelEx(&cfg, gemv_ws_kernel<W, S, OCC, TRACE>, wmap, smap, zmap, sp), "gemv launch");
+  return check_cuda(cudaLaunchKernelEx(&cfg, gemv_ws_kernel<W, S, OCC, TRACE>, wmap, smap, zmap, pmap, nmap, sp), "gemv launch");
 }
 
 // warps of the one-CTA-per-SM form: 16, or 12 where the stages of 16 do not fit
@@ -1456,6 +1593,9 @@ struct q4_layer {
   const void* scales;
   const int32_t* qzeros;
   int K, N, G, groupsize;
+  // the layer announced to follow this one (q4_layer_set_next): copies of its fields, not the handle
+  const int32_t* next_qweight;
+  int next_K, next_N;
 };
 
 extern "C" int q4_layer_create(q4_layer_t** out, const int32_t* qweight, const void* scales, const int32_t* qzeros,
@@ -1465,13 +1605,21 @@ extern "C" int q4_layer_create(q4_layer_t** out, const int32_t* qweight, const v
   if (!qweight || !scales || !qzeros) return fail(Q4_E_BADARG, "layer: null pointer");
   if (K <= 0 || N <= 0 || G <= 0 || groupsize <= 0) return fail(Q4_E_BADARG, "layer: K=%d N=%d G=%d groupsize=%d", K, N, G, groupsize);
   if (K % 32 || N % 32) return fail(Q4_E_SHAPE, "layer: K=%d and N=%d must be multiples of 32", K, N);
-  q4_layer* l = new (std::nothrow) q4_layer{qweight, scales, qzeros, K, N, G, groupsize};
+  q4_layer* l = new (std::nothrow) q4_layer{qweight, scales, qzeros, K, N, G, groupsize, nullptr, 0, 0};
   if (!l) return fail(Q4_E_BADARG, "layer: out of host memory");
   *out = l;
   return Q4_OK;
 }
 
 extern "C" void q4_layer_destroy(q4_layer_t* layer) { delete layer; }
+
+extern "C" int q4_layer_set_next(q4_layer_t* layer, const q4_layer_t* next) {
+  if (!layer) return fail(Q4_E_BADARG, "layer: null handle");
+  layer->next_qweight = next ? next->qweight : nullptr;
+  layer->next_K = next ? next->K : 0;
+  layer->next_N = next ? next->N : 0;
+  return Q4_OK;
+}
 
 extern "C" int q4_gemv_set_trace(void* device_buffer) {
   g_trace = (unsigned long long*)device_buffer;
@@ -1489,7 +1637,7 @@ extern "C" size_t q4_gemv_workspace_bytes(int M, int K, int N) {
   int S, sps;
   gemv_plan(K, N, S, sps);
   const size_t split = S > 1 ? (size_t)S * M * N * sizeof(float) : 0;           // act-order kernel
-  const size_t stream = (size_t)GEMV_MAX_CTAS * 2 * 16 * GEMV_TN * sizeof(float); // streaming kernel
+  const size_t stream = (size_t)(GEMV_MAX_CTAS + 4) * 2 * 16 * GEMV_TN * sizeof(float); // streaming kernels
   return GEMV_WS_HEAD + (split > stream ? split : stream);
 }
 
@@ -1604,16 +1752,35 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
       if (M == 1 && !v1 && groupsize == 128 && K % 256 == 0 && G == K / 128 && G <= 256 && sp.units_per_tile <= WS_MAX_UNITS_PER_TILE &&
           !(g_gemv_variant & 16)) {
         sp.work_ctas = grid;
+        sp.leave_signal = (unsigned*)p.part;              // first 256 bytes after the head; the partial sums follow
+        sp.cta_part = p.part + 64;
         CUtensorMap sm2, zm2;                             // all groups of a column tile in one box each
         if (int e = make_tmap_2d(&sm2, scales, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (uint64_t)N, (uint64_t)G, (uint64_t)N * 2,
                                  GEMV_TN, G, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
         if (int e = make_tmap_2d(&zm2, qzeros, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, (uint64_t)(N / 8), (uint64_t)G, (uint64_t)(N / 8) * 4,
                                  GEMV_TN / 8, G, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
-        const bool one_per_sm = g_gemv_variant & 8;
-        if (!one_per_sm && 1024 + (size_t)ws_layout(8, 2, G, sp.units_per_tile).total <= GF_SMEM_LIMIT2)
-          return g_trace ? launch_ws<8, 2, 2, true>(wsw, sm2, zm2, sp, grid, st) : launch_ws<8, 2, 2, false>(wsw, sm2, zm2, sp, grid, st);
+        // L2 prefetch boxes: 8 units (256 packed rows) of one column tile, or the whole tile where it is shorter
+        CUtensorMap pm2;
+        sp.prefetch_rows = (g_gemv_variant & 64) ? 0 : (K / 8 < 256 ? K / 8 : 256);
+        if (int e = make_tmap_2d(&pm2, qweight, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, (uint64_t)N, (uint64_t)(K / 8), (uint64_t)N * 4,
+                                 GEMV_TN, sp.prefetch_rows ? sp.prefetch_rows : 32, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
+        // the layer the caller announced as the next one (q4_layer_set_next): boxes of up to 256 packed rows
+        CUtensorMap nm2 = pm2;
+        sp.next_rows = sp.next_tiles = sp.next_bpt = 0;
+        sp.next_late = (g_gemv_variant & 32) ? 1 : 0;
+        if (t_next_layer && t_next_layer->qweight && !(g_gemv_variant & 64)) {
+          const int rows = t_next_layer->K / 8;
+          sp.next_rows = rows < 256 ? rows : 256;
+          sp.next_tiles = t_next_layer->N / GEMV_TN;
+          sp.next_bpt = (rows + sp.next_rows - 1) / sp.next_rows;
+          if (int e = make_tmap_2d(&nm2, t_next_layer->qweight, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, (uint64_t)t_next_layer->N, (uint64_t)rows,
+                                   (uint64_t)t_next_layer->N * 4, GEMV_TN, sp.next_rows, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
+        }
+        const bool two_per_sm = g_gemv_variant & 8;
+        if (two_per_sm && 1024 + (size_t)ws_layout(8, 2, G, sp.units_per_tile).total <= GF_SMEM_LIMIT2)
+          return g_trace ? launch_ws<8, 2, 2, true>(wsw, sm2, zm2, pm2, nm2, sp, grid, st) : launch_ws<8, 2, 2, false>(wsw, sm2, zm2, pm2, nm2, sp, grid, st);
         if (1024 + (size_t)ws_layout(16, 2, G, sp.units_per_tile).total <= GF_SMEM_LIMIT)
-          return g_trace ? launch_ws<16, 2, 1, true>(wsw, sm2, zm2, sp, grid, st) : launch_ws<16, 2, 1, false>(wsw, sm2, zm2, sp, grid, st);
+          return g_trace ? launch_ws<16, 2, 1, true>(wsw, sm2, zm2, pm2, nm2, sp, grid, st) : launch_ws<16, 2, 1, false>(wsw, sm2, zm2, pm2, nm2, sp, grid, st);
       }
       if (g_trace && M == 1 && !v1) return launch_fast<1, true>(wsw, sp, grid, st);
       return M == 1 ? launch_fast<1, false>(wsw, sp, grid, st) : M == 2 ? launch_fast<2, false>(wsw, sp, grid, st)
@@ -1669,6 +1836,10 @@ extern "C" int q4_gemv_status(const void* workspace, size_t workspace_bytes, uns
 extern "C" int q4_layer_gemv(const q4_layer_t* l, const void* x, void* y, int M,
                              void* workspace, size_t workspace_bytes, q4_stream_t stream) {
   if (!l) return fail(Q4_E_BADARG, "layer: null handle");
-  return q4_gemv(x, l->qweight, y, l->scales, l->qzeros, nullptr, nullptr, M, l->K, l->N, l->G, l->groupsize, Q4_F16, 0u,
-                 workspace, workspace_bytes, stream);
+  NextLayer nx{l->next_qweight, l->next_K, l->next_N};
+  t_next_layer = nx.qweight ? &nx : nullptr;
+  const int rc = q4_gemv(x, l->qweight, y, l->scales, l->qzeros, nullptr, nullptr, M, l->K, l->N, l->G, l->groupsize, Q4_F16, 0u,
+                         workspace, workspace_bytes, stream);
+  t_next_layer = nullptr;
+  return rc;
 }

@@ -10,10 +10,13 @@ than L2, so every launch streams its weights from HBM.  The reported value is al
 bytes (every operand once) per second, summed over ranks; ranks are independent replicas with
 their own pool (the path has no cross-GPU exchange).
 
-``--impl reference`` times the reference's composition (reconstruct to fp16, fp32 matmul —
-matmul_utils_4bit.py:114-127) restated for the CPU in oracle/q4_oracle.py on this box's host
-cores: the reference has no CPU implementation and its CUDA extension does not build against
-the installed torch.
+``--impl reference`` times the reference's own decode path on the same pool: its ``quant_cuda``
+kernels, compiled unmodified for sm_100a into oracle/_ref/ (oracle/build_ref.py), driven as
+``matmul_utils_4bit._matmul4bit_v2`` drives them in its default ``faster_mode='old_faster'``
+(matmul_utils_4bit.py:84-87).  Where that extension was never built the arm falls back to the CPU
+restatement of the reference's composition (reconstruct to fp16 + fp32 matmul,
+matmul_utils_4bit.py:114-127; oracle/q4_oracle.py) on this box's host cores; the reference itself
+has no CPU implementation of the path.
 """
 from __future__ import annotations
 

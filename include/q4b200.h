@@ -107,6 +107,14 @@ int q4_layer_create(q4_layer_t** out, const int32_t* qweight, const void* scales
 int q4_layer_gemv(const q4_layer_t* layer, const void* x, void* y, int M,
                   void* workspace, size_t workspace_bytes, q4_stream_t stream);
 void q4_layer_destroy(q4_layer_t* layer);
+/* Tells `layer` which layer the caller will run after it (NULL: none).  A decode step walks the same
+ * layers in the same order token after token; with the successor known, the one-row kernel of `layer`
+ * asks for the successor's packed weights to be brought into L2 while it computes, so that HBM streams
+ * the next layer during this one instead of idling through its tail and the next launch's start.
+ * A hint only: results never depend on it, a wrong successor costs bandwidth, not correctness.  The
+ * successor's qweight address is copied into `layer`: clear the link (set it to NULL) before that
+ * memory is freed.  No counterpart in the reference. */
+int q4_layer_set_next(q4_layer_t* layer, const q4_layer_t* next);
 
 /* The same product as q4_gemv for callers that cannot allocate device memory (no counterpart in the
  * reference; added for hosts such as a serving process that handed all of HBM to its own pools, a

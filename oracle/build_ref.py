@@ -2,6 +2,9 @@
 
     python oracle/build_ref.py [/path/to/reference]
 
+Without an argument the reference tree is looked for where ``$ALPACA_LORA_4BIT_REFERENCE`` points and then
+in a directory named ``reference`` beside this repository; where there is none, nothing is built.
+
 The two source files are compiled where they lie (``src/alpaca_lora_4bit/quant_cuda/quant_cuda.cpp`` and
 ``quant_cuda_kernel.cu``), unmodified; ``oracle/ref_shim.h`` is force-included to supply one overload the
 installed torch no longer has.  The result, ``oracle/_ref/quant_cuda_ref.so``, is test infrastructure: it lets
@@ -22,7 +25,21 @@ def built_path() -> str:
     return os.path.join(OUT, NAME + ".so")
 
 
-def build(reference_root: str = "/root/reference", verbose: bool = False) -> str | None:
+def find_reference() -> str | None:
+    """Root of the reference tree: ``$ALPACA_LORA_4BIT_REFERENCE``, else ``../reference`` seen from the
+    repository root; None if neither holds the extension's sources."""
+    cands = [os.environ.get("ALPACA_LORA_4BIT_REFERENCE"), os.path.join(os.path.dirname(os.path.dirname(HERE)), "reference")]
+    for c in cands:
+        if c and os.path.exists(os.path.join(c, "src", "alpaca_lora_4bit", "quant_cuda", "quant_cuda_kernel.cu")):
+            return c
+    return None
+
+
+def build(reference_root: str | None = None, verbose: bool = False) -> str | None:
+    if reference_root is None:
+        reference_root = find_reference()
+    if reference_root is None:
+        return None
     src = os.path.join(reference_root, "src", "alpaca_lora_4bit", "quant_cuda")
     cpp, cu = os.path.join(src, "quant_cuda.cpp"), os.path.join(src, "quant_cuda_kernel.cu")
     if not (os.path.exists(cpp) and os.path.exists(cu)):
@@ -52,5 +69,4 @@ def load():
 
 
 if __name__ == "__main__":
-    root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
-    print(build(root, verbose=True))
+    print(build(sys.argv[1] if len(sys.argv) > 1 else None, verbose=True))
