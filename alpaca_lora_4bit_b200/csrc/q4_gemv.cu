@@ -40,7 +40,8 @@ constexpr int GEMV_WARPS = 8;
 constexpr int GEMV_TN = 32;          // columns per CTA
 // Workspace layout: a fixed 64 KiB head of arrival counters (one per column tile, so the
 // counters of one shape never alias the partial sums of another), then the partial sums.
-constexpr size_t GEMV_WS_HEAD = 65536;
+constexpr size_t GEMV_WS_HEAD = 131072;           // first half: arrival counters and the status word; second half: the
+                                                  // exchange slots of the warp-specialised kernel (GEMV_WS_SLOTS)
 
 struct GemvParams {
   const __half* x;
@@ -167,10 +168,11 @@ struct GemvStreamParams {
   // workspace (after the head) through which they tell the spare CTAs that the launch is about to end
   int work_ctas;
   unsigned* leave_signal;
+  unsigned long long* slots;                      // [CTA][32]: (partial sum, flag) words of a CTA's first, shared tile
   int prefetch_rows;                              // packed rows per L2 prefetch box (0: no prefetch)
   // the layer the caller will run next (q4_layer_set_next): its packed weights are asked into L2 while this
   // one computes; column tiles, boxes per tile and packed rows per box of that layer (0 rows: none)
-  int next_tiles, next_bpt, next_rows, next_late;
+  int next_tiles, next_bpt, next_rows;
 };
 
 template <int MT>
@@ -962,7 +964,7 @@ __host__ __device__ inline WsLayout ws_layout(int W, int S, int G, int upt) {
   l.xinfo = l.xp + upt * 512;                          // x digits: 16 bytes per 8 k
   l.red = l.xinfo + upt * 16;                          // per 128 k: (2^(E-14), sum of x_int)
   l.bars = (l.red + W * GEMV_TN * 4 + 15) / 16 * 16;
-  l.total = l.bars + 8 * (2 * W * S + 4) + 16;
+  l.total = l.bars + 8 * (2 * W * S + 5) + 16 + 128;       // + the barrier and the 32 sums of the exchange
   return l;
 }
 
@@ -1002,7 +1004,7 @@ __device__ __forceinline__ void imma_u8u8_first(int (&c)[4], uint32_t a0, uint32
 }
 
 template <int W, int S, int OCC, bool TRACE>
-__global__ void __launch_bounds__((W + 1) * 32, OCC)
+__global__ void __launch_bounds__((W + 2) * 32, OCC)
 gemv_ws_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap,
                const __grid_constant__ CUtensorMap zmap, const __grid_constant__ CUtensorMap pmap,
                const __grid_constant__ CUtensorMap nmap, const GemvStreamParams sp) {
@@ -1019,8 +1021,10 @@ gemv_ws_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
   uint64_t* empty = full + W * S;                                    // [W][S]  unit has been consumed
   uint64_t* mfull = empty + W * S;                                   // [2]     metadata of a tile has landed
   uint64_t* mempty = mfull + 2;                                      // [2]     every consumer is done with it
-  volatile int* flags = reinterpret_cast<volatile int*>(mempty + 2);
-  constexpr int ALL = (W + 1) * 32, CT = W * 32;
+  uint64_t* rfull = mempty + 2;                                      // [1]     the other CTAs' sums of the owned tile are here
+  volatile int* flags = reinterpret_cast<volatile int*>(rfull + 1);
+  float* remote = reinterpret_cast<float*>(rfull + 3);               // [32]
+  constexpr int ALL = (W + 2) * 32, CT = W * 32;
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   if (threadIdx.x == 0) trace_mark_ns(trc, 40);
@@ -1052,12 +1056,13 @@ gemv_ws_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     // ---- metadata, prefetches, refills -----------------------------------------------------------------
     if (lane < 2) mbar_init(&mfull[lane], 1);
     else if (lane < 4) mbar_init(&mempty[lane - 2], W);
+    else if (lane == 5) mbar_init(rfull, 1);
     if (lane == 4) {
       flags[0] = 0;
       tma_prefetch_desc(&smap); tma_prefetch_desc(&zmap); tma_prefetch_desc(&pmap);
       if (sp.next_rows > 0) tma_prefetch_desc(&nmap);
     }
-    if (lane < 4) mbar_fence_init();
+    if (lane < 6) mbar_fence_init();
     __syncwarp();
     // scales and zero points of all groups of a column tile: one box each into slot (tile - tile_first) & 1
     auto issue_meta = [&](int tile) {
@@ -1072,9 +1077,8 @@ gemv_ws_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     };
     if (lane < 2 && tile_first + lane <= tile_last) issue_meta(tile_first + lane);     // the first two tiles: no waiting
     __syncwarp();
-    if (OCC == 1) { pdl_wait(); __nanosleep(300); }  // (see the consumers: x and the metadata first)
-    if (lane < W) {
-      constexpr unsigned MASK = (1u << W) - 1u;
+    auto issue_prefetches = [&]() {
+      if (lane >= W) return;
       if (sp.prefetch_rows > 0) {
         // Ask for the rest of this CTA's share of the layer (what the rings do not hold yet) to be brought into
         // L2 now, in boxes of `prefetch_rows` packed rows: HBM then streams at its own pace, whatever the
@@ -1096,9 +1100,12 @@ gemv_ws_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
           tma_prefetch_l2_2d(&nmap, tl * GEMV_TN, bx * sp.next_rows);
         }
       }
-    }
-    // the consumers' barriers exist from here on (they set them up and fill their rings themselves)
-    named_bar_sync_all(4, ALL);
+    };
+    // Two per SM: the prefetches go out at once.  One per SM: only after the consumers have asked for x (the
+    // barrier below) - a few kilobytes that wait microseconds when they queue behind megabytes of weights.
+    if (OCC == 2) issue_prefetches();
+    named_bar_sync_all(4, ALL);       // the consumers' barriers exist from here on (they set them up themselves)
+    if (OCC == 1) issue_prefetches();
     if (lane < W) {
       constexpr unsigned MASK = (1u << W) - 1u;
       // lane c follows consumer c: its units are u0 + c + W n; the first S of them are under way already
@@ -1136,6 +1143,30 @@ gemv_ws_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     return;
   }
 
+  // A column tile whose units are dealt to two or more CTAs: the CTA that holds its first units owns it (the tile
+  // is the last of its run), the others hold its later units at the start of their runs.  They finish their
+  // part first and leave its 32 sums, each with a flag in one 8-byte word, in their slot of the workspace;
+  // the owner's helper warp collects them while the owner's consumers are still busy, and clears the slots.
+  const bool owns_shared = u1 < (tile_last + 1) * upt && u0 <= tile_last * upt;
+  if (warp == W + 1) {
+    named_bar_sync_all(4, ALL);
+    if (!owns_shared) return;
+    pdl_wait();                                  // the workspace belongs to the stream order
+    const int c_last = unit_owner((long long)tile_last * upt + upt - 1, Gd, nu);
+    float acc = 0.f;
+    for (int cc = (int)blockIdx.x + 1; cc <= c_last; ++cc) {
+      volatile unsigned long long* slot = sp.slots + (size_t)cc * 32 + lane;
+      unsigned long long v = *slot;
+      for (int i = 0; (v >> 32) == 0ull && i < (flags[0] ? 8 : 100000); ++i) { __nanosleep(100); v = *slot; }
+      if ((v >> 32) == 0ull) { flags[0] = 1; atomicExch(sp.status, Q4_STATUS_WAIT_EXPIRED); }
+      acc += __uint_as_float((unsigned)v);       // in CTA order: the result does not depend on timing
+      *slot = 0ull;
+    }
+    remote[lane] = acc;
+    __syncwarp();
+    if (lane == 0) mbar_arrive(rfull);
+    return;
+  }
   // ---- consumers ---------------------------------------------------------------------------------------
   if (TRACE && threadIdx.x == 0 && trc) {
     unsigned smid;
@@ -1147,12 +1178,13 @@ gemv_ws_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
   if (lane < S) mbar_fence_init();
   if (warp == 0 && lane == 0) tma_prefetch_desc(&wmap);
   __syncwarp();
-  auto fill_ring = [&]() {
+  // rounds [r0, r1) of this consumer's ring
+  auto fill_ring = [&](int r0, int r1) {
     if (lane == 0) {
-      int u = u0 + warp;
+      int u = u0 + warp + W * r0;
       int tile = (int)__umulhi((unsigned)u, sp.magic_upt), ux = u - tile * upt;
 #pragma unroll 1
-      for (int r = 0; r < S && u < u1; ++r) {
+      for (int r = r0; r < r1 && u < u1; ++r) {
         mbar_arrive_expect_tx(&full[warp * S + r], GEMV_UNIT_BYTES);
         tma_load_2d(smem + (size_t)(warp * S + r) * GEMV_UNIT_BYTES, &wmap, tile * GEMV_TN, ux * GEMV_UNIT_ROWS, &full[warp * S + r]);
         u += W; ux += W;
@@ -1160,10 +1192,10 @@ gemv_ws_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
       }
     }
   };
-  // Two per SM: the copies go out at once, long before the earlier launch is done.  One per SM: this CTA
-  // started when the earlier launch was all but over, and what matters is that the few kilobytes of x (and
-  // of metadata) are asked for ahead of the megabytes of weights - behind them they wait microseconds.
-  if (OCC == 2) fill_ring();
+  // Two per SM: all copies go out at once, long before the earlier launch is done.  One per SM: this CTA
+  // started when the earlier launch was all but over; its first round goes out at once, the rest only after
+  // x has been asked for - the few kilobytes of x wait microseconds when they queue behind megabytes of weights.
+  fill_ring(0, OCC == 2 ? S : 1);
   if (threadIdx.x == 0) trace_mark_ns(trc, 41);
   // x as 16-bit block fixed point, for the whole of K, by all consumers together.  CT is a multiple of 16, so
   // the 16 lanes that share a group of 128 rows always hold the 16 blocks (of 8 rows) of one group.
@@ -1187,7 +1219,7 @@ gemv_ws_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
         blk[i] = idx < n_blocks ? b : n_blocks;
         if (base + i * CT < n_blocks) v[i] = 8 * blk[i] < K ? __ldg(xg + blk[i]) : make_uint4(0u, 0u, 0u, 0u);
       }
-      if (OCC == 1 && base == 0) fill_ring();            // x is on its way: now the weights
+      if (OCC == 1 && base == 0) fill_ring(1, S);        // x is on its way: now the rest of the ring
 #pragma unroll
       for (int i = 0; i < 4; ++i) {
         if (base + i * CT >= n_blocks) break;            // the same for the whole CTA
@@ -1258,27 +1290,15 @@ gemv_ws_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
     for (int w = 0; w < W; ++w) v += red[w * GEMV_TN + col];
     named_bar_arrive(2, CT);
     if (whole) { store_y(p, 0, tc0 + col, v); return; }
-    float* part = sp.cta_part + ((size_t)blockIdx.x * 2 + (seg_first == 0 ? 1 : 0)) * 16 * GEMV_TN;
-    __stcg(part + col, v);
-    const int c_first = unit_owner((long long)tile * upt, Gd, nu), c_last = unit_owner((long long)tile * upt + upt - 1, Gd, nu);
-    __threadfence();
-    __syncwarp();
-    unsigned last = 0;
-    if (lane == 0) last = atomicAdd(p.counters + tile, 1u) == (unsigned)(c_last - c_first);
-    last = __shfl_sync(0xffffffffu, last, 0);
-    if (!last) return;
-    __threadfence();
-    float s = 0.f;
-    for (int cc = c_first; cc <= c_last; cc += 4) {
-      float t4[4];
-#pragma unroll
-      for (int i = 0; i < 4; ++i)
-        t4[i] = cc + i <= c_last ? __ldcg(sp.cta_part + ((size_t)(cc + i) * 2 + (cc + i == c_first ? 1 : 0)) * 16 * GEMV_TN + col) : 0.f;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) s += t4[i];
+    if (seg_first > 0) {
+      // a later part of a tile another CTA owns: sum and flag in one 8-byte store (one store is atomic, so
+      // the owner never sees a flag without its sum, and nothing has to be fenced)
+      sp.slots[(size_t)blockIdx.x * 32 + col] = (1ull << 32) | (unsigned long long)__float_as_uint(v);
+      return;
     }
-    store_y(p, 0, tc0 + col, s);
-    if (lane == 0) p.counters[tile] = 0u;
+    // the first part of a tile that later CTAs continue: their sums, collected by the helper warp
+    if (!mbar_spin_bounded(rfull, 0, flags[0] ? 64u : 20000000u)) { flags[0] = 1; atomicExch(sp.status, Q4_STATUS_WAIT_EXPIRED); }
+    store_y(p, 0, tc0 + col, v + remote[col]);
   };
 
   int n = 0;
@@ -1463,7 +1483,9 @@ static thread_local const NextLayer* t_next_layer = nullptr;
 static unsigned long long* g_trace = nullptr;                 // set by q4_gemv_set_trace
 static int g_gemv_variant = 0;                                // set by q4_gemv_set_variant
 
-constexpr size_t GEMV_STATUS_OFFSET = GEMV_WS_HEAD - 4;      // status word: last 4 bytes of the head
+constexpr size_t GEMV_STATUS_OFFSET = 65536 - 4;            // status word: last 4 bytes of the head's first half
+constexpr size_t GEMV_WS_SLOTS = 65536;                     // 256-byte exchange slots, one per CTA, zero between launches
+constexpr int GEMV_WS_MAX_CTAS = 255;                       // slots that fit (the last 256 bytes hold the leave signal)
 constexpr int GEMV_MAX_CTAS = 508;                            // upper bound on SMs for workspace sizing (4 slots' worth of
                                                               // room is kept for the 256 bytes ahead of the partial sums)
 
@@ -1537,7 +1559,7 @@ static int launch_ws(const CUtensorMap& wmap, const CUtensorMap& smap, const CUt
   }
   cudaLaunchConfig_t cfg = {};
   if (OCC == 2 && grid < sm_count()) grid = sm_count();       // one CTA per SM, spare ones without work (see the kernel)
-  cfg.gridDim = dim3(grid); cfg.blockDim = dim3((W + 1) * 32);
+  cfg.gridDim = dim3(grid); cfg.blockDim = dim3((W + 2) * 32);
   cfg.dynamicSmemBytes = smem; cfg.stream = st;
   cudaLaunchAttribute at[1];
   at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
@@ -1570,15 +1592,9 @@ static int launch_fast(const CUtensorMap& map, const GemvStreamParams& sp, int g
   }
   if (fits && xc) return launch_fast_xc<MR, TRACE, true, false, W1, 1>(map, sp, grid, st);
   if constexpr (MR == 1) {
-    // one row, x per unit: the two-per-SM form, so that consecutive decode launches overlap
-    if (!(g_gemv_variant & 8)) {
-      const int wsel = (g_gemv_variant >> 5) & 3;
-      if constexpr (!TRACE) {
-        if (wsel == 1) return launch_fast_xc<1, false, false, false, 10, 2>(map, sp, grid, st);
-        if (wsel == 2) return launch_fast_xc<1, false, false, false, 8, 2>(map, sp, grid, st);
-      }
-      return launch_fast_xc<1, TRACE, false, false, 11, 2>(map, sp, grid, st);
-    }
+    // one row, x per unit, 11 warps at two CTAs per SM (variant bit 8; measured slower than 16 warps at one per
+    // SM: a warp of this kernel is bound by the latency of its own instruction stream, so fewer warps stream less)
+    if (g_gemv_variant & 8) return launch_fast_xc<1, TRACE, false, false, 11, 2>(map, sp, grid, st);
   }
   return launch_fast_xc<MR, TRACE, false, false, W1, 1>(map, sp, grid, st);
 }
@@ -1627,7 +1643,7 @@ extern "C" int q4_gemv_set_trace(void* device_buffer) {
 }
 
 extern "C" int q4_gemv_set_variant(int variant) {
-  if (variant < 0 || variant > 127 || (variant & 3) == 3) return fail(Q4_E_BADARG, "gemv: variant %d is not a valid combination", variant);
+  if (variant < 0 || variant > 127 || (variant & 3) == 3 || (variant & 32)) return fail(Q4_E_BADARG, "gemv: variant %d is not a valid combination", variant);
   g_gemv_variant = variant;
   return Q4_OK;
 }
@@ -1723,6 +1739,14 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
       if (cost_whole <= cost_split) sp.whole_tiles = 1;
       if (g_gemv_variant & 4) sp.whole_tiles = 0;         // tests and measurements: always the even split
     }
+    // One row, groups of 128, whole 256-row units: the warp-specialised kernel where its tables fit.  Its CTAs
+    // exchange the sums of a straddled tile through 8-byte (sum, flag) words that nobody waits for in the
+    // common case, but the exchange still ends about one round of units after the last unit: measured on the
+    // LLaMA-7B shapes an even split loses to whole tiles (16 warps take a tile's units in rounds of 16, and the
+    // number of rounds is the same either way), so the rule above decides for this kernel as well.
+    const bool ws_ok = M == 1 && !v1 && groupsize == 128 && K % 256 == 0 && G == K / 128 && G <= 256 &&
+                       sp.units_per_tile <= WS_MAX_UNITS_PER_TILE && !(g_gemv_variant & 16);
+    if (ws_ok && grid > GEMV_WS_MAX_CTAS) grid = GEMV_WS_MAX_CTAS;
     bool lean_ok = (long long)sp.total_units * grid < (1ll << 32);
     // group rows one unit (256 k-rows) can touch, counting a straddled group at either end
     sp.meta_rows = v1 ? 1 : (GEMV_UNIT_ROWS * 8 + groupsize - 1) / groupsize + ((GEMV_UNIT_ROWS * 8) % groupsize ? 1 : 0);
@@ -1748,12 +1772,10 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
       CUtensorMap wsw;                                    // the same boxes, chunks swizzled by the row on their way in
       if (int e = make_tmap_2d(&wsw, qweight, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, (uint64_t)N, (uint64_t)(K / 8),
                                (uint64_t)N * 4, GEMV_TN, GEMV_UNIT_ROWS, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
-      // one row, groups of 128, whole 256-row units: the warp-specialised kernel where its tables fit
-      if (M == 1 && !v1 && groupsize == 128 && K % 256 == 0 && G == K / 128 && G <= 256 && sp.units_per_tile <= WS_MAX_UNITS_PER_TILE &&
-          !(g_gemv_variant & 16)) {
+      if (ws_ok && grid <= GEMV_WS_MAX_CTAS) {
         sp.work_ctas = grid;
-        sp.leave_signal = (unsigned*)p.part;              // first 256 bytes after the head; the partial sums follow
-        sp.cta_part = p.part + 64;
+        sp.slots = (unsigned long long*)((char*)workspace + GEMV_WS_SLOTS);
+        sp.leave_signal = (unsigned*)((char*)workspace + GEMV_WS_HEAD - 4);
         CUtensorMap sm2, zm2;                             // all groups of a column tile in one box each
         if (int e = make_tmap_2d(&sm2, scales, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (uint64_t)N, (uint64_t)G, (uint64_t)N * 2,
                                  GEMV_TN, G, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
@@ -1767,7 +1789,6 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
         // the layer the caller announced as the next one (q4_layer_set_next): boxes of up to 256 packed rows
         CUtensorMap nm2 = pm2;
         sp.next_rows = sp.next_tiles = sp.next_bpt = 0;
-        sp.next_late = (g_gemv_variant & 32) ? 1 : 0;
         if (t_next_layer && t_next_layer->qweight && !(g_gemv_variant & 64)) {
           const int rows = t_next_layer->K / 8;
           sp.next_rows = rows < 256 ? rows : 256;
@@ -1828,7 +1849,7 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
 // workspace per stream, so the word lives with it and not in a device global).
 extern "C" int q4_gemv_status(const void* workspace, size_t workspace_bytes, unsigned* out) {
   if (!workspace || !out) return fail(Q4_E_BADARG, "gemv_status: null pointer");
-  if (workspace_bytes < GEMV_WS_HEAD) return fail(Q4_E_WORKSPACE, "gemv_status: a decode workspace has at least %zu bytes", GEMV_WS_HEAD);
+  if (workspace_bytes < GEMV_WS_HEAD) return fail(Q4_E_WORKSPACE, "gemv_status: a decode workspace has at least %zu bytes", (size_t)GEMV_WS_HEAD);
   if (int e = check_cuda(cudaDeviceSynchronize(), "gemv_status: synchronize")) return e;
   return check_cuda(cudaMemcpy(out, (const char*)workspace + GEMV_STATUS_OFFSET, sizeof(unsigned), cudaMemcpyDeviceToHost), "read decode status");
 }

@@ -11,7 +11,7 @@
 
 namespace q4 {
 
-constexpr size_t GEMV_STATIC_SCRATCH_BYTES = 65536 + (2u << 20);     // 2.0625 MiB per device: what every
+constexpr size_t GEMV_STATIC_SCRATCH_BYTES = 131072 + (2u << 20);    // 2.125 MiB per device: what every
                                                                     // sequential-group shape needs
 
 static __device__ __align__(256) unsigned char g_gemv_static_scratch[GEMV_STATIC_SCRATCH_BYTES];
@@ -56,6 +56,7 @@ extern "C" int q4_gemv_static(const void* x, const int32_t* qweight, void* y, co
   // start at zero; a normal call leaves them so, one whose bounded wait expired may not.  The status word
   // (the last word of the head) is left alone: it stays set until q4_gemv_static_status has reported it.
   if (int e = check_cuda(cudaMemsetAsync(scratch, 0, 65536 - 4, (cudaStream_t)stream), "clear scratch head")) return e;
+  if (int e = check_cuda(cudaMemsetAsync((char*)scratch + 65536, 0, 65536 - 4, (cudaStream_t)stream), "clear scratch head")) return e;
   return q4_gemv(x, qweight, y, scales, qzeros, g_idx, bias, M, K, N, G, groupsize, y_dtype, flags,
                  scratch, GEMV_STATIC_SCRATCH_BYTES, stream);
 }

@@ -316,7 +316,7 @@ def device_status() -> int:
             continue
         _lib.check(L.q4_gemv_status(ws.data_ptr(), ws.numel(), ctypes.byref(v)), "gemv_status")
         if v.value:
-            ws[:65536].zero_()
+            ws[:131072].zero_()
             status = status or v.value
     _lib.check(L.q4_gemv_static_status(ctypes.byref(v)), "gemv_static_status")
     return status or v.value

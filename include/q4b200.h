@@ -85,9 +85,16 @@ int q2_recons_v2(const int32_t* qweight, void* out, const void* scales, const in
  *   Without Q4_GEMV_ACT_ORDER the group of row k is k / groupsize and g_idx may be NULL.
  *   Needs K % 32 == 0, N % 32 == 0, groupsize % 32 == 0.
  * `workspace` is caller-provided device scratch of at least q4_gemv_workspace_bytes(M, K, N)
- * bytes that must be zero when first used and is left zero-filled where it has to be; calls
- * that share a workspace must be ordered on one stream.  Summation order is fixed, so results
- * are reproducible run to run. */
+ * bytes that must be zero when first used and is left zero-filled where it has to be (its first
+ * 128 KiB: arrival counters, the status word and the slots through which CTAs exchange the sums of a
+ * column tile they share); calls that share a workspace must be ordered on one stream.  Summation
+ * order is fixed, so results are reproducible run to run.
+ * One-row products (M = 1, groups of 128, K a multiple of 256) run on int8 tensor-core MMAs: x is
+ * converted to 16-bit block fixed point per group of 128 rows (x_int = rn(x * 2^(14-E)) with 2^E <=
+ * max |x| of the group < 2^(E+1)), products and sums are exact integers, and the only rounding
+ * is that of x: none for elements within a factor 16 of their group's largest, at most 2^(E-15)
+ * absolute for smaller ones (measured 2e-5 relative Frobenius error against the exact product,
+ * under the 1e-4 of the fp16-MMA kernels). */
 size_t q4_gemv_workspace_bytes(int M, int K, int N);
 int q4_gemv(const void* x, const int32_t* qweight, void* y, const void* scales,
             const int32_t* qzeros, const int32_t* g_idx, const void* bias,
@@ -119,7 +126,7 @@ int q4_layer_set_next(q4_layer_t* layer, const q4_layer_t* next);
 /* The same product as q4_gemv for callers that cannot allocate device memory (no counterpart in the
  * reference; added for hosts such as a serving process that handed all of HBM to its own pools, a
  * plugin that may not call the allocator of the process it lives in, or a latency path on which the
- * device-synchronising cudaMalloc is not acceptable).  The scratch is a 2.0625 MiB device array built
+ * device-synchronising cudaMalloc is not acceptable).  The scratch is a 2.125 MiB device array built
  * into the library (q4_gemv_static_max_bytes()), present on every GPU that loads the library until
  * the process exits; the call allocates nothing and frees nothing.  That size serves every shape
  * with sequential groups; shapes whose q4_gemv_workspace_bytes() exceeds it (16-row products over
@@ -173,8 +180,9 @@ int q4_device_status(unsigned* out);
  * (its head's last word) instead of in a device global: synchronises the device and copies the word
  * of `workspace` to *out - 0, or 0xDEAD0001 if a bounded wait inside a q4_gemv kernel that used
  * this workspace expired.  The output of that call is invalid and arrival counters in the head may
- * be left non-zero: clear the first 64 KiB of the workspace (which also clears the word) before it
- * is used again.  No counterpart in the reference, whose kernels wait on nothing. */
+ * be left non-zero: clear the first 128 KiB of the workspace (which also clears the word) before it
+ * is used again (128 KiB from the library version that exchanges shared column tiles through it).
+ * No counterpart in the reference, whose kernels wait on nothing. */
 int q4_gemv_status(const void* workspace, size_t workspace_bytes, unsigned* out);
 /* The status word of the built-in scratch of q4_gemv_static on the current device; a non-zero word
  * is cleared once it has been reported (q4_gemv_static itself re-zeroes the counters before every
@@ -193,16 +201,19 @@ int q4_gemm_set_trace(void* device_buffer);
  * otherwise), 1 = always the single-CTA kernel, 2 / 3 = always the CTA-pair kernel with 256- /
  * 512-row tiles (calls it cannot serve then fail with Q4_E_SHAPE).  For tests and measurements. */
 int q4_gemm_set_variant(int variant);
-/* Forms of the sequential-group decode kernel, for tests and measurements (process-wide; no
+/* Forms of the sequential-group decode kernels, for tests and measurements (process-wide; no
  * reference counterpart).  `variant` is a sum of:
- *   bits 0-1  how the kernel gets x: 0 = choose per shape (the default: with two or more rows every CTA
+ *   bits 0-1  products of 2..8 rows: how the kernel gets x - 0 = choose per shape (the default: every CTA
  *             re-lays the whole of x out once when it has more than one column tile's worth of units and x
  *             fits its shared memory; else every 4 KiB unit brings its own slice), 1 = always per unit,
  *             2 = per CTA wherever it fits
  *   4         deal an even share of all units to every CTA even where whole column tiles per CTA would
  *             end sooner (column tiles that straddle CTAs then meet in the workspace)
- *   8         one-row products: the one-CTA-per-SM form instead of the two-per-SM form
- *   32, 64    one-row products, two-per-SM form: 10 resp. 8 warps per CTA instead of 11
+ *   8         one-row products: the two-CTAs-per-SM form of the kernel (fewer warps per CTA, so that the next
+ *             decode launch of the stream is resident beside this one) instead of one CTA per SM
+ *   16        one-row products on the kernel that serves 2..8 rows (fp16 MMA, x re-laid per unit) instead
+ *             of the warp-specialised int8-MMA kernel
+ *   64        one-row products: no L2 prefetch of the CTA's share of the layer (nor of the next layer)
  * Values outside these combinations are refused with Q4_E_BADARG. */
 int q4_gemv_set_variant(int variant);
 

@@ -62,7 +62,7 @@ def test_static_scratch_matches_workspace_entry_point_twice(M, K, N, act, varian
 
 def test_static_scratch_refuses_oversized_shapes():
     lib = _lib.lib()
-    assert lib.q4_gemv_static_max_bytes() == 65536 + (2 << 20)
+    assert lib.q4_gemv_static_max_bytes() == 131072 + (2 << 20)
     L = synth.make_layer(128, 128, 128, False, seed=1).to(DEV)
     x = synth.make_acts(1, 128, seed=2).to(DEV)
     y = torch.empty((1, 128), dtype=torch.float32, device=DEV)
