@@ -44,11 +44,14 @@ class AutogradMatmul4bitCuda(torch.autograd.Function):
 
     @staticmethod
     @custom_fwd(device_type="cuda", cast_inputs=torch.float16)
-    def forward(ctx, x, qweight, scales, zeros, g_idx, bits, maxq):
+    def forward(ctx, x, qweight, scales, zeros, g_idx, bits, maxq, bias=None):
+        """``bias`` (not an argument of the reference's function, whose module adds the bias in a kernel of
+        its own, autograd_4bit.py:204-206): added in the epilogue of the fused product where that runs."""
         ctx.save_for_backward(qweight, scales, zeros, g_idx)
         if g_idx is None:
-            return mm4b._matmul4bit_v1_recons(x, qweight, scales, zeros)
-        return mm4b._matmul4bit_v2_recons(x, qweight, scales, zeros, g_idx)
+            out = mm4b._matmul4bit_v1_recons(x, qweight, scales, zeros)
+            return out if bias is None else out + bias.to(out.dtype)
+        return mm4b._matmul4bit_v2_recons(x, qweight, scales, zeros, g_idx, bias=bias)
 
     @staticmethod
     @custom_bwd(device_type="cuda")
@@ -60,7 +63,7 @@ class AutogradMatmul4bitCuda(torch.autograd.Function):
                 grad = mm4b._matmul4bit_v1_recons(grad_output, qweight, scales, zeros, transpose=True)
             else:
                 grad = mm4b._matmul4bit_v2_recons(grad_output, qweight, scales, zeros, g_idx, transpose=True)
-        return grad, None, None, None, None, None, None
+        return grad, None, None, None, None, None, None, None
 
 
 class AutogradMatmul2bitCuda(torch.autograd.Function):
@@ -144,6 +147,10 @@ class Autograd4bitQuantLinear(nn.Module):
         zeros = self.zeros if self.is_v1_model else self.qzeros
         if self.bits == 4:
             if torch.is_grad_enabled():
+                if AutogradMatmul4bit is AutogradMatmul4bitCuda:
+                    # the bias rides in the product's epilogue instead of a second pass over the output
+                    bias = None if (self.disable_bias or self.bias is None) else self.bias
+                    return AutogradMatmul4bit.apply(x, self.qweight, self.scales, zeros, self.g_idx, self.bits, self.maxq, bias)
                 out = AutogradMatmul4bit.apply(x, self.qweight, self.scales, zeros, self.g_idx, self.bits, self.maxq)
             else:
                 out = matmul4bit_with_backend(x, self.qweight, self.scales, zeros, self.g_idx, self.bits, self.maxq,

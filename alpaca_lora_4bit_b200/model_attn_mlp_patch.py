@@ -19,7 +19,7 @@ import torch
 import torch.nn as nn
 from torch.nn import functional as F
 
-from . import matmul_utils_4bit
+from . import fused_ops, matmul_utils_4bit
 from .autograd_4bit import Autograd4bitQuantLinear
 
 
@@ -132,6 +132,9 @@ class QuantLlamaMLP(nn.Module):
 
     def forward(self, x):
         gate, up = torch.split(self.gate_up_proj(x), self.intermediate_size, dim=-1)
+        if type(self.act_fn).__name__ in ("SiLU", "SiLUActivation"):
+            # one kernel reads the two halves of the fused output where they lie and writes the product
+            return self.down_proj(fused_ops.swiglu(gate, up))
         return self.down_proj(self.act_fn(gate) * up)
 
 

@@ -111,10 +111,31 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-# DRAM bytes (read + write) of one launch of the decode kernel, averaged over the three layer shapes:
-# dram__bytes_read.sum + dram__bytes_write.sum of one ncu capture per shape (8,754,432 / 23,463,168 /
-# 23,476,736 bytes against 8,749,056 / 23,471,616 / 23,499,264 algorithmic; summary under profiles/).
-NCU_DRAM_BYTES_PER_LAUNCH = round((8754432 + 23463168 + 23476736) / 3)
+def ncu_dram_bytes_per_launch():
+    """DRAM bytes (read + write) of one launch of the decode kernel, averaged over the three layer shapes, and the
+    kernel the capture was taken on: the ``dram_bytes_<KxN>`` and ``kernel`` lines of the ncu summary under
+    profiles/ (written from ``dram__bytes_read.sum + dram__bytes_write.sum`` of one capture per shape).  None when
+    the summary is missing or names another kernel than the one that runs now."""
+    path = os.path.join(ROOT, "profiles", "gemv_ws_kernel_c1_m1.md")
+    try:
+        vals, kernel = {}, None
+        with open(path) as f:
+            for line in f:
+                line = line.strip().strip("`")
+                if line.startswith("dram_bytes_"):
+                    k, v = line.split("=")
+                    vals[k.strip()[len("dram_bytes_"):]] = int(v.strip().replace(",", ""))
+                elif line.startswith("kernel ="):
+                    kernel = line.split("=", 1)[1].strip()
+        want = [f"{K}x{N}" for K, N in [(4096, 4096), (4096, 11008), (11008, 4096)]]
+        if kernel != DECODE_KERNEL or any(w not in vals for w in want):
+            return None
+        return round(sum(vals[w] for w in want) / 3)
+    except OSError:
+        return None
+
+
+DECODE_KERNEL = "gemv_ws_kernel<16,2,1>"
 
 
 def make_pool(copies, device, seed):
@@ -274,25 +295,62 @@ def run_ours(args, rank, world, local_rank):
         yh.copy_(torch.cat(outs, dim=1), non_blocking=True)
         torch.cuda.current_stream(dev).synchronize()
 
+    def timed_host(fn, n):
+        barrier()
+        torch.cuda.synchronize(dev)
+        t0 = time.perf_counter()
+        for _ in range(n):
+            fn()
+        torch.cuda.synchronize(dev)
+        dt = (time.perf_counter() - t0) * 1e3
+        barrier()
+        return dt
+
     with torch.no_grad():
         for _ in range(3):
             e2e_step()
-        barrier()
-        torch.cuda.synchronize(dev)
         e2e_steps = max(3, min(args.steps, 50))
-        t0 = time.perf_counter()
-        for _ in range(e2e_steps):
-            e2e_step()
-        torch.cuda.synchronize(dev)
-        e2e_ms = (time.perf_counter() - t0) * 1e3
-        barrier()
+        e2e_eager_ms = timed_host(e2e_step, e2e_steps)
+        # The same step as a decode loop runs it in production: the host -> device copies, the per-layer calls of
+        # the public entry point and the gather of the outputs recorded once as a CUDA graph (the entry point
+        # allocates its outputs from the graph's pool and keeps its workspace per stream, so it can be captured),
+        # then one replay plus the device -> host copy per step.  Host buffers in, host buffer out, every step.
+        e2e_graph, yd = None, None
+        try:
+            side = torch.cuda.Stream(dev)
+            side.wait_stream(torch.cuda.current_stream(dev))
+            with torch.cuda.stream(side):
+                e2e_step()                                     # the stream's decode workspace exists before the capture
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=side):
+                    xd = {K: v.to(dev, non_blocking=True) for K, v in xh.items()}
+                    outs = [mm4b.matmul4bit(xd[l.K], l.qweight, l.scales, l.qzeros, l.g_idx, GROUPSIZE) for l in pool]
+                    yd = torch.cat(outs, dim=1)
+            torch.cuda.current_stream(dev).wait_stream(side)
+            e2e_graph = g
+        except Exception as exc:                               # capture is an optimisation of the caller, not a requirement
+            print(f"bench: the end-to-end step could not be captured ({type(exc).__name__}: {exc}); eager calls only", file=sys.stderr)
+
+        def e2e_graph_step():
+            e2e_graph.replay()
+            yh.copy_(yd, non_blocking=True)
+            torch.cuda.current_stream(dev).synchronize()
+
+        if e2e_graph is not None:
+            ref_out = torch.cat([mm4b.matmul4bit(xh[l.K].to(dev), l.qweight, l.scales, l.qzeros, l.g_idx, GROUPSIZE) for l in pool], dim=1).cpu()
+            for _ in range(3):
+                e2e_graph_step()
+            assert torch.equal(yh, ref_out), "graph replay of the end-to-end step disagrees with the eager calls"
+            e2e_ms = timed_host(e2e_graph_step, e2e_steps)
+        else:
+            e2e_ms = e2e_eager_ms
 
     if world > 1:
-        t = torch.tensor([ms, e2e_ms], device=dev, dtype=torch.float64)
+        t = torch.tensor([ms, e2e_ms, e2e_eager_ms], device=dev, dtype=torch.float64)
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
-        ms, e2e_ms = float(t[0]), float(t[1])
-    return dict(ms=ms, e2e_ms=e2e_ms, e2e_steps=e2e_steps, n_launch=n_launch, clocks=clocks,
-                per_shape=per_shape, m_sweep=m_sweep, h2d=h2d, d2h=d2h)
+        ms, e2e_ms, e2e_eager_ms = float(t[0]), float(t[1]), float(t[2])
+    return dict(ms=ms, e2e_ms=e2e_ms, e2e_eager_ms=e2e_eager_ms, e2e_graphed=e2e_graph is not None, e2e_steps=e2e_steps,
+                n_launch=n_launch, clocks=clocks, per_shape=per_shape, m_sweep=m_sweep, h2d=h2d, d2h=d2h)
 
 
 def run_finetune(args, rank, world, local_rank):
@@ -313,6 +371,9 @@ def run_finetune(args, rank, world, local_rank):
                     std_a=0.02, std_b=0.01, seed=1)
     else:
         fs.add_lora(model, ["q_proj", "v_proj"], r=8, alpha=16, std_a=0.02, std_b=0.01, seed=1)
+    if not args.finetune_stock_elementwise:
+        from alpaca_lora_4bit_b200 import fused_ops
+        fused_ops.patch_llama(model)                   # RMSNorm, SwiGLU, rotary: one kernel each way
     fs.apply_gradient_checkpointing(model)
     model.train()
     ft = fs.LoraFinetuner(model, lr=3e-4, autocast_dtype=torch.bfloat16 if big else torch.float16)
@@ -366,17 +427,20 @@ def run_finetune(args, rank, world, local_rank):
                                              "r=8 alpha=16 q_proj,v_proj, dropout 0 (as the reference forces under checkpointing)"),
            "lora_params": fs.lora_param_count(model), "allreduce_bytes_per_step": 4 * fs.lora_param_count(model) if world > 1 else 0,
            "model_tflops_per_s": round(tps * flops_per_token / 1e12, 1), "loss_first_last": [round(losses[0], 4), round(losses[-1], 4)], "launch": "cuda_graph" if graphed else "eager",
+           "elementwise": "stock transformers modules" if args.finetune_stock_elementwise else "fused RMSNorm / SwiGLU / rotary kernels",
            "h2d_bytes_per_step": B * T * 8, "d2h_bytes_per_step": 4}
     del ft, model
     torch.cuda.empty_cache()
     return out
 
 
-def run_gemm(args, local_rank):
-    """C2: fused dequant-GEMM at M=2048 on LLaMA-13B layer shapes, act-order g128, forward and backward,
-    next to the reference's composition (reconstruct to a dense fp16 buffer + library GEMM) run with this
-    library's reconstruct kernel.  Tensor-core roofline: 2*M*K*N flop against the measured bf16 GEMM peak."""
-    from alpaca_lora_4bit_b200 import quant_cuda
+def run_gemm(args, local_rank, reference_only=False):
+    """C2: fused dequant-GEMM at M=2048 on LLaMA-13B layer shapes, act-order g128, forward and backward, next to the
+    reference's composition (reconstruct to a dense fp16 buffer + library GEMM, matmul_utils_4bit.py:114-127) run
+    twice: with this library's reconstruct kernel and with the reference's own (``vecquant4recons_v2`` of its
+    extension built unmodified into oracle/_ref, where present).  Also the M=1024 products of the LLaMA-7B step.
+    Tensor-core roofline: 2*M*K*N flop against the measured bf16 GEMM peak.  ``reference_only``: the reference
+    composition alone (the ``--impl reference`` arm; nothing of this library runs)."""
     dev = torch.device("cuda", local_rank)
     gen = torch.Generator(device=dev).manual_seed(7)
     try:
@@ -385,6 +449,14 @@ def run_gemm(args, local_rank):
         kind = "measured"
     except Exception:
         peak, kind = 1590.0, "fallback"
+    ref = None
+    try:
+        from oracle import build_ref
+        ref = build_ref.load()
+    except Exception:
+        ref = None
+    if not reference_only:
+        from alpaca_lora_4bit_b200 import quant_cuda
 
     def timed(fn, reps=10):
         for _ in range(3):
@@ -398,42 +470,53 @@ def run_gemm(args, local_rank):
         torch.cuda.synchronize(dev)
         return a.elapsed_time(b) / reps
 
-    M = 2048
-    out = {"M": M, "peak_tflops": peak, "peak_kind": kind, "shapes": {}}
-    shapes = [(5120, 5120), (5120, 13824), (13824, 5120)]
+    out = {"peak_tflops": peak, "peak_kind": kind, "shapes": {}}
+    cases = [(2048, 5120, 5120, True), (2048, 5120, 13824, True), (2048, 13824, 5120, True),
+             (1024, 4096, 4096, False), (1024, 4096, 11008, False), (1024, 11008, 4096, False)]
     if getattr(args, "gemm_shape", ""):
-        shapes = [tuple(int(v) for v in args.gemm_shape.lower().split("x"))]
-    for K, N in shapes:
+        k_, n_ = (int(v) for v in args.gemm_shape.lower().split("x"))
+        cases = [(2048, k_, n_, True)]
+    for M, K, N, act in cases:
         G = K // 128
         qw = torch.randint(-2 ** 31, 2 ** 31 - 1, (K // 8, N), device=dev, dtype=torch.int64, generator=gen).to(torch.int32)
         zw = (torch.randint(0, 2 ** 31 - 1, (G, N // 8), device=dev, dtype=torch.int64, generator=gen) & 0x66666666).to(torch.int32)
         sc = (torch.rand((G, N), device=dev, generator=gen) * 0.018 + 0.002).half()
-        gi = (torch.randperm(K, device=dev, generator=gen) // 128).int()
+        gi = ((torch.randperm(K, device=dev, generator=gen) if act else torch.arange(K, device=dev)) // 128).int()
         x = torch.randn((M, K), device=dev, generator=gen).half()
         dy = torch.randn((M, N), device=dev, generator=gen).half()
         y = torch.empty((M, N), device=dev, dtype=torch.float16)
         dx = torch.empty((M, K), device=dev, dtype=torch.float16)
         w = torch.empty((K, N), device=dev, dtype=torch.float16)
         fl = 2.0 * M * K * N / 1e9
-        r = 16                                             # LoRA r=16, alpha=32: A ~ N(0, 0.02) [16, K], B ~ N(0, 0.02) [N, 16]
-        la = (torch.randn((r, K), device=dev, generator=gen) * 0.02).half()
-        lb = (torch.randn((N, r), device=dev, generator=gen) * 0.02).half()
-        u = torch.nn.functional.pad((x @ la.t()) * 2.0, (0, 64 - r)).contiguous()
-        v = torch.nn.functional.pad((dy @ lb) * 2.0, (0, 64 - r)).contiguous()
-        tf = timed(lambda: quant_cuda.gemm(x, qw, y, sc, zw, gi))
-        tb = timed(lambda: quant_cuda.gemm(dy, qw, dx, sc, zw, gi, transpose=True))
-        tfl = timed(lambda: quant_cuda.gemm(x, qw, y, sc, zw, gi, lora_u=u, lora_w=lb))
-        tbl = timed(lambda: quant_cuda.gemm(dy, qw, dx, sc, zw, gi, transpose=True, lora_u=v, lora_w=la))
-        tr = timed(lambda: quant_cuda.vecquant4recons_v2(qw, w, sc, zw, gi))
+        row = {"M": M, "act_order": act}
         tm = timed(lambda: torch.matmul(x, w, out=y))
         tmb = timed(lambda: torch.matmul(dy, w.t(), out=dx))
-        out["shapes"][f"{K}x{N}"] = {
-            "fused_fwd_tflops": round(fl / tf, 1), "fused_bwd_tflops": round(fl / tb, 1),
-            "fused_fwd_frac": round(fl / tf / peak, 3), "fused_bwd_frac": round(fl / tb / peak, 3),
-            "fused_fwd_with_lora_r16_tflops": round(fl / tfl, 1), "fused_bwd_with_lora_r16_tflops": round(fl / tbl, 1),
-            "recons_plus_library_gemm_fwd_tflops": round(fl / (tr + tm), 1),
-            "recons_plus_library_gemm_bwd_tflops": round(fl / (tr + tmb), 1), "recons_us": round(tr * 1e3, 1)}
-        del qw, zw, sc, gi, x, dy, y, dx, w, la, lb, u, v
+        if ref is not None:
+            trr = timed(lambda: ref.vecquant4recons_v2(qw, w, sc, zw, gi))
+            row.update({"reference_recons_us": round(trr * 1e3, 1),
+                        "reference_recons_plus_library_gemm_fwd_tflops": round(fl / (trr + tm), 1),
+                        "reference_recons_plus_library_gemm_bwd_tflops": round(fl / (trr + tmb), 1)})
+        if not reference_only:
+            r = 16                                         # LoRA r=16, alpha=32: A ~ N(0, 0.02) [16, K], B ~ N(0, 0.02) [N, 16]
+            la = (torch.randn((r, K), device=dev, generator=gen) * 0.02).half()
+            lb = (torch.randn((N, r), device=dev, generator=gen) * 0.02).half()
+            u = torch.nn.functional.pad((x @ la.t()) * 2.0, (0, 64 - r)).contiguous()
+            v = torch.nn.functional.pad((dy @ lb) * 2.0, (0, 64 - r)).contiguous()
+            tf = timed(lambda: quant_cuda.gemm(x, qw, y, sc, zw, gi))
+            tb = timed(lambda: quant_cuda.gemm(dy, qw, dx, sc, zw, gi, transpose=True))
+            tfl = timed(lambda: quant_cuda.gemm(x, qw, y, sc, zw, gi, lora_u=u, lora_w=lb))
+            tbl = timed(lambda: quant_cuda.gemm(dy, qw, dx, sc, zw, gi, transpose=True, lora_u=v, lora_w=la))
+            tr = timed(lambda: quant_cuda.vecquant4recons_v2(qw, w, sc, zw, gi))
+            row.update({
+                "fused_fwd_tflops": round(fl / tf, 1), "fused_bwd_tflops": round(fl / tb, 1),
+                "fused_fwd_frac": round(fl / tf / peak, 3), "fused_bwd_frac": round(fl / tb / peak, 3),
+                "fused_fwd_with_lora_r16_tflops": round(fl / tfl, 1), "fused_bwd_with_lora_r16_tflops": round(fl / tbl, 1),
+                "recons_plus_library_gemm_fwd_tflops": round(fl / (tr + tm), 1),
+                "recons_plus_library_gemm_bwd_tflops": round(fl / (tr + tmb), 1), "recons_us": round(tr * 1e3, 1)})
+            if ref is not None:
+                row["fused_over_reference_composition"] = [round((trr + tm) / tf, 2), round((trr + tmb) / tb, 2)]
+        out["shapes"][f"M{M}_{K}x{N}"] = row
+        del qw, zw, sc, gi, x, dy, y, dx, w
     torch.cuda.empty_cache()
     return out
 
@@ -490,23 +573,41 @@ def reference_gpu(args):
             "h2d": sum(v.numel() * 2 for v in xh.values()), "d2h": yh.numel() * 2}
 
 
-def cpu_reference(sample_layers=1, reps=3, threads=None):
-    """The reference composition on the host: reconstruct fp16 [K,N] + fp32 matmul, M=1."""
+def cpu_reference(reps=3, threads=None):
+    """The reference composition on the host cores, on the one-layer configuration it is defined for (K = N = 4096,
+    groups of 128, M = 16 rows, everything from one seed): reconstruct W to fp16 (three roundings, as the
+    reference's kernel), forward ``y = x @ W`` and backward ``dx = dy @ W.T`` in fp32 - oracle/q4_oracle.py, best
+    of ``reps`` after one warm-up, each part timed on its own.  Returns the decode metric of the forward path
+    (algorithmic bytes of the 16-row product over reconstruct + forward time) and the parts."""
     from oracle import q4_oracle as orc
     if threads:
         torch.set_num_threads(threads)
-    K, N = SHAPES[0]
+    K, N, M = 4096, 4096, 16
     layer = synth.make_layer(K, N, GROUPSIZE, False, seed=0)
-    x = synth.make_acts(1, K, seed=1)
-    orc.matmul4bit_ref(x, layer.qweight, layer.scales, layer.qzeros, layer.g_idx)      # warm-up
-    best = float("inf")
-    for _ in range(reps):
-        t0 = time.perf_counter()
-        for _ in range(sample_layers):
-            orc.matmul4bit_ref(x, layer.qweight, layer.scales, layer.qzeros, layer.g_idx)
-        best = min(best, (time.perf_counter() - t0) / sample_layers)
-    gbs = synth.gemv_bytes(1, K, N, GROUPSIZE) / best / 1e9
-    return gbs, best, torch.get_num_threads()
+    x = synth.make_acts(M, K, seed=1)
+    dy = synth.make_acts(M, N, seed=2)
+
+    def best_of(fn):
+        fn()
+        best = float("inf")
+        for _ in range(reps):
+            t0 = time.perf_counter()
+            fn()
+            best = min(best, time.perf_counter() - t0)
+        return best
+
+    w = orc.recons_v2(layer.qweight, layer.scales, layer.qzeros, layer.g_idx)
+    t_rec = best_of(lambda: orc.recons_v2(layer.qweight, layer.scales, layer.qzeros, layer.g_idx))
+    t_fwd = best_of(lambda: orc.matmul_recons(x, w))
+    t_bwd = best_of(lambda: orc.matmul_recons(dy, w, transpose=True))
+    gbs = synth.gemv_bytes(M, K, N, GROUPSIZE) / (t_rec + t_fwd) / 1e9
+    parts = {"reconstruct_s": round(t_rec, 5), "forward_s": round(t_fwd, 5), "backward_s": round(t_bwd, 5),
+             "total_s": round(t_rec + t_fwd + t_bwd, 5), "threads": torch.get_num_threads(), "cpu_count": os.cpu_count()}
+    return gbs, t_rec + t_fwd, torch.get_num_threads(), parts
+
+
+CPU_SAMPLE = ("one 4096x4096 g128 layer, M=16 (the reference's single-layer CPU configuration): fp16 reconstruct + fp32 "
+              "forward, best of the repetitions; backward dx = dy @ W.T timed beside it")
 
 
 def main():
@@ -529,6 +630,8 @@ def main():
                     help="7b: LLaMA-7B, r=8 LoRA on q/v, 4 x 256 tokens, fp16 (C3); 70b: LLaMA-2-70B GQA, act-order, r=16 LoRA on "
                          "all seven projections, 1 x 2048 tokens, bf16 autocast (C4; 35 GB of int4 weights per GPU)")
     ap.add_argument("--finetune-eager", action="store_true", help="do not capture the finetune step as a CUDA graph")
+    ap.add_argument("--finetune-stock-elementwise", action="store_true",
+                    help="leave RMSNorm, SwiGLU and the rotary embedding to the stock transformers modules")
     ap.add_argument("--finetune-layers", type=int, default=0, help="override the number of decoder layers (0 = 32)")
     args = ap.parse_args()
     if args.decode_shape:
@@ -571,16 +674,17 @@ def main():
                     "e2e_with_host_copies": {"value": round(rg["e2e_gbs"], 1), "unit": UNIT, "h2d_bytes_per_step": rg["h2d"],
                                              "d2h_bytes_per_step": rg["d2h"]},
                     "gpu_launches": 0}
+            if not args.no_gemm:
+                line["gemm"] = run_gemm(args, 0, reference_only=True)     # reconstruct (its kernel) + library GEMM
             emit(line)
             return
         steps = max(1, min(args.steps, 5))
-        gbs, sec, threads = cpu_reference(reps=max(1, min(args.warmup, 2)) + steps)
+        gbs, sec, threads, parts = cpu_reference(reps=max(1, min(args.warmup, 2)) + steps)
         line = {"impl": "reference", "metric": METRIC, "value": round(gbs, 4), "unit": UNIT, "n_gpus": args.gpus,
                 "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(sec * 1e3, 3),
                 "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f16",
                 "data": "synthetic", "config": config,
-                "cpu_baseline": {"value": round(gbs, 4), "unit": UNIT, "cores": threads, "kind": "port",
-                                 "sample": "one 4096x4096 g128 layer, M=1: fp16 reconstruct + fp32 matmul, best of the steps"},
+                "cpu_baseline": dict({"value": round(gbs, 4), "unit": UNIT, "cores": threads, "kind": "port", "sample": CPU_SAMPLE}, **parts),
                 "e2e": {"value": round(gbs, 4), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0}}
         emit(line)
         return
@@ -603,22 +707,25 @@ def main():
                 "warmup": args.warmup, "ms_per_step": round(r["ms"] / args.steps, 5), "higher_is_better": True,
                 "scaling": "weak", "vs_baseline": None, "dtype": "f16", "data": "synthetic", "config": config,
                 "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                             "frac": round(achieved / peak, 4), "traffic": None if args.decode_shape else NCU_DRAM_BYTES_PER_LAUNCH,
+                             "frac": round(achieved / peak, 4), "traffic": None if args.decode_shape else ncu_dram_bytes_per_launch(),
                              "algorithmic_bytes_per_launch": round(bps / r["n_launch"]), "peak_kind": peak_kind,
-                             "kernel": "gemv_fast_kernel<1>", "avg_launch_us": round(per_launch_us, 3),
+                             "kernel": DECODE_KERNEL, "avg_launch_us": round(per_launch_us, 3),
                              "frac_of_nominal_8000": round(achieved / 8000.0, 4)},
                 "per_shape": r["per_shape"], "m_sweep": r["m_sweep"],
                 "e2e": {"value": round(e2e, 1), "unit": UNIT, "h2d_bytes_per_step": r["h2d"], "d2h_bytes_per_step": r["d2h"],
-                        "api": "matmul_utils_4bit.matmul4bit per layer; per step the activation vectors come from pinned host memory and all outputs go back in one copy; weights resident"},
+                        "api": "matmul_utils_4bit.matmul4bit per layer; per step the activation vectors come from pinned host memory and all "
+                               "outputs go back in one copy; weights resident" +
+                               ("; the step (copies in, the calls, the gather) is recorded once as a CUDA graph and replayed" if r["e2e_graphed"] else ""),
+                        "launch": "cuda_graph" if r["e2e_graphed"] else "eager",
+                        "eager_value": round(bps * world * r["e2e_steps"] / (r["e2e_eager_ms"] * 1e-3) / 1e9, 1)},
                 "gpu_launches": args.steps * r["n_launch"], "clocks": r["clocks"]}
         if gm is not None:
             line["gemm"] = gm
         if ft is not None:
             line["finetune"] = ft
         if world == 1 and not args.no_cpu:
-            gbs, sec, threads = cpu_reference(reps=3)
-            line["cpu_baseline"] = {"value": round(gbs, 4), "unit": UNIT, "cores": threads, "kind": "port",
-                                    "sample": "one 4096x4096 g128 layer, M=1: fp16 reconstruct + fp32 matmul, best of 3"}
+            gbs, sec, threads, parts = cpu_reference(reps=5)
+            line["cpu_baseline"] = dict({"value": round(gbs, 4), "unit": UNIT, "cores": threads, "kind": "port", "sample": CPU_SAMPLE}, **parts)
         emit(line)
     if world > 1:
         torch.distributed.destroy_process_group()

@@ -173,6 +173,27 @@ int q4_gemm_bwd(const void* dy, const int32_t* qweight, void* dx, const void* sc
  * One workspace serves calls that are ordered on one stream; calls that may overlap need one each. */
 size_t q4_gemm_workspace_bytes(int K, int N, int G);
 
+/* The element-wise work of a decoder layer around the quantised linears, one kernel each way (fp16 in and
+ * out, fp32 inside).  The reference leaves these to the stock modules (a handful of framework kernels each:
+ * its finetune step runs transformers' LlamaRMSNorm, LlamaMLP and apply_rotary_pos_emb, finetune.py:150-175
+ * through gradient_checkpointing.py:19-65); there is no counterpart in its extension.
+ *   q4_rmsnorm_fwd   y = weight * half(x * rsqrt(mean(x^2) + eps)) per row of H (H % 8 == 0, H <= 8192);
+ *                    rstd [rows] fp32 receives the reciprocal root (may be NULL)
+ *   q4_rmsnorm_bwd   dx for a frozen weight: rstd * (g - xh * mean(g * xh)), g = dy * weight, xh = x * rstd
+ *   q4_swiglu_fwd    out [rows, I] = half(silu(gate)) * up; gate and up are rows of `pitch` halves (two
+ *                    tensors, or the halves of one fused gate_up output)
+ *   q4_swiglu_bwd    dgate, dup (rows of `dpitch` halves) from dout, gate, up
+ *   q4_rope          rotary embedding of in [tokens, heads, D] (token pitch `in_pitch` halves) with cos / sin
+ *                    [tokens, D] into out [tokens, heads, D]; `backward` != 0 applies the transpose */
+int q4_rmsnorm_fwd(const void* x, const void* weight, void* y, float* rstd, int rows, int H, float eps, q4_stream_t stream);
+int q4_rmsnorm_bwd(const void* dy, const void* x, const void* weight, const float* rstd, void* dx, int rows, int H,
+                   q4_stream_t stream);
+int q4_swiglu_fwd(const void* gate, const void* up, void* out, int rows, int I, int pitch, q4_stream_t stream);
+int q4_swiglu_bwd(const void* dout, const void* gate, const void* up, void* dgate, void* dup, int rows, int I, int pitch,
+                  int dpitch, q4_stream_t stream);
+int q4_rope(const void* in, const void* cos, const void* sin, void* out, int tokens, int heads, int D, int in_pitch,
+            int backward, q4_stream_t stream);
+
 /* Copies the device status word to *out (synchronises the device): 0, or 0xDEAD0001 if a bounded
  * wait inside a q4_gemm_* kernel expired (its output is then invalid). */
 int q4_device_status(unsigned* out);

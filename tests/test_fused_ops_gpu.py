@@ -1,0 +1,103 @@
+"""The fused element-wise kernels (RMSNorm, SwiGLU, rotary embedding) against the stock transformers
+computation they replace: operator by operator, forward and backward, and on a whole two-layer quantised
+LLaMA (loss and LoRA gradients of the patched model against the unpatched one)."""
+import copy
+
+import pytest
+import torch
+
+from alpaca_lora_4bit_b200 import finetune_step as fs, fused_ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+def rel(a, b):
+    a, b = a.double(), b.double()
+    return float((a.detach() - b.detach()).norm() / b.detach().norm())
+
+
+@pytest.mark.parametrize("rows,H", [(1024, 4096), (7, 8192), (33, 200)])
+def test_rmsnorm_matches_stock(rows, H):
+    g = torch.Generator(device=DEV).manual_seed(rows + H)
+    x = (torch.randn((rows, H), generator=g, device=DEV) * 3).half().requires_grad_(True)
+    w = (1 + 0.1 * torch.randn(H, generator=g, device=DEV)).half()
+    dy = torch.randn((rows, H), generator=g, device=DEV).half()
+    y = fused_ops.rms_norm(x, w, 1e-5)
+    y.backward(dy)
+    got_dx = x.grad.clone(); x.grad = None
+    h = x.to(torch.float32)
+    ref = w * (h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + 1e-5)).to(torch.float16)
+    ref.backward(dy)
+    assert rel(y, ref) <= 1e-3 and float((y.float() - ref.float()).abs().max()) <= 2e-2      # same two roundings; the sums differ in order
+    assert rel(got_dx, x.grad) <= 2e-3
+    # fp64 calculus as the arbiter: the fused backward is at least as close as the stock one
+    x64 = x.detach().double().requires_grad_(True)
+    y64 = w.double() * (x64 * torch.rsqrt(x64.pow(2).mean(-1, keepdim=True) + 1e-5))
+    y64.backward(dy.double())
+    assert rel(got_dx, x64.grad) <= 1.05 * rel(x.grad, x64.grad) + 1e-5
+
+
+@pytest.mark.parametrize("rows,I,fused_input", [(1024, 11008, False), (5, 256, False), (300, 1024, True)])
+def test_swiglu_matches_stock(rows, I, fused_input):
+    g = torch.Generator(device=DEV).manual_seed(rows + I)
+    if fused_input:                                              # the two halves of one gate_up output
+        gu = (torch.randn((rows, 2 * I), generator=g, device=DEV) * 2).half().requires_grad_(True)
+        gate, up = torch.split(gu, I, dim=-1)
+    else:
+        gate = (torch.randn((rows, I), generator=g, device=DEV) * 2).half().requires_grad_(True)
+        up = torch.randn((rows, I), generator=g, device=DEV).half().requires_grad_(True)
+    d = torch.randn((rows, I), generator=g, device=DEV).half()
+    out = fused_ops.swiglu(gate, up)
+    ref = torch.nn.functional.silu(gate) * up
+    assert rel(out, ref) <= 1e-3
+    leaves = [gu] if fused_input else [gate, up]
+    got = torch.autograd.grad(out, leaves, d)
+    want = torch.autograd.grad(ref, leaves, d)
+    for a, b in zip(got, want):
+        assert rel(a, b) <= 3e-3
+
+
+@pytest.mark.parametrize("B,T,H,KV,D", [(4, 256, 32, 32, 128), (1, 77, 8, 2, 64)])
+def test_rope_matches_stock(B, T, H, KV, D):
+    g = torch.Generator(device=DEV).manual_seed(T + D)
+    q = torch.randn((B, T, H * D), generator=g, device=DEV).half().requires_grad_(True)
+    k = torch.randn((B, T, KV * D), generator=g, device=DEV).half().requires_grad_(True)
+    ang = torch.rand((B, T, D // 2), generator=g, device=DEV) * 6.28
+    cos, sin = torch.cat([ang.cos(), ang.cos()], -1).half(), torch.cat([ang.sin(), ang.sin()], -1).half()
+    qv, kv = q.view(B, T, H, D).transpose(1, 2), k.view(B, T, KV, D).transpose(1, 2)
+    qe, ke = fused_ops.apply_rotary_pos_emb(qv, kv, cos, sin)
+    c, s = cos.unsqueeze(1), sin.unsqueeze(1)
+    qr, kr = qv * c + fused_ops._rotate_half(qv) * s, kv * c + fused_ops._rotate_half(kv) * s
+    assert qe.shape == qr.shape and rel(qe, qr) <= 1e-3 and rel(ke, kr) <= 1e-3
+    dq, dk = torch.randn_like(qr), torch.randn_like(kr)
+    got = torch.autograd.grad([qe, ke], [q, k], [dq, dk])
+    want = torch.autograd.grad([qr, kr], [q, k], [dq, dk])
+    assert rel(got[0], want[0]) <= 2e-3 and rel(got[1], want[1]) <= 2e-3
+
+
+def test_patched_llama_step_matches_stock():
+    shape = fs.LlamaShape(hidden_size=512, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=8,
+                          num_key_value_heads=4, vocab_size=1000, max_position_embeddings=256)
+
+    def build(patched):
+        model = fs.build_quant_llama(shape, DEV, groupsize=128, seed=3)
+        fs.add_lora(model, ["q_proj", "v_proj"], r=8, alpha=16, seed=4)
+        if patched:
+            fused_ops.patch_llama(model)
+        fs.apply_gradient_checkpointing(model)
+        model.train()
+        return fs.LoraFinetuner(model, lr=0.0, loss_scale=64.0, dynamic_scale=False)
+
+    ids = torch.randint(0, 1000, (2, 64), generator=torch.Generator().manual_seed(9)).to(DEV)
+    from transformers.models.llama import modeling_llama as ml
+    stock_rope = ml.apply_rotary_pos_emb
+    try:
+        a = build(False)
+        la = float(a.step(ids)); ga = a.flat.buffer.clone()
+        b = build(True)
+        lb = float(b.step(ids)); gb = b.flat.buffer.clone()
+    finally:
+        ml.apply_rotary_pos_emb = stock_rope
+    assert abs(la - lb) <= 2e-3 * abs(la)
+    assert rel(gb, ga) <= 2e-2
