@@ -151,7 +151,7 @@ __global__ void swiglu_bwd_kernel(const __half* __restrict__ dout, const __half*
 // A thread handles 8 elements of the low half together with their 8 partners of the high half.
 template <bool BWD>
 __global__ void rope_kernel(const __half* __restrict__ in, const __half* __restrict__ cos, const __half* __restrict__ sin,
-                            __half* __restrict__ out, int tokens, int heads, int D, int in_pitch) {
+                            __half* __restrict__ out, int tokens, int heads, int D, int in_pitch, int table_rows) {
   const int half_v = D >> 4;                             // 8-element vectors per half head
   const size_t total = (size_t)tokens * heads * half_v;
   for (size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x; idx < total; idx += (size_t)gridDim.x * blockDim.x) {
@@ -161,8 +161,9 @@ __global__ void rope_kernel(const __half* __restrict__ in, const __half* __restr
     const int h = (int)(th - tok * heads);
     const __half* src = in + tok * in_pitch + (size_t)h * D;
     const uint4 lo = *reinterpret_cast<const uint4*>(src + 8 * j), hi = *reinterpret_cast<const uint4*>(src + (D >> 1) + 8 * j);
-    const __half* cr = cos + tok * D;
-    const __half* sr = sin + tok * D;
+    const size_t trow = tok % (size_t)table_rows;           // tables of one sequence serve every sequence of the batch
+    const __half* cr = cos + trow * D;
+    const __half* sr = sin + trow * D;
     const uint4 cl = *reinterpret_cast<const uint4*>(cr + 8 * j), ch = *reinterpret_cast<const uint4*>(cr + (D >> 1) + 8 * j);
     const uint4 sl = *reinterpret_cast<const uint4*>(sr + 8 * j), sh = *reinterpret_cast<const uint4*>(sr + (D >> 1) + 8 * j);
     const uint32_t L[4] = {lo.x, lo.y, lo.z, lo.w}, Hh[4] = {hi.x, hi.y, hi.z, hi.w};
@@ -243,14 +244,15 @@ extern "C" int q4_swiglu_bwd(const void* dout, const void* gate, const void* up,
 }
 
 extern "C" int q4_rope(const void* in, const void* cos, const void* sin, void* out, int tokens, int heads, int D, int in_pitch,
-                       int backward, q4_stream_t stream) {
+                       int table_rows, int backward, q4_stream_t stream) {
   if (!in || !cos || !sin || !out) return fail(Q4_E_BADARG, "rope: null pointer");
+  if (table_rows <= 0 || tokens % table_rows) return fail(Q4_E_BADARG, "rope: %d tokens are not a whole number of tables of %d rows", tokens, table_rows);
   if (tokens <= 0 || heads <= 0 || D <= 0 || in_pitch < heads * D) return fail(Q4_E_BADARG, "rope: tokens=%d heads=%d D=%d pitch=%d", tokens, heads, D, in_pitch);
   if (D % 16 || in_pitch % 8) return fail(Q4_E_SHAPE, "rope: D=%d must be a multiple of 16 and the pitch of 8", D);
   if (!aligned16(in) || !aligned16(cos) || !aligned16(sin) || !aligned16(out)) return fail(Q4_E_ALIGN, "rope: pointers must be 16-byte aligned");
   if (int e = check_device()) return e;
   const int grid = ew_grid((size_t)tokens * heads * (D / 16), 256);
-  if (backward) rope_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>((const __half*)in, (const __half*)cos, (const __half*)sin, (__half*)out, tokens, heads, D, in_pitch);
-  else rope_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>((const __half*)in, (const __half*)cos, (const __half*)sin, (__half*)out, tokens, heads, D, in_pitch);
+  if (backward) rope_kernel<true><<<grid, 256, 0, (cudaStream_t)stream>>>((const __half*)in, (const __half*)cos, (const __half*)sin, (__half*)out, tokens, heads, D, in_pitch, table_rows);
+  else rope_kernel<false><<<grid, 256, 0, (cudaStream_t)stream>>>((const __half*)in, (const __half*)cos, (const __half*)sin, (__half*)out, tokens, heads, D, in_pitch, table_rows);
   return check_cuda(cudaGetLastError(), "rope launch");
 }

@@ -114,7 +114,7 @@ class _Rope(torch.autograd.Function):
             src = src.contiguous()
         out = torch.empty((B, T, Hh, D), dtype=torch.float16, device=t.device)
         with _lib.on_device(t.device):
-            _lib.check(_lib.lib().q4_rope(src.data_ptr(), cos.data_ptr(), sin.data_ptr(), out.data_ptr(), B * T, Hh, D, Hh * D, 0,
+            _lib.check(_lib.lib().q4_rope(src.data_ptr(), cos.data_ptr(), sin.data_ptr(), out.data_ptr(), B * T, Hh, D, Hh * D, cos.shape[0] * cos.shape[1], 0,
                                           _lib.stream_of(t)), "rope")
         ctx.save_for_backward(cos, sin)
         return out.transpose(1, 2)
@@ -128,7 +128,7 @@ class _Rope(torch.autograd.Function):
             src = src.half().contiguous()
         out = torch.empty((B, T, Hh, D), dtype=torch.float16, device=g.device)
         with _lib.on_device(g.device):
-            _lib.check(_lib.lib().q4_rope(src.data_ptr(), cos.data_ptr(), sin.data_ptr(), out.data_ptr(), B * T, Hh, D, Hh * D, 1,
+            _lib.check(_lib.lib().q4_rope(src.data_ptr(), cos.data_ptr(), sin.data_ptr(), out.data_ptr(), B * T, Hh, D, Hh * D, cos.shape[0] * cos.shape[1], 1,
                                           _lib.stream_of(g)), "rope_bwd")
         return out.transpose(1, 2), None, None
 
@@ -142,8 +142,8 @@ def apply_rotary_pos_emb(q, k, cos, sin, unsqueeze_dim=1):
     """Drop-in for transformers' ``apply_rotary_pos_emb`` (``q``, ``k`` ``[B, heads, T, D]``, ``cos`` / ``sin``
     ``[B, T, D]``)."""
     D = q.shape[-1]
-    if (unsqueeze_dim == 1 and q.dim() == 4 and _fusable(q, k, cos, sin) and cos.dim() == 3 and cos.shape[0] == q.shape[0]
-            and cos.shape[1] == q.shape[2] and D % 16 == 0 and not cos.requires_grad and q.numel() > 0):
+    if (unsqueeze_dim == 1 and q.dim() == 4 and _fusable(q, k, cos, sin) and cos.dim() == 3 and cos.shape[0] in (1, q.shape[0])
+            and cos.shape[1] == q.shape[2] and cos.shape[2] == D and sin.shape == cos.shape and D % 16 == 0 and not cos.requires_grad and q.numel() > 0):
         c = cos if cos.is_contiguous() else cos.contiguous()
         s = sin if sin.is_contiguous() else sin.contiguous()
         return _Rope.apply(q, c, s), _Rope.apply(k, c, s)

@@ -184,7 +184,8 @@ size_t q4_gemm_workspace_bytes(int K, int N, int G);
  *                    tensors, or the halves of one fused gate_up output)
  *   q4_swiglu_bwd    dgate, dup (rows of `dpitch` halves) from dout, gate, up
  *   q4_rope          rotary embedding of in [tokens, heads, D] (token pitch `in_pitch` halves) with cos / sin
- *                    [tokens, D] into out [tokens, heads, D]; `backward` != 0 applies the transpose */
+ *                    [table_rows, D] (row = token % table_rows: the tables of one sequence serve a whole batch)
+ *                    into out [tokens, heads, D]; `backward` != 0 applies the transpose */
 int q4_rmsnorm_fwd(const void* x, const void* weight, void* y, float* rstd, int rows, int H, float eps, q4_stream_t stream);
 int q4_rmsnorm_bwd(const void* dy, const void* x, const void* weight, const float* rstd, void* dx, int rows, int H,
                    q4_stream_t stream);
@@ -192,7 +193,7 @@ int q4_swiglu_fwd(const void* gate, const void* up, void* out, int rows, int I, 
 int q4_swiglu_bwd(const void* dout, const void* gate, const void* up, void* dgate, void* dup, int rows, int I, int pitch,
                   int dpitch, q4_stream_t stream);
 int q4_rope(const void* in, const void* cos, const void* sin, void* out, int tokens, int heads, int D, int in_pitch,
-            int backward, q4_stream_t stream);
+            int table_rows, int backward, q4_stream_t stream);
 
 /* Copies the device status word to *out (synchronises the device): 0, or 0xDEAD0001 if a bounded
  * wait inside a q4_gemm_* kernel expired (its output is then invalid). */

@@ -58,12 +58,13 @@ def test_swiglu_matches_stock(rows, I, fused_input):
         assert rel(a, b) <= 3e-3
 
 
-@pytest.mark.parametrize("B,T,H,KV,D", [(4, 256, 32, 32, 128), (1, 77, 8, 2, 64)])
-def test_rope_matches_stock(B, T, H, KV, D):
+@pytest.mark.parametrize("B,T,H,KV,D,TB", [(4, 256, 32, 32, 128, 1), (1, 77, 8, 2, 64, 1), (3, 40, 4, 4, 32, 3)])
+def test_rope_matches_stock(B, T, H, KV, D, TB):
+    """TB: batch of the cos / sin tables (1 = the tables of one sequence, broadcast over the batch, as the model passes them)."""
     g = torch.Generator(device=DEV).manual_seed(T + D)
     q = torch.randn((B, T, H * D), generator=g, device=DEV).half().requires_grad_(True)
     k = torch.randn((B, T, KV * D), generator=g, device=DEV).half().requires_grad_(True)
-    ang = torch.rand((B, T, D // 2), generator=g, device=DEV) * 6.28
+    ang = torch.rand((TB, T, D // 2), generator=g, device=DEV) * 6.28
     cos, sin = torch.cat([ang.cos(), ang.cos()], -1).half(), torch.cat([ang.sin(), ang.sin()], -1).half()
     qv, kv = q.view(B, T, H, D).transpose(1, 2), k.view(B, T, KV, D).transpose(1, 2)
     qe, ke = fused_ops.apply_rotary_pos_emb(qv, kv, cos, sin)
