@@ -1,33 +1,23 @@
 // Decode product  y[M,N] (+)= x[M,K] * W  for 1 <= M <= 16 straight from the packed int4 layer.
 //
-// Bound by HBM: per weight 0.5 B of qweight plus 1/64 B of scales and 1/256 B of zero points at
-// groupsize 128; x and y are noise.  Design of the main kernel (sequential groups and v1 layers):
-//   * Persistent: one CTA per SM.  The matrix is cut into boxes of 64 packed rows x 32 columns
-//     (8 KiB, 512 k-rows x 32 outputs); the boxes, ordered column tile by column tile, are dealt to
-//     the CTAs in equal contiguous runs (stream-K), so every SM streams the same number of bytes
-//     whatever the shape.
-//   * A producer thread keeps a ring of GEMV_STAGES boxes in flight with TMA tile loads
-//     (cp.async.bulk.tensor.2d + mbarrier complete_tx): ~80 KiB outstanding per SM, which is what
-//     HBM latency x bandwidth asks for, independent of how many registers the math needs.
-//   * Eight consumer warps take two 32-row "steps" of each box.  In a step lane (g,t) reads packed
-//     row 4*step+t, columns 4g..4g+3 with one conflict-free LDS.128.  Nibbles are turned into fp16
-//     with the exponent trick (w & 0x000F000F | 0x6400 = 1024+q, one LOP3 per two weights) and fed
-//     to mma.sync.m16n8k16 as the A operand (rows = 16 output columns); x is the B operand
-//     (columns = batch).  The contraction index of the MMA is free, so the (q_j, q_j+4) pairing the
-//     mask produces is matched by permuting x with four PRMTs instead of un-shuffling weights.
-//   * The +1024 offset and the zero point leave with one extra MMA against an all-ones A tile,
-//     which yields sum_k x[k] per batch column:  y += s * (acc - (1024 + z + 1) * xsum), applied
-//     once per quantisation group in fp32.
-//   * When a CTA's run ends inside a column tile it writes its partial sums to the workspace and
-//     bumps the tile's arrival counter; the last contributor adds the partials in CTA order, so
-//     the result does not depend on scheduling.  No atomics on y, no zero-fill.
-//   * griddepcontrol: the kernel lets its successor start at once and itself waits for its
-//     predecessor only before it first touches x, y or the workspace - weights never depend on
-//     an earlier kernel, so back-to-back decode layers overlap their weight streams.
-//   * Every mbarrier wait is bounded; if one expires the kernel records a status word in the
-//     workspace, stops waiting and runs to its end (garbage out, no hang).
-// The act-order variant (group from g_idx per row) cannot factor the scale out of the
-// contraction; it dequantises per element from shared-memory scale tables instead.
+// Per weight 0.5 B of qweight plus 1/64 B of scales and 1/256 B of zero points cross HBM at groupsize
+// 128; x and y are noise.  Four kernels share the file; q4_gemv at its end picks one per call:
+//   * gemv_ws_kernel     one row, groups of 128, K in whole 256-row units: warp-specialised (a copy-issuing
+//                        warp, consumer warps, a helper for the exchange between CTAs), int8 tensor-core
+//                        MMAs on the packed words split into bytes, x as 16-bit block fixed point.
+//   * gemv_fast_kernel   1..8 rows (9..16: two launches), groups of 128 or of a multiple of 256 rows and the
+//                        first layer format: every warp streams its own 4 KiB units with TMA, fp16 MMAs
+//                        with the exponent trick, x re-laid per unit or once per CTA.
+//   * gemv_stream_kernel every other group size with sequential groups: the same streams, group test per step.
+//   * gemv_act_kernel    act-order (the group of every row from g_idx): scale and zero point per element
+//                        from shared-memory tables.
+// Common to all: the matrix is cut into units of 32 packed rows x 32 columns (4 KiB = 256 k-rows of one
+// 32-column tile) that arrive by TMA on mbarriers; W is the A operand of mma.sync (rows = output columns),
+// x the B operand (columns = batch rows); sums are kept in fp32 (or exact integers) and added in a fixed
+// order, so results are reproducible; launches carry the programmatic-dependent-launch attribute and wait
+// for the earlier kernel only before they first touch x, y or the workspace (weights never depend on an
+// earlier kernel); every wait on a barrier or a flag is bounded - on expiry the kernel records a status word
+// in the workspace (q4_gemv_status), stops waiting and runs to its end.
 #include "q4_async.cuh"
 #include <atomic>
 #include <new>
@@ -1380,6 +1370,288 @@ gemv_ws_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
   }
 }
 
+// ---- 2..8 rows, groups of 128: int8 MMAs fed by a conversion pass ------------------------------------------
+// The lean kernel re-lays x out per 4 KiB unit, which with eight rows costs twice the instructions of the
+// product itself.  Here x is converted once per call, by a small kernel of its own, into the 16-bit block
+// fixed point of the one-row kernel above (digits in MMA order, 16 bytes per 8 k and row, the rows of a block
+// 144 bytes apart so that the eight rows a quarter-warp reads fall on different banks), and the product kernel
+// brings the digits of 2048 k (one round of its eight consumer warps) with one bulk copy per round.  Every
+// CTA takes whole column tiles; within a tile unit r*8 + w goes to warp w in round r, so the warps of a round
+// share the round's slice of x.  Zero points leave as integers: (sum of q x_int) - (z + 1) (sum of x_int).
+constexpr int RW_W = 8, RW_S = 2, RW_MR = 8;
+constexpr int RW_XPITCH = (RW_MR + 1) * 16;                  // bytes per block of 8 k: 8 rows + 16 bytes of padding
+constexpr int RW_CHUNK_BLOCKS = RW_W * 32;                   // blocks of one round
+constexpr int RW_CHUNK_BYTES = RW_CHUNK_BLOCKS * RW_XPITCH;  // 36864
+
+// x fp16 [M, K] -> digits [blocks][9][16 bytes] and per (group, row) the pair (2^(E-14), sum of x_int as int bits)
+__global__ void __launch_bounds__(256)
+x_convert_kernel(const __half* __restrict__ x, unsigned char* __restrict__ xq, uint2* __restrict__ xinfo, int M, int K, int n_blocks) {
+  pdl_launch_dependents();
+  pdl_wait();                                    // x belongs to the stream order
+  const int lane = threadIdx.x & 31;
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;      // row-major over (row, block): 16 lanes share a row's group
+  if (idx >= RW_MR * n_blocks) return;
+  const int m = idx / n_blocks, blk = idx - m * n_blocks;
+  const bool live = m < M && 8 * blk < K;
+  const uint4 v = live ? __ldg(reinterpret_cast<const uint4*>(x + (size_t)m * K) + blk) : make_uint4(0u, 0u, 0u, 0u);
+  const __half2 h01 = as_h2(v.x), h23 = as_h2(v.y), h45 = as_h2(v.z), h67 = as_h2(v.w);
+  __half2 m2 = __hmax2(__hmax2(__habs2(h01), __habs2(h23)), __hmax2(__habs2(h45), __habs2(h67)));
+#pragma unroll
+  for (int d = 8; d >= 1; d >>= 1) m2 = __hmax2(m2, as_h2(__shfl_xor_sync(0xffffffffu, as_u32(m2), d)));
+  const uint32_t mb = as_u32(m2);
+  uint32_t ef = max(mb & 0x7FFFu, mb >> 16) >> 10;
+  const bool bad = ef == 31u;
+  ef = ef ? ef : 1u;
+  const float to_int = __uint_as_float((156u - ef) << 23);
+  const float from_int = bad ? __uint_as_float(0x7FC00000u) : __uint_as_float((98u + ef) << 23);
+  const float2 f01 = __half22float2(h01), f23 = __half22float2(h23), f45 = __half22float2(h45), f67 = __half22float2(h67);
+  const float magic = 12582912.f;
+  const uint32_t x0 = __float_as_uint(fmaf(f01.x, to_int, magic)), x1 = __float_as_uint(fmaf(f01.y, to_int, magic));
+  const uint32_t x2 = __float_as_uint(fmaf(f23.x, to_int, magic)), x3 = __float_as_uint(fmaf(f23.y, to_int, magic));
+  const uint32_t x4 = __float_as_uint(fmaf(f45.x, to_int, magic)), x5 = __float_as_uint(fmaf(f45.y, to_int, magic));
+  const uint32_t x6 = __float_as_uint(fmaf(f67.x, to_int, magic)), x7 = __float_as_uint(fmaf(f67.y, to_int, magic));
+  const uint32_t e02 = prmt(x0, x2, 0x5140), e46 = prmt(x4, x6, 0x5140), o13 = prmt(x1, x3, 0x5140), o57 = prmt(x5, x7, 0x5140);
+  *reinterpret_cast<uint4*>(xq + ((size_t)blk * (RW_MR + 1) + m) * 16) =
+      make_uint4(prmt(e02, e46, 0x7632), prmt(o13, o57, 0x7632), prmt(e02, e46, 0x5410), prmt(o13, o57, 0x5410));
+  int xs = (int)(((x0 + x1) + (x2 + x3)) + ((x4 + x5) + (x6 + x7)) - 8u * 0x4B400000u);
+#pragma unroll
+  for (int d = 8; d >= 1; d >>= 1) xs += __shfl_xor_sync(0xffffffffu, xs, d);
+  if ((lane & 15) == 0) xinfo[(size_t)(blk >> 4) * RW_MR + m] = make_uint2(__float_as_uint(from_int), (uint32_t)xs);
+}
+
+struct RowsParams {
+  GemvParams g;
+  int upt, n_groups, tiles, n_blocks;             // units per tile, groups, column tiles, blocks of 8 k (padded to units)
+  unsigned* status;
+  const unsigned char* xq;                        // digits, see x_convert_kernel
+  const uint2* xinfo;                             // [groups][8]
+};
+
+struct RwLayout { int stages, xring, xinfo, meta, meta_slot, meta_zp, red, bars, total; };
+__host__ __device__ inline RwLayout rw_layout(int G) {
+  RwLayout l;
+  l.stages = 0;
+  l.xring = RW_W * RW_S * GEMV_UNIT_BYTES;
+  l.xinfo = l.xring + 2 * RW_CHUNK_BYTES;
+  l.meta = (l.xinfo + G * RW_MR * 8 + 127) / 128 * 128;
+  l.meta_zp = (G * 64 + 127) / 128 * 128;
+  l.meta_slot = l.meta_zp + (G * 16 + 127) / 128 * 128;
+  l.red = l.meta + 2 * l.meta_slot;
+  l.bars = l.red + RW_W * RW_MR * GEMV_TN * 4;
+  l.total = l.bars + 8 * (2 * RW_W * RW_S + 9) + 16;
+  return l;
+}
+
+// untiled bulk copy global -> shared, completion counted on `bar` (addresses and size multiples of 16 bytes)
+__device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
+}
+
+__global__ void __launch_bounds__((RW_W + 1) * 32, 1)
+gemv_rows_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap,
+                 const __grid_constant__ CUtensorMap zmap, const RowsParams rp) {
+  extern __shared__ __align__(128) unsigned char smem_raw[];
+  unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  constexpr int W = RW_W, S = RW_S, MR = RW_MR, CT = W * 32, ALL = (W + 1) * 32;
+  const GemvParams& p = rp.g;
+  const int upt = rp.upt, G = rp.n_groups;
+  const RwLayout L = rw_layout(G);
+  unsigned char* xring = smem + L.xring;
+  const uint2* xinfo_s = reinterpret_cast<const uint2*>(smem + L.xinfo);
+  float* red = reinterpret_cast<float*>(smem + L.red);               // [W][MR][32]
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + L.bars);       // [W][S]
+  uint64_t* empty = full + W * S;                                    // [W][S]
+  uint64_t* mfull = empty + W * S;                                   // [2]
+  uint64_t* mempty = mfull + 2;                                      // [2]
+  uint64_t* xfull = mempty + 2;                                      // [2] digits of a round have landed
+  uint64_t* xempty = xfull + 2;                                      // [2] every consumer is done with them
+  uint64_t* ifull = xempty + 2;                                      // [1] the (scale, sum) table has landed
+  volatile int* flags = reinterpret_cast<volatile int*>(ifull + 1);
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t0 = (int)((long long)blockIdx.x * rp.tiles / gridDim.x), t1 = (int)((long long)(blockIdx.x + 1) * rp.tiles / gridDim.x);
+  const int rounds = (upt + W - 1) / W;                              // rounds per column tile
+  const uint32_t meta_tx = (uint32_t)G * 80u;
+
+  if (threadIdx.x < 2 * W * S) mbar_init(&full[threadIdx.x], 1);
+  else if (threadIdx.x < 2 * W * S + 2) mbar_init(&full[threadIdx.x], 1);                 // mfull
+  else if (threadIdx.x < 2 * W * S + 4) mbar_init(&full[threadIdx.x], W);                 // mempty
+  else if (threadIdx.x < 2 * W * S + 6) mbar_init(&full[threadIdx.x], 1);                 // xfull
+  else if (threadIdx.x < 2 * W * S + 8) mbar_init(&full[threadIdx.x], W);                 // xempty
+  else if (threadIdx.x == 2 * W * S + 8) mbar_init(ifull, 1);
+  if (threadIdx.x == 2 * W * S + 9) {
+    flags[0] = 0;
+    tma_prefetch_desc(&wmap); tma_prefetch_desc(&smap); tma_prefetch_desc(&zmap);
+  }
+  if (threadIdx.x < 2 * W * S + 9) mbar_fence_init();
+  __syncthreads();
+  pdl_launch_dependents();
+  auto expired = [&]() { flags[0] = 1; atomicExch(rp.status, Q4_STATUS_WAIT_EXPIRED); };
+
+  if (warp == W) {
+    // ---- issuer: lane w the units of consumer w, lane W the rounds' digits, lane W + 1 the tiles' metadata ----
+    int n = 0;                                   // units issued for this lane's consumer
+    int rc = 0;                                  // rounds issued (all tiles)
+    bool waited = false;
+    const int total_rounds = (t1 - t0) * rounds;
+    const int first_rounds = total_rounds < S ? total_rounds : S;   // rounds whose weights go out before the wait
+    for (int tile = t0; tile < t1; ++tile) {
+      const int seq = tile - t0, mslot = seq & 1;
+      if (lane == W + 1) {
+        if (seq >= 2 && !mbar_wait_sleep_bounded(&mempty[mslot], ((seq >> 1) & 1) ^ 1, 200000u)) expired();
+        unsigned char* m = smem + L.meta + mslot * L.meta_slot;
+        mbar_arrive_expect_tx(&mfull[mslot], meta_tx);
+        tma_load_2d(m, &smap, tile * GEMV_TN, 0, &mfull[mslot]);
+        tma_load_2d(m + L.meta_zp, &zmap, tile * (GEMV_TN / 8), 0, &mfull[mslot]);
+      }
+      for (int r = 0; r < rounds; ++r, ++rc) {
+        const int ux = r * W + lane;
+        if (lane < W && ux < upt) {              // weights never depend on an earlier kernel: they go first
+          const int st = n % S;
+          if (n >= S && !mbar_wait_sleep_bounded(&empty[lane * S + st], ((n / S) & 1) ^ 1, flags[0] ? 4u : 200000u)) expired();
+          mbar_arrive_expect_tx(&full[lane * S + st], GEMV_UNIT_BYTES);
+          tma_load_2d(smem + (size_t)(lane * S + st) * GEMV_UNIT_BYTES, &wmap, tile * GEMV_TN, ux * GEMV_UNIT_ROWS, &full[lane * S + st]);
+          ++n;
+        }
+        if (!waited && rc + 1 >= first_rounds) { // the rings are filling: now the digits, which the conversion kernel writes
+          __syncwarp();
+          pdl_wait();
+          waited = true;
+          if (lane == W) {
+            mbar_arrive_expect_tx(ifull, (uint32_t)G * MR * 8u);
+            bulk_load(smem + L.xinfo, rp.xinfo, (uint32_t)G * MR * 8u, ifull);
+            for (int q = 0; q <= rc; ++q) {      // the rounds passed so far; round q of the CTA is round q % rounds of its tile
+              const int rq = q % rounds;
+              const int blocks = min(RW_CHUNK_BLOCKS, rp.n_blocks - rq * RW_CHUNK_BLOCKS);
+              mbar_arrive_expect_tx(&xfull[q & 1], (uint32_t)blocks * RW_XPITCH);
+              bulk_load(xring + (q & 1) * RW_CHUNK_BYTES, rp.xq + (size_t)rq * RW_CHUNK_BYTES, (uint32_t)blocks * RW_XPITCH, &xfull[q & 1]);
+            }
+          }
+        } else if (waited && lane == W) {
+          const int xs = rc & 1;
+          if (rc >= 2 && !mbar_wait_sleep_bounded(&xempty[xs], ((rc >> 1) & 1) ^ 1, flags[0] ? 4u : 200000u)) expired();
+          const int blocks = min(RW_CHUNK_BLOCKS, rp.n_blocks - r * RW_CHUNK_BLOCKS);
+          mbar_arrive_expect_tx(&xfull[xs], (uint32_t)blocks * RW_XPITCH);
+          bulk_load(xring + xs * RW_CHUNK_BYTES, rp.xq + (size_t)r * RW_CHUNK_BYTES, (uint32_t)blocks * RW_XPITCH, &xfull[xs]);
+        }
+        __syncwarp();
+      }
+    }
+    if (!waited) pdl_wait();
+    return;
+  }
+
+  // ---- consumers ---------------------------------------------------------------------------------------------
+  pdl_wait();                                    // y belongs to the stream order
+  const int g = lane >> 2, t = lane & 3;
+  const uint32_t woff0 = 128u * (2 * t) + 16u * (g ^ (2 * t)), woff1 = 128u * (2 * t + 1) + 16u * (g ^ (2 * t + 1));
+  const unsigned char* my_stages = smem + (size_t)warp * S * GEMV_UNIT_BYTES;
+  float yacc[2][4];                              // [column pair][fragment]: columns 4g + 2 cp + (i >> 1), rows 2t + (i & 1)
+#pragma unroll
+  for (int cp = 0; cp < 2; ++cp)
+#pragma unroll
+    for (int i = 0; i < 4; ++i) yacc[cp][i] = 0.f;
+  const uint32_t lim0 = 20000000u;
+  if (!mbar_spin_bounded(ifull, 0, lim0)) expired();
+
+  int n = 0, rc = 0;
+  for (int tile = t0; tile < t1; ++tile) {
+    const int seq = tile - t0, mslot = seq & 1;
+    const unsigned char* meta = smem + L.meta + mslot * L.meta_slot;
+    if (!mbar_spin_bounded(&mfull[mslot], (seq >> 1) & 1, flags[0] ? 64u : lim0)) expired();
+    for (int r = 0; r < rounds; ++r, ++rc) {
+      const int xs = rc & 1, ux = r * W + warp;
+      if (!mbar_spin_bounded(&xfull[xs], (rc >> 1) & 1, flags[0] ? 64u : lim0)) expired();
+      if (ux < upt) {
+        const int st = n % S;
+        if (!mbar_spin_bounded(&full[warp * S + st], (n / S) & 1, flags[0] ? 64u : lim0)) expired();
+        const unsigned char* wst = my_stages + (size_t)st * GEMV_UNIT_BYTES;
+        // digits of this warp's unit: block b of the round at b * 144, row g at + 16 g
+        const unsigned char* xq = xring + xs * RW_CHUNK_BYTES + (size_t)(warp * 32 + 2 * t) * RW_XPITCH + 16 * g;
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          uint4 wv[4], xv[4];
+#pragma unroll
+          for (int uu = 0; uu < 4; ++uu) {
+            wv[uu] = *reinterpret_cast<const uint4*>(wst + ((uu & 1) ? woff1 : woff0) + 1024 * (2 * h + (uu >> 1)));
+            xv[uu] = *reinterpret_cast<const uint4*>(xq + (size_t)(8 * (2 * h + (uu >> 1)) + (uu & 1)) * RW_XPITCH);
+          }
+          int chi[2][4], clo[2][4];
+#pragma unroll
+          for (int uu = 0; uu < 4; ++uu) {
+            const uint32_t w[4] = {wv[uu].x, wv[uu].y, wv[uu].z, wv[uu].w};
+            uint32_t ev[4], od[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q) { ev[q] = w[q] & 0x0F0F0F0Fu; od[q] = (w[q] >> 4) & 0x0F0F0F0Fu; }
+            if (uu == 0) {
+              imma_u8s8_first(chi[0], ev[0], ev[1], od[0], od[1], xv[uu].x, xv[uu].y);
+              imma_u8u8_first(clo[0], ev[0], ev[1], od[0], od[1], xv[uu].z, xv[uu].w);
+              imma_u8s8_first(chi[1], ev[2], ev[3], od[2], od[3], xv[uu].x, xv[uu].y);
+              imma_u8u8_first(clo[1], ev[2], ev[3], od[2], od[3], xv[uu].z, xv[uu].w);
+            } else {
+              imma_u8s8(chi[0], ev[0], ev[1], od[0], od[1], xv[uu].x, xv[uu].y);
+              imma_u8u8(clo[0], ev[0], ev[1], od[0], od[1], xv[uu].z, xv[uu].w);
+              imma_u8s8(chi[1], ev[2], ev[3], od[2], od[3], xv[uu].x, xv[uu].y);
+              imma_u8u8(clo[1], ev[2], ev[3], od[2], od[3], xv[uu].z, xv[uu].w);
+            }
+          }
+          // close the group: integer sums minus (z + 1) * sum of x_int, times scale and the row's 2^(E-14)
+          const int grp = 2 * ux + h;
+          const uint4 inf = *reinterpret_cast<const uint4*>(xinfo_s + (size_t)grp * MR + 2 * t);    // rows 2t, 2t + 1
+          const float xsc[2] = {__uint_as_float(inf.x), __uint_as_float(inf.z)};
+          const int xsum[2] = {(int)inf.y, (int)inf.w};
+          const uint2 sc = *reinterpret_cast<const uint2*>(meta + grp * 64 + 8 * g);
+          const float2 s01 = __half22float2(as_h2(sc.x)), s23 = __half22float2(as_h2(sc.y));
+          const float s[4] = {s01.x, s01.y, s23.x, s23.y};
+          const uint32_t zw = *reinterpret_cast<const uint32_t*>(meta + L.meta_zp + grp * 16 + 4 * (g >> 1)) >> (16 * (g & 1));
+#pragma unroll
+          for (int cp = 0; cp < 2; ++cp)
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              const int col = 2 * cp + (i >> 1), row = i & 1;
+              const int z1 = (int)((zw >> (4 * col)) & 0xFu) + 1;
+              const int v = chi[cp][i] * 256 + clo[cp][i] - z1 * xsum[row];
+              yacc[cp][i] = fmaf(s[col] * xsc[row], (float)v, yacc[cp][i]);
+            }
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[warp * S + st]);
+        ++n;
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&xempty[xs]);
+    }
+    if (lane == 0) mbar_arrive(&mempty[mslot]);
+    // the tile's sums: every warp leaves its [8 rows][32 columns], the last warp adds them in warp order
+    const bool reducer = warp == W - 1;
+    if (!reducer && seq >= 1) named_bar_sync(2, CT);
+    float* mine = red + warp * MR * GEMV_TN;
+#pragma unroll
+    for (int cp = 0; cp < 2; ++cp)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        mine[(2 * t + (i & 1)) * GEMV_TN + 4 * g + 2 * cp + (i >> 1)] = yacc[cp][i];
+        yacc[cp][i] = 0.f;
+      }
+    if (!reducer) {
+      __threadfence_block();
+      named_bar_arrive(1, CT);
+    } else {
+      named_bar_sync(1, CT);
+      for (int r = 0; r < p.M; ++r) {
+        float v = 0.f;
+#pragma unroll
+        for (int w = 0; w < W; ++w) v += red[(w * MR + r) * GEMV_TN + lane];
+        store_y(p, r, tile * GEMV_TN + lane, v);
+      }
+      named_bar_arrive(2, CT);
+    }
+  }
+}
+
 // ---- act-order (group of row k = g_idx[k]) -------------------------------------------------------
 // Scale and (z+1) of the CTA's 32 columns for every group live in shared memory as half2
 // (s, z+1); every element is dequantised as s*(q - (z+1)) in fp16 pairs before the MMA.
@@ -1688,6 +1960,56 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
   if ((size_t)(N / GEMV_TN) * sizeof(unsigned) > GEMV_STATUS_OFFSET)
     return fail(Q4_E_SHAPE, "gemv: N=%d has more column tiles than the workspace head holds", N);
   if (int e = check_device()) return e;
+
+  // 2..8 rows, groups of 128, whole 256-row units, enough column tiles to give every CTA whole ones: the
+  // int8-MMA kernel fed by the conversion pass (9..16 rows: twice, below)
+  if (M >= 2 && M <= 8 && !act && !v1 && groupsize == 128 && K % 256 == 0 && G == K / 128 && G <= 256 && !(g_gemv_variant & 16) &&
+      N / GEMV_TN >= 32) {
+    const int upt = K / 256, n_blocks = upt * 32;
+    const size_t xq_bytes = (size_t)n_blocks * RW_XPITCH, info_bytes = (size_t)G * RW_MR * 8;
+    const size_t smem = 1024 + (size_t)rw_layout(G).total;
+    if (GEMV_WS_HEAD + xq_bytes + 256 + info_bytes <= workspace_bytes && smem <= GF_SMEM_LIMIT) {
+      cudaStream_t st = (cudaStream_t)stream;
+      unsigned char* xq = (unsigned char*)workspace + GEMV_WS_HEAD;
+      uint2* xinfo = (uint2*)(xq + ((xq_bytes + 255) & ~(size_t)255));
+      RowsParams rp;
+      rp.g.x = (const __half*)x; rp.g.qw = (const uint32_t*)qweight; rp.g.y = y; rp.g.scales = (const __half*)scales;
+      rp.g.qzeros = (const uint32_t*)qzeros; rp.g.g_idx = nullptr; rp.g.bias = (const __half*)bias;
+      rp.g.M = M; rp.g.K = K; rp.g.N = N; rp.g.groupsize = groupsize; rp.g.part = nullptr; rp.g.counters = nullptr;
+      rp.g.steps_total = K / 32; rp.g.steps_per_split = 0; rp.g.S = 1;
+      rp.g.y_f32 = (y_dtype == Q4_F32); rp.g.accumulate = (flags & Q4_GEMV_ACCUMULATE) ? 1 : 0; rp.g.v1 = 0;
+      rp.upt = upt; rp.n_groups = G; rp.tiles = N / GEMV_TN; rp.n_blocks = n_blocks;
+      rp.status = (unsigned*)((char*)workspace + GEMV_STATUS_OFFSET);
+      rp.xq = xq; rp.xinfo = xinfo;
+      CUtensorMap wsw, sm2, zm2;
+      if (int e = make_tmap_2d(&wsw, qweight, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, (uint64_t)N, (uint64_t)(K / 8), (uint64_t)N * 4,
+                               GEMV_TN, GEMV_UNIT_ROWS, CU_TENSOR_MAP_SWIZZLE_128B)) return e;
+      if (int e = make_tmap_2d(&sm2, scales, CU_TENSOR_MAP_DATA_TYPE_UINT16, 2, (uint64_t)N, (uint64_t)G, (uint64_t)N * 2,
+                               GEMV_TN, G, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
+      if (!aligned16(qzeros)) return fail(Q4_E_ALIGN, "gemv: qzeros must be 16-byte aligned");
+      if (int e = make_tmap_2d(&zm2, qzeros, CU_TENSOR_MAP_DATA_TYPE_UINT32, 4, (uint64_t)(N / 8), (uint64_t)G, (uint64_t)(N / 8) * 4,
+                               GEMV_TN / 8, G, CU_TENSOR_MAP_SWIZZLE_NONE)) return e;
+      static std::atomic<bool> attr_done[64];
+      int dev = 0;
+      cudaGetDevice(&dev);
+      if (dev < 0 || dev >= 64 || !attr_done[dev].load(std::memory_order_acquire)) {
+        if (int e = check_cuda(cudaFuncSetAttribute(gemv_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GF_SMEM_LIMIT),
+                               "gemv smem attribute")) return e;
+        if (dev >= 0 && dev < 64) attr_done[dev].store(true, std::memory_order_release);
+      }
+      cudaLaunchAttribute at[1];
+      at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+      at[0].val.programmaticStreamSerializationAllowed = 1;
+      cudaLaunchConfig_t c1 = {};
+      c1.gridDim = dim3((RW_MR * n_blocks + 255) / 256); c1.blockDim = dim3(256); c1.stream = st; c1.attrs = at; c1.numAttrs = 1;
+      if (int e = check_cuda(cudaLaunchKernelEx(&c1, x_convert_kernel, (const __half*)x, xq, xinfo, M, K, n_blocks), "gemv conversion launch")) return e;
+      int grid = sm_count();
+      if (grid > rp.tiles) grid = rp.tiles;
+      cudaLaunchConfig_t c2 = {};
+      c2.gridDim = dim3(grid); c2.blockDim = dim3((RW_W + 1) * 32); c2.dynamicSmemBytes = smem; c2.stream = st; c2.attrs = at; c2.numAttrs = 1;
+      return check_cuda(cudaLaunchKernelEx(&c2, gemv_rows_kernel, wsw, sm2, zm2, rp), "gemv launch");
+    }
+  }
 
   // 9..16 rows on a layer the lean kernel takes: two launches of it (8 rows, then the rest) end sooner
   // than one launch of the general streaming kernel

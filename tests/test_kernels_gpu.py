@@ -294,22 +294,42 @@ def test_gemv_work_dealing_modes(K, N, M):
 @pytest.mark.parametrize("M", [1, 3, 8])
 @pytest.mark.parametrize("K,N", [(4096, 4096), (1024, 5120), (11008, 4096), (4224, 9600), (8192, 8192)])
 def test_gemv_x_per_unit_and_per_cta_agree(K, N, M):
-    """The lean decode kernel with x brought and re-laid per 4 KiB unit (variant 1) and with the whole of x
-    re-laid once per CTA (variant 2; K = 4224 has a half-filled last unit whose padding must read as zero):
-    both within tolerance of the oracle, and the automatic choice equal to one of them bit for bit."""
+    """The fp16-MMA decode kernel (variant bit 16) with x brought and re-laid per 4 KiB unit (17) and with the
+    whole of x re-laid once per CTA (18; K = 4224 has a half-filled last unit whose padding must read as zero):
+    both within tolerance of the oracle, and its automatic choice (16) equal to one of them bit for bit.  The
+    default (0) is the int8-MMA kernel where it applies: within tolerance as well."""
     layer = synth.make_layer(K, N, 128, False, seed=K // 7 + N)
     x = synth.make_acts(M, K, seed=3 + M)
     want = orc.gemv_fp32(x, layer.qweight, layer.scales, layer.qzeros, layer.g_idx)
     got = {}
     try:
-        for v in (1, 2, 0):
+        for v in (17, 18, 16, 0):
             quant_cuda.gemv_set_variant(v)
             got[v] = gemv_gpu(layer, x, torch.float32)
             assert rel_fro(got[v], want) <= REL_TOL, v
     finally:
         quant_cuda.gemv_set_variant(0)
-    assert torch.equal(got[0], got[1]) or torch.equal(got[0], got[2])
+    assert torch.equal(got[16], got[17]) or torch.equal(got[16], got[18])
     torch.cuda.synchronize()
+    assert quant_cuda.device_status() == 0
+
+
+@pytest.mark.parametrize("M", [2, 5, 8, 11, 16])
+@pytest.mark.parametrize("K,N", [(4096, 4096), (11008, 4096), (4096, 11008), (2048, 1024), (512, 8192)])
+def test_gemv_rows_kernel(K, N, M):
+    """2..16 rows on the int8-MMA kernel fed by the conversion pass (9..16 rows: two launches), fp16 and fp32
+    outputs, accumulate and bias; twice, since the digits of x live in the workspace between the two kernels."""
+    layer = synth.make_layer(K, N, 128, False, seed=K + N + M)
+    x = synth.make_acts(M, K, seed=M)
+    want = orc.gemv_fp32(x, layer.qweight, layer.scales, layer.qzeros, layer.g_idx)
+    first = gemv_gpu(layer, x, torch.float32)
+    assert rel_fro(first, want) <= 1e-4                        # exact integer sums: only x is rounded (block fixed point)
+    assert torch.equal(first, gemv_gpu(layer, x, torch.float32))
+    assert rel_fro(gemv_gpu(layer, x, torch.float16), want) <= REL_TOL
+    y0 = torch.randn(M, N)
+    bias = torch.randn(N).half()
+    got = gemv_gpu(layer, x, torch.float32, _lib.GEMV_ACCUMULATE, y0=y0.to(DEV), bias=bias.to(DEV))
+    assert rel_fro(got, want + y0.double() + bias.double()) <= REL_TOL
     assert quant_cuda.device_status() == 0
 
 
