@@ -625,7 +625,7 @@ def main():
                          "sampler sees the GPU under this load (0 for profiler captures: warm-up replays only)")
     ap.add_argument("--decode-shape", default="", help="decode pool of one KxN layer shape instead of the three LLaMA-7B shapes, "
                                                        "e.g. 8192x28672 (for profiler captures; not the headline workload)")
-    ap.add_argument("--finetune-steps", type=int, default=5, help="timed LLaMA-7B LoRA finetune steps (0 = skip)")
+    ap.add_argument("--finetune-steps", type=int, default=30, help="timed LoRA finetune steps (0 = skip)")
     ap.add_argument("--finetune-config", default="7b", choices=["7b", "70b"],
                     help="7b: LLaMA-7B, r=8 LoRA on q/v, 4 x 256 tokens, fp16 (C3); 70b: LLaMA-2-70B GQA, act-order, r=16 LoRA on "
                          "all seven projections, 1 x 2048 tokens, bf16 autocast (C4; 35 GB of int4 weights per GPU)")
