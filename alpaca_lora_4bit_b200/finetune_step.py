@@ -143,11 +143,67 @@ class FlatGrads:
     def zero(self):
         self.buffer.zero_()
 
+    def all_reduce_sum(self, group=None) -> int:
+        """Sums the buffer over the ranks; returns the number of ranks (the divisor the optimiser applies)."""
+        import torch.distributed as dist
+        if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
+            dist.all_reduce(self.buffer, op=dist.ReduceOp.SUM, group=group)
+            return dist.get_world_size(group)
+        return 1
+
     def all_reduce_mean(self, group=None):
         import torch.distributed as dist
         if dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1:
             dist.all_reduce(self.buffer, op=dist.ReduceOp.SUM, group=group)
             self.buffer.div_(dist.get_world_size(group))
+
+
+class FlatAdamW:
+    """AdamW with loss-scale handling over flat buffers: the trainable factors become views of one fp32
+    buffer (as their gradients are views of ``FlatGrads.buffer``) and a step is one ``q4_adamw_flat`` call,
+    three launches whatever the number of adapters, with the step count and the loss scale kept on the device
+    so that the step can be captured.  Same arithmetic as ``torch.optim.AdamW`` under ``torch.amp.GradScaler``
+    (what the reference's trainer runs, finetune.py:150-170)."""
+
+    def __init__(self, params: List[nn.Parameter], flat: "FlatGrads", lr: float, betas=(0.9, 0.999), eps: float = 1e-8,
+                 weight_decay: float = 0.01, init_scale: float = 65536.0, dynamic: bool = True, growth_factor: float = 2.0,
+                 backoff_factor: float = 0.5, growth_interval: int = 2000):
+        dev = params[0].device
+        total = flat.buffer.numel()
+        self.param = torch.empty(total, dtype=torch.float32, device=dev)
+        off = 0
+        for p in params:
+            n = p.numel()
+            self.param[off:off + n].copy_(p.data.reshape(-1))
+            p.data = self.param[off:off + n].view_as(p)
+            off += n
+        self.grad = flat.buffer
+        self.exp_avg = torch.zeros_like(self.param)
+        self.exp_avg_sq = torch.zeros_like(self.param)
+        self.state = torch.tensor([0.0, float(init_scale), 0.0, 0.0], dtype=torch.float32, device=dev)
+        self.lr, self.betas, self.eps, self.weight_decay = lr, betas, eps, weight_decay
+        self.growth_factor, self.backoff_factor = growth_factor, backoff_factor
+        self.growth_interval = growth_interval if dynamic else 0
+
+    def scale(self, loss: torch.Tensor) -> torch.Tensor:
+        return loss.float() * self.state[1]
+
+    def step(self, grad_div: float = 1.0) -> None:
+        from . import _lib
+        with _lib.on_device(self.param.device):
+            _lib.check(_lib.lib().q4_adamw_flat(self.param.data_ptr(), self.grad.data_ptr(), self.exp_avg.data_ptr(),
+                                                self.exp_avg_sq.data_ptr(), self.param.numel(), self.lr, self.betas[0], self.betas[1],
+                                                self.eps, self.weight_decay, float(grad_div), self.state.data_ptr(),
+                                                self.growth_factor, self.backoff_factor, self.growth_interval,
+                                                _lib.stream_of(self.param)), "adamw_flat")
+
+    @property
+    def steps_taken(self) -> int:
+        return int(self.state[0].item())
+
+    @property
+    def loss_scale(self) -> float:
+        return float(self.state[1].item())
 
 
 class LoraFinetuner:
@@ -161,7 +217,6 @@ class LoraFinetuner:
             raise ValueError("model has no trainable parameters (wrap it with add_lora first)")
         self.flat = FlatGrads(self.params)
         on_gpu = self.params[0].is_cuda
-        self.opt = torch.optim.AdamW(self.params, lr=lr, fused=on_gpu, capturable=on_gpu)
         self._graph = None
         self._static_ids = None
         self._static_loss = None
@@ -172,7 +227,13 @@ class LoraFinetuner:
         # fp16 training as the HF Trainer does it: dynamic loss scale, steps with non-finite gradients skipped
         if dynamic_scale is None:
             dynamic_scale = self.params[0].is_cuda and autocast and autocast_dtype == torch.float16
-        self.scaler = torch.amp.GradScaler("cuda", init_scale=loss_scale) if dynamic_scale else None
+        if on_gpu:
+            # one flat optimiser kernel; a static scale is a dynamic one that never moves
+            self.opt = FlatAdamW(self.params, self.flat, lr=lr, init_scale=loss_scale, dynamic=bool(dynamic_scale))
+            self.scaler = None
+        else:
+            self.opt = torch.optim.AdamW(self.params, lr=lr)
+            self.scaler = None
 
     def capture(self, example_ids: torch.Tensor, warmup: int = 3) -> bool:
         """Record the whole step (forward, backward, gradient all-reduce, AdamW) as one CUDA graph for
@@ -216,11 +277,13 @@ class LoraFinetuner:
         dev_type = input_ids.device.type
         with torch.autocast(device_type=dev_type, dtype=self.autocast_dtype, enabled=self.autocast and dev_type == "cuda"):
             loss = self.model(input_ids=input_ids, labels=input_ids, use_cache=False).loss
-        if self.scaler is not None:
-            self.scaler.scale(loss.float()).backward()
-            self.flat.all_reduce_mean(self.group)          # scaled gradients; an overflow on any rank reaches all
-            self.scaler.step(self.opt)                     # unscales, skips the update on inf/nan
-            self.scaler.update()
+        if isinstance(self.opt, FlatAdamW):
+            # fp16 training as the HF Trainer does it: dynamic loss scale, steps with non-finite gradients skipped.
+            # The quant linears and the LoRA products compute in fp16 whatever the autocast dtype is, so a
+            # (static) scale is applied under bf16 autocast as well.
+            self.opt.scale(loss).backward()
+            world = self.flat.all_reduce_sum(self.group)   # scaled gradients; an overflow on any rank reaches all
+            self.opt.step(grad_div=world)                  # unscales, divides by the ranks, skips the update on inf/nan
         else:
             # The quant linears and the LoRA products compute in fp16 whatever the autocast dtype is (their
             # autograd functions cast their inputs to fp16, as the reference's do), so the gradients that

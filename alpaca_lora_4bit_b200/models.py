@@ -19,6 +19,7 @@ import torch.nn as nn
 import torch.nn.functional as F
 from torch.amp import custom_bwd, custom_fwd
 
+from . import _lib
 from . import matmul_utils_4bit as mm4b
 from . import quant_cuda
 from .autograd_4bit import Autograd4bitQuantLinear
@@ -91,49 +92,76 @@ class LoraLayerTwin:
 _LoraBase = _PeftLoraLayer if _HAVE_PEFT else LoraLayerTwin
 
 
+def _lora_project(x2: torch.Tensor, w: torch.Tensor, scaling: float) -> torch.Tensor:
+    """``scaling * x2 @ w.T`` as the zero-padded fp16 ``[M, 64]`` operand of the fused GEMM's LoRA stage
+    (``x2`` fp16 ``[M, C]``, ``w`` fp16 ``[r, C]``, both contiguous)."""
+    out = torch.empty((x2.shape[0], 64), dtype=torch.float16, device=x2.device)
+    with _lib.on_device(x2.device):
+        _lib.check(_lib.lib().q4_lora_project(x2.data_ptr(), w.data_ptr(), out.data_ptr(), x2.shape[0], x2.shape[1], w.shape[0],
+                                              float(scaling), _lib.stream_of(x2)), "lora_project")
+    return out
+
+
 class LoraMatmul4bit(torch.autograd.Function):
     """``y = x @ W + bias + scaling * (x @ A^T) @ B^T`` over a 4-bit v2 layer in one fused kernel, with
     the matching backward ``dx = dy @ W^T + scaling * (dy @ B) @ A`` (also one kernel) and the LoRA
     gradients ``dA = (scaling * dy @ B)^T @ x``, ``dB = dy^T @ (scaling * x @ A^T)``.
 
     Same mathematics as ``Autograd4bitQuantLinear.forward`` followed by the adapter update of
-    ``Linear4bitLt.forward`` (models.py:51-69); the two skinny products that form the rank-r
-    activations are library GEMMs, everything N- or K-wide runs inside the dequant-GEMM kernels."""
+    ``Linear4bitLt.forward`` (models.py:51-69).  The rank-r activations ``u = scaling * x A^T`` and
+    ``v = scaling * dy B`` come from ``q4_lora_project`` (one read of x or dy, written in the padded form
+    the GEMM kernels take), everything N- or K-wide runs inside the dequant-GEMM kernels, and one
+    ``q4_lora_grads`` launch produces both gradients in the factors' own dtype (fp32 for fresh PEFT
+    adapters) instead of fp16 products cast back by autograd."""
 
     @staticmethod
-    @custom_fwd(device_type="cuda", cast_inputs=torch.float16)
+    @custom_fwd(device_type="cuda")
     def forward(ctx, x, lora_a, lora_b, scaling, qweight, scales, qzeros, g_idx, bias):
         K, N = qweight.shape[0] * 8, qweight.shape[1]
-        x2 = x.reshape(-1, K).half().contiguous()
-        a_h, b_h = lora_a.half().contiguous(), lora_b.half().contiguous()
-        r = a_h.shape[0]
-        u = F.pad(torch.matmul(x2, a_h.t()) * scaling, (0, 64 - r))              # [M, 64], scaling folded in
+        x2 = x.reshape(-1, K)
+        if x2.dtype != torch.float16 or not x2.is_contiguous():
+            x2 = x2.to(torch.float16).contiguous()
+        a_h = lora_a.detach().to(torch.float16).contiguous()                     # [r, K]
+        b_h = lora_b.detach().to(torch.float16).contiguous()                     # [N, r]
+        u = _lora_project(x2, a_h, scaling)                                      # [M, 64], scaling folded in
         y = torch.empty((x2.shape[0], N), dtype=torch.float16, device=x.device)
         quant_cuda.gemm(x2, qweight, y, scales.half(), qzeros, g_idx, bias=None if bias is None else bias.half(),
                         lora_u=u, lora_w=b_h)
-        ctx.save_for_backward(x2, u, a_h, b_h, qweight, scales, qzeros, g_idx)
+        ctx.save_for_backward(x2, u, lora_a, lora_b, qweight, scales, qzeros, g_idx)
         ctx.scaling = scaling
         ctx.x_shape = x.shape
+        ctx.x_dtype = x.dtype
         return y.reshape(x.shape[:-1] + (N,))
 
     @staticmethod
     @custom_bwd(device_type="cuda")
     def backward(ctx, grad_output):
-        x2, u, a_h, b_h, qweight, scales, qzeros, g_idx = ctx.saved_tensors
+        x2, u, lora_a, lora_b, qweight, scales, qzeros, g_idx = ctx.saved_tensors
         K, N = qweight.shape[0] * 8, qweight.shape[1]
-        r = a_h.shape[0]
-        dy = grad_output.reshape(-1, N).half().contiguous()
-        v = torch.matmul(dy, b_h) * ctx.scaling                                   # [M, r]
+        r = lora_a.shape[0]
+        dy = grad_output.reshape(-1, N)
+        if dy.dtype != torch.float16 or not dy.is_contiguous():
+            dy = dy.to(torch.float16).contiguous()
+        M = dy.shape[0]
+        # v = scaling * dy @ B: the projection kernel wants its small operand as [r, N]
+        bt_h = lora_b.detach().t().to(torch.float16, memory_format=torch.contiguous_format)
+        v = _lora_project(dy, bt_h, ctx.scaling)
         dx = d_a = d_b = None
         if ctx.needs_input_grad[0]:
-            dx = torch.empty((dy.shape[0], K), dtype=torch.float16, device=dy.device)
+            dx = torch.empty((M, K), dtype=torch.float16, device=dy.device)
             quant_cuda.gemm(dy, qweight, dx, scales.half(), qzeros, g_idx, transpose=True,
-                            lora_u=F.pad(v, (0, 64 - r)), lora_w=a_h)
-            dx = dx.reshape(ctx.x_shape)
-        if ctx.needs_input_grad[1]:
-            d_a = torch.matmul(v.t(), x2)                                         # [r, K]
-        if ctx.needs_input_grad[2]:
-            d_b = torch.matmul(dy.t(), u[:, :r])                                  # [N, r]
+                            lora_u=v, lora_w=lora_a.detach().to(torch.float16).contiguous())
+            dx = dx.reshape(ctx.x_shape).to(ctx.x_dtype)
+        want_a, want_b = ctx.needs_input_grad[1], ctx.needs_input_grad[2]
+        if want_a or want_b:
+            ga = torch.empty((r, K), dtype=torch.float32, device=dy.device) if want_a else None
+            gb = torch.empty((N, r), dtype=torch.float32, device=dy.device) if want_b else None
+            with _lib.on_device(dy.device):
+                _lib.check(_lib.lib().q4_lora_grads(v.data_ptr(), x2.data_ptr(), ga.data_ptr() if want_a else None, K,
+                                                    dy.data_ptr(), u.data_ptr(), gb.data_ptr() if want_b else None, N,
+                                                    M, r, _lib.stream_of(dy)), "lora_grads")
+            d_a = ga.to(lora_a.dtype) if want_a else None
+            d_b = gb.to(lora_b.dtype) if want_b else None
         return dx, d_a, d_b, None, None, None, None, None, None
 
 

@@ -195,6 +195,33 @@ int q4_swiglu_bwd(const void* dout, const void* gate, const void* up, void* dgat
 int q4_rope(const void* in, const void* cos, const void* sin, void* out, int tokens, int heads, int D, int in_pitch,
             int table_rows, int backward, q4_stream_t stream);
 
+/* The rank-r products of a LoRA adapter around q4_gemm_fwd / q4_gemm_bwd (Linear4bitLt.forward,
+ * models.py:58-66, runs them as two nn.Linear calls and leaves the gradients to autograd; no single
+ * reference function corresponds).
+ *   q4_lora_project   out [M, 64] fp16 = scale * x [M, C] * w^T with w fp16 [r, C] (1 <= r <= 64, C % 32 == 0),
+ *                     columns r..63 written as zeros: the `lora_u` / `lora_v` operand of the GEMM entry points
+ *                     (forward: x and lora_A; backward: dy and lora_B^T)
+ *   q4_lora_grads     d_a [r, K] fp32 = v[:, :r]^T x and d_b [N, r] fp32 = dy^T u[:, :r] in one launch
+ *                     (v, u fp16 [M, 64] as produced above; x fp16 [M, K]; dy fp16 [M, N]; K, N % 32 == 0);
+ *                     either output may be NULL, its operands are then not read */
+int q4_lora_project(const void* x, const void* w, void* out, int M, int C, int r, float scale, q4_stream_t stream);
+int q4_lora_grads(const void* v, const void* x, float* d_a, int K, const void* dy, const void* u, float* d_b, int N,
+                  int M, int r, q4_stream_t stream);
+
+/* One optimiser step over flat fp32 buffers of n elements (every trainable LoRA factor a view of `param`,
+ * every gradient a view of `grad`): torch.optim.AdamW's update with torch.amp.GradScaler's loss-scale
+ * handling, which is what the reference's trainer runs (finetune.py:150-170: optim="adamw_torch", fp16=True).
+ * `state` is four device floats: steps taken, loss scale, steps since the scale changed, non-finite flag
+ * (zero before the first call except for the scale).  Three launches on `stream`: (1) state[3] = 1 if any
+ * gradient is non-finite; (2) unless it is, param/exp_avg/exp_avg_sq advance by one AdamW step on
+ * grad / (state[1] * grad_div)  (grad_div: the number of ranks whose gradients were summed into `grad`);
+ * (3) a skipped step multiplies the scale by `backoff`, `growth_interval` clean steps in a row multiply it by
+ * `growth` (growth_interval 0: the scale is static), the step count advances and the flag is cleared.
+ * Nothing returns to the host, so the call can be captured in a CUDA graph. */
+int q4_adamw_flat(float* param, const float* grad, float* exp_avg, float* exp_avg_sq, size_t n, float lr, float beta1,
+                  float beta2, float eps, float weight_decay, float grad_div, float* state, float growth, float backoff,
+                  int growth_interval, q4_stream_t stream);
+
 /* Copies the device status word to *out (synchronises the device): 0, or 0xDEAD0001 if a bounded
  * wait inside a q4_gemm_* kernel expired (its output is then invalid). */
 int q4_device_status(unsigned* out);
