@@ -22,14 +22,15 @@ def test_matches_torch_adamw_under_gradscaler(dynamic):
     flat = fs.FlatGrads(ours)
     opt = fs.FlatAdamW(ours, flat, lr=3e-3, init_scale=1024.0, dynamic=dynamic, growth_interval=3)
     ropt = torch.optim.AdamW(ref, lr=3e-3)
-    scaler = torch.amp.GradScaler("cuda", init_scale=1024.0, growth_interval=3, enabled=True)
-    if not dynamic:
-        scaler = torch.amp.GradScaler("cuda", init_scale=1024.0, growth_factor=1.0, backoff_factor=1.0, growth_interval=3)
+    # a static scale is compared with a scaler that never gets to grow and sees no overflow
+    scaler = torch.amp.GradScaler("cuda", init_scale=1024.0, growth_interval=3 if dynamic else 10 ** 9)
+    scaler.scale(torch.zeros(1, device=DEV))                                   # creates its device-side state
+    bad_steps = (2, 6) if dynamic else ()
     g = torch.Generator(device=DEV).manual_seed(2)
     taken = 0
     for step in range(9):
         grads = [torch.randn(p.shape, generator=g, device=DEV) for p in ref]
-        if step in (2, 6):
+        if step in bad_steps:
             grads[1][5, 3] = float("inf") if step == 2 else float("nan")       # a step the scaler must skip
         scale = float(scaler.get_scale())
         assert opt.loss_scale == scale
@@ -40,7 +41,7 @@ def test_matches_torch_adamw_under_gradscaler(dynamic):
         opt.step()
         scaler.step(ropt)
         scaler.update()
-        taken += step not in (2, 6)
+        taken += step not in bad_steps
         assert opt.steps_taken == taken
         for p, q in zip(ours, ref):
             assert torch.allclose(p, q, rtol=2e-6, atol=2e-7), (step, float((p - q).abs().max()))
