@@ -266,21 +266,6 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
       const WorkItem wi = work_item<SPLIT>(p, wr, item, n_pairs, T);
       const int ncon = wi.ke - wi.kb, nst = ncon + (wi.lora ? 1 : 0);    // stages of this item: j = 0 .. nst-1, contraction stage kb + j
       const int out0 = (wi.tile / m_tiles) * G2_TILE_N + 128 * (int)rank;   // first output column (n forward, k backward)
-      if (!TRANSPOSE && out0 != tab_out0) {
-        // tables for the CTA's 128 columns: scale and rn(s*(z+1)) of every group
-        if (tab_out0 >= 0) named_bar_sync(1, GM_DEQ_THREADS * GM_DEQ_GROUPS);      // all readers of the old tables are done
-        for (int i = (dw << 5) | lane; i < p.G * 16; i += GM_DEQ_THREADS * GM_DEQ_GROUPS) {
-          const int g = i >> 4, c8 = i & 15;
-          const uint4 s = __ldg(reinterpret_cast<const uint4*>(p.scales + (size_t)g * N + out0 + 8 * c8));
-          const uint32_t zw = __ldg(p.qzeros + (size_t)g * (N >> 3) + ((out0 + 8 * c8) >> 3));
-          const uint4 z = zero_terms(s, zw);
-          *reinterpret_cast<uint4*>(tab + g * 512 + 16 * c8) = s;
-          *reinterpret_cast<uint4*>(tab + g * 512 + 256 + 16 * c8) = z;
-        }
-        named_bar_sync(1, GM_DEQ_THREADS * GM_DEQ_GROUPS);
-        if (tl == 0 && dw == 0 && lane == 0) gm_mark_ns(p.trace, 104);
-        tab_out0 = out0;
-      }
       // packed words of the stage: rows (k0/8 + r), columns ncol0 .. ncol0+7
       auto word_ptr = [&](int it) -> const uint32_t* {
         const int prow = TRANSPOSE ? (out0 >> 3) + r : it * (GM_TILE_C >> 3) + r;
@@ -370,7 +355,22 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         if (tr_on) gm_mark(p.trace, 66 + 3 * (j >> 1));
         st += GM_DEQ_GROUPS;
       };
-      prefetch(j0, R0);
+      prefetch(j0, R0);                              // in flight while the tables below are built
+      if (!TRANSPOSE && out0 != tab_out0) {
+        // tables for the CTA's 128 columns: scale and rn(s*(z+1)) of every group
+        if (tab_out0 >= 0) named_bar_sync(1, GM_DEQ_THREADS * GM_DEQ_GROUPS);      // all readers of the old tables are done
+        for (int i = (dw << 5) | lane; i < p.G * 16; i += GM_DEQ_THREADS * GM_DEQ_GROUPS) {
+          const int g = i >> 4, c8 = i & 15;
+          const uint4 s = __ldg(reinterpret_cast<const uint4*>(p.scales + (size_t)g * N + out0 + 8 * c8));
+          const uint32_t zw = __ldg(p.qzeros + (size_t)g * (N >> 3) + ((out0 + 8 * c8) >> 3));
+          const uint4 z = zero_terms(s, zw);
+          *reinterpret_cast<uint4*>(tab + g * 512 + 16 * c8) = s;
+          *reinterpret_cast<uint4*>(tab + g * 512 + 256 + 16 * c8) = z;
+        }
+        named_bar_sync(1, GM_DEQ_THREADS * GM_DEQ_GROUPS);
+        if (tl == 0 && dw == 0 && lane == 0) gm_mark_ns(p.trace, 104);
+        tab_out0 = out0;
+      }
       for (int j = j0; j < nst; j += 2 * GM_DEQ_GROUPS) {
         prefetch(j + GM_DEQ_GROUPS, R1);
         task(j, R0);
@@ -419,7 +419,7 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         }
       };
       if (threadIdx.x == 384 && tl < 8) gm_mark(p.trace, 200 + 3 * tl);
-      if (lane == 0) wait_bar_idle(&acc_full[acc], acc_use & 1, abort_flag, 1000, &polls);
+      if (lane == 0) wait_bar_idle(&acc_full[acc], acc_use & 1, abort_flag, 250, &polls);
       __syncwarp();
       tc_fence_after();
       if (threadIdx.x == 384 && tl < 8) gm_mark(p.trace, 201 + 3 * tl);
