@@ -1,13 +1,17 @@
 // Decode product  y[M,N] (+)= x[M,K] * W  for 1 <= M <= 16 straight from the packed int4 layer.
 //
 // Per weight 0.5 B of qweight plus 1/64 B of scales and 1/256 B of zero points cross HBM at groupsize
-// 128; x and y are noise.  Four kernels share the file; q4_gemv at its end picks one per call:
+// 128; x and y are noise.  Five kernels share the file; q4_gemv at its end picks one per call:
 //   * gemv_ws_kernel     one row, groups of 128, K in whole 256-row units: warp-specialised (a copy-issuing
 //                        warp, consumer warps, a helper for the exchange between CTAs), int8 tensor-core
 //                        MMAs on the packed words split into bytes, x as 16-bit block fixed point.
-//   * gemv_fast_kernel   1..8 rows (9..16: two launches), groups of 128 or of a multiple of 256 rows and the
-//                        first layer format: every warp streams its own 4 KiB units with TMA, fp16 MMAs
-//                        with the exponent trick, x re-laid per unit or once per CTA.
+//   * gemv_rows_kernel   2..16 rows on the same layers, one pass over the weights: the same int8 MMAs, x
+//                        converted to block fixed point once per call by x_convert_kernel (an 8-row and a
+//                        16-row form).
+//   * gemv_fast_kernel   1..8 rows (9..16: two launches) where the two above do not apply - groups of a
+//                        multiple of 256 rows, the first layer format, layers with few column tiles: every
+//                        warp streams its own 4 KiB units with TMA, fp16 MMAs with the exponent trick, x
+//                        re-laid per unit or once per CTA.
 //   * gemv_stream_kernel every other group size with sequential groups: the same streams, group test per step.
 //   * gemv_act_kernel    act-order (the group of every row from g_idx): scale and zero point per element
 //                        from shared-memory tables.
@@ -1370,27 +1374,36 @@ gemv_ws_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__
   }
 }
 
-// ---- 2..8 rows, groups of 128: int8 MMAs fed by a conversion pass ------------------------------------------
+// ---- 2..16 rows, groups of 128: int8 MMAs fed by a conversion pass -----------------------------------------
 // The lean kernel re-lays x out per 4 KiB unit, which with eight rows costs twice the instructions of the
 // product itself.  Here x is converted once per call, by a small kernel of its own, into the 16-bit block
 // fixed point of the one-row kernel above (digits in MMA order, 16 bytes per 8 k and row, the rows of a block
-// 144 bytes apart so that the eight rows a quarter-warp reads fall on different banks), and the product kernel
-// brings the digits of 2048 k (one round of its eight consumer warps) with one bulk copy per round.  Every
-// CTA takes whole column tiles; within a tile unit r*8 + w goes to warp w in round r, so the warps of a round
-// share the round's slice of x.  Zero points leave as integers: (sum of q x_int) - (z + 1) (sum of x_int).
-constexpr int RW_W = 8, RW_S = 2, RW_MR = 8;
-constexpr int RW_XPITCH = (RW_MR + 1) * 16;                  // bytes per block of 8 k: 8 rows + 16 bytes of padding
-constexpr int RW_CHUNK_BLOCKS = RW_W * 32;                   // blocks of one round
-constexpr int RW_CHUNK_BYTES = RW_CHUNK_BLOCKS * RW_XPITCH;  // 36864
+// 16 bytes apart and the blocks an odd number of 16-byte units apart, so that the eight rows and four blocks a
+// quarter-warp reads fall on different banks), and the product kernel brings the digits of a round of its eight
+// consumer warps with bulk copies: one chunk of 2048 k per round for up to 8 rows, two chunks of 1024 k (one
+// per four warps, three slots in shared memory) for 9..16 rows, whose digits are twice as many.  Every CTA
+// takes whole column tiles; within a tile unit r*8 + w goes to warp w in round r, so the warps of a round
+// share the round's slice of x.  With 16 rows every weight fragment feeds two MMAs per digit (rows 0..7 and
+// 8..15).  Zero points leave as integers: (sum of q x_int) - (z + 1) (sum of x_int).
+constexpr int RW_W = 8, RW_S = 2;
+template <int MR> struct RwCfg {
+  static constexpr int PITCH = (MR + 1) * 16;           // bytes per block of 8 k: MR rows + 16 bytes of padding
+  static constexpr int CH = MR / 8;                     // chunks of digits per round
+  static constexpr int WC = RW_W / CH;                  // consumer warps that share a chunk
+  static constexpr int XS = MR == 8 ? 2 : 3;            // chunk slots in shared memory
+  static constexpr int CHUNK_BLOCKS = WC * 32;
+  static constexpr int CHUNK_BYTES = CHUNK_BLOCKS * PITCH;   // 36864 (8 rows), 34816 (16 rows)
+};
 
-// x fp16 [M, K] -> digits [blocks][9][16 bytes] and per (group, row) the pair (2^(E-14), sum of x_int as int bits)
+// x fp16 [M, K] -> digits [blocks][MR + 1][16 bytes] and per (group, row) the pair (2^(E-14), sum of x_int as int bits)
+template <int MR>
 __global__ void __launch_bounds__(256)
 x_convert_kernel(const __half* __restrict__ x, unsigned char* __restrict__ xq, uint2* __restrict__ xinfo, int M, int K, int n_blocks) {
   pdl_launch_dependents();
   pdl_wait();                                    // x belongs to the stream order
   const int lane = threadIdx.x & 31;
   const int idx = blockIdx.x * blockDim.x + threadIdx.x;      // row-major over (row, block): 16 lanes share a row's group
-  if (idx >= RW_MR * n_blocks) return;
+  if (idx >= MR * n_blocks) return;
   const int m = idx / n_blocks, blk = idx - m * n_blocks;
   const bool live = m < M && 8 * blk < K;
   const uint4 v = live ? __ldg(reinterpret_cast<const uint4*>(x + (size_t)m * K) + blk) : make_uint4(0u, 0u, 0u, 0u);
@@ -1411,12 +1424,12 @@ x_convert_kernel(const __half* __restrict__ x, unsigned char* __restrict__ xq, u
   const uint32_t x4 = __float_as_uint(fmaf(f45.x, to_int, magic)), x5 = __float_as_uint(fmaf(f45.y, to_int, magic));
   const uint32_t x6 = __float_as_uint(fmaf(f67.x, to_int, magic)), x7 = __float_as_uint(fmaf(f67.y, to_int, magic));
   const uint32_t e02 = prmt(x0, x2, 0x5140), e46 = prmt(x4, x6, 0x5140), o13 = prmt(x1, x3, 0x5140), o57 = prmt(x5, x7, 0x5140);
-  *reinterpret_cast<uint4*>(xq + ((size_t)blk * (RW_MR + 1) + m) * 16) =
+  *reinterpret_cast<uint4*>(xq + ((size_t)blk * (MR + 1) + m) * 16) =
       make_uint4(prmt(e02, e46, 0x7632), prmt(o13, o57, 0x7632), prmt(e02, e46, 0x5410), prmt(o13, o57, 0x5410));
   int xs = (int)(((x0 + x1) + (x2 + x3)) + ((x4 + x5) + (x6 + x7)) - 8u * 0x4B400000u);
 #pragma unroll
   for (int d = 8; d >= 1; d >>= 1) xs += __shfl_xor_sync(0xffffffffu, xs, d);
-  if ((lane & 15) == 0) xinfo[(size_t)(blk >> 4) * RW_MR + m] = make_uint2(__float_as_uint(from_int), (uint32_t)xs);
+  if ((lane & 15) == 0) xinfo[(size_t)(blk >> 4) * MR + m] = make_uint2(__float_as_uint(from_int), (uint32_t)xs);
 }
 
 struct RowsParams {
@@ -1424,21 +1437,21 @@ struct RowsParams {
   int upt, n_groups, tiles, n_blocks;             // units per tile, groups, column tiles, blocks of 8 k (padded to units)
   unsigned* status;
   const unsigned char* xq;                        // digits, see x_convert_kernel
-  const uint2* xinfo;                             // [groups][8]
+  const uint2* xinfo;                             // [groups][MR]
 };
 
-struct RwLayout { int stages, xring, xinfo, meta, meta_slot, meta_zp, red, bars, total; };
+struct RwLayout { int xring, xinfo, meta, meta_slot, meta_zp, red, bars, total; };
+template <int MR>
 __host__ __device__ inline RwLayout rw_layout(int G) {
   RwLayout l;
-  l.stages = 0;
   l.xring = RW_W * RW_S * GEMV_UNIT_BYTES;
-  l.xinfo = l.xring + 2 * RW_CHUNK_BYTES;
-  l.meta = (l.xinfo + G * RW_MR * 8 + 127) / 128 * 128;
+  l.xinfo = l.xring + RwCfg<MR>::XS * RwCfg<MR>::CHUNK_BYTES;
+  l.meta = (l.xinfo + G * MR * 8 + 127) / 128 * 128;
   l.meta_zp = (G * 64 + 127) / 128 * 128;
   l.meta_slot = l.meta_zp + (G * 16 + 127) / 128 * 128;
   l.red = l.meta + 2 * l.meta_slot;
-  l.bars = l.red + RW_W * RW_MR * GEMV_TN * 4;
-  l.total = l.bars + 8 * (2 * RW_W * RW_S + 9) + 16;
+  l.bars = l.red + RW_W * MR * GEMV_TN * 4;
+  l.total = l.bars + 8 * (2 * RW_W * RW_S + 11) + 16;
   return l;
 }
 
@@ -1448,15 +1461,17 @@ __device__ __forceinline__ void bulk_load(void* dst, const void* src, uint32_t b
                ::"r"(smem_u32(dst)), "l"(src), "r"(bytes), "r"(smem_u32(bar)) : "memory");
 }
 
+template <int MR>
 __global__ void __launch_bounds__((RW_W + 1) * 32, 1)
 gemv_rows_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant__ CUtensorMap smap,
                  const __grid_constant__ CUtensorMap zmap, const RowsParams rp) {
   extern __shared__ __align__(128) unsigned char smem_raw[];
   unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  constexpr int W = RW_W, S = RW_S, MR = RW_MR, CT = W * 32, ALL = (W + 1) * 32;
+  using C = RwCfg<MR>;
+  constexpr int W = RW_W, S = RW_S, CT = W * 32, RH = MR / 8;
   const GemvParams& p = rp.g;
   const int upt = rp.upt, G = rp.n_groups;
-  const RwLayout L = rw_layout(G);
+  const RwLayout L = rw_layout<MR>(G);
   unsigned char* xring = smem + L.xring;
   const uint2* xinfo_s = reinterpret_cast<const uint2*>(smem + L.xinfo);
   float* red = reinterpret_cast<float*>(smem + L.red);               // [W][MR][32]
@@ -1464,9 +1479,9 @@ gemv_rows_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
   uint64_t* empty = full + W * S;                                    // [W][S]
   uint64_t* mfull = empty + W * S;                                   // [2]
   uint64_t* mempty = mfull + 2;                                      // [2]
-  uint64_t* xfull = mempty + 2;                                      // [2] digits of a round have landed
-  uint64_t* xempty = xfull + 2;                                      // [2] every consumer is done with them
-  uint64_t* ifull = xempty + 2;                                      // [1] the (scale, sum) table has landed
+  uint64_t* xfull = mempty + 2;                                      // [3] the digits of a chunk have landed
+  uint64_t* xempty = xfull + 3;                                      // [3] the chunk's consumers are done with them
+  uint64_t* ifull = xempty + 3;                                      // [1] the (scale, sum) table has landed
   volatile int* flags = reinterpret_cast<volatile int*>(ifull + 1);
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
@@ -1477,14 +1492,14 @@ gemv_rows_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
   if (threadIdx.x < 2 * W * S) mbar_init(&full[threadIdx.x], 1);
   else if (threadIdx.x < 2 * W * S + 2) mbar_init(&full[threadIdx.x], 1);                 // mfull
   else if (threadIdx.x < 2 * W * S + 4) mbar_init(&full[threadIdx.x], W);                 // mempty
-  else if (threadIdx.x < 2 * W * S + 6) mbar_init(&full[threadIdx.x], 1);                 // xfull
-  else if (threadIdx.x < 2 * W * S + 8) mbar_init(&full[threadIdx.x], W);                 // xempty
-  else if (threadIdx.x == 2 * W * S + 8) mbar_init(ifull, 1);
-  if (threadIdx.x == 2 * W * S + 9) {
+  else if (threadIdx.x < 2 * W * S + 7) mbar_init(&full[threadIdx.x], 1);                 // xfull
+  else if (threadIdx.x < 2 * W * S + 10) mbar_init(&full[threadIdx.x], C::WC);            // xempty
+  else if (threadIdx.x == 2 * W * S + 10) mbar_init(ifull, 1);
+  if (threadIdx.x == 2 * W * S + 11) {
     flags[0] = 0;
     tma_prefetch_desc(&wmap); tma_prefetch_desc(&smap); tma_prefetch_desc(&zmap);
   }
-  if (threadIdx.x < 2 * W * S + 9) mbar_fence_init();
+  if (threadIdx.x < 2 * W * S + 11) mbar_fence_init();
   __syncthreads();
   pdl_launch_dependents();
   auto expired = [&]() { flags[0] = 1; atomicExch(rp.status, Q4_STATUS_WAIT_EXPIRED); };
@@ -1493,9 +1508,19 @@ gemv_rows_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
     // ---- issuer: lane w the units of consumer w, lane W the rounds' digits, lane W + 1 the tiles' metadata ----
     int n = 0;                                   // units issued for this lane's consumer
     int rc = 0;                                  // rounds issued (all tiles)
+    int xq_next = 0;                             // chunks of digits issued (lane W): chunk q = round q / CH of the CTA, part q % CH
     bool waited = false;
     const int total_rounds = (t1 - t0) * rounds;
     const int first_rounds = total_rounds < S ? total_rounds : S;   // rounds whose weights go out before the wait
+    // chunk q of the CTA: blocks [(q / CH % rounds) * W * 32 + (q % CH) * CHUNK_BLOCKS, + CHUNK_BLOCKS) of the digits
+    auto issue_chunk = [&](int q) {
+      const int slot = q % C::XS;
+      if (q >= C::XS && !mbar_wait_sleep_bounded(&xempty[slot], ((q / C::XS) & 1) ^ 1, flags[0] ? 4u : 200000u)) expired();
+      const int b0 = ((q / C::CH) % rounds) * (W * 32) + (q % C::CH) * C::CHUNK_BLOCKS;
+      const int blocks = min(C::CHUNK_BLOCKS, rp.n_blocks - b0);
+      mbar_arrive_expect_tx(&xfull[slot], blocks > 0 ? (uint32_t)blocks * C::PITCH : 0u);
+      if (blocks > 0) bulk_load(xring + slot * C::CHUNK_BYTES, rp.xq + (size_t)b0 * C::PITCH, (uint32_t)blocks * C::PITCH, &xfull[slot]);
+    };
     for (int tile = t0; tile < t1; ++tile) {
       const int seq = tile - t0, mslot = seq & 1;
       if (lane == W + 1) {
@@ -1521,20 +1546,10 @@ gemv_rows_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
           if (lane == W) {
             mbar_arrive_expect_tx(ifull, (uint32_t)G * MR * 8u);
             bulk_load(smem + L.xinfo, rp.xinfo, (uint32_t)G * MR * 8u, ifull);
-            for (int q = 0; q <= rc; ++q) {      // the rounds passed so far; round q of the CTA is round q % rounds of its tile
-              const int rq = q % rounds;
-              const int blocks = min(RW_CHUNK_BLOCKS, rp.n_blocks - rq * RW_CHUNK_BLOCKS);
-              mbar_arrive_expect_tx(&xfull[q & 1], (uint32_t)blocks * RW_XPITCH);
-              bulk_load(xring + (q & 1) * RW_CHUNK_BYTES, rp.xq + (size_t)rq * RW_CHUNK_BYTES, (uint32_t)blocks * RW_XPITCH, &xfull[q & 1]);
-            }
           }
-        } else if (waited && lane == W) {
-          const int xs = rc & 1;
-          if (rc >= 2 && !mbar_wait_sleep_bounded(&xempty[xs], ((rc >> 1) & 1) ^ 1, flags[0] ? 4u : 200000u)) expired();
-          const int blocks = min(RW_CHUNK_BLOCKS, rp.n_blocks - r * RW_CHUNK_BLOCKS);
-          mbar_arrive_expect_tx(&xfull[xs], (uint32_t)blocks * RW_XPITCH);
-          bulk_load(xring + xs * RW_CHUNK_BYTES, rp.xq + (size_t)r * RW_CHUNK_BYTES, (uint32_t)blocks * RW_XPITCH, &xfull[xs]);
         }
+        if (waited && lane == W)                 // the digits of every round passed so far
+          for (; xq_next < (rc + 1) * C::CH; ++xq_next) issue_chunk(xq_next);
         __syncwarp();
       }
     }
@@ -1547,13 +1562,16 @@ gemv_rows_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
   const int g = lane >> 2, t = lane & 3;
   const uint32_t woff0 = 128u * (2 * t) + 16u * (g ^ (2 * t)), woff1 = 128u * (2 * t + 1) + 16u * (g ^ (2 * t + 1));
   const unsigned char* my_stages = smem + (size_t)warp * S * GEMV_UNIT_BYTES;
-  float yacc[2][4];                              // [column pair][fragment]: columns 4g + 2 cp + (i >> 1), rows 2t + (i & 1)
+  float yacc[RH][2][4];                          // [row half][column pair][fragment]: columns 4g + 2 cp + (i >> 1), rows 8 rh + 2t + (i & 1)
 #pragma unroll
-  for (int cp = 0; cp < 2; ++cp)
+  for (int rh = 0; rh < RH; ++rh)
 #pragma unroll
-    for (int i = 0; i < 4; ++i) yacc[cp][i] = 0.f;
+    for (int cp = 0; cp < 2; ++cp)
+#pragma unroll
+      for (int i = 0; i < 4; ++i) yacc[rh][cp][i] = 0.f;
   const uint32_t lim0 = 20000000u;
   if (!mbar_spin_bounded(ifull, 0, lim0)) expired();
+  const int part = warp / C::WC, wc = warp % C::WC;
 
   int n = 0, rc = 0;
   for (int tile = t0; tile < t1; ++tile) {
@@ -1561,59 +1579,64 @@ gemv_rows_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
     const unsigned char* meta = smem + L.meta + mslot * L.meta_slot;
     if (!mbar_spin_bounded(&mfull[mslot], (seq >> 1) & 1, flags[0] ? 64u : lim0)) expired();
     for (int r = 0; r < rounds; ++r, ++rc) {
-      const int xs = rc & 1, ux = r * W + warp;
-      if (!mbar_spin_bounded(&xfull[xs], (rc >> 1) & 1, flags[0] ? 64u : lim0)) expired();
+      const int q = rc * C::CH + part, xs = q % C::XS, ux = r * W + warp;
+      if (!mbar_spin_bounded(&xfull[xs], (q / C::XS) & 1, flags[0] ? 64u : lim0)) expired();
       if (ux < upt) {
         const int st = n % S;
         if (!mbar_spin_bounded(&full[warp * S + st], (n / S) & 1, flags[0] ? 64u : lim0)) expired();
         const unsigned char* wst = my_stages + (size_t)st * GEMV_UNIT_BYTES;
-        // digits of this warp's unit: block b of the round at b * 144, row g at + 16 g
-        const unsigned char* xq = xring + xs * RW_CHUNK_BYTES + (size_t)(warp * 32 + 2 * t) * RW_XPITCH + 16 * g;
+        // digits of this warp's unit: block b of the chunk at b * PITCH, row m at + 16 m
+        const unsigned char* xq = xring + xs * C::CHUNK_BYTES + (size_t)(wc * 32 + 2 * t) * C::PITCH + 16 * g;
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-          uint4 wv[4], xv[4];
+          int chi[RH][2][4], clo[RH][2][4];
 #pragma unroll
           for (int uu = 0; uu < 4; ++uu) {
-            wv[uu] = *reinterpret_cast<const uint4*>(wst + ((uu & 1) ? woff1 : woff0) + 1024 * (2 * h + (uu >> 1)));
-            xv[uu] = *reinterpret_cast<const uint4*>(xq + (size_t)(8 * (2 * h + (uu >> 1)) + (uu & 1)) * RW_XPITCH);
-          }
-          int chi[2][4], clo[2][4];
+            const uint4 wv = *reinterpret_cast<const uint4*>(wst + ((uu & 1) ? woff1 : woff0) + 1024 * (2 * h + (uu >> 1)));
+            uint4 xv[RH];
 #pragma unroll
-          for (int uu = 0; uu < 4; ++uu) {
-            const uint32_t w[4] = {wv[uu].x, wv[uu].y, wv[uu].z, wv[uu].w};
+            for (int rh = 0; rh < RH; ++rh)
+              xv[rh] = *reinterpret_cast<const uint4*>(xq + (size_t)(8 * (2 * h + (uu >> 1)) + (uu & 1)) * C::PITCH + 128 * rh);
+            const uint32_t w[4] = {wv.x, wv.y, wv.z, wv.w};
             uint32_t ev[4], od[4];
 #pragma unroll
-            for (int q = 0; q < 4; ++q) { ev[q] = w[q] & 0x0F0F0F0Fu; od[q] = (w[q] >> 4) & 0x0F0F0F0Fu; }
-            if (uu == 0) {
-              imma_u8s8_first(chi[0], ev[0], ev[1], od[0], od[1], xv[uu].x, xv[uu].y);
-              imma_u8u8_first(clo[0], ev[0], ev[1], od[0], od[1], xv[uu].z, xv[uu].w);
-              imma_u8s8_first(chi[1], ev[2], ev[3], od[2], od[3], xv[uu].x, xv[uu].y);
-              imma_u8u8_first(clo[1], ev[2], ev[3], od[2], od[3], xv[uu].z, xv[uu].w);
-            } else {
-              imma_u8s8(chi[0], ev[0], ev[1], od[0], od[1], xv[uu].x, xv[uu].y);
-              imma_u8u8(clo[0], ev[0], ev[1], od[0], od[1], xv[uu].z, xv[uu].w);
-              imma_u8s8(chi[1], ev[2], ev[3], od[2], od[3], xv[uu].x, xv[uu].y);
-              imma_u8u8(clo[1], ev[2], ev[3], od[2], od[3], xv[uu].z, xv[uu].w);
+            for (int q4 = 0; q4 < 4; ++q4) { ev[q4] = w[q4] & 0x0F0F0F0Fu; od[q4] = (w[q4] >> 4) & 0x0F0F0F0Fu; }
+#pragma unroll
+            for (int rh = 0; rh < RH; ++rh) {
+              if (uu == 0) {
+                imma_u8s8_first(chi[rh][0], ev[0], ev[1], od[0], od[1], xv[rh].x, xv[rh].y);
+                imma_u8u8_first(clo[rh][0], ev[0], ev[1], od[0], od[1], xv[rh].z, xv[rh].w);
+                imma_u8s8_first(chi[rh][1], ev[2], ev[3], od[2], od[3], xv[rh].x, xv[rh].y);
+                imma_u8u8_first(clo[rh][1], ev[2], ev[3], od[2], od[3], xv[rh].z, xv[rh].w);
+              } else {
+                imma_u8s8(chi[rh][0], ev[0], ev[1], od[0], od[1], xv[rh].x, xv[rh].y);
+                imma_u8u8(clo[rh][0], ev[0], ev[1], od[0], od[1], xv[rh].z, xv[rh].w);
+                imma_u8s8(chi[rh][1], ev[2], ev[3], od[2], od[3], xv[rh].x, xv[rh].y);
+                imma_u8u8(clo[rh][1], ev[2], ev[3], od[2], od[3], xv[rh].z, xv[rh].w);
+              }
             }
           }
           // close the group: integer sums minus (z + 1) * sum of x_int, times scale and the row's 2^(E-14)
           const int grp = 2 * ux + h;
-          const uint4 inf = *reinterpret_cast<const uint4*>(xinfo_s + (size_t)grp * MR + 2 * t);    // rows 2t, 2t + 1
-          const float xsc[2] = {__uint_as_float(inf.x), __uint_as_float(inf.z)};
-          const int xsum[2] = {(int)inf.y, (int)inf.w};
           const uint2 sc = *reinterpret_cast<const uint2*>(meta + grp * 64 + 8 * g);
           const float2 s01 = __half22float2(as_h2(sc.x)), s23 = __half22float2(as_h2(sc.y));
           const float s[4] = {s01.x, s01.y, s23.x, s23.y};
           const uint32_t zw = *reinterpret_cast<const uint32_t*>(meta + L.meta_zp + grp * 16 + 4 * (g >> 1)) >> (16 * (g & 1));
 #pragma unroll
-          for (int cp = 0; cp < 2; ++cp)
+          for (int rh = 0; rh < RH; ++rh) {
+            const uint4 inf = *reinterpret_cast<const uint4*>(xinfo_s + (size_t)grp * MR + 8 * rh + 2 * t);    // rows 8 rh + 2t, + 1
+            const float xsc[2] = {__uint_as_float(inf.x), __uint_as_float(inf.z)};
+            const int xsum[2] = {(int)inf.y, (int)inf.w};
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              const int col = 2 * cp + (i >> 1), row = i & 1;
-              const int z1 = (int)((zw >> (4 * col)) & 0xFu) + 1;
-              const int v = chi[cp][i] * 256 + clo[cp][i] - z1 * xsum[row];
-              yacc[cp][i] = fmaf(s[col] * xsc[row], (float)v, yacc[cp][i]);
-            }
+            for (int cp = 0; cp < 2; ++cp)
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                const int col = 2 * cp + (i >> 1), row = i & 1;
+                const int z1 = (int)((zw >> (4 * col)) & 0xFu) + 1;
+                const int v = chi[rh][cp][i] * 256 + clo[rh][cp][i] - z1 * xsum[row];
+                yacc[rh][cp][i] = fmaf(s[col] * xsc[row], (float)v, yacc[rh][cp][i]);
+              }
+          }
         }
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
         __syncwarp();
@@ -1625,17 +1648,19 @@ gemv_rows_kernel(const __grid_constant__ CUtensorMap wmap, const __grid_constant
       if (lane == 0) mbar_arrive(&xempty[xs]);
     }
     if (lane == 0) mbar_arrive(&mempty[mslot]);
-    // the tile's sums: every warp leaves its [8 rows][32 columns], the last warp adds them in warp order
+    // the tile's sums: every warp leaves its [MR rows][32 columns], the last warp adds them in warp order
     const bool reducer = warp == W - 1;
     if (!reducer && seq >= 1) named_bar_sync(2, CT);
     float* mine = red + warp * MR * GEMV_TN;
 #pragma unroll
-    for (int cp = 0; cp < 2; ++cp)
+    for (int rh = 0; rh < RH; ++rh)
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        mine[(2 * t + (i & 1)) * GEMV_TN + 4 * g + 2 * cp + (i >> 1)] = yacc[cp][i];
-        yacc[cp][i] = 0.f;
-      }
+      for (int cp = 0; cp < 2; ++cp)
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          mine[(8 * rh + 2 * t + (i & 1)) * GEMV_TN + 4 * g + 2 * cp + (i >> 1)] = yacc[rh][cp][i];
+          yacc[rh][cp][i] = 0.f;
+        }
     if (!reducer) {
       __threadfence_block();
       named_bar_arrive(1, CT);
@@ -1961,13 +1986,15 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
     return fail(Q4_E_SHAPE, "gemv: N=%d has more column tiles than the workspace head holds", N);
   if (int e = check_device()) return e;
 
-  // 2..8 rows, groups of 128, whole 256-row units, enough column tiles to give every CTA whole ones: the
-  // int8-MMA kernel fed by the conversion pass (9..16 rows: twice, below)
-  if (M >= 2 && M <= 8 && !act && !v1 && groupsize == 128 && K % 256 == 0 && G == K / 128 && G <= 256 && !(g_gemv_variant & 16) &&
+  // 2..16 rows, groups of 128, whole 256-row units, enough column tiles to give every CTA whole ones: the
+  // int8-MMA kernel fed by the conversion pass, in its 8-row or its 16-row form
+  if (M >= 2 && !act && !v1 && groupsize == 128 && K % 256 == 0 && G == K / 128 && G <= 256 && !(g_gemv_variant & 16) &&
       N / GEMV_TN >= 32) {
+    const bool wide = M > 8;
+    const int MR = wide ? 16 : 8, pitch = (MR + 1) * 16;
     const int upt = K / 256, n_blocks = upt * 32;
-    const size_t xq_bytes = (size_t)n_blocks * RW_XPITCH, info_bytes = (size_t)G * RW_MR * 8;
-    const size_t smem = 1024 + (size_t)rw_layout(G).total;
+    const size_t xq_bytes = (size_t)n_blocks * pitch, info_bytes = (size_t)G * MR * 8;
+    const size_t smem = 1024 + (size_t)(wide ? rw_layout<16>(G).total : rw_layout<8>(G).total);
     if (GEMV_WS_HEAD + xq_bytes + 256 + info_bytes <= workspace_bytes && smem <= GF_SMEM_LIMIT) {
       cudaStream_t st = (cudaStream_t)stream;
       unsigned char* xq = (unsigned char*)workspace + GEMV_WS_HEAD;
@@ -1993,7 +2020,9 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
       int dev = 0;
       cudaGetDevice(&dev);
       if (dev < 0 || dev >= 64 || !attr_done[dev].load(std::memory_order_acquire)) {
-        if (int e = check_cuda(cudaFuncSetAttribute(gemv_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GF_SMEM_LIMIT),
+        if (int e = check_cuda(cudaFuncSetAttribute(gemv_rows_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GF_SMEM_LIMIT),
+                               "gemv smem attribute")) return e;
+        if (int e = check_cuda(cudaFuncSetAttribute(gemv_rows_kernel<16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)GF_SMEM_LIMIT),
                                "gemv smem attribute")) return e;
         if (dev >= 0 && dev < 64) attr_done[dev].store(true, std::memory_order_release);
       }
@@ -2001,13 +2030,16 @@ extern "C" int q4_gemv(const void* x, const int32_t* qweight, void* y, const voi
       at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
       at[0].val.programmaticStreamSerializationAllowed = 1;
       cudaLaunchConfig_t c1 = {};
-      c1.gridDim = dim3((RW_MR * n_blocks + 255) / 256); c1.blockDim = dim3(256); c1.stream = st; c1.attrs = at; c1.numAttrs = 1;
-      if (int e = check_cuda(cudaLaunchKernelEx(&c1, x_convert_kernel, (const __half*)x, xq, xinfo, M, K, n_blocks), "gemv conversion launch")) return e;
+      c1.gridDim = dim3((MR * n_blocks + 255) / 256); c1.blockDim = dim3(256); c1.stream = st; c1.attrs = at; c1.numAttrs = 1;
+      if (int e = check_cuda(wide ? cudaLaunchKernelEx(&c1, x_convert_kernel<16>, (const __half*)x, xq, xinfo, M, K, n_blocks)
+                                  : cudaLaunchKernelEx(&c1, x_convert_kernel<8>, (const __half*)x, xq, xinfo, M, K, n_blocks),
+                             "gemv conversion launch")) return e;
       int grid = sm_count();
       if (grid > rp.tiles) grid = rp.tiles;
       cudaLaunchConfig_t c2 = {};
       c2.gridDim = dim3(grid); c2.blockDim = dim3((RW_W + 1) * 32); c2.dynamicSmemBytes = smem; c2.stream = st; c2.attrs = at; c2.numAttrs = 1;
-      return check_cuda(cudaLaunchKernelEx(&c2, gemv_rows_kernel, wsw, sm2, zm2, rp), "gemv launch");
+      return check_cuda(wide ? cudaLaunchKernelEx(&c2, gemv_rows_kernel<16>, wsw, sm2, zm2, rp)
+                             : cudaLaunchKernelEx(&c2, gemv_rows_kernel<8>, wsw, sm2, zm2, rp), "gemv launch");
     }
   }
 

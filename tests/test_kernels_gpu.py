@@ -314,10 +314,10 @@ def test_gemv_x_per_unit_and_per_cta_agree(K, N, M):
     assert quant_cuda.device_status() == 0
 
 
-@pytest.mark.parametrize("M", [2, 5, 8, 11, 16])
+@pytest.mark.parametrize("M", [2, 5, 8, 9, 11, 16])
 @pytest.mark.parametrize("K,N", [(4096, 4096), (11008, 4096), (4096, 11008), (2048, 1024), (512, 8192)])
 def test_gemv_rows_kernel(K, N, M):
-    """2..16 rows on the int8-MMA kernel fed by the conversion pass (9..16 rows: two launches), fp16 and fp32
+    """2..16 rows on the int8-MMA kernel fed by the conversion pass (its 8-row and its 16-row form), fp16 and fp32
     outputs, accumulate and bias; twice, since the digits of x live in the workspace between the two kernels."""
     layer = synth.make_layer(K, N, 128, False, seed=K + N + M)
     x = synth.make_acts(M, K, seed=M)
