@@ -429,6 +429,25 @@ def run_finetune(args, rank, world, local_rank):
            "model_tflops_per_s": round(tps * flops_per_token / 1e12, 1), "loss_first_last": [round(losses[0], 4), round(losses[-1], 4)], "launch": "cuda_graph" if graphed else "eager",
            "elementwise": "stock transformers modules" if args.finetune_stock_elementwise else "fused RMSNorm / SwiGLU / rotary kernels",
            "h2d_bytes_per_step": B * T * 8, "d2h_bytes_per_step": 4}
+    if args.finetune_profile and local_rank == 0:
+        # device time per kernel of ONE eager step (torch.profiler; outside the timed region, after it)
+        import collections
+        from torch.profiler import ProfilerActivity, profile
+        ids = ids_host[0].to(dev)
+        ft._eager_step(ids)
+        torch.cuda.synchronize(dev)
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            ft._eager_step(ids)
+            torch.cuda.synchronize(dev)
+        agg = collections.defaultdict(lambda: [0.0, 0])
+        for e in prof.events():
+            if e.device_type == torch.autograd.DeviceType.CUDA:
+                agg[e.name][0] += e.device_time
+                agg[e.name][1] += 1
+        total = sum(v[0] for v in agg.values())
+        out["kernels"] = {"sum_ms": round(total / 1e3, 2), "launches": sum(v[1] for v in agg.values()),
+                          "top": [[name[:96], c, round(t / 1e3, 3), round(100 * t / total, 1)]
+                                  for name, (t, c) in sorted(agg.items(), key=lambda kv: -kv[1][0])[:24]]}
     del ft, model
     torch.cuda.empty_cache()
     return out
@@ -474,8 +493,9 @@ def run_gemm(args, local_rank, reference_only=False):
     cases = [(2048, 5120, 5120, True), (2048, 5120, 13824, True), (2048, 13824, 5120, True),
              (1024, 4096, 4096, False), (1024, 4096, 11008, False), (1024, 11008, 4096, False)]
     if getattr(args, "gemm_shape", ""):
-        k_, n_ = (int(v) for v in args.gemm_shape.lower().split("x"))
-        cases = [(2048, k_, n_, True)]
+        dims = [int(v) for v in args.gemm_shape.lower().split("x")]
+        # KxN: the act-order M=2048 case of that layer; MxKxN: that many rows with sequential groups (the finetune shapes)
+        cases = [(2048, dims[0], dims[1], True)] if len(dims) == 2 else [(dims[0], dims[1], dims[2], False)]
     for M, K, N, act in cases:
         G = K // 128
         qw = torch.randint(-2 ** 31, 2 ** 31 - 1, (K // 8, N), device=dev, dtype=torch.int64, generator=gen).to(torch.int32)
@@ -619,7 +639,8 @@ def main():
     ap.add_argument("--copies", type=int, default=8, help="distinct copies of each layer shape per GPU")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-gemm", action="store_true", help="skip the M=2048 fused GEMM leg")
-    ap.add_argument("--gemm-shape", default="", help="restrict the GEMM leg to one KxN shape, e.g. 5120x13824 (for profiler captures)")
+    ap.add_argument("--gemm-shape", default="", help="restrict the GEMM leg to one shape: KxN (M=2048, act-order), e.g. 5120x13824, or MxKxN (sequential groups), "
+                         "e.g. 1024x4096x4096 (for profiler captures)")
     ap.add_argument("--load-seconds", type=float, default=0.4,
                     help="keep replaying the decode graph for at least this long before the timed region, so that the clock "
                          "sampler sees the GPU under this load (0 for profiler captures: warm-up replays only)")
@@ -630,6 +651,8 @@ def main():
                     help="7b: LLaMA-7B, r=8 LoRA on q/v, 4 x 256 tokens, fp16 (C3); 70b: LLaMA-2-70B GQA, act-order, r=16 LoRA on "
                          "all seven projections, 1 x 2048 tokens, bf16 autocast (C4; 35 GB of int4 weights per GPU)")
     ap.add_argument("--finetune-eager", action="store_true", help="do not capture the finetune step as a CUDA graph")
+    ap.add_argument("--finetune-profile", action="store_true",
+                    help="after the timed steps run one eager step under torch.profiler and add its per-kernel device times as finetune.kernels")
     ap.add_argument("--finetune-stock-elementwise", action="store_true",
                     help="leave RMSNorm, SwiGLU and the rotary embedding to the stock transformers modules")
     ap.add_argument("--finetune-layers", type=int, default=0, help="override the number of decoder layers (0 = 32)")
