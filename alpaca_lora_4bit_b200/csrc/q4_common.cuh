@@ -34,6 +34,12 @@ __device__ __forceinline__ uint32_t prmt(uint32_t a, uint32_t b, uint32_t sel) {
 __device__ __forceinline__ __half2 as_h2(uint32_t v) { return *reinterpret_cast<__half2*>(&v); }
 __device__ __forceinline__ uint32_t as_u32(__half2 v) { return *reinterpret_cast<uint32_t*>(&v); }
 
+// SiLU as every kernel of the library computes it (the fused gate_up epilogue and the element-wise SwiGLU kernel
+// must agree to the bit).
+// Approximate reciprocal and exponential (2 ulp each): the result is rounded to fp16 right away, and an IEEE
+// division costs more instructions than the rest of an epilogue's work per element.
+__device__ __forceinline__ float silu_f(float v) { return __fdividef(v, 1.f + __expf(-v)); }
+
 // Streaming 128-bit load that does not allocate in L1 (weights are read exactly once).
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
   uint4 v;

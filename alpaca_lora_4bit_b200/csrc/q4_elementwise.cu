@@ -107,7 +107,6 @@ rmsnorm_bwd_kernel(const __half* __restrict__ dy, const __half* __restrict__ x, 
 
 // ---- SwiGLU: out = half(silu(gate)) * up ------------------------------------------------------------------
 // gate and up are rows of pitch `pitch` halves (two tensors, or the two halves of one fused gate_up output).
-__device__ __forceinline__ float silu_f(float v) { return v / (1.f + __expf(-v)); }
 
 __global__ void swiglu_fwd_kernel(const __half* __restrict__ gate, const __half* __restrict__ up, __half* __restrict__ out,
                                   int rows, int I, int pitch) {

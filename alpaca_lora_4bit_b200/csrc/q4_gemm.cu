@@ -352,7 +352,7 @@ static long long gemm2_estimate(int M, int nout, int T, int P, int mh, bool ws_o
 static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, void* out, const void* scales,
                        const int32_t* qzeros, const int32_t* g_idx, const void* bias, const void* lora_u,
                        const void* lora_w, int lora_r, int M, int K, int N, int G, void* workspace, size_t workspace_bytes,
-                       q4_stream_t stream) {
+                       q4_stream_t stream, bool swiglu = false, const void* zp_cached = nullptr) {
   if (!act || !qweight || !out || !scales || !qzeros || !g_idx) return fail(Q4_E_BADARG, "gemm: null pointer");
   if (M <= 0 || K <= 0 || N <= 0 || G <= 0) return fail(Q4_E_BADARG, "gemm: M=%d K=%d N=%d G=%d", M, K, N, G);
   if (K % 128 || N % 128) return fail(Q4_E_SHAPE, "gemm: K=%d and N=%d must be multiples of 128", K, N);
@@ -369,11 +369,13 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
   const bool wide_ok = nout % G2_TILE_N == 0 && stages2w > 0;
   if ((g_gemm_variant == 2 && !pair_ok) || (g_gemm_variant == 3 && !wide_ok))
     return fail(Q4_E_SHAPE, "gemm: the CTA-pair kernel needs %d output columns to be a multiple of 256 and G=%d tables to fit", nout, G);
-  const bool use_pair = (pair_ok && g_gemm_variant != 1) || g_gemm_variant == 3;
+  if (swiglu && (transpose || lora_r > 0 || !pair_ok || N % 256))
+    return fail(Q4_E_SHAPE, "gemm: the fused gate_up product needs the CTA-pair kernel (N=%d a multiple of 256, G=%d tables that fit) and no low-rank term", N, G);
+  const bool use_pair = (pair_ok && g_gemm_variant != 1) || g_gemm_variant == 3 || swiglu;
   // 512-row tiles halve the dequant work per flop but leave fewer, larger tiles to deal: take the
   // form the estimate favours
   const int P_est = sm_count() / 2 > 0 ? sm_count() / 2 : 1;
-  const size_t zp_need = transpose ? (((size_t)G * N * sizeof(__half) + 255) & ~(size_t)255) : 0;
+  const size_t zp_need = transpose && !zp_cached ? (((size_t)G * N * sizeof(__half) + 255) & ~(size_t)255) : 0;
   auto ws_ok_for = [&](int m) { return workspace && workspace_bytes >= Q4_GEMM_WS_COUNTER_BYTES + zp_need + (size_t)P_est * m * Q4_GEMM_WS_SLICE_BYTES; };
   int mh = 1;
   if (use_pair && g_gemm_variant == 3) mh = 2;
@@ -441,6 +443,14 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
     }
     attr_done[use_pair ? 1 : 0][tr][dev] = true;
   }
+  static bool swiglu_attr_done[64] = {false};
+  if (swiglu && !swiglu_attr_done[dev]) {
+    const void* fns[4] = {(const void*)q4_gemm2_kernel<false, false, 1, true>, (const void*)q4_gemm2_kernel<false, true, 1, true>,
+                          (const void*)q4_gemm2_kernel<false, false, 2, true>, (const void*)q4_gemm2_kernel<false, true, 2, true>};
+    for (const void* f2 : fns)
+      if (int e = check_cuda(cudaFuncSetAttribute(f2, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024), "gemm smem attribute")) return e;
+    swiglu_attr_done[dev] = true;
+  }
   if (use_pair) {
     const int tile_m = 256 * mh;
     const int n_tiles = (nout / G2_TILE_N) * ((M + tile_m - 1) / tile_m);
@@ -450,7 +460,9 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
     // backward: table of zero terms in the workspace, filled by a small kernel ahead of the GEMM
     p.zp_table = nullptr;
     const size_t zp_bytes = ((size_t)G * N * sizeof(__half) + 255) & ~(size_t)255;
-    if (transpose && ws && workspace_bytes >= ws_off + zp_bytes) {
+    if (transpose && zp_cached) {
+      p.zp_table = (const __half*)zp_cached;                 // the caller keeps the table of this layer
+    } else if (transpose && ws && workspace_bytes >= ws_off + zp_bytes) {
       p.zp_table = (const __half*)(ws + ws_off);
       const int total8 = G * (N / 8);
       zp_table_kernel<<<(total8 + 255) / 256, 256, 0, st>>>((const __half*)scales, (const uint32_t*)qzeros, (__half*)(ws + ws_off), total8);
@@ -468,7 +480,11 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
     p.ws_counters = (unsigned*)ws;
     const dim3 grid(2 * pairs), block(G2_THREADS);
 #define Q4_LAUNCH2(TR, SP, MHV) q4_gemm2_kernel<TR, SP, MHV><<<grid, block, smem, st>>>(amap, umap, p)
-    if (mh == 2) {
+#define Q4_LAUNCH2S(SP, MHV) q4_gemm2_kernel<false, SP, MHV, true><<<grid, block, smem, st>>>(amap, umap, p)
+    if (swiglu) {
+      if (mh == 2) { if (f > 1) Q4_LAUNCH2S(true, 2); else Q4_LAUNCH2S(false, 2); }
+      else { if (f > 1) Q4_LAUNCH2S(true, 1); else Q4_LAUNCH2S(false, 1); }
+    } else if (mh == 2) {
       if (f > 1) { if (transpose) Q4_LAUNCH2(true, true, 2); else Q4_LAUNCH2(false, true, 2); }
       else { if (transpose) Q4_LAUNCH2(true, false, 2); else Q4_LAUNCH2(false, false, 2); }
     } else {
@@ -476,6 +492,7 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
       else { if (transpose) Q4_LAUNCH2(true, false, 1); else Q4_LAUNCH2(false, false, 1); }
     }
 #undef Q4_LAUNCH2
+#undef Q4_LAUNCH2S
   } else {
     const dim3 grid(nout / GM_TILE_N, (M + GM_TILE_M - 1) / GM_TILE_M), block(GM_THREADS);
     if (transpose) q4_gemm_kernel<true><<<grid, block, smem, st>>>(amap, umap, p);
@@ -496,10 +513,34 @@ extern "C" int q4_gemm_fwd(const void* x, const int32_t* qweight, void* y, const
   return gemm_launch(false, x, qweight, y, scales, qzeros, g_idx, bias, lora_u, lora_b, lora_r, M, K, N, G, workspace, workspace_bytes, stream);
 }
 
+extern "C" int q4_gemm_fwd_swiglu(const void* x, const int32_t* qweight, void* out, const void* scales, const int32_t* qzeros,
+                                  const int32_t* g_idx, const void* bias, int M, int K, int N, int G, void* workspace,
+                                  size_t workspace_bytes, q4_stream_t stream) {
+  return gemm_launch(false, x, qweight, out, scales, qzeros, g_idx, bias, nullptr, nullptr, 0, M, K, N, G, workspace, workspace_bytes, stream, true);
+}
+
 extern "C" int q4_gemm_bwd(const void* dy, const int32_t* qweight, void* dx, const void* scales, const int32_t* qzeros,
                            const int32_t* g_idx, const void* lora_v, const void* lora_a, int lora_r,
                            int M, int K, int N, int G, void* workspace, size_t workspace_bytes, q4_stream_t stream) {
   return gemm_launch(true, dy, qweight, dx, scales, qzeros, g_idx, nullptr, lora_v, lora_a, lora_r, M, K, N, G, workspace, workspace_bytes, stream);
+}
+
+extern "C" int q4_zero_term_table(const void* scales, const int32_t* qzeros, void* out, int G, int N, q4_stream_t stream) {
+  if (!scales || !qzeros || !out) return fail(Q4_E_BADARG, "zero_term_table: null pointer");
+  if (G <= 0 || N <= 0 || N % 8) return fail(Q4_E_SHAPE, "zero_term_table: G=%d N=%d (N a multiple of 8)", G, N);
+  if (!aligned16(scales) || !aligned16(out)) return fail(Q4_E_ALIGN, "zero_term_table: pointers must be 16-byte aligned");
+  if (int e = check_device()) return e;
+  const int total8 = G * (N / 8);
+  zp_table_kernel<<<(total8 + 255) / 256, 256, 0, (cudaStream_t)stream>>>((const __half*)scales, (const uint32_t*)qzeros, (__half*)out, total8);
+  return check_cuda(cudaGetLastError(), "zero_term_table launch");
+}
+
+extern "C" int q4_gemm_bwd_table(const void* dy, const int32_t* qweight, void* dx, const void* scales, const int32_t* qzeros,
+                                 const void* zero_terms, const int32_t* g_idx, const void* lora_v, const void* lora_a, int lora_r,
+                                 int M, int K, int N, int G, void* workspace, size_t workspace_bytes, q4_stream_t stream) {
+  if (!zero_terms || !aligned16(zero_terms)) return fail(Q4_E_BADARG, "gemm_bwd_table: needs a 16-byte aligned zero-term table");
+  return gemm_launch(true, dy, qweight, dx, scales, qzeros, g_idx, nullptr, lora_v, lora_a, lora_r, M, K, N, G, workspace, workspace_bytes, stream,
+                     false, zero_terms);
 }
 
 extern "C" int q4_gemm_set_variant(int variant) {

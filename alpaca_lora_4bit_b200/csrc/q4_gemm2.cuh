@@ -122,7 +122,11 @@ __device__ __forceinline__ int stage_owner(long long u, int n, long long total) 
 // overlaps the MMAs of the next.  MH = 2: 512-row tiles (256 rows per CTA, two MMAs per 16
 // contraction elements on the same dequantised operand): half the dequant work per flop, which is
 // what bounds the MH = 1 form; both accumulators belong to the one tile in flight.
-template <bool TRANSPOSE, bool SPLIT, int MH>
+// SWIGLU (forward only): the layer is a fused [gate | up] projection of 2 I columns and the output is
+// half(silu(half(gate))) * half(up), [M, I]: the even CTA of a pair dequantises 128 gate columns, the odd CTA the
+// 128 up columns of the same positions, so every accumulator row holds both operands of 128 outputs and the
+// product is taken in the epilogue (the roundings are those of the gate_up product followed by the SwiGLU kernel).
+template <bool TRANSPOSE, bool SPLIT, int MH, bool SWIGLU = false>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G2_THREADS, 1)
 q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap umap, const GemmParams p) {
   extern __shared__ unsigned char smem_raw[];
@@ -265,7 +269,8 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
     for (int item = 0; item < wr.n_items; ++item, ++tl) {
       const WorkItem wi = work_item<SPLIT>(p, wr, item, n_pairs, T);
       const int ncon = wi.ke - wi.kb, nst = ncon + (wi.lora ? 1 : 0);    // stages of this item: j = 0 .. nst-1, contraction stage kb + j
-      const int out0 = (wi.tile / m_tiles) * G2_TILE_N + 128 * (int)rank;   // first output column (n forward, k backward)
+      // first column this CTA dequantises (n forward, k backward)
+      const int out0 = SWIGLU ? (wi.tile / m_tiles) * 128 + (int)rank * (p.N >> 1) : (wi.tile / m_tiles) * G2_TILE_N + 128 * (int)rank;
       // packed words of the stage: rows (k0/8 + r), columns ncol0 .. ncol0+7
       auto word_ptr = [&](int it) -> const uint32_t* {
         const int prow = TRANSPOSE ? (out0 >> 3) + r : it * (GM_TILE_C >> 3) + r;
@@ -392,12 +397,13 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
     for (int item = 0; item < wr.n_items; ++item, ++tl) {
       const WorkItem wi = work_item<SPLIT>(p, wr, item, n_pairs, T);
       const int acc = MH == 1 ? (tl & 1) : 0, acc_use = MH == 1 ? (tl >> 1) : tl;
-      const int col0 = (wi.tile / m_tiles) * G2_TILE_N;
+      const int col0 = (wi.tile / m_tiles) * (SWIGLU ? 128 : G2_TILE_N);
+      const int out_pitch = SWIGLU ? (p.N >> 1) : n_out_total;
       int m = 0;                                                     // output row of this thread, set per accumulator below
       // 32 fp32 sums of row m, columns col0 + 32 cb ..: (+bias) -> fp16 -> global
       auto emit = [&](int cb, const uint32_t (&v)[32]) {
         if (m >= p.M) return;
-        __half* dst = p.out + (size_t)m * n_out_total + col0 + cb * 32;
+        __half* dst = p.out + (size_t)m * out_pitch + col0 + cb * 32;
         uint32_t o[16];
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
@@ -477,18 +483,82 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
           }
         };
         const uint32_t tsrc = tmem_acc + ((uint32_t)(32 * quarter) << 16) + (acc + h) * 256;
-        if (!(reducer && m < p.M)) {
+        if constexpr (SWIGLU) {
+          // accumulator columns 32 cb .. (gate) and 128 + 32 cb .. (up) of this thread's row together
+#pragma unroll 1
+          for (int cb = 0; cb < 4; ++cb) {
+            uint32_t gv[32], uv[32];
+            __syncwarp();                                  // the lanes of rows past M skipped the stores: whole again for the aligned load
+            tmem_ld32(tsrc + cb * 32, gv);
+            tmem_ld32(tsrc + 128 + cb * 32, uv);
+            tmem_ld_wait();
+            if (shared_tile && !reducer) {
+              if (m < p.M) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  *reinterpret_cast<uint4*>(part + ((cb * 8 + j) * 32 + lane) * 4) = make_uint4(gv[4 * j], gv[4 * j + 1], gv[4 * j + 2], gv[4 * j + 3]);
+                  *reinterpret_cast<uint4*>(part + (((cb + 4) * 8 + j) * 32 + lane) * 4) = make_uint4(uv[4 * j], uv[4 * j + 1], uv[4 * j + 2], uv[4 * j + 3]);
+                }
+              }
+              continue;
+            }
+            if (reducer) {
+              for (int cc = c_first + 1; cc <= c_last; ++cc) {
+                const float* s2 = part_of(cc, h);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                  const float4 a = __ldcg(reinterpret_cast<const float4*>(s2 + ((cb * 8 + j) * 32 + lane) * 4));
+                  const float4 b = __ldcg(reinterpret_cast<const float4*>(s2 + (((cb + 4) * 8 + j) * 32 + lane) * 4));
+                  gv[4 * j] = __float_as_uint(__uint_as_float(gv[4 * j]) + a.x); gv[4 * j + 1] = __float_as_uint(__uint_as_float(gv[4 * j + 1]) + a.y);
+                  gv[4 * j + 2] = __float_as_uint(__uint_as_float(gv[4 * j + 2]) + a.z); gv[4 * j + 3] = __float_as_uint(__uint_as_float(gv[4 * j + 3]) + a.w);
+                  uv[4 * j] = __float_as_uint(__uint_as_float(uv[4 * j]) + b.x); uv[4 * j + 1] = __float_as_uint(__uint_as_float(uv[4 * j + 1]) + b.y);
+                  uv[4 * j + 2] = __float_as_uint(__uint_as_float(uv[4 * j + 2]) + b.z); uv[4 * j + 3] = __float_as_uint(__uint_as_float(uv[4 * j + 3]) + b.w);
+                }
+              }
+            }
+            if (m < p.M) {
+              __half* dst = p.out + (size_t)m * out_pitch + col0 + cb * 32;
+              uint32_t o[16];
+#pragma unroll
+              for (int e = 0; e < 16; ++e) {
+                float g0 = __uint_as_float(gv[2 * e]), g1 = __uint_as_float(gv[2 * e + 1]);
+                float u0 = __uint_as_float(uv[2 * e]), u1 = __uint_as_float(uv[2 * e + 1]);
+                if (p.bias) {
+                  g0 += __half2float(p.bias[col0 + cb * 32 + 2 * e]); g1 += __half2float(p.bias[col0 + cb * 32 + 2 * e + 1]);
+                  u0 += __half2float(p.bias[out_pitch + col0 + cb * 32 + 2 * e]); u1 += __half2float(p.bias[out_pitch + col0 + cb * 32 + 2 * e + 1]);
+                }
+                const float2 gf = __half22float2(__floats2half2_rn(g0, g1));      // the gate as the unfused product would have stored it
+                o[e] = as_u32(__hmul2(__floats2half2_rn(silu_f(gf.x), silu_f(gf.y)), __floats2half2_rn(u0, u1)));
+              }
+              if (out_aligned32) {
+                asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]),
+                             "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");
+                asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst + 16), "r"(o[8]), "r"(o[9]), "r"(o[10]), "r"(o[11]),
+                             "r"(o[12]), "r"(o[13]), "r"(o[14]), "r"(o[15]) : "memory");
+              } else {
+#pragma unroll
+                for (int q = 0; q < 4; ++q) *reinterpret_cast<uint4*>(dst + 8 * q) = make_uint4(o[4 * q], o[4 * q + 1], o[4 * q + 2], o[4 * q + 3]);
+              }
+            }
+          }
+        } else if (!reducer) {                             // (warp-uniform: rows past M of a shared tile add whatever the
+                                                           // workspace holds and store nothing)
           // two register buffers: the TMEM load of the next 32 columns is in flight while these are consumed
+          // (the lanes of rows past M leave `consume` early: __syncwarp makes the warp whole again before every
+          // warp-wide TMEM instruction)
           uint32_t va[32], vb[32];
+          __syncwarp();
           tmem_ld32(tsrc, va);
 #pragma unroll 1
           for (int cb = 0; cb < G2_TILE_N / 32; cb += 2) {
             tmem_ld_wait();
             tmem_ld32(tsrc + (cb + 1) * 32, vb);
             consume(cb, va);
+            __syncwarp();
             tmem_ld_wait();
             if (cb + 2 < G2_TILE_N / 32) tmem_ld32(tsrc + (cb + 2) * 32, va);
             consume(cb + 1, vb);
+            __syncwarp();
           }
         } else {
           // adding up a shared tile: what takes long is the first other contributor's sums coming from L2, so
@@ -501,6 +571,7 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
 #pragma unroll 1
           for (int cb = 0; cb < G2_TILE_N / 32; ++cb) {
             uint32_t v[32];
+            __syncwarp();
             tmem_ld32(tsrc + cb * 32, v);
             tmem_ld_wait();
 #pragma unroll

@@ -237,6 +237,30 @@ def decode_v2(x, qweight, scales, zeros, groupsize, plan_key=None):
 _gemm_ws_bytes: dict = {}
 
 
+# Zero terms rn(scale * (zero + 1)) [G, N] of the layers whose backward has run, keyed by the identity of the
+# packed zero-point tensor and dropped with it: the table depends on the frozen layer only, a finetune step runs
+# every layer's backward once per step, and deriving it ahead of every call is a kernel launch per call
+# (2 G N bytes per layer are kept instead, 1.6 % of the packed weights).  ``cache_zero_terms = False`` restores
+# the derivation per call.
+cache_zero_terms = True
+_zero_term_tables: dict = {}
+
+
+def _zero_terms(scales, zeros, G, N, st):
+    key = id(zeros)
+    hit = _zero_term_tables.get(key)
+    if hit is not None and hit[1] == (zeros.data_ptr(), scales.data_ptr(), zeros._version, scales._version):
+        return hit[0]
+    if torch.cuda.is_current_stream_capturing():
+        return None                                    # no allocation inside a capture: this call derives the table itself
+    import weakref
+    table = torch.empty((G, N), dtype=torch.float16, device=scales.device)
+    _lib.check(_lib.lib().q4_zero_term_table(scales.data_ptr(), zeros.data_ptr(), table.data_ptr(), G, N, st), "zero_term_table")
+    ref = weakref.ref(zeros, lambda _r, key=key: _zero_term_tables.pop(key, None))
+    _zero_term_tables[key] = (table, (zeros.data_ptr(), scales.data_ptr(), zeros._version, scales._version), ref)
+    return table
+
+
 def gemm(x, qweight, out, scales, zeros, g_idx, transpose=False, bias=None, lora_u=None, lora_w=None) -> None:
     """Fused large-M product on the tensor cores: ``out = x @ W (+ bias)`` or, with ``transpose``,
     ``out = x @ W.T``; ``x``, ``out``, ``scales`` fp16, W never leaves shared memory.
@@ -268,13 +292,47 @@ def gemm(x, qweight, out, scales, zeros, g_idx, transpose=False, bias=None, lora
             need = _gemm_ws_bytes[(K, N, G)] = int(L.q4_gemm_workspace_bytes(K, N, G))
         ws = _lib.gemm_workspace_for(dev, st, need)
         if transpose:
-            rc = L.q4_gemm_bwd(x.data_ptr(), qweight.data_ptr(), out.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
-                               g_idx.data_ptr(), _lib.ptr(lora_u), _lib.ptr(lora_w), r, M, K, N, G, ws.data_ptr(), ws.numel(), st)
+            zt = _zero_terms(scales, zeros, G, N, st) if cache_zero_terms else None
+            if zt is not None:
+                rc = L.q4_gemm_bwd_table(x.data_ptr(), qweight.data_ptr(), out.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
+                                         zt.data_ptr(), g_idx.data_ptr(), _lib.ptr(lora_u), _lib.ptr(lora_w), r, M, K, N, G,
+                                         ws.data_ptr(), ws.numel(), st)
+            else:
+                rc = L.q4_gemm_bwd(x.data_ptr(), qweight.data_ptr(), out.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
+                                   g_idx.data_ptr(), _lib.ptr(lora_u), _lib.ptr(lora_w), r, M, K, N, G, ws.data_ptr(), ws.numel(), st)
         else:
             rc = L.q4_gemm_fwd(x.data_ptr(), qweight.data_ptr(), out.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
                                g_idx.data_ptr(), _lib.ptr(bias), _lib.ptr(lora_u), _lib.ptr(lora_w), r, M, K, N, G,
                                ws.data_ptr(), ws.numel(), st)
     _lib.check(rc, "gemm")
+
+
+def gemm_swiglu(x, qweight, out, scales, zeros, g_idx, bias=None) -> None:
+    """``out [M, I] = half(silu(half(x @ W_gate))) * half(x @ W_up)`` for a fused ``[K, 2 I]`` gate/up layer in one
+    kernel (the SwiGLU product in the GEMM epilogue): what ``gemm`` followed by the element-wise kernel computes,
+    without the ``[M, 2 I]`` tensor.  Raises for layers the CTA-pair kernel does not take (``gemm_swiglu_supported``)."""
+    dev = _lib.require_cuda(x, qweight, out, scales, zeros, g_idx, bias)
+    R, N = qweight.shape
+    K, M, G = R * 8, x.shape[0], scales.shape[0]
+    if x.shape != (M, K) or out.shape != (M, N // 2):
+        raise RuntimeError(f"quant_cuda: gemm_swiglu shapes x{tuple(x.shape)} out{tuple(out.shape)} do not match the layer [{K},{N}]")
+    if x.dtype != torch.float16 or out.dtype != torch.float16 or scales.dtype != torch.float16:
+        raise RuntimeError("quant_cuda: gemm_swiglu takes fp16 x, out and scales")
+    L = _lib.lib()
+    with _lib.on_device(dev):
+        st = _lib.stream_of(x)
+        need = _gemm_ws_bytes.get((K, N, G))
+        if need is None:
+            need = _gemm_ws_bytes[(K, N, G)] = int(L.q4_gemm_workspace_bytes(K, N, G))
+        ws = _lib.gemm_workspace_for(dev, st, need)
+        rc = L.q4_gemm_fwd_swiglu(x.data_ptr(), qweight.data_ptr(), out.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
+                                  g_idx.data_ptr(), _lib.ptr(bias), M, K, N, G, ws.data_ptr(), ws.numel(), st)
+    _lib.check(rc, "gemm_swiglu")
+
+
+def gemm_swiglu_supported(K: int, N: int, G: int) -> bool:
+    """Layers ``gemm_swiglu`` takes: K % 128 == 0, N % 256 == 0 and scale tables that leave the pair kernel three stages."""
+    return K % 128 == 0 and N % 256 == 0 and (1024 + 3 * 32768 + 512 + 2 * G * 128 * 2) <= 227 * 1024
 
 
 def gemm_supported(K: int, N: int, G: int, transpose: bool) -> bool:

@@ -161,6 +161,27 @@ int q4_gemm_fwd(const void* x, const int32_t* qweight, void* y, const void* scal
 int q4_gemm_bwd(const void* dy, const int32_t* qweight, void* dx, const void* scales, const int32_t* qzeros,
                 const int32_t* g_idx, const void* lora_v, const void* lora_a, int lora_r,
                 int M, int K, int N, int G, void* workspace, size_t workspace_bytes, q4_stream_t stream);
+
+/* The fused [gate | up] projection of a LLaMA MLP with its SwiGLU product in the GEMM epilogue: qweight, scales,
+ * qzeros describe a [K, N = 2 I] layer whose first I columns are gate_proj and whose last I are up_proj (as
+ * make_fused_mlp concatenates them, model_attn_mlp_patch.py:165-247 of the reference, which then computes
+ * act_fn(gate) * up on the [M, 2 I] product, :229-232); out [M, I] fp16 = half(silu(half(x W_gate + b))) *
+ * half(x W_up + b), the roundings of q4_gemm_fwd followed by q4_swiglu_fwd without the [M, 2 I] tensor ever
+ * reaching memory.  N % 256 == 0; bias [N] or NULL; workspace as for q4_gemm_fwd. */
+int q4_gemm_fwd_swiglu(const void* x, const int32_t* qweight, void* out, const void* scales, const int32_t* qzeros,
+                       const int32_t* g_idx, const void* bias, int M, int K, int N, int G, void* workspace,
+                       size_t workspace_bytes, q4_stream_t stream);
+
+/* The backward with the layer's zero terms kept by the caller: q4_zero_term_table fills out [G, N] fp16 with
+ * rn(scale * (zero + 1)) of every group and column (what q4_gemm_bwd otherwise derives into its workspace with
+ * a small kernel ahead of every call - the table depends on the frozen layer only), q4_gemm_bwd_table is
+ * q4_gemm_bwd reading that table.  A training step calls the backward of every layer once per step, so a host
+ * that keeps the tables (2 G N bytes per layer, 1.6 % of the packed weights) saves that kernel per call.  No
+ * reference counterpart. */
+int q4_zero_term_table(const void* scales, const int32_t* qzeros, void* out, int G, int N, q4_stream_t stream);
+int q4_gemm_bwd_table(const void* dy, const int32_t* qweight, void* dx, const void* scales, const int32_t* qzeros,
+                      const void* zero_terms, const int32_t* g_idx, const void* lora_v, const void* lora_a, int lora_r,
+                      int M, int K, int N, int G, void* workspace, size_t workspace_bytes, q4_stream_t stream);
 /* Optional scratch for the two calls above (no reference counterpart: the reference's scratch is
  * the dense fp16 copy of W it reconstructs).  `workspace` may be NULL; with at least
  * q4_gemm_workspace_bytes(K, N, G) bytes of device memory, 16-byte aligned, whose first 64 KiB are

@@ -309,3 +309,59 @@ def test_linear4bitlt_lora_training_step(fused):
     assert rel_fro(x.grad, dyc.float() @ w.t() + dx_l) <= REL_TOL
     assert rel_fro(m.lora_A["default"].weight.grad, dA) <= 5e-3
     assert rel_fro(m.lora_B["default"].weight.grad, dB) <= 5e-3
+
+
+@pytest.mark.parametrize("M,K,I,act", [(300, 512, 256, False), (1024, 4096, 11008, False), (2048, 1024, 1408, True), (64, 256, 128, False), (520, 5120, 13824, False)])
+def test_gate_up_product_with_swiglu_in_the_epilogue(M, K, I, act):
+    """q4_gemm_fwd_swiglu on a fused [gate | up] layer against q4_gemm_fwd followed by the element-wise SwiGLU
+    kernel (the same roundings: equal up to the order in which shared tiles add their partial sums) and against
+    silu(gate) * up of the oracle's products; with and without bias, both tile heights."""
+    from alpaca_lora_4bit_b200 import fused_ops
+    layer = synth.make_layer(K, 2 * I, 128, act, seed=K + I).to(DEV)
+    x = synth.make_acts(M, K, seed=M).to(DEV)
+    bias = (torch.randn(2 * I, generator=torch.Generator().manual_seed(1)) * 0.1).half().to(DEV)
+    w = orc.recons_v2(layer.qweight.cpu(), layer.scales.cpu(), layer.qzeros.cpu(), layer.g_idx.cpu()).to(DEV).float()
+    for b in (None, bias):
+        full = torch.empty(M, 2 * I, dtype=torch.float16, device=DEV)
+        quant_cuda.gemm(x, layer.qweight, full, layer.scales, layer.qzeros, layer.g_idx, bias=b)
+        want = fused_ops.swiglu(full[:, :I], full[:, I:])
+        exact = x.float() @ w + (0 if b is None else b.float())
+        exact = torch.nn.functional.silu(exact[:, :I]) * exact[:, I:]
+        for variant in (0, 2, 3):
+            quant_cuda.gemm_set_variant(variant)
+            try:
+                got = torch.full((M, I), 9.0, dtype=torch.float16, device=DEV)
+                quant_cuda.gemm_swiglu(x, layer.qweight, got, layer.scales, layer.qzeros, layer.g_idx, bias=b)
+            finally:
+                quant_cuda.gemm_set_variant(0)
+            assert rel_fro(got, want) <= 1e-3, (variant, rel_fro(got, want))
+            assert rel_fro(got, exact) <= 3e-3
+            assert float((got == want).float().mean()) >= 0.98              # the same roundings: almost every element equal
+    assert quant_cuda.device_status() == 0
+
+
+def test_backward_with_cached_zero_terms_is_the_same_product():
+    """quant_cuda.gemm keeps rn(s (z + 1)) [G, N] of a layer after its first backward (q4_zero_term_table,
+    q4_gemm_bwd_table) instead of deriving it into the workspace ahead of every call: same bits either way, one
+    table per layer, dropped with the layer's tensors."""
+    import gc
+    layer = synth.make_layer(1024, 768, 128, True, seed=5).to(DEV)
+    dy = synth.make_acts(300, 768, seed=6).to(DEV)
+    outs = []
+    for cached in (False, True, True):
+        quant_cuda.cache_zero_terms = cached
+        try:
+            dx = torch.empty(300, 1024, dtype=torch.float16, device=DEV)
+            quant_cuda.gemm(dy, layer.qweight, dx, layer.scales, layer.qzeros, layer.g_idx, transpose=True)
+            outs.append(dx)
+        finally:
+            quant_cuda.cache_zero_terms = True
+    assert torch.equal(outs[0], outs[1]) and torch.equal(outs[1], outs[2])
+    key = id(layer.qzeros)
+    assert key in quant_cuda._zero_term_tables
+    table = quant_cuda._zero_term_tables[key][0]
+    z1 = (((layer.qzeros.cpu().view(-1, 96, 1) >> (4 * torch.arange(8).view(1, 1, 8))) & 0xF) + 1).reshape(8, 768).half()
+    assert torch.equal(table.cpu(), layer.scales.cpu() * z1)              # rn(s * (z + 1)), as the reconstruct rounds it
+    del layer, table
+    gc.collect()
+    assert key not in quant_cuda._zero_term_tables

@@ -25,10 +25,13 @@ def small_llama(kv_heads, seed):
     return fs.build_quant_llama(shape, DEV, groupsize=128, seed=seed).eval()
 
 
+@pytest.mark.parametrize("epilogue_rows", [1024, 9])          # SwiGLU as its own kernel, and in the gate_up GEMM's epilogue
 @pytest.mark.parametrize("kv_heads", [8, 2])                  # multi-head, and grouped-query (narrower k / v)
-def test_fused_attention_and_mlp_match_the_unpatched_model(kv_heads):
+def test_fused_attention_and_mlp_match_the_unpatched_model(kv_heads, epilogue_rows):
     ids = torch.randint(0, 512, (2, 160), generator=torch.Generator().manual_seed(1)).to(DEV)
     one = ids[:, :1]
+    keep_rows = patch.swiglu_epilogue_rows
+    patch.swiglu_epilogue_rows = epilogue_rows
     try:
         with torch.no_grad():
             plain = small_llama(kv_heads, seed=11)
@@ -43,6 +46,7 @@ def test_fused_attention_and_mlp_match_the_unpatched_model(kv_heads):
             got_next = fused(ids[:, -1:] * 0 + 7, past_key_values=out2.past_key_values, use_cache=True).logits
     finally:
         mm4b.cache_buffer = True
+        patch.swiglu_epilogue_rows = keep_rows
     layer0 = fused.model.layers[0]
     assert isinstance(layer0.self_attn, patch.QuantLlamaAttention) and isinstance(layer0.mlp, patch.QuantLlamaMLP)
     assert layer0.self_attn.qkv_proj.out_features == 1024 + 2 * 128 * kv_heads
