@@ -279,6 +279,7 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__
 #pragma unroll 1
     for (int cb = 0; cb < GM_TILE_N / 32; ++cb) {
       uint32_t v[32];
+      __syncwarp();                                // the lanes of rows past M skipped the stores: whole again for the warp-wide load
       tmem_ld32(tmem_acc + ((uint32_t)(32 * quarter) << 16) + 128 * half + cb * 32, v);
       tmem_ld_wait();
       if (m < p.M) {
@@ -364,7 +365,14 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
   if (workspace && !aligned16(workspace)) return fail(Q4_E_ALIGN, "gemm: the workspace must be 16-byte aligned");
   if (int e = check_device()) return e;
   const int contract = transpose ? N : K, nout = transpose ? K : N;
-  const int stages2 = gemm2_stages(transpose, G, 1), stages2w = gemm2_stages(transpose, G, 2);
+  // forward with the caller's zero-term table: scales and zero terms come from L2 as in the backward, and the
+  // shared memory the tables would take goes to pipeline stages (CTA-pair kernel only)
+  const bool may_drop_tables = !transpose && zp_cached != nullptr && !swiglu;
+  int stages2 = gemm2_stages(transpose, G, 1), stages2w = gemm2_stages(transpose, G, 2);
+  const int stages2_nt = may_drop_tables ? gemm2_stages(true, G, 1) : stages2, stages2w_nt = may_drop_tables ? gemm2_stages(true, G, 2) : stages2w;
+  // the table is used where it buys a stage for both tile heights (or makes the pair kernel possible at all)
+  const bool no_tables = transpose || (may_drop_tables && stages2_nt > stages2 && stages2w_nt > stages2w);
+  if (no_tables && !transpose) { stages2 = stages2_nt; stages2w = stages2w_nt; }
   const bool pair_ok = nout % G2_TILE_N == 0 && stages2 > 0;
   const bool wide_ok = nout % G2_TILE_N == 0 && stages2w > 0;
   if ((g_gemm_variant == 2 && !pair_ok) || (g_gemm_variant == 3 && !wide_ok))
@@ -388,7 +396,7 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
   int stages = GM_MAX_STAGES;
   while (stages > 2 && gemm_smem_bytes(transpose, G, stages) > 227 * 1024) --stages;
   if (use_pair) stages = mh == 2 ? stages2w : stages2;
-  const size_t smem = use_pair ? gemm2_smem_bytes(transpose, G, stages, mh) : gemm_smem_bytes(transpose, G, stages);
+  const size_t smem = use_pair ? gemm2_smem_bytes(no_tables, G, stages, mh) : gemm_smem_bytes(transpose, G, stages);
   if (smem > 227 * 1024) return fail(Q4_E_SHAPE, "gemm: scale tables for G=%d groups do not fit shared memory", G);
 
   GemmParams p;
@@ -460,7 +468,7 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
     // backward: table of zero terms in the workspace, filled by a small kernel ahead of the GEMM
     p.zp_table = nullptr;
     const size_t zp_bytes = ((size_t)G * N * sizeof(__half) + 255) & ~(size_t)255;
-    if (transpose && zp_cached) {
+    if (zp_cached && (transpose || no_tables)) {
       p.zp_table = (const __half*)zp_cached;                 // the caller keeps the table of this layer
     } else if (transpose && ws && workspace_bytes >= ws_off + zp_bytes) {
       p.zp_table = (const __half*)(ws + ws_off);
@@ -540,6 +548,14 @@ extern "C" int q4_gemm_bwd_table(const void* dy, const int32_t* qweight, void* d
                                  int M, int K, int N, int G, void* workspace, size_t workspace_bytes, q4_stream_t stream) {
   if (!zero_terms || !aligned16(zero_terms)) return fail(Q4_E_BADARG, "gemm_bwd_table: needs a 16-byte aligned zero-term table");
   return gemm_launch(true, dy, qweight, dx, scales, qzeros, g_idx, nullptr, lora_v, lora_a, lora_r, M, K, N, G, workspace, workspace_bytes, stream,
+                     false, zero_terms);
+}
+
+extern "C" int q4_gemm_fwd_table(const void* x, const int32_t* qweight, void* y, const void* scales, const int32_t* qzeros,
+                                 const void* zero_terms, const int32_t* g_idx, const void* bias, const void* lora_u, const void* lora_b,
+                                 int lora_r, int M, int K, int N, int G, void* workspace, size_t workspace_bytes, q4_stream_t stream) {
+  if (!zero_terms || !aligned16(zero_terms)) return fail(Q4_E_BADARG, "gemm_fwd_table: needs a 16-byte aligned zero-term table");
+  return gemm_launch(false, x, qweight, y, scales, qzeros, g_idx, bias, lora_u, lora_b, lora_r, M, K, N, G, workspace, workspace_bytes, stream,
                      false, zero_terms);
 }
 

@@ -351,6 +351,9 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
           const int ncol = it * GM_TILE_C + 8 * chunk16;             // global column of the task
           if (p.zp_table) deq_task_global_zp(rows8, off, w, tga, tgb, p.scales + ncol, p.zp_table + ncol, N);
           else deq_task_global(rows8, off, w, tga, tgb, p.scales + ncol, p.qzeros + (ncol >> 3), N);
+        } else if (p.zp_table) {                     // forward without shared-memory tables: the caller keeps the zero terms
+          const int ncol = out0 + 8 * chunk16;
+          deq_task_global_zp(rows8, off, w, C.ga, C.gb, p.scales + ncol, p.zp_table + ncol, N);
         } else {
           deq_task_tables(rows8, off, w, C.ga, C.gb, tab + 16 * chunk16);
         }
@@ -361,7 +364,7 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         st += GM_DEQ_GROUPS;
       };
       prefetch(j0, R0);                              // in flight while the tables below are built
-      if (!TRANSPOSE && out0 != tab_out0) {
+      if (!TRANSPOSE && !p.zp_table && out0 != tab_out0) {
         // tables for the CTA's 128 columns: scale and rn(s*(z+1)) of every group
         if (tab_out0 >= 0) named_bar_sync(1, GM_DEQ_THREADS * GM_DEQ_GROUPS);      // all readers of the old tables are done
         for (int i = (dw << 5) | lane; i < p.G * 16; i += GM_DEQ_THREADS * GM_DEQ_GROUPS) {

@@ -53,25 +53,9 @@ def get_buffer(shape_of_qweight, dtype=torch.float16, device='cuda', bits=4):
     return buf
 
 
-_seq_cache: dict = {}        # id(g_idx) -> (weak reference, storage address, version counter, answer)
 
 
-def _groups_are_sequential(g_idx, groups: int) -> bool:
-    """True when ``g_idx[k] == k // (K / groups)`` for every row, i.e. the layer was quantised without
-    act-order and its groups can be derived from the row index.  One comparison per tensor (it synchronises the
-    device), remembered for as long as the tensor lives and is not written to."""
-    import weakref
-    key = id(g_idx)
-    hit = _seq_cache.get(key)
-    if hit is not None and hit[0]() is g_idx and hit[1] == g_idx.data_ptr() and hit[2] == g_idx._version:
-        return hit[3]
-    K = g_idx.numel()
-    ok = groups > 0 and K % groups == 0
-    if ok:
-        want = torch.arange(K, device=g_idx.device, dtype=torch.int64) // (K // groups)
-        ok = bool(torch.equal(g_idx.reshape(-1).to(torch.int64), want))
-    _seq_cache[key] = (weakref.ref(g_idx, lambda _r, key=key: _seq_cache.pop(key, None)), g_idx.data_ptr(), g_idx._version, ok)
-    return ok
+_groups_are_sequential = quant_cuda.groups_are_sequential
 
 
 def _decode(x, qweight, scales, zeros, g_idx, groupsize, flags):

@@ -237,12 +237,37 @@ def decode_v2(x, qweight, scales, zeros, groupsize, plan_key=None):
 _gemm_ws_bytes: dict = {}
 
 
+_seq_cache: dict = {}        # id(g_idx) -> (weak reference, storage address, version counter, answer)
+
+
+def groups_are_sequential(g_idx, groups: int) -> bool:
+    """True when ``g_idx[k] == k // (K / groups)`` for every row, i.e. the layer was quantised without
+    act-order and its groups can be derived from the row index.  One comparison per tensor (it synchronises the
+    device), remembered for as long as the tensor lives and is not written to; during a stream capture a tensor
+    that has not been looked at yet counts as not sequential."""
+    import weakref
+    key = id(g_idx)
+    hit = _seq_cache.get(key)
+    if hit is not None and hit[0]() is g_idx and hit[1] == g_idx.data_ptr() and hit[2] == g_idx._version:
+        return hit[3]
+    if g_idx.is_cuda and torch.cuda.is_current_stream_capturing():
+        return False
+    K = g_idx.numel()
+    ok = groups > 0 and K % groups == 0
+    if ok:
+        want = torch.arange(K, device=g_idx.device, dtype=torch.int64) // (K // groups)
+        ok = bool(torch.equal(g_idx.reshape(-1).to(torch.int64), want))
+    _seq_cache[key] = (weakref.ref(g_idx, lambda _r, key=key: _seq_cache.pop(key, None)), g_idx.data_ptr(), g_idx._version, ok)
+    return ok
+
+
 # Zero terms rn(scale * (zero + 1)) [G, N] of the layers whose backward has run, keyed by the identity of the
 # packed zero-point tensor and dropped with it: the table depends on the frozen layer only, a finetune step runs
 # every layer's backward once per step, and deriving it ahead of every call is a kernel launch per call
 # (2 G N bytes per layer are kept instead, 1.6 % of the packed weights).  ``cache_zero_terms = False`` restores
 # the derivation per call.
 cache_zero_terms = True
+forward_table_groups = 64       # forward products of layers with this many groups or more read the kept table too
 _zero_term_tables: dict = {}
 
 
@@ -301,9 +326,20 @@ def gemm(x, qweight, out, scales, zeros, g_idx, transpose=False, bias=None, lora
                 rc = L.q4_gemm_bwd(x.data_ptr(), qweight.data_ptr(), out.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
                                    g_idx.data_ptr(), _lib.ptr(lora_u), _lib.ptr(lora_w), r, M, K, N, G, ws.data_ptr(), ws.numel(), st)
         else:
-            rc = L.q4_gemm_fwd(x.data_ptr(), qweight.data_ptr(), out.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
-                               g_idx.data_ptr(), _lib.ptr(bias), _lib.ptr(lora_u), _lib.ptr(lora_w), r, M, K, N, G,
-                               ws.data_ptr(), ws.numel(), st)
+            # Many sequential groups: the scale tables of all groups would cost the kernel a pipeline stage, so it is
+            # given the kept table and reads scales and zero terms from L2 instead (the library ignores the table where
+            # that gains no stage; with act-order every row of a task would need its own pair of loads: measured slower).
+            zt = None
+            if cache_zero_terms and G >= forward_table_groups and N % 256 == 0 and groups_are_sequential(g_idx, G):
+                zt = _zero_terms(scales, zeros, G, N, st)
+            if zt is not None:
+                rc = L.q4_gemm_fwd_table(x.data_ptr(), qweight.data_ptr(), out.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
+                                         zt.data_ptr(), g_idx.data_ptr(), _lib.ptr(bias), _lib.ptr(lora_u), _lib.ptr(lora_w), r, M, K, N, G,
+                                         ws.data_ptr(), ws.numel(), st)
+            else:
+                rc = L.q4_gemm_fwd(x.data_ptr(), qweight.data_ptr(), out.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
+                                   g_idx.data_ptr(), _lib.ptr(bias), _lib.ptr(lora_u), _lib.ptr(lora_w), r, M, K, N, G,
+                                   ws.data_ptr(), ws.numel(), st)
     _lib.check(rc, "gemm")
 
 

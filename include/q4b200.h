@@ -182,6 +182,13 @@ int q4_zero_term_table(const void* scales, const int32_t* qzeros, void* out, int
 int q4_gemm_bwd_table(const void* dy, const int32_t* qweight, void* dx, const void* scales, const int32_t* qzeros,
                       const void* zero_terms, const int32_t* g_idx, const void* lora_v, const void* lora_a, int lora_r,
                       int M, int K, int N, int G, void* workspace, size_t workspace_bytes, q4_stream_t stream);
+/* The forward with the same table: scales and zero terms are then read from global memory (L2) per dequant task,
+ * as the backward reads them, instead of from shared-memory tables of all groups x the CTA's 128 columns, and the
+ * shared memory the tables would take (512 bytes per group: 43 KiB at K = 11008) goes to pipeline stages.  Worth
+ * it on layers with many groups; same arguments and results as q4_gemm_fwd otherwise. */
+int q4_gemm_fwd_table(const void* x, const int32_t* qweight, void* y, const void* scales, const int32_t* qzeros,
+                      const void* zero_terms, const int32_t* g_idx, const void* bias, const void* lora_u, const void* lora_b,
+                      int lora_r, int M, int K, int N, int G, void* workspace, size_t workspace_bytes, q4_stream_t stream);
 /* Optional scratch for the two calls above (no reference counterpart: the reference's scratch is
  * the dense fp16 copy of W it reconstructs).  `workspace` may be NULL; with at least
  * q4_gemm_workspace_bytes(K, N, G) bytes of device memory, 16-byte aligned, whose first 64 KiB are
