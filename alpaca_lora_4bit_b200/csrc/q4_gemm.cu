@@ -482,7 +482,14 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
     bool stream = false;
     int pairs = n_tiles < P ? n_tiles : P;
     gemm2_estimate(M, nout, T, P, mh, ws && workspace_bytes >= ws_off + (size_t)P * mh * Q4_GEMM_WS_SLICE_BYTES, &stream);
-    if (stream) pairs = P;
+    if (stream) {
+      // Fewer tiles than half the pairs: take a whole number of pairs per tile, so that every tile is shared by the
+      // same number of pairs in equal parts and a pair has one piece of one tile.  Cut into P runs the pieces fall
+      // anywhere, a pair's run can lie inside one tile, and the tile's reducer then waits for a contributor that ends
+      // when it does (32 tiles x 172 stages at 1024 rows: 90.2 us on 74 pairs, 78.6 us on 64).
+      const int per_tile = n_tiles > 0 ? P / n_tiles : 0;
+      pairs = per_tile >= 2 ? n_tiles * per_tile : P;
+    }
     const int f = stream ? 2 : 1;
     p.ws_partials = (float*)(ws + ws_off);
     p.ws_counters = (unsigned*)ws;
