@@ -7,7 +7,8 @@
 // [M, wide] activation once and produce something tiny, so they are bound by that read; u and v leave in the
 // [M, 64] zero-padded fp16 form the GEMM kernels take as their extra pipeline stage, and the gradients leave in
 // fp32, the dtype of the factors.
-#include "q4_common.cuh"
+#include "q4_async.cuh"
+#include <atomic>
 
 namespace q4 {
 
@@ -16,11 +17,7 @@ __device__ __forceinline__ void mma_f16_16816(float (&c)[4], uint32_t a0, uint32
                : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
 
-__device__ __forceinline__ uint32_t cluster_ctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
 __device__ __forceinline__ uint32_t cluster_nctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_nctarank;" : "=r"(r)); return r; }
-__device__ __forceinline__ void cluster_sync_all() {
-  asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
 __device__ __forceinline__ float ld_dsmem_f32(const float* local, uint32_t rank) {
   uint32_t remote;
   float v;
@@ -30,71 +27,115 @@ __device__ __forceinline__ float ld_dsmem_f32(const float* local, uint32_t rank)
 }
 
 // ---- out [M, 64] = scale * X [M, C] W^T, W [r, C]; columns r..63 are written as zeros --------------------
-// A CTA owns eight rows and a slice of the contraction; its sixteen warps share the slice (warp w takes the
-// 32-element blocks w, w + 16, ...) and meet in shared memory, and the CTAs that share the rows form a
-// thread-block cluster whose first CTA adds the partial results in rank order through distributed shared memory.
-// Many short warps instead of a few long ones: the read is bound by the round trips to L2, and what hides them
-// here is the number of loads in flight per SM (eight warps that walked a 4096-wide row in sixteen trips took
-// 8.5 us for 8 MB; the compiler does not keep more than a trip's loads in flight however the loop is written).
-// A lane reads 16 contiguous bytes of its row of X and of its row of W per block: which four of the MMA's sixteen
-// k-slots those eight elements occupy is the same for both operands, so the order of the sum is the only thing
-// the re-mapping changes.  Rows 8..15 of the MMA tile stay zero.
-constexpr int LP_ROWS = 8, LP_WARPS = 16, LP_THREADS = LP_WARPS * 32;
+// A CTA owns eight rows of X and walks the contraction in chunks (2048 elements for r <= 16) that arrive in shared
+// memory as bulk copies, one per staged row (the eight rows of X and the r rows of W) on the chunk's mbarrier; its
+// eight warps share a chunk (warp w takes the 32-element blocks w, w + 8, ...) and meet in shared memory at the end.
+// What the forms of this kernel measured at 1024 rows x 4096: plain loads, 8.6 us (the compiler keeps one block's
+// loads in flight per warp however the loop is written, so a row is walked in sixteen round trips to L2); the
+// contraction split over a cluster of CTAs, 7.5-8.9 us (more warps, but a cluster launch alone costs 3 us);
+// 16-byte cp.async copies of everything at once, 5.2 us (one SM pulls its 128 KB through the load/store path at
+// 40-60 GB/s); bulk copies, 3.6 us (the two library kernels and the pad it replaces: 9.3 us + 3).
+// A lane takes 16 contiguous bytes of its row of X and of its row of W per block: which four of the MMA's
+// sixteen k-slots those eight elements occupy is the same for both operands, so the order of the sum is the
+// only thing the re-mapping changes.  Rows 8..15 of the MMA tile stay zero.
+constexpr int LP_ROWS = 8, LP_WARPS = 8, LP_THREADS = LP_WARPS * 32;
+// chunk length and ring depth per output width: as much of the contraction in flight at once as shared memory holds
+// (a CTA's time is the number of round trips to L2 it has to wait for, one after the other)
+__host__ __device__ constexpr int lp_chunk(int nt) { return nt <= 2 ? 2048 : (nt == 4 ? 1024 : 512); }
+__host__ __device__ constexpr int lp_stages(int nt) { return nt == 1 ? 3 : 2; }
+__host__ __device__ constexpr int lp_pitch(int nt) { return lp_chunk(nt) * 2 + 16; }   // bytes per staged row; + 16 keeps the eight rows a quarter-warp reads on different banks
 
 template <int NT>                                // 8-column tiles of the output that r reaches into
 __global__ void __launch_bounds__(LP_THREADS)
 lora_project_kernel(const __half* __restrict__ X, const __half* __restrict__ W, __half* __restrict__ out, int M, int C, int r, float scale) {
-  __shared__ float red[LP_WARPS][LP_ROWS][8 * NT + 1];
-  __shared__ float part[LP_ROWS][64];
+  extern __shared__ __align__(128) unsigned char lp_smem[];
+  constexpr int ROWS = LP_ROWS + 8 * NT;         // staged rows per chunk: 8 of X, then 8 NT of W
+  constexpr int LP_CHUNK = lp_chunk(NT), LP_PITCH = lp_pitch(NT), STAGE = ROWS * LP_PITCH, LP_NS = lp_stages(NT);
+  float* red = reinterpret_cast<float*>(lp_smem + LP_NS * STAGE);          // [warps][8 rows][8 NT + 1]
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
-  // Rows past M and rows of W past r are read from a valid row instead and dropped when the result is stored,
-  // so that every load of the loop is unconditional.
-  const int row = min(blockIdx.x * LP_ROWS + g, M - 1);
-  const uint4* xr = reinterpret_cast<const uint4*>(X + (size_t)row * C) + t;
-  const uint4* wr[NT];
-#pragma unroll
-  for (int nt = 0; nt < NT; ++nt) wr[nt] = reinterpret_cast<const uint4*>(W + (size_t)min(8 * nt + g, r - 1) * C) + t;
+  const int n_chunks = (C + LP_CHUNK - 1) / LP_CHUNK;
+
+  // Rows past M and rows of W past r are staged from a valid row instead and dropped when the result is stored.
+  // One bulk copy per staged row and chunk, issued by the thread of that row; the chunk's barrier counts the bytes.
+  uint64_t* bars = reinterpret_cast<uint64_t*>(red + LP_WARPS * LP_ROWS * (8 * NT + 1) + 1);
+  bars = reinterpret_cast<uint64_t*>((reinterpret_cast<uintptr_t>(bars) + 7) & ~(uintptr_t)7);
+  __shared__ int gave_up;
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < LP_NS; ++i) mbar_init(&bars[i], 1);
+    gave_up = 0;
+    mbar_fence_init();
+  }
+  __syncthreads();
+  auto load_chunk = [&](int c) {
+    unsigned char* st = lp_smem + (c % LP_NS) * STAGE;
+    const int k0 = c * LP_CHUNK, kn = min(LP_CHUNK, C - k0);               // elements of this chunk (a multiple of 32)
+    if (threadIdx.x == 0) mbar_arrive_expect_tx(&bars[c % LP_NS], (uint32_t)(ROWS * kn * 2));
+    __syncthreads();                             // the expectation is posted before any copy can complete on the barrier
+    if (threadIdx.x < ROWS) {
+      const int row = threadIdx.x;
+      const __half* src = row < LP_ROWS ? X + (size_t)min(blockIdx.x * LP_ROWS + row, M - 1) * C
+                                        : W + (size_t)min(row - LP_ROWS, r - 1) * C;
+      asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                   ::"r"(smem_u32(st + row * LP_PITCH)), "l"(src + k0), "r"((uint32_t)(kn * 2)), "r"(smem_u32(&bars[c % LP_NS])) : "memory");
+    }
+  };
+
   float acc[NT][4];
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt)
 #pragma unroll
     for (int i = 0; i < 4; ++i) acc[nt][i] = 0.f;
-  const uint32_t rank = cluster_ctarank(), n_ranks = cluster_nctarank();
-  const int blocks = C >> 5;
-  const int b_begin = (int)((long long)blocks * rank / n_ranks), b_end = (int)((long long)blocks * (rank + 1) / n_ranks);
-#pragma unroll 2
-  for (int b = b_begin + warp; b < b_end; b += LP_WARPS) {
-    const uint4 xv = __ldg(xr + 4 * b);
 #pragma unroll
-    for (int nt = 0; nt < NT; ++nt) {
-      const uint4 wv = __ldg(wr[nt] + 4 * b);
-      mma_f16_16816(acc[nt], xv.x, 0u, xv.y, 0u, wv.x, wv.y);
-      mma_f16_16816(acc[nt], xv.z, 0u, xv.w, 0u, wv.z, wv.w);
+  for (int c = 0; c < LP_NS - 1; ++c)
+    if (c < n_chunks) load_chunk(c);
+  for (int c = 0; c < n_chunks; ++c) {
+    if (c + LP_NS - 1 < n_chunks) {
+      __syncthreads();                           // everyone is done with chunk c - 1, whose slot the next copy overwrites
+      load_chunk(c + LP_NS - 1);
+    }
+    {                                            // chunk c has landed (bounded wait: on expiry the result is dropped)
+      const uint32_t parity = (uint32_t)((c / LP_NS) & 1);
+      bool ok = mbar_test_wait(&bars[c % LP_NS], parity);
+      for (uint32_t i = 0; !ok && i < (gave_up ? 4u : 4000000u); ++i) ok = mbar_test_wait(&bars[c % LP_NS], parity);
+      if (!ok) gave_up = 1;
+    }
+    const unsigned char* st = lp_smem + (c % LP_NS) * STAGE;
+    const int blocks = min(LP_CHUNK, C - c * LP_CHUNK) >> 5;
+    for (int b = warp; b < blocks; b += LP_WARPS) {
+      const uint4 xv = *reinterpret_cast<const uint4*>(st + g * LP_PITCH + 64 * b + 16 * t);
+#pragma unroll
+      for (int nt = 0; nt < NT; ++nt) {
+        const uint4 wv = *reinterpret_cast<const uint4*>(st + (LP_ROWS + 8 * nt + g) * LP_PITCH + 64 * b + 16 * t);
+        mma_f16_16816(acc[nt], xv.x, 0u, xv.y, 0u, wv.x, wv.y);
+        mma_f16_16816(acc[nt], xv.z, 0u, xv.w, 0u, wv.z, wv.w);
+      }
     }
   }
 #pragma unroll
   for (int nt = 0; nt < NT; ++nt) {
-    red[warp][g][8 * nt + 2 * t] = acc[nt][0];
-    red[warp][g][8 * nt + 2 * t + 1] = acc[nt][1];
+    red[(warp * LP_ROWS + g) * (8 * NT + 1) + 8 * nt + 2 * t] = acc[nt][0];
+    red[(warp * LP_ROWS + g) * (8 * NT + 1) + 8 * nt + 2 * t + 1] = acc[nt][1];
   }
   __syncthreads();
-  // this CTA's share of the sum, 8 rows x 64 columns (zeros past the tiles r reaches into)
-  const int orow = threadIdx.x >> 6, col = threadIdx.x & 63;
-  {
-    float s = 0.f;
-    if (col < 8 * NT && col < r) {
+  // 8 rows x 32 column pairs: one half2 per thread
+  const int orow = threadIdx.x >> 5, cp = threadIdx.x & 31;
+  if (blockIdx.x * LP_ROWS + orow < M) {
+    float s0 = 0.f, s1 = 0.f;
+    if (2 * cp < 8 * NT) {
 #pragma unroll
-      for (int w = 0; w < LP_WARPS; ++w) s += red[w][orow][col];
+      for (int w = 0; w < LP_WARPS; ++w) {
+        s0 += red[(w * LP_ROWS + orow) * (8 * NT + 1) + 2 * cp];
+        s1 += red[(w * LP_ROWS + orow) * (8 * NT + 1) + 2 * cp + 1];
+      }
     }
-    part[orow][col] = s;
+    if (2 * cp >= r) s0 = 0.f;
+    if (2 * cp + 1 >= r) s1 = 0.f;
+    reinterpret_cast<__half2*>(out + (size_t)(blockIdx.x * LP_ROWS + orow) * 64)[cp] = __floats2half2_rn(s0 * scale, s1 * scale);
   }
-  cluster_sync_all();
-  if (rank == 0 && blockIdx.x * LP_ROWS + orow < M) {
-    float s = 0.f;
-    for (uint32_t q = 0; q < n_ranks; ++q) s += ld_dsmem_f32(&part[orow][col], q);
-    out[(size_t)(blockIdx.x * LP_ROWS + orow) * 64 + col] = __float2half_rn(s * scale);
-  }
-  cluster_sync_all();                            // nobody leaves while its share is still being read
+}
+
+template <int NT> static size_t lora_project_smem() {
+  return (size_t)lp_stages(NT) * (LP_ROWS + 8 * NT) * lp_pitch(NT) + (size_t)LP_WARPS * LP_ROWS * (8 * NT + 1) * sizeof(float) + 64;
 }
 
 // ---- out [j, c] (or out [c, j]) = sum over m of S [m, j] X [m, c], j < r, S of pitch 64 --------------------
@@ -229,26 +270,26 @@ extern "C" int q4_lora_project(const void* x, const void* w, void* out, int M, i
   if (C % 32) return fail(Q4_E_SHAPE, "lora_project: the contraction length %d must be a multiple of 32", C);
   if (!aligned16(x) || !aligned16(w) || !aligned16(out)) return fail(Q4_E_ALIGN, "lora_project: pointers must be 16-byte aligned");
   if (int e = check_device()) return e;
-  const int tiles = (M + LP_ROWS - 1) / LP_ROWS;
-  // slices of the contraction per row tile (= CTAs per cluster): enough CTAs for three per SM, 16 blocks or more each
-  int split = 1;
-  while (split < 8 && tiles * split < 3 * sm_count() && C / 32 >= 2 * LP_WARPS * split) split *= 2;
-  cudaLaunchConfig_t cfg = {};
-  cudaLaunchAttribute at[1];
-  at[0].id = cudaLaunchAttributeClusterDimension;
-  at[0].val.clusterDim.x = 1; at[0].val.clusterDim.y = (unsigned)split; at[0].val.clusterDim.z = 1;
-  cfg.gridDim = dim3((unsigned)tiles, (unsigned)split); cfg.blockDim = dim3(LP_THREADS);
-  cfg.dynamicSmemBytes = 0; cfg.stream = (cudaStream_t)stream; cfg.attrs = at; cfg.numAttrs = 1;
+  const int grid = (M + LP_ROWS - 1) / LP_ROWS;
+  const cudaStream_t st = (cudaStream_t)stream;
   const __half *xh = (const __half*)x, *wh = (const __half*)w;
   __half* oh = (__half*)out;
-  cudaError_t le;
-  switch ((r + 7) / 8) {
-    case 1: le = cudaLaunchKernelEx(&cfg, lora_project_kernel<1>, xh, wh, oh, M, C, r, scale); break;
-    case 2: le = cudaLaunchKernelEx(&cfg, lora_project_kernel<2>, xh, wh, oh, M, C, r, scale); break;
-    case 3: case 4: le = cudaLaunchKernelEx(&cfg, lora_project_kernel<4>, xh, wh, oh, M, C, r, scale); break;
-    default: le = cudaLaunchKernelEx(&cfg, lora_project_kernel<8>, xh, wh, oh, M, C, r, scale); break;
+  static std::atomic<bool> attr_done[64];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev < 0 || dev >= 64 || !attr_done[dev].load(std::memory_order_acquire)) {
+    if (int e = check_cuda(cudaFuncSetAttribute(lora_project_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lora_project_smem<4>()), "lora_project smem attribute")) return e;
+    if (int e = check_cuda(cudaFuncSetAttribute(lora_project_kernel<8>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lora_project_smem<8>()), "lora_project smem attribute")) return e;
+    if (int e = check_cuda(cudaFuncSetAttribute(lora_project_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lora_project_smem<2>()), "lora_project smem attribute")) return e;
+    if (int e = check_cuda(cudaFuncSetAttribute(lora_project_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)lora_project_smem<1>()), "lora_project smem attribute")) return e;
+    if (dev >= 0 && dev < 64) attr_done[dev].store(true, std::memory_order_release);
   }
-  if (le != cudaSuccess) return check_cuda(le, "lora_project launch");
+  switch ((r + 7) / 8) {
+    case 1: lora_project_kernel<1><<<grid, LP_THREADS, lora_project_smem<1>(), st>>>(xh, wh, oh, M, C, r, scale); break;
+    case 2: lora_project_kernel<2><<<grid, LP_THREADS, lora_project_smem<2>(), st>>>(xh, wh, oh, M, C, r, scale); break;
+    case 3: case 4: lora_project_kernel<4><<<grid, LP_THREADS, lora_project_smem<4>(), st>>>(xh, wh, oh, M, C, r, scale); break;
+    default: lora_project_kernel<8><<<grid, LP_THREADS, lora_project_smem<8>(), st>>>(xh, wh, oh, M, C, r, scale); break;
+  }
   return check_cuda(cudaGetLastError(), "lora_project launch");
 }
 
