@@ -61,7 +61,7 @@ _SIGNATURES = {
     "q4_lora_project": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, ctypes.c_float, c_void_p]),
     "q4_lora_grads": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),
     "q4_adamw_flat": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_size_t, ctypes.c_float, ctypes.c_float, ctypes.c_float,
-                              ctypes.c_float, ctypes.c_float, ctypes.c_float, c_void_p, ctypes.c_float, ctypes.c_float, c_int, c_void_p]),
+                              ctypes.c_float, ctypes.c_float, ctypes.c_float, c_void_p, ctypes.c_float, ctypes.c_float, c_int, c_void_p, c_void_p]),
     "q4_device_status": (c_int, [ctypes.POINTER(c_uint)]),
     "q4_gemv_status": (c_int, [c_void_p, c_size_t, ctypes.POINTER(c_uint)]),
     "q4_gemv_static_status": (c_int, [ctypes.POINTER(c_uint)]),

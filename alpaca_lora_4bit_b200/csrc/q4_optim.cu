@@ -32,7 +32,8 @@ flat_nonfinite_kernel(const float* __restrict__ grad, size_t n, float* __restric
 
 __global__ void __launch_bounds__(OPT_THREADS)
 flat_adamw_kernel(float* __restrict__ param, const float* __restrict__ grad, float* __restrict__ m, float* __restrict__ v, size_t n,
-                  float lr, float beta1, float beta2, float eps, float weight_decay, float grad_div, const float* __restrict__ state) {
+                  float lr, float beta1, float beta2, float eps, float weight_decay, float grad_div, const float* __restrict__ state,
+                  __half* __restrict__ shadow) {
   if (state[3] != 0.f) return;                                       // non-finite gradients: the step is skipped
   const float step = state[0] + 1.f;
   const float inv = 1.f / (state[1] * grad_div);
@@ -44,7 +45,9 @@ flat_adamw_kernel(float* __restrict__ param, const float* __restrict__ grad, flo
     const float vi = beta2 * v[i] + (1.f - beta2) * g * g;
     m[i] = mi;
     v[i] = vi;
-    param[i] = param[i] * decay - step_size * (mi / (sqrtf(vi) * inv_sqrt_bc2 + eps));
+    const float pn = param[i] * decay - step_size * (mi / (sqrtf(vi) * inv_sqrt_bc2 + eps));
+    param[i] = pn;
+    if (shadow) shadow[i] = __float2half_rn(pn);                       // the fp16 copy the kernels of the next step read
   }
 }
 
@@ -71,7 +74,7 @@ using namespace q4;
 
 extern "C" int q4_adamw_flat(float* param, const float* grad, float* exp_avg, float* exp_avg_sq, size_t n, float lr, float beta1,
                              float beta2, float eps, float weight_decay, float grad_div, float* state, float growth, float backoff,
-                             int growth_interval, q4_stream_t stream) {
+                             int growth_interval, void* half_shadow, q4_stream_t stream) {
   if (!param || !grad || !exp_avg || !exp_avg_sq || !state) return fail(Q4_E_BADARG, "adamw_flat: null pointer");
   if (n == 0) return Q4_OK;
   if (!aligned16(grad)) return fail(Q4_E_ALIGN, "adamw_flat: the gradient buffer must be 16-byte aligned");
@@ -82,7 +85,8 @@ extern "C" int q4_adamw_flat(float* param, const float* grad, float* exp_avg, fl
   const size_t want = (n + OPT_THREADS - 1) / OPT_THREADS;
   const int grid = (int)(want < (size_t)(8 * sm_count()) ? want : (size_t)(8 * sm_count()));
   flat_nonfinite_kernel<<<grid, OPT_THREADS, 0, st>>>(grad, n, state);
-  flat_adamw_kernel<<<grid, OPT_THREADS, 0, st>>>(param, grad, exp_avg, exp_avg_sq, n, lr, beta1, beta2, eps, weight_decay, grad_div, state);
+  flat_adamw_kernel<<<grid, OPT_THREADS, 0, st>>>(param, grad, exp_avg, exp_avg_sq, n, lr, beta1, beta2, eps, weight_decay, grad_div, state,
+                                                  (__half*)half_shadow);
   scale_update_kernel<<<1, 1, 0, st>>>(state, growth, backoff, growth_interval);
   return check_cuda(cudaGetLastError(), "adamw_flat launch");
 }

@@ -170,12 +170,22 @@ class FlatAdamW:
                  backoff_factor: float = 0.5, growth_interval: int = 2000):
         dev = params[0].device
         total = flat.buffer.numel()
+        self.params = params
         self.param = torch.empty(total, dtype=torch.float32, device=dev)
         off = 0
         for p in params:
             n = p.numel()
             self.param[off:off + n].copy_(p.data.reshape(-1))
             p.data = self.param[off:off + n].view_as(p)
+            off += n
+        # fp16 copy of the parameters, refreshed by the optimiser kernel: the LoRA kernels compute in fp16 and would
+        # otherwise cast every factor on every use (three times per step under checkpointing)
+        self.param_h = self.param.to(torch.float16)
+        off = 0
+        for p in params:
+            n = p.numel()
+            p._q4_half = self.param_h[off:off + n].view_as(p)
+            p._q4_half_version = p._version            # an in-place write to the parameter invalidates the copy (see refresh_half)
             off += n
         self.grad = flat.buffer
         self.exp_avg = torch.zeros_like(self.param)
@@ -188,6 +198,13 @@ class FlatAdamW:
     def scale(self, loss: torch.Tensor) -> torch.Tensor:
         return loss.float() * self.state[1]
 
+    def refresh_half(self) -> None:
+        """Re-derive the fp16 copies after the parameters were written by anything but ``step`` (a loaded adapter,
+        a manual edit): the kernels read the copies, and a captured step reads them without asking."""
+        self.param_h.copy_(self.param)
+        for p in self.params:
+            p._q4_half_version = p._version
+
     def step(self, grad_div: float = 1.0) -> None:
         from . import _lib
         with _lib.on_device(self.param.device):
@@ -195,7 +212,7 @@ class FlatAdamW:
                                                 self.exp_avg_sq.data_ptr(), self.param.numel(), self.lr, self.betas[0], self.betas[1],
                                                 self.eps, self.weight_decay, float(grad_div), self.state.data_ptr(),
                                                 self.growth_factor, self.backoff_factor, self.growth_interval,
-                                                _lib.stream_of(self.param)), "adamw_flat")
+                                                self.param_h.data_ptr(), _lib.stream_of(self.param)), "adamw_flat")
 
     @property
     def steps_taken(self) -> int:
@@ -244,6 +261,8 @@ class LoraFinetuner:
         if not example_ids.is_cuda:
             return False
         try:
+            if isinstance(self.opt, FlatAdamW):
+                self.opt.refresh_half()            # the captured kernels read the fp16 copies as they are replayed
             self._static_ids = example_ids.clone()
             side = torch.cuda.Stream(device=example_ids.device)
             side.wait_stream(torch.cuda.current_stream(example_ids.device))

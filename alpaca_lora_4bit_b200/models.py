@@ -102,6 +102,15 @@ def _lora_project(x2: torch.Tensor, w: torch.Tensor, scaling: float) -> torch.Te
     return out
 
 
+def _half_of(p: torch.Tensor) -> torch.Tensor:
+    """fp16 contiguous copy of a LoRA factor: the copy its optimiser keeps beside it (``_q4_half``, refreshed by the
+    flat AdamW kernel) when there is one, else a cast."""
+    h = getattr(p, "_q4_half", None)
+    if h is not None and h.shape == p.shape and h.device == p.device and getattr(p, "_q4_half_version", -1) == p._version:
+        return h
+    return p.detach().to(torch.float16).contiguous()
+
+
 class LoraMatmul4bit(torch.autograd.Function):
     """``y = x @ W + bias + scaling * (x @ A^T) @ B^T`` over a 4-bit v2 layer in one fused kernel, with
     the matching backward ``dx = dy @ W^T + scaling * (dy @ B) @ A`` (also one kernel) and the LoRA
@@ -121,8 +130,7 @@ class LoraMatmul4bit(torch.autograd.Function):
         x2 = x.reshape(-1, K)
         if x2.dtype != torch.float16 or not x2.is_contiguous():
             x2 = x2.to(torch.float16).contiguous()
-        a_h = lora_a.detach().to(torch.float16).contiguous()                     # [r, K]
-        b_h = lora_b.detach().to(torch.float16).contiguous()                     # [N, r]
+        a_h, b_h = _half_of(lora_a), _half_of(lora_b)                            # [r, K], [N, r]
         u = _lora_project(x2, a_h, scaling)                                      # [M, 64], scaling folded in
         y = torch.empty((x2.shape[0], N), dtype=torch.float16, device=x.device)
         quant_cuda.gemm(x2, qweight, y, scales.half(), qzeros, g_idx, bias=None if bias is None else bias.half(),
@@ -144,13 +152,13 @@ class LoraMatmul4bit(torch.autograd.Function):
             dy = dy.to(torch.float16).contiguous()
         M = dy.shape[0]
         # v = scaling * dy @ B: the projection kernel wants its small operand as [r, N]
-        bt_h = lora_b.detach().t().to(torch.float16, memory_format=torch.contiguous_format)
+        bt_h = _half_of(lora_b).t().contiguous()
         v = _lora_project(dy, bt_h, ctx.scaling)
         dx = d_a = d_b = None
         if ctx.needs_input_grad[0]:
             dx = torch.empty((M, K), dtype=torch.float16, device=dy.device)
             quant_cuda.gemm(dy, qweight, dx, scales.half(), qzeros, g_idx, transpose=True,
-                            lora_u=v, lora_w=lora_a.detach().to(torch.float16).contiguous())
+                            lora_u=v, lora_w=_half_of(lora_a))
             dx = dx.reshape(ctx.x_shape).to(ctx.x_dtype)
         want_a, want_b = ctx.needs_input_grad[1], ctx.needs_input_grad[2]
         if want_a or want_b:

@@ -245,10 +245,12 @@ int q4_lora_grads(const void* v, const void* x, float* d_a, int K, const void* d
  * grad / (state[1] * grad_div)  (grad_div: the number of ranks whose gradients were summed into `grad`);
  * (3) a skipped step multiplies the scale by `backoff`, `growth_interval` clean steps in a row multiply it by
  * `growth` (growth_interval 0: the scale is static), the step count advances and the flag is cleared.
- * Nothing returns to the host, so the call can be captured in a CUDA graph. */
+ * `half_shadow` (n halves, or NULL) receives the updated parameters rounded to fp16, which is what the LoRA kernels
+ * of the next step read (a skipped step leaves it as it was).  Nothing returns to the host, so the call can be
+ * captured in a CUDA graph. */
 int q4_adamw_flat(float* param, const float* grad, float* exp_avg, float* exp_avg_sq, size_t n, float lr, float beta1,
                   float beta2, float eps, float weight_decay, float grad_div, float* state, float growth, float backoff,
-                  int growth_interval, q4_stream_t stream);
+                  int growth_interval, void* half_shadow, q4_stream_t stream);
 
 /* Copies the device status word to *out (synchronises the device): 0, or 0xDEAD0001 if a bounded
  * wait inside a q4_gemm_* kernel expired (its output is then invalid). */

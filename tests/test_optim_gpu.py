@@ -65,3 +65,24 @@ def test_gradients_summed_over_ranks_are_divided():
     # the parameters are views of one buffer, in order
     assert ours[0].data_ptr() == opt.param.data_ptr()
     assert ours[1].data_ptr() == opt.param.data_ptr() + 4 * ours[0].numel()
+
+
+def test_half_copies_follow_the_parameters():
+    """The optimiser kernel keeps an fp16 copy of every parameter for the LoRA kernels (``_q4_half``); an in-place
+    write to a parameter makes ``models._half_of`` cast again until ``refresh_half``."""
+    from alpaca_lora_4bit_b200 import models
+    ps = _params(7)
+    flat = fs.FlatGrads(ps)
+    opt = fs.FlatAdamW(ps, flat, lr=1e-2, init_scale=1.0, dynamic=False)
+    for p in ps:
+        assert torch.equal(p._q4_half, p.detach().half()) and models._half_of(p) is p._q4_half
+    for p in ps:
+        p.grad.copy_(torch.randn(p.shape, device=DEV))
+    opt.step()
+    for p in ps:
+        assert torch.equal(p._q4_half, p.detach().half()) and models._half_of(p) is p._q4_half
+    with torch.no_grad():
+        ps[0].mul_(2.0)
+    assert models._half_of(ps[0]) is not ps[0]._q4_half and torch.equal(models._half_of(ps[0]), ps[0].detach().half())
+    opt.refresh_half()
+    assert models._half_of(ps[0]) is ps[0]._q4_half and torch.equal(ps[0]._q4_half, ps[0].detach().half())
