@@ -44,14 +44,16 @@ class AutogradMatmul4bitCuda(torch.autograd.Function):
 
     @staticmethod
     @custom_fwd(device_type="cuda", cast_inputs=torch.float16)
-    def forward(ctx, x, qweight, scales, zeros, g_idx, bits, maxq, bias=None):
+    def forward(ctx, x, qweight, scales, zeros, g_idx, bits, maxq, bias=None, residual=None):
         """``bias`` (not an argument of the reference's function, whose module adds the bias in a kernel of
-        its own, autograd_4bit.py:204-206): added in the epilogue of the fused product where that runs."""
+        its own, autograd_4bit.py:204-206) and ``residual`` (the skip path a decoder layer adds after the
+        projection): added in the epilogue of the fused product where that runs."""
         ctx.save_for_backward(qweight, scales, zeros, g_idx)
         if g_idx is None:
             out = mm4b._matmul4bit_v1_recons(x, qweight, scales, zeros)
-            return out if bias is None else out + bias.to(out.dtype)
-        return mm4b._matmul4bit_v2_recons(x, qweight, scales, zeros, g_idx, bias=bias)
+            out = out if bias is None else out + bias.to(out.dtype)
+            return out if residual is None else out + residual.to(out.dtype)
+        return mm4b._matmul4bit_v2_recons(x, qweight, scales, zeros, g_idx, bias=bias, residual=residual)
 
     @staticmethod
     @custom_bwd(device_type="cuda")
@@ -63,7 +65,8 @@ class AutogradMatmul4bitCuda(torch.autograd.Function):
                 grad = mm4b._matmul4bit_v1_recons(grad_output, qweight, scales, zeros, transpose=True)
             else:
                 grad = mm4b._matmul4bit_v2_recons(grad_output, qweight, scales, zeros, g_idx, transpose=True)
-        return grad, None, None, None, None, None, None, None
+        res_grad = grad_output if (len(ctx.needs_input_grad) > 8 and ctx.needs_input_grad[8]) else None
+        return (grad, None, None, None, None, None, None, None, res_grad)[:max(len(ctx.needs_input_grad), 7)]
 
 
 class AutogradMatmul2bitCuda(torch.autograd.Function):
@@ -143,14 +146,32 @@ class Autograd4bitQuantLinear(nn.Module):
         self.register_buffer('bias', torch.zeros(out_features))
         self.register_buffer('qweight', torch.empty((in_features // per_word, out_features), dtype=torch.int32))
 
+    def take_residual(self):
+        """The skip-path tensor a patched decoder layer left for this call (``offer_residual``), or None: whoever
+        computes this module's output adds it, in the product's epilogue where that is possible."""
+        return self.__dict__.pop("_q4_residual", None)
+
+    def offer_residual(self, residual) -> None:
+        """Called by a decoder layer patched by ``fused_ops.patch_llama`` right before the block that ends in this
+        projection: the next ``forward`` returns ``projection + residual``."""
+        self.__dict__["_q4_residual"] = residual
+
     def forward(self, x):
+        residual = self.take_residual()
+        out = self._forward(x, residual)
+        return out
+
+    def _forward(self, x, residual=None):
         zeros = self.zeros if self.is_v1_model else self.qzeros
         if self.bits == 4:
             if torch.is_grad_enabled():
                 if AutogradMatmul4bit is AutogradMatmul4bitCuda:
-                    # the bias rides in the product's epilogue instead of a second pass over the output
+                    # bias and residual ride in the product's epilogue instead of further passes over the output
                     bias = None if (self.disable_bias or self.bias is None) else self.bias
-                    return AutogradMatmul4bit.apply(x, self.qweight, self.scales, zeros, self.g_idx, self.bits, self.maxq, bias)
+                    if residual is not None and residual.dtype != torch.float16:
+                        out = AutogradMatmul4bit.apply(x, self.qweight, self.scales, zeros, self.g_idx, self.bits, self.maxq, bias)
+                        return out + residual.to(out.dtype)
+                    return AutogradMatmul4bit.apply(x, self.qweight, self.scales, zeros, self.g_idx, self.bits, self.maxq, bias, residual)
                 out = AutogradMatmul4bit.apply(x, self.qweight, self.scales, zeros, self.g_idx, self.bits, self.maxq)
             else:
                 out = matmul4bit_with_backend(x, self.qweight, self.scales, zeros, self.g_idx, self.bits, self.maxq,
@@ -161,6 +182,8 @@ class Autograd4bitQuantLinear(nn.Module):
             raise ValueError('Unsupported bitwidth.')
         if not self.disable_bias and self.bias is not None:
             out = out + self.bias.to(out.dtype)
+        if residual is not None:
+            out = out + residual.to(out.dtype)
         return out
 
 

@@ -54,6 +54,7 @@ struct GemmParams {
   const uint32_t* qzeros;   // [G, N/8]
   const int* g_idx;         // [K]
   const __half* bias;       // [N_out] or null (forward only)
+  const __half* residual;   // [M, N_out] added to the output, or null (forward only)
   __half* out;              // [M, N_out]
   int M, K, N, G;
   int n_contract_tiles;     // contraction length / 64
@@ -295,7 +296,13 @@ q4_gemm_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__
               f0 += __half2float(p.bias[out0 + cb * 32 + 8 * q + 2 * e]);
               f1 += __half2float(p.bias[out0 + cb * 32 + 8 * q + 2 * e + 1]);
             }
-            ov[e] = as_u32(__floats2half2_rn(f0, f1));
+            __half2 hv = __floats2half2_rn(f0, f1);
+            if (!TRANSPOSE && p.residual) {              // rounded first, as the separate add of the decoder layer would see it
+              const float2 rr = __half22float2(*reinterpret_cast<const __half2*>(p.residual + (size_t)m * n_out_total + out0 + cb * 32 + 8 * q + 2 * e));
+              const float2 yy = __half22float2(hv);
+              hv = __floats2half2_rn(yy.x + rr.x, yy.y + rr.y);
+            }
+            ov[e] = as_u32(hv);
           }
           *reinterpret_cast<uint4*>(dst + 8 * q) = o;
         }
@@ -353,7 +360,7 @@ static long long gemm2_estimate(int M, int nout, int T, int P, int mh, bool ws_o
 static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, void* out, const void* scales,
                        const int32_t* qzeros, const int32_t* g_idx, const void* bias, const void* lora_u,
                        const void* lora_w, int lora_r, int M, int K, int N, int G, void* workspace, size_t workspace_bytes,
-                       q4_stream_t stream, bool swiglu = false, const void* zp_cached = nullptr) {
+                       q4_stream_t stream, bool swiglu = false, const void* zp_cached = nullptr, const void* residual = nullptr) {
   if (!act || !qweight || !out || !scales || !qzeros || !g_idx) return fail(Q4_E_BADARG, "gemm: null pointer");
   if (M <= 0 || K <= 0 || N <= 0 || G <= 0) return fail(Q4_E_BADARG, "gemm: M=%d K=%d N=%d G=%d", M, K, N, G);
   if (K % 128 || N % 128) return fail(Q4_E_SHAPE, "gemm: K=%d and N=%d must be multiples of 128", K, N);
@@ -363,6 +370,7 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
   if (lora_r > 0 && (!lora_u || !lora_w || !aligned16(lora_u) || !aligned16(lora_w)))
     return fail(Q4_E_BADARG, "gemm: the low-rank term needs 16-byte aligned lora_u [M,64] and lora_w");
   if (workspace && !aligned16(workspace)) return fail(Q4_E_ALIGN, "gemm: the workspace must be 16-byte aligned");
+  if (residual && (transpose || swiglu || !aligned16(residual))) return fail(Q4_E_BADARG, "gemm: a residual needs the plain forward and 16-byte alignment");
   if (int e = check_device()) return e;
   const int contract = transpose ? N : K, nout = transpose ? K : N;
   // forward with the caller's zero-term table: scales and zero terms come from L2 as in the backward, and the
@@ -402,6 +410,7 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
   GemmParams p;
   p.qw = (const uint32_t*)qweight; p.scales = (const __half*)scales; p.qzeros = (const uint32_t*)qzeros;
   p.g_idx = g_idx; p.bias = (const __half*)bias; p.out = (__half*)out;
+  p.residual = (!transpose && !swiglu) ? (const __half*)residual : nullptr;
   p.M = M; p.K = K; p.N = N; p.G = G;
   p.n_contract_tiles = contract / GM_TILE_C;
   p.stages = stages;
@@ -564,6 +573,15 @@ extern "C" int q4_gemm_fwd_table(const void* x, const int32_t* qweight, void* y,
   if (!zero_terms || !aligned16(zero_terms)) return fail(Q4_E_BADARG, "gemm_fwd_table: needs a 16-byte aligned zero-term table");
   return gemm_launch(false, x, qweight, y, scales, qzeros, g_idx, bias, lora_u, lora_b, lora_r, M, K, N, G, workspace, workspace_bytes, stream,
                      false, zero_terms);
+}
+
+extern "C" int q4_gemm_fwd_residual(const void* x, const int32_t* qweight, void* y, const void* scales, const int32_t* qzeros,
+                                    const void* zero_terms, const int32_t* g_idx, const void* bias, const void* residual,
+                                    const void* lora_u, const void* lora_b, int lora_r, int M, int K, int N, int G, void* workspace,
+                                    size_t workspace_bytes, q4_stream_t stream) {
+  if (zero_terms && !aligned16(zero_terms)) return fail(Q4_E_ALIGN, "gemm_fwd_residual: the zero-term table must be 16-byte aligned");
+  return gemm_launch(false, x, qweight, y, scales, qzeros, g_idx, bias, lora_u, lora_b, lora_r, M, K, N, G, workspace, workspace_bytes, stream,
+                     false, zero_terms, residual);
 }
 
 extern "C" int q4_gemm_set_variant(int variant) {

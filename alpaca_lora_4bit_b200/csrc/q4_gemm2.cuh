@@ -417,6 +417,19 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
           }
           o[e] = as_u32(__floats2half2_rn(f0, f1));
         }
+        if (!TRANSPOSE && !SWIGLU && p.residual) {         // y = x W + bias + residual: the add of the decoder layer's skip path
+          const uint4* rp = reinterpret_cast<const uint4*>(p.residual + (size_t)m * out_pitch + col0 + cb * 32);
+#pragma unroll
+          for (int q = 0; q < 4; ++q) {
+            const uint4 rv = __ldg(rp + q);
+            const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const float2 a = __half22float2(as_h2(o[4 * q + e])), b = __half22float2(as_h2(rw[e]));
+              o[4 * q + e] = as_u32(__floats2half2_rn(a.x + b.x, a.y + b.y));
+            }
+          }
+        }
         if (out_aligned32) {                               // whole 32-byte sectors per store instruction
           asm volatile("st.global.v8.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8};" ::"l"(dst), "r"(o[0]), "r"(o[1]), "r"(o[2]), "r"(o[3]),
                        "r"(o[4]), "r"(o[5]), "r"(o[6]), "r"(o[7]) : "memory");

@@ -152,12 +152,52 @@ def apply_rotary_pos_emb(q, k, cos, sin, unsqueeze_dim=1):
     return (q * cos) + (_rotate_half(q) * sin), (k * cos) + (_rotate_half(k) * sin)
 
 
+def _decoder_layer_forward(layer):
+    """``LlamaDecoderLayer.forward`` with the two skip-path adds handed to the projections that end the blocks
+    (``o_proj``, ``down_proj``): a quant linear that was offered the residual returns ``projection + residual``,
+    from its GEMM's epilogue where the fused kernel runs.  A projection that is not a quant linear, or a block that
+    never called it, leaves the add here."""
+    from .autograd_4bit import Autograd4bitQuantLinear
+
+    def closing(block, name):
+        proj = getattr(block, name, None)
+        return proj if isinstance(proj, Autograd4bitQuantLinear) else None
+
+    def forward(hidden_states, attention_mask=None, position_ids=None, past_key_values=None, use_cache=False,
+                position_embeddings=None, **kwargs):
+        residual = hidden_states
+        hidden_states = layer.input_layernorm(hidden_states)
+        proj = closing(layer.self_attn, "o_proj")
+        if proj is not None:
+            proj.offer_residual(residual)
+        hidden_states, _ = layer.self_attn(hidden_states=hidden_states, attention_mask=attention_mask, position_ids=position_ids,
+                                           past_key_values=past_key_values, use_cache=use_cache,
+                                           position_embeddings=position_embeddings, **kwargs)
+        if proj is None or proj.take_residual() is not None:          # not taken: the add is still owed
+            hidden_states = residual + hidden_states
+        residual = hidden_states
+        hidden_states = layer.post_attention_layernorm(hidden_states)
+        proj = closing(layer.mlp, "down_proj")
+        if proj is not None:
+            proj.offer_residual(residual)
+        hidden_states = layer.mlp(hidden_states)
+        if proj is None or proj.take_residual() is not None:
+            hidden_states = residual + hidden_states
+        return hidden_states
+
+    return forward
+
+
 def patch_llama(model: nn.Module) -> nn.Module:
-    """Route the RMSNorms, the SwiGLU products and the rotary embedding of a transformers LLaMA through the
-    fused operators above.  The norm and MLP modules are patched per instance; the rotary function is a
-    module-level name of ``transformers.models.llama.modeling_llama`` and is replaced there (the replacement
-    computes exactly the stock expression whenever the fused path does not apply)."""
+    """Route the RMSNorms, the SwiGLU products, the rotary embedding and the skip-path adds of a transformers LLaMA
+    through the fused operators above.  The norm, MLP and decoder-layer modules are patched per instance; the rotary
+    function is a module-level name of ``transformers.models.llama.modeling_llama`` and is replaced there (the
+    replacement computes exactly the stock expression whenever the fused path does not apply).  Call it before
+    anything wraps the layers' ``forward`` (gradient checkpointing)."""
     from transformers.models.llama import modeling_llama as ml
+    for mod in model.modules():
+        if isinstance(mod, ml.LlamaDecoderLayer) and "forward" not in mod.__dict__:
+            mod.forward = _decoder_layer_forward(mod)
     for mod in model.modules():
         if isinstance(mod, ml.LlamaRMSNorm):
             mod.forward = (lambda h, _m=mod: rms_norm(h, _m.weight, _m.variance_epsilon))

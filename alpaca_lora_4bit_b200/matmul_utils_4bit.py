@@ -132,10 +132,15 @@ def _with_bias(out, bias):
     return out if bias is None else out + bias.to(out.dtype)
 
 
-def _matmul4bit_v2_recons(x, qweight, scales, zeros, g_idx, transpose=False, bias=None):
+def _plus(out, residual):
+    return out if residual is None else out + residual.reshape(out.shape).to(out.dtype)
+
+
+def _matmul4bit_v2_recons(x, qweight, scales, zeros, g_idx, transpose=False, bias=None, residual=None):
     """Large-M product on a v2 layer (matmul_utils_4bit.py:114-127): ``x @ W`` or, with
-    ``transpose``, ``x @ W.T`` (the backward of the layer).  ``bias`` (forward only; not an argument of the
-    reference's function): added to the product, inside the kernel where the fused path runs."""
+    ``transpose``, ``x @ W.T`` (the backward of the layer).  ``bias`` and ``residual`` (forward only; not
+    arguments of the reference's function): added to the product - the residual to the rounded product, as a
+    separate fp16 add would - inside the kernel where the fused path runs."""
     if debug:
         print('_matmul4bit_v2_recons')
     _check_inner(x, qweight, 8, transpose)
@@ -148,8 +153,8 @@ def _matmul4bit_v2_recons(x, qweight, scales, zeros, g_idx, transpose=False, bia
         # sequential; any other goes to the decode kernel that looks the group of every row up.
         G = scales.shape[0]
         if not act_order and K % G == 0 and (K // G) % 32 == 0 and _groups_are_sequential(g_idx, G):
-            return _with_bias(_decode(x, qweight, scales, zeros, None, K // G, 0), bias)
-        return _with_bias(_decode(x, qweight, scales, zeros, g_idx, max(K // G, 1), _lib.GEMV_ACT_ORDER), bias)
+            return _plus(_with_bias(_decode(x, qweight, scales, zeros, None, K // G, 0), bias), residual)
+        return _plus(_with_bias(_decode(x, qweight, scales, zeros, g_idx, max(K // G, 1), _lib.GEMV_ACT_ORDER), bias), residual)
     if (fused_gemm and x.dtype == torch.float16 and scales.dtype == torch.float16
             and quant_cuda.gemm_supported(K, N, scales.shape[0], transpose)):
         x2 = x.reshape(-1, x.shape[-1])
@@ -158,11 +163,19 @@ def _matmul4bit_v2_recons(x, qweight, scales, zeros, g_idx, transpose=False, bia
         out = torch.empty((x2.shape[0], K if transpose else N), dtype=torch.float16, device=x.device)
         if x2.shape[0] > 0:                   # no rows: nothing to launch
             b16 = None if (bias is None or transpose) else (bias if bias.dtype == torch.float16 else bias.half())
-            quant_cuda.gemm(x2, qweight, out, scales, zeros, g_idx, transpose=transpose, bias=b16)
+            res2 = None
+            if residual is not None and not transpose and residual.dtype == torch.float16 and residual.numel() == out.numel():
+                res2 = residual.reshape(out.shape)
+                res2 = res2 if res2.is_contiguous() else None
+            quant_cuda.gemm(x2, qweight, out, scales, zeros, g_idx, transpose=transpose, bias=b16, residual=res2)
+            if residual is not None and res2 is None:
+                out = _plus(out, residual)
+        elif residual is not None:
+            out = _plus(out, residual)
         return out.reshape(x.shape[:-1] + (out.shape[-1],))
     buffer = get_buffer(qweight.shape, dtype=scales.dtype, device=qweight.device)
     quant_cuda.vecquant4recons_v2(qweight, buffer, scales, zeros, g_idx)
-    return _with_bias(_dense_matmul(x, buffer, transpose), None if transpose else bias)
+    return _plus(_with_bias(_dense_matmul(x, buffer, transpose), None if transpose else bias), None if transpose else residual)
 
 
 def _matmul2bit_v2_recons(x, qweight, scales, zeros, g_idx, transpose=False):

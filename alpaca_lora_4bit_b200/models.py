@@ -125,7 +125,7 @@ class LoraMatmul4bit(torch.autograd.Function):
 
     @staticmethod
     @custom_fwd(device_type="cuda")
-    def forward(ctx, x, lora_a, lora_b, scaling, qweight, scales, qzeros, g_idx, bias):
+    def forward(ctx, x, lora_a, lora_b, scaling, qweight, scales, qzeros, g_idx, bias, residual=None):
         K, N = qweight.shape[0] * 8, qweight.shape[1]
         x2 = x.reshape(-1, K)
         if x2.dtype != torch.float16 or not x2.is_contiguous():
@@ -133,8 +133,14 @@ class LoraMatmul4bit(torch.autograd.Function):
         a_h, b_h = _half_of(lora_a), _half_of(lora_b)                            # [r, K], [N, r]
         u = _lora_project(x2, a_h, scaling)                                      # [M, 64], scaling folded in
         y = torch.empty((x2.shape[0], N), dtype=torch.float16, device=x.device)
+        res2 = None
+        if residual is not None and residual.dtype == torch.float16 and residual.numel() == y.numel():
+            res2 = residual.reshape(y.shape)
+            res2 = res2 if res2.is_contiguous() else None
         quant_cuda.gemm(x2, qweight, y, scales.half(), qzeros, g_idx, bias=None if bias is None else bias.half(),
-                        lora_u=u, lora_w=b_h)
+                        lora_u=u, lora_w=b_h, residual=res2)
+        if residual is not None and res2 is None:
+            y = y + residual.reshape(y.shape).to(y.dtype)
         ctx.save_for_backward(x2, u, lora_a, lora_b, qweight, scales, qzeros, g_idx)
         ctx.scaling = scaling
         ctx.x_shape = x.shape
@@ -170,7 +176,8 @@ class LoraMatmul4bit(torch.autograd.Function):
                                                     M, r, _lib.stream_of(dy)), "lora_grads")
             d_a = ga.to(lora_a.dtype) if want_a else None
             d_b = gb.to(lora_b.dtype) if want_b else None
-        return dx, d_a, d_b, None, None, None, None, None, None
+        d_res = grad_output if (len(ctx.needs_input_grad) > 9 and ctx.needs_input_grad[9]) else None
+        return (dx, d_a, d_b, None, None, None, None, None, None, d_res)[:max(len(ctx.needs_input_grad), 9)]
 
 
 class Linear4bitLt(Autograd4bitQuantLinear, _LoraBase):
@@ -211,12 +218,15 @@ class Linear4bitLt(Autograd4bitQuantLinear, _LoraBase):
         return name
 
     def forward(self, x: torch.Tensor):
+        residual = self.take_residual()                   # left by a patched decoder layer: this call returns projection + residual
         name = self._fused_adapter(x)
         if name is not None:
             bias = None if (self.disable_bias or self.bias is None) else self.bias
             return LoraMatmul4bit.apply(x, self.lora_A[name].weight, self.lora_B[name].weight, self.scaling[name],
-                                        self.qweight, self.scales, self.qzeros, self.g_idx, bias)
-        result = Autograd4bitQuantLinear.forward(self, x)
+                                        self.qweight, self.scales, self.qzeros, self.g_idx, bias, residual)
+        result = Autograd4bitQuantLinear._forward(self, x, None)
+        if residual is not None:
+            result = result + residual.to(result.dtype)
         if self.disable_adapters:
             return result
         previous_dtype = result.dtype

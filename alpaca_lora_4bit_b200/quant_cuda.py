@@ -286,19 +286,22 @@ def _zero_terms(scales, zeros, G, N, st):
     return table
 
 
-def gemm(x, qweight, out, scales, zeros, g_idx, transpose=False, bias=None, lora_u=None, lora_w=None) -> None:
+def gemm(x, qweight, out, scales, zeros, g_idx, transpose=False, bias=None, lora_u=None, lora_w=None, residual=None) -> None:
     """Fused large-M product on the tensor cores: ``out = x @ W (+ bias)`` or, with ``transpose``,
     ``out = x @ W.T``; ``x``, ``out``, ``scales`` fp16, W never leaves shared memory.
 
     ``lora_u`` fp16 ``[M, 64]`` (columns beyond the rank zero) with ``lora_w`` adds the low-rank term in
     the same kernel: forward ``+ lora_u[:, :r] @ lora_w.T`` with ``lora_w = lora_B [N, r]``; transpose
-    ``+ lora_u[:, :r] @ lora_w`` with ``lora_w = lora_A [r, K]``."""
-    dev = _lib.require_cuda(x, qweight, out, scales, zeros, g_idx, bias, lora_u, lora_w)
+    ``+ lora_u[:, :r] @ lora_w`` with ``lora_w = lora_A [r, K]``.  ``residual`` fp16 ``[M, N]`` (forward only) is
+    added to the rounded product in the epilogue: ``out = half(half(x @ W + bias) + residual)``."""
+    dev = _lib.require_cuda(x, qweight, out, scales, zeros, g_idx, bias, lora_u, lora_w, residual)
     R, N = qweight.shape
     K = R * 8
     M = x.shape[0]
     G = scales.shape[0]
     inner, outer = (N, K) if transpose else (K, N)
+    if residual is not None and (transpose or residual.shape != (M, N) or residual.dtype != torch.float16 or not residual.is_contiguous()):
+        raise RuntimeError("quant_cuda: gemm takes a contiguous fp16 residual [M, N] with the forward product only")
     if x.shape != (M, inner) or out.shape != (M, outer):
         raise RuntimeError(f"quant_cuda: gemm shapes x{tuple(x.shape)} out{tuple(out.shape)} do not match the layer [{K},{N}]")
     if x.dtype != torch.float16 or out.dtype != torch.float16 or scales.dtype != torch.float16:
@@ -332,7 +335,11 @@ def gemm(x, qweight, out, scales, zeros, g_idx, transpose=False, bias=None, lora
             zt = None
             if cache_zero_terms and G >= forward_table_groups and N % 256 == 0 and groups_are_sequential(g_idx, G):
                 zt = _zero_terms(scales, zeros, G, N, st)
-            if zt is not None:
+            if residual is not None:
+                rc = L.q4_gemm_fwd_residual(x.data_ptr(), qweight.data_ptr(), out.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
+                                            _lib.ptr(zt), g_idx.data_ptr(), _lib.ptr(bias), residual.data_ptr(), _lib.ptr(lora_u),
+                                            _lib.ptr(lora_w), r, M, K, N, G, ws.data_ptr(), ws.numel(), st)
+            elif zt is not None:
                 rc = L.q4_gemm_fwd_table(x.data_ptr(), qweight.data_ptr(), out.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
                                          zt.data_ptr(), g_idx.data_ptr(), _lib.ptr(bias), _lib.ptr(lora_u), _lib.ptr(lora_w), r, M, K, N, G,
                                          ws.data_ptr(), ws.numel(), st)

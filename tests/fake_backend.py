@@ -43,12 +43,14 @@ def gemm_supported(K, N, G, transpose):
     return K % 128 == 0 and N % 128 == 0
 
 
-def gemm(x, qweight, out, scales, zeros, g_idx, transpose=False, bias=None):
+def gemm(x, qweight, out, scales, zeros, g_idx, transpose=False, bias=None, residual=None):
     w = orc.recons_v2(qweight, scales, zeros, g_idx).float()
     y = x.float() @ (w.t() if transpose else w)
     if bias is not None:
         y = y + bias.float()
     out.copy_(y)
+    if residual is not None:
+        out.add_(residual)
 
 
 @contextlib.contextmanager

@@ -102,3 +102,52 @@ def test_patched_llama_step_matches_stock():
         ml.apply_rotary_pos_emb = stock_rope
     assert abs(la - lb) <= 2e-3 * abs(la)
     assert rel(gb, ga) <= 2e-2
+
+
+def test_skip_path_adds_in_the_projection_epilogues():
+    """patch_llama hands the two residual adds of every decoder layer to o_proj / down_proj
+    (``q4_gemm_fwd_residual``): same logits and same LoRA gradients as the model with the stock layer forward,
+    where the adds are torch kernels; the product itself (quant_cuda.gemm with a residual) equals product + add to the bit."""
+    from alpaca_lora_4bit_b200 import quant_cuda, synth
+    layer = synth.make_layer(1024, 768, 128, False, seed=3).to(DEV)
+    x = synth.make_acts(300, 1024, seed=4).to(DEV)
+    res = synth.make_acts(300, 768, seed=5).to(DEV)
+    bias = (torch.randn(768, generator=torch.Generator().manual_seed(6)) * 0.1).half().to(DEV)
+    for variant in (0, 1, 2, 3):
+        quant_cuda.gemm_set_variant(variant)
+        try:
+            plain = torch.empty(300, 768, dtype=torch.float16, device=DEV)
+            quant_cuda.gemm(x, layer.qweight, plain, layer.scales, layer.qzeros, layer.g_idx, bias=bias)
+            fused = torch.empty_like(plain)
+            quant_cuda.gemm(x, layer.qweight, fused, layer.scales, layer.qzeros, layer.g_idx, bias=bias, residual=res)
+        finally:
+            quant_cuda.gemm_set_variant(0)
+        assert torch.equal(fused, plain + res), variant
+
+    ids = torch.randint(0, 256, (2, 96), generator=torch.Generator().manual_seed(8)).to(DEV)
+    shape = fs.LlamaShape(hidden_size=512, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=8,
+                          num_key_value_heads=4, vocab_size=256, max_position_embeddings=256)
+
+    def run(patch_layers):
+        model = fs.build_quant_llama(shape, DEV, groupsize=128, seed=2)
+        fs.add_lora(model, ["q_proj", "v_proj", "o_proj", "down_proj"], r=8, alpha=16, seed=3)
+        if patch_layers:
+            fused_ops.patch_llama(model)
+            assert "forward" in model.model.layers[0].__dict__
+        fs.apply_gradient_checkpointing(model)
+        model.train()
+        ft = fs.LoraFinetuner(model, lr=0.0, loss_scale=64.0, dynamic_scale=False)
+        loss = float(ft.step(ids))
+        torch.cuda.synchronize()
+        for layer_ in model.model.layers:                       # nothing is left behind on the projections
+            assert "_q4_residual" not in layer_.self_attn.o_proj.__dict__ and "_q4_residual" not in layer_.mlp.down_proj.__dict__
+        return loss, ft.flat.buffer.clone()
+
+    stock_rope = __import__("transformers.models.llama.modeling_llama", fromlist=["x"]).apply_rotary_pos_emb
+    try:
+        loss_p, g_p = run(True)
+    finally:
+        __import__("transformers.models.llama.modeling_llama", fromlist=["x"]).apply_rotary_pos_emb = stock_rope
+    loss_s, g_s = run(False)
+    assert abs(loss_p - loss_s) <= 2e-3 * abs(loss_s)
+    assert float((g_p - g_s).norm() / g_s.norm()) <= 2e-2
