@@ -48,7 +48,7 @@ _SIGNATURES = {
     "q4_gemm_workspace_bytes": (c_size_t, [c_int, c_int, c_int]),
     "q4_zero_term_table": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "q4_gemm_fwd_residual": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
+                                     c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "q4_gemm_fwd_table": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                                   c_int, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "q4_gemm_bwd_table": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,

@@ -70,7 +70,8 @@ struct GemmParams {
   // shared tile (indexed by the first contributing pair), zero between launches.
   float* ws_partials;
   unsigned* ws_counters;
-  const __half* zp_table;   // backward: rn(s * (z+1)) for every [group, column], or null
+  const __half* zp_table;   // rn(s * (z+1)) for every [group, column], or null
+  int seq_shift;            // > 0: the caller promises g_idx[k] == k >> seq_shift (sequential groups of 2^seq_shift rows)
 };
 
 __device__ __forceinline__ void gm_mark(unsigned long long* tr, int slot) {
@@ -360,7 +361,8 @@ static long long gemm2_estimate(int M, int nout, int T, int P, int mh, bool ws_o
 static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, void* out, const void* scales,
                        const int32_t* qzeros, const int32_t* g_idx, const void* bias, const void* lora_u,
                        const void* lora_w, int lora_r, int M, int K, int N, int G, void* workspace, size_t workspace_bytes,
-                       q4_stream_t stream, bool swiglu = false, const void* zp_cached = nullptr, const void* residual = nullptr) {
+                       q4_stream_t stream, bool swiglu = false, const void* zp_cached = nullptr, const void* residual = nullptr,
+                       int seq_groupsize = 0) {
   if (!act || !qweight || !out || !scales || !qzeros || !g_idx) return fail(Q4_E_BADARG, "gemm: null pointer");
   if (M <= 0 || K <= 0 || N <= 0 || G <= 0) return fail(Q4_E_BADARG, "gemm: M=%d K=%d N=%d G=%d", M, K, N, G);
   if (K % 128 || N % 128) return fail(Q4_E_SHAPE, "gemm: K=%d and N=%d must be multiples of 128", K, N);
@@ -379,7 +381,12 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
   int stages2 = gemm2_stages(transpose, G, 1), stages2w = gemm2_stages(transpose, G, 2);
   const int stages2_nt = may_drop_tables ? gemm2_stages(true, G, 1) : stages2, stages2w_nt = may_drop_tables ? gemm2_stages(true, G, 2) : stages2w;
   // the table is used where it buys a stage for both tile heights (or makes the pair kernel possible at all)
-  const bool no_tables = transpose || (may_drop_tables && stages2_nt > stages2 && stages2w_nt > stages2w);
+  // groups promised sequential (a power of two of at least 8 rows): the forward fetches a task's scales and zero terms
+  // one task ahead with its packed words, so the table is taken whether or not it buys a stage
+  int seq_shift = 0;
+  if (seq_groupsize >= 8 && (seq_groupsize & (seq_groupsize - 1)) == 0 && (long long)seq_groupsize * G >= K)
+    while ((1 << seq_shift) < seq_groupsize) ++seq_shift;
+  const bool no_tables = transpose || (may_drop_tables && ((stages2_nt > stages2 && stages2w_nt > stages2w) || seq_shift > 0));
   if (no_tables && !transpose) { stages2 = stages2_nt; stages2w = stages2w_nt; }
   const bool pair_ok = nout % G2_TILE_N == 0 && stages2 > 0;
   const bool wide_ok = nout % G2_TILE_N == 0 && stages2w > 0;
@@ -418,6 +425,7 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
   p.lora_w = lora_r > 0 ? (const __half*)lora_w : nullptr;
   p.lora_r = lora_r;
   p.ws_partials = nullptr; p.ws_counters = nullptr; p.zp_table = nullptr;
+  p.seq_shift = (!transpose && no_tables) ? seq_shift : 0;
   const int box_rows = use_pair ? 128 * mh : GM_TILE_M;    // activation rows one TMA copy brings
   CUtensorMap amap;
   if (int e = make_tmap_2d(&amap, act, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, (uint64_t)contract, (uint64_t)M,
@@ -577,11 +585,11 @@ extern "C" int q4_gemm_fwd_table(const void* x, const int32_t* qweight, void* y,
 
 extern "C" int q4_gemm_fwd_residual(const void* x, const int32_t* qweight, void* y, const void* scales, const int32_t* qzeros,
                                     const void* zero_terms, const int32_t* g_idx, const void* bias, const void* residual,
-                                    const void* lora_u, const void* lora_b, int lora_r, int M, int K, int N, int G, void* workspace,
-                                    size_t workspace_bytes, q4_stream_t stream) {
+                                    const void* lora_u, const void* lora_b, int lora_r, int M, int K, int N, int G,
+                                    int sequential_groupsize, void* workspace, size_t workspace_bytes, q4_stream_t stream) {
   if (zero_terms && !aligned16(zero_terms)) return fail(Q4_E_ALIGN, "gemm_fwd_residual: the zero-term table must be 16-byte aligned");
   return gemm_launch(false, x, qweight, y, scales, qzeros, g_idx, bias, lora_u, lora_b, lora_r, M, K, N, G, workspace, workspace_bytes, stream,
-                     false, zero_terms, residual);
+                     false, zero_terms, residual, zero_terms ? sequential_groupsize : 0);
 }
 
 extern "C" int q4_gemm_set_variant(int variant) {

@@ -302,7 +302,11 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         // (4096 x 4096 at 1024 rows, the same layer again and again: 41.9 -> 37.4 us with this line; 1 % of a
         // LLaMA-7B finetune step, where every layer's words come from HBM).
         if (it + 2 * GM_DEQ_GROUPS < wi.ke) asm volatile("prefetch.global.L2 [%0];" ::"l"(word_ptr(it + 2 * GM_DEQ_GROUPS)));
-        if (!TRANSPOSE) {
+        if (!TRANSPOSE && p.seq_shift > 0) {         // sequential groups by the caller's word: scales and zero terms ahead, no g_idx
+          const size_t at = (size_t)((it * GM_TILE_C + 8 * r) >> p.seq_shift) * N + out0 + 8 * chunk16;
+          R.ga = ldg_pinned_int4(p.scales + at);
+          R.gb = ldg_pinned_int4(p.zp_table + at);
+        } else if (!TRANSPOSE) {
           R.ga = ldg_pinned_int4(p.g_idx + it * GM_TILE_C + 8 * r);
           R.gb = ldg_pinned_int4(p.g_idx + it * GM_TILE_C + 8 * r + 4);
         } else if (pre_sz) {
@@ -365,6 +369,10 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
             deq_task_uniform(rows8, off, w, sv, zv);
           } else if (p.zp_table) deq_task_global_zp(rows8, off, w, tga, tgb, p.scales + ncol, p.zp_table + ncol, N);
           else deq_task_global(rows8, off, w, tga, tgb, p.scales + ncol, p.qzeros + (ncol >> 3), N);
+        } else if (p.seq_shift > 0) {                // forward, sequential groups: everything the task needs came with its words
+          const uint4 sv = make_uint4((uint32_t)C.ga.x, (uint32_t)C.ga.y, (uint32_t)C.ga.z, (uint32_t)C.ga.w);
+          const uint4 zv = make_uint4((uint32_t)C.gb.x, (uint32_t)C.gb.y, (uint32_t)C.gb.z, (uint32_t)C.gb.w);
+          deq_task_uniform(rows8, off, w, sv, zv);
         } else if (p.zp_table) {                     // forward without shared-memory tables: the caller keeps the zero terms
           const int ncol = out0 + 8 * chunk16;
           deq_task_global_zp(rows8, off, w, C.ga, C.gb, p.scales + ncol, p.zp_table + ncol, N);

@@ -267,7 +267,7 @@ def groups_are_sequential(g_idx, groups: int) -> bool:
 # (2 G N bytes per layer are kept instead, 1.6 % of the packed weights).  ``cache_zero_terms = False`` restores
 # the derivation per call.
 cache_zero_terms = True
-forward_table_groups = 64       # forward products of layers with this many groups or more read the kept table too
+promise_sequential_groups = True     # forward: tell the kernel that group = row / groupsize where that was checked
 _zero_term_tables: dict = {}
 
 
@@ -329,20 +329,18 @@ def gemm(x, qweight, out, scales, zeros, g_idx, transpose=False, bias=None, lora
                 rc = L.q4_gemm_bwd(x.data_ptr(), qweight.data_ptr(), out.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
                                    g_idx.data_ptr(), _lib.ptr(lora_u), _lib.ptr(lora_w), r, M, K, N, G, ws.data_ptr(), ws.numel(), st)
         else:
-            # Many sequential groups: the scale tables of all groups would cost the kernel a pipeline stage, so it is
-            # given the kept table and reads scales and zero terms from L2 instead (the library ignores the table where
-            # that gains no stage; with act-order every row of a task would need its own pair of loads: measured slower).
-            zt = None
-            if cache_zero_terms and G >= forward_table_groups and N % 256 == 0 and groups_are_sequential(g_idx, G):
+            # Sequential groups (checked once per layer): the kernel is given the kept table of zero terms and the word
+            # that group = row / groupsize, so that it fetches a task's scales and zero terms ahead with its packed
+            # words instead of building shared-memory tables of all groups per tile.  (With act-order every row of a
+            # task would need its own pair of loads: measured slower, so the table is not offered.)
+            zt, seq_gs = None, 0
+            if cache_zero_terms and N % 256 == 0 and K % G == 0 and groups_are_sequential(g_idx, G):
                 zt = _zero_terms(scales, zeros, G, N, st)
-            if residual is not None:
+                seq_gs = K // G if (zt is not None and promise_sequential_groups) else 0
+            if zt is not None or residual is not None:
                 rc = L.q4_gemm_fwd_residual(x.data_ptr(), qweight.data_ptr(), out.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
-                                            _lib.ptr(zt), g_idx.data_ptr(), _lib.ptr(bias), residual.data_ptr(), _lib.ptr(lora_u),
-                                            _lib.ptr(lora_w), r, M, K, N, G, ws.data_ptr(), ws.numel(), st)
-            elif zt is not None:
-                rc = L.q4_gemm_fwd_table(x.data_ptr(), qweight.data_ptr(), out.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
-                                         zt.data_ptr(), g_idx.data_ptr(), _lib.ptr(bias), _lib.ptr(lora_u), _lib.ptr(lora_w), r, M, K, N, G,
-                                         ws.data_ptr(), ws.numel(), st)
+                                            _lib.ptr(zt), g_idx.data_ptr(), _lib.ptr(bias), _lib.ptr(residual), _lib.ptr(lora_u),
+                                            _lib.ptr(lora_w), r, M, K, N, G, seq_gs, ws.data_ptr(), ws.numel(), st)
             else:
                 rc = L.q4_gemm_fwd(x.data_ptr(), qweight.data_ptr(), out.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
                                    g_idx.data_ptr(), _lib.ptr(bias), _lib.ptr(lora_u), _lib.ptr(lora_w), r, M, K, N, G,

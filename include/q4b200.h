@@ -191,11 +191,15 @@ int q4_gemm_fwd_table(const void* x, const int32_t* qweight, void* y, const void
                       int lora_r, int M, int K, int N, int G, void* workspace, size_t workspace_bytes, q4_stream_t stream);
 /* The forward with the skip path of a decoder layer in its epilogue: y = half(half(x W + bias) + residual),
  * residual fp16 [M, N] (the two roundings of the product followed by the fp16 add that LlamaDecoderLayer.forward
- * runs after o_proj and down_proj).  `zero_terms` as for q4_gemm_fwd_table, or NULL; `residual` may be NULL. */
+ * runs after o_proj and down_proj).  `zero_terms` as for q4_gemm_fwd_table, or NULL; `residual` may be NULL.
+ * `sequential_groupsize` (with a table only; 0 = no promise): the caller's word that g_idx[k] == k / groupsize for a
+ * groupsize that is a power of two - the kernel then does not read g_idx at all, fetches a dequant task's scales
+ * and zero terms one task ahead with its packed words and builds no shared-memory tables (a wrong promise gives
+ * wrong products, nothing worse). */
 int q4_gemm_fwd_residual(const void* x, const int32_t* qweight, void* y, const void* scales, const int32_t* qzeros,
                          const void* zero_terms, const int32_t* g_idx, const void* bias, const void* residual,
-                         const void* lora_u, const void* lora_b, int lora_r, int M, int K, int N, int G, void* workspace,
-                         size_t workspace_bytes, q4_stream_t stream);
+                         const void* lora_u, const void* lora_b, int lora_r, int M, int K, int N, int G,
+                         int sequential_groupsize, void* workspace, size_t workspace_bytes, q4_stream_t stream);
 /* Optional scratch for the two calls above (no reference counterpart: the reference's scratch is
  * the dense fp16 copy of W it reconstructs).  `workspace` may be NULL; with at least
  * q4_gemm_workspace_bytes(K, N, G) bytes of device memory, 16-byte aligned, whose first 64 KiB are

@@ -365,3 +365,45 @@ def test_backward_with_cached_zero_terms_is_the_same_product():
     del layer, table
     gc.collect()
     assert key not in quant_cuda._zero_term_tables
+
+
+@pytest.mark.parametrize("M,K,N,g", [(300, 1024, 768, 128), (129, 1024, 256, -1), (520, 2048, 512, 32), (70, 11008, 256, 128),
+                                     (40, 11008, 256, -1), (260, 1536, 512, 8)])
+def test_forward_with_sequential_groups_promised_is_the_same_product(M, K, N, g):
+    """Layers without act-order: quant_cuda.gemm hands the forward the kept zero-term table and the word that
+    group = row / groupsize (``sequential_groupsize`` of q4_gemm_fwd_residual), and the kernel fetches scales and
+    zero terms with a task's packed words instead of building tables per tile.  Same bits as the kernel with its
+    shared-memory tables and as the kept table read through g_idx (no promise; q4_gemm_fwd_table), for group sizes
+    down to the 8 rows of a task, one group over all rows (a power of two, or 11008 rows where no shift exists and
+    the promise is dropped by the library) and in the 512-row form."""
+    from alpaca_lora_4bit_b200 import _lib
+    layer = synth.make_layer(K, N, g, False, seed=K + N).to(DEV)
+    x = synth.make_acts(M, K, seed=M).to(DEV)
+    outs = {}
+    tables_fit = layer.scales.shape[0] <= 128      # 192 groups of tables leave the CTA-pair kernel no stage: the kept table is what admits it
+    for variant in (2, 3):
+        try:
+            for mode, cached, promise in (("smem", False, False), ("table", True, False), ("promised", True, True)):
+                quant_cuda.gemm_set_variant(variant if (cached or tables_fit) else 0)
+                quant_cuda.cache_zero_terms, quant_cuda.promise_sequential_groups = cached, promise
+                y = torch.empty(M, N, dtype=torch.float16, device=DEV)
+                quant_cuda.gemm(x, layer.qweight, y, layer.scales, layer.qzeros, layer.g_idx)
+                outs[variant, mode] = y
+            table = quant_cuda._zero_term_tables[id(layer.qzeros)][0]
+            y = torch.empty(M, N, dtype=torch.float16, device=DEV)
+            st = torch.cuda.current_stream().cuda_stream
+            ws = _lib.gemm_workspace_for(x.device, st, int(_lib.lib().q4_gemm_workspace_bytes(K, N, layer.scales.shape[0])))
+            rc = _lib.lib().q4_gemm_fwd_table(x.data_ptr(), layer.qweight.data_ptr(), y.data_ptr(), layer.scales.data_ptr(),
+                                              layer.qzeros.data_ptr(), table.data_ptr(), layer.g_idx.data_ptr(), None, None, None, 0,
+                                              M, K, N, layer.scales.shape[0], ws.data_ptr(), ws.numel(), st)
+            assert rc == 0
+            outs[variant, "abi"] = y
+        finally:
+            quant_cuda.gemm_set_variant(0)
+            quant_cuda.cache_zero_terms, quant_cuda.promise_sequential_groups = True, True
+        for mode in ("table", "promised", "abi"):
+            assert torch.equal(outs[variant, mode], outs[variant, "smem"]), (variant, mode)
+    assert quant_cuda.device_status() == 0
+    host = layer.to("cpu")
+    want = orc.matmul4bit_ref(x.cpu(), host.qweight, host.scales, host.qzeros, host.g_idx)
+    assert rel_fro(outs[2, "promised"], want) <= REL_TOL
