@@ -53,8 +53,8 @@ _SIGNATURES = {
                                   c_int, c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "q4_gemm_bwd_table": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                   c_int, c_int, c_int, c_int, c_void_p, c_size_t, c_void_p]),
-    "q4_gemm_fwd_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
-                                   c_void_p, c_size_t, c_void_p]),
+    "q4_gemm_fwd_swiglu": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                   c_int, c_int, c_void_p, c_size_t, c_void_p]),
     "q4_rmsnorm_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, ctypes.c_float, c_void_p]),
     "q4_rmsnorm_bwd": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p]),
     "q4_swiglu_fwd": (c_int, [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]),

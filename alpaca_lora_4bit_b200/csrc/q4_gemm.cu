@@ -377,7 +377,7 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
   const int contract = transpose ? N : K, nout = transpose ? K : N;
   // forward with the caller's zero-term table: scales and zero terms come from L2 as in the backward, and the
   // shared memory the tables would take goes to pipeline stages (CTA-pair kernel only)
-  const bool may_drop_tables = !transpose && zp_cached != nullptr && !swiglu;
+  const bool may_drop_tables = !transpose && zp_cached != nullptr;
   int stages2 = gemm2_stages(transpose, G, 1), stages2w = gemm2_stages(transpose, G, 2);
   const int stages2_nt = may_drop_tables ? gemm2_stages(true, G, 1) : stages2, stages2w_nt = may_drop_tables ? gemm2_stages(true, G, 2) : stages2w;
   // the table is used where it buys a stage for both tile heights (or makes the pair kernel possible at all)
@@ -546,9 +546,11 @@ extern "C" int q4_gemm_fwd(const void* x, const int32_t* qweight, void* y, const
 }
 
 extern "C" int q4_gemm_fwd_swiglu(const void* x, const int32_t* qweight, void* out, const void* scales, const int32_t* qzeros,
-                                  const int32_t* g_idx, const void* bias, int M, int K, int N, int G, void* workspace,
-                                  size_t workspace_bytes, q4_stream_t stream) {
-  return gemm_launch(false, x, qweight, out, scales, qzeros, g_idx, bias, nullptr, nullptr, 0, M, K, N, G, workspace, workspace_bytes, stream, true);
+                                  const void* zero_terms, const int32_t* g_idx, const void* bias, int M, int K, int N, int G,
+                                  int sequential_groupsize, void* workspace, size_t workspace_bytes, q4_stream_t stream) {
+  if (zero_terms && !aligned16(zero_terms)) return fail(Q4_E_ALIGN, "gemm_fwd_swiglu: the zero-term table must be 16-byte aligned");
+  return gemm_launch(false, x, qweight, out, scales, qzeros, g_idx, bias, nullptr, nullptr, 0, M, K, N, G, workspace, workspace_bytes, stream,
+                     true, zero_terms, nullptr, zero_terms ? sequential_groupsize : 0);
 }
 
 extern "C" int q4_gemm_bwd(const void* dy, const int32_t* qweight, void* dx, const void* scales, const int32_t* qzeros,

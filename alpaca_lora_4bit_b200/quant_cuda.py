@@ -366,8 +366,12 @@ def gemm_swiglu(x, qweight, out, scales, zeros, g_idx, bias=None) -> None:
         if need is None:
             need = _gemm_ws_bytes[(K, N, G)] = int(L.q4_gemm_workspace_bytes(K, N, G))
         ws = _lib.gemm_workspace_for(dev, st, need)
+        zt, seq_gs = None, 0                    # sequential groups: kept zero-term table and the promise, as in gemm()
+        if cache_zero_terms and K % G == 0 and groups_are_sequential(g_idx, G):
+            zt = _zero_terms(scales, zeros, G, N, st)
+            seq_gs = K // G if (zt is not None and promise_sequential_groups) else 0
         rc = L.q4_gemm_fwd_swiglu(x.data_ptr(), qweight.data_ptr(), out.data_ptr(), scales.data_ptr(), zeros.data_ptr(),
-                                  g_idx.data_ptr(), _lib.ptr(bias), M, K, N, G, ws.data_ptr(), ws.numel(), st)
+                                  _lib.ptr(zt), g_idx.data_ptr(), _lib.ptr(bias), M, K, N, G, seq_gs, ws.data_ptr(), ws.numel(), st)
     _lib.check(rc, "gemm_swiglu")
 
 

@@ -167,10 +167,11 @@ int q4_gemm_bwd(const void* dy, const int32_t* qweight, void* dx, const void* sc
  * make_fused_mlp concatenates them, model_attn_mlp_patch.py:165-247 of the reference, which then computes
  * act_fn(gate) * up on the [M, 2 I] product, :229-232); out [M, I] fp16 = half(silu(half(x W_gate + b))) *
  * half(x W_up + b), the roundings of q4_gemm_fwd followed by q4_swiglu_fwd without the [M, 2 I] tensor ever
- * reaching memory.  N % 256 == 0; bias [N] or NULL; workspace as for q4_gemm_fwd. */
+ * reaching memory.  N % 256 == 0; bias [N] or NULL; workspace as for q4_gemm_fwd; `zero_terms` (the [G, N] table of
+ * q4_zero_term_table, or NULL) and `sequential_groupsize` as for q4_gemm_fwd_residual. */
 int q4_gemm_fwd_swiglu(const void* x, const int32_t* qweight, void* out, const void* scales, const int32_t* qzeros,
-                       const int32_t* g_idx, const void* bias, int M, int K, int N, int G, void* workspace,
-                       size_t workspace_bytes, q4_stream_t stream);
+                       const void* zero_terms, const int32_t* g_idx, const void* bias, int M, int K, int N, int G,
+                       int sequential_groupsize, void* workspace, size_t workspace_bytes, q4_stream_t stream);
 
 /* The backward with the layer's zero terms kept by the caller: q4_zero_term_table fills out [G, N] fp16 with
  * rn(scale * (zero + 1)) of every group and column (what q4_gemm_bwd otherwise derives into its workspace with

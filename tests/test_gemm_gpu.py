@@ -337,6 +337,20 @@ def test_gate_up_product_with_swiglu_in_the_epilogue(M, K, I, act):
             assert rel_fro(got, want) <= 1e-3, (variant, rel_fro(got, want))
             assert rel_fro(got, exact) <= 3e-3
             assert float((got == want).float().mean()) >= 0.98              # the same roundings: almost every element equal
+            if not act:                        # sequential groups: kept table and promise by default; same bits without either
+                for cached, promise in ((False, False), (True, False)):
+                    quant_cuda.gemm_set_variant(variant)
+                    quant_cuda.cache_zero_terms, quant_cuda.promise_sequential_groups = cached, promise
+                    try:
+                        other = torch.empty_like(got)
+                        quant_cuda.gemm_swiglu(x, layer.qweight, other, layer.scales, layer.qzeros, layer.g_idx, bias=b)
+                    finally:
+                        quant_cuda.gemm_set_variant(0)
+                        quant_cuda.cache_zero_terms, quant_cuda.promise_sequential_groups = True, True
+                    if variant:                # a fixed tile height: the same schedule, so the same sums
+                        assert torch.equal(other, got), (variant, cached, promise)
+                    else:
+                        assert rel_fro(other, got) <= 1e-3
     assert quant_cuda.device_status() == 0
 
 
