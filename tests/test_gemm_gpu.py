@@ -53,6 +53,39 @@ def test_gemm_selects_rows_of_w_bit_exactly(transpose):
     assert torch.equal(got.view(torch.int16), want.contiguous().view(torch.int16))
 
 
+@pytest.mark.parametrize("transpose", [False, True])
+@pytest.mark.parametrize("act", [False, True])
+@pytest.mark.parametrize("scale_case", ["usual", "subnormal", "large", "mixed"])
+def test_gemm_dequant_is_bit_exact_over_the_scale_range(scale_case, act, transpose):
+    """The same one-hot selection on the CTA-pair kernels (N a multiple of 256), for scales whose products are
+    subnormal, for scales of 2 and more - where a task of one group takes the three-instruction form of rn(s q)
+    instead of the fused multiply-add with -1024 s - and for layers that mix both in neighbouring columns; with
+    the kept zero-term table and the sequential-group promise (no act-order) and with shared-memory tables."""
+    layer = synth.make_layer(512, 512, 128, act, seed=7)
+    g = torch.Generator().manual_seed(3)
+    if scale_case == "subnormal":
+        layer.scales.mul_(2.0 ** -9)
+    elif scale_case == "large":
+        layer.scales.mul_(300.0)
+    elif scale_case == "mixed":
+        layer.scales.mul_(torch.where(torch.rand(512, generator=g) < 0.3, 300.0, 1.0).half())
+        layer.scales[1, 5] = 0.0
+    w = orc.recons_v2(layer.qweight, layer.scales, layer.qzeros, layer.g_idx)
+    x = torch.zeros((512, 512), dtype=torch.float16)
+    x[torch.arange(512), torch.arange(512)] = 1.0
+    want = w.t().contiguous() if transpose else w
+    for variant in (2, 3):
+        for cached in (True, False):
+            quant_cuda.gemm_set_variant(variant)
+            quant_cuda.cache_zero_terms = cached
+            try:
+                got = run_gemm(layer, x, transpose).cpu()
+            finally:
+                quant_cuda.gemm_set_variant(0)
+                quant_cuda.cache_zero_terms = True
+            assert torch.equal(got.view(torch.int16), want.contiguous().view(torch.int16)), (variant, cached)
+
+
 def test_gemm_bias_forward():
     layer = synth.make_layer(512, 256, 128, False, seed=7)
     x = synth.make_acts(64, 512, seed=8)
