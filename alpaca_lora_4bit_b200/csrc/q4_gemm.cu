@@ -328,7 +328,8 @@ __global__ void zp_table_kernel(const __half* __restrict__ scales, const uint32_
 }
 
 static int g_gemm_variant = 0;                // 0 = choose per shape, 1 = single-CTA kernel, 2 = CTA-pair kernel with 256-row tiles,
-                                              // 3 = CTA-pair kernel with 512-row tiles
+                                              // 3 = CTA-pair kernel with 512-row tiles, 4 = weights-in-TMEM kernel (forward,
+                                              // sequential groups promised), 5 = as 0 but never the weights-in-TMEM kernel
 
 static size_t gemm_smem_bytes(bool transpose, int G, int stages) {
   return 1024 + (size_t)stages * GM_STAGE_BYTES + 256 + (transpose ? 0 : (size_t)2 * G * GM_TILE_N * sizeof(__half));
@@ -337,6 +338,7 @@ static size_t gemm_smem_bytes(bool transpose, int G, int stages) {
 }  // namespace q4
 
 #include "q4_gemm2.cuh"
+#include "q4_gemm3.cuh"
 
 using namespace q4;
 
@@ -364,6 +366,7 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
                        q4_stream_t stream, bool swiglu = false, const void* zp_cached = nullptr, const void* residual = nullptr,
                        int seq_groupsize = 0) {
   if (!act || !qweight || !out || !scales || !qzeros || !g_idx) return fail(Q4_E_BADARG, "gemm: null pointer");
+  const int gv = g_gemm_variant == 5 ? 0 : g_gemm_variant;
   if (M <= 0 || K <= 0 || N <= 0 || G <= 0) return fail(Q4_E_BADARG, "gemm: M=%d K=%d N=%d G=%d", M, K, N, G);
   if (K % 128 || N % 128) return fail(Q4_E_SHAPE, "gemm: K=%d and N=%d must be multiples of 128", K, N);
   if (!aligned16(act) || !aligned16(qweight) || !aligned16(out) || !aligned16(scales) || !aligned16(g_idx))
@@ -390,24 +393,29 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
   if (no_tables && !transpose) { stages2 = stages2_nt; stages2w = stages2w_nt; }
   const bool pair_ok = nout % G2_TILE_N == 0 && stages2 > 0;
   const bool wide_ok = nout % G2_TILE_N == 0 && stages2w > 0;
-  if ((g_gemm_variant == 2 && !pair_ok) || (g_gemm_variant == 3 && !wide_ok))
+  if ((gv == 2 && !pair_ok) || (gv == 3 && !wide_ok))
     return fail(Q4_E_SHAPE, "gemm: the CTA-pair kernel needs %d output columns to be a multiple of 256 and G=%d tables to fit", nout, G);
   if (swiglu && (transpose || lora_r > 0 || !pair_ok || N % 256))
     return fail(Q4_E_SHAPE, "gemm: the fused gate_up product needs the CTA-pair kernel (N=%d a multiple of 256, G=%d tables that fit) and no low-rank term", N, G);
-  const bool use_pair = (pair_ok && g_gemm_variant != 1) || g_gemm_variant == 3 || swiglu;
+  const bool use_pair = (pair_ok && gv != 1) || gv == 3 || swiglu;
+  // weights-in-TMEM kernel: forward, groups of at least the 64 contraction elements of a stage promised sequential
+  const bool tm_ok = !transpose && !swiglu && no_tables && seq_shift >= 6 && nout % G2_TILE_N == 0;
+  if (gv == 4 && !tm_ok)
+    return fail(Q4_E_SHAPE, "gemm: the weights-in-TMEM kernel takes the forward of a layer with N=%d a multiple of 256, its zero-term table and sequential groups of 64 rows or more", N);
   // 512-row tiles halve the dequant work per flop but leave fewer, larger tiles to deal: take the
   // form the estimate favours
   const int P_est = sm_count() / 2 > 0 ? sm_count() / 2 : 1;
   const size_t zp_need = transpose && !zp_cached ? (((size_t)G * N * sizeof(__half) + 255) & ~(size_t)255) : 0;
   auto ws_ok_for = [&](int m) { return workspace && workspace_bytes >= Q4_GEMM_WS_COUNTER_BYTES + zp_need + (size_t)P_est * m * Q4_GEMM_WS_SLICE_BYTES; };
   int mh = 1;
-  if (use_pair && g_gemm_variant == 3) mh = 2;
-  else if (use_pair && g_gemm_variant == 0 && wide_ok && M > 256) {
+  if (use_pair && gv == 3) mh = 2;
+  else if (use_pair && gv == 0 && wide_ok && M > 256) {
     bool s1, s2;
     const long long e1 = gemm2_estimate(M, nout, contract / GM_TILE_C, P_est, 1, ws_ok_for(1), &s1);
     const long long e2 = gemm2_estimate(M, nout, contract / GM_TILE_C, P_est, 2, ws_ok_for(2), &s2);
     if (e2 < e1) mh = 2;
   }
+  const bool use_tm = tm_ok && use_pair && (gv == 4 || (gv == 0 && g_gemm_variant != 5 && mh == 1));
   int stages = GM_MAX_STAGES;
   while (stages > 2 && gemm_smem_bytes(transpose, G, stages) > 227 * 1024) --stages;
   if (use_pair) stages = mh == 2 ? stages2w : stages2;
@@ -492,6 +500,18 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
       const int total8 = G * (N / 8);
       zp_table_kernel<<<(total8 + 255) / 256, 256, 0, st>>>((const __half*)scales, (const uint32_t*)qzeros, (__half*)(ws + ws_off), total8);
       ws_off += zp_bytes;
+    }
+    if (use_tm) {
+      static bool tm_attr_done[64] = {false};
+      if (!tm_attr_done[dev]) {
+        if (int e = check_cuda(cudaFuncSetAttribute((const void*)q4_gemm3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm3_smem_bytes()),
+                               "gemm smem attribute")) return e;
+        tm_attr_done[dev] = true;
+      }
+      const int tiles3 = (nout / G2_TILE_N) * ((M + 255) / 256);
+      const int pairs3 = tiles3 < P ? tiles3 : P;
+      q4_gemm3_kernel<<<dim3(2 * pairs3), dim3(G3_THREADS), gemm3_smem_bytes(), st>>>(amap, umap, p);
+      return check_cuda(cudaGetLastError(), "gemm launch");
     }
     // Whole tiles per pair, round after round - or, when the last round would leave pairs idle for
     // longer than the exchange of partial sums costs (about a dozen stages), all tiles x stages as one
@@ -595,7 +615,9 @@ extern "C" int q4_gemm_fwd_residual(const void* x, const int32_t* qweight, void*
 }
 
 extern "C" int q4_gemm_set_variant(int variant) {
-  if (variant < 0 || variant > 3) return fail(Q4_E_BADARG, "gemm_set_variant: %d is not 0 (choose per shape), 1 (single CTA), 2 (CTA pair, 256-row tiles) or 3 (CTA pair, 512-row tiles)", variant);
+  if (variant < 0 || variant > 5)
+    return fail(Q4_E_BADARG, "gemm_set_variant: %d is not 0 (choose per shape), 1 (single CTA), 2 (CTA pair, 256-row tiles), 3 (CTA pair, 512-row tiles), "
+                "4 (weights in TMEM) or 5 (choose per shape among 1-3)", variant);
   g_gemm_variant = variant;
   return Q4_OK;
 }

@@ -200,7 +200,13 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
     }
   } else if (warp == 1) {
     // ---------------- MMA issuer (even CTA only) ----------------
-    if (rank == 0 && lane == 0) {
+    // The whole warp walks the loop, so that stage counters and descriptors are warp-uniform values (uniform
+    // registers, where the tensor-core instructions take their operands from) and one elected lane issues: with a
+    // single lane in a divergent branch every operand took a trip through the vector registers, and 4 MMAs + commit
+    // cost the issuing thread 850 cycles where the MMAs need 540.
+    if (rank == 0) {
+      uint32_t leader;
+      asm volatile("{\n\t.reg .pred P;\n\telect.sync _|P, 0xffffffff;\n\tselp.u32 %0, 1, 0, P;\n\t}" : "=r"(leader));
       constexpr uint32_t idesc = idesc_f16(256, 256, !TRANSPOSE);
       // descriptors of stage 0; the same descriptors address the same offsets in both CTAs' shared memory.
       // A: K-major, 128-byte rows, 8-row groups 1024 B apart, 16 contraction elements = 32 B.
@@ -221,36 +227,39 @@ q4_gemm2_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         tc_fence_after();
         const uint32_t d_tmem = tmem_acc + acc * 256;
         constexpr uint64_t H_STEP = G2_HALF_BYTES >> 4;   // next 128 activation rows of the stage
-        const bool tron = p.trace != nullptr && tl == 1;
+        const bool tron = p.trace != nullptr && tl == 1 && lane == 0;
         for (int it = 0; it < nst; ++it) {
           if (tron && it < 12) gm_mark(p.trace, 5 * it);
           wait_bar_cluster(&full[st], use & 1, abort_flag, &polls);
-          if (tl == 0 && (it & 7) == 0 && it < 256) gm_mark_ns(p.trace, 110 + (it >> 3));
+          if (p.trace && lane == 0 && tl == 0 && (it & 7) == 0 && it < 256) gm_mark_ns(p.trace, 110 + (it >> 3));
           if (tron && it < 12) gm_mark(p.trace, 5 * it + 2);
           tc_fence_after();
-          if (it < ncon) {
+          if (leader) {
+            if (it < ncon) {
 #pragma unroll
-            for (int ks = 0; ks < 4; ++ks)
+              for (int ks = 0; ks < 4; ++ks)
 #pragma unroll
-              for (int h = 0; h < MH; ++h)
-                umma_f16_pair(d_tmem + h * 256, ad + ks * A_STEP + h * H_STEP, bd + ks * B_STEP, idesc, (it > 0 || ks > 0) ? 1u : 0u);
-          } else {
-            for (int ks = 0; ks < lora_ks; ++ks)
+                for (int h = 0; h < MH; ++h)
+                  umma_f16_pair(d_tmem + h * 256, ad + ks * A_STEP + h * H_STEP, bd + ks * B_STEP, idesc, (it > 0 || ks > 0) ? 1u : 0u);
+            } else {
+              for (int ks = 0; ks < lora_ks; ++ks)
 #pragma unroll
-              for (int h = 0; h < MH; ++h)
-                umma_f16_pair(d_tmem + h * 256, ad + ks * A_STEP + h * H_STEP, bd + ks * B_STEP, idesc, 1u);
+                for (int h = 0; h < MH; ++h)
+                  umma_f16_pair(d_tmem + h * 256, ad + ks * A_STEP + h * H_STEP, bd + ks * B_STEP, idesc, 1u);
+            }
+            umma_commit_pair(&empty[st]);              // frees the stage in both CTAs
           }
-          if (tron && it < 12) gm_mark(p.trace, 5 * it + 3);
-          umma_commit_pair(&empty[st]);                // frees the stage in both CTAs
+          __syncwarp();
           if (tron && it < 12) gm_mark(p.trace, 5 * it + 4);
           ad += ST_STEP; bd += ST_STEP;
           if (++st == S) { st = 0; ++use; ad = ad0; bd = bd0; }
         }
-        umma_commit_pair(&acc_full[acc]);
-        if (tl == 0) gm_mark_ns(p.trace, 102);
-        if (item == wr.n_items - 1) gm_mark_ns(p.trace, 103);
+        if (leader) umma_commit_pair(&acc_full[acc]);
+        __syncwarp();
+        if (lane == 0 && tl == 0) gm_mark_ns(p.trace, 102);
+        if (lane == 0 && item == wr.n_items - 1) gm_mark_ns(p.trace, 103);
       }
-      if (p.trace) p.trace[(size_t)blockIdx.x * 256 + 241] = polls;
+      if (p.trace && lane == 0) p.trace[(size_t)blockIdx.x * 256 + 241] = polls;
     }
   } else if (dw >= 0) {
     // ---------------- dequantisers: this CTA's 128 output columns of every stage ----------------

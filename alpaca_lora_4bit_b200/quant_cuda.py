@@ -389,7 +389,9 @@ def gemm_supported(K: int, N: int, G: int, transpose: bool) -> bool:
 
 def gemm_set_variant(variant: int) -> None:
     """Which fused GEMM kernel ``gemm`` launches: 0 = chosen per shape (default), 1 = single-CTA kernel,
-    2 / 3 = CTA-pair kernel with 256- / 512-row tiles (output columns must be a multiple of 256)."""
+    2 / 3 = CTA-pair kernel with 256- / 512-row tiles (output columns must be a multiple of 256), 4 = the forward
+    kernel with the dequantised weights in tensor memory (sequential groups promised, zero-term table kept),
+    5 = chosen per shape among 1-3."""
     _lib.check(_lib.lib().q4_gemm_set_variant(int(variant)), "gemm_set_variant")
 
 
