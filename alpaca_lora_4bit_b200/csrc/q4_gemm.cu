@@ -415,7 +415,11 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
     const long long e2 = gemm2_estimate(M, nout, contract / GM_TILE_C, P_est, 2, ws_ok_for(2), &s2);
     if (e2 < e1) mh = 2;
   }
-  const bool use_tm = tm_ok && use_pair && (gv == 4 || (gv == 0 && g_gemm_variant != 5 && mh == 1));
+  // taken where the pair kernel would run 256-row tiles, and where all its tiles fit one round (one accumulator:
+  // the epilogue of a tile is not overlapped with the next)
+  const bool use_tm = tm_ok && use_pair &&
+                      (gv == 4 || (gv == 0 && g_gemm_variant != 5 && (mh == 1 || (long long)(nout / G2_TILE_N) * ((M + 255) / 256) <= P_est)));
+  if (use_tm) mh = 1;                          // its TMA boxes are 128 activation rows, as for 256-row tiles
   int stages = GM_MAX_STAGES;
   while (stages > 2 && gemm_smem_bytes(transpose, G, stages) > 227 * 1024) --stages;
   if (use_pair) stages = mh == 2 ? stages2w : stages2;

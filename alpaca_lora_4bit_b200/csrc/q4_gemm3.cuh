@@ -102,6 +102,32 @@ q4_gemm3_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
   const int n_tiles = m_tiles * (N / G2_TILE_N);
   const int n_items = pair < n_tiles ? (n_tiles - pair + n_pairs - 1) / n_pairs : 0;
 
+  // A dequant warp asks for the words of its first task before the set-up below (barriers, TMEM, the cluster's
+  // meeting: about a microsecond): the loads depend on none of it.
+  struct TaskRegs { uint32_t w[8]; uint32_t s, z; };
+  const bool is_deq = warp >= 4 && warp < 4 + 4 * G3_GROUPS;
+  auto column_of = [&](int tile) { return (tile / m_tiles) * G2_TILE_N + 128 * (int)rank + 32 * (warp & 3) + lane; };
+  auto prefetch = [&](int n, int j, TaskRegs& R) __attribute__((always_inline)) {
+    if (j >= T) return;
+    const uint32_t* wcol = p.qw + n;
+    const uint32_t* src = wcol + (size_t)(j * (GM_TILE_C >> 3)) * N;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) R.w[i] = ldg_pinned_u32(src + (size_t)i * N);
+    const size_t at = (size_t)((j * GM_TILE_C) >> p.seq_shift) * N + n;
+    R.s = ldg_pinned_u16(p.scales + at);
+    R.z = ldg_pinned_u16(p.zp_table + at);
+    // the words of the group's task after the next, asked into L2 (eight rows of 128 bytes per warp)
+    if (j + 2 * G3_GROUPS < T && lane < 8)
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(wcol - lane + (size_t)((j + 2 * G3_GROUPS) * (GM_TILE_C >> 3) + lane) * N));
+  };
+  TaskRegs R0, R1;
+  if (is_deq && n_items > 0) {
+    const int n = column_of(pair), j = (warp - 4) >> 2;
+    prefetch(n, j, R0);
+    if (j + G3_GROUPS < T && lane < 8)
+      asm volatile("prefetch.global.L2 [%0];" ::"l"(p.qw + n - lane + (size_t)((j + G3_GROUPS) * (GM_TILE_C >> 3) + lane) * N));
+  }
+
   if (threadIdx.x == 0) {
     gm_mark_ns(p.trace, 100);
     for (int i = 0; i < S; ++i) { mbar_init(&full[i], 1 + 8); mbar_init(&empty[i], 1); }
@@ -177,27 +203,12 @@ q4_gemm3_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
     // ---------------- dequantisers: one output column per thread, 64 contraction elements per task ----------------
     const int grp = (warp - 4) >> 2;                               // takes the stage uses u with u % G3_GROUPS == grp
     const int quarter = warp & 3;
-    const int col = 32 * quarter + lane;                           // TMEM lane = column within this CTA's 128
     const uint32_t full0 = mapa_u32(smem_u32(full), 0);
     const uint32_t tdst0 = tmem_base + ((uint32_t)(32 * quarter) << 16) + G3_TMEM_A0;
     int gbase = 0;                                                 // stage uses of all earlier tiles
-    struct TaskRegs { uint32_t w[8]; uint32_t s, z; };
     for (int item = 0; item < n_items; ++item) {
       const int tile = pair + item * n_pairs;
-      const int n = (tile / m_tiles) * G2_TILE_N + 128 * (int)rank + col;
-      const uint32_t* wcol = p.qw + n;
-      auto prefetch = [&](int j, TaskRegs& R) __attribute__((always_inline)) {
-        if (j >= T) return;
-        const uint32_t* src = wcol + (size_t)(j * (GM_TILE_C >> 3)) * N;
-#pragma unroll
-        for (int i = 0; i < 8; ++i) R.w[i] = ldg_pinned_u32(src + (size_t)i * N);
-        const size_t at = (size_t)((j * GM_TILE_C) >> p.seq_shift) * N + n;
-        R.s = ldg_pinned_u16(p.scales + at);
-        R.z = ldg_pinned_u16(p.zp_table + at);
-        // the words of the group's task after the next, asked into L2 (eight rows of 128 bytes per warp)
-        if (j + 2 * G3_GROUPS < T && lane < 8)
-          asm volatile("prefetch.global.L2 [%0];" ::"l"(wcol - lane + (size_t)((j + 2 * G3_GROUPS) * (GM_TILE_C >> 3) + lane) * N));
-      };
+      const int n = column_of(tile);
       auto task = [&](int j, const TaskRegs& C) __attribute__((always_inline)) {
         const int u = gbase + j, st = u & (S - 1), use = u >> 3;
         uint32_t o[32];
@@ -231,14 +242,13 @@ q4_gemm3_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         if (lane == 0) mbar_arrive_cluster(full0 + 8 * st);
       };
       int j = (grp + G3_GROUPS - gbase % G3_GROUPS) % G3_GROUPS;   // this group's first stage of the tile
-      TaskRegs R0, R1;
-      prefetch(j, R0);
+      if (item > 0) prefetch(n, j, R0);                            // (the first tile's came before the set-up)
       while (j < nst) {
-        prefetch(j + G3_GROUPS, R1);
+        prefetch(n, j + G3_GROUPS, R1);
         task(j, R0);
         j += G3_GROUPS;
         if (j >= nst) break;
-        prefetch(j + G3_GROUPS, R0);
+        prefetch(n, j + G3_GROUPS, R0);
         task(j, R1);
         j += G3_GROUPS;
       }
@@ -256,7 +266,7 @@ q4_gemm3_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
       const int m_base = (tile % m_tiles) * 256;
       const int rows = min(256, p.M - m_base);                     // rows of x the tile really has
       const float bv = p.bias ? __half2float(p.bias[n0 + lane]) : 0.f;
-      if (lane == 0) wait_bar_idle(acc_full, item & 1, abort_flag, 250);
+      if (lane == 0) wait_bar_idle(acc_full, item & 1, abort_flag, 100);
       __syncwarp();
       tc_fence_after();
       if (lane == 0 && item == n_items - 1) gm_mark_ns(p.trace, 105);

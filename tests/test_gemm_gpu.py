@@ -454,3 +454,77 @@ def test_forward_with_sequential_groups_promised_is_the_same_product(M, K, N, g)
     host = layer.to("cpu")
     want = orc.matmul4bit_ref(x.cpu(), host.qweight, host.scales, host.qzeros, host.g_idx)
     assert rel_fro(outs[2, "promised"], want) <= REL_TOL
+
+
+@pytest.mark.parametrize("M,K,N,g", [(128, 128, 256, 128), (300, 1024, 768, 128), (256, 512, 512, 64), (77, 2048, 256, -1),
+                                     (513, 1024, 512, 128), (1000, 4096, 1024, 128)])
+def test_forward_with_weights_in_tensor_memory(M, K, N, g):
+    """q4_gemm3_kernel (variant 4: the dequantised weights are the A operand in TMEM, a thread per output column):
+    within tolerance of the oracle, and bit-identical to the CTA-pair kernel where that takes whole tiles (the same
+    fp16 operands, the same order of accumulation along K), plain and with bias, skip-path add and low-rank term;
+    rows that are not a multiple of 128, groups from the 64 rows of a stage up to all of K."""
+    layer = synth.make_layer(K, N, g, False, seed=K + N).to(DEV)
+    x = synth.make_acts(M, K, seed=M).to(DEV)
+    gen = torch.Generator(device=DEV).manual_seed(M)
+    bias = (torch.randn(N, generator=gen, device=DEV) * 0.1).half()
+    res = torch.randn(M, N, generator=gen, device=DEV).half()
+    r = 8
+    u = torch.zeros(M, 64, device=DEV, dtype=torch.float16)
+    u[:, :r] = torch.randn(M, r, generator=gen, device=DEV).half()
+    lw = (torch.randn(N, r, generator=gen, device=DEV) * 0.1).half()
+
+    def run(variant, **kw):
+        quant_cuda.gemm_set_variant(variant)
+        try:
+            y = torch.full((M + 2, N), -9.0, dtype=torch.float16, device=DEV)
+            quant_cuda.gemm(x, layer.qweight, y[1:M + 1], layer.scales, layer.qzeros, layer.g_idx, **kw)
+        finally:
+            quant_cuda.gemm_set_variant(0)
+        assert bool((y[0] == -9.0).all()) and bool((y[M + 1] == -9.0).all())        # rows around the output untouched
+        return y[1:M + 1]
+
+    def same(a, b):                  # long contractions on few tiles: the pair kernel deals K out to several pairs and adds in another order
+        return torch.equal(a, b) if K <= 2048 else rel_fro(a, b) <= 1e-3
+
+    plain = run(4)
+    assert same(plain, run(2))
+    full = run(4, bias=bias, residual=res, lora_u=u, lora_w=lw)
+    assert same(full, run(2, bias=bias, residual=res, lora_u=u, lora_w=lw))
+    assert torch.equal(run(4, residual=res), plain + res)
+    host = layer.to("cpu")
+    want = orc.matmul4bit_ref(x.cpu(), host.qweight, host.scales, host.qzeros, host.g_idx)
+    assert rel_fro(plain, want) <= REL_TOL
+    assert quant_cuda.device_status() == 0
+
+
+def test_tensor_memory_kernel_is_chosen_and_refused_where_it_should_be():
+    """Default choice: the forward of a sequential layer whose 256 x 256 tiles fit one round goes to the
+    weights-in-TMEM kernel even where the pair kernel would have taken 512-row tiles (the activation boxes must
+    then be those of 128 rows: 1024 x 11008 x 4096 is the down projection of LLaMA-7B in the finetune step) -
+    same product as without it; act-order layers, groups below 64 rows and the backward are refused by variant 4."""
+    layer = synth.make_layer(11008, 4096, 128, False, seed=2).to(DEV)
+    x = synth.make_acts(1024, 11008, seed=3).to(DEV)
+    outs = []
+    for variant in (5, 0, 4):
+        quant_cuda.gemm_set_variant(variant)
+        try:
+            y = torch.empty(1024, 4096, dtype=torch.float16, device=DEV)
+            quant_cuda.gemm(x, layer.qweight, y, layer.scales, layer.qzeros, layer.g_idx)
+            outs.append(y)
+        finally:
+            quant_cuda.gemm_set_variant(0)
+    assert torch.equal(outs[1], outs[2])                    # the default took the same kernel as variant 4
+    assert rel_fro(outs[1], outs[0]) <= 1e-3                # the pair kernel adds the halves of K in another order
+    assert quant_cuda.device_status() == 0
+    act = synth.make_layer(512, 512, 128, True, seed=4).to(DEV)
+    small = synth.make_layer(512, 512, 32, False, seed=5).to(DEV)
+    seq = synth.make_layer(512, 512, 128, False, seed=6).to(DEV)
+    xa = synth.make_acts(64, 512, seed=7).to(DEV)
+    quant_cuda.gemm_set_variant(4)
+    try:
+        for bad, tr in ((act, False), (small, False), (seq, True)):
+            with pytest.raises(RuntimeError):
+                quant_cuda.gemm(xa, bad.qweight, torch.empty(64, 512, dtype=torch.float16, device=DEV), bad.scales, bad.qzeros, bad.g_idx,
+                                transpose=tr)
+    finally:
+        quant_cuda.gemm_set_variant(0)
