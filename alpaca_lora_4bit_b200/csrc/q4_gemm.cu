@@ -415,10 +415,10 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
     const long long e2 = gemm2_estimate(M, nout, contract / GM_TILE_C, P_est, 2, ws_ok_for(2), &s2);
     if (e2 < e1) mh = 2;
   }
-  // taken where the pair kernel would run 256-row tiles, and where all its tiles fit one round (one accumulator:
-  // the epilogue of a tile is not overlapped with the next)
+  // taken where the pair kernel would run 256-row tiles, where all its tiles fit one round, and up to 1024 rows (beyond,
+  // 512-row tiles of the pair kernel - half the dequant work per flop - measured faster on the wide layers)
   const bool use_tm = tm_ok && use_pair &&
-                      (gv == 4 || (gv == 0 && g_gemm_variant != 5 && (mh == 1 || (long long)(nout / G2_TILE_N) * ((M + 255) / 256) <= P_est)));
+                      (gv == 4 || (gv == 0 && g_gemm_variant != 5 && (mh == 1 || M <= 1024 || (long long)(nout / G2_TILE_N) * ((M + 255) / 256) <= P_est)));
   if (use_tm) mh = 1;                          // its TMA boxes are 128 activation rows, as for 256-row tiles
   int stages = GM_MAX_STAGES;
   while (stages > 2 && gemm_smem_bytes(transpose, G, stages) > 227 * 1024) --stages;
@@ -508,13 +508,27 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
     if (use_tm) {
       static bool tm_attr_done[64] = {false};
       if (!tm_attr_done[dev]) {
-        if (int e = check_cuda(cudaFuncSetAttribute((const void*)q4_gemm3_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm3_smem_bytes()),
-                               "gemm smem attribute")) return e;
+        for (const void* f3 : {(const void*)q4_gemm3_kernel<false>, (const void*)q4_gemm3_kernel<true>})
+          if (int e = check_cuda(cudaFuncSetAttribute(f3, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)gemm3_smem_bytes()), "gemm smem attribute")) return e;
         tm_attr_done[dev] = true;
       }
+      // whole tiles round after round, or - where the last round would leave pairs idle for longer than the exchange
+      // of partial sums costs - all tiles x stages as one sequence in equal runs (as for the pair kernel below)
       const int tiles3 = (nout / G2_TILE_N) * ((M + 255) / 256);
-      const int pairs3 = tiles3 < P ? tiles3 : P;
-      q4_gemm3_kernel<<<dim3(2 * pairs3), dim3(G3_THREADS), gemm3_smem_bytes(), st>>>(amap, umap, p);
+      int pairs3 = tiles3 < P ? tiles3 : P;
+      bool stream3 = false;
+      const long long total3 = (long long)tiles3 * T;
+      // (measured: every further item of a pair's run and the exchange cost about 30 stages together; tiles cut
+      // between several whole pairs - fewer tiles than pairs - never paid)
+      if (ws && workspace_bytes >= ws_off + (size_t)P * Q4_GEMM_WS_SLICE_BYTES && T >= 8 && tiles3 > P && tiles3 % P != 0 &&
+          total3 * P < (1ll << 32)) {
+        const long long whole = (long long)((tiles3 + P - 1) / P) * T, dealt = (total3 + P - 1) / P + 30;
+        stream3 = dealt < whole;
+      }
+      p.ws_partials = (float*)(ws + ws_off);
+      p.ws_counters = (unsigned*)ws;
+      if (stream3) q4_gemm3_kernel<true><<<dim3(2 * pairs3), dim3(G3_THREADS), gemm3_smem_bytes(), st>>>(amap, umap, p);
+      else q4_gemm3_kernel<false><<<dim3(2 * pairs3), dim3(G3_THREADS), gemm3_smem_bytes(), st>>>(amap, umap, p);
       return check_cuda(cudaGetLastError(), "gemm launch");
     }
     // Whole tiles per pair, round after round - or, when the last round would leave pairs idle for

@@ -19,7 +19,8 @@
 // store and its completion, about 1500 cycles where the MMAs of a stage take 540, so three tasks have to be in
 // flight); warps 16-19 epilogue.  Whole tiles per pair, round after round.
 // The accumulator's lanes are output columns, so a thread of the epilogue holds 32 rows of one column: a warp
-// turns its 32 x 32 block over in shared memory and stores rows of 64 bytes, four lanes each.
+// first moves its 32 columns x 256 rows into shared memory as fp16 (and hands the accumulator back: the MMAs of the
+// pair's next item start while the stores run), then stores rows of 64 bytes, four lanes each.
 // Every wait is bounded as in the pair kernel.
 #pragma once
 
@@ -31,7 +32,7 @@ constexpr int G3_TMEM_A0 = 256;               // first TMEM column of the operan
 constexpr int G3_BAR_BYTES = 512;
 constexpr int G3_GROUPS = 3;                  // dequant groups of four warps
 constexpr int G3_THREADS = 32 * (4 + 4 * G3_GROUPS + 4);
-constexpr int G3_TURN_BYTES = 4 * 2 * 2048;   // per epilogue warp two buffers of 32 rows x 32 columns fp16
+constexpr int G3_TURN_BYTES = 4 * 256 * 64;    // per epilogue warp its 32 columns of all 256 rows of a tile, fp16
 
 __device__ __forceinline__ void umma_f16_pair_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
   asm volatile(
@@ -77,6 +78,9 @@ __device__ __forceinline__ void deq_word_k(uint32_t w, uint32_t s2, uint32_t c2,
   }
 }
 
+// SPLIT as in the pair kernel: whole tiles per pair, or equal runs of the sequence of all tiles x stages with the
+// partial sums of a shared tile meeting in the workspace (added in pair order by the pair whose run starts the tile).
+template <bool SPLIT>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(G3_THREADS, 1)
 q4_gemm3_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant__ CUtensorMap umap, const GemmParams p) {
   extern __shared__ unsigned char smem_raw[];
@@ -96,11 +100,11 @@ q4_gemm3_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
   const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
   const int T = p.n_contract_tiles;
   const int lora_ks = (p.lora_r + 15) >> 4;
-  const int nst = T + (p.lora_r > 0 ? 1 : 0);          // stages of a tile: the contraction, then the low-rank term
   const int N = p.N;
   const int m_tiles = (p.M + 255) / 256;
   const int n_tiles = m_tiles * (N / G2_TILE_N);
-  const int n_items = pair < n_tiles ? (n_tiles - pair + n_pairs - 1) / n_pairs : 0;
+  const WorkRange wr = work_range<SPLIT>(pair, n_pairs, n_tiles, T);
+  const int n_items = wr.n_items;
 
   // A dequant warp asks for the words of its first task before the set-up below (barriers, TMEM, the cluster's
   // meeting: about a microsecond): the loads depend on none of it.
@@ -122,10 +126,9 @@ q4_gemm3_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
   };
   TaskRegs R0, R1;
   if (is_deq && n_items > 0) {
-    const int n = column_of(pair), j = (warp - 4) >> 2;
-    prefetch(n, j, R0);
-    if (j + G3_GROUPS < T && lane < 8)
-      asm volatile("prefetch.global.L2 [%0];" ::"l"(p.qw + n - lane + (size_t)((j + G3_GROUPS) * (GM_TILE_C >> 3) + lane) * N));
+    const WorkItem w0 = work_item<SPLIT>(p, wr, 0, n_pairs, T);
+    const int n = column_of(w0.tile), j = w0.kb + ((warp - 4) >> 2);
+    if (j < w0.ke) prefetch(n, j, R0);
   }
 
   if (threadIdx.x == 0) {
@@ -150,13 +153,15 @@ q4_gemm3_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
       int st = 0, use = 0;
       const uint32_t full0 = mapa_u32(smem_u32(full), 0);
       for (int item = 0; item < n_items; ++item) {
-        const int tile = pair + item * n_pairs;
-        const int m0 = (tile % m_tiles) * 256 + 128 * (int)rank;
+        const WorkItem wi = work_item<SPLIT>(p, wr, item, n_pairs, T);
+        const int m0 = (wi.tile % m_tiles) * 256 + 128 * (int)rank;
+        const int nst = wi.ke - wi.kb + (wi.lora ? 1 : 0);
         for (int j = 0; j < nst; ++j) {
+          const int it = wi.kb + j;
           if (use > 0) wait_bar_idle(&empty[st], (use - 1) & 1, abort_flag, 200);
           if (rank == 0) mbar_arrive_expect_tx(&full[st], 2 * G3_X_BYTES);
           unsigned char* dst = stages + (size_t)st * G3_X_BYTES;
-          if (j < T) tma_load_2d_pair(dst, &amap, j * GM_TILE_C, m0, full0 + 8 * st);
+          if (it < wi.ke) tma_load_2d_pair(dst, &amap, it * GM_TILE_C, m0, full0 + 8 * st);
           else tma_load_2d_pair(dst, &umap, 0, m0, full0 + 8 * st);
           if (++st == S) { st = 0; ++use; }
         }
@@ -176,6 +181,8 @@ q4_gemm3_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
       int st = 0, use = 0;
       uint64_t bd = bd0;
       for (int item = 0; item < n_items; ++item) {
+        const WorkItem wi = work_item<SPLIT>(p, wr, item, n_pairs, T);
+        const int ncon = wi.ke - wi.kb, nst = ncon + (wi.lora ? 1 : 0);
         if (item > 0) wait_bar_cluster(acc_empty, (item - 1) & 1, abort_flag);
         tc_fence_after();
         for (int it = 0; it < nst; ++it) {
@@ -183,7 +190,7 @@ q4_gemm3_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
           if (p.trace && lane == 0 && item == 0 && (it & 7) == 0 && it < 64) gm_mark_ns(p.trace, 110 + (it >> 3));
           tc_fence_after();
           const uint32_t a_tmem = tmem_base + G3_TMEM_A0 + 32 * st;
-          const int nks = it < T ? 4 : lora_ks;
+          const int nks = it < ncon ? 4 : lora_ks;
           if (leader) {
             for (int ks = 0; ks < nks; ++ks)
               umma_f16_pair_ts(tmem_base, a_tmem + 8 * ks, bd + ks * B_STEP, idesc, (it > 0 || ks > 0) ? 1u : 0u);
@@ -207,12 +214,13 @@ q4_gemm3_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
     const uint32_t tdst0 = tmem_base + ((uint32_t)(32 * quarter) << 16) + G3_TMEM_A0;
     int gbase = 0;                                                 // stage uses of all earlier tiles
     for (int item = 0; item < n_items; ++item) {
-      const int tile = pair + item * n_pairs;
-      const int n = column_of(tile);
+      const WorkItem wi = work_item<SPLIT>(p, wr, item, n_pairs, T);
+      const int n = column_of(wi.tile);
+      const int ncon = wi.ke - wi.kb, nst = ncon + (wi.lora ? 1 : 0);       // stages of this item: j = 0 .. nst-1, contraction stage kb + j
       auto task = [&](int j, const TaskRegs& C) __attribute__((always_inline)) {
         const int u = gbase + j, st = u & (S - 1), use = u >> 3;
         uint32_t o[32];
-        if (j == T) {
+        if (j == ncon) {
           // low-rank stage: lane = column n holds lora_B[n][0..r), zero beyond
           const __half* src = p.lora_w + (size_t)n * p.lora_r;
 #pragma unroll
@@ -242,13 +250,14 @@ q4_gemm3_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         if (lane == 0) mbar_arrive_cluster(full0 + 8 * st);
       };
       int j = (grp + G3_GROUPS - gbase % G3_GROUPS) % G3_GROUPS;   // this group's first stage of the tile
-      if (item > 0) prefetch(n, j, R0);                            // (the first tile's came before the set-up)
+      auto ask = [&](int jj, TaskRegs& R) __attribute__((always_inline)) { if (jj < ncon) prefetch(n, wi.kb + jj, R); };
+      if (item > 0) ask(j, R0);                                    // (the first item's came before the set-up)
       while (j < nst) {
-        prefetch(n, j + G3_GROUPS, R1);
+        ask(j + G3_GROUPS, R1);
         task(j, R0);
         j += G3_GROUPS;
         if (j >= nst) break;
-        prefetch(n, j + G3_GROUPS, R0);
+        ask(j + G3_GROUPS, R0);
         task(j, R1);
         j += G3_GROUPS;
       }
@@ -258,12 +267,12 @@ q4_gemm3_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
     // ---------------- epilogue: TMEM -> registers -> (+bias) -> fp16 -> turned over in shared memory -> (+residual) -> global ----------------
     const int quarter = warp & 3;
     const uint32_t acc_empty0 = mapa_u32(smem_u32(acc_empty), 0);
-    unsigned char* mine = turn + quarter * 4096;                   // two buffers of [32 rows][32 columns] fp16
+    unsigned char* mine = turn + quarter * 16384;                  // [256 rows][32 columns] fp16
     const int rr = lane >> 2, cc = lane & 3;                       // reading back: row rr + 8 i, 16-byte chunk cc
     for (int item = 0; item < n_items; ++item) {
-      const int tile = pair + item * n_pairs;
-      const int n0 = (tile / m_tiles) * G2_TILE_N + 128 * (int)rank + 32 * quarter;     // this warp's 32 output columns
-      const int m_base = (tile % m_tiles) * 256;
+      const WorkItem wi = work_item<SPLIT>(p, wr, item, n_pairs, T);
+      const int n0 = (wi.tile / m_tiles) * G2_TILE_N + 128 * (int)rank + 32 * quarter;     // this warp's 32 output columns
+      const int m_base = (wi.tile % m_tiles) * 256;
       const int rows = min(256, p.M - m_base);                     // rows of x the tile really has
       const float bv = p.bias ? __half2float(p.bias[n0 + lane]) : 0.f;
       if (lane == 0) wait_bar_idle(acc_full, item & 1, abort_flag, 100);
@@ -272,41 +281,101 @@ q4_gemm3_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
       if (lane == 0 && item == n_items - 1) gm_mark_ns(p.trace, 105);
       const uint32_t tsrc = tmem_base + ((uint32_t)(32 * quarter) << 16);
       const int nb = (rows + 31) >> 5;                             // blocks of 32 rows that hold anything
+      // Partial sums of a run: this warp's 32 columns x 256 rows as [block][j][lane][4 floats] (512 contiguous bytes
+      // per 16-byte access of the warp), indexed [contributing pair][CTA of the pair][lane quarter].
+      const size_t part_floats = 8 * 8 * 32 * 4;
+      auto part_of = [&](int cpair) -> float* { return p.ws_partials + (((size_t)cpair * 2 + rank) * 4 + quarter) * part_floats; };
+      const bool shared_tile = SPLIT && wi.split;
+      const bool reducer = shared_tile && wi.kb == 0;
+      int c_first = 0, c_last = 0;
+      unsigned* cnt = nullptr;
+      if (shared_tile) {
+        const long long total = (long long)n_tiles * T;
+        c_first = stage_owner((long long)wi.tile * T, n_pairs, total);
+        c_last = stage_owner((long long)wi.tile * T + T - 1, n_pairs, total);
+        cnt = p.ws_counters + ((size_t)c_first * 2 + rank) * 4 + quarter;
+      }
+      if (reducer) {
+        if (lane == 0) {
+          const unsigned want = (unsigned)(c_last - c_first);
+          bool ok = false;
+          const uint32_t lim = *abort_flag ? 4u : 500000u;                    // x 200 ns
+          for (uint32_t i = 0; i < lim && !ok; ++i) {
+            unsigned have;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(have) : "l"(cnt) : "memory");
+            ok = have >= want;
+            if (!ok) __nanosleep(200);
+          }
+          if (!ok) { *abort_flag = 1; atomicExch(&g_gemm_status, Q4_STATUS_WAIT_EXPIRED); }
+        }
+        __syncwarp();
+        __threadfence();
+      }
 #pragma unroll 1
       for (int cb = 0; cb < nb; ++cb) {
         uint32_t v[32];
         tmem_ld32(tsrc + cb * 32, v);
         tmem_ld_wait();
-        unsigned char* buf = mine + (cb & 1) * 2048;
+        if (shared_tile && !reducer) {
+          float* part = part_of(pair);
+#pragma unroll
+          for (int q = 0; q < 8; ++q)
+            *reinterpret_cast<uint4*>(part + ((cb * 8 + q) * 32 + lane) * 4) = make_uint4(v[4 * q], v[4 * q + 1], v[4 * q + 2], v[4 * q + 3]);
+          continue;
+        }
+        if (reducer) {
+          for (int c2 = c_first + 1; c2 <= c_last; ++c2) {
+            const float* src = part_of(c2);
+#pragma unroll
+            for (int q = 0; q < 8; ++q) {
+              const float4 a = __ldcg(reinterpret_cast<const float4*>(src + ((cb * 8 + q) * 32 + lane) * 4));
+              v[4 * q] = __float_as_uint(__uint_as_float(v[4 * q]) + a.x); v[4 * q + 1] = __float_as_uint(__uint_as_float(v[4 * q + 1]) + a.y);
+              v[4 * q + 2] = __float_as_uint(__uint_as_float(v[4 * q + 2]) + a.z); v[4 * q + 3] = __float_as_uint(__uint_as_float(v[4 * q + 3]) + a.w);
+            }
+          }
+        }
+        unsigned char* buf = mine + cb * 2048;
         // this thread's column, rows 32 cb ..: one half per row, 64 bytes per row across the warp
 #pragma unroll
         for (int t = 0; t < 32; ++t)
           *reinterpret_cast<__half*>(buf + t * 64 + lane * 2) = __float2half_rn(__uint_as_float(v[t]) + bv);
-        __syncwarp();
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const int r = rr + 8 * i, m = m_base + cb * 32 + r;
-          uint4 o = *reinterpret_cast<const uint4*>(buf + r * 64 + cc * 16);
-          if (m < p.M) {
-            const size_t at = (size_t)m * N + n0 + 8 * cc;
-            if (p.residual) {                                      // rounded first, as the separate add of the decoder layer would see it
-              const uint4 rv = __ldg(reinterpret_cast<const uint4*>(p.residual + at));
-              uint32_t* ov = reinterpret_cast<uint32_t*>(&o);
-              const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float2 a = __half22float2(as_h2(ov[e])), b = __half22float2(as_h2(rw[e]));
-                ov[e] = as_u32(__floats2half2_rn(a.x + b.x, a.y + b.y));
-              }
-            }
-            *reinterpret_cast<uint4*>(p.out + at) = o;
-          }
-        }
-        // (the other buffer is written next: its readers passed the __syncwarp above one block ago)
       }
+      // this warp has read its part of the accumulator: the even CTA may start the next item
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive_cluster(acc_empty0);
+      if (!(shared_tile && !reducer)) {
+#pragma unroll 1
+        for (int cb = 0; cb < nb; ++cb) {
+          const unsigned char* buf = mine + cb * 2048;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            const int r = rr + 8 * i, m = m_base + cb * 32 + r;
+            uint4 o = *reinterpret_cast<const uint4*>(buf + r * 64 + cc * 16);
+            if (m < p.M) {
+              const size_t at = (size_t)m * N + n0 + 8 * cc;
+              if (p.residual) {                                    // rounded first, as the separate add of the decoder layer would see it
+                const uint4 rv = __ldg(reinterpret_cast<const uint4*>(p.residual + at));
+                uint32_t* ov = reinterpret_cast<uint32_t*>(&o);
+                const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                  const float2 a = __half22float2(as_h2(ov[e])), b = __half22float2(as_h2(rw[e]));
+                  ov[e] = as_u32(__floats2half2_rn(a.x + b.x, a.y + b.y));
+                }
+              }
+              *reinterpret_cast<uint4*>(p.out + at) = o;
+            }
+          }
+        }
+        __syncwarp();                                      // the rows are read before the next item overwrites them
+      }
+      if (shared_tile && !reducer) {                       // publish: sums, then the count
+        __threadfence();
+        __syncwarp();
+        if (lane == 0) atomicAdd(cnt, 1u);
+      }
+      if (reducer && lane == 0) *cnt = 0;                  // every contributor has been counted: ready for the next launch
     }
   }
   if (threadIdx.x == G3_THREADS - 128) gm_mark_ns(p.trace, 106);
