@@ -158,7 +158,7 @@ q4_gemm3_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         const int nst = wi.ke - wi.kb + (wi.lora ? 1 : 0);
         for (int j = 0; j < nst; ++j) {
           const int it = wi.kb + j;
-          if (use > 0) wait_bar_idle(&empty[st], (use - 1) & 1, abort_flag, 200);
+          if (use > 0) wait_bar_idle(&empty[st], (use - 1) & 1, abort_flag, 40);
           if (rank == 0) mbar_arrive_expect_tx(&full[st], 2 * G3_X_BYTES);
           unsigned char* dst = stages + (size_t)st * G3_X_BYTES;
           if (it < wi.ke) tma_load_2d_pair(dst, &amap, it * GM_TILE_C, m0, full0 + 8 * st);
@@ -240,7 +240,7 @@ q4_gemm3_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
             for (int i = 0; i < 8; ++i) deq_word_k<false>(C.w[i], s2, 0u, z2, o + 4 * i);
           }
         }
-        if (use > 0 && lane == 0) wait_bar_idle(&empty[st], (use - 1) & 1, abort_flag, 100);
+        if (use > 0 && lane == 0) wait_bar_idle(&empty[st], (use - 1) & 1, abort_flag, 40);
         __syncwarp();
         tc_fence_after();
         tmem_st32(tdst0 + 32 * st, o);

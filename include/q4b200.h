@@ -287,10 +287,13 @@ int q4_gemv_set_trace(void* device_buffer);
 /* Same for the fused GEMM kernels: 256 uint64 slots per CTA (buffer of 256 * 8 * number-of-CTAs bytes). */
 int q4_gemm_set_trace(void* device_buffer);
 /* Which fused GEMM kernel q4_gemm_fwd / q4_gemm_bwd launch (process-wide; no reference counterpart):
- * 0 = choose per shape (the default: the CTA-pair kernel when the number of output columns is a
- * multiple of 256 - with 512-row tiles when M > 256, else 256-row tiles - and the single-CTA kernel
- * otherwise), 1 = always the single-CTA kernel, 2 / 3 = always the CTA-pair kernel with 256- /
- * 512-row tiles (calls it cannot serve then fail with Q4_E_SHAPE).  For tests and measurements. */
+ * 0 = choose per shape (the default: with the number of output columns a multiple of 256, the CTA-pair kernel
+ * with 256- or 512-row tiles, whichever its estimate favours, or - forward only, when the caller keeps the
+ * zero-term table and promises sequential groups of 64 rows or more - the kernel that holds the dequantised
+ * weights in tensor memory, where 256-row tiles would be chosen, where its tiles fit one round, and up to 1024
+ * rows; the single-CTA kernel otherwise), 1 = always the single-CTA kernel, 2 / 3 = always the CTA-pair kernel
+ * with 256- / 512-row tiles, 4 = always the weights-in-tensor-memory kernel (calls a forced kernel cannot serve
+ * fail with Q4_E_SHAPE), 5 = as 0 without the weights-in-tensor-memory kernel.  For tests and measurements. */
 int q4_gemm_set_variant(int variant);
 /* Forms of the sequential-group decode kernels, for tests and measurements (process-wide; no
  * reference counterpart).  `variant` is a sum of:
