@@ -91,7 +91,8 @@ q4_gemm3_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
   uint64_t* empty = full + 8;                                                   // both CTAs: stage read by the MMAs
   uint64_t* acc_full = empty + 8;                                               // both CTAs: accumulator complete
   uint64_t* acc_empty = acc_full + 1;                                           // even CTA: 4 epilogue warps x 2 CTAs
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 1);
+  uint64_t* last_full = acc_empty + 1;                                          // both CTAs: the pair's last accumulator complete (one use)
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(last_full + 1);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   unsigned char* turn = smem + S * G3_X_BYTES + G3_BAR_BYTES;
 
@@ -134,7 +135,7 @@ q4_gemm3_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
   if (threadIdx.x == 0) {
     gm_mark_ns(p.trace, 100);
     for (int i = 0; i < S; ++i) { mbar_init(&full[i], 1 + 8); mbar_init(&empty[i], 1); }
-    mbar_init(acc_full, 1); mbar_init(acc_empty, 8);
+    mbar_init(acc_full, 1); mbar_init(acc_empty, 8); mbar_init(last_full, 1);
     *abort_flag = 0;
     mbar_fence_init();
     tma_prefetch_desc(&amap);
@@ -146,6 +147,40 @@ q4_gemm3_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
   if (threadIdx.x == 0) gm_mark_ns(p.trace, 101);
+
+  // One block of 32 rows of a warp's 32 output columns: (+bias) -> fp16 -> shared memory, one half per row and lane.
+  auto block_to_smem = [&](unsigned char* buf, const uint32_t (&v)[32], float bv) __attribute__((always_inline)) {
+#pragma unroll
+    for (int t = 0; t < 32; ++t)
+      *reinterpret_cast<__half*>(buf + t * 64 + lane * 2) = __float2half_rn(__uint_as_float(v[t]) + bv);
+  };
+  // ... and from there to global memory: rows of 64 bytes, four lanes each, with the skip-path add
+  auto block_to_global = [&](const unsigned char* buf, int m0, int n0) __attribute__((always_inline)) {
+    const int rr = lane >> 2, cc = lane & 3;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int r = rr + 8 * i, m = m0 + r;
+      uint4 o = *reinterpret_cast<const uint4*>(buf + r * 64 + cc * 16);
+      if (m < p.M) {
+        const size_t at = (size_t)m * N + n0 + 8 * cc;
+        if (p.residual) {                                          // rounded first, as the separate add of the decoder layer would see it
+          const uint4 rv = __ldg(reinterpret_cast<const uint4*>(p.residual + at));
+          uint32_t* ov = reinterpret_cast<uint32_t*>(&o);
+          const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const float2 a = __half22float2(as_h2(ov[e])), b = __half22float2(as_h2(rw[e]));
+            ov[e] = as_u32(__floats2half2_rn(a.x + b.x, a.y + b.y));
+          }
+        }
+        *reinterpret_cast<uint4*>(p.out + at) = o;
+      }
+    }
+  };
+  // The pair's last item, when it is a whole tile: nothing follows it, so the dequant warps (three per TMEM lane
+  // quarter) share its epilogue with the epilogue warp of their quarter, blocks of 32 rows dealt round robin.
+  const WorkItem w_last = work_item<SPLIT>(p, wr, n_items > 0 ? n_items - 1 : 0, n_pairs, T);
+  const bool share_last = n_items > 0 && !(SPLIT && w_last.split);
 
   if (warp == 0) {
     // ---------------- TMA producer: this CTA's 128 rows of x (or of lora_u) of every stage ----------------
@@ -200,7 +235,7 @@ q4_gemm3_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
           bd += ST_STEP;
           if (++st == S) { st = 0; ++use; bd = bd0; }
         }
-        if (leader) umma_commit_pair(acc_full);
+        if (leader) { umma_commit_pair(acc_full); if (item == n_items - 1) umma_commit_pair(last_full); }
         __syncwarp();
         if (lane == 0 && item == 0) gm_mark_ns(p.trace, 102);
         if (lane == 0 && item == n_items - 1) gm_mark_ns(p.trace, 103);
@@ -263,24 +298,48 @@ q4_gemm3_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
       }
       gbase += nst;
     }
+    if (share_last) {
+      const int n0 = (w_last.tile / m_tiles) * G2_TILE_N + 128 * (int)rank + 32 * quarter;
+      const int m_base = (w_last.tile % m_tiles) * 256;
+      const int nb = (min(256, p.M - m_base) + 31) >> 5;
+      const float bv = p.bias ? __half2float(p.bias[n0 + lane]) : 0.f;
+      // the quarter's shared-memory rows are free once its epilogue warp has stored the item before (a meeting of
+      // the quarter's four warps: named barrier 1 + quarter)
+      named_bar_sync(1 + quarter, 128);
+      if (lane == 0) wait_bar_idle(last_full, 0, abort_flag, 100);
+      __syncwarp();
+      tc_fence_after();
+      unsigned char* mine = turn + quarter * 16384;
+#pragma unroll 1
+      for (int cb = grp; cb < nb; cb += G3_GROUPS + 1) {
+        uint32_t v[32];
+        tmem_ld32(tmem_base + ((uint32_t)(32 * quarter) << 16) + cb * 32, v);
+        tmem_ld_wait();
+        block_to_smem(mine + cb * 2048, v, bv);
+        __syncwarp();
+        block_to_global(mine + cb * 2048, m_base + cb * 32, n0);
+      }
+    }
   } else if (warp >= 4 + 4 * G3_GROUPS) {
     // ---------------- epilogue: TMEM -> registers -> (+bias) -> fp16 -> turned over in shared memory -> (+residual) -> global ----------------
     const int quarter = warp & 3;
     const uint32_t acc_empty0 = mapa_u32(smem_u32(acc_empty), 0);
     unsigned char* mine = turn + quarter * 16384;                  // [256 rows][32 columns] fp16
-    const int rr = lane >> 2, cc = lane & 3;                       // reading back: row rr + 8 i, 16-byte chunk cc
     for (int item = 0; item < n_items; ++item) {
       const WorkItem wi = work_item<SPLIT>(p, wr, item, n_pairs, T);
       const int n0 = (wi.tile / m_tiles) * G2_TILE_N + 128 * (int)rank + 32 * quarter;     // this warp's 32 output columns
       const int m_base = (wi.tile % m_tiles) * 256;
       const int rows = min(256, p.M - m_base);                     // rows of x the tile really has
       const float bv = p.bias ? __half2float(p.bias[n0 + lane]) : 0.f;
+      if (share_last && item == n_items - 1) named_bar_sync(1 + quarter, 128);     // the helpers may use this quarter's rows from here
       if (lane == 0) wait_bar_idle(acc_full, item & 1, abort_flag, 100);
       __syncwarp();
       tc_fence_after();
       if (lane == 0 && item == n_items - 1) gm_mark_ns(p.trace, 105);
       const uint32_t tsrc = tmem_base + ((uint32_t)(32 * quarter) << 16);
       const int nb = (rows + 31) >> 5;                             // blocks of 32 rows that hold anything
+      const bool shared_out = share_last && item == n_items - 1;   // the dequant warps take the blocks cb % 4 = 0, 1, 2
+      const int cb0 = shared_out ? G3_GROUPS : 0, cbs = shared_out ? G3_GROUPS + 1 : 1;
       // Partial sums of a run: this warp's 32 columns x 256 rows as [block][j][lane][4 floats] (512 contiguous bytes
       // per 16-byte access of the warp), indexed [contributing pair][CTA of the pair][lane quarter].
       const size_t part_floats = 8 * 8 * 32 * 4;
@@ -312,7 +371,7 @@ q4_gemm3_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
         __threadfence();
       }
 #pragma unroll 1
-      for (int cb = 0; cb < nb; ++cb) {
+      for (int cb = cb0; cb < nb; cb += cbs) {
         uint32_t v[32];
         tmem_ld32(tsrc + cb * 32, v);
         tmem_ld_wait();
@@ -334,11 +393,7 @@ q4_gemm3_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
             }
           }
         }
-        unsigned char* buf = mine + cb * 2048;
-        // this thread's column, rows 32 cb ..: one half per row, 64 bytes per row across the warp
-#pragma unroll
-        for (int t = 0; t < 32; ++t)
-          *reinterpret_cast<__half*>(buf + t * 64 + lane * 2) = __float2half_rn(__uint_as_float(v[t]) + bv);
+        block_to_smem(mine + cb * 2048, v, bv);
       }
       // this warp has read its part of the accumulator: the even CTA may start the next item
       tc_fence_before();
@@ -346,28 +401,7 @@ q4_gemm3_kernel(const __grid_constant__ CUtensorMap amap, const __grid_constant_
       if (lane == 0) mbar_arrive_cluster(acc_empty0);
       if (!(shared_tile && !reducer)) {
 #pragma unroll 1
-        for (int cb = 0; cb < nb; ++cb) {
-          const unsigned char* buf = mine + cb * 2048;
-#pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            const int r = rr + 8 * i, m = m_base + cb * 32 + r;
-            uint4 o = *reinterpret_cast<const uint4*>(buf + r * 64 + cc * 16);
-            if (m < p.M) {
-              const size_t at = (size_t)m * N + n0 + 8 * cc;
-              if (p.residual) {                                    // rounded first, as the separate add of the decoder layer would see it
-                const uint4 rv = __ldg(reinterpret_cast<const uint4*>(p.residual + at));
-                uint32_t* ov = reinterpret_cast<uint32_t*>(&o);
-                const uint32_t rw[4] = {rv.x, rv.y, rv.z, rv.w};
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                  const float2 a = __half22float2(as_h2(ov[e])), b = __half22float2(as_h2(rw[e]));
-                  ov[e] = as_u32(__floats2half2_rn(a.x + b.x, a.y + b.y));
-                }
-              }
-              *reinterpret_cast<uint4*>(p.out + at) = o;
-            }
-          }
-        }
+        for (int cb = cb0; cb < nb; cb += cbs) block_to_global(mine + cb * 2048, m_base + cb * 32, n0);
         __syncwarp();                                      // the rows are read before the next item overwrites them
       }
       if (shared_tile && !reducer) {                       // publish: sums, then the count
