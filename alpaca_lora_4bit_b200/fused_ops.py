@@ -188,13 +188,41 @@ def _decoder_layer_forward(layer):
     return forward
 
 
-def patch_llama(model: nn.Module) -> nn.Module:
+def _fuse_gate_up(model: nn.Module) -> int:
+    """Replace every ``LlamaMLP`` whose gate and up projections are plain 4-bit quant linears with the same group
+    layout (no adapters on them) by ``QuantLlamaMLP`` - the reference's fused inference MLP
+    (model_attn_mlp_patch.py:165-247), which trains as well: one product of 2 I columns forward, one product over a
+    contraction of 2 I backward (the sum of the two input gradients happens in the accumulator), the SwiGLU kernel
+    reading and writing the halves of the fused tensor in place.  Returns the number of MLPs replaced."""
+    from transformers.models.llama import modeling_llama as ml
+    from .autograd_4bit import Autograd4bitQuantLinear
+    from . import model_attn_mlp_patch as patch
+    done = 0
+    for parent in list(model.modules()):
+        for name, child in list(parent.named_children()):
+            if not isinstance(child, ml.LlamaMLP):
+                continue
+            g, u = getattr(child, "gate_proj", None), getattr(child, "up_proj", None)
+            if type(g) is not Autograd4bitQuantLinear or type(u) is not Autograd4bitQuantLinear:
+                continue
+            if g.is_v1_model or u.is_v1_model or g.bits != 4 or u.bits != 4 or g.groupsize != u.groupsize or not torch.equal(g.g_idx, u.g_idx):
+                continue
+            setattr(parent, name, patch.QuantLlamaMLP(child))
+            done += 1
+    return done
+
+
+def patch_llama(model: nn.Module, fuse_gate_up: bool = False) -> nn.Module:
     """Route the RMSNorms, the SwiGLU products, the rotary embedding and the skip-path adds of a transformers LLaMA
     through the fused operators above.  The norm, MLP and decoder-layer modules are patched per instance; the rotary
     function is a module-level name of ``transformers.models.llama.modeling_llama`` and is replaced there (the
     replacement computes exactly the stock expression whenever the fused path does not apply).  Call it before
-    anything wraps the layers' ``forward`` (gradient checkpointing)."""
+    anything wraps the layers' ``forward`` (gradient checkpointing).  ``fuse_gate_up`` also concatenates the gate
+    and up projections of every MLP that carries no adapter on them (``_fuse_gate_up``; the packed tensors of the
+    two layers are copied into one and the sources freed)."""
     from transformers.models.llama import modeling_llama as ml
+    if fuse_gate_up:
+        _fuse_gate_up(model)
     for mod in model.modules():
         if isinstance(mod, ml.LlamaDecoderLayer) and "forward" not in mod.__dict__:
             mod.forward = _decoder_layer_forward(mod)

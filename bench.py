@@ -373,7 +373,8 @@ def run_finetune(args, rank, world, local_rank):
         fs.add_lora(model, ["q_proj", "v_proj"], r=8, alpha=16, std_a=0.02, std_b=0.01, seed=1)
     if not args.finetune_stock_elementwise:
         from alpaca_lora_4bit_b200 import fused_ops
-        fused_ops.patch_llama(model)                   # RMSNorm, SwiGLU, rotary: one kernel each way
+        # RMSNorm, SwiGLU, rotary: one kernel each way; gate and up as one layer where no adapter sits on them
+        fused_ops.patch_llama(model, fuse_gate_up=not args.finetune_separate_gate_up)
     fs.apply_gradient_checkpointing(model)
     model.train()
     ft = fs.LoraFinetuner(model, lr=3e-4, autocast_dtype=torch.bfloat16 if big else torch.float16)
@@ -428,6 +429,7 @@ def run_finetune(args, rank, world, local_rank):
            "lora_params": fs.lora_param_count(model), "allreduce_bytes_per_step": 4 * fs.lora_param_count(model) if world > 1 else 0,
            "model_tflops_per_s": round(tps * flops_per_token / 1e12, 1), "loss_first_last": [round(losses[0], 4), round(losses[-1], 4)], "launch": "cuda_graph" if graphed else "eager",
            "elementwise": "stock transformers modules" if args.finetune_stock_elementwise else "fused RMSNorm / SwiGLU / rotary kernels",
+           "gate_up": "two layers" if (args.finetune_stock_elementwise or args.finetune_separate_gate_up or big) else "one fused layer [K, 2 I]",
            "h2d_bytes_per_step": B * T * 8, "d2h_bytes_per_step": 4}
     if args.finetune_profile and local_rank == 0:
         # device time per kernel of ONE eager step (torch.profiler; outside the timed region, after it)
@@ -655,6 +657,8 @@ def main():
                     help="after the timed steps run one eager step under torch.profiler and add its per-kernel device times as finetune.kernels")
     ap.add_argument("--finetune-stock-elementwise", action="store_true",
                     help="leave RMSNorm, SwiGLU and the rotary embedding to the stock transformers modules")
+    ap.add_argument("--finetune-separate-gate-up", action="store_true",
+                    help="keep gate_proj and up_proj two layers (default: one fused layer where no adapter sits on them)")
     ap.add_argument("--finetune-layers", type=int, default=0, help="override the number of decoder layers (0 = 32)")
     args = ap.parse_args()
     if args.decode_shape:

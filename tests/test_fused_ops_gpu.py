@@ -151,3 +151,36 @@ def test_skip_path_adds_in_the_projection_epilogues():
     loss_s, g_s = run(False)
     assert abs(loss_p - loss_s) <= 2e-3 * abs(loss_s)
     assert float((g_p - g_s).norm() / g_s.norm()) <= 2e-2
+
+
+def test_fused_gate_up_trains_like_two_layers():
+    """patch_llama(fuse_gate_up=True) replaces the MLPs (no adapter on gate / up) by the fused-gate/up module: same
+    loss and same LoRA gradients as the model with two layers, through checkpointing and the whole finetune step;
+    an MLP with an adapter on gate_proj is left alone."""
+    from alpaca_lora_4bit_b200 import model_attn_mlp_patch as patch
+    ids = torch.randint(0, 256, (2, 96), generator=torch.Generator().manual_seed(8)).to(DEV)
+    shape = fs.LlamaShape(hidden_size=512, intermediate_size=1024, num_hidden_layers=2, num_attention_heads=8,
+                          num_key_value_heads=4, vocab_size=256, max_position_embeddings=256)
+
+    def run(fuse, targets):
+        model = fs.build_quant_llama(shape, DEV, groupsize=128, seed=2)
+        fs.add_lora(model, targets, r=8, alpha=16, seed=3)
+        fused_ops.patch_llama(model, fuse_gate_up=fuse)
+        n_fused = sum(isinstance(m, patch.QuantLlamaMLP) for m in model.modules())
+        fs.apply_gradient_checkpointing(model)
+        model.train()
+        ft = fs.LoraFinetuner(model, lr=0.0, loss_scale=64.0, dynamic_scale=False)
+        loss = float(ft.step(ids))
+        torch.cuda.synchronize()
+        return loss, ft.flat.buffer.clone(), n_fused
+
+    stock_rope = __import__("transformers.models.llama.modeling_llama", fromlist=["x"]).apply_rotary_pos_emb
+    try:
+        loss_f, g_f, n_f = run(True, ["q_proj", "v_proj", "down_proj"])
+        loss_s, g_s, n_s = run(False, ["q_proj", "v_proj", "down_proj"])
+        _, _, n_adapter = run(True, ["q_proj", "gate_proj"])
+    finally:
+        __import__("transformers.models.llama.modeling_llama", fromlist=["x"]).apply_rotary_pos_emb = stock_rope
+    assert n_f == 2 and n_s == 0 and n_adapter == 0
+    assert abs(loss_f - loss_s) <= 2e-3 * abs(loss_s)
+    assert float((g_f - g_s).norm() / g_s.norm()) <= 2e-2
