@@ -90,6 +90,46 @@ class _SwiGLU(torch.autograd.Function):
         return dg.reshape(ctx.shape), du.reshape(ctx.shape)
 
 
+class _SwiGLUFused(torch.autograd.Function):
+    """``silu(gu[..., :I]) * gu[..., I:]`` on one fused gate_up output: the backward writes both halves of one
+    gradient tensor, so nothing concatenates them afterwards."""
+
+    @staticmethod
+    def forward(ctx, gu):
+        I = gu.shape[-1] // 2
+        g2 = gu.reshape(-1, 2 * I)
+        out = torch.empty((g2.shape[0], I), dtype=torch.float16, device=gu.device)
+        with _lib.on_device(gu.device):
+            _lib.check(_lib.lib().q4_swiglu_fwd(g2.data_ptr(), g2.data_ptr() + 2 * I, out.data_ptr(), g2.shape[0], I, 2 * I,
+                                                _lib.stream_of(gu)), "swiglu")
+        ctx.save_for_backward(g2)
+        ctx.shape = gu.shape
+        return out.reshape(gu.shape[:-1] + (I,))
+
+    @staticmethod
+    def backward(ctx, dout):
+        (g2,) = ctx.saved_tensors
+        rows, I = g2.shape[0], g2.shape[1] // 2
+        d = dout.reshape(rows, I)
+        if d.dtype != torch.float16 or not d.is_contiguous():
+            d = d.half().contiguous()
+        dgu = torch.empty((rows, 2 * I), dtype=torch.float16, device=d.device)
+        with _lib.on_device(d.device):
+            _lib.check(_lib.lib().q4_swiglu_bwd(d.data_ptr(), g2.data_ptr(), g2.data_ptr() + 2 * I, dgu.data_ptr(), dgu.data_ptr() + 2 * I,
+                                                rows, I, 2 * I, 2 * I, _lib.stream_of(d)), "swiglu_bwd")
+        return dgu.reshape(ctx.shape)
+
+
+def swiglu_fused(gu: torch.Tensor) -> torch.Tensor:
+    """``silu(gate) * up`` for ``gu = [gate | up]`` along the last dimension (the output of a fused gate_up
+    projection); falls back to ``swiglu`` on the two halves where the kernel does not apply."""
+    I = gu.shape[-1] // 2
+    if _fusable(gu) and gu.shape[-1] == 2 * I and I % 8 == 0 and gu.numel() > 0 and gu.is_contiguous() and gu.data_ptr() % 16 == 0:
+        return _SwiGLUFused.apply(gu)
+    gate, up = torch.split(gu, I, dim=-1)
+    return swiglu(gate, up)
+
+
 def swiglu(gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     """``silu(gate) * up`` (the product inside ``LlamaMLP.forward``); ``gate`` and ``up`` may be the two halves of
     one fused gate_up output (rows of a common pitch)."""

@@ -160,10 +160,12 @@ class QuantLlamaMLP(nn.Module):
         h = self._fused_product(x)
         if h is not None:
             return self.down_proj(h)
-        gate, up = torch.split(self.gate_up_proj(x), self.intermediate_size, dim=-1)
+        gu = self.gate_up_proj(x)
         if type(self.act_fn).__name__ in ("SiLU", "SiLUActivation"):
-            # one kernel reads the two halves of the fused output where they lie and writes the product
-            return self.down_proj(fused_ops.swiglu(gate, up))
+            # one kernel reads the two halves of the fused output where they lie and writes the product (and, in the
+            # backward, the two halves of one gradient tensor)
+            return self.down_proj(fused_ops.swiglu_fused(gu))
+        gate, up = torch.split(gu, self.intermediate_size, dim=-1)
         return self.down_proj(self.act_fn(gate) * up)
 
 

@@ -184,3 +184,21 @@ def test_fused_gate_up_trains_like_two_layers():
     assert n_f == 2 and n_s == 0 and n_adapter == 0
     assert abs(loss_f - loss_s) <= 2e-3 * abs(loss_s)
     assert float((g_f - g_s).norm() / g_s.norm()) <= 2e-2
+
+
+@pytest.mark.parametrize("rows,I", [(300, 1024), (1024, 11008), (5, 8)])
+def test_swiglu_on_a_fused_gate_up_tensor(rows, I):
+    """swiglu_fused takes [gate | up] as one tensor and returns one gradient tensor for it: same values as the
+    two-tensor form (and as the stock expression), no concatenation in the backward."""
+    g = torch.Generator(device=DEV).manual_seed(rows + I)
+    gu = (torch.randn((2, rows, 2 * I), generator=g, device=DEV) * 2).half().requires_grad_(True)
+    d = torch.randn((2, rows, I), generator=g, device=DEV).half()
+    out = fused_ops.swiglu_fused(gu)
+    gate, up = torch.split(gu, I, dim=-1)
+    assert torch.equal(out, fused_ops.swiglu(gate, up))
+    ref = torch.nn.functional.silu(gate) * up
+    assert rel(out, ref) <= 1e-3
+    (got,) = torch.autograd.grad(out, [gu], d)
+    (two,) = torch.autograd.grad(fused_ops.swiglu(gate, up), [gu], d)
+    (want,) = torch.autograd.grad(ref, [gu], d)
+    assert torch.equal(got, two) and rel(got, want) <= 3e-3
