@@ -528,3 +528,36 @@ def test_tensor_memory_kernel_is_chosen_and_refused_where_it_should_be():
                                 transpose=tr)
     finally:
         quant_cuda.gemm_set_variant(0)
+
+
+@pytest.mark.parametrize("M,K,N", [(1024, 4096, 11008), (700, 2048, 20480)])
+def test_tensor_memory_kernel_with_runs_dealt_across_pairs(M, K, N):
+    """More 256 x 256 tiles than CTA pairs and a last round that would leave most pairs idle: the weights-in-TMEM
+    kernel deals tiles x stages as one sequence (stream-K), shared tiles meet in the workspace.  Same product as the
+    pair kernel (which adds K in another order: tolerance), plain and with bias, skip-path add and a rank-16 term
+    (the low-rank stage goes with the run that reaches the end of a tile); twice in a row (the counters are left
+    zero); the workspace status stays clean."""
+    layer = synth.make_layer(K, N, 128, False, seed=K + N).to(DEV)
+    x = synth.make_acts(M, K, seed=M).to(DEV)
+    gen = torch.Generator(device=DEV).manual_seed(M)
+    bias = (torch.randn(N, generator=gen, device=DEV) * 0.1).half()
+    res = torch.randn(M, N, generator=gen, device=DEV).half()
+    r = 16
+    u = torch.zeros(M, 64, device=DEV, dtype=torch.float16)
+    u[:, :r] = torch.randn(M, r, generator=gen, device=DEV).half()
+    lw = (torch.randn(N, r, generator=gen, device=DEV) * 0.1).half()
+
+    def run(variant, **kw):
+        quant_cuda.gemm_set_variant(variant)
+        try:
+            y = torch.empty(M, N, dtype=torch.float16, device=DEV)
+            quant_cuda.gemm(x, layer.qweight, y, layer.scales, layer.qzeros, layer.g_idx, **kw)
+        finally:
+            quant_cuda.gemm_set_variant(0)
+        return y
+
+    for kw in ({}, dict(bias=bias, residual=res, lora_u=u, lora_w=lw)):
+        a, b, c = run(4, **kw), run(4, **kw), run(5, **kw)
+        assert torch.equal(a, b)                                   # deterministic: partial sums are added in pair order
+        assert rel_fro(a, c) <= 1e-3
+    assert quant_cuda.device_status() == 0
