@@ -1,9 +1,10 @@
 // The fused dequant-GEMM forward with the dequantised weights in TENSOR MEMORY (tcgen05.mma with its A operand
 // in TMEM), for layers whose groups are sequential by the caller's word.  Included by q4_gemm.cu after q4_gemm2.cuh.
 //
-// The pair kernel of q4_gemm2.cuh keeps both operands in shared memory: per 64 contraction elements an SM takes
-// 16 KiB of TMA writes, 16 KiB of dequant stores and 32 KiB of tensor-core reads through a 128 B/clk shared memory,
-// and with 256-row tiles that traffic, not the MMAs, sets the stage time.  Here the product is transposed,
+// The pair kernel of q4_gemm2.cuh keeps both operands in shared memory: a dequant task there is eight swizzled
+// 16-byte stores behind scale and zero-term vectors of eight columns, a proxy fence and a barrier, and per 64
+// contraction elements an SM takes 16 KiB of dequant stores on top of 16 KiB of TMA writes and 32 KiB of tensor-core
+// reads.  Here the product is transposed,
 // y^T = W^T x^T: the weights are the A operand (M side: 256 output columns per pair, 128 per CTA = one TMEM lane
 // each), the activations the B operand (N side: 256 rows of x per tile, 128 per CTA, K-major by TMA exactly as
 // before).  A dequant thread owns one output column: the eight packed words of its column and a stage are eight
@@ -17,7 +18,7 @@
 // lane in the even CTA issues the MMAs; warps 4-15 dequantise (warp & 3 = its TMEM lane quarter; three groups of
 // four warps take every third stage use: a task is a chain of loads, arithmetic, the wait for the slot, the TMEM
 // store and its completion, about 1500 cycles where the MMAs of a stage take 540, so three tasks have to be in
-// flight); warps 16-19 epilogue.  Whole tiles per pair, round after round.
+// flight); warps 16-19 epilogue.  Whole tiles per pair round after round, or (SPLIT) equal runs of tiles x stages.
 // The accumulator's lanes are output columns, so a thread of the epilogue holds 32 rows of one column: a warp
 // first moves its 32 columns x 256 rows into shared memory as fp16 (and hands the accumulator back: the MMAs of the
 // pair's next item start while the stores run), then stores rows of 64 bytes, four lanes each.
@@ -27,6 +28,7 @@
 namespace q4 {
 
 constexpr int G3_STAGES = 8;                  // operand stages in TMEM = activation stages in shared memory
+static_assert(G3_STAGES == 8, "a stage use u lies in slot u & 7, use u >> 3");
 constexpr int G3_X_BYTES = 128 * GM_TILE_C * 2;           // 16 KiB: this CTA's 128 activation rows of a stage
 constexpr int G3_TMEM_A0 = 256;               // first TMEM column of the operand stages
 constexpr int G3_BAR_BYTES = 512;
