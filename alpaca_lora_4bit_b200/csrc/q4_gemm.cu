@@ -525,6 +525,17 @@ static int gemm_launch(bool transpose, const void* act, const int32_t* qweight, 
         const long long whole = (long long)((tiles3 + P - 1) / P) * T, dealt = (total3 + P - 1) / P + 30;
         stream3 = dealt < whole;
       }
+      // Few tiles and a long contraction (short prompts: one row tile, 16 column tiles of a 4096-wide layer on 74
+      // pairs): every tile is cut between a whole number of pairs.  The exchange costs about 12 + 7 nb stages (nb =
+      // blocks of 32 rows a tile really has: the partial sums of the other rows are neither written nor read), so it
+      // pays for short prompts and long contractions (64 rows at 4096 x 4096: 25.7 -> 18.4 us; 32 rows at 11008 x 4096:
+      // 58.2 -> 24.8 us) and not at 256 rows of 4096 x 4096 (27.3 -> 32.8 us).
+      if (!stream3 && ws && workspace_bytes >= ws_off + (size_t)P * Q4_GEMM_WS_SLICE_BYTES && tiles3 * 2 <= P && T >= 16) {
+        int per_tile = P / tiles3;
+        if (per_tile > T / 8) per_tile = T / 8;
+        const int nb = ((M < 256 ? M : 256) + 31) / 32;
+        if (per_tile >= 2 && (long long)T * (per_tile - 1) / per_tile > 12 + 7 * nb) { stream3 = true; pairs3 = tiles3 * per_tile; }
+      }
       p.ws_partials = (float*)(ws + ws_off);
       p.ws_counters = (unsigned*)ws;
       if (stream3) q4_gemm3_kernel<true><<<dim3(2 * pairs3), dim3(G3_THREADS), gemm3_smem_bytes(), st>>>(amap, umap, p);

@@ -530,13 +530,14 @@ def test_tensor_memory_kernel_is_chosen_and_refused_where_it_should_be():
         quant_cuda.gemm_set_variant(0)
 
 
-@pytest.mark.parametrize("M,K,N", [(1024, 4096, 11008), (700, 2048, 20480)])
+@pytest.mark.parametrize("M,K,N", [(1024, 4096, 11008), (700, 2048, 20480), (64, 4096, 1024), (40, 11008, 4096), (300, 8192, 2048)])
 def test_tensor_memory_kernel_with_runs_dealt_across_pairs(M, K, N):
     """More 256 x 256 tiles than CTA pairs and a last round that would leave most pairs idle: the weights-in-TMEM
     kernel deals tiles x stages as one sequence (stream-K), shared tiles meet in the workspace.  Same product as the
     pair kernel (which adds K in another order: tolerance), plain and with bias, skip-path add and a rank-16 term
     (the low-rank stage goes with the run that reaches the end of a tile); twice in a row (the counters are left
-    zero); the workspace status stays clean."""
+    zero); the workspace status stays clean.  The short-prompt cases have few tiles and a long contraction: every
+    tile is cut between several whole pairs."""
     layer = synth.make_layer(K, N, 128, False, seed=K + N).to(DEV)
     x = synth.make_acts(M, K, seed=M).to(DEV)
     gen = torch.Generator(device=DEV).manual_seed(M)
